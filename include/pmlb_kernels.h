@@ -1,0 +1,263 @@
+/*
+ * pmlb_kernels.h -- C ABI of the sm_100a kernel library behind the PlaidML `cuda` device.
+ *
+ * This is the layer the reference fills with libxsmm: JIT-compiled x86 code calls
+ * `plaidml_rt_xsmm_*_dispatch_f32` once per tile shape and `*_invoke_f32` per tile
+ * (pmlc/rt/xsmm.cc:17-56, 235-342, 457-856).  Here a *dispatch* builds a plan for a whole
+ * contraction (tile shape, instruction descriptor, scratch size) and an *invoke* enqueues
+ * the kernels of that plan on a CUDA stream.  Plain pointers and sizes only; every
+ * pointer passed to an invoke is a device pointer unless stated otherwise.
+ *
+ * Conventions
+ *   - every function returns a pmlb_status; pmlb_last_error() gives the message of the
+ *     last failure on the calling thread;
+ *   - no entry point falls back to the CPU: without a usable sm_100 device the dispatch
+ *     functions fail with PMLB_ERR_UNSUPPORTED;
+ *   - dispatch functions may allocate device scratch (released by pmlb_plan_free);
+ *     invoke functions never allocate and never synchronise.
+ */
+#ifndef PMLB_KERNELS_H_
+#define PMLB_KERNELS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  PMLB_OK = 0,
+  PMLB_ERR_INVALID = 1,     /* bad argument */
+  PMLB_ERR_CUDA = 2,        /* a CUDA call failed */
+  PMLB_ERR_UNSUPPORTED = 3, /* shape / type outside what the kernel covers */
+  PMLB_ERR_TIMEOUT = 4      /* a device-side wait gave up; see pmlb_plan_check */
+} pmlb_status;
+
+/* Element types.  Values equal plaidml_datatype (plaidml/core/ffi.h:139-156) so that a
+ * TensorShape's dtype can be passed through unchanged; BFLOAT16 is appended. */
+typedef enum {
+  PMLB_BOOL = 4,
+  PMLB_I8 = 5,
+  PMLB_U8 = 6,
+  PMLB_I16 = 7,
+  PMLB_U16 = 8,
+  PMLB_I32 = 9,
+  PMLB_U32 = 10,
+  PMLB_I64 = 11,
+  PMLB_U64 = 12,
+  PMLB_F16 = 13,
+  PMLB_F32 = 14,
+  PMLB_F64 = 15,
+  PMLB_BF16 = 16
+} pmlb_dtype;
+
+/* Aggregations and combinations of a Tile contraction; values equal plaidml_agg_op /
+ * plaidml_combo_op (plaidml/edsl/ffi.h:218-233). */
+typedef enum { PMLB_AGG_NONE = 0, PMLB_AGG_SUM, PMLB_AGG_MAX, PMLB_AGG_MIN, PMLB_AGG_PROD, PMLB_AGG_ASSIGN } pmlb_agg;
+typedef enum { PMLB_COMBO_NONE = 0, PMLB_COMBO_MUL, PMLB_COMBO_ADD, PMLB_COMBO_EQ, PMLB_COMBO_COND } pmlb_combo;
+
+/* Epilogue steps fused into the GEMM / convolution kernels; the role of the reference's
+ * `_bias`, `_relu` and `_relu_beta1` microkernel variants (pmlc/rt/xsmm.cc:58-233). */
+enum {
+  PMLB_EPI_BIAS = 1,     /* out[.., j] += bias[j]; bias is f32 (float paths) or i32 (int8 path) */
+  PMLB_EPI_RESIDUAL = 2, /* out += residual (same shape and element type as out) */
+  PMLB_EPI_RELU = 4,     /* x < 0 ? 0 : x, as pmlc/conversion/pxa_to_affine/pxa_to_affine.cc:312-332 */
+  PMLB_EPI_ROWMAX = 8    /* additionally reduce each output row with max into `rowmax` (f32) */
+};
+
+const char* pmlb_last_error(void);
+const char* pmlb_version(void);
+
+/* Number of CUDA devices with compute capability 10.x; 0 when there is none. */
+int pmlb_device_count(void);
+
+typedef struct pmlb_plan pmlb_plan;
+
+void pmlb_plan_free(pmlb_plan* plan);
+
+/* Device scratch the plan holds, in bytes (0 when its kernels need none). */
+size_t pmlb_plan_scratch_bytes(const pmlb_plan* plan);
+
+/* Synchronises `stream` and reports whether any kernel of the plan recorded a device-side
+ * error since the last check (a bounded wait that expired): PMLB_OK or PMLB_ERR_TIMEOUT. */
+pmlb_status pmlb_plan_check(pmlb_plan* plan, void* stream);
+
+/* Name of the kernel family a plan resolved to ("tc_gemm", "tc_conv", "row_reduce", ...). */
+const char* pmlb_plan_kind(const pmlb_plan* plan);
+
+/* ---------------------------------------------------------------- GEMM
+ * C[b, i, j] = sum_k A[b, i, k] * B[b, k, j]   (b_is_nk == 0, B stored [k][n])
+ * C[b, i, j] = sum_k A[b, i, k] * B[b, j, k]   (b_is_nk == 1, B stored [n][k])
+ * Replaces plaidml_rt_xsmm_gemm/brgemm_{dispatch,invoke}_f32 (pmlc/rt/xsmm.cc:17-56,235-287)
+ * and, for int8 / 16-bit inputs, the plain LLVM loops the x86 target emits for
+ * non-f32 contractions (pmlc/target/x86/pipeline.cc:185-202).
+ *
+ * in_dtype / out_dtype:  F32 -> F32 (three TF32 products per term, f32 accumulate)
+ *                        BF16 or F16 -> F32, BF16 or F16 (f32 accumulate)
+ *                        I8 -> I32, or I8 (two's-complement wrap of the 32-bit sum)
+ * A batch stride of 0 shares one matrix between all batch entries.
+ */
+typedef struct {
+  int32_t in_dtype;
+  int32_t out_dtype;
+  int32_t m, n, k, batch;
+  int64_t lda, ldb, ldc;             /* elements between rows */
+  int64_t stride_a, stride_b, stride_c; /* elements between batch entries */
+  int32_t b_is_nk;
+  int32_t epilogue;                  /* PMLB_EPI_* */
+  int64_t ldr, stride_r;             /* residual row / batch strides (elements) */
+  int32_t tile_n;                    /* 0 = choose; 64, 128 or 256 forces the tile width */
+  int32_t flags;                     /* PMLB_GEMM_* */
+} pmlb_gemm_desc;
+
+/* With b_is_nk == 0 the 16-bit and 8-bit kernels read B tiles straight from the [k][n]
+ * matrix (an "MN-major" tensor-core operand).  This flag makes the plan transpose B into
+ * [n][k] scratch first and run the K-major kernel instead. */
+#define PMLB_GEMM_TRANSPOSE_B 1
+
+pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* desc, pmlb_plan** plan);
+
+/* `rowmax` (f32[batch * m]) is written only with PMLB_EPI_ROWMAX; `c` may then be NULL to
+ * skip materialising the product. */
+pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream, const void* a, const void* b, void* c,
+                             const void* bias, const void* residual, float* rowmax);
+
+/* ---------------------------------------------------------------- convolution
+ * NHWC activation [n, h, w, c] (*) filter [r, s, c, k] -> [n, p, q, k]:
+ *   O[n, y, x, ko] = sum_{fr, fs, ci} I[n, stride_h*y + dil_h*fr - pad_h, stride_w*x + dil_w*fs - pad_w, ci]
+ *                                      * F[fr, fs, ci, ko]
+ * with out-of-range taps skipped, i.e. the contraction op::convolution builds for
+ * NXC / XCK layouts (plaidml/op/lib/ops.cc:1351-1357,1405-1446).  Replaces
+ * plaidml_rt_xsmm_brgemm_offs_* (pmlc/rt/xsmm.cc:289-342,650-856).
+ * in_dtype BF16 or F16; out_dtype F32, BF16 or F16; f32 accumulate.
+ */
+typedef struct {
+  int32_t in_dtype;
+  int32_t out_dtype;
+  int32_t n, h, w, c;
+  int32_t r, s, k;
+  int32_t p, q;
+  int32_t stride_h, stride_w;
+  int32_t pad_h, pad_w;
+  int32_t dil_h, dil_w;
+  int32_t epilogue;
+  int32_t tile_n;
+} pmlb_conv_desc;
+
+pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* desc, pmlb_plan** plan);
+
+/* One-time re-layout of the filter from [r][s][c][k] (filter_dtype F32, BF16 or F16) into the
+ * plan's K-major scratch copy; the analogue of the reference's `init` closure that packs
+ * constants once per executable (pmlc/rt/jit_executable.cc:404-420). */
+pmlb_status pmlb_conv_set_filter(pmlb_plan* plan, void* stream, const void* filter_rsck,
+                                 int32_t filter_dtype);
+
+pmlb_status pmlb_conv_invoke(pmlb_plan* plan, void* stream, const void* input, void* output,
+                             const void* bias, const void* residual);
+
+/* ---------------------------------------------------------------- reductions
+ * out[o, i] = agg_{r} in[o, r, i] for agg in {SUM, MAX, MIN}; in is dense
+ * [outer][reduce][inner].  inner == 1 is the row reduction (row max of cfg "Q.K^T then
+ * max"), inner > 1 the strided one (global average pooling sums).  These are the
+ * contractions the x86 target leaves as plain loops (pmlc/dialect/pxa/transforms/
+ * stencil_gemm.cc:60-75 matches add-of-mul only).  out_dtype == dtype, or F32 for a
+ * BF16/F16 input summed in f32.  `scale` multiplies the result (1/count for a mean).
+ */
+typedef struct {
+  int32_t agg;
+  int32_t dtype;
+  int32_t out_dtype;
+  int32_t reserved;
+  int64_t outer, reduce, inner;
+  double scale;
+} pmlb_reduce_desc;
+
+pmlb_status pmlb_reduce_dispatch(const pmlb_reduce_desc* desc, pmlb_plan** plan);
+pmlb_status pmlb_reduce_invoke(pmlb_plan* plan, void* stream, const void* in, void* out);
+
+/* NHWC window pooling: out[n, y, x, c] = agg over the r x s window, out-of-range taps
+ * skipped (plaidml/op/lib/ops.cc:2562-2703).  agg MAX, MIN or SUM; with `average` the sum is
+ * divided by the number of in-range taps (include_padding == 0) or by r*s. */
+typedef struct {
+  int32_t agg;
+  int32_t dtype;
+  int32_t n, h, w, c;
+  int32_t r, s;
+  int32_t p, q;
+  int32_t stride_h, stride_w;
+  int32_t pad_h, pad_w;
+  int32_t average;
+  int32_t include_padding;
+} pmlb_pool_desc;
+
+pmlb_status pmlb_pool_dispatch(const pmlb_pool_desc* desc, pmlb_plan** plan);
+pmlb_status pmlb_pool_invoke(pmlb_plan* plan, void* stream, const void* in, void* out);
+
+/* ---------------------------------------------------------------- general contraction
+ * Any bounded Tile contraction (pmlc/dialect/tile/ir/ops.td:20-83 after
+ * tile-compute-bounds, pmlc/dialect/tile/transforms/contraction.cc:657-681):
+ *   for x in box:  if every access is in range, every constraint holds and every index
+ *                  expression is integral:  O[s(x)] = agg(O[s(x)], combo(T1[a1(x)], ..))
+ * Index expressions are affine with rational coefficients: coordinate of tensor dim d is
+ * (off[d] + sum_i coef[d][i] * x_i) / den[d].  Slow but complete; the planner only sends
+ * here what no specialised kernel covers.
+ */
+#define PMLB_MAX_IDX 10
+#define PMLB_MAX_RANK 8
+#define PMLB_MAX_CONS 8
+
+typedef struct {
+  int32_t dtype;
+  int32_t rank;
+  int64_t sizes[PMLB_MAX_RANK];
+  int64_t strides[PMLB_MAX_RANK]; /* elements */
+  int32_t coef[PMLB_MAX_RANK][PMLB_MAX_IDX];
+  int64_t off[PMLB_MAX_RANK];
+  int32_t den[PMLB_MAX_RANK];     /* >= 1 */
+} pmlb_access;
+
+typedef struct {
+  int32_t agg;
+  int32_t combo;
+  int32_t n_idx;
+  int32_t n_src;                  /* 1..3 */
+  int64_t range[PMLB_MAX_IDX];    /* x_i in [0, range[i]) */
+  pmlb_access out;
+  pmlb_access src[3];
+  int32_t n_cons;
+  int32_t has_init;               /* 1: `init` holds a tensor broadcast-compatible with out */
+  int32_t cons_coef[PMLB_MAX_CONS][PMLB_MAX_IDX];
+  int64_t cons_off[PMLB_MAX_CONS];
+  int64_t cons_range[PMLB_MAX_CONS]; /* 0 <= off + coef . x < range */
+  pmlb_access init;               /* indexed by the output coordinates (coef unused):
+                                     strides 0 on broadcast dims */
+} pmlb_contract_desc;
+
+pmlb_status pmlb_contract_dispatch(const pmlb_contract_desc* desc, pmlb_plan** plan);
+pmlb_status pmlb_contract_invoke(pmlb_plan* plan, void* stream, const void* src0, const void* src1,
+                                 const void* src2, const void* init, void* out);
+
+/* ---------------------------------------------------------------- element-wise
+ * out = op(in0, in1, in2) with numpy-style broadcasting (pmlc/ast/eval.cc:46-105); the
+ * operations are the tile dialect's eltwise set (pmlc/dialect/tile/ir/eltwise.td:121-170),
+ * named by the same mnemonics ("add", "cmp_lt", "select", "cast", ...).
+ */
+typedef struct {
+  char op[24];
+  int32_t n_in;                        /* 1..3 */
+  int32_t rank;
+  int32_t out_dtype;
+  int32_t in_dtype[3];
+  int64_t sizes[PMLB_MAX_RANK];        /* output shape (dense row-major) */
+  int64_t in_strides[3][PMLB_MAX_RANK];/* elements; 0 on broadcast dims */
+} pmlb_eltwise_desc;
+
+pmlb_status pmlb_eltwise_dispatch(const pmlb_eltwise_desc* desc, pmlb_plan** plan);
+pmlb_status pmlb_eltwise_invoke(pmlb_plan* plan, void* stream, const void* in0, const void* in1,
+                                const void* in2, void* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PMLB_KERNELS_H_ */

@@ -1,0 +1,440 @@
+// General Tile contraction and element-wise kernels: complete but unspecialised.
+//
+// contraction  one thread per output element.  When every output coordinate is a single
+//              index variable (the usual case) those variables are read off the element's
+//              position and the thread loops over the remaining (reduction) variables;
+//              otherwise the thread loops over the whole index box and keeps the points
+//              that land on its element.  A point contributes only if every tensor access
+//              is in range, every constraint holds and every rational index is integral.
+// eltwise      one thread per output element, operands read through broadcast strides.
+//
+// Arithmetic happens in the contraction's element type: integers wrap (computed in 64
+// bits and truncated on store), f16 / bf16 round after every operation, max / min are a
+// compare-and-select with an ordered compare.
+#include "generic.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math.h>
+
+namespace pmlb {
+
+namespace {
+
+// ------------------------------------------------------------------ typed access
+
+template <class T>
+__device__ __forceinline__ T load_as(const void* base, int dtype, long long i) {
+  switch (dtype) {
+    case PMLB_BOOL:
+    case PMLB_U8: return static_cast<T>(static_cast<const uint8_t*>(base)[i]);
+    case PMLB_I8: return static_cast<T>(static_cast<const int8_t*>(base)[i]);
+    case PMLB_I16: return static_cast<T>(static_cast<const int16_t*>(base)[i]);
+    case PMLB_U16: return static_cast<T>(static_cast<const uint16_t*>(base)[i]);
+    case PMLB_I32: return static_cast<T>(static_cast<const int32_t*>(base)[i]);
+    case PMLB_U32: return static_cast<T>(static_cast<const uint32_t*>(base)[i]);
+    case PMLB_I64: return static_cast<T>(static_cast<const long long*>(base)[i]);
+    case PMLB_U64: return static_cast<T>(static_cast<const unsigned long long*>(base)[i]);
+    case PMLB_F16: return static_cast<T>(__half2float(static_cast<const __half*>(base)[i]));
+    case PMLB_BF16:
+      return static_cast<T>(__bfloat162float(static_cast<const __nv_bfloat16*>(base)[i]));
+    case PMLB_F32: return static_cast<T>(static_cast<const float*>(base)[i]);
+    case PMLB_F64: return static_cast<T>(static_cast<const double*>(base)[i]);
+    default: return T(0);
+  }
+}
+
+// Float -> integer conversions saturate in CUDA; the reference's fptosi is undefined out
+// of range, so any choice is conforming.
+template <class T>
+__device__ __forceinline__ void store_as(void* base, int dtype, long long i, T v) {
+  switch (dtype) {
+    case PMLB_BOOL: static_cast<uint8_t*>(base)[i] = (v != T(0)) ? 1 : 0; break;
+    case PMLB_U8: static_cast<uint8_t*>(base)[i] = static_cast<uint8_t>(static_cast<long long>(v)); break;
+    case PMLB_I8: static_cast<int8_t*>(base)[i] = static_cast<int8_t>(static_cast<long long>(v)); break;
+    case PMLB_I16: static_cast<int16_t*>(base)[i] = static_cast<int16_t>(static_cast<long long>(v)); break;
+    case PMLB_U16: static_cast<uint16_t*>(base)[i] = static_cast<uint16_t>(static_cast<long long>(v)); break;
+    case PMLB_I32: static_cast<int32_t*>(base)[i] = static_cast<int32_t>(static_cast<long long>(v)); break;
+    case PMLB_U32: static_cast<uint32_t*>(base)[i] = static_cast<uint32_t>(static_cast<long long>(v)); break;
+    case PMLB_I64: static_cast<long long*>(base)[i] = static_cast<long long>(v); break;
+    case PMLB_U64: static_cast<unsigned long long*>(base)[i] = static_cast<unsigned long long>(v); break;
+    case PMLB_F16: static_cast<__half*>(base)[i] = __float2half_rn(static_cast<float>(v)); break;
+    case PMLB_BF16: static_cast<__nv_bfloat16*>(base)[i] = __float2bfloat16_rn(static_cast<float>(v)); break;
+    case PMLB_F32: static_cast<float*>(base)[i] = static_cast<float>(v); break;
+    case PMLB_F64: static_cast<double*>(base)[i] = static_cast<double>(v); break;
+    default: break;
+  }
+}
+
+__device__ __forceinline__ bool dtype_is_float(int dt) {
+  return dt == PMLB_F16 || dt == PMLB_BF16 || dt == PMLB_F32 || dt == PMLB_F64;
+}
+
+// Rounds / wraps a value of the compute class to what the element type can hold.
+template <class T>
+__device__ __forceinline__ T narrow(T v, int dtype) {
+  if constexpr (sizeof(T) == 4) {  // float class
+    if (dtype == PMLB_F16) return __half2float(__float2half_rn(v));
+    if (dtype == PMLB_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+    return v;
+  } else if constexpr (static_cast<T>(0.5) != T(0)) {  // double
+    return v;
+  } else {
+    switch (dtype) {
+      case PMLB_BOOL: return (v != 0) ? T(1) : T(0);
+      case PMLB_I8: return static_cast<T>(static_cast<int8_t>(v));
+      case PMLB_U8: return static_cast<T>(static_cast<uint8_t>(v));
+      case PMLB_I16: return static_cast<T>(static_cast<int16_t>(v));
+      case PMLB_U16: return static_cast<T>(static_cast<uint16_t>(v));
+      case PMLB_I32: return static_cast<T>(static_cast<int32_t>(v));
+      case PMLB_U32: return static_cast<T>(static_cast<uint32_t>(v));
+      default: return v;
+    }
+  }
+}
+
+template <class T>
+__device__ __forceinline__ T agg_identity(int agg, int dtype) {
+  constexpr bool is_float = static_cast<T>(0.5) != T(0);
+  if (agg == PMLB_AGG_PROD) return T(1);
+  if (agg == PMLB_AGG_MAX) {
+    if constexpr (is_float) return static_cast<T>(-INFINITY);
+    switch (dtype) {
+      case PMLB_I8: return static_cast<T>(-128);
+      case PMLB_I16: return static_cast<T>(-32768);
+      case PMLB_I32: return static_cast<T>(-2147483647 - 1);
+      case PMLB_I64: return static_cast<T>(-9223372036854775807LL - 1);
+      default: return T(0);
+    }
+  }
+  if (agg == PMLB_AGG_MIN) {
+    if constexpr (is_float) return static_cast<T>(INFINITY);
+    switch (dtype) {
+      case PMLB_BOOL: return T(1);
+      case PMLB_I8: return static_cast<T>(127);
+      case PMLB_U8: return static_cast<T>(255);
+      case PMLB_I16: return static_cast<T>(32767);
+      case PMLB_U16: return static_cast<T>(65535);
+      case PMLB_I32: return static_cast<T>(2147483647);
+      case PMLB_U32: return static_cast<T>(4294967295LL);
+      case PMLB_I64: return static_cast<T>(9223372036854775807LL);
+      default: return static_cast<T>(~0ULL);
+    }
+  }
+  return T(0);
+}
+
+__device__ __forceinline__ long long floor_div_exact(long long num, int den, bool* integral) {
+  if (den == 1) return num;
+  const long long q = num / den;
+  if (q * den != num) *integral = false;
+  return q;
+}
+
+// ------------------------------------------------------------------ contraction
+
+template <class T>
+__global__ void __launch_bounds__(256) contract_kernel(const __grid_constant__ GenericParams p) {
+  const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= p.out_elems) return;
+
+  long long oc[PMLB_MAX_RANK];
+  long long rem = e;
+  long long out_off = 0, init_off = 0;
+  for (int d = p.out.rank - 1; d >= 0; --d) {
+    oc[d] = rem % p.out.sizes[d];
+    rem /= p.out.sizes[d];
+    out_off += oc[d] * p.out.strides[d];
+    init_off += oc[d] * p.init.strides[d];
+  }
+
+  long long x[PMLB_MAX_IDX];
+  for (int i = 0; i < PMLB_MAX_IDX; ++i) x[i] = 0;
+  bool alive = true;
+  if (p.direct) {
+    for (int d = 0; d < p.out.rank; ++d) {
+      const int v = p.out_var[d];
+      const long long xv = oc[d] - p.out.off[d];
+      if (xv < 0 || xv >= p.range[v]) alive = false;
+      x[v] = xv;
+    }
+  }
+  for (int j = 0; j < p.n_loop; ++j) {
+    if (p.range[p.loop_var[j]] <= 0) alive = false;
+  }
+
+  T acc = p.has_init ? narrow<T>(load_as<T>(p.initp, p.init.dtype, init_off), p.out.dtype)
+                     : agg_identity<T>(p.agg, p.out.dtype);
+
+  while (alive) {
+    bool ok = true;
+    if (!p.direct) {
+      for (int d = 0; d < p.out.rank && ok; ++d) {
+        long long num = p.out.off[d];
+        for (int i = 0; i < p.n_idx; ++i) num += static_cast<long long>(p.out.coef[d][i]) * x[i];
+        const long long c = floor_div_exact(num, p.out.den[d], &ok);
+        if (c != oc[d]) ok = false;
+      }
+    }
+    for (int c = 0; c < p.n_cons && ok; ++c) {
+      long long v = p.cons_off[c];
+      for (int i = 0; i < p.n_idx; ++i) v += static_cast<long long>(p.cons_coef[c][i]) * x[i];
+      if (v < 0 || v >= p.cons_range[c]) ok = false;
+    }
+    long long soff[3] = {0, 0, 0};
+    for (int s = 0; s < p.n_src && ok; ++s) {
+      const GAccess& a = p.src[s];
+      for (int d = 0; d < a.rank; ++d) {
+        long long num = a.off[d];
+        for (int i = 0; i < p.n_idx; ++i) num += static_cast<long long>(a.coef[d][i]) * x[i];
+        const long long c = floor_div_exact(num, a.den[d], &ok);
+        if (c < 0 || c >= a.sizes[d]) ok = false;
+        soff[s] += c * a.strides[d];
+      }
+    }
+    if (ok) {
+      T v;
+      const int odt = p.out.dtype;
+      switch (p.combo) {
+        case PMLB_COMBO_MUL:
+          v = narrow<T>(load_as<T>(p.srcp[0], p.src[0].dtype, soff[0]) *
+                            load_as<T>(p.srcp[1], p.src[1].dtype, soff[1]),
+                        odt);
+          break;
+        case PMLB_COMBO_ADD:
+          v = narrow<T>(load_as<T>(p.srcp[0], p.src[0].dtype, soff[0]) +
+                            load_as<T>(p.srcp[1], p.src[1].dtype, soff[1]),
+                        odt);
+          break;
+        case PMLB_COMBO_EQ: {
+          bool eq;
+          if (dtype_is_float(p.src[0].dtype) || dtype_is_float(p.src[1].dtype)) {
+            eq = load_as<double>(p.srcp[0], p.src[0].dtype, soff[0]) ==
+                 load_as<double>(p.srcp[1], p.src[1].dtype, soff[1]);
+          } else {
+            eq = load_as<long long>(p.srcp[0], p.src[0].dtype, soff[0]) ==
+                 load_as<long long>(p.srcp[1], p.src[1].dtype, soff[1]);
+          }
+          v = eq ? T(1) : T(0);
+          break;
+        }
+        case PMLB_COMBO_COND: {
+          bool eq;
+          if (dtype_is_float(p.src[0].dtype) || dtype_is_float(p.src[1].dtype)) {
+            eq = load_as<double>(p.srcp[0], p.src[0].dtype, soff[0]) ==
+                 load_as<double>(p.srcp[1], p.src[1].dtype, soff[1]);
+          } else {
+            eq = load_as<long long>(p.srcp[0], p.src[0].dtype, soff[0]) ==
+                 load_as<long long>(p.srcp[1], p.src[1].dtype, soff[1]);
+          }
+          v = eq ? narrow<T>(load_as<T>(p.srcp[2], p.src[2].dtype, soff[2]), odt) : T(0);
+          break;
+        }
+        default:
+          v = narrow<T>(load_as<T>(p.srcp[0], p.src[0].dtype, soff[0]), odt);
+          break;
+      }
+      switch (p.agg) {
+        case PMLB_AGG_SUM: acc = narrow<T>(acc + v, odt); break;
+        case PMLB_AGG_PROD: acc = narrow<T>(acc * v, odt); break;
+        case PMLB_AGG_MAX: acc = (acc > v) ? acc : v; break;
+        case PMLB_AGG_MIN: acc = (acc < v) ? acc : v; break;
+        default: acc = v; break;
+      }
+    }
+    int j = p.n_loop - 1;
+    while (j >= 0) {
+      const int v = p.loop_var[j];
+      if (++x[v] < p.range[v]) break;
+      x[v] = 0;
+      --j;
+    }
+    if (j < 0) break;
+  }
+  store_as<T>(p.outp, p.out.dtype, out_off, acc);
+}
+
+// ------------------------------------------------------------------ eltwise
+
+template <class T>
+__device__ __forceinline__ T ew_apply(int op, T a, T b, T c, bool a_nz) {
+  constexpr bool is_float = static_cast<T>(0.5) != T(0);
+  switch (op) {
+    case kEwIdent: return a;
+    case kEwAdd: return a + b;
+    case kEwSub: return a - b;
+    case kEwMul: return a * b;
+    case kEwDiv:
+      if constexpr (is_float) return a / b;
+      else return b == T(0) ? T(0) : a / b;
+    case kEwMod:
+      if constexpr (is_float) return static_cast<T>(fmod(static_cast<double>(a), static_cast<double>(b)));
+      else return b == T(0) ? T(0) : a % b;
+    case kEwMax: return (a > b) ? a : b;
+    case kEwMin: return (a < b) ? a : b;
+    case kEwNeg: return T(0) - a;
+    case kEwAbs: return a < T(0) ? T(0) - a : a;
+    case kEwRelu: return a < T(0) ? T(0) : a;
+    case kEwSign: return a > T(0) ? T(1) : (a < T(0) ? T(0) - T(1) : T(0));
+    case kEwSelect: return a_nz ? b : c;
+    case kEwCmpEq: return a == b ? T(1) : T(0);
+    case kEwCmpNe: return a != b ? T(1) : T(0);
+    case kEwCmpLt: return a < b ? T(1) : T(0);
+    case kEwCmpLe: return a <= b ? T(1) : T(0);
+    case kEwCmpGt: return a > b ? T(1) : T(0);
+    case kEwCmpGe: return a >= b ? T(1) : T(0);
+    case kEwLogicalAnd: return (a != T(0) && b != T(0)) ? T(1) : T(0);
+    case kEwLogicalOr: return (a != T(0) || b != T(0)) ? T(1) : T(0);
+    case kEwLogicalXor: return ((a != T(0)) != (b != T(0))) ? T(1) : T(0);
+    case kEwLogicalNot: return a == T(0) ? T(1) : T(0);
+    default: break;
+  }
+  if constexpr (is_float) {
+    const double x = static_cast<double>(a);
+    const double y = static_cast<double>(b);
+    switch (op) {
+      case kEwExp: return static_cast<T>(exp(x));
+      case kEwLog: return static_cast<T>(log(x));
+      case kEwSqrt: return static_cast<T>(sqrt(x));
+      case kEwRsqrt: return static_cast<T>(1.0 / sqrt(x));
+      case kEwTanh: return static_cast<T>(tanh(x));
+      case kEwSigmoid: return static_cast<T>(1.0 / (1.0 + exp(-x)));
+      case kEwSin: return static_cast<T>(sin(x));
+      case kEwCos: return static_cast<T>(cos(x));
+      case kEwTan: return static_cast<T>(tan(x));
+      case kEwSinh: return static_cast<T>(sinh(x));
+      case kEwCosh: return static_cast<T>(cosh(x));
+      case kEwAsin: return static_cast<T>(asin(x));
+      case kEwAcos: return static_cast<T>(acos(x));
+      case kEwAtan: return static_cast<T>(atan(x));
+      case kEwAsinh: return static_cast<T>(asinh(x));
+      case kEwAcosh: return static_cast<T>(acosh(x));
+      case kEwAtanh: return static_cast<T>(atanh(x));
+      case kEwErf: return static_cast<T>(erf(x));
+      case kEwPow: return static_cast<T>(pow(x, y));
+      case kEwFloor: return static_cast<T>(floor(x));
+      case kEwCeil: return static_cast<T>(ceil(x));
+      case kEwRound: return static_cast<T>(round(x));
+      default: return a;
+    }
+  } else {
+    switch (op) {
+      case kEwBitAnd: return a & b;
+      case kEwBitOr: return a | b;
+      case kEwBitXor: return a ^ b;
+      case kEwBitNot: return ~a;
+      case kEwBitShl: return (b < T(0) || b >= T(64)) ? T(0) : static_cast<T>(a << b);
+      case kEwBitShr: return (b < T(0) || b >= T(64)) ? T(0) : static_cast<T>(a >> b);
+      case kEwPow: {
+        T r = 1;
+        for (T i = 0; i < b; ++i) r *= a;
+        return r;
+      }
+      case kEwFloor:
+      case kEwCeil:
+      case kEwRound: return a;
+      default: return a;
+    }
+  }
+}
+
+// `T` is the class the operation is evaluated in (chosen from the operand types for
+// comparisons, from the result type otherwise); `arith_dtype` is the element type results
+// are rounded / wrapped to before the final conversion to the output type.
+template <class T>
+__global__ void __launch_bounds__(256) eltwise_kernel(const __grid_constant__ EltwiseParams p) {
+  const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= p.elems) return;
+  long long rem = e;
+  long long off[3] = {0, 0, 0};
+  for (int d = p.rank - 1; d >= 0; --d) {
+    const long long c = rem % p.sizes[d];
+    rem /= p.sizes[d];
+    off[0] += c * p.in_strides[0][d];
+    off[1] += c * p.in_strides[1][d];
+    off[2] += c * p.in_strides[2][d];
+  }
+  T a = T(0), b = T(0), c = T(0);
+  bool a_nz = false;
+  if (p.op == kEwSelect) {
+    // the condition keeps its own type; the branches are read in the result class
+    a_nz = load_as<double>(p.in[0], p.in_dtype[0], off[0]) != 0.0;
+    b = narrow<T>(load_as<T>(p.in[1], p.in_dtype[1], off[1]), p.arith_dtype);
+    c = narrow<T>(load_as<T>(p.in[2], p.in_dtype[2], off[2]), p.arith_dtype);
+  } else {
+    a = load_as<T>(p.in[0], p.in_dtype[0], off[0]);
+    if (p.n_in > 1) b = load_as<T>(p.in[1], p.in_dtype[1], off[1]);
+    if (p.n_in > 2) c = load_as<T>(p.in[2], p.in_dtype[2], off[2]);
+    if (p.narrow_inputs) {
+      a = narrow<T>(a, p.arith_dtype);
+      b = narrow<T>(b, p.arith_dtype);
+      c = narrow<T>(c, p.arith_dtype);
+    }
+  }
+  T r = ew_apply<T>(p.op, a, b, c, a_nz);
+  if (p.narrow_result) r = narrow<T>(r, p.arith_dtype);
+  store_as<T>(p.out, p.out_dtype, e, r);
+}
+
+template <class T>
+__global__ void __launch_bounds__(256) fill_kernel(void* out, int dtype, long long n, T value) {
+  const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e < n) store_as<T>(out, dtype, e, value);
+}
+
+unsigned grid_for(long long elems) { return static_cast<unsigned>((elems + 255) / 256); }
+
+}  // namespace
+
+int dtype_class(int dtype) {
+  switch (dtype) {
+    case PMLB_F16:
+    case PMLB_BF16:
+    case PMLB_F32: return kClassF32;
+    case PMLB_F64: return kClassF64;
+    case PMLB_BOOL:
+    case PMLB_U8:
+    case PMLB_U16:
+    case PMLB_U32:
+    case PMLB_U64: return kClassU64;
+    case PMLB_I8:
+    case PMLB_I16:
+    case PMLB_I32:
+    case PMLB_I64: return kClassI64;
+    default: return -1;
+  }
+}
+
+cudaError_t launch_contract(const GenericParams& p, cudaStream_t stream) {
+  if (p.out_elems <= 0) return cudaSuccess;
+  const unsigned grid = grid_for(p.out_elems);
+  switch (dtype_class(p.out.dtype)) {
+    case kClassF32: contract_kernel<float><<<grid, 256, 0, stream>>>(p); break;
+    case kClassF64: contract_kernel<double><<<grid, 256, 0, stream>>>(p); break;
+    case kClassI64: contract_kernel<long long><<<grid, 256, 0, stream>>>(p); break;
+    case kClassU64: contract_kernel<unsigned long long><<<grid, 256, 0, stream>>>(p); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_eltwise(const EltwiseParams& p, cudaStream_t stream) {
+  if (p.elems <= 0) return cudaSuccess;
+  const unsigned grid = grid_for(p.elems);
+  switch (p.compute_class) {
+    case kClassF32: eltwise_kernel<float><<<grid, 256, 0, stream>>>(p); break;
+    case kClassF64: eltwise_kernel<double><<<grid, 256, 0, stream>>>(p); break;
+    case kClassI64: eltwise_kernel<long long><<<grid, 256, 0, stream>>>(p); break;
+    case kClassU64: eltwise_kernel<unsigned long long><<<grid, 256, 0, stream>>>(p); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fill_f32(float* out, long long n, float value, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  fill_kernel<float><<<grid_for(n), 256, 0, stream>>>(out, PMLB_F32, n, value);
+  return cudaGetLastError();
+}
+
+}  // namespace pmlb

@@ -1,0 +1,729 @@
+// extern "C" surface of the kernel library: validates descriptors, owns plan scratch,
+// sequences the preparation kernels and the main kernel of each plan.
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "generic.h"
+#include "pmlb_kernels.h"
+#include "prepass.h"
+#include "reduce.h"
+#include "tc_gemm.cuh"
+#include "tc_launch.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+pmlb_status fail(pmlb_status code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+
+pmlb_status cuda_fail(cudaError_t e, const char* what) {
+  return fail(PMLB_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+int elem_bytes_of(int dtype) {
+  switch (dtype) {
+    case PMLB_BOOL:
+    case PMLB_I8:
+    case PMLB_U8: return 1;
+    case PMLB_I16:
+    case PMLB_U16:
+    case PMLB_F16:
+    case PMLB_BF16: return 2;
+    case PMLB_I32:
+    case PMLB_U32:
+    case PMLB_F32: return 4;
+    case PMLB_I64:
+    case PMLB_U64:
+    case PMLB_F64: return 8;
+    default: return 0;
+  }
+}
+
+long long round_up(long long v, long long m) { return (v + m - 1) / m * m; }
+
+bool have_sm100(std::string* why) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    *why = "no CUDA device is visible; this library has no CPU path";
+    return false;
+  }
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int major = 0;
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (major != 10) {
+    *why = "the current CUDA device is not compute capability 10.x (sm_100a kernels only)";
+    return false;
+  }
+  return true;
+}
+
+enum PlanKind { kPlanGemm, kPlanConv, kPlanReduce, kPlanPool, kPlanContract, kPlanEltwise };
+
+}  // namespace
+
+struct pmlb_plan {
+  PlanKind kind;
+  const char* kind_name = "";
+  int device = 0;
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  int* status = nullptr;  // device word shared by the plan's tensor-core launches
+
+  pmlb_gemm_desc gemm;
+  long long kpad = 0;       // fp32 path: padded K of the split copies
+  bool transpose_b = false; // 8/16-bit path: B goes through [n][k] scratch
+  bool split = false;
+
+  pmlb_conv_desc conv;
+  bool filter_set = false;
+
+  pmlb_reduce_desc reduce;
+  pmlb_pool_desc pool;
+  pmlb::GenericParams generic;
+  pmlb::EltwiseParams eltwise;
+};
+
+namespace {
+
+pmlb_status alloc_plan_memory(pmlb_plan* plan, size_t scratch_bytes, bool need_status) {
+  cudaGetDevice(&plan->device);
+  if (scratch_bytes > 0) {
+    cudaError_t e = cudaMalloc(&plan->scratch, scratch_bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(plan scratch)");
+    plan->scratch_bytes = scratch_bytes;
+  }
+  if (need_status) {
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&plan->status), sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(plan status)");
+    e = cudaMemset(plan->status, 0, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(plan status)");
+  }
+  return PMLB_OK;
+}
+
+int ew_opcode(const char* name) {
+  static const struct {
+    const char* name;
+    int code;
+  } table[] = {
+      {"ident", pmlb::kEwIdent}, {"assign", pmlb::kEwIdent}, {"cast", pmlb::kEwIdent},
+      {"add", pmlb::kEwAdd}, {"sub", pmlb::kEwSub}, {"mul", pmlb::kEwMul}, {"div", pmlb::kEwDiv},
+      {"mod", pmlb::kEwMod}, {"max", pmlb::kEwMax}, {"min", pmlb::kEwMin}, {"neg", pmlb::kEwNeg},
+      {"abs", pmlb::kEwAbs}, {"relu", pmlb::kEwRelu}, {"sign", pmlb::kEwSign},
+      {"select", pmlb::kEwSelect}, {"cmp_eq", pmlb::kEwCmpEq}, {"cmp_ne", pmlb::kEwCmpNe},
+      {"cmp_lt", pmlb::kEwCmpLt}, {"cmp_le", pmlb::kEwCmpLe}, {"cmp_gt", pmlb::kEwCmpGt},
+      {"cmp_ge", pmlb::kEwCmpGe}, {"logical_and", pmlb::kEwLogicalAnd},
+      {"logical_or", pmlb::kEwLogicalOr}, {"logical_xor", pmlb::kEwLogicalXor},
+      {"logical_not", pmlb::kEwLogicalNot}, {"exp", pmlb::kEwExp}, {"log", pmlb::kEwLog},
+      {"sqrt", pmlb::kEwSqrt}, {"rsqrt", pmlb::kEwRsqrt}, {"tanh", pmlb::kEwTanh},
+      {"sigmoid", pmlb::kEwSigmoid}, {"sin", pmlb::kEwSin}, {"cos", pmlb::kEwCos},
+      {"tan", pmlb::kEwTan}, {"sinh", pmlb::kEwSinh}, {"cosh", pmlb::kEwCosh},
+      {"asin", pmlb::kEwAsin}, {"acos", pmlb::kEwAcos}, {"atan", pmlb::kEwAtan},
+      {"asinh", pmlb::kEwAsinh}, {"acosh", pmlb::kEwAcosh}, {"atanh", pmlb::kEwAtanh},
+      {"erf", pmlb::kEwErf}, {"pow", pmlb::kEwPow}, {"floor", pmlb::kEwFloor},
+      {"ceil", pmlb::kEwCeil}, {"round", pmlb::kEwRound}, {"bit_and", pmlb::kEwBitAnd},
+      {"bit_or", pmlb::kEwBitOr}, {"bit_xor", pmlb::kEwBitXor}, {"bit_not", pmlb::kEwBitNot},
+      {"bit_shl", pmlb::kEwBitShl}, {"bit_shr", pmlb::kEwBitShr},
+  };
+  for (const auto& e : table) {
+    if (std::strcmp(e.name, name) == 0) return e.code;
+  }
+  return -1;
+}
+
+bool is_compare(int op) {
+  return (op >= pmlb::kEwCmpEq && op <= pmlb::kEwLogicalNot);
+}
+
+void copy_access(const pmlb_access& in, pmlb::GAccess* out, int n_idx) {
+  std::memset(out, 0, sizeof(*out));
+  out->dtype = in.dtype;
+  out->rank = in.rank;
+  for (int d = 0; d < in.rank; ++d) {
+    out->sizes[d] = in.sizes[d];
+    out->strides[d] = in.strides[d];
+    out->off[d] = in.off[d];
+    out->den[d] = in.den[d] >= 1 ? in.den[d] : 1;
+    for (int i = 0; i < n_idx; ++i) out->coef[d][i] = in.coef[d][i];
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* pmlb_last_error(void) { return g_last_error.c_str(); }
+
+const char* pmlb_version(void) { return "plaidml-b200 kernels 0.1 (sm_100a)"; }
+
+int pmlb_device_count(void) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  int good = 0;
+  for (int d = 0; d < count; ++d) {
+    int major = 0;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, d);
+    if (major == 10) ++good;
+  }
+  return good;
+}
+
+void pmlb_plan_free(pmlb_plan* plan) {
+  if (!plan) return;
+  if (plan->scratch) cudaFree(plan->scratch);
+  if (plan->status) cudaFree(plan->status);
+  delete plan;
+}
+
+size_t pmlb_plan_scratch_bytes(const pmlb_plan* plan) { return plan ? plan->scratch_bytes : 0; }
+
+const char* pmlb_plan_kind(const pmlb_plan* plan) { return plan ? plan->kind_name : ""; }
+
+pmlb_status pmlb_plan_check(pmlb_plan* plan, void* stream) {
+  if (!plan) return fail(PMLB_ERR_INVALID, "null plan");
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+  if (!plan->status) return PMLB_OK;
+  int code = 0;
+  e = cudaMemcpy(&code, plan->status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
+  if (code != 0) {
+    cudaMemset(plan->status, 0, sizeof(int));
+    return fail(PMLB_ERR_TIMEOUT,
+                "a device-side pipeline wait gave up (role code " + std::to_string(code) + ")");
+  }
+  return PMLB_OK;
+}
+
+// ------------------------------------------------------------------ GEMM
+
+pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* d, pmlb_plan** out) {
+  if (!d || !out) return fail(PMLB_ERR_INVALID, "null argument");
+  *out = nullptr;
+  std::string why;
+  if (!have_sm100(&why)) return fail(PMLB_ERR_UNSUPPORTED, why);
+  if (d->m <= 0 || d->n <= 0 || d->k <= 0 || d->batch <= 0) {
+    return fail(PMLB_ERR_INVALID, "gemm: m, n, k and batch must be positive");
+  }
+  const int in = d->in_dtype, od = d->out_dtype;
+  const bool f32 = in == PMLB_F32;
+  const bool h16 = in == PMLB_BF16 || in == PMLB_F16;
+  const bool i8 = in == PMLB_I8;
+  if (f32) {
+    if (od != PMLB_F32) return fail(PMLB_ERR_UNSUPPORTED, "gemm: f32 inputs produce f32");
+  } else if (h16) {
+    if (od != PMLB_F32 && od != PMLB_BF16 && od != PMLB_F16) {
+      return fail(PMLB_ERR_UNSUPPORTED, "gemm: 16-bit inputs produce f32, bf16 or f16");
+    }
+  } else if (i8) {
+    if (od != PMLB_I32 && od != PMLB_I8) {
+      return fail(PMLB_ERR_UNSUPPORTED, "gemm: int8 inputs produce int32 or int8");
+    }
+    if (d->epilogue & PMLB_EPI_ROWMAX) {
+      return fail(PMLB_ERR_UNSUPPORTED, "gemm: row max is a float epilogue");
+    }
+  } else {
+    return fail(PMLB_ERR_UNSUPPORTED, "gemm: input type must be f32, bf16, f16 or int8");
+  }
+  const int eb = elem_bytes_of(in);
+  const long long min_lda = d->k;
+  const long long min_ldb = d->b_is_nk ? d->k : d->n;
+  if (d->lda < min_lda || d->ldb < min_ldb || d->ldc < d->n) {
+    return fail(PMLB_ERR_INVALID, "gemm: leading dimension smaller than the row length");
+  }
+  pmlb_plan* plan = new (std::nothrow) pmlb_plan();
+  if (!plan) return fail(PMLB_ERR_INVALID, "out of host memory");
+  plan->kind = kPlanGemm;
+  plan->kind_name = "tc_gemm";
+  plan->gemm = *d;
+  size_t scratch = 0;
+  if (f32) {
+    plan->split = true;
+    plan->kpad = round_up(d->k, 4);
+    const long long a_mats = d->stride_a != 0 ? d->batch : 1;
+    const long long b_mats = d->stride_b != 0 ? d->batch : 1;
+    scratch = static_cast<size_t>(2 * 4 * plan->kpad * (a_mats * d->m + b_mats * d->n));
+  } else {
+    if ((d->lda * eb) % 16 != 0 || (d->stride_a * eb) % 16 != 0) {
+      delete plan;
+      return fail(PMLB_ERR_UNSUPPORTED, "gemm: A rows must start on 16-byte boundaries");
+    }
+    const bool b_aligned = (d->ldb * eb) % 16 == 0 && (d->stride_b * eb) % 16 == 0;
+    if (d->b_is_nk) {
+      if (!b_aligned) {
+        delete plan;
+        return fail(PMLB_ERR_UNSUPPORTED, "gemm: B rows must start on 16-byte boundaries");
+      }
+    } else if ((d->flags & PMLB_GEMM_TRANSPOSE_B) || !b_aligned) {
+      plan->transpose_b = true;
+      plan->kpad = round_up(d->k, 16 / eb);
+      const long long b_mats = d->stride_b != 0 ? d->batch : 1;
+      scratch = static_cast<size_t>(b_mats * d->n * plan->kpad * eb);
+    }
+  }
+  pmlb_status st = alloc_plan_memory(plan, scratch, true);
+  if (st != PMLB_OK) {
+    pmlb_plan_free(plan);
+    return st;
+  }
+  if (plan->transpose_b && plan->scratch) {
+    // the K tail of the transposed copy must read as zero
+    cudaMemset(plan->scratch, 0, plan->scratch_bytes);
+  }
+  *out = plan;
+  return PMLB_OK;
+}
+
+pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream_v, const void* a, const void* b, void* c,
+                             const void* bias, const void* residual, float* rowmax) {
+  if (!plan || plan->kind != kPlanGemm) return fail(PMLB_ERR_INVALID, "not a gemm plan");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const pmlb_gemm_desc& d = plan->gemm;
+  if (!a || !b) return fail(PMLB_ERR_INVALID, "gemm: null operand");
+  if ((d.epilogue & PMLB_EPI_BIAS) && !bias) return fail(PMLB_ERR_INVALID, "gemm: bias missing");
+  if ((d.epilogue & PMLB_EPI_RESIDUAL) && !residual) return fail(PMLB_ERR_INVALID, "gemm: residual missing");
+  if ((d.epilogue & PMLB_EPI_ROWMAX) && !rowmax) return fail(PMLB_ERR_INVALID, "gemm: rowmax missing");
+  if (!(d.epilogue & PMLB_EPI_ROWMAX) && !c) return fail(PMLB_ERR_INVALID, "gemm: null output");
+
+  pmlb::TcLaunch L;
+  L.elem_bytes = elem_bytes_of(d.in_dtype);
+  L.is_f16 = d.in_dtype == PMLB_F16;
+  L.m = d.m;
+  L.n = d.n;
+  L.k = d.k;
+  L.batch = d.batch;
+  L.out = c;
+  L.ldc = d.ldc;
+  L.out_batch_stride = d.stride_c;
+  L.out_dtype = d.out_dtype;
+  L.epi_flags = d.epilogue;
+  L.bias = bias;
+  L.residual = residual;
+  L.ldr = d.ldr;
+  L.res_batch_stride = d.stride_r;
+  L.rowmax = rowmax;
+  L.status = plan->status;
+  L.bn_override = d.tile_n;
+
+  if (plan->split) {
+    const long long kp = plan->kpad;
+    const long long a_mats = d.stride_a != 0 ? d.batch : 1;
+    const long long b_mats = d.stride_b != 0 ? d.batch : 1;
+    float* a_hi = static_cast<float*>(plan->scratch);
+    float* a_lo = a_hi + a_mats * d.m * kp;
+    float* b_hi = a_lo + a_mats * d.m * kp;
+    float* b_lo = b_hi + b_mats * d.n * kp;
+    cudaError_t e = pmlb::launch_split_tf32(static_cast<const float*>(a), d.lda, d.stride_a, a_hi,
+                                            a_lo, kp, static_cast<long long>(d.m) * kp, d.m, d.k,
+                                            static_cast<int>(a_mats), false, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "split(A)");
+    if (d.b_is_nk) {
+      e = pmlb::launch_split_tf32(static_cast<const float*>(b), d.ldb, d.stride_b, b_hi, b_lo, kp,
+                                  static_cast<long long>(d.n) * kp, d.n, d.k,
+                                  static_cast<int>(b_mats), false, stream);
+    } else {
+      e = pmlb::launch_split_tf32(static_cast<const float*>(b), d.ldb, d.stride_b, b_hi, b_lo, kp,
+                                  static_cast<long long>(d.n) * kp, d.k, d.n,
+                                  static_cast<int>(b_mats), true, stream);
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "split(B)");
+    L.nsplit = 2;
+    L.a0 = a_hi;
+    L.a1 = a_lo;
+    L.lda = kp;
+    L.a_batch_stride = d.stride_a != 0 ? static_cast<long long>(d.m) * kp : 0;
+    L.b0 = b_hi;
+    L.b1 = b_lo;
+    L.ldb = kp;
+    L.b_batch_stride = d.stride_b != 0 ? static_cast<long long>(d.n) * kp : 0;
+    L.b_mn = false;
+  } else {
+    L.a0 = a;
+    L.lda = d.lda;
+    L.a_batch_stride = d.stride_a;
+    if (plan->transpose_b) {
+      const long long kp = plan->kpad;
+      const long long b_mats = d.stride_b != 0 ? d.batch : 1;
+      cudaError_t e = pmlb::launch_transpose(b, d.ldb, d.stride_b, plan->scratch, kp,
+                                             static_cast<long long>(d.n) * kp, d.k, d.n,
+                                             static_cast<int>(b_mats), L.elem_bytes, stream);
+      if (e != cudaSuccess) return cuda_fail(e, "transpose(B)");
+      L.b0 = plan->scratch;
+      L.ldb = kp;
+      L.b_batch_stride = d.stride_b != 0 ? static_cast<long long>(d.n) * kp : 0;
+      L.b_mn = false;
+    } else {
+      L.b0 = b;
+      L.ldb = d.ldb;
+      L.b_batch_stride = d.stride_b;
+      L.b_mn = !d.b_is_nk;
+    }
+  }
+  if (d.epilogue & PMLB_EPI_ROWMAX) {
+    cudaError_t e = pmlb::launch_fill_f32(rowmax, static_cast<long long>(d.batch) * d.m,
+                                          -__builtin_inff(), stream);
+    if (e != cudaSuccess) return cuda_fail(e, "fill(rowmax)");
+  }
+  std::string err;
+  const int rc = pmlb::tc_launch(L, stream, &err);
+  if (rc != 0) return fail(static_cast<pmlb_status>(rc), "gemm: " + err);
+  return PMLB_OK;
+}
+
+// ------------------------------------------------------------------ convolution
+
+pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* d, pmlb_plan** out) {
+  if (!d || !out) return fail(PMLB_ERR_INVALID, "null argument");
+  *out = nullptr;
+  std::string why;
+  if (!have_sm100(&why)) return fail(PMLB_ERR_UNSUPPORTED, why);
+  if (d->in_dtype != PMLB_BF16 && d->in_dtype != PMLB_F16) {
+    return fail(PMLB_ERR_UNSUPPORTED, "conv: activations must be bf16 or f16");
+  }
+  if (d->out_dtype != PMLB_F32 && d->out_dtype != PMLB_BF16 && d->out_dtype != PMLB_F16) {
+    return fail(PMLB_ERR_UNSUPPORTED, "conv: output must be f32, bf16 or f16");
+  }
+  if (d->n <= 0 || d->h <= 0 || d->w <= 0 || d->c <= 0 || d->r <= 0 || d->s <= 0 || d->k <= 0 ||
+      d->p <= 0 || d->q <= 0 || d->stride_h <= 0 || d->stride_w <= 0 || d->dil_h <= 0 ||
+      d->dil_w <= 0 || d->pad_h < 0 || d->pad_w < 0) {
+    return fail(PMLB_ERR_INVALID, "conv: bad geometry");
+  }
+  if (d->c % 8 != 0) {
+    return fail(PMLB_ERR_UNSUPPORTED, "conv: channel count must be a multiple of 8");
+  }
+  // every output pixel's first tap must lie inside the im2col bounding box
+  const int upper_w = (d->q - 1) * d->stride_w + 1 - d->pad_w - d->w;
+  const int upper_h = (d->p - 1) * d->stride_h + 1 - d->pad_h - d->h;
+  if (d->pad_w > 128 || d->pad_h > 128 || upper_w < -128 || upper_w > 127 || upper_h < -128 ||
+      upper_h > 127 || d->stride_w > 8 || d->stride_h > 8) {
+    return fail(PMLB_ERR_UNSUPPORTED, "conv: geometry outside the im2col descriptor range");
+  }
+  if (d->epilogue & PMLB_EPI_ROWMAX) return fail(PMLB_ERR_UNSUPPORTED, "conv: no row max");
+  pmlb_plan* plan = new (std::nothrow) pmlb_plan();
+  if (!plan) return fail(PMLB_ERR_INVALID, "out of host memory");
+  plan->kind = kPlanConv;
+  plan->kind_name = "tc_conv";
+  plan->conv = *d;
+  const size_t scratch = static_cast<size_t>(d->k) * d->r * d->s * d->c * 2;
+  pmlb_status st = alloc_plan_memory(plan, scratch, true);
+  if (st != PMLB_OK) {
+    pmlb_plan_free(plan);
+    return st;
+  }
+  *out = plan;
+  return PMLB_OK;
+}
+
+pmlb_status pmlb_conv_set_filter(pmlb_plan* plan, void* stream, const void* filter, int32_t dtype) {
+  if (!plan || plan->kind != kPlanConv) return fail(PMLB_ERR_INVALID, "not a conv plan");
+  if (!filter) return fail(PMLB_ERR_INVALID, "conv: null filter");
+  if (dtype != PMLB_F32 && dtype != PMLB_BF16 && dtype != PMLB_F16) {
+    return fail(PMLB_ERR_UNSUPPORTED, "conv: filter must be f32, bf16 or f16");
+  }
+  const pmlb_conv_desc& d = plan->conv;
+  cudaError_t e = pmlb::launch_filter_relayout(filter, dtype, plan->scratch, d.in_dtype, d.r * d.s,
+                                               d.c, d.k, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "filter relayout");
+  plan->filter_set = true;
+  return PMLB_OK;
+}
+
+pmlb_status pmlb_conv_invoke(pmlb_plan* plan, void* stream, const void* input, void* output,
+                             const void* bias, const void* residual) {
+  if (!plan || plan->kind != kPlanConv) return fail(PMLB_ERR_INVALID, "not a conv plan");
+  if (!plan->filter_set) return fail(PMLB_ERR_INVALID, "conv: pmlb_conv_set_filter not called");
+  if (!input || !output) return fail(PMLB_ERR_INVALID, "conv: null tensor");
+  const pmlb_conv_desc& d = plan->conv;
+  if ((d.epilogue & PMLB_EPI_BIAS) && !bias) return fail(PMLB_ERR_INVALID, "conv: bias missing");
+  if ((d.epilogue & PMLB_EPI_RESIDUAL) && !residual) return fail(PMLB_ERR_INVALID, "conv: residual missing");
+  pmlb::ConvGeom g;
+  g.n = d.n; g.h = d.h; g.w = d.w; g.c = d.c;
+  g.r = d.r; g.s = d.s; g.p = d.p; g.q = d.q;
+  g.stride_h = d.stride_h; g.stride_w = d.stride_w;
+  g.pad_h = d.pad_h; g.pad_w = d.pad_w;
+  g.dil_h = d.dil_h; g.dil_w = d.dil_w;
+  pmlb::TcLaunch L;
+  L.elem_bytes = 2;
+  L.is_f16 = d.in_dtype == PMLB_F16;
+  L.m = d.n * d.p * d.q;
+  L.n = d.k;
+  L.k = d.r * d.s * d.c;
+  L.batch = 1;
+  L.a0 = input;
+  L.b0 = plan->scratch;
+  L.conv = &g;
+  L.out = output;
+  L.ldc = d.k;
+  L.out_dtype = d.out_dtype;
+  L.epi_flags = d.epilogue;
+  L.bias = bias;
+  L.residual = residual;
+  L.ldr = d.k;
+  L.status = plan->status;
+  L.bn_override = d.tile_n;
+  std::string err;
+  const int rc = pmlb::tc_launch(L, static_cast<cudaStream_t>(stream), &err);
+  if (rc != 0) return fail(static_cast<pmlb_status>(rc), "conv: " + err);
+  return PMLB_OK;
+}
+
+// ------------------------------------------------------------------ reductions
+
+pmlb_status pmlb_reduce_dispatch(const pmlb_reduce_desc* d, pmlb_plan** out) {
+  if (!d || !out) return fail(PMLB_ERR_INVALID, "null argument");
+  *out = nullptr;
+  std::string why;
+  if (!have_sm100(&why)) return fail(PMLB_ERR_UNSUPPORTED, why);
+  if (d->outer < 0 || d->reduce < 0 || d->inner <= 0) return fail(PMLB_ERR_INVALID, "reduce: bad extents");
+  if (!pmlb::reduce_supported(d->agg, d->dtype, d->out_dtype)) {
+    return fail(PMLB_ERR_UNSUPPORTED, "reduce: aggregation / type combination not covered");
+  }
+  pmlb_plan* plan = new (std::nothrow) pmlb_plan();
+  if (!plan) return fail(PMLB_ERR_INVALID, "out of host memory");
+  plan->kind = kPlanReduce;
+  plan->kind_name = d->inner == 1 ? "row_reduce" : "strided_reduce";
+  plan->reduce = *d;
+  cudaGetDevice(&plan->device);
+  *out = plan;
+  return PMLB_OK;
+}
+
+pmlb_status pmlb_reduce_invoke(pmlb_plan* plan, void* stream, const void* in, void* outp) {
+  if (!plan || plan->kind != kPlanReduce) return fail(PMLB_ERR_INVALID, "not a reduce plan");
+  if (!in || !outp) return fail(PMLB_ERR_INVALID, "reduce: null tensor");
+  const pmlb_reduce_desc& d = plan->reduce;
+  const float scale = d.scale == 0.0 ? 1.f : static_cast<float>(d.scale);
+  cudaError_t e = pmlb::launch_reduce(d.agg, d.dtype, d.out_dtype, in, outp, d.outer, d.reduce,
+                                      d.inner, scale, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "reduce launch");
+  return PMLB_OK;
+}
+
+pmlb_status pmlb_pool_dispatch(const pmlb_pool_desc* d, pmlb_plan** out) {
+  if (!d || !out) return fail(PMLB_ERR_INVALID, "null argument");
+  *out = nullptr;
+  std::string why;
+  if (!have_sm100(&why)) return fail(PMLB_ERR_UNSUPPORTED, why);
+  if (!pmlb::pool_supported(d->agg, d->dtype)) {
+    return fail(PMLB_ERR_UNSUPPORTED, "pool: aggregation / type combination not covered");
+  }
+  if (d->n <= 0 || d->h <= 0 || d->w <= 0 || d->c <= 0 || d->r <= 0 || d->s <= 0 || d->p <= 0 ||
+      d->q <= 0 || d->stride_h <= 0 || d->stride_w <= 0) {
+    return fail(PMLB_ERR_INVALID, "pool: bad geometry");
+  }
+  pmlb_plan* plan = new (std::nothrow) pmlb_plan();
+  if (!plan) return fail(PMLB_ERR_INVALID, "out of host memory");
+  plan->kind = kPlanPool;
+  plan->kind_name = "nhwc_pool";
+  plan->pool = *d;
+  cudaGetDevice(&plan->device);
+  *out = plan;
+  return PMLB_OK;
+}
+
+pmlb_status pmlb_pool_invoke(pmlb_plan* plan, void* stream, const void* in, void* outp) {
+  if (!plan || plan->kind != kPlanPool) return fail(PMLB_ERR_INVALID, "not a pool plan");
+  if (!in || !outp) return fail(PMLB_ERR_INVALID, "pool: null tensor");
+  const pmlb_pool_desc& d = plan->pool;
+  pmlb::PoolGeom g;
+  g.agg = d.agg;
+  g.n = d.n; g.h = d.h; g.w = d.w; g.c = d.c;
+  g.r = d.r; g.s = d.s; g.p = d.p; g.q = d.q;
+  g.stride_h = d.stride_h; g.stride_w = d.stride_w;
+  g.pad_h = d.pad_h; g.pad_w = d.pad_w;
+  g.average = d.average;
+  g.include_padding = d.include_padding;
+  cudaError_t e = pmlb::launch_pool(g, d.dtype, in, outp, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "pool launch");
+  return PMLB_OK;
+}
+
+// ------------------------------------------------------------------ general contraction
+
+pmlb_status pmlb_contract_dispatch(const pmlb_contract_desc* d, pmlb_plan** out) {
+  if (!d || !out) return fail(PMLB_ERR_INVALID, "null argument");
+  *out = nullptr;
+  std::string why;
+  if (!have_sm100(&why)) return fail(PMLB_ERR_UNSUPPORTED, why);
+  if (d->n_idx < 0 || d->n_idx > PMLB_MAX_IDX || d->n_src < 1 || d->n_src > 3 || d->n_cons < 0 ||
+      d->n_cons > PMLB_MAX_CONS || d->out.rank < 0 || d->out.rank > PMLB_MAX_RANK) {
+    return fail(PMLB_ERR_INVALID, "contract: descriptor counts out of range");
+  }
+  const int need_src = d->combo == PMLB_COMBO_NONE ? 1 : (d->combo == PMLB_COMBO_COND ? 3 : 2);
+  if (d->n_src != need_src) return fail(PMLB_ERR_INVALID, "contract: operand count does not match the combination");
+  if (pmlb::dtype_class(d->out.dtype) < 0) return fail(PMLB_ERR_INVALID, "contract: bad output type");
+  for (int s = 0; s < d->n_src; ++s) {
+    if (d->src[s].rank < 0 || d->src[s].rank > PMLB_MAX_RANK || pmlb::dtype_class(d->src[s].dtype) < 0) {
+      return fail(PMLB_ERR_INVALID, "contract: bad operand");
+    }
+  }
+  pmlb_plan* plan = new (std::nothrow) pmlb_plan();
+  if (!plan) return fail(PMLB_ERR_INVALID, "out of host memory");
+  plan->kind = kPlanContract;
+  plan->kind_name = "generic_contract";
+  pmlb::GenericParams& p = plan->generic;
+  std::memset(&p, 0, sizeof(p));
+  p.agg = d->agg;
+  p.combo = d->combo;
+  p.n_idx = d->n_idx;
+  p.n_src = d->n_src;
+  p.n_cons = d->n_cons;
+  p.has_init = d->has_init;
+  for (int i = 0; i < d->n_idx; ++i) p.range[i] = d->range[i];
+  copy_access(d->out, &p.out, d->n_idx);
+  for (int s = 0; s < d->n_src; ++s) copy_access(d->src[s], &p.src[s], d->n_idx);
+  if (d->has_init) {
+    copy_access(d->init, &p.init, 0);
+    p.init.rank = d->out.rank;
+  }
+  for (int c = 0; c < d->n_cons; ++c) {
+    for (int i = 0; i < d->n_idx; ++i) p.cons_coef[c][i] = d->cons_coef[c][i];
+    p.cons_off[c] = d->cons_off[c];
+    p.cons_range[c] = d->cons_range[c];
+  }
+  long long elems = 1;
+  for (int dd = 0; dd < d->out.rank; ++dd) elems *= d->out.sizes[dd];
+  p.out_elems = elems;
+  // direct mode: each output dim is exactly one distinct index variable
+  bool direct = true;
+  bool used[PMLB_MAX_IDX] = {false};
+  for (int dd = 0; dd < d->out.rank && direct; ++dd) {
+    int var = -1;
+    for (int i = 0; i < d->n_idx; ++i) {
+      if (d->out.coef[dd][i] != 0) {
+        if (var >= 0 || d->out.coef[dd][i] != 1) direct = false;
+        var = i;
+      }
+    }
+    if (var < 0 || p.out.den[dd] != 1 || used[var]) direct = false;
+    if (direct) {
+      used[var] = true;
+      p.out_var[dd] = var;
+    }
+  }
+  p.direct = direct ? 1 : 0;
+  p.n_loop = 0;
+  for (int i = 0; i < d->n_idx; ++i) {
+    if (!direct || !used[i]) p.loop_var[p.n_loop++] = i;
+  }
+  cudaGetDevice(&plan->device);
+  *out = plan;
+  return PMLB_OK;
+}
+
+pmlb_status pmlb_contract_invoke(pmlb_plan* plan, void* stream, const void* src0, const void* src1,
+                                 const void* src2, const void* init, void* outp) {
+  if (!plan || plan->kind != kPlanContract) return fail(PMLB_ERR_INVALID, "not a contraction plan");
+  pmlb::GenericParams p = plan->generic;
+  p.srcp[0] = src0;
+  p.srcp[1] = src1;
+  p.srcp[2] = src2;
+  p.initp = init;
+  p.outp = outp;
+  if (!outp || !src0 || (p.n_src > 1 && !src1) || (p.n_src > 2 && !src2) || (p.has_init && !init)) {
+    return fail(PMLB_ERR_INVALID, "contract: null tensor");
+  }
+  cudaError_t e = pmlb::launch_contract(p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "contract launch");
+  return PMLB_OK;
+}
+
+// ------------------------------------------------------------------ element-wise
+
+pmlb_status pmlb_eltwise_dispatch(const pmlb_eltwise_desc* d, pmlb_plan** out) {
+  if (!d || !out) return fail(PMLB_ERR_INVALID, "null argument");
+  *out = nullptr;
+  std::string why;
+  if (!have_sm100(&why)) return fail(PMLB_ERR_UNSUPPORTED, why);
+  char name[25];
+  std::memcpy(name, d->op, 24);
+  name[24] = 0;
+  const int op = ew_opcode(name);
+  if (op < 0) return fail(PMLB_ERR_UNSUPPORTED, std::string("eltwise: unknown operation '") + name + "'");
+  if (d->n_in < 1 || d->n_in > 3 || d->rank < 0 || d->rank > PMLB_MAX_RANK) {
+    return fail(PMLB_ERR_INVALID, "eltwise: descriptor counts out of range");
+  }
+  if (pmlb::dtype_class(d->out_dtype) < 0) return fail(PMLB_ERR_INVALID, "eltwise: bad output type");
+  pmlb_plan* plan = new (std::nothrow) pmlb_plan();
+  if (!plan) return fail(PMLB_ERR_INVALID, "out of host memory");
+  plan->kind = kPlanEltwise;
+  plan->kind_name = "eltwise";
+  pmlb::EltwiseParams& p = plan->eltwise;
+  std::memset(&p, 0, sizeof(p));
+  p.op = op;
+  p.n_in = d->n_in;
+  p.rank = d->rank;
+  p.out_dtype = d->out_dtype;
+  long long elems = 1;
+  for (int i = 0; i < d->rank; ++i) {
+    p.sizes[i] = d->sizes[i];
+    elems *= d->sizes[i];
+    for (int s = 0; s < 3; ++s) p.in_strides[s][i] = d->in_strides[s][i];
+  }
+  p.elems = elems;
+  bool any_float = false, all_unsigned = true, any_f64 = false;
+  for (int s = 0; s < d->n_in; ++s) {
+    p.in_dtype[s] = d->in_dtype[s];
+    const int cls = pmlb::dtype_class(d->in_dtype[s]);
+    if (cls < 0) {
+      delete plan;
+      return fail(PMLB_ERR_INVALID, "eltwise: bad operand type");
+    }
+    if (cls == pmlb::kClassF32 || cls == pmlb::kClassF64) any_float = true;
+    if (cls == pmlb::kClassF64) any_f64 = true;
+    if (cls != pmlb::kClassU64) all_unsigned = false;
+  }
+  (void)any_f64;
+  const bool is_cast = std::strcmp(name, "cast") == 0 || std::strcmp(name, "ident") == 0 ||
+                       std::strcmp(name, "assign") == 0;
+  if (is_compare(op)) {
+    // compare in a class wide enough for every operand; the result is 0 / 1
+    p.compute_class = any_float ? pmlb::kClassF64 : (all_unsigned ? pmlb::kClassU64 : pmlb::kClassI64);
+    p.arith_dtype = any_float ? PMLB_F64 : (all_unsigned ? PMLB_U64 : PMLB_I64);
+    p.narrow_inputs = 0;
+    p.narrow_result = 0;
+  } else if (is_cast) {
+    p.compute_class = pmlb::dtype_class(d->out_dtype);
+    if (d->out_dtype == PMLB_BOOL && any_float) p.compute_class = pmlb::kClassF64;
+    p.arith_dtype = d->out_dtype;
+    p.narrow_inputs = 0;
+    p.narrow_result = 0;
+  } else {
+    p.compute_class = pmlb::dtype_class(d->out_dtype);
+    p.arith_dtype = d->out_dtype;
+    p.narrow_inputs = 1;
+    p.narrow_result = 1;
+  }
+  cudaGetDevice(&plan->device);
+  *out = plan;
+  return PMLB_OK;
+}
+
+pmlb_status pmlb_eltwise_invoke(pmlb_plan* plan, void* stream, const void* in0, const void* in1,
+                                const void* in2, void* outp) {
+  if (!plan || plan->kind != kPlanEltwise) return fail(PMLB_ERR_INVALID, "not an eltwise plan");
+  pmlb::EltwiseParams p = plan->eltwise;
+  p.in[0] = in0;
+  p.in[1] = in1;
+  p.in[2] = in2;
+  p.out = outp;
+  if (!outp || !in0 || (p.n_in > 1 && !in1) || (p.n_in > 2 && !in2)) {
+    return fail(PMLB_ERR_INVALID, "eltwise: null tensor");
+  }
+  cudaError_t e = pmlb::launch_eltwise(p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "eltwise launch");
+  return PMLB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+#include "prepass.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "pmlb_kernels.h"
+
+namespace pmlb {
+
+namespace {
+
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+// 32x32 tiles through shared memory so that both the read and the (possibly transposed)
+// write are row-contiguous.
+__global__ void __launch_bounds__(256)
+split_tf32_kernel(const float* __restrict__ in, long long ld, long long in_batch,
+                  float* __restrict__ hi, float* __restrict__ lo, long long out_ld,
+                  long long out_batch, int rows, int cols, bool transpose) {
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z;
+  const float* src = in + static_cast<long long>(b) * in_batch;
+  float* dhi = hi + static_cast<long long>(b) * out_batch;
+  float* dlo = lo + static_cast<long long>(b) * out_batch;
+  const int r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int i = ty; i < 32; i += 8) {
+    const int r = r0 + i, c = c0 + tx;
+    tile[i][tx] = (r < rows && c < cols) ? src[static_cast<long long>(r) * ld + c] : 0.f;
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    float x;
+    long long o;
+    bool inside;
+    if (transpose) {
+      // output row = input column c0 + i, output column = input row r0 + tx
+      x = tile[tx][i];
+      inside = (c0 + i) < cols && (r0 + tx) < out_ld;
+      o = static_cast<long long>(c0 + i) * out_ld + (r0 + tx);
+    } else {
+      x = tile[i][tx];
+      inside = (r0 + i) < rows && (c0 + tx) < out_ld;
+      o = static_cast<long long>(r0 + i) * out_ld + (c0 + tx);
+    }
+    if (inside) {
+      const float h = tf32_round(x);
+      dhi[o] = h;
+      dlo[o] = tf32_round(x - h);
+    }
+  }
+}
+
+template <class T>
+__global__ void __launch_bounds__(256)
+transpose_kernel(const T* __restrict__ in, long long ld, long long in_batch, T* __restrict__ out,
+                 long long out_ld, long long out_batch, int rows, int cols) {
+  __shared__ T tile[32][33];
+  const int b = blockIdx.z;
+  const T* src = in + static_cast<long long>(b) * in_batch;
+  T* dst = out + static_cast<long long>(b) * out_batch;
+  const int r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int i = ty; i < 32; i += 8) {
+    const int r = r0 + i, c = c0 + tx;
+    if (r < rows && c < cols) tile[i][tx] = src[static_cast<long long>(r) * ld + c];
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int oc = c0 + i, orow = r0 + tx;
+    if (oc < cols && orow < rows) dst[static_cast<long long>(oc) * out_ld + orow] = tile[tx][i];
+  }
+}
+
+__device__ __forceinline__ float load_filter(const void* p, int dtype, long long i) {
+  if (dtype == PMLB_F32) return static_cast<const float*>(p)[i];
+  if (dtype == PMLB_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+__global__ void __launch_bounds__(256)
+filter_relayout_kernel(const void* __restrict__ in, int in_dtype, void* __restrict__ out,
+                       int out_dtype, int taps, int c, int k) {
+  const long long id = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long total = static_cast<long long>(taps) * c * k;
+  if (id >= total) return;
+  // id walks the output [k][taps][c]
+  const int ci = static_cast<int>(id % c);
+  const long long rem = id / c;
+  const int t = static_cast<int>(rem % taps);
+  const int ko = static_cast<int>(rem / taps);
+  const float v = load_filter(in, in_dtype, (static_cast<long long>(t) * c + ci) * k + ko);
+  if (out_dtype == PMLB_BF16) {
+    static_cast<__nv_bfloat16*>(out)[id] = __float2bfloat16_rn(v);
+  } else {
+    static_cast<__half*>(out)[id] = __float2half_rn(v);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_split_tf32(const float* in, long long ld, long long in_batch, float* hi,
+                              float* lo, long long out_ld, long long out_batch, int rows, int cols,
+                              int batch, bool transpose, cudaStream_t stream) {
+  // cover the padded output extent so that the pad is written (as zeros)
+  const int out_rows = transpose ? cols : rows;
+  const int out_cols = static_cast<int>(out_ld);
+  const int cover_rows = transpose ? out_cols : out_rows;  // in input-row units
+  const int cover_cols = transpose ? out_rows : out_cols;  // in input-col units
+  dim3 grid((cover_cols + 31) / 32, (cover_rows + 31) / 32, batch);
+  split_tf32_kernel<<<grid, 256, 0, stream>>>(in, ld, in_batch, hi, lo, out_ld, out_batch, rows,
+                                              cols, transpose);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_transpose(const void* in, long long ld, long long in_batch, void* out,
+                             long long out_ld, long long out_batch, int rows, int cols, int batch,
+                             int elem_bytes, cudaStream_t stream) {
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch);
+  switch (elem_bytes) {
+    case 1:
+      transpose_kernel<uint8_t><<<grid, 256, 0, stream>>>(
+          static_cast<const uint8_t*>(in), ld, in_batch, static_cast<uint8_t*>(out), out_ld,
+          out_batch, rows, cols);
+      break;
+    case 2:
+      transpose_kernel<uint16_t><<<grid, 256, 0, stream>>>(
+          static_cast<const uint16_t*>(in), ld, in_batch, static_cast<uint16_t*>(out), out_ld,
+          out_batch, rows, cols);
+      break;
+    case 4:
+      transpose_kernel<uint32_t><<<grid, 256, 0, stream>>>(
+          static_cast<const uint32_t*>(in), ld, in_batch, static_cast<uint32_t*>(out), out_ld,
+          out_batch, rows, cols);
+      break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_filter_relayout(const void* in, int in_dtype, void* out, int out_dtype, int taps,
+                                   int c, int k, cudaStream_t stream) {
+  const long long total = static_cast<long long>(taps) * c * k;
+  if (total <= 0) return cudaSuccess;
+  filter_relayout_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      in, in_dtype, out, out_dtype, taps, c, k);
+  return cudaGetLastError();
+}
+
+}  // namespace pmlb

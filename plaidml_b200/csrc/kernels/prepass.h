@@ -1,0 +1,26 @@
+// Operand preparation kernels that run before a tensor-core contraction.
+#pragma once
+
+#include <cuda_runtime.h>
+
+namespace pmlb {
+
+// fp32 [rows][cols] (row stride `ld`) -> TF32 hi and lo parts with hi + lo == x up to
+// 2^-22 relative.  transpose == false writes [rows][cols_pad], true writes [cols][rows_pad];
+// the padded tail of every output row is zero-filled.  `batch` matrices, `in_batch` /
+// `out_batch` elements apart.
+cudaError_t launch_split_tf32(const float* in, long long ld, long long in_batch, float* hi,
+                              float* lo, long long out_ld, long long out_batch, int rows, int cols,
+                              int batch, bool transpose, cudaStream_t stream);
+
+// Generic 2-D transpose of `elem_bytes`-sized elements: in [rows][cols] -> out [cols][out_ld].
+cudaError_t launch_transpose(const void* in, long long ld, long long in_batch, void* out,
+                             long long out_ld, long long out_batch, int rows, int cols, int batch,
+                             int elem_bytes, cudaStream_t stream);
+
+// Filter [taps][c][k] (element type `in_dtype`: f32, bf16 or f16) -> [k][taps][c] in the
+// 16-bit `out_dtype`.
+cudaError_t launch_filter_relayout(const void* in, int in_dtype, void* out, int out_dtype, int taps,
+                                   int c, int k, cudaStream_t stream);
+
+}  // namespace pmlb

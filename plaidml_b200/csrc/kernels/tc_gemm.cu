@@ -1,0 +1,352 @@
+// Host side of the tensor-core contraction kernel: tensor-map encoding, tile-shape
+// choice and launch.  No allocation happens here; callers own every buffer.
+#include "tc_launch.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "tc_gemm_kernel.cuh"
+
+namespace pmlb {
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+using EncodeIm2colFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                    const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                    cuuint32_t, cuuint32_t, const cuuint32_t*,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn g_encode_tiled = nullptr;
+EncodeIm2colFn g_encode_im2col = nullptr;
+std::once_flag g_driver_once;
+
+void load_driver_entry_points() {
+  std::call_once(g_driver_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      g_encode_im2col = reinterpret_cast<EncodeIm2colFn>(fn);
+    }
+  });
+}
+
+CUtensorMapDataType map_dtype(int eb, bool is_f16) {
+  if (eb == 4) return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  if (eb == 2) return is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+}
+
+// 3-D tiled map, 128-byte swizzle, zero fill outside the tensor.
+bool encode3d(CUtensorMap* map, CUtensorMapDataType dt, int eb, const void* base, uint64_t d0,
+              uint64_t d1, uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes,
+              uint32_t b0, uint32_t b1, uint32_t b2, std::string* err) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (stride1_bytes & 15u) != 0 ||
+      (stride2_bytes & 15u) != 0) {
+    *err = "operand base address and row strides must be multiples of 16 bytes";
+    return false;
+  }
+  if (b0 * static_cast<uint32_t>(eb) != 128u || b1 > 256u || b2 > 256u) {
+    *err = "internal: bad TMA box";
+    return false;
+  }
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {b0, b1, b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode_tiled(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    *err = "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r));
+    return false;
+  }
+  return true;
+}
+
+uint32_t make_idesc(int eb, bool is_f16, bool b_mn, int bn) {
+  // bits: [4,6) D format, [7,10) A format, [10,13) B format, 15 A major, 16 B major,
+  //       [17,23) N >> 3, [24,29) M >> 4
+  uint32_t cfmt, abfmt;
+  if (eb == 1) {
+    cfmt = 2;   // s32
+    abfmt = 1;  // signed 8 bit
+  } else if (eb == 4) {
+    cfmt = 1;   // f32
+    abfmt = 2;  // tf32
+  } else {
+    cfmt = 1;
+    abfmt = is_f16 ? 0u : 1u;
+  }
+  uint32_t d = 0;
+  d |= cfmt << 4;
+  d |= abfmt << 7;
+  d |= abfmt << 10;
+  d |= (b_mn ? 1u : 0u) << 16;
+  d |= static_cast<uint32_t>(bn >> 3) << 17;
+  d |= static_cast<uint32_t>(128 >> 4) << 24;
+  return d;
+}
+
+template <class Cfg>
+cudaError_t launch_cfg(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
+                       const CUtensorMap& b1, const TcParams& p, int grid, cudaStream_t stream) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  // The attribute is per device; set it on every call (cheap) rather than once.
+  (void)once;
+  attr_err = cudaFuncSetAttribute(tc_contract_kernel<Cfg>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+  if (attr_err != cudaSuccess) return attr_err;
+  tc_contract_kernel<Cfg><<<grid, 192, Cfg::SMEM_BYTES, stream>>>(a0, a1, b0, b1, p);
+  return cudaGetLastError();
+}
+
+int pick_bn(const TcLaunch& L, int num_sms) {
+  if (L.bn_override == 64 || L.bn_override == 128 || L.bn_override == 256) return L.bn_override;
+  const int max_bn = (L.nsplit == 2) ? 128 : 256;
+  if (L.n <= 64) return 64;
+  if (L.n <= 128) return 128;
+  if (max_bn == 128) return 128;
+  // 256-wide tiles halve the A re-reads; use them once they still fill the machine.
+  const long long tiles256 =
+      static_cast<long long>(L.batch) * ((L.m + 127) / 128) * ((L.n + 255) / 256);
+  if (L.n % 256 == 0 || L.n > 512) {
+    if (tiles256 >= num_sms) return 256;
+  }
+  return 128;
+}
+
+}  // namespace
+
+bool tc_supported(std::string* why) {
+  load_driver_entry_points();
+  if (!g_encode_tiled || !g_encode_im2col) {
+    if (why) *why = "CUDA driver does not export cuTensorMapEncodeTiled/Im2col";
+    return false;
+  }
+  return true;
+}
+
+int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
+  load_driver_entry_points();
+  if (!g_encode_tiled || !g_encode_im2col) {
+    *err = "CUDA driver does not export the tensor-map encoders";
+    return 3;
+  }
+  if (L.m <= 0 || L.n <= 0 || L.k <= 0 || L.batch <= 0) {
+    *err = "empty problem";
+    return 1;
+  }
+  const int eb = L.elem_bytes;
+  if (!(eb == 1 || eb == 2 || eb == 4) || (eb == 4) != (L.nsplit == 2) ||
+      (L.nsplit != 1 && L.nsplit != 2)) {
+    *err = "unsupported element size / split combination";
+    return 1;
+  }
+  int dev = 0, num_sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+
+  int bn = pick_bn(L, num_sms);
+  const int bk = 128 / eb;
+  if (L.b_mn && bn < bk) bn = bk;           // MN-major B tiles are whole 128-byte chunks of N
+  if (L.b_mn && L.nsplit == 2) {
+    *err = "fp32 operands reach this kernel pre-split and K-major";
+    return 1;
+  }
+  if (L.conv && (L.b_mn || L.nsplit != 1 || eb != 2)) {
+    *err = "im2col path takes 16-bit K-major operands";
+    return 1;
+  }
+
+  TcParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.m = L.m;
+  p.n = L.n;
+  p.k = L.k;
+  p.batch = L.batch;
+  p.tiles_m = (L.m + 127) / 128;
+  p.tiles_n = (L.n + bn - 1) / bn;
+  p.group_m = 16;
+  p.a_bz = L.a_batch_stride != 0 ? 1 : 0;
+  p.b_bz = L.b_batch_stride != 0 ? 1 : 0;
+  p.out = L.out;
+  p.ldc = L.ldc;
+  p.out_batch = L.out_batch_stride;
+  p.out_dtype = L.out_dtype;
+  p.epi_flags = L.epi_flags;
+  p.bias = L.bias;
+  p.residual = L.residual;
+  p.ldr = L.ldr;
+  p.res_batch = L.res_batch_stride;
+  p.rowmax = L.rowmax;
+  p.status = L.status;
+  p.idesc = make_idesc(eb, L.is_f16, L.b_mn, bn);
+
+  const CUtensorMapDataType dt = map_dtype(eb, L.is_f16);
+  CUtensorMap ta0, ta1, tb0, tb1;
+  std::memset(&ta0, 0, sizeof(ta0));
+  std::memset(&ta1, 0, sizeof(ta1));
+  std::memset(&tb0, 0, sizeof(tb0));
+  std::memset(&tb1, 0, sizeof(tb1));
+
+  if (L.conv) {
+    const ConvGeom& g = *L.conv;
+    if (g.c % 8 != 0) {
+      *err = "im2col path needs the channel count to be a multiple of 8";
+      return 3;
+    }
+    p.conv_p = g.p;
+    p.conv_q = g.q;
+    p.conv_s = g.s;
+    p.conv_cblocks = (g.c + bk - 1) / bk;
+    p.conv_stride_h = g.stride_h;
+    p.conv_stride_w = g.stride_w;
+    p.conv_lower_h = -g.pad_h;
+    p.conv_lower_w = -g.pad_w;
+    p.conv_dil_h = g.dil_h;
+    p.conv_dil_w = g.dil_w;
+    p.num_kb = g.r * g.s * p.conv_cblocks;
+    // activation (C, W, H, N), bounding box chosen so that exactly p x q base pixels exist
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.c), static_cast<cuuint64_t>(g.w),
+                          static_cast<cuuint64_t>(g.h), static_cast<cuuint64_t>(g.n)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(g.c) * eb,
+                             static_cast<cuuint64_t>(g.c) * g.w * eb,
+                             static_cast<cuuint64_t>(g.c) * g.w * g.h * eb};
+    // upper corner such that (extent + upper - lower - 1) / stride + 1 == outputs
+    int lower[2] = {-g.pad_w, -g.pad_h};
+    int upper[2] = {(g.q - 1) * g.stride_w + 1 - g.pad_w - g.w,
+                    (g.p - 1) * g.stride_h + 1 - g.pad_h - g.h};
+    cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(g.stride_w),
+                          static_cast<cuuint32_t>(g.stride_h), 1};
+    if ((reinterpret_cast<uintptr_t>(L.a0) & 15u) != 0) {
+      *err = "activation base address must be 16-byte aligned";
+      return 1;
+    }
+    CUresult r = g_encode_im2col(&ta0, dt, 4, const_cast<void*>(L.a0), dims, strides, lower, upper,
+                                 static_cast<cuuint32_t>(bk), 128u, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      *err = "cuTensorMapEncodeIm2col failed with code " + std::to_string(static_cast<int>(r));
+      return 2;
+    }
+    {
+      // Drivers up to CUDA 13.1 encode im2col maps of tensors below 128 KiB with a
+      // flag that makes the copy misbehave; CUTLASS clears it the same way.
+      int driver_version = 0;
+      cudaDriverGetVersion(&driver_version);
+      const unsigned long long bytes =
+          static_cast<unsigned long long>(g.c) * g.w * g.h * g.n * eb;
+      if (driver_version <= 13010 && bytes < 131072ull) {
+        reinterpret_cast<uint64_t*>(&ta0)[1] &= ~(1ull << 21);
+      }
+    }
+    ta1 = ta0;
+    // weights [k_out][taps][c]
+    const int taps = g.r * g.s;
+    if (!encode3d(&tb0, dt, eb, L.b0, g.c, taps, L.n, static_cast<uint64_t>(g.c) * eb,
+                  static_cast<uint64_t>(g.c) * taps * eb, bk, 1, bn, err)) {
+      return 1;
+    }
+    tb1 = tb0;
+  } else {
+    p.num_kb = (L.k + bk - 1) / bk;
+    const uint64_t a_bs = p.a_bz ? static_cast<uint64_t>(L.a_batch_stride) * eb
+                                 : static_cast<uint64_t>(L.lda) * eb * L.m;
+    if (!encode3d(&ta0, dt, eb, L.a0, L.k, L.m, p.a_bz ? L.batch : 1,
+                  static_cast<uint64_t>(L.lda) * eb, a_bs, bk, 128, 1, err)) {
+      return 1;
+    }
+    ta1 = ta0;
+    if (L.nsplit == 2 &&
+        !encode3d(&ta1, dt, eb, L.a1, L.k, L.m, p.a_bz ? L.batch : 1,
+                  static_cast<uint64_t>(L.lda) * eb, a_bs, bk, 128, 1, err)) {
+      return 1;
+    }
+    if (L.b_mn) {
+      const uint64_t b_bs = p.b_bz ? static_cast<uint64_t>(L.b_batch_stride) * eb
+                                   : static_cast<uint64_t>(L.ldb) * eb * L.k;
+      if (!encode3d(&tb0, dt, eb, L.b0, L.n, L.k, p.b_bz ? L.batch : 1,
+                    static_cast<uint64_t>(L.ldb) * eb, b_bs, bk, bk, 1, err)) {
+        return 1;
+      }
+      tb1 = tb0;
+    } else {
+      const uint64_t b_bs = p.b_bz ? static_cast<uint64_t>(L.b_batch_stride) * eb
+                                   : static_cast<uint64_t>(L.ldb) * eb * L.n;
+      if (!encode3d(&tb0, dt, eb, L.b0, L.k, L.n, p.b_bz ? L.batch : 1,
+                    static_cast<uint64_t>(L.ldb) * eb, b_bs, bk, bn, 1, err)) {
+        return 1;
+      }
+      tb1 = tb0;
+      if (L.nsplit == 2 &&
+          !encode3d(&tb1, dt, eb, L.b1, L.k, L.n, p.b_bz ? L.batch : 1,
+                    static_cast<uint64_t>(L.ldb) * eb, b_bs, bk, bn, 1, err)) {
+        return 1;
+      }
+    }
+  }
+
+  const long long total = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n;
+  if (total > 0x7fffffffLL) {
+    *err = "too many tiles";
+    return 1;
+  }
+  int grid = static_cast<int>(std::min<long long>(total, num_sms));
+  if (L.grid_override > 0) grid = std::min<long long>(total, L.grid_override);
+
+  cudaError_t ce = cudaErrorInvalidValue;
+#define PMLB_TC_CASE(EB, BN, NS, IM, MN)                                               \
+  if (eb == EB && bn == BN && L.nsplit == NS && (L.conv != nullptr) == IM && L.b_mn == MN) { \
+    ce = launch_cfg<TcCfg<EB, BN, NS, IM, MN>>(ta0, ta1, tb0, tb1, p, grid, stream);    \
+  } else
+  PMLB_TC_CASE(2, 64, 1, false, false)
+  PMLB_TC_CASE(2, 128, 1, false, false)
+  PMLB_TC_CASE(2, 256, 1, false, false)
+  PMLB_TC_CASE(2, 64, 1, false, true)
+  PMLB_TC_CASE(2, 128, 1, false, true)
+  PMLB_TC_CASE(2, 256, 1, false, true)
+  PMLB_TC_CASE(2, 64, 1, true, false)
+  PMLB_TC_CASE(2, 128, 1, true, false)
+  PMLB_TC_CASE(2, 256, 1, true, false)
+  PMLB_TC_CASE(1, 64, 1, false, false)
+  PMLB_TC_CASE(1, 128, 1, false, false)
+  PMLB_TC_CASE(1, 256, 1, false, false)
+  PMLB_TC_CASE(1, 128, 1, false, true)
+  PMLB_TC_CASE(1, 256, 1, false, true)
+  PMLB_TC_CASE(4, 64, 2, false, false)
+  PMLB_TC_CASE(4, 128, 2, false, false) {
+    *err = "no kernel instance for this tile configuration";
+    return 3;
+  }
+#undef PMLB_TC_CASE
+  if (ce != cudaSuccess) {
+    *err = std::string("kernel launch failed: ") + cudaGetErrorString(ce);
+    return 2;
+  }
+  return 0;
+}
+
+}  // namespace pmlb

@@ -1,0 +1,58 @@
+// Device-side parameter block shared by the tensor-core contraction kernel and
+// the host code that plans it.
+#pragma once
+
+#include <cuda.h>
+#include <stdint.h>
+
+namespace pmlb {
+
+// Element types seen by the epilogue (values follow the public pmlb_dtype enum).
+enum : int {
+  kDtF32 = 14,
+  kDtF16 = 13,
+  kDtBF16 = 16,
+  kDtI8 = 5,
+  kDtI32 = 9,
+};
+
+enum : int {
+  kEpiBias = 1,      // add bias[col] (f32 for float accumulators, i32 for integer ones)
+  kEpiResidual = 2,  // add residual[row, col] (same element type as the output)
+  kEpiRelu = 4,      // x < 0 ? 0 : x (ordered compare: NaN passes through)
+  kEpiRowMax = 8,    // do not store the tile; fold it into rowmax[row] with atomic max
+};
+
+struct TcParams {
+  // Problem (per batch entry): C[m, n] = sum_k A[m, k] * B[n, k]
+  int m, n, k, batch;
+  int tiles_m, tiles_n;  // tiles per batch entry
+  int num_kb;            // k-blocks (of 128 bytes of K) per tile
+  int group_m;           // m-tiles per rasterisation group (L2 reuse of B panels)
+  int a_bz, b_bz;        // 1: operand has a batch dimension, 0: one matrix shared by all entries
+
+  // Implicit-GEMM convolution (A fetched by im2col TMA); unused for plain GEMM.
+  int conv_p, conv_q;          // output rows / columns per image
+  int conv_s;                  // filter taps along W
+  int conv_cblocks;            // channel blocks per filter tap
+  int conv_stride_h, conv_stride_w;
+  int conv_lower_h, conv_lower_w;  // bounding-box lower corner (= -pad)
+  int conv_dil_h, conv_dil_w;
+
+  // Epilogue
+  void* out;
+  long long ldc;         // elements between output rows
+  long long out_batch;   // elements between batch entries
+  int out_dtype;
+  int epi_flags;
+  const void* bias;
+  const void* residual;
+  long long ldr;
+  long long res_batch;
+  float* rowmax;         // kEpiRowMax target, [batch * m]
+
+  uint32_t idesc;        // tcgen05 instruction descriptor
+  int* status;           // device word: 0 = ok, otherwise the first error code seen
+};
+
+}  // namespace pmlb

@@ -1,0 +1,62 @@
+// Host-side description of one launch of the tensor-core contraction kernel.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <string>
+
+namespace pmlb {
+
+// NHWC activation [n, h, w, c] convolved with r x s taps into [n, p, q, k_out].
+struct ConvGeom {
+  int n, h, w, c;
+  int r, s;
+  int p, q;
+  int stride_h, stride_w;
+  int pad_h, pad_w;  // zero padding before the first row / column
+  int dil_h, dil_w;
+};
+
+struct TcLaunch {
+  int elem_bytes = 2;   // 1 (int8), 2 (bf16 / f16), 4 (fp32 pre-split into TF32 hi / lo)
+  bool is_f16 = false;  // 2-byte operands are IEEE half instead of bfloat16
+  int nsplit = 1;       // 2: a0/b0 hold the hi parts, a1/b1 the lo parts
+  bool b_mn = false;    // false: B stored [n][k]; true: B stored [k][n]
+  int m = 0, n = 0, k = 0, batch = 1;
+
+  const void* a0 = nullptr;
+  const void* a1 = nullptr;
+  long long lda = 0;             // elements between rows of A
+  long long a_batch_stride = 0;  // elements between batch entries, 0 = shared
+  const void* b0 = nullptr;
+  const void* b1 = nullptr;
+  long long ldb = 0;
+  long long b_batch_stride = 0;
+
+  const ConvGeom* conv = nullptr;  // non-null: A is an NHWC activation fetched by im2col TMA,
+                                   // B holds the weights as [k_out][r*s][c]
+
+  void* out = nullptr;
+  long long ldc = 0;
+  long long out_batch_stride = 0;
+  int out_dtype = 14;
+  int epi_flags = 0;
+  const void* bias = nullptr;
+  const void* residual = nullptr;
+  long long ldr = 0;
+  long long res_batch_stride = 0;
+  float* rowmax = nullptr;
+
+  int* status = nullptr;  // device word that receives a non-zero code if a wait times out
+
+  int bn_override = 0;    // 0 = choose; else 64, 128 or 256
+  int grid_override = 0;  // 0 = one CTA per SM
+};
+
+// Returns 0 on success; otherwise 1 (invalid argument), 2 (CUDA error) or
+// 3 (unsupported) with a message in *err.
+int tc_launch(const TcLaunch& launch, cudaStream_t stream, std::string* err);
+
+bool tc_supported(std::string* why);
+
+}  // namespace pmlb

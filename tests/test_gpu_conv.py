@@ -1,0 +1,128 @@
+"""Parity of the implicit-GEMM (im2col TMA) convolution kernel with the CPU oracle."""
+
+import numpy as np
+import pytest
+
+import oracle
+from plaidml_b200 import kernels as K
+from gpu_util import as_f32, check_close, dev, dev_bf16, empty, ptr, rng
+
+pytestmark = pytest.mark.gpu
+
+
+def out_size(i, f, s, pad_before, pad_after, d=1):
+    return (i + pad_before + pad_after - d * (f - 1) - 1) // s + 1
+
+
+def run_conv(seed, n, h, w, c, r, s, k, stride=1, pad=None, out_dtype=K.F32, epilogue=0, tile_n=0, dil=1,
+             same_upper=False):
+    g = rng(seed)
+    if pad is None:
+        pad = (r - 1) // 2
+    if same_upper:
+        # SAME_UPPER of plaidml/op/lib/ops.cc:347-382: out = ceil(in / stride), the odd pad goes after
+        p, q = -(-h // stride), -(-w // stride)
+        pad_h = max(0, (p - 1) * stride + r - h) // 2
+        pad_w = max(0, (q - 1) * stride + s - w) // 2
+    else:
+        pad_h = pad_w = pad
+        p = out_size(h, r, stride, pad, pad, dil)
+        q = out_size(w, s, stride, pad, pad, dil)
+    x = dev_bf16(g.uniform(0, 1, size=(n, h, w, c)))
+    f32 = (g.standard_normal((r, s, c, k)) * np.sqrt(2.0 / (r * s * c))).astype(np.float32)
+    f_bf = oracle.bf16_to_f32(oracle.f32_to_bf16(f32))
+    bias = g.standard_normal(k).astype(np.float32) if epilogue & K.EPI_BIAS else None
+    res = dev_bf16(g.standard_normal((n, p, q, k))) if epilogue & K.EPI_RESIDUAL and out_dtype == K.BF16 else None
+    if epilogue & K.EPI_RESIDUAL and out_dtype == K.F32:
+        res = dev(g.standard_normal((n, p, q, k)).astype(np.float32))
+    d = K.ConvDesc()
+    d.in_dtype, d.out_dtype = K.BF16, out_dtype
+    d.n, d.h, d.w, d.c, d.r, d.s, d.k, d.p, d.q = n, h, w, c, r, s, k, p, q
+    d.stride_h = d.stride_w = stride
+    d.pad_h, d.pad_w = pad_h, pad_w
+    d.dil_h = d.dil_w = dil
+    d.epilogue, d.tile_n = epilogue, tile_n
+    plan = K.Plan("conv", d)
+    f_dev = dev(f32)
+    plan.set_filter(ptr(f_dev), K.F32)
+    out = empty((n, p, q, k), out_dtype)
+    out.fill_(0)
+    bias_dev = dev(bias) if bias is not None else None
+    plan.conv(ptr(x), ptr(out), ptr(bias_dev), ptr(res))
+    plan.check()
+    ref = oracle.conv2d_nhwc_f32(as_f32(x), f_bf, bias, None if res is None else as_f32(res), (stride, stride),
+                                 (pad_h, pad_w), (dil, dil), bool(epilogue & K.EPI_RELU), out_hw=(p, q))
+    return as_f32(out), ref, plan
+
+
+def test_conv1x1():
+    out, ref, plan = run_conv(1, 2, 16, 16, 64, 1, 1, 64)
+    assert plan.kernel == "tc_conv"
+    check_close(out, ref, 1e-4)
+
+
+def test_conv3x3_same_small():
+    out, ref, _ = run_conv(2, 2, 16, 16, 64, 3, 3, 64)
+    check_close(out, ref, 1e-4)
+
+
+def test_conv3x3_56x56_reference_layer():
+    # the layer of plaidml/edsl/tests/edsl_test.cc:685-712: 1x56x56x64 (*) 3x3x64x64, same padding
+    out, ref, _ = run_conv(3, 1, 56, 56, 64, 3, 3, 64)
+    check_close(out, ref, 1e-4)
+
+
+def test_conv3x3_bias_relu_bf16_out():
+    out, ref, _ = run_conv(4, 4, 28, 28, 128, 3, 3, 128, out_dtype=K.BF16, epilogue=K.EPI_BIAS | K.EPI_RELU)
+    check_close(out, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+
+
+def test_conv3x3_stride2():
+    out, ref, _ = run_conv(5, 2, 28, 28, 64, 3, 3, 128, stride=2)
+    check_close(out, ref, 1e-4)
+
+
+def test_conv3x3_stride2_same_upper():
+    out, ref, _ = run_conv(6, 2, 28, 28, 64, 3, 3, 64, stride=2, same_upper=True)
+    check_close(out, ref, 1e-4)
+
+
+def test_conv1x1_stride2_residual_relu():
+    out, ref, _ = run_conv(7, 2, 28, 28, 128, 1, 1, 256, stride=2, pad=0, out_dtype=K.BF16,
+                           epilogue=K.EPI_BIAS | K.EPI_RESIDUAL | K.EPI_RELU)
+    check_close(out, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+
+
+def test_conv_channels_not_multiple_of_block():
+    # 32 and 96 input channels: the last (only) channel block is partly out of range
+    out, ref, _ = run_conv(8, 2, 14, 14, 32, 3, 3, 64)
+    check_close(out, ref, 1e-4)
+    out, ref, _ = run_conv(9, 2, 14, 14, 96, 3, 3, 48)
+    check_close(out, ref, 1e-4)
+
+
+def test_conv7x7_stride2_pad3():
+    out, ref, _ = run_conv(10, 2, 32, 32, 8, 7, 7, 64, stride=2, pad=3)
+    check_close(out, ref, 1e-4)
+
+
+def test_conv_small_tensor_below_128k():
+    # activation tensor smaller than 128 KiB
+    out, ref, _ = run_conv(11, 1, 8, 8, 64, 3, 3, 64)
+    check_close(out, ref, 1e-4)
+
+
+def test_conv_dilated():
+    out, ref, _ = run_conv(12, 2, 20, 20, 64, 3, 3, 64, pad=2, dil=2)
+    check_close(out, ref, 1e-4)
+
+
+def test_conv_rejects_odd_channels():
+    d = K.ConvDesc()
+    d.in_dtype, d.out_dtype = K.BF16, K.F32
+    d.n, d.h, d.w, d.c, d.r, d.s, d.k, d.p, d.q = 1, 8, 8, 3, 3, 3, 8, 8, 8
+    d.stride_h = d.stride_w = d.dil_h = d.dil_w = 1
+    d.pad_h = d.pad_w = 1
+    with pytest.raises(K.KernelError) as e:
+        K.Plan("conv", d)
+    assert e.value.status == K.ERR_UNSUPPORTED

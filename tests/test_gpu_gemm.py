@@ -1,0 +1,221 @@
+"""Parity of the tcgen05 GEMM kernels with the CPU oracle, through the kernel C ABI."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from plaidml_b200 import kernels as K
+from gpu_util import as_f32, bits16, check_close, dev, dev_bf16, empty, max_rel, ptr, rng
+
+pytestmark = pytest.mark.gpu
+
+
+def run_gemm(in_dtype, out_dtype, a_t, b_t, m, n, k, batch=1, b_is_nk=True, epilogue=0, bias=None, residual=None,
+             tile_n=0, flags=0, stride_a=None, stride_b=None, want_rowmax=False, store=True):
+    d = K.GemmDesc()
+    d.in_dtype, d.out_dtype = in_dtype, out_dtype
+    d.m, d.n, d.k, d.batch = m, n, k, batch
+    d.lda = k
+    d.ldb = k if b_is_nk else n
+    d.ldc = n
+    d.stride_a = m * k if stride_a is None else stride_a
+    d.stride_b = n * k if stride_b is None else stride_b
+    d.stride_c = m * n
+    d.b_is_nk = int(b_is_nk)
+    d.epilogue = epilogue
+    d.ldr, d.stride_r = n, m * n
+    d.tile_n, d.flags = tile_n, flags
+    plan = K.Plan("gemm", d)
+    c = empty((batch, m, n), out_dtype) if store else None
+    if c is not None:
+        c.fill_(0)
+    rowmax = empty((batch, m), K.F32) if want_rowmax else None
+    plan.gemm(ptr(a_t), ptr(b_t), ptr(c), ptr(bias), ptr(residual), ptr(rowmax))
+    plan.check()
+    return c, rowmax, plan
+
+
+def bf16_case(seed, m, n, k, batch=1, b_is_nk=True, **kw):
+    g = rng(seed)
+    a = dev_bf16(g.standard_normal((batch, m, k)))
+    bshape = (batch, n, k) if b_is_nk else (batch, k, n)
+    b = dev_bf16(g.standard_normal(bshape))
+    c, _, plan = run_gemm(K.BF16, K.F32, a, b, m, n, k, batch, b_is_nk, **kw)
+    ref = oracle.gemm_h16_f32(bits16(a), bits16(b), False, b_is_nk)
+    return c.cpu().numpy(), ref, plan
+
+
+# --- bf16, both operands K-major (the Q.K^T shape) -------------------------------------
+
+def test_bf16_nt_single_tile():
+    c, ref, plan = bf16_case(1, 128, 128, 64)
+    assert plan.kernel == "tc_gemm"
+    check_close(c, ref, 1e-4)
+
+
+def test_bf16_nt_multi_kblock():
+    c, ref, _ = bf16_case(2, 128, 128, 512)
+    check_close(c, ref, 1e-4)
+
+
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+def test_bf16_nt_multi_tile(tile_n):
+    c, ref, _ = bf16_case(3, 384, 512, 256, tile_n=tile_n)
+    check_close(c, ref, 1e-4)
+
+
+def test_bf16_nt_ragged():
+    # M, N not multiples of the tile; K not a multiple of the 64-element k-block
+    c, ref, _ = bf16_case(4, 200, 136, 72)
+    check_close(c, ref, 1e-4)
+
+
+def test_bf16_nt_batched_many_tiles():
+    # more tiles than SMs: every CTA walks several tiles and both TMEM accumulators
+    c, ref, _ = bf16_case(5, 256, 256, 128, batch=40)
+    check_close(c, ref, 1e-4)
+
+
+def test_bf16_nt_shared_b():
+    g = rng(6)
+    a = dev_bf16(g.standard_normal((3, 130, 64)))
+    b = dev_bf16(g.standard_normal((1, 96, 64)))
+    c, _, _ = run_gemm(K.BF16, K.F32, a, b, 130, 96, 64, batch=3, stride_b=0)
+    ref = oracle.gemm_h16_f32(bits16(a), bits16(b), False, True)
+    check_close(c.cpu().numpy(), ref, 1e-4)
+
+
+# --- bf16, B stored [k][n] (the Tile GEMM C[i,j] += A[i,k] * B[k,j]) ---------------------
+
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+def test_bf16_nn(tile_n):
+    c, ref, _ = bf16_case(7, 256, 512, 192, b_is_nk=False, tile_n=tile_n)
+    check_close(c, ref, 1e-4)
+
+
+def test_bf16_nn_ragged():
+    c, ref, _ = bf16_case(8, 130, 200, 88, b_is_nk=False)
+    check_close(c, ref, 1e-4)
+
+
+def test_bf16_nn_via_transposed_scratch():
+    c, ref, plan = bf16_case(9, 256, 320, 136, b_is_nk=False, flags=K.GEMM_TRANSPOSE_B)
+    assert plan.scratch_bytes > 0
+    check_close(c, ref, 1e-4)
+
+
+# --- epilogues -----------------------------------------------------------------------------
+
+def test_bf16_bias_relu_bf16_out():
+    g = rng(10)
+    m, n, k = 256, 192, 128
+    a = dev_bf16(g.standard_normal((1, m, k)))
+    b = dev_bf16(g.standard_normal((1, n, k)))
+    bias = dev(g.standard_normal(n).astype(np.float32))
+    res = dev_bf16(g.standard_normal((1, m, n)))
+    c, _, _ = run_gemm(K.BF16, K.BF16, a, b, m, n, k, epilogue=K.EPI_BIAS | K.EPI_RESIDUAL | K.EPI_RELU,
+                       bias=bias, residual=res)
+    ref = oracle.gemm_h16_f32(bits16(a), bits16(b), False, True)
+    ref = ref + bias.cpu().numpy()[None, None, :] + as_f32(res)
+    ref = np.where(ref < 0, 0, ref)
+    ref_bf16 = oracle.bf16_to_f32(oracle.f32_to_bf16(ref))
+    # 1e-2 relative: the stated tolerance for bf16 results (one bf16 ulp is 2^-8)
+    check_close(as_f32(c), ref_bf16, 1e-2)
+
+
+def test_f16_nt():
+    g = rng(11)
+    m, n, k = 128, 128, 128
+    a = dev(g.standard_normal((1, m, k)).astype(np.float16))
+    b = dev(g.standard_normal((1, n, k)).astype(np.float16))
+    c, _, _ = run_gemm(K.F16, K.F32, a, b, m, n, k)
+    ref = oracle.gemm_h16_f32(bits16(a), bits16(b), True, True)
+    check_close(c.cpu().numpy(), ref, 1e-4)
+
+
+def test_bf16_rowmax_epilogue():
+    g = rng(12)
+    batch, m, n, k = 4, 256, 512, 64
+    a = dev_bf16(g.standard_normal((batch, m, k)))
+    b = dev_bf16(g.standard_normal((batch, n, k)))
+    c, rowmax, _ = run_gemm(K.BF16, K.F32, a, b, m, n, k, batch=batch, epilogue=K.EPI_ROWMAX, want_rowmax=True)
+    s = c.cpu().numpy()
+    # exact given identical S: the fused max sees the same f32 values that were stored
+    np.testing.assert_array_equal(rowmax.cpu().numpy(), s.max(axis=2))
+    _, rowmax2, _ = run_gemm(K.BF16, K.F32, a, b, m, n, k, batch=batch, epilogue=K.EPI_ROWMAX, want_rowmax=True,
+                             store=False)
+    np.testing.assert_array_equal(rowmax2.cpu().numpy(), s.max(axis=2))
+
+
+# --- int8 -> int32, bit exact ---------------------------------------------------------------
+
+def int8_case(seed, m, n, k, b_is_nk, **kw):
+    g = rng(seed)
+    a = g.integers(-128, 128, size=(1, m, k), dtype=np.int8)
+    bshape = (1, n, k) if b_is_nk else (1, k, n)
+    b = g.integers(-128, 128, size=bshape, dtype=np.int8)
+    c, _, plan = run_gemm(K.I8, K.I32, dev(a), dev(b), m, n, k, 1, b_is_nk, **kw)
+    return c.cpu().numpy(), oracle.gemm_i8_i32(a, b, b_is_nk), plan
+
+
+def test_int8_nt_exact():
+    c, ref, _ = int8_case(20, 256, 256, 512, True)
+    np.testing.assert_array_equal(c, ref)
+
+
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_int8_nn_exact(tile_n):
+    c, ref, _ = int8_case(21, 384, 512, 384, False, tile_n=tile_n)
+    np.testing.assert_array_equal(c, ref)
+
+
+def test_int8_nn_ragged_exact():
+    c, ref, _ = int8_case(22, 200, 144, 208, False)
+    np.testing.assert_array_equal(c, ref)
+
+
+def test_int8_nn_via_transposed_scratch_exact():
+    c, ref, _ = int8_case(23, 256, 256, 256, False, flags=K.GEMM_TRANSPOSE_B)
+    np.testing.assert_array_equal(c, ref)
+
+
+def test_int8_wraps_to_int8():
+    # int8 (*) int8 without casts yields int8: the 32-bit sum truncated (GEMM_INT8 of
+    # plaidml/edsl/examples/gemm.cc)
+    g = rng(24)
+    m = n = k = 128
+    a = g.integers(-128, 128, size=(1, m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(1, n, k), dtype=np.int8)
+    c, _, _ = run_gemm(K.I8, K.I8, dev(a), dev(b), m, n, k)
+    ref = oracle.gemm_i8_i32(a, b, True).astype(np.int8)
+    np.testing.assert_array_equal(c.cpu().numpy(), ref)
+
+
+# --- fp32 as 3xTF32 ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("b_is_nk", [True, False])
+def test_f32_3xtf32(b_is_nk):
+    g = rng(30)
+    m, n, k = 256, 192, 320
+    a = g.uniform(-1, 1, size=(1, m, k)).astype(np.float32)
+    b = g.uniform(-1, 1, size=(1, n, k) if b_is_nk else (1, k, n)).astype(np.float32)
+    c, _, plan = run_gemm(K.F32, K.F32, dev(a), dev(b), m, n, k, 1, b_is_nk)
+    assert plan.scratch_bytes > 0
+    ref64 = oracle.gemm_f32_acc64(a, b, b_is_nk)
+    ref32 = oracle.gemm_f32(a, b, b_is_nk)
+    err = max_rel(c.cpu().numpy(), ref64)
+    err_cpu = max_rel(ref32, ref64)
+    print(f"3xTF32 max-rel vs f64: {err:.3e}; f32 CPU loop vs f64: {err_cpu:.3e}")
+    # 1e-5 relative: the tolerance the reference's own f32 Dot test uses (edsl_test.cc:448-486)
+    assert err < 1e-5
+    check_close(c.cpu().numpy(), ref32, 1e-5)
+
+
+def test_f32_ragged():
+    g = rng(31)
+    m, n, k = 70, 50, 37
+    a = g.uniform(-1, 1, size=(1, m, k)).astype(np.float32)
+    b = g.uniform(-1, 1, size=(1, k, n)).astype(np.float32)
+    c, _, _ = run_gemm(K.F32, K.F32, dev(a), dev(b), m, n, k, 1, False)
+    assert max_rel(c.cpu().numpy(), oracle.gemm_f32_acc64(a, b, False)) < 1e-5
