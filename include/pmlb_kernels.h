@@ -63,7 +63,8 @@ enum {
   PMLB_EPI_BIAS = 1,     /* out[.., j] += bias[j]; bias is f32 (float paths) or i32 (int8 path) */
   PMLB_EPI_RESIDUAL = 2, /* out += residual (same shape and element type as out) */
   PMLB_EPI_RELU = 4,     /* x < 0 ? 0 : x, as pmlc/conversion/pxa_to_affine/pxa_to_affine.cc:312-332 */
-  PMLB_EPI_ROWMAX = 8    /* additionally reduce each output row with max into `rowmax` (f32) */
+  PMLB_EPI_ROWMAX = 8    /* additionally reduce each output row with max into `rowmax` (f32);
+                            not combinable with the other steps */
 };
 
 const char* pmlb_last_error(void);
@@ -71,6 +72,11 @@ const char* pmlb_version(void);
 
 /* Number of CUDA devices with compute capability 10.x; 0 when there is none. */
 int pmlb_device_count(void);
+
+/* Debugging aid: while `device_buffer` (4 * 2048 * 3 int64, zero-filled by the caller) is
+ * set, CTA 0 of every tensor-core launch logs {tile, event, clock64} records of its producer,
+ * MMA and epilogue warps to it.  NULL (the default) turns logging off. */
+void pmlb_debug_set_trace(void* device_buffer);
 
 typedef struct pmlb_plan pmlb_plan;
 
@@ -115,6 +121,9 @@ typedef struct {
  * matrix (an "MN-major" tensor-core operand).  This flag makes the plan transpose B into
  * [n][k] scratch first and run the K-major kernel instead. */
 #define PMLB_GEMM_TRANSPOSE_B 1
+/* Take the epilogue that serves outputs whose rows are not 16-byte aligned even when the
+ * staged TMA-store epilogue would apply (for testing that path). */
+#define PMLB_GEMM_PLAIN_STORES 2
 
 pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* desc, pmlb_plan** plan);
 

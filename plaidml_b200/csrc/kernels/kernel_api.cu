@@ -65,6 +65,10 @@ bool have_sm100(std::string* why) {
   return true;
 }
 
+// Debugging aid (see pmlb_debug_set_trace): device buffer that CTA 0 of the next tensor-core
+// launches logs its pipeline timeline to.
+long long* g_trace_buffer = nullptr;
+
 enum PlanKind { kPlanGemm, kPlanConv, kPlanReduce, kPlanPool, kPlanContract, kPlanEltwise };
 
 }  // namespace
@@ -179,6 +183,10 @@ int pmlb_device_count(void) {
   return good;
 }
 
+void pmlb_debug_set_trace(void* device_buffer) {
+  g_trace_buffer = static_cast<long long*>(device_buffer);
+}
+
 void pmlb_plan_free(pmlb_plan* plan) {
   if (!plan) return;
   if (plan->scratch) cudaFree(plan->scratch);
@@ -235,6 +243,9 @@ pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* d, pmlb_plan** out) {
     }
   } else {
     return fail(PMLB_ERR_UNSUPPORTED, "gemm: input type must be f32, bf16, f16 or int8");
+  }
+  if ((d->epilogue & PMLB_EPI_ROWMAX) && (d->epilogue & ~PMLB_EPI_ROWMAX)) {
+    return fail(PMLB_ERR_UNSUPPORTED, "gemm: row max cannot be combined with other epilogue steps");
   }
   const int eb = elem_bytes_of(in);
   const long long min_lda = d->k;
@@ -315,6 +326,8 @@ pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream_v, const void* a, con
   L.rowmax = rowmax;
   L.status = plan->status;
   L.bn_override = d.tile_n;
+  L.force_slow_epilogue = (d.flags & PMLB_GEMM_PLAIN_STORES) != 0;
+  L.trace = g_trace_buffer;
 
   if (plan->split) {
     const long long kp = plan->kpad;

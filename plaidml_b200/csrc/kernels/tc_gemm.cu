@@ -7,13 +7,25 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
 
 #include "tc_gemm_kernel.cuh"
+#include "tc_instances.h"
 
 namespace pmlb {
+
+// every instance is compiled in one of the tc_inst_*.cu files
+#define PMLB_TC_EXTERN(EB, BN, NS, IM, MN, OB, G)                                              \
+  extern template cudaError_t launch_cfg<TcCfg<EB, BN, NS, IM, MN, OB, G>>(                     \
+      const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,          \
+      const CUtensorMap&, const TcParams&, int, cudaStream_t);
+PMLB_TC_LIST_H16(PMLB_TC_EXTERN, 1)
+PMLB_TC_LIST_H16(PMLB_TC_EXTERN, 2)
+PMLB_TC_LIST_MISC(PMLB_TC_EXTERN)
+#undef PMLB_TC_EXTERN
 
 namespace {
 
@@ -107,19 +119,26 @@ uint32_t make_idesc(int eb, bool is_f16, bool b_mn, int bn) {
   return d;
 }
 
-template <class Cfg>
-cudaError_t launch_cfg(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
-                       const CUtensorMap& b1, const TcParams& p, int grid, cudaStream_t stream) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  // The attribute is per device; set it on every call (cheap) rather than once.
-  (void)once;
-  attr_err = cudaFuncSetAttribute(tc_contract_kernel<Cfg>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-  if (attr_err != cudaSuccess) return attr_err;
-  tc_contract_kernel<Cfg><<<grid, 192, Cfg::SMEM_BYTES, stream>>>(a0, a1, b0, b1, p);
-  return cudaGetLastError();
+int out_bytes_of(int dtype) {
+  switch (dtype) {
+    case kDtF32:
+    case kDtI32: return 4;
+    case kDtBF16:
+    case kDtF16: return 2;
+    default: return 1;
+  }
 }
+
+CUtensorMapDataType out_map_dtype(int dtype) {
+  switch (dtype) {
+    case kDtF32: return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    case kDtI32: return CU_TENSOR_MAP_DATA_TYPE_INT32;
+    case kDtF16: return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    default: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int pick_bn(const TcLaunch& L, int num_sms) {
   if (L.bn_override == 64 || L.bn_override == 128 || L.bn_override == 256) return L.bn_override;
@@ -201,10 +220,12 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   p.res_batch = L.res_batch_stride;
   p.rowmax = L.rowmax;
   p.status = L.status;
+  p.trace = L.trace;
   p.idesc = make_idesc(eb, L.is_f16, L.b_mn, bn);
 
   const CUtensorMapDataType dt = map_dtype(eb, L.is_f16);
-  CUtensorMap ta0, ta1, tb0, tb1;
+  CUtensorMap ta0, ta1, tb0, tb1, tc_map;
+  std::memset(&tc_map, 0, sizeof(tc_map));
   std::memset(&ta0, 0, sizeof(ta0));
   std::memset(&ta1, 0, sizeof(ta1));
   std::memset(&tb0, 0, sizeof(tb0));
@@ -309,6 +330,33 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     }
   }
 
+  // Staged TMA-store epilogue when every output (and residual) row starts on a 16-byte
+  // boundary; otherwise the kernel's transpose-and-store path.
+  const int ob = out_bytes_of(L.out_dtype);
+  const int ob_tmpl = (eb == 2 && ob == 2) ? 2 : 4;
+  {
+    bool fast = (ob == 2 || ob == 4) && ob == ob_tmpl;
+    if (L.out != nullptr) {
+      fast = fast && aligned16(L.out) && (L.ldc * ob) % 16 == 0 &&
+             (L.batch == 1 || (L.out_batch_stride * ob) % 16 == 0);
+    }
+    if (L.epi_flags & kEpiResidual) {
+      fast = fast && aligned16(L.residual) && (L.ldr * ob) % 16 == 0 &&
+             (L.batch == 1 || (L.res_batch_stride * ob) % 16 == 0);
+    }
+    if (L.epi_flags & kEpiBias) fast = fast && aligned16(L.bias);
+    if (L.force_slow_epilogue) fast = false;
+    if (fast && L.out != nullptr) {
+      const uint64_t c_bs = L.batch > 1 ? static_cast<uint64_t>(L.out_batch_stride) * ob
+                                        : static_cast<uint64_t>(L.ldc) * ob * L.m;
+      if (!encode3d(&tc_map, out_map_dtype(L.out_dtype), ob, L.out, L.n, L.m, L.batch,
+                    static_cast<uint64_t>(L.ldc) * ob, c_bs, 128 / ob, 32, 1, err)) {
+        return 1;
+      }
+    }
+    p.fast_epi = fast ? 1 : 0;
+  }
+
   const long long total = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n;
   if (total > 0x7fffffffLL) {
     *err = "too many tiles";
@@ -318,30 +366,31 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   if (L.grid_override > 0) grid = std::min<long long>(total, L.grid_override);
 
   cudaError_t ce = cudaErrorInvalidValue;
-#define PMLB_TC_CASE(EB, BN, NS, IM, MN)                                               \
-  if (eb == EB && bn == BN && L.nsplit == NS && (L.conv != nullptr) == IM && L.b_mn == MN) { \
-    ce = launch_cfg<TcCfg<EB, BN, NS, IM, MN>>(ta0, ta1, tb0, tb1, p, grid, stream);    \
-  } else
-  PMLB_TC_CASE(2, 64, 1, false, false)
-  PMLB_TC_CASE(2, 128, 1, false, false)
-  PMLB_TC_CASE(2, 256, 1, false, false)
-  PMLB_TC_CASE(2, 64, 1, false, true)
-  PMLB_TC_CASE(2, 128, 1, false, true)
-  PMLB_TC_CASE(2, 256, 1, false, true)
-  PMLB_TC_CASE(2, 64, 1, true, false)
-  PMLB_TC_CASE(2, 128, 1, true, false)
-  PMLB_TC_CASE(2, 256, 1, true, false)
-  PMLB_TC_CASE(1, 64, 1, false, false)
-  PMLB_TC_CASE(1, 128, 1, false, false)
-  PMLB_TC_CASE(1, 256, 1, false, false)
-  PMLB_TC_CASE(1, 128, 1, false, true)
-  PMLB_TC_CASE(1, 256, 1, false, true)
-  PMLB_TC_CASE(4, 64, 2, false, false)
-  PMLB_TC_CASE(4, 128, 2, false, false) {
+  // Two epilogue groups when the main loop of a tile is short next to its epilogue.
+  int groups = p.num_kb <= 24 ? 2 : 1;
+  if (L.epi_groups_override == 1 || L.epi_groups_override == 2) groups = L.epi_groups_override;
+  if (const char* env = std::getenv("PMLB_TC_EPI_GROUPS")) {
+    if (env[0] == '1' || env[0] == '2') groups = env[0] - '0';
+  }
+  bool launched = false;
+#define PMLB_TC_CASE(EB, BN, NS, IM, MN, OB, G)                                                 \
+  if (!launched && eb == EB && bn == BN && L.nsplit == NS && (L.conv != nullptr) == IM &&       \
+      L.b_mn == MN && ob_tmpl == OB && groups == G) {                                           \
+    ce = launch_cfg<TcCfg<EB, BN, NS, IM, MN, OB, G>>(ta0, ta1, tb0, tb1, tc_map, p, grid,      \
+                                                     stream);                                   \
+    launched = true;                                                                            \
+  }
+  for (int attempt = 0; attempt < 2 && !launched; ++attempt) {
+    PMLB_TC_LIST_H16(PMLB_TC_CASE, 1)
+    PMLB_TC_LIST_H16(PMLB_TC_CASE, 2)
+    PMLB_TC_LIST_MISC(PMLB_TC_CASE)
+    if (!launched) groups = 1;  // not every shape has a two-group instance
+  }
+#undef PMLB_TC_CASE
+  if (!launched) {
     *err = "no kernel instance for this tile configuration";
     return 3;
   }
-#undef PMLB_TC_CASE
   if (ce != cudaSuccess) {
     *err = std::string("kernel launch failed: ") + cudaGetErrorString(ce);
     return 2;

@@ -51,8 +51,11 @@ struct TcParams {
   long long res_batch;
   float* rowmax;         // kEpiRowMax target, [batch * m]
 
+  int fast_epi;          // 1: staged TMA-store epilogue (needs 16-byte aligned output rows)
+
   uint32_t idesc;        // tcgen05 instruction descriptor
   int* status;           // device word: 0 = ok, otherwise the first error code seen
+  long long* trace;      // debugging: CTA 0 logs (role, tile, event, clock64) records here, or null
 };
 
 }  // namespace pmlb

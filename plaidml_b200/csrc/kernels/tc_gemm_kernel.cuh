@@ -5,9 +5,11 @@
 //                      128-byte-swizzled operand tiles (A by tiled or im2col TMA).
 //   warp 1 (one lane)  MMA issuer: tcgen05.mma from shared memory into one of two
 //                      TMEM accumulators, tcgen05.commit to hand stages back.
-//   warps 2..5         epilogue: tcgen05.ld the finished accumulator, transpose
-//                      through shared memory so that global stores are row-
-//                      contiguous, apply bias / residual / ReLU / cast, store.
+//   warps 2..5         epilogue: tcgen05.ld the finished accumulator, apply bias /
+//                      residual / ReLU / cast in registers, stage 32 rows x 128
+//                      bytes in swizzled shared memory and hand them to a TMA
+//                      store (outputs whose rows are not 16-byte aligned take a
+//                      slower path through a shared-memory transpose).
 // The second accumulator lets the epilogue of tile i overlap the main loop of
 // tile i+1.
 //
@@ -25,8 +27,16 @@
 
 namespace pmlb {
 
-template <int EB, int BN_, int NSPLIT_, bool A_IM2COL_, bool B_MN_>
+template <int EB, int BN_, int NSPLIT_, bool A_IM2COL_, bool B_MN_, int OUT_BYTES_ = 4,
+          int EPI_GROUPS_ = 1>
 struct TcCfg {
+  // 1: four epilogue warps drain both TMEM accumulators in turn (TMEM loads software-
+  //    pipelined); 2: eight warps, one group of four per accumulator, for shapes whose main
+  //    loop per tile is shorter than the epilogue (small K).
+  static constexpr int EPI_GROUPS = EPI_GROUPS_;
+  static constexpr int THREADS = 64 + 128 * EPI_GROUPS_;
+  static constexpr int OUT_BYTES = OUT_BYTES_;  // element size the staged epilogue packs to
+  static constexpr int CW = 128 / OUT_BYTES_;   // output columns per 128-byte staged row
   static constexpr int BM = 128;
   static constexpr int BN = BN_;
   static constexpr int NSPLIT = NSPLIT_;
@@ -37,11 +47,12 @@ struct TcCfg {
   static constexpr int A_TILE = BM * 128;   // bytes
   static constexpr int B_TILE = BN * 128;   // bytes
   static constexpr int STAGE = NSPLIT * (A_TILE + B_TILE);
-  static constexpr int RING_BUDGET = 196 * 1024;
+  static constexpr int STG_BYTES = EPI_GROUPS_ * 4 * 2 * 4096;  // per epilogue warp: two 32-row x 128-byte buffers
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_LIMIT = 232448;                     // 227 KB per CTA
+  static constexpr int RING_BUDGET = SMEM_LIMIT - 1024 - STG_BYTES - BAR_BYTES;
   static constexpr int STAGES_RAW = RING_BUDGET / STAGE;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int STG_BYTES = 4 * 32 * 33 * 4;  // per-warp 32x33 f32 transpose pads
-  static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE + STG_BYTES + BAR_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;            // 128, 256 or 512
   static constexpr int KIND = EB == 2 ? kMmaF16 : (EB == 4 ? kMmaTf32 : kMmaI8);
@@ -100,6 +111,20 @@ __device__ __forceinline__ void epilogue_store(const TcParams& p, long long out_
   }
 }
 
+// Pipeline timeline for debugging: CTA 0 appends {tile, event, clock64} triples to one of four
+// lanes of the trace buffer (0 producer, 1 MMA issuer, 2 and 3 the first warp of each epilogue
+// group).  A null trace pointer (the normal case) costs one predictable branch per event.
+constexpr int kTraceRecords = 2048;
+__device__ __forceinline__ void trace_event(const TcParams& p, int role, int& n, int tile, int ev) {
+  if (p.trace != nullptr && blockIdx.x == 0 && n < kTraceRecords) {
+    long long* r = p.trace + (static_cast<long long>(role) * kTraceRecords + n) * 3;
+    r[0] = tile;
+    r[1] = ev;
+    r[2] = clock64();
+    ++n;
+  }
+}
+
 struct TileCoord {
   int b, tm, tn;
 };
@@ -119,12 +144,159 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int t) {
   return c;
 }
 
+// Epilogue arithmetic on one staged chunk: CW accumulator columns of this thread's row.
+// FULL: the chunk lies wholly inside the matrix, so no per-column guards are needed and
+// bias / residual come in 16-byte loads.  The guarded variant serves the last chunk of
+// a ragged N.
+template <bool FULL, bool IS_INT, int OB, int CW>
+__device__ __forceinline__ float epi_apply(const TcParams& p, uint32_t (&v)[CW], int col0, int row,
+                                           long long res_row, bool out_bf16) {
+  const int nvalid = FULL ? CW : (p.n - col0);
+  const bool want_res = (p.epi_flags & kEpiResidual) && row < p.m;
+  float chunk_best = -INFINITY;
+  if constexpr (IS_INT) {
+    // 32-bit integer results (OB == 4)
+    if (p.epi_flags & kEpiBias) {
+      const int* bp = static_cast<const int*>(p.bias) + col0;
+      if constexpr (FULL) {
+#pragma unroll
+        for (int i = 0; i < CW / 4; ++i) {
+          const int4 b4 = __ldg(reinterpret_cast<const int4*>(bp) + i);
+          v[4 * i + 0] += static_cast<uint32_t>(b4.x);
+          v[4 * i + 1] += static_cast<uint32_t>(b4.y);
+          v[4 * i + 2] += static_cast<uint32_t>(b4.z);
+          v[4 * i + 3] += static_cast<uint32_t>(b4.w);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < CW; ++j) {
+          if (j < nvalid) v[j] += static_cast<uint32_t>(__ldg(bp + j));
+        }
+      }
+    }
+    if (want_res) {
+      const int* rp = static_cast<const int*>(p.residual) + res_row + col0;
+      if constexpr (FULL) {
+#pragma unroll
+        for (int i = 0; i < CW / 4; ++i) {
+          const int4 r4 = __ldg(reinterpret_cast<const int4*>(rp) + i);
+          v[4 * i + 0] += static_cast<uint32_t>(r4.x);
+          v[4 * i + 1] += static_cast<uint32_t>(r4.y);
+          v[4 * i + 2] += static_cast<uint32_t>(r4.z);
+          v[4 * i + 3] += static_cast<uint32_t>(r4.w);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < CW; ++j) {
+          if (j < nvalid) v[j] += static_cast<uint32_t>(rp[j]);
+        }
+      }
+    }
+    if (p.epi_flags & kEpiRelu) {
+#pragma unroll
+      for (int j = 0; j < CW; ++j) v[j] = static_cast<uint32_t>(max(static_cast<int>(v[j]), 0));
+    }
+  } else {
+    if (p.epi_flags & kEpiBias) {
+      const float* bp = static_cast<const float*>(p.bias) + col0;
+      if constexpr (FULL) {
+#pragma unroll
+        for (int i = 0; i < CW / 4; ++i) {
+          const float4 b4 = __ldg(reinterpret_cast<const float4*>(bp) + i);
+          v[4 * i + 0] = __float_as_uint(__uint_as_float(v[4 * i + 0]) + b4.x);
+          v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + b4.y);
+          v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + b4.z);
+          v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + b4.w);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < CW; ++j) {
+          if (j < nvalid) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldg(bp + j));
+        }
+      }
+    }
+    if (want_res) {
+      if constexpr (FULL) {
+        const uint4* rp = reinterpret_cast<const uint4*>(
+            static_cast<const char*>(p.residual) + (res_row + col0) * OB);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 r4 = __ldg(rp + i);
+          const uint32_t w[4] = {r4.x, r4.y, r4.z, r4.w};
+          if constexpr (OB == 4) {
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              v[4 * i + h] = __float_as_uint(__uint_as_float(v[4 * i + h]) + __uint_as_float(w[h]));
+            }
+          } else {
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              float r0, r1;
+              if (out_bf16) {
+                r0 = __uint_as_float(w[h] << 16);
+                r1 = __uint_as_float(w[h] & 0xffff0000u);
+              } else {
+                const __half2 hh = *reinterpret_cast<const __half2*>(&w[h]);
+                r0 = __low2float(hh);
+                r1 = __high2float(hh);
+              }
+              const int j = 8 * i + 2 * h;
+              v[j] = __float_as_uint(__uint_as_float(v[j]) + r0);
+              v[j + 1] = __float_as_uint(__uint_as_float(v[j + 1]) + r1);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < CW; ++j) {
+          if (j < nvalid) {
+            float r;
+            if constexpr (OB == 4) {
+              r = static_cast<const float*>(p.residual)[res_row + col0 + j];
+            } else if (out_bf16) {
+              r = __bfloat162float(static_cast<const __nv_bfloat16*>(p.residual)[res_row + col0 + j]);
+            } else {
+              r = __half2float(static_cast<const __half*>(p.residual)[res_row + col0 + j]);
+            }
+            v[j] = __float_as_uint(__uint_as_float(v[j]) + r);
+          }
+        }
+      }
+    }
+    if (p.epi_flags & kEpiRelu) {
+#pragma unroll
+      for (int j = 0; j < CW; ++j) {
+        const float x = __uint_as_float(v[j]);
+        v[j] = __float_as_uint(x < 0.f ? 0.f : x);
+      }
+    }
+    if (p.epi_flags & kEpiRowMax) {
+      // Balanced tree of hardware max operations.  For non-NaN values this equals the
+      // compare-and-select chain of the definition; with NaNs the definition itself
+      // depends on the visiting order.
+      float mx[CW];
+#pragma unroll
+      for (int j = 0; j < CW; ++j) {
+        mx[j] = (FULL || j < nvalid) ? __uint_as_float(v[j]) : -INFINITY;
+      }
+#pragma unroll
+      for (int w = CW / 2; w > 0; w >>= 1) {
+#pragma unroll
+        for (int j = 0; j < w; ++j) mx[j] = fmaxf(mx[j], mx[j + w]);
+      }
+      chunk_best = mx[0];
+    }
+  }
+  return chunk_best;
+}
+
 template <class Cfg>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
 tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
                    const __grid_constant__ CUtensorMap tm_a1,
                    const __grid_constant__ CUtensorMap tm_b0,
                    const __grid_constant__ CUtensorMap tm_b1,
+                   const __grid_constant__ CUtensorMap tm_c,
                    const __grid_constant__ TcParams p) {
   constexpr int BN = Cfg::BN;
   constexpr int BK = Cfg::BK;
@@ -187,6 +359,7 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int ntrace = 0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const TileCoord tc = tile_coord(p, t);
         int pix_w = 0, pix_h = 0, pix_n = 0;
@@ -206,6 +379,7 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
             ok = false;
             break;
           }
+          trace_event(p, 0, ntrace, t, kb);
           const uint32_t fb = full_bar(stage);
           mbar_arrive_expect_tx(fb, Cfg::STAGE);
           const uint32_t s_a = ring + stage * Cfg::STAGE;
@@ -253,11 +427,14 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      int ntrace = 0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        trace_event(p, 1, ntrace, t, 0);
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
           if (*abort_code == 0) *abort_code = 2;
           break;
         }
+        trace_event(p, 1, ntrace, t, 1);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < p.num_kb; ++kb) {
@@ -267,6 +444,7 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
             break;
           }
           tc_fence_after_sync();
+          if (kb == 0) trace_event(p, 1, ntrace, t, 2);
           const uint32_t s_a = ring + stage * Cfg::STAGE;
           const uint32_t s_b = s_a + NSPLIT * Cfg::A_TILE;
 #pragma unroll
@@ -298,6 +476,7 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
         }
         if (!ok) break;
         tc_commit(tfull_bar(acc));
+        trace_event(p, 1, ntrace, t, 3);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;
@@ -307,70 +486,227 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
   } else {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;                     // TMEM lane quarter this warp may read
-    float* stg = stg_all + q * (32 * 33);
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      const TileCoord tc = tile_coord(p, t);
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
-        if (*abort_code == 0) *abort_code = 4;
-        break;
-      }
-      tc_fence_after_sync();
-      const int row0 = tc.tm * 128 + q * 32;     // first row of this warp
-      const int col_base = tc.tn * BN;
-      const uint32_t t_acc =
-          tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(q * 32) << 16);
-      const long long out_b = static_cast<long long>(tc.b) * p.out_batch;
-      const long long res_b = static_cast<long long>(tc.b) * p.res_batch;
-      float row_best = -INFINITY;
+    const int ew = warp - 2;                    // epilogue warp number
+    const int grp = ew >> 2;                    // epilogue group (accumulator owner when two)
+    constexpr int G = Cfg::EPI_GROUPS;
+    // Local tile number `it` selects the accumulator (it & 1) and its barrier phase
+    // ((it >> 1) & 1); with two groups, group g takes the tiles with (it & 1) == g.
+    if (p.fast_epi) {
+      constexpr int CW = Cfg::CW;
+      constexpr int OB = Cfg::OUT_BYTES;
+      const uint32_t stage_buf = smem_u32(stg_all) + static_cast<uint32_t>(ew) * 8192u;
+      uint32_t nbuf = 0;
+      const bool out_bf16 = p.out_dtype == kDtBF16;
+      int it = 0;
+      int ntrace = 0;
+      const bool tracer = (q == 2) && lane == 0;   // first warp of each group (warps 2 and 6)
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+        if (G == 2 && (it & 1) != grp) continue;
+        const int acc = it & 1;
+        const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
+        const TileCoord tc = tile_coord(p, t);
+        if (tracer) trace_event(p, 2 + grp, ntrace, t, 0);
+        if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+          if (*abort_code == 0) *abort_code = 4;
+          break;
+        }
+        if (tracer) trace_event(p, 2 + grp, ntrace, t, 1);
+        tc_fence_after_sync();
+        const int row0 = tc.tm * 128 + q * 32;
+        const int row = row0 + lane;
+        const int col_base = tc.tn * BN;
+        const uint32_t t_acc =
+            tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(q * 32) << 16);
+        const long long res_row =
+            static_cast<long long>(tc.b) * p.res_batch + static_cast<long long>(row) * p.ldr;
+        float row_best = -INFINITY;
 
-#pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
-        const int col0 = col_base + ch * 32;
-        uint32_t v[32];
-        tmem_ld_32x32(t_acc + ch * 32, v);
-        tmem_ld_wait();
-        if (ch == BN / 32 - 1) {
-          // accumulator fully read: hand it back before finishing the stores
+        constexpr int NCH = BN / CW;
+        auto issue_load = [&](uint32_t(&v)[CW], int ch) {
+          uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[0]);
+          tmem_ld_32x32(t_acc + ch * CW, lo);
+          if constexpr (CW == 64) {
+            uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[32]);
+            tmem_ld_32x32(t_acc + ch * CW + 32, hi);
+          }
+        };
+        // Pins the registers of a finished TMEM load behind the wait: the empty volatile asm
+        // statements cannot be moved above `tcgen05.wait::ld`, so neither can their users.
+        auto pin = [&](uint32_t(&v)[CW]) {
+#pragma unroll
+          for (int j = 0; j < CW; ++j) asm volatile("" : "+r"(v[j]));
+        };
+        auto release_acc = [&]() {
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(tempty_bar(acc));
-        }
-        if (col0 >= p.n) continue;   // warp-uniform
-        if (p.epi_flags & kEpiRowMax) {
-          if constexpr (!IS_INT) {
+        };
+        auto process = [&](uint32_t(&v)[CW], int ch) {
+          const int col0 = col_base + ch * CW;
+          if (col0 >= p.n) return;                    // warp-uniform
+          const float chunk_best =
+              (col0 + CW <= p.n)
+                  ? epi_apply<true, IS_INT, OB, CW>(p, v, col0, row, res_row, out_bf16)
+                  : epi_apply<false, IS_INT, OB, CW>(p, v, col0, row, res_row, out_bf16);
+          if (p.epi_flags & kEpiRowMax) row_best = fmaxf(row_best, chunk_best);
+          if (p.out == nullptr || row0 >= p.m) return;   // warp-uniform
+
+          uint4 o[8];
+          if constexpr (OB == 4) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float x = __uint_as_float(v[j]);
-              if (col0 + j < p.n && x > row_best) row_best = x;
+            for (int i = 0; i < 8; ++i) o[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              uint32_t w[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                const float x0 = __uint_as_float(v[8 * i + 2 * h]);
+                const float x1 = __uint_as_float(v[8 * i + 2 * h + 1]);
+                if (out_bf16) {
+                  const __nv_bfloat162 pk = __floats2bfloat162_rn(x0, x1);
+                  w[h] = *reinterpret_cast<const uint32_t*>(&pk);
+                } else {
+                  const __half2 pk = __floats2half2_rn(x0, x1);
+                  w[h] = *reinterpret_cast<const uint32_t*>(&pk);
+                }
+              }
+              o[i] = make_uint4(w[0], w[1], w[2], w[3]);
             }
           }
-          if (p.out == nullptr) continue;
-        }
+          // the buffer used two chunks ago must have been read by its TMA store
+          if (lane == 0) bulk_wait_group_read<1>();
+          __syncwarp();
+          const uint32_t buf = stage_buf + (nbuf & 1u) * 4096u;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = __uint_as_float(v[j]);
-        __syncwarp();
-        const int col = col0 + lane;
-        if (col < p.n) {
-          const int rows = min(32, p.m - row0);
-          for (int r = 0; r < rows; ++r) {
-            const long long row = row0 + r;
-            epilogue_store<IS_INT>(p, out_b + row * p.ldc + col, res_b + row * p.ldr + col, col,
-                                   __float_as_uint(stg[r * 33 + lane]));
+          for (int i = 0; i < 8; ++i) {
+            st_shared_v4(buf + lane * 128 + ((i ^ (lane & 7)) << 4), o[i]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tm_c, buf, col0, row0, tc.b);
+            bulk_commit_group();
+          }
+          ++nbuf;
+        };
+        // Two register sets: the TMEM load of chunk ch + 1 is in flight while chunk ch is
+        // converted, staged and stored.
+        if constexpr (G == 1) {
+          uint32_t va[CW], vb[CW];
+          issue_load(va, 0);
+#pragma unroll 1
+          for (int ch = 0; ch < NCH; ch += 2) {
+            tmem_ld_wait();
+            pin(va);
+            if (ch + 1 < NCH) issue_load(vb, ch + 1);
+            if (ch == NCH - 1) release_acc();
+            process(va, ch);
+            if (ch + 1 < NCH) {
+              tmem_ld_wait();
+              pin(vb);
+              if (ch + 2 < NCH) issue_load(va, ch + 2);
+              if (ch + 1 == NCH - 1) release_acc();
+              process(vb, ch + 1);
+            }
+          }
+        } else {
+          // two warps per scheduler hide each other's latencies; one register set suffices
+          uint32_t va[CW];
+#pragma unroll 1
+          for (int ch = 0; ch < NCH; ++ch) {
+            issue_load(va, ch);
+            tmem_ld_wait();
+            pin(va);
+            if (tracer) trace_event(p, 2 + grp, ntrace, t, 10 + ch);
+            if (ch == NCH - 1) release_acc();
+            process(va, ch);
+            if (tracer) trace_event(p, 2 + grp, ntrace, t, 30 + ch);
           }
         }
-        __syncwarp();
-      }
-      if (p.epi_flags & kEpiRowMax) {
-        const int row = row0 + lane;
-        if (row < p.m) {
-          atomic_max_float(p.rowmax + static_cast<long long>(tc.b) * p.m + row, row_best);
+        if (p.epi_flags & kEpiRowMax) {
+          if (row < p.m) {
+            atomic_max_float(p.rowmax + static_cast<long long>(tc.b) * p.m + row, row_best);
+          }
         }
       }
-      if (++acc == 2) {
-        acc = 0;
-        acc_phase ^= 1u;
+      // staged rows must be read out (and the writes done) before shared memory goes away
+      if (lane == 0) bulk_wait_group<0>();
+      __syncwarp();
+    } else {
+      float* stg = stg_all + ew * 2048;          // this warp's 8 KB, used as a 32 x 33 pad
+      int it = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+        if (G == 2 && (it & 1) != grp) continue;
+        const int acc = it & 1;
+        const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
+        const TileCoord tc = tile_coord(p, t);
+        if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+          if (*abort_code == 0) *abort_code = 4;
+          break;
+        }
+        tc_fence_after_sync();
+        const int row0 = tc.tm * 128 + q * 32;     // first row of this warp
+        const int col_base = tc.tn * BN;
+        const uint32_t t_acc =
+            tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(q * 32) << 16);
+        const long long out_b = static_cast<long long>(tc.b) * p.out_batch;
+        const long long res_b = static_cast<long long>(tc.b) * p.res_batch;
+        float row_best = -INFINITY;
+
+#pragma unroll 1
+        for (int ch = 0; ch < BN / 32; ++ch) {
+          const int col0 = col_base + ch * 32;
+          uint32_t v[32];
+          tmem_ld_32x32(t_acc + ch * 32, v);
+          tmem_ld_wait();
+          if (ch == BN / 32 - 1) {
+            // accumulator fully read: hand it back before finishing the stores
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+          }
+          if (col0 >= p.n) continue;   // warp-uniform
+          if ((p.epi_flags & kEpiRowMax) && p.out == nullptr) {
+            if constexpr (!IS_INT) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float x = __uint_as_float(v[j]);
+                if (col0 + j < p.n && x > row_best) row_best = x;
+              }
+            }
+            continue;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = __uint_as_float(v[j]);
+          __syncwarp();
+          const int col = col0 + lane;
+          if (col < p.n) {
+            const int rows = min(32, p.m - row0);
+            for (int r = 0; r < rows; ++r) {
+              const long long row = row0 + r;
+              epilogue_store<IS_INT>(p, out_b + row * p.ldc + col, res_b + row * p.ldr + col, col,
+                                     __float_as_uint(stg[r * 33 + lane]));
+            }
+          }
+          __syncwarp();
+          if (p.epi_flags & kEpiRowMax) {
+            // row max of what was stored: reread this warp's rows of the chunk
+            if constexpr (!IS_INT) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float x = __uint_as_float(v[j]);
+                if (col0 + j < p.n && x > row_best) row_best = x;
+              }
+            }
+          }
+        }
+        if (p.epi_flags & kEpiRowMax) {
+          const int row = row0 + lane;
+          if (row < p.m) {
+            atomic_max_float(p.rowmax + static_cast<long long>(tc.b) * p.m + row, row_best);
+          }
+        }
       }
     }
   }
@@ -396,6 +732,18 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
+}
+
+template <class Cfg>
+cudaError_t launch_cfg(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
+                       const CUtensorMap& b1, const CUtensorMap& c, const TcParams& p, int grid,
+                       cudaStream_t stream) {
+  // The attribute is per device, so it is set on every call (a cheap host-side update).
+  const cudaError_t attr_err = cudaFuncSetAttribute(
+      tc_contract_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+  if (attr_err != cudaSuccess) return attr_err;
+  tc_contract_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(a0, a1, b0, b1, c, p);
+  return cudaGetLastError();
 }
 
 }  // namespace pmlb

@@ -1,0 +1,37 @@
+// The instantiations of the tensor-core contraction kernel, as X-macro lists shared by the
+// files that compile them and the dispatcher that selects one.
+// X(element bytes, tile N, operand split, A by im2col, B stored [k][n], output bytes, epilogue groups)
+#pragma once
+
+#define PMLB_TC_LIST_H16(X, G)      \
+  X(2, 64, 1, false, false, 4, G)   \
+  X(2, 64, 1, false, false, 2, G)   \
+  X(2, 128, 1, false, false, 4, G)  \
+  X(2, 128, 1, false, false, 2, G)  \
+  X(2, 256, 1, false, false, 4, G)  \
+  X(2, 256, 1, false, false, 2, G)  \
+  X(2, 64, 1, false, true, 4, G)    \
+  X(2, 64, 1, false, true, 2, G)    \
+  X(2, 128, 1, false, true, 4, G)   \
+  X(2, 128, 1, false, true, 2, G)   \
+  X(2, 256, 1, false, true, 4, G)   \
+  X(2, 256, 1, false, true, 2, G)   \
+  X(2, 64, 1, true, false, 4, G)    \
+  X(2, 64, 1, true, false, 2, G)    \
+  X(2, 128, 1, true, false, 4, G)   \
+  X(2, 128, 1, true, false, 2, G)   \
+  X(2, 256, 1, true, false, 4, G)   \
+  X(2, 256, 1, true, false, 2, G)
+
+#define PMLB_TC_LIST_MISC(X)        \
+  X(1, 64, 1, false, false, 4, 1)   \
+  X(1, 128, 1, false, false, 4, 1)  \
+  X(1, 256, 1, false, false, 4, 1)  \
+  X(1, 128, 1, false, true, 4, 1)   \
+  X(1, 256, 1, false, true, 4, 1)   \
+  X(1, 64, 1, false, false, 4, 2)   \
+  X(1, 128, 1, false, false, 4, 2)  \
+  X(1, 128, 1, false, true, 4, 2)   \
+  X(4, 64, 2, false, false, 4, 1)   \
+  X(4, 128, 2, false, false, 4, 1)  \
+  X(4, 64, 2, false, false, 4, 2)

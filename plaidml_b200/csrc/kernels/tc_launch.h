@@ -47,9 +47,12 @@ struct TcLaunch {
   long long res_batch_stride = 0;
   float* rowmax = nullptr;
 
+  long long* trace = nullptr;  // debugging: device buffer of 4 * 2048 * 3 int64 for CTA 0's timeline
   int* status = nullptr;  // device word that receives a non-zero code if a wait times out
 
+  bool force_slow_epilogue = false;  // testing: take the transpose-and-store epilogue
   int bn_override = 0;    // 0 = choose; else 64, 128 or 256
+  int epi_groups_override = 0;  // 0 = choose; else 1 or 2
   int grid_override = 0;  // 0 = one CTA per SM
 };
 

@@ -19,6 +19,7 @@ AGG_NONE, AGG_SUM, AGG_MAX, AGG_MIN, AGG_PROD, AGG_ASSIGN = range(6)
 COMBO_NONE, COMBO_MUL, COMBO_ADD, COMBO_EQ, COMBO_COND = range(5)
 EPI_BIAS, EPI_RESIDUAL, EPI_RELU, EPI_ROWMAX = 1, 2, 4, 8
 GEMM_TRANSPOSE_B = 1
+GEMM_PLAIN_STORES = 2
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = range(5)
 
 MAX_IDX, MAX_RANK, MAX_CONS = 10, 8, 8

@@ -124,6 +124,50 @@ def test_bf16_bias_relu_bf16_out():
     check_close(as_f32(c), ref_bf16, 1e-2)
 
 
+def test_bf16_residual_partial_chunk_and_plain_stores():
+    # N = 200 leaves a partial 64-column chunk; the same case through the plain-store epilogue
+    g = rng(13)
+    m, n, k = 160, 200, 64
+    a = dev_bf16(g.standard_normal((2, m, k)))
+    b = dev_bf16(g.standard_normal((2, n, k)))
+    bias = dev(g.standard_normal(n).astype(np.float32))
+    res = dev_bf16(g.standard_normal((2, m, n)))
+    ref = oracle.gemm_h16_f32(bits16(a), bits16(b), False, True)
+    ref = ref + bias.cpu().numpy()[None, None, :] + as_f32(res)
+    ref = oracle.bf16_to_f32(oracle.f32_to_bf16(np.where(ref < 0, 0, ref)))
+    outs = []
+    for flags in (0, K.GEMM_PLAIN_STORES):
+        c, _, _ = run_gemm(K.BF16, K.BF16, a, b, m, n, k, batch=2, flags=flags,
+                           epilogue=K.EPI_BIAS | K.EPI_RESIDUAL | K.EPI_RELU, bias=bias, residual=res)
+        check_close(as_f32(c), ref, 1e-2)
+        outs.append(bits16(c))
+    np.testing.assert_array_equal(outs[0], outs[1])   # both epilogues round identically
+
+
+def test_f32_out_residual_f32():
+    g = rng(14)
+    m, n, k = 256, 128, 64
+    a = dev_bf16(g.standard_normal((1, m, k)))
+    b = dev_bf16(g.standard_normal((1, n, k)))
+    res = dev(g.standard_normal((1, m, n)).astype(np.float32))
+    c, _, _ = run_gemm(K.BF16, K.F32, a, b, m, n, k, epilogue=K.EPI_RESIDUAL, residual=res)
+    ref = oracle.gemm_h16_f32(bits16(a), bits16(b), False, True) + res.cpu().numpy()
+    check_close(c.cpu().numpy(), ref, 1e-4)
+
+
+def test_int8_bias_relu_residual_exact():
+    g = rng(15)
+    m, n, k = 256, 160, 128
+    a = g.integers(-128, 128, size=(1, m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(1, n, k), dtype=np.int8)
+    bias = g.integers(-1000, 1000, size=n, dtype=np.int32)
+    res = g.integers(-100000, 100000, size=(1, m, n), dtype=np.int32)
+    c, _, _ = run_gemm(K.I8, K.I32, dev(a), dev(b), m, n, k, bias=dev(bias), residual=dev(res),
+                       epilogue=K.EPI_BIAS | K.EPI_RESIDUAL | K.EPI_RELU)
+    ref = oracle.gemm_i8_i32(a, b, True) + bias[None, None, :] + res
+    np.testing.assert_array_equal(c.cpu().numpy(), np.maximum(ref, 0))
+
+
 def test_f16_nt():
     g = rng(11)
     m, n, k = 128, 128, 128
