@@ -89,6 +89,11 @@ size_t pmlb_plan_scratch_bytes(const pmlb_plan* plan);
  * error since the last check (a bounded wait that expired): PMLB_OK or PMLB_ERR_TIMEOUT. */
 pmlb_status pmlb_plan_check(pmlb_plan* plan, void* stream);
 
+/* Makes the plan record device-side errors in `device_word` (an int in device memory owned by
+ * the caller, zero-initialised) instead of its own word, so that one readback covers many
+ * plans.  pmlb_plan_check then reads that word. */
+pmlb_status pmlb_plan_share_status(pmlb_plan* plan, int* device_word);
+
 /* Name of the kernel family a plan resolved to ("tc_gemm", "tc_conv", "row_reduce", ...). */
 const char* pmlb_plan_kind(const pmlb_plan* plan);
 

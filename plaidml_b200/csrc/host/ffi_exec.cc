@@ -1,0 +1,69 @@
+// C ABI: devices, JIT and run.  Reference counterparts: plaidml/exec/ffi.cc:42-123.
+#include <mutex>
+
+#include "pml_exec.h"
+
+using pml::ffiWrap;
+using pml::ffiWrapVoid;
+
+extern "C" {
+
+void plaidml_exec_init(plaidml_error* err) {
+  ffiWrapVoid(err, [&] {});
+}
+
+plaidml_strings* plaidml_devices_get(plaidml_error* err) {
+  return ffiWrap<plaidml_strings*>(err, nullptr, [&] {
+    std::vector<plaidml_string*> out;
+    for (const std::string& d : pml::listDevices()) out.push_back(new plaidml_string{d});
+    return pml::makeList<plaidml_strings, plaidml_string*>(out);
+  });
+}
+
+plaidml_executable* plaidml_jit(plaidml_error* err, plaidml_program* program, const char* raw_device) {
+  return ffiWrap<plaidml_executable*>(err, nullptr, [&] {
+    std::string device(raw_device ? raw_device : "");
+    if (device.empty()) device = pml::Settings::instance().get("PLAIDML_DEVICE");
+    if (!program->program->compiled) {
+      throw std::runtime_error("Program must be compiled (plaidml_program_compile) before plaidml_jit");
+    }
+    const int index = pml::parseDeviceId(device);
+    return new plaidml_executable{std::make_shared<pml::Executable>(program->program, index)};
+  });
+}
+
+void plaidml_executable_free(plaidml_error* err, plaidml_executable* exec) {
+  ffiWrapVoid(err, [&] { delete exec; });
+}
+
+double plaidml_executable_run(plaidml_error* err, plaidml_executable* exec, size_t ninputs, plaidml_buffer** inputs,
+                              size_t noutputs, plaidml_buffer** outputs) {
+  return ffiWrap<double>(err, 0.0, [&] {
+    std::vector<pml::BufferPtr> ins, outs;
+    for (size_t i = 0; i < ninputs; ++i) ins.push_back(inputs[i]->buffer);
+    for (size_t i = 0; i < noutputs; ++i) outs.push_back(outputs[i]->buffer);
+    return exec->exec->run(ins, outs);
+  });
+}
+
+plaidml_string* pmlb_exec_describe(plaidml_error* err, plaidml_executable* exec) {
+  return ffiWrap<plaidml_string*>(err, nullptr, [&] { return new plaidml_string{exec->exec->describe()}; });
+}
+
+size_t pmlb_exec_launch_count(plaidml_error* err, plaidml_executable* exec) {
+  return ffiWrap<size_t>(err, 0, [&] { return exec->exec->launchCount(); });
+}
+
+double pmlb_exec_run_resident(plaidml_error* err, plaidml_executable* exec, size_t iters) {
+  return ffiWrap<double>(err, 0.0, [&] { return exec->exec->runResident(iters); });
+}
+
+void* pmlb_exec_output_device_ptr(plaidml_error* err, plaidml_executable* exec, size_t index, size_t* nbytes) {
+  return ffiWrap<void*>(err, nullptr, [&] { return exec->exec->outputDevicePtr(index, nbytes); });
+}
+
+void* pmlb_exec_stream(plaidml_error* err, plaidml_executable* exec) {
+  return ffiWrap<void*>(err, nullptr, [&] { return static_cast<void*>(exec->exec->stream()); });
+}
+
+}  // extern "C"

@@ -1,0 +1,789 @@
+// The operation library: plaidml_op_make(name, args) builds EDSL expressions for named
+// tensor operations.  Reference counterpart: plaidml/op/lib/ops.cc (argument conventions per
+// operation are cited below); the registry there is plaidml/op/lib/ops.cc:3632-3680.
+//
+// Scope: the operations that build the contraction path's networks and tests -- convolution
+// (forward, ungrouped), pool, dot, relu, mean / sum / max / min / prod, softmax -- plus the
+// thin element-wise and layout ones that cost a few lines each.
+#include <functional>
+#include <map>
+#include <set>
+
+#include "pml_ast.h"
+
+using pml::ExprNode;
+using pml::ExprPtr;
+using pml::PolyPtr;
+using pml::VarNode;
+using pml::VarPtr;
+
+namespace {
+
+// ------------------------------------------------------------------ small builder layer
+
+pml::TensorShape shapeOf(const ExprPtr& e) {
+  pml::Evaluator local;
+  return local.getShape(e);
+}
+
+PolyPtr newIndex(const std::string& name = "") {
+  auto p = std::make_shared<pml::PolyNode>();
+  p->kind = pml::PolyNode::Index;
+  p->name = name;
+  return p;
+}
+
+PolyPtr polyLit(int64_t v) {
+  auto p = std::make_shared<pml::PolyNode>();
+  p->kind = pml::PolyNode::Literal;
+  p->value = v;
+  return p;
+}
+
+PolyPtr polyOp(pml::AffineOp op, PolyPtr a, PolyPtr b) {
+  auto p = std::make_shared<pml::PolyNode>();
+  p->kind = pml::PolyNode::Op;
+  p->op = op;
+  p->operands = {std::move(a), std::move(b)};
+  return p;
+}
+PolyPtr operator+(PolyPtr a, PolyPtr b) { return polyOp(pml::AffineOp::Add, std::move(a), std::move(b)); }
+PolyPtr operator-(PolyPtr a, PolyPtr b) { return polyOp(pml::AffineOp::Sub, std::move(a), std::move(b)); }
+PolyPtr operator*(int64_t a, PolyPtr b) { return polyOp(pml::AffineOp::Mul, polyLit(a), std::move(b)); }
+PolyPtr operator+(PolyPtr a, int64_t b) { return std::move(a) + polyLit(b); }
+PolyPtr operator-(PolyPtr a, int64_t b) { return std::move(a) - polyLit(b); }
+
+struct Operand {
+  ExprPtr tensor;
+  std::vector<PolyPtr> idxs;
+};
+
+struct Cons {
+  PolyPtr lhs;
+  int64_t rhs;
+};
+
+ExprPtr contraction(pml::AggKind agg, pml::ComboKind combo, const std::vector<int64_t>& dims,
+                    const std::vector<PolyPtr>& idxs, const std::vector<Operand>& srcs,
+                    const std::vector<Cons>& cons = {}, const std::string& name = "") {
+  auto node = std::make_shared<ExprNode>(ExprNode::Contraction);
+  node->name = name;
+  node->agg = agg;
+  node->combo = combo;
+  for (size_t i = 0; i < dims.size(); ++i) {
+    node->sinkDims.push_back(pml::makeDimLiteral(dims[i]));
+    node->sinkIdxs.push_back(idxs[i]);
+  }
+  for (const Operand& o : srcs) node->srcs.push_back({o.tensor, o.idxs});
+  for (const Cons& c : cons) node->constraints.push_back({c.lhs, pml::makeDimLiteral(c.rhs)});
+  pml::Evaluator local;
+  local.verify(node);
+  return node;
+}
+
+ExprPtr intrinsic(const std::string& fn, const std::vector<ExprPtr>& args, const std::string& name = "") {
+  auto node = std::make_shared<ExprNode>(ExprNode::Intrinsic);
+  node->op = fn;
+  node->name = name;
+  node->operands = args;
+  pml::Evaluator local;
+  local.verify(node);
+  return node;
+}
+
+ExprPtr litInt(int64_t v) {
+  auto node = std::make_shared<ExprNode>(ExprNode::ConstSigned);
+  node->ivalue = v;
+  return node;
+}
+
+ExprPtr litFloat(double v) {
+  auto node = std::make_shared<ExprNode>(ExprNode::ConstFloat);
+  node->fvalue = v;
+  return node;
+}
+
+ExprPtr castTo(const ExprPtr& e, pml::DType dt) {
+  auto node = std::make_shared<ExprNode>(ExprNode::Cast);
+  node->dtype = dt;
+  node->expr = e;
+  return node;
+}
+
+ExprPtr reshapeTo(const ExprPtr& e, const std::vector<int64_t>& dims) {
+  std::vector<ExprPtr> args = {e};
+  for (int64_t d : dims) args.push_back(litInt(d));
+  return intrinsic("reshape", args);
+}
+
+// ------------------------------------------------------------------ argument access
+
+VarPtr exprValue(const ExprPtr& e) {
+  auto v = std::make_shared<VarNode>();
+  v->kind = VarNode::Expr;
+  v->expr = e;
+  return v;
+}
+
+const std::vector<VarPtr>& asTuple(const VarPtr& v, const char* what) {
+  if (v->kind != VarNode::Tuple) throw std::runtime_error(std::string(what) + ": expected a tuple");
+  return v->tuple;
+}
+
+ExprPtr asTensor(const VarPtr& v) {
+  switch (v->kind) {
+    case VarNode::Expr: return v->expr;
+    case VarNode::Int: return litInt(v->i);
+    case VarNode::Float: return litFloat(v->f);
+    case VarNode::Dim: {
+      auto node = std::make_shared<ExprNode>(ExprNode::Dim);
+      node->dim = v->dim;
+      return node;
+    }
+    default: throw std::runtime_error("Expected a tensor argument");
+  }
+}
+
+int64_t asInt(const VarPtr& v) {
+  if (v->kind == VarNode::Int) return v->i;
+  if (v->kind == VarNode::Dim) {
+    pml::Evaluator local;
+    return local.evaluate(v->dim);
+  }
+  throw std::runtime_error("Expected an integer argument");
+}
+
+bool asBool(const VarPtr& v) { return asInt(v) != 0; }
+
+std::string asStr(const VarPtr& v) {
+  if (v->kind == VarNode::Str) return v->s;
+  if (v->kind == VarNode::None) return "";
+  throw std::runtime_error("Expected a string argument");
+}
+
+std::vector<int64_t> asIntTuple(const VarPtr& v) {
+  std::vector<int64_t> out;
+  if (v->kind == VarNode::None) return out;
+  for (const VarPtr& e : asTuple(v, "integer tuple")) out.push_back(asInt(e));
+  return out;
+}
+
+int64_t normalizeAxis(int64_t axis, size_t ndims, const char* op) {
+  const int64_t a = axis < 0 ? axis + static_cast<int64_t>(ndims) : axis;
+  if (a < 0 || a >= static_cast<int64_t>(ndims)) {
+    throw std::runtime_error(std::string("Axis out of range for ") + op + " op (axis " + std::to_string(axis) +
+                             " requested for tensors with " + std::to_string(ndims) + " dimensions)");
+  }
+  return a;
+}
+
+enum AutoPad { kPadExplicit = 0, kPadSameLower = 1, kPadSameUpper = 2, kPadValid = 3 };
+enum Layout { kNXC = 0, kNCX = 1, kKCX = 2, kXCK = 3 };
+enum PoolMode { kPoolAvg = 0, kPoolMax = 1, kPoolMin = 2, kPoolSum = 3 };
+
+// plaidml/op/lib/ops.cc:347-382
+void paddingAndOutput(int64_t in, int64_t filter, int64_t stride, int autopad, int64_t padLo, int64_t padHi,
+                      int64_t dilation, int64_t dataDilation, bool ceilMode, int64_t* padBefore, int64_t* out) {
+  const int64_t iEff = dataDilation * (in - 1) + 1;
+  const int64_t fEff = dilation * (filter - 1) + 1;
+  const int64_t ceilTerm = ceilMode ? stride - 1 : 0;
+  switch (autopad) {
+    case kPadExplicit:
+      *padBefore = padLo;
+      *out = (iEff + padLo + padHi - fEff + stride + ceilTerm) / stride;
+      return;
+    case kPadValid:
+      *padBefore = 0;
+      *out = (iEff - fEff + stride + ceilTerm) / stride;
+      return;
+    case kPadSameLower:
+    case kPadSameUpper: {
+      *out = (iEff + stride - 1) / stride;
+      const int64_t lowerTerm = autopad == kPadSameLower ? 1 : 0;
+      *padBefore = (std::max<int64_t>(0, (*out - 1) * stride + fEff - iEff) + lowerTerm) / 2;
+      return;
+    }
+    default: throw std::runtime_error("Unexpected autopadding mode");
+  }
+}
+
+// ------------------------------------------------------------------ reductions (AggregationAxes, ops.cc:71-127)
+
+struct AggAxes {
+  std::vector<PolyPtr> srcIdxs, dstIdxs;
+  std::vector<int64_t> dstDims;
+  std::set<size_t> axes;
+  AggAxes(const pml::TensorShape& shape, const VarPtr& inAxes, bool keepdims) {
+    const size_t n = shape.rank();
+    for (size_t i = 0; i < n; ++i) srcIdxs.push_back(newIndex());
+    if (inAxes->kind == VarNode::None) {
+      for (size_t i = 0; i < n; ++i) axes.insert(i);
+    } else if (inAxes->kind == VarNode::Tuple) {
+      for (const VarPtr& a : inAxes->tuple) axes.insert(static_cast<size_t>(normalizeAxis(asInt(a), n, "aggregation")));
+    } else {
+      axes.insert(static_cast<size_t>(normalizeAxis(asInt(inAxes), n, "aggregation")));
+    }
+    for (size_t i = 0; i < n; ++i) {
+      if (axes.count(i)) {
+        if (keepdims) {
+          dstIdxs.push_back(newIndex());
+          dstDims.push_back(1);
+        }
+      } else {
+        dstIdxs.push_back(srcIdxs[i]);
+        dstDims.push_back(shape.sizes[i]);
+      }
+    }
+  }
+};
+
+VarPtr reduceOp(const VarPtr& value, pml::AggKind agg, const char* name) {
+  const auto& args = asTuple(value, name);
+  if (args.size() != 3) throw std::runtime_error(std::string(name) + " expects 3 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const pml::TensorShape shape = shapeOf(I);
+  if (args[1]->kind == VarNode::Tuple && args[1]->tuple.empty()) return exprValue(I);
+  AggAxes ax(shape, args[1], asBool(args[2]));
+  return exprValue(contraction(agg, pml::ComboKind::none, ax.dstDims, ax.dstIdxs, {{I, ax.srcIdxs}}, {}, name));
+}
+
+// ------------------------------------------------------------------ operations
+
+// plaidml/op/lib/ops.cc:1512-1561
+VarPtr opDot(const VarPtr& value) {
+  const auto& args = asTuple(value, "dot");
+  if (args.size() != 3) throw std::runtime_error("dot expects 3 arguments");
+  ExprPtr X = asTensor(args[0]), Y = asTensor(args[1]);
+  std::string name = asStr(args[2]);
+  if (name.empty()) name = "dot";
+  const pml::TensorShape xs = shapeOf(X), ys = shapeOf(Y);
+  if (xs.dtype != ys.dtype) {
+    throw std::runtime_error(std::string("Invalid dtype in dot: X.dtype = '") + pml::dtypeName(xs.dtype) +
+                             "', Y.dtype = '" + pml::dtypeName(ys.dtype) + "'");
+  }
+  if (xs.rank() == 1 && ys.rank() == 1) {
+    if (xs.sizes[0] != ys.sizes[0]) throw std::runtime_error("bind dims mismatch in dot");
+    PolyPtr i = newIndex();
+    return exprValue(contraction(pml::AggKind::add, pml::ComboKind::mul, {}, {}, {{X, {i}}, {Y, {i}}}, {}, name));
+  }
+  if (xs.rank() >= 1 && ys.rank() >= 2) {
+    std::vector<PolyPtr> xi, yi;
+    for (size_t i = 0; i < xs.rank(); ++i) xi.push_back(newIndex());
+    for (size_t i = 0; i < ys.rank(); ++i) yi.push_back(newIndex());
+    PolyPtr z = newIndex();
+    xi[xs.rank() - 1] = z;
+    yi[ys.rank() - 2] = z;
+    if (xs.sizes.back() != ys.sizes[ys.rank() - 2]) throw std::runtime_error("bind dims mismatch in dot");
+    std::vector<int64_t> od;
+    std::vector<PolyPtr> oi;
+    for (size_t i = 0; i + 1 < xs.rank(); ++i) {
+      od.push_back(xs.sizes[i]);
+      oi.push_back(xi[i]);
+    }
+    for (size_t i = 0; i + 2 < ys.rank(); ++i) {
+      od.push_back(ys.sizes[i]);
+      oi.push_back(yi[i]);
+    }
+    od.push_back(ys.sizes.back());
+    oi.push_back(yi.back());
+    return exprValue(contraction(pml::AggKind::add, pml::ComboKind::mul, od, oi, {{X, xi}, {Y, yi}}, {}, name));
+  }
+  throw std::runtime_error("Unsupported dims for dot operation");
+}
+
+// plaidml/op/lib/ops.cc:879-1467, forward pass, ungrouped, layouts NXC/XCK or NCX/KCX
+VarPtr opConvolution(const VarPtr& value) {
+  const auto& args = asTuple(value, "convolution");
+  if (args.size() != 18) throw std::runtime_error("Convolution op expects 18 arguments");
+  ExprPtr I = asTensor(args[0]), F = asTensor(args[1]);
+  std::vector<int64_t> strides = asIntTuple(args[2]);
+  std::vector<int64_t> dilations = asIntTuple(args[3]);
+  std::vector<int64_t> dataDilations = asIntTuple(args[4]);
+  const std::vector<int64_t> filterShape = asIntTuple(args[5]);
+  const int64_t groups = asInt(args[6]);
+  const int autopad = static_cast<int>(asInt(args[7]));
+  std::vector<int64_t> manualPadding = asIntTuple(args[8]);
+  const int inputLayout = static_cast<int>(asInt(args[9]));
+  const int filterLayout = static_cast<int>(asInt(args[10]));
+  std::string name = asStr(args[13]);
+  const int64_t derivMode = asInt(args[15]);
+  if (name.empty()) name = "conv";
+  if (groups != 1) throw std::runtime_error("Grouped convolutions are not offered by the cuda target's op library");
+  if (derivMode != 0) throw std::runtime_error("Only the forward convolution is offered by the cuda target's op library");
+  if (!(inputLayout == kNXC && filterLayout == kXCK) && !(inputLayout == kNCX && filterLayout == kKCX)) {
+    throw std::runtime_error("Convolution layouts must be NXC with XCK or NCX with KCX");
+  }
+  const pml::TensorShape is = shapeOf(I), fs = shapeOf(F);
+  if (is.rank() < 3 || fs.rank() != is.rank()) {
+    throw std::runtime_error("Convolution input and filter ranks are inconsistent");
+  }
+  const size_t sr = is.rank() - 2;  // spatial rank
+  if (strides.empty()) strides.assign(sr, 1);
+  if (dilations.empty()) dilations.assign(sr, 1);
+  if (dataDilations.empty()) dataDilations.assign(sr, 1);
+  if (strides.size() != sr || dilations.size() != sr || dataDilations.size() != sr) {
+    throw std::runtime_error("Convolution strides / dilations do not match the spatial rank");
+  }
+  for (int64_t d : dataDilations) {
+    if (d != 1) throw std::runtime_error("Data dilation is not offered by the cuda target's op library");
+  }
+  if (!manualPadding.empty() && autopad != kPadExplicit) {
+    throw std::runtime_error("Autopadding and manual padding both requested for single conv operation");
+  }
+  if (manualPadding.size() > 2 * sr) throw std::runtime_error("Inconsistent spatial rank: more manual padding than spatial dims");
+  // padding is listed as all "before" values, then all "after" values; missing ones are 0
+  std::vector<int64_t> padLo(sr, 0), padHi(sr, 0);
+  {
+    const size_t half = manualPadding.size() / 2;
+    for (size_t i = 0; i < half && i < sr; ++i) {
+      padLo[i] = manualPadding[i];
+      padHi[i] = manualPadding[half + i];
+    }
+  }
+  const bool nxc = inputLayout == kNXC;
+  const int64_t N = is.sizes[0];
+  const int64_t CI = nxc ? is.sizes.back() : is.sizes[1];
+  std::vector<int64_t> X(sr), K(sr);
+  for (size_t i = 0; i < sr; ++i) {
+    X[i] = nxc ? is.sizes[1 + i] : is.sizes[2 + i];
+    K[i] = nxc ? fs.sizes[i] : fs.sizes[2 + i];
+  }
+  const int64_t FCI = nxc ? fs.sizes[sr] : fs.sizes[1];
+  const int64_t CO = nxc ? fs.sizes[sr + 1] : fs.sizes[0];
+  if (FCI != CI) throw std::runtime_error("Convolution input channels do not match the filter");
+  if (!filterShape.empty()) {
+    if (filterShape.size() != sr) throw std::runtime_error("Filter shape does not match the spatial rank");
+    for (size_t i = 0; i < sr; ++i) {
+      if (filterShape[i] != K[i]) throw std::runtime_error("Filter shape does not match the filter tensor");
+    }
+  }
+  PolyPtr n = newIndex("n"), ci = newIndex("ci"), co = newIndex("co");
+  std::vector<PolyPtr> x, k, inSpatial;
+  std::vector<int64_t> outSpatial;
+  for (size_t i = 0; i < sr; ++i) {
+    x.push_back(newIndex("x" + std::to_string(i)));
+    k.push_back(newIndex("k" + std::to_string(i)));
+    int64_t padBefore = 0, outSize = 0;
+    paddingAndOutput(X[i], K[i], strides[i], autopad, padLo[i], padHi[i], dilations[i], 1, false, &padBefore, &outSize);
+    outSpatial.push_back(outSize);
+    inSpatial.push_back(strides[i] * x[i] + dilations[i] * k[i] - padBefore);
+  }
+  std::vector<PolyPtr> iIdx, fIdx, oIdx;
+  std::vector<int64_t> oDims;
+  if (nxc) {
+    iIdx.push_back(n);
+    for (auto& p : inSpatial) iIdx.push_back(p);
+    iIdx.push_back(ci);
+    for (auto& p : k) fIdx.push_back(p);
+    fIdx.push_back(ci);
+    fIdx.push_back(co);
+    oIdx.push_back(n);
+    oDims.push_back(N);
+    for (size_t i = 0; i < sr; ++i) {
+      oIdx.push_back(x[i]);
+      oDims.push_back(outSpatial[i]);
+    }
+    oIdx.push_back(co);
+    oDims.push_back(CO);
+  } else {
+    iIdx.push_back(n);
+    iIdx.push_back(ci);
+    for (auto& p : inSpatial) iIdx.push_back(p);
+    fIdx.push_back(co);
+    fIdx.push_back(ci);
+    for (auto& p : k) fIdx.push_back(p);
+    oIdx.push_back(n);
+    oDims.push_back(N);
+    oIdx.push_back(co);
+    oDims.push_back(CO);
+    for (size_t i = 0; i < sr; ++i) {
+      oIdx.push_back(x[i]);
+      oDims.push_back(outSpatial[i]);
+    }
+  }
+  return exprValue(contraction(pml::AggKind::add, pml::ComboKind::mul, oDims, oIdx, {{I, iIdx}, {F, fIdx}}, {}, name));
+}
+
+// plaidml/op/lib/ops.cc:2562-2703
+VarPtr opPool(const VarPtr& value) {
+  const auto& args = asTuple(value, "pool");
+  if (args.size() != 10) throw std::runtime_error("PlaidML pool op expects 10 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const int mode = static_cast<int>(asInt(args[1]));
+  const std::vector<int64_t> poolSize = asIntTuple(args[2]);
+  const std::vector<int64_t> strides = asIntTuple(args[3]);
+  const int autopad = static_cast<int>(asInt(args[4]));
+  std::vector<int64_t> manualPadding = asIntTuple(args[5]);
+  const int layout = static_cast<int>(asInt(args[6]));
+  const bool includePadding = asBool(args[7]);
+  const bool ceilMode = asBool(args[8]);
+  std::string name = asStr(args[9]);
+  if (name.empty()) name = "pool";
+  const pml::TensorShape is = shapeOf(I);
+  const size_t sr = poolSize.size();
+  if (!manualPadding.empty() && autopad != kPadExplicit) {
+    throw std::runtime_error("Autopadding and manual padding both requested for single pool operation");
+  }
+  if (strides.size() != sr) throw std::runtime_error("Inconsistent spatial rank in pool op");
+  if (is.rank() != sr + 2) throw std::runtime_error("Inconsistent spatial rank in pool op");
+  if (layout != kNXC && layout != kNCX) throw std::runtime_error("Tensor layout requested in pool op does not apply to pooling");
+  std::vector<int64_t> padLo(sr, 0), padHi(sr, 0);
+  {
+    const size_t half = manualPadding.size() / 2;
+    for (size_t i = 0; i < half && i < sr; ++i) {
+      padLo[i] = manualPadding[i];
+      padHi[i] = manualPadding[half + i];
+    }
+  }
+  const bool nxc = layout == kNXC;
+  PolyPtr n = newIndex("n"), c = newIndex("c");
+  std::vector<PolyPtr> x, k, inSpatial;
+  std::vector<int64_t> outSpatial;
+  std::vector<Cons> cons;
+  for (size_t i = 0; i < sr; ++i) {
+    const int64_t X = nxc ? is.sizes[1 + i] : is.sizes[2 + i];
+    x.push_back(newIndex("x" + std::to_string(i)));
+    k.push_back(newIndex("k" + std::to_string(i)));
+    int64_t padBefore = 0, outSize = 0;
+    paddingAndOutput(X, poolSize[i], strides[i], autopad, padLo[i], padHi[i], 1, 1, ceilMode, &padBefore, &outSize);
+    outSpatial.push_back(outSize);
+    inSpatial.push_back(strides[i] * x[i] + k[i] - padBefore);
+    cons.push_back({k[i], poolSize[i]});
+  }
+  const int64_t N = is.sizes[0], C = nxc ? is.sizes.back() : is.sizes[1];
+  std::vector<PolyPtr> iIdx = {n}, oIdx = {n};
+  std::vector<int64_t> oDims = {N};
+  if (!nxc) {
+    iIdx.push_back(c);
+    oIdx.push_back(c);
+    oDims.push_back(C);
+  }
+  for (size_t i = 0; i < sr; ++i) {
+    iIdx.push_back(inSpatial[i]);
+    oIdx.push_back(x[i]);
+    oDims.push_back(outSpatial[i]);
+  }
+  if (nxc) {
+    iIdx.push_back(c);
+    oIdx.push_back(c);
+    oDims.push_back(C);
+  }
+  const pml::AggKind agg = mode == kPoolMax ? pml::AggKind::max : (mode == kPoolMin ? pml::AggKind::min : pml::AggKind::add);
+  ExprPtr O = contraction(agg, pml::ComboKind::none, oDims, oIdx, {{I, iIdx}}, cons, name);
+  if (mode != kPoolAvg) return exprValue(O);
+  if (includePadding) {
+    int64_t total = 1;
+    for (int64_t s : poolSize) total *= s;
+    return exprValue(intrinsic("div", {O, litInt(total)}));
+  }
+  // average over the taps that fall inside the input: count them with a second contraction
+  ExprPtr one = castTo(litInt(1), is.dtype);
+  ExprPtr ones = contraction(pml::AggKind::assign, pml::ComboKind::none, is.sizes, oIdx, {{one, {}}}, {}, name);
+  ExprPtr count = contraction(pml::AggKind::add, pml::ComboKind::none, oDims, oIdx, {{ones, iIdx}}, cons, name);
+  return exprValue(intrinsic("div", {O, count}));
+}
+
+// plaidml/op/lib/ops.cc:2705-2728
+VarPtr opRelu(const VarPtr& value) {
+  const auto& args = asTuple(value, "relu");
+  if (args.size() != 5) throw std::runtime_error("relu expects 5 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const VarPtr& alpha = args[1];
+  const VarPtr& maxValue = args[2];
+  const VarPtr& threshold = args[3];
+  const double T = threshold->kind == VarNode::None ? 0.0 : (threshold->kind == VarNode::Float ? threshold->f : static_cast<double>(asInt(threshold)));
+  const bool alphaZero = alpha->kind == VarNode::None || (alpha->kind == VarNode::Float && alpha->f == 0.0);
+  if (alphaZero && maxValue->kind == VarNode::None && T == 0.0) return exprValue(intrinsic("relu", {I}));
+  const pml::DType dt = shapeOf(I).dtype;
+  ExprPtr A = alpha->kind == VarNode::None ? litFloat(0.0) : asTensor(alpha);
+  ExprPtr shifted = intrinsic("sub", {I, litFloat(T)});
+  ExprPtr O = intrinsic("select", {intrinsic("cmp_lt", {I, litFloat(T)}), castTo(intrinsic("mul", {A, shifted}), dt), I});
+  if (maxValue->kind != VarNode::None) {
+    ExprPtr M = castTo(asTensor(maxValue), dt);
+    O = intrinsic("select", {intrinsic("cmp_lt", {O, M}), O, M});
+  }
+  return exprValue(O);
+}
+
+// plaidml/op/lib/ops.cc:1970-2003
+VarPtr opMean(const VarPtr& value) {
+  const auto& args = asTuple(value, "mean");
+  if (args.size() != 3) throw std::runtime_error("mean expects 3 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const pml::TensorShape shape = shapeOf(I);
+  if (shape.rank() == 0) return exprValue(I);
+  if (args[1]->kind == VarNode::Tuple && args[1]->tuple.empty()) return exprValue(I);
+  AggAxes ax(shape, args[1], asBool(args[2]));
+  ExprPtr SO = contraction(pml::AggKind::add, pml::ComboKind::none, ax.dstDims, ax.dstIdxs, {{I, ax.srcIdxs}}, {}, "mean");
+  int64_t denom = 1;
+  for (size_t a : ax.axes) denom *= shape.sizes[a];
+  return exprValue(intrinsic("div", {SO, litInt(denom)}));
+}
+
+// plaidml/op/lib/ops.cc:3049-3099 (the soft-max axis must be the last one here)
+VarPtr opSoftmax(const VarPtr& value) {
+  const auto& args = asTuple(value, "softmax");
+  if (args.size() != 3) throw std::runtime_error("softmax expects 3 arguments");
+  ExprPtr I = asTensor(args[0]);
+  std::string name = asStr(args[2]);
+  if (name.empty()) name = "softmax";
+  const pml::TensorShape shape = shapeOf(I);
+  const int64_t axis = normalizeAxis(asInt(args[1]), shape.rank(), "softmax");
+  if (axis != static_cast<int64_t>(shape.rank()) - 1) {
+    throw std::runtime_error("softmax over an inner axis: transpose it to the last axis first");
+  }
+  std::vector<PolyPtr> idxs, ridxs;
+  std::vector<int64_t> rdims = shape.sizes;
+  for (size_t i = 0; i < shape.rank(); ++i) idxs.push_back(newIndex());
+  ridxs = idxs;
+  rdims[axis] = 1;
+  ridxs[axis] = polyLit(0);
+  ExprPtr M = contraction(pml::AggKind::max, pml::ComboKind::none, rdims, ridxs, {{I, idxs}}, {}, name);
+  ExprPtr E = intrinsic("exp", {intrinsic("sub", {I, M})});
+  ExprPtr Nrm = contraction(pml::AggKind::add, pml::ComboKind::none, rdims, ridxs, {{E, idxs}}, {}, name);
+  return exprValue(intrinsic("div", {E, Nrm}));
+}
+
+VarPtr unary(const VarPtr& value, const char* fn) {
+  ExprPtr I = value->kind == VarNode::Tuple ? asTensor(value->tuple.at(0)) : asTensor(value);
+  return exprValue(intrinsic(fn, {I}));
+}
+
+VarPtr opSquare(const VarPtr& value) {
+  ExprPtr I = value->kind == VarNode::Tuple ? asTensor(value->tuple.at(0)) : asTensor(value);
+  return exprValue(intrinsic("mul", {I, I}));
+}
+
+VarPtr opMaximum(const VarPtr& value) {
+  const auto& args = asTuple(value, "maximum");
+  if (args.size() != 2) throw std::runtime_error("maximum expects 2 arguments");
+  ExprPtr X = asTensor(args[0]), Y = asTensor(args[1]);
+  return exprValue(intrinsic("select", {intrinsic("cmp_lt", {X, Y}), Y, X}));
+}
+
+VarPtr opMinimum(const VarPtr& value) {
+  const auto& args = asTuple(value, "minimum");
+  if (args.size() != 2) throw std::runtime_error("minimum expects 2 arguments");
+  ExprPtr X = asTensor(args[0]), Y = asTensor(args[1]);
+  return exprValue(intrinsic("select", {intrinsic("cmp_lt", {X, Y}), X, Y}));
+}
+
+VarPtr opClip(const VarPtr& value) {
+  const auto& args = asTuple(value, "clip");
+  if (args.size() != 3) throw std::runtime_error("clip expects 3 arguments");
+  ExprPtr O = asTensor(args[0]);
+  if (args[1]->kind != VarNode::None) {
+    ExprPtr lo = asTensor(args[1]);
+    O = intrinsic("select", {intrinsic("cmp_gt", {O, lo}), O, lo});
+  }
+  if (args[2]->kind != VarNode::None) {
+    ExprPtr hi = asTensor(args[2]);
+    O = intrinsic("select", {intrinsic("cmp_lt", {O, hi}), O, hi});
+  }
+  return exprValue(O);
+}
+
+VarPtr opReshape(const VarPtr& value) {
+  const auto& args = asTuple(value, "reshape");
+  if (args.size() != 2) throw std::runtime_error("reshape expects 2 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const pml::TensorShape shape = shapeOf(I);
+  std::vector<int64_t> dims;
+  int64_t known = 1;
+  int fill = -1;
+  const auto& want = asTuple(args[1], "reshape dims");
+  for (size_t i = 0; i < want.size(); ++i) {
+    int64_t d = asInt(want[i]);
+    if (d == 0) d = i < shape.rank() ? shape.sizes[i] : 0;  // 0 copies the input extent
+    if (d == -1) {
+      if (fill >= 0) throw std::runtime_error("reshape: at most one dimension may be -1");
+      fill = static_cast<int>(i);
+      d = 1;
+    } else {
+      known *= d;
+    }
+    dims.push_back(d);
+  }
+  if (fill >= 0) dims[fill] = known ? shape.elements() / known : 0;
+  return exprValue(reshapeTo(I, dims));
+}
+
+VarPtr opTranspose(const VarPtr& value) {
+  const auto& args = asTuple(value, "transpose");
+  if (args.size() != 2) throw std::runtime_error("transpose expects 2 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const pml::TensorShape shape = shapeOf(I);
+  std::vector<int64_t> pattern;
+  if (args[1]->kind == VarNode::None) {
+    for (size_t i = 0; i < shape.rank(); ++i) pattern.push_back(static_cast<int64_t>(shape.rank() - 1 - i));
+  } else {
+    pattern = asIntTuple(args[1]);
+  }
+  if (pattern.size() != shape.rank()) throw std::runtime_error("transpose pattern does not match the tensor rank");
+  std::vector<PolyPtr> iIdx, oIdx;
+  std::vector<int64_t> oDims;
+  for (size_t i = 0; i < shape.rank(); ++i) iIdx.push_back(newIndex());
+  for (int64_t a : pattern) {
+    const int64_t ax = normalizeAxis(a, shape.rank(), "transpose");
+    oIdx.push_back(iIdx[ax]);
+    oDims.push_back(shape.sizes[ax]);
+  }
+  return exprValue(contraction(pml::AggKind::assign, pml::ComboKind::none, oDims, oIdx, {{I, iIdx}}, {}, "transpose"));
+}
+
+VarPtr opSqueeze(const VarPtr& value) {
+  const auto& args = asTuple(value, "squeeze");
+  ExprPtr I = asTensor(args.at(0));
+  const pml::TensorShape shape = shapeOf(I);
+  std::set<int64_t> axes;
+  for (int64_t a : asIntTuple(args.at(1))) axes.insert(normalizeAxis(a, shape.rank(), "squeeze"));
+  std::vector<int64_t> dims;
+  for (size_t i = 0; i < shape.rank(); ++i) {
+    if (axes.count(static_cast<int64_t>(i))) {
+      if (shape.sizes[i] != 1) throw std::runtime_error("squeeze: axis extent is not 1");
+    } else {
+      dims.push_back(shape.sizes[i]);
+    }
+  }
+  return exprValue(reshapeTo(I, dims));
+}
+
+VarPtr opUnsqueeze(const VarPtr& value) {
+  const auto& args = asTuple(value, "unsqueeze");
+  ExprPtr I = asTensor(args.at(0));
+  const pml::TensorShape shape = shapeOf(I);
+  std::vector<int64_t> axes = asIntTuple(args.at(1));
+  const size_t newRank = shape.rank() + axes.size();
+  std::set<int64_t> at;
+  for (int64_t a : axes) at.insert(normalizeAxis(a, newRank, "unsqueeze"));
+  std::vector<int64_t> dims;
+  size_t src = 0;
+  for (size_t i = 0; i < newRank; ++i) {
+    if (at.count(static_cast<int64_t>(i))) dims.push_back(1);
+    else dims.push_back(shape.sizes[src++]);
+  }
+  return exprValue(reshapeTo(I, dims));
+}
+
+VarPtr opFlip(const VarPtr& value) {
+  const auto& args = asTuple(value, "flip");
+  ExprPtr I = asTensor(args.at(0));
+  const pml::TensorShape shape = shapeOf(I);
+  const int64_t axis = normalizeAxis(asInt(args.at(1)), shape.rank(), "flip");
+  std::vector<PolyPtr> iIdx, oIdx;
+  for (size_t i = 0; i < shape.rank(); ++i) iIdx.push_back(newIndex());
+  oIdx = iIdx;
+  oIdx[axis] = polyLit(shape.sizes[axis] - 1) - iIdx[axis];
+  return exprValue(contraction(pml::AggKind::assign, pml::ComboKind::none, shape.sizes, oIdx, {{I, iIdx}}, {}, "flip"));
+}
+
+// plaidml/op/lib/ops.cc cumsum: O[.., i, ..] += I[.., i - k, ..] with k < N
+VarPtr opCumsum(const VarPtr& value) {
+  const auto& args = asTuple(value, "cumsum");
+  ExprPtr I = asTensor(args.at(0));
+  const pml::TensorShape shape = shapeOf(I);
+  const int64_t axis = normalizeAxis(asInt(args.at(1)), shape.rank(), "cumsum");
+  std::vector<PolyPtr> oIdx, iIdx;
+  for (size_t i = 0; i < shape.rank(); ++i) oIdx.push_back(newIndex());
+  iIdx = oIdx;
+  PolyPtr k = newIndex("k");
+  iIdx[axis] = oIdx[axis] - k;
+  return exprValue(contraction(pml::AggKind::add, pml::ComboKind::none, shape.sizes, oIdx, {{I, iIdx}},
+                               {{k, shape.sizes[axis]}}, "cumsum"));
+}
+
+VarPtr opVariance(const VarPtr& value) {
+  const auto& args = asTuple(value, "variance");
+  if (args.size() != 3) throw std::runtime_error("variance expects 3 arguments");
+  ExprPtr I = asTensor(args[0]);
+  auto keep = std::make_shared<VarNode>();
+  keep->kind = VarNode::Int;
+  keep->i = 1;
+  auto meanArgs = std::make_shared<VarNode>();
+  meanArgs->kind = VarNode::Tuple;
+  meanArgs->tuple = {args[0], args[1], keep};
+  ExprPtr mean = opMean(meanArgs)->expr;
+  ExprPtr diff = intrinsic("sub", {I, mean});
+  auto sqArgs = std::make_shared<VarNode>();
+  sqArgs->kind = VarNode::Tuple;
+  sqArgs->tuple = {exprValue(intrinsic("mul", {diff, diff})), args[1], args[2]};
+  return opMean(sqArgs);
+}
+
+VarPtr opSpatialPadding(const VarPtr& value) {
+  const auto& args = asTuple(value, "spatial_padding");
+  if (args.size() != 4) throw std::runtime_error("spatial_padding expects 4 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const std::vector<int64_t> lo = asIntTuple(args[1]), hi = asIntTuple(args[2]);
+  const int layout = static_cast<int>(asInt(args[3]));
+  const pml::TensorShape shape = shapeOf(I);
+  const size_t sr = shape.rank() - 2;
+  if (lo.size() != sr || hi.size() != sr) throw std::runtime_error("spatial_padding: pads do not match the spatial rank");
+  const size_t first = layout == kNXC ? 1 : 2;
+  std::vector<PolyPtr> iIdx, oIdx;
+  std::vector<int64_t> oDims = shape.sizes;
+  for (size_t i = 0; i < shape.rank(); ++i) iIdx.push_back(newIndex());
+  oIdx = iIdx;
+  for (size_t i = 0; i < sr; ++i) {
+    oDims[first + i] += lo[i] + hi[i];
+    oIdx[first + i] = iIdx[first + i] + lo[i];
+  }
+  return exprValue(contraction(pml::AggKind::assign, pml::ComboKind::none, oDims, oIdx, {{I, iIdx}}, {}, "spatial_padding"));
+}
+
+VarPtr opElu(const VarPtr& value) {
+  const auto& args = asTuple(value, "elu");
+  ExprPtr I = asTensor(args.at(0));
+  ExprPtr alpha = asTensor(args.at(1));
+  ExprPtr neg = intrinsic("mul", {alpha, intrinsic("sub", {intrinsic("exp", {I}), litFloat(1.0)})});
+  return exprValue(intrinsic("select", {intrinsic("cmp_lt", {I, litFloat(0.0)}), castTo(neg, shapeOf(I).dtype), I}));
+}
+
+const std::map<std::string, std::function<VarPtr(const VarPtr&)>>& registry() {
+  static const std::map<std::string, std::function<VarPtr(const VarPtr&)>> ops = {
+      {"abs", [](const VarPtr& v) { return unary(v, "abs"); }},
+      {"clip", opClip},
+      {"convolution", opConvolution},
+      {"cumsum", opCumsum},
+      {"dot", opDot},
+      {"elu", opElu},
+      {"flip", opFlip},
+      {"max", [](const VarPtr& v) { return reduceOp(v, pml::AggKind::max, "max"); }},
+      {"maximum", opMaximum},
+      {"mean", opMean},
+      {"min", [](const VarPtr& v) { return reduceOp(v, pml::AggKind::min, "min"); }},
+      {"minimum", opMinimum},
+      {"pool", opPool},
+      {"prod", [](const VarPtr& v) { return reduceOp(v, pml::AggKind::mul, "prod"); }},
+      {"relu", opRelu},
+      {"reshape", opReshape},
+      {"sigmoid", [](const VarPtr& v) { return unary(v, "sigmoid"); }},
+      {"softmax", opSoftmax},
+      {"spatial_padding", opSpatialPadding},
+      {"square", opSquare},
+      {"squeeze", opSqueeze},
+      {"sum", [](const VarPtr& v) { return reduceOp(v, pml::AggKind::add, "sum"); }},
+      {"transpose", opTranspose},
+      {"unsqueeze", opUnsqueeze},
+      {"variance", opVariance},
+  };
+  return ops;
+}
+
+}  // namespace
+
+extern "C" {
+
+plaidml_value* plaidml_op_make(plaidml_error* err, const char* op_name, plaidml_value* value) {
+  return pml::ffiWrap<plaidml_value*>(err, nullptr, [&] {
+    const auto& ops = registry();
+    auto it = ops.find(op_name ? op_name : "");
+    if (it == ops.end()) {
+      throw std::runtime_error(std::string("Operation '") + (op_name ? op_name : "") +
+                               "' is not in the cuda target's op library");
+    }
+    return new plaidml_value{it->second(value->node)};
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,1287 @@
+// Planner and executor of the `cuda` device.
+#include "pml_exec.h"
+
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+#include <map>
+#include <regex>
+#include <set>
+#include <sstream>
+
+extern "C" pmlb_status pmlb_plan_share_status(pmlb_plan* plan, int* device_word);
+
+namespace pml {
+
+namespace {
+
+void cudaCheck(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+void pmlbCheck(pmlb_status s, const std::string& what) {
+  if (s != PMLB_OK) throw std::runtime_error(what + ": " + pmlb_last_error());
+}
+
+int pmlbAgg(AggKind a) {
+  switch (a) {
+    case AggKind::add: return PMLB_AGG_SUM;
+    case AggKind::max: return PMLB_AGG_MAX;
+    case AggKind::min: return PMLB_AGG_MIN;
+    case AggKind::mul: return PMLB_AGG_PROD;
+    default: return PMLB_AGG_ASSIGN;
+  }
+}
+
+int pmlbCombo(ComboKind c) {
+  switch (c) {
+    case ComboKind::mul: return PMLB_COMBO_MUL;
+    case ComboKind::add: return PMLB_COMBO_ADD;
+    case ComboKind::eq: return PMLB_COMBO_EQ;
+    case ComboKind::cond: return PMLB_COMBO_COND;
+    default: return PMLB_COMBO_NONE;
+  }
+}
+
+std::string shapeStr(const std::vector<int64_t>& v) {
+  std::ostringstream os;
+  for (size_t i = 0; i < v.size(); ++i) os << (i ? "x" : "") << v[i];
+  return os.str();
+}
+
+// One index variable's use inside one tensor access.
+struct VarUse {
+  bool present = false;
+  int64_t stride = 0;  // elements, in the dense layout of the tensor
+};
+
+// A contraction with extent-1 variables folded away and integer coefficients checked.
+struct Simplified {
+  bool ok = false;
+  size_t n = 0;
+  std::vector<int64_t> extent;
+  // per tensor (0 = out, 1.. = sources), per dim: integer coefficients and constant
+  std::vector<std::vector<std::vector<int64_t>>> coef;
+  std::vector<std::vector<int64_t>> cst;
+};
+
+Simplified simplify(const BoundedContraction& c) {
+  Simplified s;
+  s.n = c.nIdx();
+  s.extent = c.extent;
+  auto addTensor = [&](const std::vector<Affine>& forms) -> bool {
+    std::vector<std::vector<int64_t>> cf;
+    std::vector<int64_t> cs;
+    for (const Affine& a : forms) {
+      std::vector<int64_t> row(s.n, 0);
+      Rational k = a.constant;
+      for (size_t i = 0; i < s.n; ++i) {
+        const Rational ci = i < a.coef.size() ? a.coef[i] : Rational(0);
+        k = k + ci * Rational(c.lower[i]);           // shift variables to start at 0
+        if (c.extent[i] <= 1 || ci.isZero()) continue;  // a single-valued variable is a constant
+        if (!ci.isInt()) return false;
+        row[i] = ci.num;
+      }
+      if (!k.isInt()) return false;
+      cf.push_back(row);
+      cs.push_back(k.num);
+    }
+    s.coef.push_back(cf);
+    s.cst.push_back(cs);
+    return true;
+  };
+  if (!addTensor(c.sink)) return s;
+  for (const auto& src : c.srcs) {
+    if (!addTensor(src)) return s;
+  }
+  // constraints must be implied by the ranges: single variable, unit coefficient
+  for (const auto& con : c.cons) {
+    int var = -1;
+    Rational k = con.first.constant;
+    for (size_t i = 0; i < s.n; ++i) {
+      const Rational ci = i < con.first.coef.size() ? con.first.coef[i] : Rational(0);
+      k = k + ci * Rational(c.lower[i]);
+      if (ci.isZero() || c.extent[i] <= 1) continue;
+      if (var >= 0 || !(ci.num == 1 && ci.den == 1)) return s;
+      var = static_cast<int>(i);
+    }
+    if (!k.isInt() || k.num < 0) return s;
+    const int64_t ext = var >= 0 ? c.extent[var] : 1;
+    if (k.num + ext > con.second) return s;
+  }
+  for (size_t i = 0; i < s.n; ++i) {
+    if (c.extent[i] <= 0) return s;
+  }
+  s.ok = true;
+  return s;
+}
+
+// Is dim `d` of tensor `t` exactly one variable (coefficient 1, constant 0)?  Returns the
+// variable or -1; -2 when the dim is a constant 0 (all its variables single-valued).
+int pureVar(const Simplified& s, size_t t, size_t d) {
+  int var = -1;
+  for (size_t i = 0; i < s.n; ++i) {
+    if (s.coef[t][d][i] == 0) continue;
+    if (var >= 0 || s.coef[t][d][i] != 1) return -1;
+    var = static_cast<int>(i);
+  }
+  if (s.cst[t][d] != 0) return -1;
+  return var >= 0 ? var : -2;
+}
+
+}  // namespace
+
+// ==================================================================== planner
+
+class Planner {
+ public:
+  Planner(Executable* exe) : exe_(exe), prog_(*exe->prog_) {}
+
+  void run() {
+    const size_t nv = prog_.values.size();
+    uses_.assign(nv, 0);
+    isOutput_.assign(nv, false);
+    for (const POp& op : prog_.ops) {
+      for (int o : op.operands) ++uses_[o];
+    }
+    for (int o : prog_.outputs) {
+      ++uses_[o];
+      isOutput_[o] = true;
+    }
+    users_.assign(nv, {});
+    for (size_t i = 0; i < prog_.ops.size(); ++i) {
+      for (int o : prog_.ops[i].operands) users_[o].push_back(static_cast<int>(i));
+    }
+    absorbed_.assign(prog_.ops.size(), false);
+    alias_.assign(nv, -1);
+
+    // ---- phase A: choose a kernel for every operation, fusing neighbours into it
+    for (size_t i = 0; i < prog_.ops.size(); ++i) {
+      if (absorbed_[i]) continue;
+      const POp& op = prog_.ops[i];
+      Pending pd;
+      pd.op = static_cast<int>(i);
+      pd.position = static_cast<int>(i);
+      pd.result = op.result;
+      switch (op.kind) {
+        case POp::Reshape:
+          alias_[op.result] = op.operands[0];
+          continue;
+        case POp::Contraction:
+          planContraction(&pd);
+          break;
+        case POp::Cast:
+        case POp::Eltwise:
+          pd.kind = Pending::Eltwise;
+          pd.inputs = op.operands;
+          break;
+      }
+      pending_.push_back(std::move(pd));
+    }
+
+    // A step with fused consumers runs where its last consumer stood, so that operands
+    // joined late (a residual computed by a sibling branch) are ready.
+    std::stable_sort(pending_.begin(), pending_.end(),
+                     [](const Pending& x, const Pending& y) { return x.position < y.position; });
+
+    // ---- phase B: which steps are needed for the outputs
+    std::vector<bool> needed(nv, false);
+    for (int o : prog_.outputs) needed[root(o)] = true;
+    std::vector<bool> keep(pending_.size(), false);
+    for (size_t k = pending_.size(); k-- > 0;) {
+      Pending& pd = pending_[k];
+      if (!needed[root(pd.result)]) continue;
+      keep[k] = true;
+      for (int in : pd.inputs) needed[root(in)] = true;
+    }
+
+    // ---- phase C: device memory, then kernel plans
+    allocate(needed);
+    for (size_t k = 0; k < pending_.size(); ++k) {
+      if (keep[k]) emit(pending_[k]);
+    }
+  }
+
+ private:
+  struct Pending {
+    enum Kind { Gemm, Conv, Reduce, Pool, Generic, Eltwise } kind = Generic;
+    int op = -1;
+    int position = -1;          // program position the step runs at: its last fused operation
+    int result = -1;            // value the step writes (after fused consumers)
+    std::vector<int> inputs;    // values the step reads
+    std::string fused;          // description of fused neighbours
+    pmlb_gemm_desc gemm;
+    pmlb_conv_desc conv;
+    pmlb_reduce_desc reduce;
+    pmlb_pool_desc pool;
+    int a = -1, b = -1, bias = -1, residual = -1;  // value ids
+    bool swapped = false;
+  };
+
+  int root(int v) const {
+    while (alias_[v] >= 0) v = alias_[v];
+    return v;
+  }
+
+  const PValue& val(int v) const { return prog_.values[v]; }
+
+  // Looks through a widening cast feeding a contraction: returns the cast's source if
+  // `v` is cast(bf16|f16 -> f32) or cast(si8 -> si32), else v itself.
+  int throughCast(int v) const {
+    const PValue& pv = val(v);
+    if (pv.def < 0) return v;
+    const POp& op = prog_.ops[pv.def];
+    if (op.kind != POp::Cast) return v;
+    const DType from = val(op.operands[0]).shape.dtype, to = pv.shape.dtype;
+    const bool ok = (to == DType::f32 && (from == DType::bf16 || from == DType::f16)) ||
+                    (to == DType::si32 && from == DType::si8);
+    return ok ? op.operands[0] : v;
+  }
+
+  bool denseValue(int v) const { return val(root(v)).shape.isDense(); }
+
+  // ------------------------------------------------------------ contraction planning
+  void planContraction(Pending* pd) {
+    const POp& op = prog_.ops[pd->op];
+    const BoundedContraction& c = *op.c;
+    pd->kind = Pending::Generic;
+    pd->inputs = op.operands;
+    for (int o : op.operands) {
+      if (!denseValue(o)) throw std::runtime_error("The cuda target takes dense row-major tensors");
+    }
+    const Simplified s = simplify(c);
+    if (s.ok && !c.hasInit && !getenvFlag("PLAIDML_CUDA_GENERIC_ONLY")) {
+      if (c.agg == AggKind::add && c.combo == ComboKind::mul) {
+        if (tryConv(pd, s) || tryGemm(pd, s)) return;
+      }
+      if (c.combo == ComboKind::none && (c.agg == AggKind::add || c.agg == AggKind::max || c.agg == AggKind::min)) {
+        if (tryPool(pd, s) || tryReduce(pd, s)) return;
+      }
+    }
+  }
+
+  static bool getenvFlag(const char* name) {
+    const char* v = std::getenv(name);
+    return v && v[0] && v[0] != '0';
+  }
+
+  // Element type triple of a tensor-core contraction; false if the operand types do not
+  // form one of the supported combinations.
+  bool tcTypes(int opA, int opB, DType resultType, int* a, int* b, int* inDtype, int* outDtype) const {
+    const int ca = throughCast(opA), cb = throughCast(opB);
+    const DType ta = val(ca).shape.dtype, tb = val(cb).shape.dtype;
+    if (ta != tb) {
+      // mixed: fall back to the un-cast operands
+      const DType ua = val(opA).shape.dtype, ub = val(opB).shape.dtype;
+      if (ua != ub) return false;
+      *a = opA;
+      *b = opB;
+      return tcTypesPlain(ua, resultType, inDtype, outDtype);
+    }
+    if ((ca != opA) != (cb != opB)) {
+      // only one side is a cast: e.g. f32 x cast(bf16): use both as written
+      const DType ua = val(opA).shape.dtype, ub = val(opB).shape.dtype;
+      if (ua != ub) return false;
+      *a = opA;
+      *b = opB;
+      return tcTypesPlain(ua, resultType, inDtype, outDtype);
+    }
+    *a = ca;
+    *b = cb;
+    if (ca != opA) {
+      // both operands widened by casts: narrow inputs, wide accumulate
+      if (ta == DType::si8 && resultType == DType::si32) {
+        *inDtype = PMLB_I8;
+        *outDtype = PMLB_I32;
+        return true;
+      }
+      if ((ta == DType::bf16 || ta == DType::f16) && resultType == DType::f32) {
+        *inDtype = ta == DType::bf16 ? PMLB_BF16 : PMLB_F16;
+        *outDtype = PMLB_F32;
+        return true;
+      }
+      return false;
+    }
+    return tcTypesPlain(ta, resultType, inDtype, outDtype);
+  }
+
+  static bool tcTypesPlain(DType t, DType resultType, int* inDtype, int* outDtype) {
+    if (t != resultType) return false;
+    switch (t) {
+      case DType::f32: *inDtype = PMLB_F32; *outDtype = PMLB_F32; return true;
+      case DType::bf16: *inDtype = PMLB_BF16; *outDtype = PMLB_BF16; return true;
+      case DType::f16: *inDtype = PMLB_F16; *outDtype = PMLB_F16; return true;
+      case DType::si8: *inDtype = PMLB_I8; *outDtype = PMLB_I8; return true;
+      default: return false;
+    }
+  }
+
+  // Walks the single-use consumer chain of a tensor-core contraction and folds
+  // bias add -> residual add -> relu -> cast into its epilogue.
+  void fuseEpilogue(Pending* pd, int inDtype, int* outDtype, int64_t nCols, int* epilogue) {
+    const bool intPath = inDtype == PMLB_I8;
+    struct Link {
+      int op;
+      int flag;        // PMLB_EPI_* this link adds, 0 for the cast
+      int value;       // value the link produces
+    };
+    std::vector<Link> chain;
+    int cur = pd->result;
+    int stage = 0;  // 0 nothing yet, 1 bias, 2 residual, 3 relu, 4 cast
+    int bias = -1, resWritten = -1, resSource = -1;
+    int castDtype = -1;
+    while (stage < 4) {
+      if (uses_[cur] != 1 || isOutput_[cur] || users_[cur].size() != 1) break;
+      const int ui = users_[cur][0];
+      const POp& u = prog_.ops[ui];
+      const TensorShape& rs = val(u.result).shape;
+      if (rs.sizes != val(cur).shape.sizes) break;
+      int flag = -1;
+      if (u.kind == POp::Eltwise && u.mnemonic == "add" && u.operands.size() == 2 && stage < 3 &&
+          rs.dtype == val(cur).shape.dtype) {
+        const int other = u.operands[0] == cur ? u.operands[1] : u.operands[0];
+        const TensorShape& os = val(other).shape;
+        const bool isBias = stage < 1 && os.rank() >= 1 && os.sizes.back() == nCols && os.elements() == nCols &&
+                            denseValue(other) && os.dtype == (intPath ? DType::si32 : DType::f32);
+        if (isBias) {
+          bias = other;
+          flag = PMLB_EPI_BIAS;
+          stage = 1;
+        } else if (stage < 2 && os.sizes == rs.sizes && denseValue(other)) {
+          resWritten = other;
+          resSource = throughCast(other);
+          flag = PMLB_EPI_RESIDUAL;
+          stage = 2;
+        }
+      } else if (u.kind == POp::Eltwise && u.mnemonic == "relu" && stage < 3 && rs.dtype == val(cur).shape.dtype) {
+        flag = PMLB_EPI_RELU;
+        stage = 3;
+      } else if (u.kind == POp::Cast && !intPath && *outDtype == PMLB_F32 &&
+                 (rs.dtype == DType::bf16 || rs.dtype == DType::f16)) {
+        castDtype = rs.dtype == DType::bf16 ? PMLB_BF16 : PMLB_F16;
+        flag = 0;
+        stage = 4;
+      }
+      if (flag < 0) break;
+      chain.push_back({ui, flag, u.result});
+      cur = u.result;
+    }
+    // The kernel reads the residual in the element type it stores: keep the residual (and
+    // what follows it) only if one of its two forms has that type.
+    int finalDtype = castDtype >= 0 ? castDtype : *outDtype;
+    int residual = -1;
+    if (resWritten >= 0) {
+      if (static_cast<int>(val(resSource).shape.dtype) == finalDtype) {
+        residual = resSource;
+      } else if (static_cast<int>(val(resWritten).shape.dtype) == finalDtype) {
+        residual = resWritten;
+      } else {
+        size_t cut = 0;
+        while (cut < chain.size() && chain[cut].flag != PMLB_EPI_RESIDUAL) ++cut;
+        chain.resize(cut);
+        finalDtype = *outDtype;
+      }
+    }
+    int flags = 0;
+    for (const Link& l : chain) {
+      flags |= l.flag;
+      absorbed_[l.op] = true;
+      pd->position = std::max(pd->position, l.op);
+    }
+    if (!chain.empty()) pd->result = chain.back().value;
+    pd->bias = (flags & PMLB_EPI_BIAS) ? bias : -1;
+    pd->residual = residual;
+    if (pd->bias >= 0) pd->inputs.push_back(pd->bias);
+    if (residual >= 0) pd->inputs.push_back(residual);
+    *outDtype = finalDtype;
+    *epilogue = flags;
+    std::ostringstream os;
+    if (flags & PMLB_EPI_BIAS) os << "+bias";
+    if (flags & PMLB_EPI_RESIDUAL) os << "+residual";
+    if (flags & PMLB_EPI_RELU) os << "+relu";
+    if (!chain.empty() && chain.back().flag == 0) os << "+cast";
+    pd->fused = os.str();
+  }
+
+  // Per-variable strides of every tensor if all its dims are pure variables.
+  bool pureStrides(const Simplified& s, size_t t, const TensorShape& shape, std::vector<VarUse>* out) const {
+    out->assign(s.n, VarUse());
+    const std::vector<int64_t> st = shape.denseStrides();
+    for (size_t d = 0; d < shape.rank(); ++d) {
+      const int v = pureVar(s, t, d);
+      if (v == -1) return false;
+      if (v == -2) continue;
+      if ((*out)[v].present) return false;  // diagonal access
+      (*out)[v].present = true;
+      (*out)[v].stride = st[d];
+    }
+    return true;
+  }
+
+  struct Merged {
+    bool any = false;
+    int64_t extent = 1;
+    int64_t strideOut = 0, strideA = 0, strideB = 0;
+  };
+
+  // Merges the variables of one class (ordered outer to inner by `key` stride) into a
+  // single dimension; false if they are not contiguous in every tensor holding them.
+  static bool mergeClass(const std::vector<int>& vars, const Simplified& s, const std::vector<VarUse>& o,
+                         const std::vector<VarUse>& a, const std::vector<VarUse>& b, int keyTensor, Merged* m) {
+    std::vector<int> order = vars;
+    auto key = [&](int v) {
+      return keyTensor == 0 ? o[v].stride : (keyTensor == 1 ? a[v].stride : b[v].stride);
+    };
+    std::sort(order.begin(), order.end(), [&](int x, int y) { return key(x) > key(y); });
+    m->any = !order.empty();
+    m->extent = 1;
+    for (size_t i = 0; i < order.size(); ++i) {
+      const int v = order[i];
+      m->extent *= s.extent[v];
+      if (i + 1 < order.size()) {
+        const int w = order[i + 1];
+        if (o[v].present && o[v].stride != o[w].stride * s.extent[w]) return false;
+        if (a[v].present && a[v].stride != a[w].stride * s.extent[w]) return false;
+        if (b[v].present && b[v].stride != b[w].stride * s.extent[w]) return false;
+      }
+    }
+    if (!order.empty()) {
+      const int inner = order.back();
+      m->strideOut = o[inner].stride;
+      m->strideA = a[inner].stride;
+      m->strideB = b[inner].stride;
+    }
+    return true;
+  }
+
+  bool tryGemm(Pending* pd, const Simplified& s) {
+    const POp& op = prog_.ops[pd->op];
+    if (op.operands.size() != 2) return false;
+    const TensorShape& outShape = val(op.result).shape;
+    for (int order = 0; order < 2; ++order) {
+      const int opA = op.operands[order], opB = op.operands[1 - order];
+      const size_t tA = 1 + order, tB = 2 - order;
+      int a, b, inDtype, outDtype;
+      if (!tcTypes(opA, opB, outShape.dtype, &a, &b, &inDtype, &outDtype)) return false;
+      std::vector<VarUse> uo, ua, ub;
+      if (!pureStrides(s, 0, outShape, &uo) || !pureStrides(s, tA, val(opA).shape, &ua) ||
+          !pureStrides(s, tB, val(opB).shape, &ub)) {
+        return false;
+      }
+      std::vector<int> mv, nv, kv, bv;
+      bool bad = false;
+      for (size_t i = 0; i < s.n; ++i) {
+        if (s.extent[i] <= 1) continue;
+        const bool io = uo[i].present, ia = ua[i].present, ib = ub[i].present;
+        if (io && ia && ib) bv.push_back(static_cast<int>(i));
+        else if (io && ia) mv.push_back(static_cast<int>(i));
+        else if (io && ib) nv.push_back(static_cast<int>(i));
+        else if (ia && ib) kv.push_back(static_cast<int>(i));
+        else bad = true;
+      }
+      if (bad || kv.empty()) continue;
+      Merged M, N, K, B;
+      if (!mergeClass(mv, s, uo, ua, ub, 0, &M) || !mergeClass(nv, s, uo, ua, ub, 0, &N) ||
+          !mergeClass(kv, s, uo, ua, ub, 1, &K) || !mergeClass(bv, s, uo, ua, ub, 0, &B)) {
+        continue;
+      }
+      // layout the kernel takes: out [batch][m][n] with n contiguous, A with k contiguous
+      if (N.any && N.strideOut != 1) continue;
+      if (K.strideA != 1) continue;
+      const bool bIsNk = K.strideB == 1 && (!N.any || N.strideB >= K.extent);
+      const bool bIsKn = N.any ? (N.strideB == 1 && K.strideB >= N.extent) : false;
+      if (!bIsNk && !bIsKn) continue;
+      if (M.extent > INT32_MAX || N.extent > INT32_MAX || K.extent > INT32_MAX || B.extent > INT32_MAX) continue;
+      // batch must be outermost in the output
+      if (B.any && M.any && B.strideOut < M.strideOut * M.extent) continue;
+      pmlb_gemm_desc d;
+      std::memset(&d, 0, sizeof(d));
+      d.in_dtype = inDtype;
+      d.m = static_cast<int32_t>(M.extent);
+      d.n = static_cast<int32_t>(N.extent);
+      d.k = static_cast<int32_t>(K.extent);
+      d.batch = static_cast<int32_t>(B.extent);
+      d.lda = M.any ? M.strideA : K.extent;
+      d.ldc = M.any ? M.strideOut : N.extent;
+      d.b_is_nk = bIsNk ? 1 : 0;
+      d.ldb = bIsNk ? (N.any ? N.strideB : K.extent) : K.strideB;
+      d.stride_a = B.any ? B.strideA : 0;
+      d.stride_b = B.any ? B.strideB : 0;
+      d.stride_c = B.any ? B.strideOut : 0;
+      if (d.lda < d.k || d.ldc < d.n) continue;
+      if (inDtype != PMLB_F32) {
+        // rows of A (and of a [n][k] B) must start on 16-byte boundaries for TMA
+        const int64_t eb = inDtype == PMLB_I8 ? 1 : 2;
+        if ((d.lda * eb) % 16 != 0 || (d.stride_a * eb) % 16 != 0) continue;
+        if (bIsNk && ((d.ldb * eb) % 16 != 0 || (d.stride_b * eb) % 16 != 0)) continue;
+      }
+      pd->kind = Pending::Gemm;
+      pd->a = a;
+      pd->b = b;
+      pd->inputs = {a, b};
+      int epi = 0;
+      fuseEpilogue(pd, inDtype, &outDtype, N.extent, &epi);
+      d.out_dtype = outDtype;
+      d.epilogue = epi;
+      d.ldr = d.ldc;
+      d.stride_r = d.stride_c;
+      pd->gemm = d;
+      return true;
+    }
+    return false;
+  }
+
+  // out[n, x0, x1, co] += I[n, s0*x0 + d0*k0 - p0, s1*x1 + d1*k1 - p1, ci] * F[k0, k1, ci, co]
+  bool tryConv(Pending* pd, const Simplified& s) {
+    const POp& op = prog_.ops[pd->op];
+    if (op.operands.size() != 2) return false;
+    const TensorShape& outShape = val(op.result).shape;
+    if (outShape.rank() != 4) return false;
+    for (int order = 0; order < 2; ++order) {
+      const int opI = op.operands[order], opF = op.operands[1 - order];
+      const size_t tI = 1 + order, tF = 2 - order;
+      const TensorShape& is = val(opI).shape;
+      const TensorShape& fs = val(opF).shape;
+      if (is.rank() != 4 || fs.rank() != 4) continue;
+      const int vn = pureVar(s, 0, 0), vx0 = pureVar(s, 0, 1), vx1 = pureVar(s, 0, 2), vco = pureVar(s, 0, 3);
+      const int vk0 = pureVar(s, tF, 0), vk1 = pureVar(s, tF, 1), vci = pureVar(s, tF, 2), vco2 = pureVar(s, tF, 3);
+      if (vn == -1 || vx0 == -1 || vx1 == -1 || vco < 0 || vk0 == -1 || vk1 == -1 || vci < 0 || vco2 != vco) continue;
+      if (pureVar(s, tI, 0) != vn || pureVar(s, tI, 3) != vci) continue;
+      // spatial dims of the input: stride * x + dilation * k - pad
+      int64_t stride[2] = {1, 1}, dil[2] = {1, 1}, pad[2] = {0, 0};
+      const int vx[2] = {vx0, vx1}, vk[2] = {vk0, vk1};
+      bool okSpatial = true;
+      for (int d = 0; d < 2 && okSpatial; ++d) {
+        const auto& row = s.coef[tI][1 + d];
+        for (size_t i = 0; i < s.n; ++i) {
+          if (row[i] == 0) continue;
+          if (static_cast<int>(i) == vx[d]) stride[d] = row[i];
+          else if (static_cast<int>(i) == vk[d]) dil[d] = row[i];
+          else okSpatial = false;
+        }
+        if (vx[d] >= 0 && row[vx[d]] <= 0) okSpatial = false;
+        if (vk[d] >= 0 && row[vk[d]] <= 0) okSpatial = false;
+        pad[d] = -s.cst[tI][1 + d];
+        if (pad[d] < 0) okSpatial = false;
+      }
+      if (!okSpatial) continue;
+      // every variable must be one of the seven
+      std::set<int> known = {vn, vx0, vx1, vco, vk0, vk1, vci};
+      bool extra = false;
+      for (size_t i = 0; i < s.n; ++i) {
+        if (s.extent[i] > 1 && !known.count(static_cast<int>(i))) extra = true;
+      }
+      if (extra) continue;
+      auto ext = [&](int v) { return v >= 0 ? s.extent[v] : 1; };
+      // the recognised variables must span the tensors completely
+      if (ext(vn) != outShape.sizes[0] || ext(vx0) != outShape.sizes[1] || ext(vx1) != outShape.sizes[2] ||
+          ext(vco) != outShape.sizes[3] || ext(vk0) != fs.sizes[0] || ext(vk1) != fs.sizes[1] ||
+          ext(vci) != fs.sizes[2] || ext(vci) != is.sizes[3] || ext(vn) != is.sizes[0]) {
+        continue;
+      }
+      int a, b, inDtype, outDtype;
+      if (!tcTypes(opI, opF, outShape.dtype, &a, &b, &inDtype, &outDtype)) continue;
+      if (inDtype != PMLB_BF16 && inDtype != PMLB_F16) continue;
+      if (is.sizes[3] % 8 != 0) continue;
+      // plain 1x1 stride-1 convolutions are GEMMs; let that path take them
+      if (fs.sizes[0] == 1 && fs.sizes[1] == 1 && stride[0] == 1 && stride[1] == 1 && pad[0] == 0 && pad[1] == 0) {
+        return false;
+      }
+      pmlb_conv_desc d;
+      std::memset(&d, 0, sizeof(d));
+      d.in_dtype = inDtype;
+      d.n = static_cast<int32_t>(is.sizes[0]);
+      d.h = static_cast<int32_t>(is.sizes[1]);
+      d.w = static_cast<int32_t>(is.sizes[2]);
+      d.c = static_cast<int32_t>(is.sizes[3]);
+      d.r = static_cast<int32_t>(fs.sizes[0]);
+      d.s = static_cast<int32_t>(fs.sizes[1]);
+      d.k = static_cast<int32_t>(fs.sizes[3]);
+      d.p = static_cast<int32_t>(outShape.sizes[1]);
+      d.q = static_cast<int32_t>(outShape.sizes[2]);
+      d.stride_h = static_cast<int32_t>(stride[0]);
+      d.stride_w = static_cast<int32_t>(stride[1]);
+      d.pad_h = static_cast<int32_t>(pad[0]);
+      d.pad_w = static_cast<int32_t>(pad[1]);
+      d.dil_h = static_cast<int32_t>(dil[0]);
+      d.dil_w = static_cast<int32_t>(dil[1]);
+      if (d.pad_h > 127 || d.pad_w > 127 || d.stride_h > 8 || d.stride_w > 8) continue;
+      pd->kind = Pending::Conv;
+      pd->a = a;
+      pd->b = b;
+      pd->inputs = {a, b};
+      int epi = 0;
+      fuseEpilogue(pd, inDtype, &outDtype, outShape.sizes[3], &epi);
+      d.out_dtype = outDtype;
+      d.epilogue = epi;
+      pd->conv = d;
+      return true;
+    }
+    return false;
+  }
+
+  // out[outer..., inner...] = agg over reduce... of in[outer..., reduce..., inner...]
+  bool tryReduce(Pending* pd, const Simplified& s) {
+    const POp& op = prog_.ops[pd->op];
+    const BoundedContraction& c = *op.c;
+    if (op.operands.size() != 1) return false;
+    const int src = throughCastForReduce(op.operands[0], val(op.result).shape.dtype, c.agg);
+    const TensorShape& outShape = val(op.result).shape;
+    const TensorShape& inShape = val(op.operands[0]).shape;
+    std::vector<VarUse> uo, ui;
+    if (!pureStrides(s, 0, outShape, &uo) || !pureStrides(s, 1, inShape, &ui)) return false;
+    // walk the input dims outer -> inner: kept dims, then reduced dims, then kept dims
+    int phase = 0;  // 0 outer, 1 reduce, 2 inner
+    int64_t outer = 1, red = 1, inner = 1;
+    std::vector<int> keptOrder;
+    for (size_t d = 0; d < inShape.rank(); ++d) {
+      const int v = pureVar(s, 1, d);
+      if (v == -1) return false;
+      if (v == -2) {
+        if (inShape.sizes[d] != 1) return false;  // a fixed slice of a larger dim
+        continue;
+      }
+      if (s.extent[v] != inShape.sizes[d]) return false;
+      const bool kept = uo[v].present;
+      if (kept) {
+        if (phase == 1) phase = 2;
+        (phase == 0 ? outer : inner) *= s.extent[v];
+        keptOrder.push_back(v);
+      } else {
+        if (phase == 2) return false;
+        phase = 1;
+        red *= s.extent[v];
+      }
+    }
+    // kept variables must appear in the output in the same order, densely
+    std::vector<int> outOrder;
+    for (size_t d = 0; d < outShape.rank(); ++d) {
+      const int v = pureVar(s, 0, d);
+      if (v == -1) return false;
+      if (v == -2) {
+        if (outShape.sizes[d] != 1) return false;
+        continue;
+      }
+      if (s.extent[v] != outShape.sizes[d]) return false;
+      outOrder.push_back(v);
+    }
+    if (outOrder != keptOrder) return false;
+    const DType inDt = val(src).shape.dtype, outDt = outShape.dtype;
+    pmlb_reduce_desc d;
+    std::memset(&d, 0, sizeof(d));
+    d.agg = pmlbAgg(c.agg);
+    d.dtype = static_cast<int>(inDt);
+    d.out_dtype = static_cast<int>(outDt);
+    d.outer = outer;
+    d.reduce = red;
+    d.inner = inner;
+    d.scale = 1.0;
+    const bool typesOk = (inDt == outDt && (inDt == DType::f32 || inDt == DType::bf16 || inDt == DType::f16 ||
+                                            inDt == DType::si32 || inDt == DType::si8)) ||
+                         (outDt == DType::f32 && (inDt == DType::bf16 || inDt == DType::f16));
+    if (!typesOk) return false;
+    pd->kind = Pending::Reduce;
+    pd->reduce = d;
+    pd->a = src;
+    pd->inputs = {src};
+    return true;
+  }
+
+  // sum(cast(x: 16-bit float -> f32)) can read x directly (the widening is exact); for
+  // max / min only when nothing else is gained, so keep the cast there.
+  int throughCastForReduce(int v, DType resultType, AggKind agg) const {
+    if (agg != AggKind::add || resultType != DType::f32) return v;
+    const int c = throughCast(v);
+    const DType t = val(c).shape.dtype;
+    return (t == DType::bf16 || t == DType::f16) ? c : v;
+  }
+
+  // out[n, x0, x1, c] = agg I[n, s0*x0 + k0 - p0, s1*x1 + k1 - p1, c]
+  bool tryPool(Pending* pd, const Simplified& s) {
+    const POp& op = prog_.ops[pd->op];
+    const BoundedContraction& c = *op.c;
+    if (op.operands.size() != 1) return false;
+    const TensorShape& outShape = val(op.result).shape;
+    const TensorShape& is = val(op.operands[0]).shape;
+    if (outShape.rank() != 4 || is.rank() != 4 || is.dtype != outShape.dtype) return false;
+    const int vn = pureVar(s, 0, 0), vx0 = pureVar(s, 0, 1), vx1 = pureVar(s, 0, 2), vc = pureVar(s, 0, 3);
+    if (vn == -1 || vx0 == -1 || vx1 == -1 || vc == -1) return false;
+    if (pureVar(s, 1, 0) != vn || pureVar(s, 1, 3) != vc) return false;
+    int64_t stride[2] = {1, 1}, pad[2] = {0, 0}, win[2] = {1, 1};
+    const int vx[2] = {vx0, vx1};
+    int vk[2] = {-1, -1};
+    for (int d = 0; d < 2; ++d) {
+      const auto& row = s.coef[1][1 + d];
+      for (size_t i = 0; i < s.n; ++i) {
+        if (row[i] == 0) continue;
+        if (static_cast<int>(i) == vx[d]) {
+          stride[d] = row[i];
+        } else if (vk[d] < 0 && row[i] == 1) {
+          vk[d] = static_cast<int>(i);
+          win[d] = s.extent[i];
+        } else {
+          return false;
+        }
+      }
+      if (vx[d] >= 0 && stride[d] <= 0) return false;
+      pad[d] = -s.cst[1][1 + d];
+      if (pad[d] < 0) return false;
+    }
+    if (vk[0] >= 0 && vk[0] == vk[1]) return false;
+    std::set<int> known = {vn, vx0, vx1, vc, vk[0], vk[1]};
+    for (size_t i = 0; i < s.n; ++i) {
+      if (s.extent[i] > 1 && !known.count(static_cast<int>(i))) return false;
+    }
+    // window variables must not appear in the output
+    for (int d = 0; d < 2; ++d) {
+      if (vk[d] >= 0) {
+        for (size_t od = 0; od < 4; ++od) {
+          if (s.coef[0][od][vk[d]] != 0) return false;
+        }
+      }
+    }
+    auto ext = [&](int v) { return v >= 0 ? s.extent[v] : 1; };
+    if (ext(vn) != outShape.sizes[0] || ext(vx0) != outShape.sizes[1] || ext(vx1) != outShape.sizes[2] ||
+        ext(vc) != outShape.sizes[3] || ext(vn) != is.sizes[0] || ext(vc) != is.sizes[3]) {
+      return false;
+    }
+    if (win[0] == 1 && win[1] == 1 && stride[0] == 1 && stride[1] == 1) return false;  // a copy, not a pool
+    const DType dt = is.dtype;
+    if (!(dt == DType::f32 || dt == DType::bf16 || dt == DType::f16 || dt == DType::si32 || dt == DType::si8)) return false;
+    pmlb_pool_desc d;
+    std::memset(&d, 0, sizeof(d));
+    d.agg = pmlbAgg(c.agg);
+    d.dtype = static_cast<int>(dt);
+    d.n = static_cast<int32_t>(is.sizes[0]);
+    d.h = static_cast<int32_t>(is.sizes[1]);
+    d.w = static_cast<int32_t>(is.sizes[2]);
+    d.c = static_cast<int32_t>(is.sizes[3]);
+    d.r = static_cast<int32_t>(win[0]);
+    d.s = static_cast<int32_t>(win[1]);
+    d.p = static_cast<int32_t>(outShape.sizes[1]);
+    d.q = static_cast<int32_t>(outShape.sizes[2]);
+    d.stride_h = static_cast<int32_t>(stride[0]);
+    d.stride_w = static_cast<int32_t>(stride[1]);
+    d.pad_h = static_cast<int32_t>(pad[0]);
+    d.pad_w = static_cast<int32_t>(pad[1]);
+    pd->kind = Pending::Pool;
+    pd->pool = d;
+    pd->a = op.operands[0];
+    pd->inputs = {op.operands[0]};
+    return true;
+  }
+
+  // ------------------------------------------------------------ memory
+  void allocate(const std::vector<bool>& needed) {
+    const size_t nv = prog_.values.size();
+    exe_->dev_.assign(nv, nullptr);
+    std::vector<size_t> offset(nv, 0);
+    size_t total = 0;
+    for (size_t v = 0; v < nv; ++v) {
+      const PValue& pv = prog_.values[v];
+      if (pv.kind == PValue::LiteralValue) continue;
+      if (alias_[v] >= 0) continue;
+      const bool arg = pv.kind == PValue::Input;
+      if (!needed[v] && !arg) continue;
+      size_t bytes = pv.shape.byteSize();
+      if (bytes == 0) bytes = 16;
+      offset[v] = total;
+      total += (bytes + 255) / 256 * 256;
+    }
+    exe_->arenaBytes_ = total ? total : 256;
+    cudaCheck(cudaMalloc(reinterpret_cast<void**>(&exe_->arena_), exe_->arenaBytes_), "cudaMalloc(program arena)");
+    for (size_t v = 0; v < nv; ++v) {
+      const PValue& pv = prog_.values[v];
+      if (pv.kind == PValue::LiteralValue || alias_[v] >= 0) continue;
+      if (!needed[v] && pv.kind != PValue::Input) continue;
+      exe_->dev_[v] = exe_->arena_ + offset[v];
+    }
+    for (size_t v = 0; v < nv; ++v) {
+      if (alias_[v] >= 0) exe_->dev_[v] = exe_->dev_[root(static_cast<int>(v))];
+    }
+    // constants are uploaded once, like the reference packs them in its `init` closure
+    for (size_t v = 0; v < nv; ++v) {
+      const PValue& pv = prog_.values[v];
+      if ((pv.kind == PValue::Constant || pv.kind == PValue::InternalConstant) && exe_->dev_[v]) {
+        cudaCheck(cudaMemcpyAsync(exe_->dev_[v], pv.constant->data(), pv.shape.byteSize(), cudaMemcpyHostToDevice,
+                                  exe_->stream_),
+                  "upload of a constant");
+      }
+    }
+    cudaCheck(cudaStreamSynchronize(exe_->stream_), "constant upload");
+  }
+
+  char* dev(int v) const {
+    char* p = exe_->dev_[v];
+    if (!p) throw std::runtime_error("internal: value %" + std::to_string(v) + " was never materialised");
+    return p;
+  }
+
+  // ------------------------------------------------------------ kernel plans
+  void emit(const Pending& pd) {
+    const POp& op = prog_.ops[pd.op];
+    Step st;
+    const std::string label = op.label.empty() ? op.mnemonic : op.label;
+    switch (pd.kind) {
+      case Pending::Gemm: {
+        pmlb_plan* plan = nullptr;
+        pmlb_status rc = pmlb_gemm_dispatch(&pd.gemm, &plan);
+        if (rc == PMLB_ERR_UNSUPPORTED) {
+          emitGenericFallback(pd, std::string("tensor-core GEMM not applicable: ") + pmlb_last_error());
+          return;
+        }
+        pmlbCheck(rc, "gemm dispatch for '" + label + "'");
+        pmlbCheck(pmlb_plan_share_status(plan, exe_->status_), "status word");
+        st.plan = plan;
+        st.kernel = "tc_gemm";
+        std::ostringstream os;
+        os << label << " b" << pd.gemm.batch << " m" << pd.gemm.m << " n" << pd.gemm.n << " k" << pd.gemm.k
+           << " in=" << dtypeName(static_cast<DType>(pd.gemm.in_dtype)) << " out=" << dtypeName(static_cast<DType>(pd.gemm.out_dtype))
+           << (pd.gemm.b_is_nk ? " B[n][k]" : " B[k][n]") << pd.fused;
+        st.detail = os.str();
+        st.launches = 1 + (pd.gemm.in_dtype == PMLB_F32 ? 2 : 0);
+        const void* a = dev(pd.a);
+        const void* b = dev(pd.b);
+        void* c = dev(pd.result);
+        const void* bias = pd.bias >= 0 ? dev(pd.bias) : nullptr;
+        const void* res = pd.residual >= 0 ? dev(pd.residual) : nullptr;
+        st.launch = [plan, a, b, c, bias, res](cudaStream_t s) {
+          return pmlb_gemm_invoke(plan, s, a, b, c, bias, res, nullptr);
+        };
+        break;
+      }
+      case Pending::Conv: {
+        pmlb_plan* plan = nullptr;
+        pmlb_status rc = pmlb_conv_dispatch(&pd.conv, &plan);
+        if (rc == PMLB_ERR_UNSUPPORTED) {
+          emitGenericFallback(pd, std::string("implicit-GEMM convolution not applicable: ") + pmlb_last_error());
+          return;
+        }
+        pmlbCheck(rc, "conv dispatch for '" + label + "'");
+        pmlbCheck(pmlb_plan_share_status(plan, exe_->status_), "status word");
+        st.plan = plan;
+        st.kernel = "tc_conv";
+        std::ostringstream os;
+        const pmlb_conv_desc& d = pd.conv;
+        os << label << " n" << d.n << " " << d.h << "x" << d.w << "x" << d.c << " (*) " << d.r << "x" << d.s << "/"
+           << d.stride_h << " pad" << d.pad_h << " -> " << d.p << "x" << d.q << "x" << d.k
+           << " out=" << dtypeName(static_cast<DType>(d.out_dtype)) << pd.fused;
+        st.detail = os.str();
+        const void* x = dev(pd.a);
+        const void* f = dev(pd.b);
+        void* out = dev(pd.result);
+        const void* bias = pd.bias >= 0 ? dev(pd.bias) : nullptr;
+        const void* res = pd.residual >= 0 ? dev(pd.residual) : nullptr;
+        const int fdt = static_cast<int>(val(pd.b).shape.dtype);
+        const PValue::Kind fk = val(root(pd.b)).kind;
+        if (fk == PValue::Constant || fk == PValue::InternalConstant) {
+          // weights known now: lay them out once
+          pmlbCheck(pmlb_conv_set_filter(plan, exe_->stream_, f, fdt), "filter layout");
+          st.launch = [plan, x, out, bias, res](cudaStream_t s) { return pmlb_conv_invoke(plan, s, x, out, bias, res); };
+        } else {
+          st.launches = 2;
+          st.launch = [plan, x, f, fdt, out, bias, res](cudaStream_t s) {
+            pmlb_status r = pmlb_conv_set_filter(plan, s, f, fdt);
+            if (r != PMLB_OK) return r;
+            return pmlb_conv_invoke(plan, s, x, out, bias, res);
+          };
+        }
+        break;
+      }
+      case Pending::Reduce: {
+        pmlb_plan* plan = nullptr;
+        pmlb_status rc = pmlb_reduce_dispatch(&pd.reduce, &plan);
+        if (rc == PMLB_ERR_UNSUPPORTED) {
+          emitGenericFallback(pd, "reduction kernel not applicable");
+          return;
+        }
+        pmlbCheck(rc, "reduce dispatch for '" + label + "'");
+        st.plan = plan;
+        st.kernel = pmlb_plan_kind(plan);
+        std::ostringstream os;
+        os << label << " outer" << pd.reduce.outer << " reduce" << pd.reduce.reduce << " inner" << pd.reduce.inner;
+        st.detail = os.str();
+        const void* in = dev(pd.a);
+        void* out = dev(pd.result);
+        st.launch = [plan, in, out](cudaStream_t s) { return pmlb_reduce_invoke(plan, s, in, out); };
+        break;
+      }
+      case Pending::Pool: {
+        pmlb_plan* plan = nullptr;
+        pmlb_status rc = pmlb_pool_dispatch(&pd.pool, &plan);
+        if (rc == PMLB_ERR_UNSUPPORTED) {
+          emitGenericFallback(pd, "pooling kernel not applicable");
+          return;
+        }
+        pmlbCheck(rc, "pool dispatch for '" + label + "'");
+        st.plan = plan;
+        st.kernel = "nhwc_pool";
+        std::ostringstream os;
+        os << label << " " << pd.pool.r << "x" << pd.pool.s << "/" << pd.pool.stride_h;
+        st.detail = os.str();
+        const void* in = dev(pd.a);
+        void* out = dev(pd.result);
+        st.launch = [plan, in, out](cudaStream_t s) { return pmlb_pool_invoke(plan, s, in, out); };
+        break;
+      }
+      case Pending::Generic:
+        emitGeneric(pd, "");
+        return;
+      case Pending::Eltwise:
+        emitEltwise(pd);
+        return;
+    }
+    exe_->steps_.push_back(std::move(st));
+  }
+
+  // A specialised plan was refused at dispatch: undo its fusions and run the contraction,
+  // then the fused element-wise operations, on the general kernels.
+  void emitGenericFallback(const Pending& pd, const std::string& why) {
+    const POp& op = prog_.ops[pd.op];
+    if (pd.result != op.result) {
+      throw std::runtime_error("Contraction '" + op.label + "': " + why +
+                               " (after its consumers were fused; re-run with PLAIDML_CUDA_GENERIC_ONLY=1)");
+    }
+    // operands that were reached through casts are read with their own types
+    Pending g = pd;
+    g.kind = Pending::Generic;
+    std::vector<int> ins;
+    if (pd.kind == Pending::Gemm || pd.kind == Pending::Conv) {
+      // keep the looked-through sources in the original operand order
+      ins = pd.swapped ? std::vector<int>{pd.b, pd.a} : std::vector<int>{pd.a, pd.b};
+      // operand order of the contraction is that of op.operands; match by looking through casts
+      std::vector<int> ordered;
+      for (int o : op.operands) {
+        const int t = throughCast(o);
+        ordered.push_back((t == pd.a || t == pd.b) ? t : o);
+      }
+      ins = ordered;
+    } else {
+      ins = {pd.a};
+    }
+    g.inputs = ins;
+    emitGeneric(g, why);
+  }
+
+  void emitGeneric(const Pending& pd, const std::string& why) {
+    const POp& op = prog_.ops[pd.op];
+    const BoundedContraction& c = *op.c;
+    const TensorShape& outShape = val(op.result).shape;
+    if (c.nIdx() > PMLB_MAX_IDX) throw std::runtime_error("Contraction uses more than 10 index variables");
+    if (c.cons.size() > PMLB_MAX_CONS) throw std::runtime_error("Contraction has more than 8 constraints");
+    pmlb_contract_desc d;
+    std::memset(&d, 0, sizeof(d));
+    d.agg = pmlbAgg(c.agg);
+    d.combo = pmlbCombo(c.combo);
+    d.n_idx = static_cast<int32_t>(c.nIdx());
+    d.n_src = static_cast<int32_t>(c.srcs.size());
+    for (size_t i = 0; i < c.nIdx(); ++i) d.range[i] = c.extent[i];
+    auto fill = [&](pmlb_access* acc, const std::vector<Affine>& forms, const TensorShape& shape, DType dt) {
+      if (shape.rank() > PMLB_MAX_RANK) throw std::runtime_error("Tensors of rank above 8 are not supported");
+      acc->dtype = static_cast<int32_t>(dt);
+      acc->rank = static_cast<int32_t>(shape.rank());
+      const std::vector<int64_t> st = shape.denseStrides();
+      for (size_t dd = 0; dd < shape.rank(); ++dd) {
+        acc->sizes[dd] = shape.sizes[dd];
+        acc->strides[dd] = st[dd];
+        const Affine& a = forms[dd];
+        int64_t den = a.constant.den;
+        for (size_t i = 0; i < c.nIdx(); ++i) {
+          const int64_t di = i < a.coef.size() ? a.coef[i].den : 1;
+          den = den / std::__gcd(den, di) * di;
+        }
+        Rational k = a.constant;
+        for (size_t i = 0; i < c.nIdx(); ++i) {
+          const Rational ci = i < a.coef.size() ? a.coef[i] : Rational(0);
+          k = k + ci * Rational(c.lower[i]);
+          acc->coef[dd][i] = static_cast<int32_t>(ci.num * (den / ci.den));
+        }
+        acc->off[dd] = k.num * (den / k.den);
+        acc->den[dd] = static_cast<int32_t>(den);
+      }
+    };
+    fill(&d.out, c.sink, outShape, outShape.dtype);
+    std::vector<const void*> srcPtrs;
+    for (size_t s2 = 0; s2 < c.srcs.size(); ++s2) {
+      const int v = pd.inputs.size() > s2 ? pd.inputs[s2] : op.operands[s2];
+      fill(&d.src[s2], c.srcs[s2], val(op.operands[s2]).shape, val(v).shape.dtype);
+      srcPtrs.push_back(dev(v));
+    }
+    while (srcPtrs.size() < 3) srcPtrs.push_back(nullptr);
+    d.n_cons = static_cast<int32_t>(c.cons.size());
+    for (size_t q = 0; q < c.cons.size(); ++q) {
+      const Affine& a = c.cons[q].first;
+      int64_t den = a.constant.den;
+      for (size_t i = 0; i < c.nIdx(); ++i) {
+        const int64_t di = i < a.coef.size() ? a.coef[i].den : 1;
+        den = den / std::__gcd(den, di) * di;
+      }
+      Rational k = a.constant;
+      for (size_t i = 0; i < c.nIdx(); ++i) {
+        const Rational ci = i < a.coef.size() ? a.coef[i] : Rational(0);
+        k = k + ci * Rational(c.lower[i]);
+        d.cons_coef[q][i] = static_cast<int32_t>(ci.num * (den / ci.den));
+      }
+      // 0 <= form < bound, scaled by the common denominator
+      d.cons_off[q] = k.num * (den / k.den);
+      d.cons_range[q] = c.cons[q].second * den;
+    }
+    const void* initPtr = nullptr;
+    if (c.hasInit) {
+      const int iv = op.operands.back();
+      const TensorShape& is = val(iv).shape;
+      d.has_init = 1;
+      d.init.dtype = static_cast<int32_t>(is.dtype);
+      d.init.rank = static_cast<int32_t>(outShape.rank());
+      const std::vector<int64_t> st = is.denseStrides();
+      const size_t shift = outShape.rank() - is.rank();
+      for (size_t dd = 0; dd < outShape.rank(); ++dd) {
+        d.init.sizes[dd] = outShape.sizes[dd];
+        d.init.den[dd] = 1;
+        if (dd < shift) {
+          d.init.strides[dd] = 0;
+        } else {
+          const size_t sd = dd - shift;
+          d.init.strides[dd] = (is.sizes[sd] == 1 && outShape.sizes[dd] != 1) ? 0 : st[sd];
+        }
+      }
+      initPtr = dev(iv);
+    }
+    pmlb_plan* plan = nullptr;
+    pmlbCheck(pmlb_contract_dispatch(&d, &plan), "general contraction dispatch for '" + op.label + "'");
+    Step st;
+    st.plan = plan;
+    st.kernel = "generic_contract";
+    st.detail = (op.label.empty() ? std::string("contract") : op.label) + " -> " + outShape.str() +
+                (why.empty() ? "" : " [" + why + "]");
+    void* out = dev(op.result);
+    const void* s0 = srcPtrs[0];
+    const void* s1 = srcPtrs[1];
+    const void* s2p = srcPtrs[2];
+    st.launch = [plan, s0, s1, s2p, initPtr, out](cudaStream_t s) {
+      return pmlb_contract_invoke(plan, s, s0, s1, s2p, initPtr, out);
+    };
+    exe_->steps_.push_back(std::move(st));
+  }
+
+  void emitEltwise(const Pending& pd) {
+    const POp& op = prog_.ops[pd.op];
+    const TensorShape& outShape = val(op.result).shape;
+    if (outShape.rank() > PMLB_MAX_RANK) throw std::runtime_error("Tensors of rank above 8 are not supported");
+    if (op.operands.size() > 3) throw std::runtime_error("Element-wise '" + op.mnemonic + "' takes more than three operands");
+    pmlb_eltwise_desc d;
+    std::memset(&d, 0, sizeof(d));
+    std::strncpy(d.op, op.mnemonic.c_str(), sizeof(d.op) - 1);
+    d.n_in = static_cast<int32_t>(op.operands.size());
+    d.rank = static_cast<int32_t>(outShape.rank());
+    d.out_dtype = static_cast<int32_t>(outShape.dtype);
+    for (size_t i = 0; i < outShape.rank(); ++i) d.sizes[i] = outShape.sizes[i];
+    const void* ins[3] = {nullptr, nullptr, nullptr};
+    for (size_t k = 0; k < op.operands.size(); ++k) {
+      const TensorShape& is = val(op.operands[k]).shape;
+      d.in_dtype[k] = static_cast<int32_t>(is.dtype);
+      const std::vector<int64_t> st = is.denseStrides();
+      if (is.rank() > outShape.rank()) throw std::runtime_error("Element-wise operand has higher rank than the result");
+      const size_t shift = outShape.rank() - is.rank();
+      for (size_t dd = shift; dd < outShape.rank(); ++dd) {
+        const size_t sd = dd - shift;
+        d.in_strides[k][dd] = (is.sizes[sd] == 1 && outShape.sizes[dd] != 1) ? 0 : st[sd];
+      }
+      ins[k] = dev(op.operands[k]);
+    }
+    pmlb_plan* plan = nullptr;
+    pmlbCheck(pmlb_eltwise_dispatch(&d, &plan), "element-wise dispatch for '" + op.mnemonic + "'");
+    Step st;
+    st.plan = plan;
+    st.kernel = "eltwise";
+    st.detail = op.mnemonic + " -> " + outShape.str();
+    void* out = dev(op.result);
+    const void* i0 = ins[0];
+    const void* i1 = ins[1];
+    const void* i2 = ins[2];
+    st.launch = [plan, i0, i1, i2, out](cudaStream_t s) { return pmlb_eltwise_invoke(plan, s, i0, i1, i2, out); };
+    exe_->steps_.push_back(std::move(st));
+  }
+
+  Executable* exe_;
+  const Program& prog_;
+  std::vector<int> uses_;
+  std::vector<bool> isOutput_;
+  std::vector<std::vector<int>> users_;
+  std::vector<bool> absorbed_;
+  std::vector<int> alias_;
+  std::vector<Pending> pending_;
+};
+
+// ==================================================================== executable
+
+Executable::Executable(std::shared_ptr<Program> program, int device) : prog_(std::move(program)), device_(device) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    throw std::runtime_error("No CUDA device is available; the cuda target has no CPU execution path");
+  }
+  if (device < 0 || device >= count) throw std::runtime_error("No such device: cuda." + std::to_string(device));
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  int major = 0;
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device_);
+  if (major != 10) throw std::runtime_error("cuda." + std::to_string(device) + " is not an sm_100 device");
+  for (int id : prog_->inputs) {
+    if (!prog_->values[id].shape.isDense()) throw std::runtime_error("The cuda target takes dense row-major inputs");
+  }
+  cudaCheck(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+  cudaCheck(cudaEventCreate(&evStart_), "cudaEventCreate");
+  cudaCheck(cudaEventCreate(&evStop_), "cudaEventCreate");
+  cudaCheck(cudaMalloc(reinterpret_cast<void**>(&status_), sizeof(int)), "cudaMalloc(status)");
+  cudaCheck(cudaMemset(status_, 0, sizeof(int)), "cudaMemset(status)");
+  try {
+    Planner planner(this);
+    planner.run();
+    cudaCheck(cudaStreamSynchronize(stream_), "executable set-up");
+  } catch (...) {
+    for (Step& s : steps_) pmlb_plan_free(s.plan);
+    steps_.clear();
+    if (arena_) cudaFree(arena_);
+    cudaFree(status_);
+    cudaEventDestroy(evStart_);
+    cudaEventDestroy(evStop_);
+    cudaStreamDestroy(stream_);
+    throw;
+  }
+}
+
+Executable::~Executable() {
+  cudaSetDevice(device_);
+  if (stream_) cudaStreamSynchronize(stream_);
+  for (Step& s : steps_) pmlb_plan_free(s.plan);
+  if (arena_) cudaFree(arena_);
+  if (status_) cudaFree(status_);
+  if (evStart_) cudaEventDestroy(evStart_);
+  if (evStop_) cudaEventDestroy(evStop_);
+  if (stream_) cudaStreamDestroy(stream_);
+}
+
+void Executable::enqueueSteps() {
+  for (Step& s : steps_) {
+    const pmlb_status rc = s.launch(stream_);
+    if (rc != PMLB_OK) throw std::runtime_error("Kernel step '" + s.kernel + " " + s.detail + "' failed: " + pmlb_last_error());
+  }
+}
+
+void Executable::checkStatus() {
+  int code = 0;
+  cudaCheck(cudaMemcpyAsync(&code, status_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "status readback");
+  cudaCheck(cudaStreamSynchronize(stream_), "run");
+  if (code != 0) {
+    cudaMemset(status_, 0, sizeof(int));
+    throw std::runtime_error("A device-side pipeline wait gave up (role code " + std::to_string(code) + ")");
+  }
+}
+
+double Executable::run(const std::vector<BufferPtr>& inputs, const std::vector<BufferPtr>& outputs) {
+  // argument checks of plaidml_executable_run (plaidml/exec/ffi.cc:92-120)
+  if (inputs.size() != prog_->inputs.size()) {
+    throw std::runtime_error("Program expects " + std::to_string(prog_->inputs.size()) + " inputs, but " +
+                             std::to_string(inputs.size()) + " were specified");
+  }
+  if (outputs.size() != prog_->outputs.size()) {
+    throw std::runtime_error("Program expects " + std::to_string(prog_->outputs.size()) + " outputs, but " +
+                             std::to_string(outputs.size()) + " were specified");
+  }
+  for (size_t i = 0; i < inputs.size(); ++i) {
+    const TensorShape& want = prog_->values[prog_->inputs[i]].shape;
+    if (inputs[i]->shape() != want) {
+      throw std::runtime_error("Shape mismatch for input buffer " + std::to_string(i) + ", expected '" + want.str() +
+                               "' but '" + inputs[i]->shape().str() + "' was specified");
+    }
+  }
+  for (size_t i = 0; i < outputs.size(); ++i) {
+    const TensorShape& want = prog_->values[prog_->outputs[i]].shape;
+    if (outputs[i]->shape() != want) {
+      throw std::runtime_error("Shape mismatch for output buffer " + std::to_string(i) + ", expected '" + want.str() +
+                               "' but '" + outputs[i]->shape().str() + "' was specified");
+    }
+  }
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  const auto t0 = std::chrono::steady_clock::now();
+  for (size_t i = 0; i < inputs.size(); ++i) {
+    const int id = prog_->inputs[i];
+    const size_t bytes = prog_->values[id].shape.byteSize();
+    if (bytes) {
+      cudaCheck(cudaMemcpyAsync(dev_[id], inputs[i]->data(), bytes, cudaMemcpyHostToDevice, stream_), "input upload");
+    }
+  }
+  inputsResident_ = true;
+  enqueueSteps();
+  for (size_t i = 0; i < outputs.size(); ++i) {
+    const int id = prog_->outputs[i];
+    const size_t bytes = prog_->values[id].shape.byteSize();
+    if (bytes) {
+      cudaCheck(cudaMemcpyAsync(outputs[i]->data(), dev_[id], bytes, cudaMemcpyDeviceToHost, stream_), "output download");
+    }
+  }
+  checkStatus();
+  const auto t1 = std::chrono::steady_clock::now();
+  return std::chrono::duration<double, std::milli>(t1 - t0).count();
+}
+
+double Executable::runResident(size_t iters) {
+  if (!inputsResident_) throw std::runtime_error("run the executable once before re-running it on resident inputs");
+  if (iters == 0) return 0.0;
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  cudaCheck(cudaEventRecord(evStart_, stream_), "cudaEventRecord");
+  for (size_t i = 0; i < iters; ++i) enqueueSteps();
+  cudaCheck(cudaEventRecord(evStop_, stream_), "cudaEventRecord");
+  checkStatus();
+  float ms = 0.f;
+  cudaCheck(cudaEventElapsedTime(&ms, evStart_, evStop_), "cudaEventElapsedTime");
+  return static_cast<double>(ms) / static_cast<double>(iters);
+}
+
+std::string Executable::describe() const {
+  std::ostringstream os;
+  for (const Step& s : steps_) os << s.kernel << " " << s.detail << "\n";
+  return os.str();
+}
+
+size_t Executable::launchCount() const {
+  size_t n = 0;
+  for (const Step& s : steps_) n += static_cast<size_t>(s.launches);
+  return n;
+}
+
+void* Executable::outputDevicePtr(size_t index, size_t* nbytes) const {
+  if (index >= prog_->outputs.size()) throw std::runtime_error("No such output");
+  const int id = prog_->outputs[index];
+  if (nbytes) *nbytes = prog_->values[id].shape.byteSize();
+  return dev_[id];
+}
+
+// ==================================================================== devices / targets
+
+std::vector<std::string> listDevices() {
+  std::vector<std::string> out;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess) {
+    cudaGetLastError();
+    return out;
+  }
+  for (int d = 0; d < count; ++d) {
+    int major = 0;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, d);
+    if (major == 10) out.push_back("cuda." + std::to_string(d));
+  }
+  return out;
+}
+
+int parseDeviceId(const std::string& id) {
+  static const std::regex re("([a-zA-Z0-9_]+(?:-[a-zA-Z0-9_]+)*)\\.([0-9]+)");
+  std::smatch m;
+  if (!std::regex_match(id, m, re)) throw std::runtime_error("Invalid device id: '" + id + "'");
+  if (m[1].str() != "cuda") throw std::runtime_error("Unknown runtime '" + m[1].str() + "': the only device family is 'cuda'");
+  return std::stoi(m[2].str());
+}
+
+std::vector<std::string> listTargets() { return {"cuda"}; }
+
+}  // namespace pml

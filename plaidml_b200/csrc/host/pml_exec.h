@@ -1,0 +1,76 @@
+// The `cuda` target and device: planning of a program into kernel steps and its execution.
+//
+// Stands where the reference has pmlc/target/x86 (pipeline.cc:259-402: bounds, padding,
+// stencil recognition, gemm+bias+relu combining) and pmlc/rt (jit_executable.cc:340-526:
+// argument binding, one-time constant packing, invoke).  Differences by design:
+//   - recognition works on the bounded contraction's per-tensor strides, like the
+//     reference's GEMM stencil (pmlc/dialect/pxa/transforms/stencil_gemm.cc:296-321), but
+//     selects a whole-problem kernel instead of a tile size;
+//   - every value lives in device memory between steps; host buffers are touched only by
+//     the input upload and the output download of plaidml_executable_run;
+//   - there is no CPU execution path: a contraction no specialised kernel covers runs on the
+//     general CUDA contraction kernel.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <functional>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "pml_program.h"
+#include "pmlb_kernels.h"
+
+namespace pml {
+
+struct Step {
+  std::string kernel;   // kernel family, e.g. "tc_gemm"
+  std::string detail;   // human-readable description (operation name, shape, fusions)
+  pmlb_plan* plan = nullptr;
+  int launches = 1;     // kernel launches this step enqueues
+  std::function<pmlb_status(cudaStream_t)> launch;
+};
+
+class Executable {
+ public:
+  Executable(std::shared_ptr<Program> program, int device);
+  ~Executable();
+  Executable(const Executable&) = delete;
+  Executable& operator=(const Executable&) = delete;
+
+  double run(const std::vector<BufferPtr>& inputs, const std::vector<BufferPtr>& outputs);
+  double runResident(size_t iters);
+  std::string describe() const;
+  size_t launchCount() const;
+  void* outputDevicePtr(size_t index, size_t* nbytes) const;
+  cudaStream_t stream() const { return stream_; }
+  const Program& program() const { return *prog_; }
+
+ private:
+  friend class Planner;
+  void enqueueSteps();
+  void checkStatus();
+
+  std::shared_ptr<Program> prog_;
+  int device_ = 0;
+  cudaStream_t stream_ = nullptr;
+  cudaEvent_t evStart_ = nullptr, evStop_ = nullptr;
+  char* arena_ = nullptr;
+  size_t arenaBytes_ = 0;
+  std::vector<char*> dev_;        // device address per value id (null if never materialised)
+  std::vector<Step> steps_;
+  int* status_ = nullptr;          // device word shared by all tensor-core plans
+  bool inputsResident_ = false;
+};
+
+// Device ids follow the reference's pattern name(-name)*.N (pmlc/rt/device_id.cc:13-38).
+std::vector<std::string> listDevices();
+int parseDeviceId(const std::string& id);  // "cuda.3" -> 3; throws on anything else
+std::vector<std::string> listTargets();
+
+}  // namespace pml
+
+struct plaidml_executable {
+  std::shared_ptr<pml::Executable> exec;
+};

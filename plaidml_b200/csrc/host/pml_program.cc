@@ -1,0 +1,617 @@
+// Lowering of the expression tree to the flat program, including contraction bounds.
+#include "pml_program.h"
+
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <limits>
+#include <numeric>
+#include <sstream>
+
+namespace pml {
+
+// ------------------------------------------------------------------ rationals
+
+Rational::Rational(int64_t n, int64_t d) {
+  if (d == 0) throw std::runtime_error("Division by zero in index expression");
+  if (d < 0) {
+    n = -n;
+    d = -d;
+  }
+  const int64_t g = std::gcd(n < 0 ? -n : n, d);
+  num = g ? n / g : n;
+  den = g ? d / g : d;
+}
+Rational operator+(Rational a, Rational b) { return Rational(a.num * b.den + b.num * a.den, a.den * b.den); }
+Rational operator-(Rational a, Rational b) { return Rational(a.num * b.den - b.num * a.den, a.den * b.den); }
+Rational operator*(Rational a, Rational b) { return Rational(a.num * b.num, a.den * b.den); }
+Rational operator/(Rational a, Rational b) { return Rational(a.num * b.den, a.den * b.num); }
+
+static int64_t floorDiv(int64_t a, int64_t b) {
+  int64_t q = a / b;
+  if ((a % b != 0) && ((a < 0) != (b < 0))) --q;
+  return q;
+}
+static int64_t ceilR(Rational r) { return -floorDiv(-r.num, r.den); }
+static int64_t floorR(Rational r) { return floorDiv(r.num, r.den); }
+
+// ------------------------------------------------------------------ index polynomials
+
+size_t IndexNumbering::indexOf(const PolyNode* node) {
+  auto it = ids_.find(node);
+  if (it != ids_.end()) return it->second;
+  const size_t id = names_.size();
+  ids_[node] = id;
+  names_.push_back(node->name.empty() ? "x" + std::to_string(id) : node->name);
+  return id;
+}
+
+static bool isConstant(const Affine& a) {
+  for (const Rational& c : a.coef) {
+    if (!c.isZero()) return false;
+  }
+  return true;
+}
+
+Affine evalPoly(const PolyPtr& poly, IndexNumbering* idxs, Evaluator* ev) {
+  Affine out;
+  switch (poly->kind) {
+    case PolyNode::Dim:
+      out.constant = Rational(ev->evaluate(poly->dim));
+      return out;
+    case PolyNode::Literal:
+      out.constant = Rational(poly->value);
+      return out;
+    case PolyNode::Index: {
+      const size_t id = idxs->indexOf(poly.get());
+      out.resize(id + 1);
+      out.coef[id] = Rational(1);
+      return out;
+    }
+    case PolyNode::Op: {
+      if (poly->op == AffineOp::Neg) {
+        if (poly->operands.size() != 1) throw std::runtime_error("Negation takes one operand");
+        Affine a = evalPoly(poly->operands[0], idxs, ev);
+        for (auto& c : a.coef) c = Rational(0) - c;
+        a.constant = Rational(0) - a.constant;
+        return a;
+      }
+      if (poly->operands.size() != 2) throw std::runtime_error("Binary index operation takes two operands");
+      Affine a = evalPoly(poly->operands[0], idxs, ev);
+      Affine b = evalPoly(poly->operands[1], idxs, ev);
+      const size_t n = std::max(a.coef.size(), b.coef.size());
+      a.resize(n);
+      b.resize(n);
+      switch (poly->op) {
+        case AffineOp::Add:
+          for (size_t i = 0; i < n; ++i) a.coef[i] = a.coef[i] + b.coef[i];
+          a.constant = a.constant + b.constant;
+          return a;
+        case AffineOp::Sub:
+          for (size_t i = 0; i < n; ++i) a.coef[i] = a.coef[i] - b.coef[i];
+          a.constant = a.constant - b.constant;
+          return a;
+        case AffineOp::Mul:
+          if (isConstant(b)) {
+            for (size_t i = 0; i < n; ++i) a.coef[i] = a.coef[i] * b.constant;
+            a.constant = a.constant * b.constant;
+            return a;
+          }
+          if (isConstant(a)) {
+            for (size_t i = 0; i < n; ++i) b.coef[i] = b.coef[i] * a.constant;
+            b.constant = b.constant * a.constant;
+            return b;
+          }
+          throw std::runtime_error("Non-linear polynomial: index expressions may only be multiplied by constants");
+        case AffineOp::Div:
+          if (!isConstant(b)) throw std::runtime_error("Index expressions may only be divided by constants");
+          if (b.constant.isZero()) throw std::runtime_error("Division by zero in index expression");
+          for (size_t i = 0; i < n; ++i) a.coef[i] = a.coef[i] / b.constant;
+          a.constant = a.constant / b.constant;
+          return a;
+        case AffineOp::Max:
+        case AffineOp::Min: {
+          if (!isConstant(a) || !isConstant(b)) throw std::runtime_error("max / min of index variables is not affine");
+          const bool aLess = a.constant.num * b.constant.den < b.constant.num * a.constant.den;
+          return (poly->op == AffineOp::Max) == aLess ? b : a;
+        }
+        default: break;
+      }
+      throw std::runtime_error("Invalid index operation");
+    }
+  }
+  throw std::runtime_error("Invalid index polynomial");
+}
+
+// ------------------------------------------------------------------ bounds
+
+void computeBounds(BoundedContraction* c, const TensorShape& out, const std::vector<TensorShape>& srcShapes) {
+  const size_t n = c->nIdx();
+  struct Cond {
+    Affine f;
+    int64_t bound;
+  };
+  std::vector<Cond> conds;
+  auto add = [&](Affine f, int64_t bound) {
+    f.resize(n);
+    conds.push_back({std::move(f), bound});
+  };
+  for (size_t d = 0; d < c->sink.size(); ++d) add(c->sink[d], out.sizes[d]);
+  for (size_t s = 0; s < c->srcs.size(); ++s) {
+    if (c->srcs[s].size() != srcShapes[s].rank()) {
+      throw std::runtime_error("Contraction operand is indexed with " + std::to_string(c->srcs[s].size()) +
+                               " indices but has rank " + std::to_string(srcShapes[s].rank()));
+    }
+    for (size_t d = 0; d < c->srcs[s].size(); ++d) add(c->srcs[s][d], srcShapes[s].sizes[d]);
+  }
+  for (const auto& con : c->cons) add(con.first, con.second);
+
+  constexpr int64_t kInf = std::numeric_limits<int64_t>::max() / 4;
+  std::vector<int64_t> lo(n, -kInf), hi(n, kInf);
+  bool changed = true;
+  for (int iter = 0; iter < 64 && changed; ++iter) {
+    changed = false;
+    for (const Cond& cd : conds) {
+      for (size_t j = 0; j < n; ++j) {
+        const Rational aj = cd.f.coef[j];
+        if (aj.isZero()) continue;
+        // range of the rest of the form
+        bool minFinite = true, maxFinite = true;
+        Rational rmin = cd.f.constant, rmax = cd.f.constant;
+        for (size_t i = 0; i < n; ++i) {
+          if (i == j || cd.f.coef[i].isZero()) continue;
+          const Rational ai = cd.f.coef[i];
+          const bool pos = ai.num > 0;
+          const int64_t l = pos ? lo[i] : hi[i];  // bound giving the smaller product
+          const int64_t h = pos ? hi[i] : lo[i];
+          if (l <= -kInf || l >= kInf) minFinite = false; else rmin = rmin + ai * Rational(l);
+          if (h <= -kInf || h >= kInf) maxFinite = false; else rmax = rmax + ai * Rational(h);
+        }
+        // 0 <= aj * xj + rest <= bound - 1
+        // => aj * xj >= -rmax   and   aj * xj <= bound - 1 - rmin
+        if (maxFinite) {
+          const Rational v = (Rational(0) - rmax) / aj;
+          if (aj.num > 0) {
+            const int64_t nl = ceilR(v);
+            if (nl > lo[j]) { lo[j] = nl; changed = true; }
+          } else {
+            const int64_t nh = floorR(v);
+            if (nh < hi[j]) { hi[j] = nh; changed = true; }
+          }
+        }
+        if (minFinite) {
+          const Rational v = (Rational(cd.bound - 1) - rmin) / aj;
+          if (aj.num > 0) {
+            const int64_t nh = floorR(v);
+            if (nh < hi[j]) { hi[j] = nh; changed = true; }
+          } else {
+            const int64_t nl = ceilR(v);
+            if (nl > lo[j]) { lo[j] = nl; changed = true; }
+          }
+        }
+      }
+    }
+  }
+  c->lower.assign(n, 0);
+  c->extent.assign(n, 0);
+  for (size_t i = 0; i < n; ++i) {
+    if (lo[i] <= -kInf || hi[i] >= kInf) {
+      throw std::runtime_error("Unbounded index '" + c->idxNames[i] + "' in contraction: no tensor dimension or constraint limits it");
+    }
+    c->lower[i] = lo[i];
+    c->extent[i] = hi[i] >= lo[i] ? hi[i] - lo[i] + 1 : 0;
+  }
+}
+
+// ------------------------------------------------------------------ scalar constants
+
+static uint16_t f32ToBf16(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>((u >> 16) | 0x40);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return static_cast<uint16_t>(u >> 16);
+}
+
+static uint16_t f32ToF16(float f) {
+  const __half h = __float2half_rn(f);
+  uint16_t u;
+  std::memcpy(&u, &h, 2);
+  return u;
+}
+
+BufferPtr makeScalarConstant(DType dtype, const Literal& lit) {
+  DType dt = dtype;
+  if (dt == DType::six) dt = DType::si32;
+  if (dt == DType::uix) dt = DType::ui32;
+  if (dt == DType::fx) dt = DType::f32;
+  BufferPtr buf = Buffer::allocate(TensorShape(dt));
+  const double asF = lit.kind == Literal::Float ? lit.f : (lit.kind == Literal::Signed ? static_cast<double>(lit.i) : static_cast<double>(lit.u));
+  const int64_t asI = lit.kind == Literal::Float ? static_cast<int64_t>(lit.f) : (lit.kind == Literal::Signed ? lit.i : static_cast<int64_t>(lit.u));
+  char* p = buf->data();
+  switch (dt) {
+    case DType::i1: { uint8_t v = asF != 0; std::memcpy(p, &v, 1); break; }
+    case DType::si8: case DType::ui8: { int8_t v = static_cast<int8_t>(asI); std::memcpy(p, &v, 1); break; }
+    case DType::si16: case DType::ui16: { int16_t v = static_cast<int16_t>(asI); std::memcpy(p, &v, 2); break; }
+    case DType::si32: case DType::ui32: { int32_t v = static_cast<int32_t>(asI); std::memcpy(p, &v, 4); break; }
+    case DType::si64: case DType::ui64: { std::memcpy(p, &asI, 8); break; }
+    case DType::f16: { uint16_t v = f32ToF16(static_cast<float>(asF)); std::memcpy(p, &v, 2); break; }
+    case DType::bf16: { uint16_t v = f32ToBf16(static_cast<float>(asF)); std::memcpy(p, &v, 2); break; }
+    case DType::f32: { float v = static_cast<float>(asF); std::memcpy(p, &v, 4); break; }
+    case DType::f64: { std::memcpy(p, &asF, 8); break; }
+    default: throw std::runtime_error("Cannot materialise a literal of this type");
+  }
+  return buf;
+}
+
+// ------------------------------------------------------------------ printing
+
+static std::string affineStr(const Affine& a, const std::vector<std::string>& names) {
+  std::ostringstream os;
+  bool any = false;
+  for (size_t i = 0; i < a.coef.size(); ++i) {
+    if (a.coef[i].isZero()) continue;
+    if (any) os << " + ";
+    if (!(a.coef[i].num == 1 && a.coef[i].den == 1)) {
+      os << a.coef[i].num;
+      if (a.coef[i].den != 1) os << "/" << a.coef[i].den;
+      os << "*";
+    }
+    os << names[i];
+    any = true;
+  }
+  if (!a.constant.isZero() || !any) {
+    if (any) os << " + ";
+    os << a.constant.num;
+    if (a.constant.den != 1) os << "/" << a.constant.den;
+  }
+  return os.str();
+}
+
+std::string Program::str() const {
+  static const char* aggNames[] = {"assign", "add", "max", "min", "mul"};
+  static const char* comboNames[] = {"none", "add", "cond", "eq", "mul"};
+  std::ostringstream os;
+  os << "program @" << name << "(";
+  bool first = true;
+  for (int id : inputs) {
+    os << (first ? "" : ", ") << "%" << id << ": " << values[id].shape.str();
+    first = false;
+  }
+  for (int id : constants) {
+    os << (first ? "" : ", ") << "%" << id << ": " << values[id].shape.str() << " {const}";
+    first = false;
+  }
+  os << ") {\n";
+  for (const POp& op : ops) {
+    os << "  %" << op.result << " = ";
+    if (op.kind == POp::Contraction) {
+      const BoundedContraction& c = *op.c;
+      os << "tile.contract " << aggNames[static_cast<int>(c.agg)] << ", " << comboNames[static_cast<int>(c.combo)];
+      os << " sink (";
+      for (size_t d = 0; d < c.sink.size(); ++d) os << (d ? ", " : "") << affineStr(c.sink[d], c.idxNames);
+      os << ")";
+      for (size_t s = 0; s < c.srcs.size(); ++s) {
+        os << " %" << op.operands[s] << "(";
+        for (size_t d = 0; d < c.srcs[s].size(); ++d) os << (d ? ", " : "") << affineStr(c.srcs[s][d], c.idxNames);
+        os << ")";
+      }
+      if (c.hasInit) os << " init %" << op.operands.back();
+      os << " {";
+      for (size_t i = 0; i < c.nIdx(); ++i) {
+        os << (i ? ", " : "") << c.idxNames[i] << " in [" << c.lower[i] << ", " << c.lower[i] + c.extent[i] << ")";
+      }
+      os << "}";
+      for (const auto& con : c.cons) os << " where 0 <= " << affineStr(con.first, c.idxNames) << " < " << con.second;
+      if (!op.label.empty()) os << " name=\"" << op.label << "\"";
+    } else {
+      os << "tile." << op.mnemonic;
+      for (size_t i = 0; i < op.operands.size(); ++i) os << (i ? ", %" : " %") << op.operands[i];
+    }
+    os << " : " << values[op.result].shape.str() << "\n";
+  }
+  os << "  return";
+  for (size_t i = 0; i < outputs.size(); ++i) os << (i ? ", %" : " %") << outputs[i];
+  os << "\n}\n";
+  return os.str();
+}
+
+// ------------------------------------------------------------------ builder
+
+namespace {
+
+class Builder {
+ public:
+  explicit Builder(Program* p) : prog_(p) {}
+
+  int addValue(PValue v) {
+    prog_->values.push_back(std::move(v));
+    return static_cast<int>(prog_->values.size()) - 1;
+  }
+
+  int lower(const ExprPtr& e) {
+    auto it = memo_.find(e.get());
+    if (it != memo_.end()) return it->second;
+    const int id = lowerNode(e);
+    memo_[e.get()] = id;
+    return id;
+  }
+
+  void bindInput(const ExprPtr& e, const TensorShape* shape) {
+    if (e->kind != ExprNode::Input) throw std::runtime_error("Program inputs must be input placeholders");
+    if (shape && *shape != e->shape) e->shape = *shape;
+    PValue v;
+    v.kind = PValue::Input;
+    v.shape = e->shape;
+    v.name = e->name;
+    const int id = addValue(v);
+    memo_[e.get()] = id;
+    prog_->inputs.push_back(id);
+  }
+
+  int emit(POp op, const TensorShape& shape) {
+    PValue v;
+    v.kind = PValue::Temp;
+    v.shape = shape;
+    v.shape.strides.clear();
+    v.name = op.label;
+    v.def = static_cast<int>(prog_->ops.size());
+    op.result = addValue(v);
+    prog_->ops.push_back(std::move(op));
+    return prog_->ops.back().result;
+  }
+
+  // A literal operand becomes a rank-0 internal constant of `dtype`.
+  int materialise(int id, DType dtype) {
+    const PValue& v = prog_->values[id];
+    if (v.kind != PValue::LiteralValue) return id;
+    PValue c;
+    c.kind = PValue::InternalConstant;
+    c.constant = makeScalarConstant(dtype, v.literal);
+    c.shape = c.constant->shape();
+    c.name = "literal";
+    return addValue(c);
+  }
+
+  Evaluator ev;
+
+ private:
+  int literal(const ExprPtr& e, Literal lit, DType dt) {
+    (void)e;
+    PValue v;
+    v.kind = PValue::LiteralValue;
+    v.shape = TensorShape(dt);
+    v.literal = lit;
+    return addValue(v);
+  }
+
+  int lowerNode(const ExprPtr& e) {
+    switch (e->kind) {
+      case ExprNode::Input:
+        throw std::runtime_error("Input '" + e->name + "' is used by the program but was not listed among its inputs");
+      case ExprNode::ConstTensor: {
+        PValue v;
+        v.kind = PValue::Constant;
+        v.constant = e->buffer;
+        v.shape = e->buffer->shape();
+        v.name = e->name;
+        const int id = addValue(v);
+        prog_->constants.push_back(id);
+        return id;
+      }
+      case ExprNode::ConstSigned: {
+        Literal l;
+        l.kind = Literal::Signed;
+        l.i = e->ivalue;
+        return literal(e, l, DType::six);
+      }
+      case ExprNode::ConstUnsigned: {
+        Literal l;
+        l.kind = Literal::Unsigned;
+        l.u = e->uvalue;
+        return literal(e, l, DType::uix);
+      }
+      case ExprNode::ConstFloat: {
+        Literal l;
+        l.kind = Literal::Float;
+        l.f = e->fvalue;
+        return literal(e, l, DType::fx);
+      }
+      case ExprNode::Dim: {
+        Literal l;
+        l.kind = Literal::Signed;
+        l.i = ev.evaluate(e->dim);
+        return literal(e, l, DType::six);
+      }
+      case ExprNode::Pragma: return lower(e->expr);
+      case ExprNode::Element: {
+        const ExprPtr& src = e->expr;
+        if (src->kind == ExprNode::Layer) {
+          if (e->ordinal >= src->results.size()) throw std::runtime_error("Out of bounds element ordinal");
+          return lower(src->results[e->ordinal]);
+        }
+        if (e->ordinal == 0) return lower(src);
+        throw std::runtime_error("Only layers have multiple results on the cuda target");
+      }
+      case ExprNode::Layer:
+        if (e->results.size() == 1) return lower(e->results[0]);
+        throw std::runtime_error("Missing element needed to resolve multiple results.");
+      case ExprNode::Cast: {
+        const int src = lower(e->expr);
+        const TensorShape shape = ev.getShape(e);
+        if (prog_->values[src].kind == PValue::LiteralValue) return materialise(src, e->dtype);
+        if (prog_->values[src].shape.dtype == e->dtype) return src;
+        POp op;
+        op.kind = POp::Cast;
+        op.mnemonic = "cast";
+        op.operands = {src};
+        return emit(op, shape);
+      }
+      case ExprNode::Contraction: return lowerContraction(e);
+      case ExprNode::Intrinsic: return lowerIntrinsic(e);
+    }
+    throw std::runtime_error("Invalid expression node");
+  }
+
+  int lowerContraction(const ExprPtr& e) {
+    const TensorShape outShape = ev.getShape(e);
+    auto c = std::make_shared<BoundedContraction>();
+    c->agg = e->agg;
+    c->combo = e->combo;
+    const size_t need = e->combo == ComboKind::none ? 1 : (e->combo == ComboKind::cond ? 3 : 2);
+    if (e->srcs.size() != need) {
+      throw std::runtime_error("Contraction '" + e->name + "' has " + std::to_string(e->srcs.size()) +
+                               " operands but its combination takes " + std::to_string(need));
+    }
+    IndexNumbering idxs;
+    for (const PolyPtr& p : e->sinkIdxs) c->sink.push_back(evalPoly(p, &idxs, &ev));
+    std::vector<TensorShape> srcShapes;
+    POp op;
+    op.kind = POp::Contraction;
+    op.mnemonic = "contract";
+    op.label = e->name;
+    for (const PolyMap& src : e->srcs) {
+      std::vector<Affine> forms;
+      for (const PolyPtr& p : src.idxs) forms.push_back(evalPoly(p, &idxs, &ev));
+      c->srcs.push_back(std::move(forms));
+      const int id = lower(src.ref);
+      if (prog_->values[id].kind == PValue::LiteralValue) {
+        throw std::runtime_error("'contraction' operand data type is ambiguous, use a cast");
+      }
+      srcShapes.push_back(prog_->values[id].shape);
+      op.operands.push_back(id);
+    }
+    for (const Constraint& con : e->constraints) {
+      c->cons.emplace_back(evalPoly(con.lhs, &idxs, &ev), ev.evaluate(con.rhs));
+    }
+    c->idxNames = idxs.names();
+    const size_t n = c->nIdx();
+    for (Affine& a : c->sink) a.resize(n);
+    for (auto& forms : c->srcs) {
+      for (Affine& a : forms) a.resize(n);
+    }
+    for (auto& con : c->cons) con.first.resize(n);
+    computeBounds(c.get(), outShape, srcShapes);
+    if (e->init) {
+      int init = lower(e->init);
+      init = materialise(init, outShape.dtype);
+      const TensorShape& is = prog_->values[init].shape;
+      // the initial value must broadcast to the output shape
+      std::vector<TensorShape> both = {outShape, is};
+      if (inferShape(both).sizes != outShape.sizes) throw std::runtime_error("Contraction initial value does not broadcast to the result shape");
+      c->hasInit = true;
+      op.operands.push_back(init);
+    }
+    op.c = c;
+    return emit(op, outShape);
+  }
+
+  int lowerIntrinsic(const ExprPtr& e) {
+    const TensorShape shape = ev.getShape(e);
+    const std::string& name = e->op;
+    if (name == "index") {
+      int64_t axis = 0;
+      if (!getIntegerValue(&ev, e->operands[0], &axis) || axis < 0 || static_cast<size_t>(axis) >= shape.rank()) {
+        throw std::runtime_error("'index' requires a valid axis");
+      }
+      // depends on the shape only: computed here, uploaded once with the executable
+      BufferPtr buf = Buffer::allocate(shape);
+      int32_t* p = reinterpret_cast<int32_t*>(buf->data());
+      const std::vector<int64_t> st = shape.denseStrides();
+      for (int64_t i = 0; i < shape.elements(); ++i) p[i] = static_cast<int32_t>((i / st[axis]) % shape.sizes[axis]);
+      PValue v;
+      v.kind = PValue::InternalConstant;
+      v.constant = buf;
+      v.shape = shape;
+      v.name = "index";
+      return addValue(v);
+    }
+    if (name == "shape") {
+      const TensorShape src = ev.getShape(e->operands[0]);
+      BufferPtr buf = Buffer::allocate(shape);
+      int32_t* p = reinterpret_cast<int32_t*>(buf->data());
+      for (size_t i = 0; i < src.rank(); ++i) p[i] = static_cast<int32_t>(src.sizes[i]);
+      PValue v;
+      v.kind = PValue::InternalConstant;
+      v.constant = buf;
+      v.shape = shape;
+      v.name = "shape";
+      return addValue(v);
+    }
+    if (name == "reshape") {
+      const int src = lower(e->operands[0]);
+      if (prog_->values[src].shape.elements() != shape.elements()) {
+        throw std::runtime_error("'reshape' changes the number of elements");
+      }
+      POp op;
+      op.kind = POp::Reshape;
+      op.mnemonic = "reshape";
+      op.label = e->name;
+      op.operands = {src};
+      return emit(op, shape);
+    }
+    // element-wise
+    std::vector<int> ids;
+    DType promoted = DType::invalid;
+    for (const ExprPtr& o : e->operands) {
+      const int id = lower(o);
+      ids.push_back(id);
+      promoted = promote(promoted, prog_->values[id].shape.dtype);
+    }
+    if (name == "select" && ids.size() == 3) {
+      // the condition keeps its type; the branches are promoted together
+      promoted = promote(prog_->values[ids[1]].shape.dtype, prog_->values[ids[2]].shape.dtype);
+      ids[0] = materialise(ids[0], DType::i1);
+      ids[1] = materialise(ids[1], promoted);
+      ids[2] = materialise(ids[2], promoted);
+    } else {
+      for (int& id : ids) id = materialise(id, promoted);
+    }
+    POp op;
+    op.kind = POp::Eltwise;
+    op.mnemonic = name;
+    op.label = e->name;
+    op.operands = ids;
+    TensorShape result = shape;
+    if (isAmbiguous(result.dtype)) {
+      result.dtype = result.dtype == DType::fx ? DType::f32 : (result.dtype == DType::six ? DType::si32 : DType::ui32);
+    }
+    return emit(op, result);
+  }
+
+  Program* prog_;
+  std::unordered_map<const ExprNode*, int> memo_;
+};
+
+}  // namespace
+
+std::shared_ptr<Program> buildProgram(const std::string& name, const std::vector<ExprPtr>& inputs,
+                                      const std::vector<const TensorShape*>& shapes,
+                                      const std::vector<ExprPtr>& outputs) {
+  auto prog = std::make_shared<Program>();
+  prog->name = name;
+  Builder b(prog.get());
+  for (size_t i = 0; i < inputs.size(); ++i) b.bindInput(inputs[i], i < shapes.size() ? shapes[i] : nullptr);
+  std::vector<int> seen;
+  for (const ExprPtr& out : outputs) {
+    int id = b.lower(out);
+    const PValue::Kind kind = prog->values[id].kind;
+    if (kind == PValue::LiteralValue) id = b.materialise(id, prog->values[id].shape.dtype);
+    const bool dup = std::find(seen.begin(), seen.end(), id) != seen.end();
+    if (prog->values[id].kind != PValue::Temp || dup) {
+      // outputs are distinct buffers written by the program (pmlc/ast/builder.cc:560-590)
+      POp op;
+      op.kind = POp::Eltwise;
+      op.mnemonic = "ident";
+      op.operands = {id};
+      id = b.emit(op, prog->values[id].shape);
+    }
+    seen.push_back(id);
+    prog->outputs.push_back(id);
+  }
+  return prog;
+}
+
+}  // namespace pml

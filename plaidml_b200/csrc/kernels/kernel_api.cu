@@ -80,6 +80,7 @@ struct pmlb_plan {
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   int* status = nullptr;  // device word shared by the plan's tensor-core launches
+  bool owns_status = true;
 
   pmlb_gemm_desc gemm;
   long long kpad = 0;       // fp32 path: padded K of the split copies
@@ -190,8 +191,16 @@ void pmlb_debug_set_trace(void* device_buffer) {
 void pmlb_plan_free(pmlb_plan* plan) {
   if (!plan) return;
   if (plan->scratch) cudaFree(plan->scratch);
-  if (plan->status) cudaFree(plan->status);
+  if (plan->status && plan->owns_status) cudaFree(plan->status);
   delete plan;
+}
+
+pmlb_status pmlb_plan_share_status(pmlb_plan* plan, int* device_word) {
+  if (!plan || !device_word) return fail(PMLB_ERR_INVALID, "null argument");
+  if (plan->status && plan->owns_status) cudaFree(plan->status);
+  plan->status = device_word;
+  plan->owns_status = false;
+  return PMLB_OK;
 }
 
 size_t pmlb_plan_scratch_bytes(const pmlb_plan* plan) { return plan ? plan->scratch_bytes : 0; }

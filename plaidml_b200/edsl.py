@@ -1,0 +1,522 @@
+"""The Tile EDSL in Python: ``TensorDim``, ``TensorIndex``, ``Tensor``, ``Contraction`` and the
+element-wise intrinsics, over the C calls of ``include/plaidml_ffi.h``.
+
+API mirror of the reference's ``plaidml/edsl/__init__.py:32-1180`` (same class and function
+names, same operator overloads) so that programs written against it run unchanged.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+from .core import Buffer, DType, Program, TensorShape
+from .ffi import ForeignObject, decode_str, ffi, ffi_call, lib
+
+
+# ---------------------------------------------------------------------- dims
+
+def _as_dim(x) -> "TensorDim":
+    if isinstance(x, TensorDim):
+        return x
+    if isinstance(x, (int, np.integer)):
+        return TensorDim(expr=ffi_call(lib.plaidml_dim_expr_int, int(x)))
+    raise TypeError(f"cannot use {type(x).__name__} as a tensor dimension")
+
+
+def _dim_op(op, *args) -> "TensorDim":
+    raw = [_as_dim(a).as_ptr() for a in args]
+    return TensorDim(expr=ffi_call(lib.plaidml_dim_expr_op, op, len(raw), raw))
+
+
+class TensorDim(ForeignObject):
+    """A symbolic tensor dimension, bound to a size by ``Tensor.bind_dims``."""
+
+    __ffi_del__ = lib.plaidml_dim_expr_free
+    __ffi_repr__ = lib.plaidml_dim_expr_repr
+
+    def __init__(self, expr=None):
+        if expr is None:
+            expr = ffi_call(lib.plaidml_dim_expr_none)
+        elif isinstance(expr, (int, np.integer)):
+            expr = ffi_call(lib.plaidml_dim_expr_int, int(expr))
+        super().__init__(expr)
+
+    def _bind(self, expr):
+        self.take_ptr()
+        self._ffi_obj = expr
+
+    def __neg__(self):
+        return _dim_op(lib.PLAIDML_INT_OP_NEG, self)
+
+    def __add__(self, o):
+        return _dim_op(lib.PLAIDML_INT_OP_ADD, self, o)
+
+    def __radd__(self, o):
+        return _dim_op(lib.PLAIDML_INT_OP_ADD, o, self)
+
+    def __sub__(self, o):
+        return _dim_op(lib.PLAIDML_INT_OP_SUB, self, o)
+
+    def __rsub__(self, o):
+        return _dim_op(lib.PLAIDML_INT_OP_SUB, o, self)
+
+    def __mul__(self, o):
+        return _dim_op(lib.PLAIDML_INT_OP_MUL, self, o)
+
+    def __rmul__(self, o):
+        return _dim_op(lib.PLAIDML_INT_OP_MUL, o, self)
+
+    def __floordiv__(self, o):
+        return _dim_op(lib.PLAIDML_INT_OP_DIV, self, o)
+
+    def __rfloordiv__(self, o):
+        return _dim_op(lib.PLAIDML_INT_OP_DIV, o, self)
+
+
+def dim_max(a, b):
+    return _dim_op(lib.PLAIDML_INT_OP_MAX, a, b)
+
+
+def dim_min(a, b):
+    return _dim_op(lib.PLAIDML_INT_OP_MIN, a, b)
+
+
+# ---------------------------------------------------------------------- indices
+
+def _as_poly(x) -> "TensorIndex":
+    if isinstance(x, TensorIndex):
+        return x
+    if isinstance(x, (int, np.integer)):
+        return TensorIndex(expr=ffi_call(lib.plaidml_poly_expr_literal, int(x)))
+    if isinstance(x, TensorDim):
+        return TensorIndex(expr=ffi_call(lib.plaidml_poly_expr_dim, x.as_ptr()))
+    raise TypeError(f"cannot use {type(x).__name__} in an index expression")
+
+
+def _poly_op(op, *args) -> "TensorIndex":
+    raw = [_as_poly(a).as_ptr() for a in args]
+    return TensorIndex(expr=ffi_call(lib.plaidml_poly_expr_op, op, len(raw), raw))
+
+
+class Constraint:
+    """``lhs < rhs`` (and implicitly ``0 <= lhs``)."""
+
+    def __init__(self, lhs, rhs):
+        self.lhs = lhs
+        self.rhs = rhs
+
+
+class TensorIndex(ForeignObject):
+    """An index variable of a contraction, or an affine expression of such variables."""
+
+    __ffi_del__ = lib.plaidml_poly_expr_free
+    __ffi_repr__ = lib.plaidml_poly_expr_repr
+
+    def __init__(self, expr=None, name=""):
+        if expr is None:
+            expr = ffi_call(lib.plaidml_poly_expr_index, name.encode())
+        super().__init__(expr)
+
+    def __lt__(self, rhs):
+        return Constraint(self, _as_dim(rhs))
+
+    def __neg__(self):
+        return _poly_op(lib.PLAIDML_INT_OP_NEG, self)
+
+    def __add__(self, o):
+        return _poly_op(lib.PLAIDML_INT_OP_ADD, self, o)
+
+    def __radd__(self, o):
+        return _poly_op(lib.PLAIDML_INT_OP_ADD, o, self)
+
+    def __sub__(self, o):
+        return _poly_op(lib.PLAIDML_INT_OP_SUB, self, o)
+
+    def __rsub__(self, o):
+        return _poly_op(lib.PLAIDML_INT_OP_SUB, o, self)
+
+    def __mul__(self, o):
+        return _poly_op(lib.PLAIDML_INT_OP_MUL, self, o)
+
+    def __rmul__(self, o):
+        return _poly_op(lib.PLAIDML_INT_OP_MUL, o, self)
+
+    def __floordiv__(self, o):
+        return _poly_op(lib.PLAIDML_INT_OP_DIV, self, o)
+
+    def __rfloordiv__(self, o):
+        return _poly_op(lib.PLAIDML_INT_OP_DIV, o, self)
+
+
+def TensorDims(count):
+    return [TensorDim() for _ in range(count)]
+
+
+def TensorIndexes(count):
+    return [TensorIndex() for _ in range(count)]
+
+
+# ---------------------------------------------------------------------- tensors
+
+class IndexedTensor:
+    """``T[i, j]`` or a combination of such accesses inside a contraction."""
+
+    def __init__(self, op, ref=None, idxs=None, args=None):
+        self._op = op
+        self._ref = ref
+        self._idxs = idxs
+        self._args = args
+
+    def __add__(self, rhs):
+        return IndexedTensor(lib.PLAIDML_COMBO_OP_ADD, args=(self, rhs))
+
+    def __mul__(self, rhs):
+        return IndexedTensor(lib.PLAIDML_COMBO_OP_MUL, args=(self, rhs))
+
+    def __eq__(self, rhs):
+        return IndexedTensor(lib.PLAIDML_COMBO_OP_EQ, args=(self, rhs))
+
+
+def cond(lhs, rhs, true_case):
+    """``(lhs == rhs) ? true_case : 0`` as a contraction combination."""
+    return IndexedTensor(lib.PLAIDML_COMBO_OP_COND, args=(lhs, rhs, true_case))
+
+
+def _as_tensor(x) -> "Tensor":
+    if isinstance(x, Tensor):
+        return x
+    if isinstance(x, bool):
+        return Tensor(expr=ffi_call(lib.plaidml_expr_int, int(x)))
+    if isinstance(x, (int, np.integer)):
+        return Tensor(expr=ffi_call(lib.plaidml_expr_int, int(x)))
+    if isinstance(x, (float, np.floating)):
+        return Tensor(expr=ffi_call(lib.plaidml_expr_float, float(x)))
+    if isinstance(x, TensorDim):
+        return Tensor(expr=ffi_call(lib.plaidml_expr_dim, x.as_ptr()))
+    raise TypeError(f"cannot use {type(x).__name__} as a tensor")
+
+
+def intrinsic(fn, *args, name=""):
+    tensors = [_as_tensor(a) for a in args]
+    raw = [t.as_ptr() for t in tensors]
+    return Tensor(expr=ffi_call(lib.plaidml_expr_intrinsic, fn.encode(), len(raw), raw, name.encode()))
+
+
+class Tensor(ForeignObject):
+    __ffi_del__ = lib.plaidml_expr_free
+    __ffi_repr__ = lib.plaidml_expr_repr
+
+    def __init__(self, expr=None, value=None):
+        if expr is None:
+            if value is None:
+                raise ValueError("a Tensor needs an expression or a literal value")
+            expr = _as_tensor(value).take_ptr()
+        super().__init__(expr)
+
+    def __getitem__(self, key):
+        if not isinstance(key, (tuple, list)):
+            key = (key,)
+        return IndexedTensor(lib.PLAIDML_COMBO_OP_NONE, ref=self, idxs=tuple(key))
+
+    def __hash__(self):
+        return id(self)
+
+    # element-wise arithmetic
+    def __neg__(self):
+        return intrinsic("neg", self)
+
+    def __invert__(self):
+        return intrinsic("bit_not", self)
+
+    def __add__(self, o):
+        return intrinsic("add", self, o)
+
+    def __radd__(self, o):
+        return intrinsic("add", o, self)
+
+    def __sub__(self, o):
+        return intrinsic("sub", self, o)
+
+    def __rsub__(self, o):
+        return intrinsic("sub", o, self)
+
+    def __mul__(self, o):
+        return intrinsic("mul", self, o)
+
+    def __rmul__(self, o):
+        return intrinsic("mul", o, self)
+
+    def __truediv__(self, o):
+        return intrinsic("div", self, o)
+
+    def __rtruediv__(self, o):
+        return intrinsic("div", o, self)
+
+    __div__ = __truediv__
+    __rdiv__ = __rtruediv__
+
+    def __mod__(self, o):
+        return intrinsic("mod", self, o)
+
+    def __eq__(self, o):
+        return intrinsic("cmp_eq", self, o)
+
+    def __ne__(self, o):
+        return intrinsic("cmp_ne", self, o)
+
+    def __lt__(self, o):
+        return intrinsic("cmp_lt", self, o)
+
+    def __gt__(self, o):
+        return intrinsic("cmp_gt", self, o)
+
+    def __le__(self, o):
+        return intrinsic("cmp_le", self, o)
+
+    def __ge__(self, o):
+        return intrinsic("cmp_ge", self, o)
+
+    def __lshift__(self, o):
+        return intrinsic("bit_shl", self, o)
+
+    def __rshift__(self, o):
+        return intrinsic("bit_shr", self, o)
+
+    def __and__(self, o):
+        return intrinsic("bit_and", self, o)
+
+    def __or__(self, o):
+        return intrinsic("bit_or", self, o)
+
+    def __xor__(self, o):
+        return intrinsic("bit_xor", self, o)
+
+    # shape queries
+    def compute_shape(self) -> TensorShape:
+        return TensorShape(ptr=ffi_call(lib.plaidml_expr_get_shape, self.as_ptr()))
+
+    @property
+    def dtype(self) -> DType:
+        return DType(ffi_call(lib.plaidml_expr_get_dtype, self.as_ptr()))
+
+    @property
+    def rank(self) -> int:
+        return ffi_call(lib.plaidml_expr_get_rank, self.as_ptr())
+
+    def bind_dims(self, *dims):
+        """Binds unbound ``TensorDim`` objects to this tensor's sizes and checks bound ones."""
+        dims = [d if isinstance(d, TensorDim) else _as_dim(d) for d in dims]
+        handles = [d.as_ptr() for d in dims]
+        ffi_call(lib.plaidml_expr_bind_dims, self.as_ptr(), len(handles), handles)
+
+    def element(self, ordinal):
+        return Tensor(expr=ffi_call(lib.plaidml_expr_element, self.as_ptr(), ordinal))
+
+
+class Contraction:
+    """``Contraction().outShape(..).outAccess(..).sum(A[i, k] * B[k, j]).build()``"""
+
+    def __init__(self, name=""):
+        self._name = name
+        self._dims = ()
+        self._idxs = ()
+        self._constraints = []
+        self._rhs = None
+        self._agg = None
+        self._init = None
+
+    def outShape(self, *dims):
+        self._dims = dims[0] if len(dims) == 1 and isinstance(dims[0], (list, tuple)) else dims
+        return self
+
+    def outAccess(self, *idxs):
+        self._idxs = idxs[0] if len(idxs) == 1 and isinstance(idxs[0], (list, tuple)) else idxs
+        return self
+
+    def _set(self, agg, rhs):
+        self._agg = agg
+        self._rhs = rhs
+        return self
+
+    def assign(self, rhs):
+        return self._set(lib.PLAIDML_AGG_OP_ASSIGN, rhs)
+
+    def max(self, rhs):
+        return self._set(lib.PLAIDML_AGG_OP_MAX, rhs)
+
+    def min(self, rhs):
+        return self._set(lib.PLAIDML_AGG_OP_MIN, rhs)
+
+    def product(self, rhs):
+        return self._set(lib.PLAIDML_AGG_OP_PROD, rhs)
+
+    def sum(self, rhs):
+        return self._set(lib.PLAIDML_AGG_OP_SUM, rhs)
+
+    def init(self, rhs):
+        self._init = rhs
+        return self
+
+    def add_constraint(self, constraint):
+        self._constraints.append(constraint)
+        return self
+
+    def add_constraints(self, constraints):
+        self._constraints.extend(constraints)
+        return self
+
+    def build(self) -> Tensor:
+        rhs = self._rhs
+        if isinstance(rhs, Tensor):
+            rhs = IndexedTensor(lib.PLAIDML_COMBO_OP_NONE, ref=rhs, idxs=())
+        elif not isinstance(rhs, IndexedTensor):
+            rhs = IndexedTensor(lib.PLAIDML_COMBO_OP_NONE, ref=_as_tensor(rhs), idxs=())
+        dims = [_as_dim(d) for d in self._dims]
+        idxs = [_as_poly(i) for i in self._idxs]
+        init = self._init.as_ptr() if self._init is not None else ffi.NULL
+        tensor = Tensor(expr=ffi_call(lib.plaidml_expr_contraction, self._agg, rhs._op, len(idxs),
+                                      [i.as_ptr() for i in idxs], [d.as_ptr() for d in dims], init,
+                                      self._name.encode()))
+        operands = [rhs] if rhs._op == lib.PLAIDML_COMBO_OP_NONE else list(rhs._args)
+        for operand in operands:
+            if not isinstance(operand, IndexedTensor) or operand._ref is None:
+                raise TypeError("contraction operands must be indexed tensors, e.g. A[i, k]")
+            polys = [_as_poly(i) for i in operand._idxs]
+            ffi_call(lib.plaidml_contraction_add_operand, tensor.as_ptr(), operand._ref.as_ptr(), len(polys),
+                     [p.as_ptr() for p in polys])
+        for c in self._constraints:
+            ffi_call(lib.plaidml_contraction_add_constraint, tensor.as_ptr(), c.lhs.as_ptr(), c.rhs.as_ptr())
+        ffi_call(lib.plaidml_contraction_build, tensor.as_ptr())
+        return tensor
+
+
+def Placeholder(dtype_or_shape, dims=(), name=""):
+    if isinstance(dtype_or_shape, TensorShape):
+        shape = dtype_or_shape
+    elif isinstance(dtype_or_shape, DType):
+        shape = TensorShape(dtype_or_shape, dims)
+    else:
+        raise TypeError(f"Unsupported type {type(dtype_or_shape)} for dtype_or_shape")
+    return Tensor(expr=ffi_call(lib.plaidml_expr_input, shape.as_ptr(), name.encode()))
+
+
+def Constant(buffer_or_array, name="", dtype=None):
+    """A constant tensor from a ``Buffer`` or a numpy array (``dtype`` relabels uint16 as bf16)."""
+    if isinstance(buffer_or_array, Buffer):
+        buf = buffer_or_array
+    else:
+        arr = np.ascontiguousarray(buffer_or_array)
+        shape = TensorShape(dtype if dtype is not None else DType.from_numpy(arr.dtype), arr.shape)
+        buf = Buffer(shape)
+        buf.copy_from_ndarray(arr)
+    t = Tensor(expr=ffi_call(lib.plaidml_expr_constant, buf.as_ptr(), name.encode()))
+    t._buffer = buf
+    return t
+
+
+# ---------------------------------------------------------------------- intrinsics
+
+def cast(x, dtype):
+    return Tensor(expr=ffi_call(lib.plaidml_expr_cast, _as_tensor(x).as_ptr(), int(dtype)))
+
+
+def _unary(name):
+    def fn(x):
+        return intrinsic(name, x)
+    fn.__name__ = name
+    fn.__doc__ = f"Element-wise ``{name}``."
+    return fn
+
+
+abs = _unary("abs")
+ceil = _unary("ceil")
+cos = _unary("cos")
+cosh = _unary("cosh")
+exp = _unary("exp")
+floor = _unary("floor")
+ident = _unary("ident")
+log = _unary("log")
+relu = _unary("relu")
+round = _unary("round")
+sigmoid = _unary("sigmoid")
+sin = _unary("sin")
+sinh = _unary("sinh")
+sqrt = _unary("sqrt")
+tan = _unary("tan")
+tanh = _unary("tanh")
+erf = _unary("erf")
+
+
+def max(x, y):
+    return intrinsic("max", x, y)
+
+
+def min(x, y):
+    return intrinsic("min", x, y)
+
+
+def pow(x, y):
+    return intrinsic("pow", x, y)
+
+
+def select(cond_, true_case, false_case):
+    return intrinsic("select", cond_, true_case, false_case)
+
+
+def reshape(x, dims):
+    return intrinsic("reshape", x, *dims)
+
+
+def index(dims, axis):
+    return intrinsic("index", axis, *dims)
+
+
+def shape(x):
+    return intrinsic("shape", x)
+
+
+def trace(x, msg):
+    """Accepted for compatibility; the cuda target records no host-side trace points."""
+    return x
+
+
+# ---------------------------------------------------------------------- values (op-library arguments)
+
+class Value(ForeignObject):
+    __ffi_del__ = lib.plaidml_value_free
+    __ffi_repr__ = lib.plaidml_value_repr
+
+    def __init__(self, value):
+        if isinstance(value, Value):
+            ptr = ffi_call(lib.plaidml_value_clone, value.as_ptr())
+        elif isinstance(value, ffi.CData):
+            ptr = value
+        elif value is None:
+            ptr = ffi_call(lib.plaidml_value_none)
+        elif isinstance(value, bool):
+            ptr = ffi_call(lib.plaidml_value_int, int(value))
+        elif isinstance(value, (int, np.integer)):
+            ptr = ffi_call(lib.plaidml_value_int, int(value))
+        elif isinstance(value, TensorDim):
+            ptr = ffi_call(lib.plaidml_value_dim, value.as_ptr())
+        elif isinstance(value, (float, np.floating)):
+            ptr = ffi_call(lib.plaidml_value_float, float(value))
+        elif isinstance(value, Tensor):
+            ptr = ffi_call(lib.plaidml_value_expr, value.as_ptr())
+        elif isinstance(value, (list, tuple)):
+            elts = [Value(v) for v in value]
+            ptr = ffi_call(lib.plaidml_value_tuple, len(elts), [e.as_ptr() for e in elts])
+        elif isinstance(value, str):
+            ptr = ffi_call(lib.plaidml_value_str, value.encode())
+        elif hasattr(value, "value") and isinstance(value.value, int):  # enums
+            ptr = ffi_call(lib.plaidml_value_int, int(value.value))
+        else:
+            raise TypeError(f"Unsupported type {type(value)} for value={value}")
+        super().__init__(ptr)
+
+    def as_tensor(self) -> Tensor:
+        return Tensor(expr=ffi_call(lib.plaidml_value_expr_get, self.as_ptr()))
+
+
+def build_program(name, inputs, outputs, shapes=None) -> Program:
+    return Program(name, inputs, outputs, shapes=shapes)

@@ -1,0 +1,168 @@
+"""The operation library from Python.  Mirror of ``plaidml/op/__init__.py`` / ``plaidml/op/op.h``:
+each function packs its arguments into a value tuple for ``plaidml_op_make``."""
+
+from __future__ import annotations
+
+import enum
+
+from . import edsl
+from .ffi import ffi_call, lib
+
+
+def op(op_name, args):
+    value = edsl.Value(args)
+    return edsl.Value(ffi_call(lib.plaidml_op_make, op_name.encode(), value.as_ptr()))
+
+
+class AutoGroupMode(enum.IntEnum):
+    UNGROUPED = 0
+    EXPLICIT = 1
+    AUTO = 2
+    DEPTHWISE = 3
+
+
+class AutoPadMode(enum.IntEnum):
+    EXPLICIT = 0
+    SAME_LOWER = 1
+    SAME_UPPER = 2
+    VALID = 3
+
+
+class ConvDerivMode(enum.IntEnum):
+    NONE = 0
+    DATA = 1
+    FILTER = 2
+
+
+class GroupLayout(enum.IntEnum):
+    NONE = 0
+    SEPARATE = 1
+    IN_C = 2
+    IN_K = 3
+
+
+class PoolMode(enum.IntEnum):
+    AVG = 0
+    MAX = 1
+    MIN = 2
+    SUM = 3
+
+
+class TensorLayout(enum.IntEnum):
+    NXC = 0
+    NCX = 1
+    KCX = 2
+    XCK = 3
+    GKCX = 4
+    XGCK = 5
+
+
+def convolution(I, F, strides=None, dilations=None, data_dilations=None, filter_shape=None, groups=1,
+                autopad_mode=AutoPadMode.SAME_UPPER, manual_padding=None, input_layout=TensorLayout.NXC,
+                filter_layout=TensorLayout.XCK, group_layout=GroupLayout.NONE, winograd_allowed=False, name="",
+                autogroup_mode=AutoGroupMode.UNGROUPED, deriv_mode=ConvDerivMode.NONE, result_shape=None,
+                infer_result_shape=False):
+    args = [I, F, list(strides or []), list(dilations or []), list(data_dilations or []), list(filter_shape or []),
+            groups, int(autopad_mode), list(manual_padding or []), int(input_layout), int(filter_layout),
+            int(group_layout), winograd_allowed, name, int(autogroup_mode), int(deriv_mode),
+            list(result_shape or []), infer_result_shape]
+    return op("convolution", args).as_tensor()
+
+
+def pool(I, pool_mode, pool_size, strides, autopad_mode, manual_padding, input_layout, include_padding_in_avg=False,
+         use_ceil_for_output_shape=False, name=""):
+    args = [I, int(pool_mode), list(pool_size), list(strides), int(autopad_mode), list(manual_padding),
+            int(input_layout), include_padding_in_avg, use_ceil_for_output_shape, name]
+    return op("pool", args).as_tensor()
+
+
+def dot(x, y, name=""):
+    return op("dot", [x, y, name]).as_tensor()
+
+
+def relu(x, alpha=None, max_value=None, threshold=0.0, name=""):
+    return op("relu", [x, alpha, max_value, threshold, name]).as_tensor()
+
+
+def mean(x, axes=None, keepdims=False):
+    return op("mean", [x, axes, keepdims]).as_tensor()
+
+
+def sum(x, axes=None, keepdims=False):
+    return op("sum", [x, axes, keepdims]).as_tensor()
+
+
+def max(x, axes=None, keepdims=False):
+    return op("max", [x, axes, keepdims]).as_tensor()
+
+
+def min(x, axes=None, keepdims=False):
+    return op("min", [x, axes, keepdims]).as_tensor()
+
+
+def prod(x, axes=None, keepdims=False):
+    return op("prod", [x, axes, keepdims]).as_tensor()
+
+
+def variance(x, axes=None, keepdims=False):
+    return op("variance", [x, axes, keepdims]).as_tensor()
+
+
+def softmax(x, axis, name=""):
+    return op("softmax", [x, axis, name]).as_tensor()
+
+
+def maximum(x, y):
+    return op("maximum", [x, y]).as_tensor()
+
+
+def minimum(x, y):
+    return op("minimum", [x, y]).as_tensor()
+
+
+def clip(x, lo=None, hi=None):
+    return op("clip", [x, lo, hi]).as_tensor()
+
+
+def abs(x):
+    return op("abs", [x]).as_tensor()
+
+
+def sigmoid(x):
+    return op("sigmoid", [x]).as_tensor()
+
+
+def square(x):
+    return op("square", x).as_tensor()
+
+
+def reshape(x, dims):
+    return op("reshape", [x, list(dims)]).as_tensor()
+
+
+def transpose(x, axes=None):
+    return op("transpose", [x, None if axes is None else list(axes)]).as_tensor()
+
+
+def squeeze(x, axes):
+    return op("squeeze", [x, list(axes)]).as_tensor()
+
+
+def unsqueeze(x, axes):
+    return op("unsqueeze", [x, list(axes)]).as_tensor()
+
+
+def flip(x, axis):
+    return op("flip", [x, axis]).as_tensor()
+
+
+def cumsum(x, axis):
+    return op("cumsum", [x, axis]).as_tensor()
+
+
+def elu(x, alpha):
+    return op("elu", [x, alpha]).as_tensor()
+
+
+def spatial_padding(x, lo_pads, hi_pads, data_layout=TensorLayout.NXC):
+    return op("spatial_padding", [x, list(lo_pads), list(hi_pads), int(data_layout)]).as_tensor()
