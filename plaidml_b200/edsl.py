@@ -24,7 +24,8 @@ def _as_dim(x) -> "TensorDim":
 
 
 def _dim_op(op, *args) -> "TensorDim":
-    raw = [_as_dim(a).as_ptr() for a in args]
+    dims = [_as_dim(a) for a in args]  # keeps temporaries alive across the call
+    raw = [d.as_ptr() for d in dims]
     return TensorDim(expr=ffi_call(lib.plaidml_dim_expr_op, op, len(raw), raw))
 
 
@@ -94,7 +95,8 @@ def _as_poly(x) -> "TensorIndex":
 
 
 def _poly_op(op, *args) -> "TensorIndex":
-    raw = [_as_poly(a).as_ptr() for a in args]
+    polys = [_as_poly(a) for a in args]  # keeps temporaries alive across the call
+    raw = [p.as_ptr() for p in polys]
     return TensorIndex(expr=ffi_call(lib.plaidml_poly_expr_op, op, len(raw), raw))
 
 
@@ -118,7 +120,7 @@ class TensorIndex(ForeignObject):
         super().__init__(expr)
 
     def __lt__(self, rhs):
-        return Constraint(self, _as_dim(rhs))
+        return Constraint(self, _as_dim(rhs))  # the Constraint keeps both operands alive
 
     def __neg__(self):
         return _poly_op(lib.PLAIDML_INT_OP_NEG, self)
@@ -417,7 +419,8 @@ def Constant(buffer_or_array, name="", dtype=None):
 # ---------------------------------------------------------------------- intrinsics
 
 def cast(x, dtype):
-    return Tensor(expr=ffi_call(lib.plaidml_expr_cast, _as_tensor(x).as_ptr(), int(dtype)))
+    t = _as_tensor(x)  # held until the call returns
+    return Tensor(expr=ffi_call(lib.plaidml_expr_cast, t.as_ptr(), int(dtype)))
 
 
 def _unary(name):

@@ -1,0 +1,203 @@
+"""End-to-end parity through the reference-facing API: programs built with the EDSL, compiled
+for the `cuda` target and run on `cuda.0`, checked against the reference's known-answer
+vectors and against the CPU oracle on seeded inputs."""
+
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle
+from plaidml_b200 import core, edsl, op
+from plaidml_b200.core import Buffer, DType, Program, bf16_bits_to_f32, f32_to_bf16_bits
+from plaidml_b200.edsl import Contraction, Placeholder, TensorDims, TensorIndexes, cast
+from plaidml_b200.exec import Executable, Runner, list_devices
+
+import edsl_programs as P
+from gpu_util import check_close, max_rel, rng
+
+pytestmark = pytest.mark.gpu
+
+KATS = json.loads((Path(__file__).parent / "golden" / "reference_kats.json").read_text())
+
+
+def test_devices_and_targets():
+    assert core.list_targets() == ["cuda"]
+    devs = list_devices()
+    assert devs and devs[0] == "cuda.0"
+
+
+@pytest.mark.parametrize("kat", KATS, ids=[k["name"] for k in KATS])
+def test_reference_known_answers(kat):
+    program = P.GOLDEN_BUILDERS[kat["name"]]()
+    runner = Runner(program, "cuda.0")
+    ins = [np.array(v).reshape(s.sizes).astype(s.dtype.into_numpy()) for v, s in zip(kat["inputs"], program.inputs)]
+    outs = runner.run(ins)
+    for got, want, shape in zip(outs, kat["outputs"], program.outputs):
+        want = np.array(want).reshape(shape.sizes)
+        if got.dtype.kind == "f":
+            # the reference checks floats exactly against its own backend; ours may order the
+            # additions differently: one float32 ulp of slack
+            np.testing.assert_allclose(got, want.astype(got.dtype), rtol=3e-7)
+        else:
+            np.testing.assert_array_equal(got, want.astype(got.dtype))
+
+
+def test_known_answers_also_on_the_general_kernel(monkeypatch):
+    monkeypatch.setenv("PLAIDML_CUDA_GENERIC_ONLY", "1")
+    for kat in KATS:
+        if not kat["name"].startswith("GEMM"):
+            continue
+        program = P.GOLDEN_BUILDERS[kat["name"]]()
+        runner = Runner(program, "cuda.0")
+        assert "generic_contract" in runner.executable.describe()
+        ins = [np.array(v).reshape(s.sizes).astype(s.dtype.into_numpy()) for v, s in zip(kat["inputs"], program.inputs)]
+        got = runner.run(ins)[0]
+        want = np.array(kat["outputs"][0]).reshape(3, 3)
+        if got.dtype.kind == "f":
+            np.testing.assert_allclose(got, want, rtol=3e-7)
+        else:
+            np.testing.assert_array_equal(got, want.astype(got.dtype))
+
+
+def test_fp32_tile_gemm_1024_within_1e5():
+    # configuration 1: C[i,j] += A[i,k] * B[k,j], M = N = K = 1024, uniform [-1, 1)
+    g = rng(1234)
+    a = g.uniform(-1, 1, size=(1024, 1024)).astype(np.float32)
+    b = g.uniform(-1, 1, size=(1024, 1024)).astype(np.float32)
+    A, B, C = P.tile_gemm(DType.FLOAT32, 1024, 1024, 1024)
+    runner = Runner(Program("gemm_f32", [A, B], [C]), "cuda.0")
+    assert runner.executable.describe().startswith("tc_gemm")
+    got = runner.run([a, b])[0]
+    ref64 = oracle.gemm_f32_acc64(a, b)
+    assert max_rel(got, ref64) < 1e-5
+    check_close(got, oracle.gemm_f32(a, b), 1e-5)
+
+
+def test_int8_tile_gemm_bit_exact():
+    # configuration 2 at a size the CPU oracle finishes quickly; operands cast to int32
+    g = rng(1235)
+    m = n = k = 512
+    a = g.integers(-128, 128, size=(m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(k, n), dtype=np.int8)
+    A, B, C = P.tile_gemm(DType.INT8, m, n, k, acc=DType.INT32)
+    runner = Runner(Program("gemm_i8", [A, B], [C]), "cuda.0")
+    desc = runner.executable.describe()
+    assert desc.startswith("tc_gemm") and "in=si8 out=si32" in desc
+    np.testing.assert_array_equal(runner.run([a, b])[0], oracle.gemm_i8_i32(a, b))
+
+
+def test_int8_without_casts_wraps_like_the_reference():
+    g = rng(1236)
+    a = g.integers(-128, 128, size=(64, 48), dtype=np.int8)
+    b = g.integers(-128, 128, size=(48, 32), dtype=np.int8)
+    A, B, C = P.tile_gemm(DType.INT8, 64, 32, 48)
+    got = Runner(Program("gemm_i8_wrap", [A, B], [C]), "cuda.0").run([a, b])[0]
+    np.testing.assert_array_equal(got, oracle.gemm_i8_i32(a, b).astype(np.int8))
+
+
+def test_conv_bias_relu_bf16_fused():
+    # configuration 3 at batch 4
+    g = rng(1237)
+    n, h, w, c, k = 4, 56, 56, 64, 64
+    x = f32_to_bf16_bits(g.uniform(0, 1, size=(n, h, w, c)))
+    f = f32_to_bf16_bits(g.standard_normal((3, 3, c, k)) * np.sqrt(2.0 / 576))
+    bias = (g.standard_normal(k) * 0.1).astype(np.float32)
+    program = P.conv_bias_relu(n, h, w, c, k, filt=f, bias=bias)
+    runner = Runner(program, "cuda.0")
+    desc = runner.executable.describe()
+    assert desc.count("\n") == 1 and desc.startswith("tc_conv") and "+bias+relu+cast" in desc, desc
+    got = bf16_bits_to_f32(runner.run([x])[0])
+    ref = oracle.conv2d_nhwc_f32(bf16_bits_to_f32(x), bf16_bits_to_f32(f), bias, None, pad=(1, 1), relu=True)
+    # 1e-2 relative: the stated tolerance for this configuration (bf16 result)
+    check_close(got, bf16_bits_to_f32(f32_to_bf16_bits(ref)), 1e-2)
+
+
+def test_qk_batched_gemm_then_row_max():
+    # configuration 5 at batch 8: S[b,i,j] += Q[b,i,k] * K[b,j,k] (bf16 in, f32 acc), R[b,i] >= S[b,i,j]
+    g = rng(1238)
+    b, m, k = 8, 512, 64
+    q = f32_to_bf16_bits(g.standard_normal((b, m, k)))
+    kk = f32_to_bf16_bits(g.standard_normal((b, m, k)))
+    Q, Kt, S = P.tile_gemm(DType.BFLOAT16, m, m, k, acc=DType.FLOAT32, batch=b, b_transposed=True)
+    bb, i, j = TensorIndexes(3)
+    R = Contraction(name="rowmax").outShape(b, m).outAccess(bb, i).max(S[bb, i, j]).build()
+    runner = Runner(Program("qk_rowmax", [Q, Kt], [S, R]), "cuda.0")
+    desc = runner.executable.describe()
+    assert "tc_gemm" in desc and "row_reduce" in desc, desc
+    s_out, r_out = runner.run([q, kk])
+    ref = oracle.gemm_h16_f32(q, kk, False, True)
+    check_close(s_out, ref, 1e-2)
+    np.testing.assert_array_equal(r_out, s_out.max(axis=2))   # exact given identical S
+
+
+def test_maxpool_and_mean_and_softmax():
+    g = rng(1239)
+    x = g.standard_normal((2, 12, 12, 16)).astype(np.float32)
+    I = Placeholder(DType.FLOAT32, x.shape)
+    pooled = op.pool(I, op.PoolMode.MAX, [3, 3], [2, 2], op.AutoPadMode.EXPLICIT, [1, 1, 1, 1], op.TensorLayout.NXC)
+    avg = op.mean(pooled, axes=[1, 2])
+    sm = op.softmax(avg, axis=1)
+    runner = Runner(Program("pool_mean_softmax", [I], [pooled, avg, sm]), "cuda.0")
+    desc = runner.executable.describe()
+    assert "nhwc_pool" in desc and "strided_reduce" in desc, desc
+    got_pool, got_avg, got_sm = runner.run([x])
+    ref_pool = oracle.pool2d_nhwc_f32(x, "max", (3, 3), (2, 2), (1, 1), (6, 6))
+    np.testing.assert_array_equal(got_pool, ref_pool)
+    ref_avg = ref_pool.astype(np.float64).mean(axis=(1, 2))
+    np.testing.assert_allclose(got_avg, ref_avg, rtol=1e-5, atol=1e-6)
+    e = np.exp(ref_avg - ref_avg.max(axis=1, keepdims=True))
+    np.testing.assert_allclose(got_sm, e / e.sum(axis=1, keepdims=True), rtol=1e-5, atol=1e-7)
+
+
+def test_avgpool_counts_only_in_range_taps():
+    g = rng(1240)
+    x = g.standard_normal((1, 7, 7, 4)).astype(np.float32)
+    I = Placeholder(DType.FLOAT32, x.shape)
+    O = op.pool(I, op.PoolMode.AVG, [3, 3], [1, 1], op.AutoPadMode.SAME_UPPER, [], op.TensorLayout.NXC)
+    got = Runner(Program("avgpool", [I], [O]), "cuda.0").run([x])[0]
+    ref = oracle.pool2d_nhwc_f32(x, "sum", (3, 3), (1, 1), (1, 1), (7, 7), average=True)
+    np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-6)
+
+
+def test_residual_block_fusion_and_order():
+    # relu(conv_c(x) + bias + shortcut(x)) with the shortcut branch lowered after the main one
+    g = rng(1241)
+    n, h, w, c, k = 2, 14, 14, 64, 128
+    x = f32_to_bf16_bits(g.uniform(0, 1, size=(n, h, w, c)))
+    f1 = f32_to_bf16_bits(g.standard_normal((1, 1, c, k)) * np.sqrt(2.0 / c))
+    f2 = f32_to_bf16_bits(g.standard_normal((1, 1, c, k)) * np.sqrt(2.0 / c))
+    b1 = (g.standard_normal(k) * 0.1).astype(np.float32)
+    I = Placeholder(DType.BFLOAT16, [n, h, w, c])
+    xi = cast(I, DType.FLOAT32)
+    F1 = cast(edsl.Constant(f1, dtype=DType.BFLOAT16), DType.FLOAT32)
+    F2 = cast(edsl.Constant(f2, dtype=DType.BFLOAT16), DType.FLOAT32)
+    main = op.convolution(xi, F1, name="main") + edsl.Constant(b1)
+    short = cast(cast(op.convolution(xi, F2, name="shortcut"), DType.BFLOAT16), DType.FLOAT32)
+    O = cast(op.relu(main + short), DType.BFLOAT16)
+    runner = Runner(Program("block", [I], [O]), "cuda.0")
+    desc = runner.executable.describe()
+    assert "+bias+residual+relu+cast" in desc, desc
+    got = bf16_bits_to_f32(runner.run([x])[0])
+    xf = bf16_bits_to_f32(x)
+    sc = bf16_bits_to_f32(f32_to_bf16_bits(oracle.conv2d_nhwc_f32(xf, bf16_bits_to_f32(f2))))
+    ref = oracle.conv2d_nhwc_f32(xf, bf16_bits_to_f32(f1), b1, sc, relu=True)
+    check_close(got, bf16_bits_to_f32(f32_to_bf16_bits(ref)), 1e-2)
+
+
+def test_run_argument_checks_and_timing():
+    A, B, C = P.tile_gemm(DType.FLOAT32, 16, 16, 16)
+    program = Program("chk", [A, B], [C]).compile("cuda")
+    exe = Executable(program, "cuda.0")
+    a = Buffer(program.inputs[0])
+    b = Buffer(program.inputs[1])
+    c = Buffer(program.outputs[0])
+    ms = exe.run([a, b], [c])
+    assert ms > 0
+    with pytest.raises(core.Error, match="expects 2 inputs"):
+        exe.run([a], [c])
+    wrong = Buffer(core.TensorShape(DType.FLOAT32, [16, 8]))
+    with pytest.raises(core.Error, match="Shape mismatch"):
+        exe.run([a, wrong], [c])
+    assert exe.run_resident(3) > 0 and exe.launch_count >= 1
