@@ -279,6 +279,10 @@ size_t pmlb_exec_launch_count(plaidml_error* err, plaidml_executable* exec);
  * the last plaidml_executable_run (no host copies) and returns the mean milliseconds per
  * iteration measured with CUDA events on the executable's stream. */
 double pmlb_exec_run_resident(plaidml_error* err, plaidml_executable* exec, size_t iters);
+/* Like pmlb_exec_run_resident, but every pass is bracketed by its own CUDA event pair and,
+ * with `flush_l2`, preceded by an untimed overwrite of a 256 MiB device buffer so that no
+ * pass finds its operands in the 126 MB L2. */
+double pmlb_exec_time_steps(plaidml_error* err, plaidml_executable* exec, size_t iters, bool flush_l2);
 /* Device address and byte size of output `index` (valid until the executable is freed). */
 void* pmlb_exec_output_device_ptr(plaidml_error* err, plaidml_executable* exec, size_t index, size_t* nbytes);
 /* CUDA stream (cudaStream_t) the executable enqueues on. */

@@ -58,6 +58,10 @@ double pmlb_exec_run_resident(plaidml_error* err, plaidml_executable* exec, size
   return ffiWrap<double>(err, 0.0, [&] { return exec->exec->runResident(iters); });
 }
 
+double pmlb_exec_time_steps(plaidml_error* err, plaidml_executable* exec, size_t iters, bool flush_l2) {
+  return ffiWrap<double>(err, 0.0, [&] { return exec->exec->timeSteps(iters, flush_l2); });
+}
+
 void* pmlb_exec_output_device_ptr(plaidml_error* err, plaidml_executable* exec, size_t index, size_t* nbytes) {
   return ffiWrap<void*>(err, nullptr, [&] { return exec->exec->outputDevicePtr(index, nbytes); });
 }

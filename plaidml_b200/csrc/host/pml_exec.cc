@@ -1155,6 +1155,7 @@ Executable::~Executable() {
   if (stream_) cudaStreamSynchronize(stream_);
   for (Step& s : steps_) pmlb_plan_free(s.plan);
   if (arena_) cudaFree(arena_);
+  if (flush_) cudaFree(flush_);
   if (status_) cudaFree(status_);
   if (evStart_) cudaEventDestroy(evStart_);
   if (evStop_) cudaEventDestroy(evStop_);
@@ -1236,6 +1237,27 @@ double Executable::runResident(size_t iters) {
   float ms = 0.f;
   cudaCheck(cudaEventElapsedTime(&ms, evStart_, evStop_), "cudaEventElapsedTime");
   return static_cast<double>(ms) / static_cast<double>(iters);
+}
+
+double Executable::timeSteps(size_t iters, bool flushL2) {
+  if (!inputsResident_) throw std::runtime_error("run the executable once before timing it on resident inputs");
+  if (iters == 0) return 0.0;
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  constexpr size_t kFlushBytes = 256u << 20;  // twice the 126 MB L2
+  if (flushL2 && !flush_) cudaCheck(cudaMalloc(reinterpret_cast<void**>(&flush_), kFlushBytes), "cudaMalloc(L2 flush)");
+  double total = 0.0;
+  for (size_t i = 0; i < iters; ++i) {
+    if (flushL2) cudaCheck(cudaMemsetAsync(flush_, static_cast<int>(i & 0xff), kFlushBytes, stream_), "L2 flush");
+    cudaCheck(cudaEventRecord(evStart_, stream_), "cudaEventRecord");
+    enqueueSteps();
+    cudaCheck(cudaEventRecord(evStop_, stream_), "cudaEventRecord");
+    cudaCheck(cudaEventSynchronize(evStop_), "cudaEventSynchronize");
+    float ms = 0.f;
+    cudaCheck(cudaEventElapsedTime(&ms, evStart_, evStop_), "cudaEventElapsedTime");
+    total += ms;
+  }
+  checkStatus();
+  return total / static_cast<double>(iters);
 }
 
 std::string Executable::describe() const {

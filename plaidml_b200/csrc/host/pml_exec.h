@@ -41,6 +41,9 @@ class Executable {
 
   double run(const std::vector<BufferPtr>& inputs, const std::vector<BufferPtr>& outputs);
   double runResident(size_t iters);
+  // Mean milliseconds of one pass of the kernel sequence, each pass timed by its own event pair;
+  // with flushL2 a 256 MiB buffer is overwritten before every pass (outside the timed span).
+  double timeSteps(size_t iters, bool flushL2);
   std::string describe() const;
   size_t launchCount() const;
   void* outputDevicePtr(size_t index, size_t* nbytes) const;
@@ -57,6 +60,7 @@ class Executable {
   cudaStream_t stream_ = nullptr;
   cudaEvent_t evStart_ = nullptr, evStop_ = nullptr;
   char* arena_ = nullptr;
+  char* flush_ = nullptr;
   size_t arenaBytes_ = 0;
   std::vector<char*> dev_;        // device address per value id (null if never materialised)
   std::vector<Step> steps_;

@@ -37,6 +37,10 @@ class Executable(ForeignObject):
         """Mean milliseconds per iteration of the kernel sequence on device-resident inputs."""
         return ffi_call(lib.pmlb_exec_run_resident, self.as_ptr(), iters)
 
+    def time_steps(self, iters: int = 1, flush_l2: bool = True) -> float:
+        """Mean milliseconds per pass, each pass timed alone (CUDA events), L2 flushed before it."""
+        return ffi_call(lib.pmlb_exec_time_steps, self.as_ptr(), iters, flush_l2)
+
     def output_device_ptr(self, index: int = 0) -> tuple[int, int]:
         nbytes = ffi.new("size_t*")
         ptr = ffi_call(lib.pmlb_exec_output_device_ptr, self.as_ptr(), index, nbytes)

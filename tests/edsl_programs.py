@@ -97,37 +97,5 @@ GOLDEN_BUILDERS = {
 }
 
 
-# ---------------------------------------------------------------- the benchmark configurations
-
-def tile_gemm(dtype_in: DType, m, n, k, acc: DType = None, batch=None, b_transposed=False):
-    """C[i,j] += A[i,k] * B[k,j] (optionally with operands cast to a wider accumulate type,
-    a leading batch dimension, or B stored [j,k])."""
-    ashape = [m, k] if batch is None else [batch, m, k]
-    bshape = ([n, k] if b_transposed else [k, n]) if batch is None else ([batch, n, k] if b_transposed else [batch, k, n])
-    A = Placeholder(dtype_in, ashape, name="A")
-    B = Placeholder(dtype_in, bshape, name="B")
-    a = cast(A, acc) if acc is not None else A
-    b = cast(B, acc) if acc is not None else B
-    i, j, kk, bb = TensorIndexes(4)
-    if batch is None:
-        rhs = a[i, kk] * (b[j, kk] if b_transposed else b[kk, j])
-        C = Contraction(name="gemm").outShape(m, n).outAccess(i, j).sum(rhs).build()
-    else:
-        rhs = a[bb, i, kk] * (b[bb, j, kk] if b_transposed else b[bb, kk, j])
-        C = Contraction(name="bgemm").outShape(batch, m, n).outAccess(bb, i, j).sum(rhs).build()
-    return A, B, C
-
-
-def conv_bias_relu(n, h, w, cin, cout, r=3, s=3, out_bf16=True, filt=None, bias=None, stride=1):
-    """NHWC conv as a Tile contraction (through op.convolution) + bias + ReLU, bf16 storage with
-    f32 accumulate."""
-    I = Placeholder(DType.BFLOAT16, [n, h, w, cin], name="I")
-    F = edsl.Constant(filt, name="F", dtype=DType.BFLOAT16)
-    Bz = edsl.Constant(bias, name="bias")
-    O = op.convolution(cast(I, DType.FLOAT32), cast(F, DType.FLOAT32), strides=[stride, stride],
-                       autopad_mode=op.AutoPadMode.EXPLICIT, manual_padding=[(r - 1) // 2, (s - 1) // 2, (r - 1) // 2, (s - 1) // 2],
-                       name="conv")
-    O = op.relu(O + Bz)
-    if out_bf16:
-        O = cast(O, DType.BFLOAT16)
-    return Program("conv_bias_relu", [I], [O])
+# the benchmark configurations live in the package so that bench.py can use them too
+from plaidml_b200.programs import conv_bias_relu, tile_gemm  # noqa: E402,F401
