@@ -34,7 +34,7 @@ M_PER_GPU, N_DIM, K_DIM = 4096, 4096, 4096
 WORKLOAD = "cfg2: int8 x int8 -> int32 Tile GEMM, N=K=4096, M=4096 rows per GPU (rows of M sharded)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one tc_contract launch of this workload, from
 # the ncu capture summarised in profiles/tc_gemm_i8_4096.md
-NCU_TRAFFIC_BYTES = None
+NCU_TRAFFIC_BYTES = 52.58e6
 
 
 def measured_peaks() -> dict:

@@ -494,6 +494,7 @@ pmlb_status pmlb_conv_invoke(pmlb_plan* plan, void* stream, const void* input, v
   L.ldr = d.k;
   L.status = plan->status;
   L.bn_override = d.tile_n;
+  L.trace = g_trace_buffer;
   std::string err;
   const int rc = pmlb::tc_launch(L, static_cast<cudaStream_t>(stream), &err);
   if (rc != 0) return fail(static_cast<pmlb_status>(rc), "conv: " + err);
