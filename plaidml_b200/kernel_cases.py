@@ -1,0 +1,77 @@
+"""Small, self-contained runs of single hot-path configurations, for profilers.
+
+    python -m plaidml_b200.kernel_cases <case> [passes]
+
+Each case builds its program through the EDSL, runs it once through ``plaidml_executable_run``
+(inputs seeded, uploaded from host buffers) and then repeats the device-resident kernel
+sequence ``passes`` times (default 3) without L2 flushing, so that a profiler sees a handful of
+launches of the kernel of interest:
+
+    i8_4k      int8 -> int32 Tile GEMM 4096^3            (tc_contract_kernel, int8, B as [k][n])
+    bf16_4k    bf16 Tile GEMM 4096^3, f32 accumulate     (tc_contract_kernel, bf16)
+    f32_1k     fp32 Tile GEMM 1024^3 via three TF32 products
+    conv3      conv 3x3 56x56 64->64 + bias + ReLU, batch 16
+    conv3_full the same at batch 128
+    qk         batched Q.K^T 128 x (512x512x64) + row max
+    resnet N   ResNet-50 v1.5 at batch N
+"""
+
+from __future__ import annotations
+
+import sys
+
+import numpy as np
+
+from . import programs
+from .core import DType, Program, f32_to_bf16_bits
+from .edsl import Contraction, TensorIndexes
+from .exec import Runner
+
+
+def main(argv) -> None:
+    case = argv[1] if len(argv) > 1 else "i8_4k"
+    g = np.random.Generator(np.random.PCG64(7))
+    passes = 3
+    if case == "i8_4k":
+        A, B, C = programs.tile_gemm(DType.INT8, 4096, 4096, 4096, acc=DType.INT32)
+        r = Runner(Program(case, [A, B], [C]), "cuda.0")
+        ins = [g.integers(-128, 128, (4096, 4096), dtype=np.int8) for _ in range(2)]
+    elif case == "bf16_4k":
+        A, B, C = programs.tile_gemm(DType.BFLOAT16, 4096, 4096, 4096, acc=DType.FLOAT32, out_bf16=True)
+        r = Runner(Program(case, [A, B], [C]), "cuda.0")
+        ins = [f32_to_bf16_bits(g.standard_normal((4096, 4096))) for _ in range(2)]
+    elif case == "f32_1k":
+        A, B, C = programs.tile_gemm(DType.FLOAT32, 1024, 1024, 1024)
+        r = Runner(Program(case, [A, B], [C]), "cuda.0")
+        ins = [g.uniform(-1, 1, (1024, 1024)).astype(np.float32) for _ in range(2)]
+    elif case in ("conv3", "conv3_full"):
+        n = 16 if case == "conv3" else 128
+        f = f32_to_bf16_bits(g.standard_normal((3, 3, 64, 64)) * np.sqrt(2.0 / 576))
+        r = Runner(programs.conv_bias_relu(n, 56, 56, 64, 64, filt=f, bias=np.zeros(64, np.float32)), "cuda.0")
+        ins = [f32_to_bf16_bits(g.uniform(0, 1, (n, 56, 56, 64)))]
+    elif case == "qk":
+        Q, Kt, S = programs.tile_gemm(DType.BFLOAT16, 512, 512, 64, acc=DType.FLOAT32, batch=128, b_transposed=True)
+        bb, i, j = TensorIndexes(3)
+        R = Contraction(name="rowmax").outShape(128, 512).outAccess(bb, i).max(S[bb, i, j]).build()
+        r = Runner(Program(case, [Q, Kt], [S, R]), "cuda.0")
+        ins = [f32_to_bf16_bits(g.standard_normal((128, 512, 64))) for _ in range(2)]
+    elif case == "resnet":
+        batch = int(argv[2]) if len(argv) > 2 else 32
+        prog, _ = programs.resnet50(batch)
+        r = Runner(prog, "cuda.0")
+        img = np.zeros((batch, 224, 224, 8), np.float32)
+        img[..., :3] = g.uniform(0, 1, (batch, 224, 224, 3))
+        ins = [f32_to_bf16_bits(img)]
+        passes = 1
+    else:
+        raise SystemExit(__doc__)
+    if len(argv) > 2 and case != "resnet":
+        passes = int(argv[2])
+    r.run(ins)
+    ms = r.executable.time_steps(passes, False)
+    print(f"{case}: {ms:.4f} ms per pass over {passes} passes; {r.executable.launch_count} launches per pass")
+    print(r.executable.describe())
+
+
+if __name__ == "__main__":
+    main(sys.argv)
