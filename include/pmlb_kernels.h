@@ -137,6 +137,30 @@ pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* desc, pmlb_plan** plan);
 pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream, const void* a, const void* b, void* c,
                              const void* bias, const void* residual, float* rowmax);
 
+/* ---------------------------------------------------------------- fp32 GEMM without allocation
+ * (no counterpart in the reference)
+ *
+ * For hosts that own all device memory themselves and must not see this library allocate: a
+ * server whose arena was sized to the card, a plug-in inside another framework's allocator, a
+ * loop that cannot take the stall of a driver allocation.  Computes what pmlb_gemm_dispatch /
+ * pmlb_gemm_invoke compute for in_dtype = out_dtype = F32, batch = 1, no epilogue:
+ *     C[i, j] = sum_k A[i, k] * B[k, j]   (b_is_nk == 0)   or   A[i, k] * B[j, k]   (b_is_nk != 0)
+ * but keeps its scratch (the TF32 hi / lo copies of A and B) in a fixed device array inside the
+ * library image of PMLB_NOALLOC_SCRATCH_BYTES, which every GPU that loads the library holds
+ * until the process ends.  It calls no cudaMalloc / cudaFree and no allocating routine.
+ *   - Limit: 8 * (m + n) * round_up(k, 4) + 256 bytes must fit in the array (1024^3 needs
+ *     16 MiB); larger problems return PMLB_ERR_UNSUPPORTED with the sizes in the message.
+ *   - The first call on each device looks the array's address up (with that device current);
+ *     make that first call before starting any stream capture.
+ *   - All calls share the one array per device and each call overwrites it: two calls whose
+ *     kernels can overlap on the GPU (different streams, no dependency) race.  Serialise them.
+ *   - `wait` != 0 synchronises the stream before returning and reports a device-side pipeline
+ *     time-out as PMLB_ERR_TIMEOUT; with `wait` == 0 the call only enqueues.
+ * a, b, c are device pointers; lda / ldb / ldc count elements between rows. */
+#define PMLB_NOALLOC_SCRATCH_BYTES (32u << 20)
+pmlb_status pmlb_gemm_f32_noalloc(void* stream, const float* a, const float* b, float* c, int32_t m, int32_t n,
+                                  int32_t k, int64_t lda, int64_t ldb, int64_t ldc, int32_t b_is_nk, int32_t wait);
+
 /* ---------------------------------------------------------------- convolution
  * NHWC activation [n, h, w, c] (*) filter [r, s, c, k] -> [n, p, q, k]:
  *   O[n, y, x, ko] = sum_{fr, fs, ci} I[n, stride_h*y + dil_h*fr - pad_h, stride_w*x + dil_w*fs - pad_w, ci]

@@ -22,6 +22,13 @@ pmlb_status fail(pmlb_status code, const std::string& msg) {
   return code;
 }
 
+}  // namespace
+
+// Lets the other translation units of the library report through pmlb_last_error().
+void pmlb_set_last_error_message(const std::string& msg) { g_last_error = msg; }
+
+namespace {
+
 pmlb_status cuda_fail(cudaError_t e, const char* what) {
   return fail(PMLB_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
 }
