@@ -30,6 +30,8 @@ import numpy as np
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+from plaidml_b200 import shard  # noqa: E402  (pure Python; the CUDA library loads on first use)
+
 M_PER_GPU, N_DIM, K_DIM = 4096, 4096, 4096
 WORKLOAD = "cfg2: int8 x int8 -> int32 Tile GEMM, N=K=4096, M=4096 rows per GPU (rows of M sharded)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one tc_contract launch of this workload, from
@@ -97,7 +99,7 @@ def seeded_inputs(rank: int):
     # PRNG of the measurement plan: PCG64, seed = 1234 + configuration index (+ rank for the shard)
     g = np.random.Generator(np.random.PCG64(1234 + 2))
     b = g.integers(-128, 128, size=(K_DIM, N_DIM), dtype=np.int8)
-    ga = np.random.Generator(np.random.PCG64(1234 + 2 + 1000 * (rank + 1)))
+    ga = np.random.Generator(np.random.PCG64(shard.shard_seed(1234 + 2, rank)))
     a = ga.integers(-128, 128, size=(M_PER_GPU, K_DIM), dtype=np.int8)
     return a, b
 
@@ -210,9 +212,8 @@ def main() -> None:
         run_reference_arm(args)
         return
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
+    info = shard.RankInfo.from_env()
+    rank, local_rank, world = info.rank, info.local_rank, info.world
     warm = max(3, args.warmup)
 
     import torch
@@ -223,18 +224,13 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     def barrier():
-        if dist is not None:
-            dist.barrier()
+        shard.barrier(dist)
         torch.cuda.synchronize()
 
     def max_over_ranks(x: float) -> float:
-        if dist is None:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=f"cuda:{local_rank}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return shard.max_over_ranks(dist, x, f"cuda:{local_rank}")
 
-    device = f"cuda.{local_rank}"
+    device = info.device_id
     runner = build_gemm_runner(device)
     exe = runner.executable
     a, b = seeded_inputs(rank)

@@ -117,7 +117,7 @@ plaidml_shape* plaidml_shape_clone(plaidml_error* err, plaidml_shape* shape) {
 }
 
 plaidml_string* plaidml_shape_repr(plaidml_error* err, plaidml_shape* shape) {
-  return ffiWrap<plaidml_string*>(err, nullptr, [&] { return new plaidml_string{shape->shape.str()}; });
+  return ffiWrap<plaidml_string*>(err, nullptr, [&] { return new plaidml_string{shape->shape.repr()}; });
 }
 
 size_t plaidml_shape_get_rank(plaidml_error* err, plaidml_shape* shape) {

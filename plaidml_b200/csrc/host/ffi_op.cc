@@ -26,6 +26,19 @@ pml::TensorShape shapeOf(const ExprPtr& e) {
   return local.getShape(e);
 }
 
+// Manual padding lists all "before" values, then all "after" values.  Missing "before" values are 0 and
+// a missing "after" value repeats the "before" value of its dimension (plaidml/op/lib/ops.cc:420-436).
+void splitManualPadding(std::vector<int64_t> pads, size_t rank, std::vector<int64_t>* lo, std::vector<int64_t>* hi) {
+  if (pads.size() > 2 * rank) {
+    throw std::runtime_error("Inconsistent spatial rank: operation with " + std::to_string(rank) + " spatial dimensions had " +
+                             std::to_string(pads.size()) + " manual padding values given");
+  }
+  while (pads.size() < rank) pads.push_back(0);
+  while (pads.size() < 2 * rank) pads.push_back(pads[pads.size() - rank]);
+  lo->assign(pads.begin(), pads.begin() + rank);
+  hi->assign(pads.begin() + rank, pads.end());
+}
+
 PolyPtr newIndex(const std::string& name = "") {
   auto p = std::make_shared<pml::PolyNode>();
   p->kind = pml::PolyNode::Index;
@@ -330,16 +343,8 @@ VarPtr opConvolution(const VarPtr& value) {
   if (!manualPadding.empty() && autopad != kPadExplicit) {
     throw std::runtime_error("Autopadding and manual padding both requested for single conv operation");
   }
-  if (manualPadding.size() > 2 * sr) throw std::runtime_error("Inconsistent spatial rank: more manual padding than spatial dims");
-  // padding is listed as all "before" values, then all "after" values; missing ones are 0
-  std::vector<int64_t> padLo(sr, 0), padHi(sr, 0);
-  {
-    const size_t half = manualPadding.size() / 2;
-    for (size_t i = 0; i < half && i < sr; ++i) {
-      padLo[i] = manualPadding[i];
-      padHi[i] = manualPadding[half + i];
-    }
-  }
+  std::vector<int64_t> padLo, padHi;
+  splitManualPadding(manualPadding, sr, &padLo, &padHi);
   const bool nxc = inputLayout == kNXC;
   const int64_t N = is.sizes[0];
   const int64_t CI = nxc ? is.sizes.back() : is.sizes[1];
@@ -427,14 +432,8 @@ VarPtr opPool(const VarPtr& value) {
   if (strides.size() != sr) throw std::runtime_error("Inconsistent spatial rank in pool op");
   if (is.rank() != sr + 2) throw std::runtime_error("Inconsistent spatial rank in pool op");
   if (layout != kNXC && layout != kNCX) throw std::runtime_error("Tensor layout requested in pool op does not apply to pooling");
-  std::vector<int64_t> padLo(sr, 0), padHi(sr, 0);
-  {
-    const size_t half = manualPadding.size() / 2;
-    for (size_t i = 0; i < half && i < sr; ++i) {
-      padLo[i] = manualPadding[i];
-      padHi[i] = manualPadding[half + i];
-    }
-  }
+  std::vector<int64_t> padLo, padHi;
+  splitManualPadding(manualPadding, sr, &padLo, &padHi);
   const bool nxc = layout == kNXC;
   PolyPtr n = newIndex("n"), c = newIndex("c");
   std::vector<PolyPtr> x, k, inSpatial;

@@ -115,6 +115,23 @@ std::string TensorShape::str() const {
   return os.str();
 }
 
+// The spelling plaidml_shape_repr returns in the reference (pmlc/util/shape.cc:69-91): sizes joined by 'x'
+// (a zero size prints as '?'), the element type, then the strides only when the shape carries them.
+std::string TensorShape::repr() const {
+  std::ostringstream os;
+  for (int64_t s : sizes) {
+    if (s) os << s; else os << '?';
+    os << 'x';
+  }
+  os << dtypeName(dtype);
+  if (!strides.empty()) {
+    os << ", [";
+    for (size_t i = 0; i < strides.size(); ++i) os << (i ? "x" : "") << strides[i];
+    os << ']';
+  }
+  return os.str();
+}
+
 bool TensorShape::operator==(const TensorShape& rhs) const {
   return dtype == rhs.dtype && sizes == rhs.sizes && effectiveStrides() == rhs.effectiveStrides();
 }

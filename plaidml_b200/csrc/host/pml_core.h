@@ -54,7 +54,8 @@ struct TensorShape {
   std::vector<int64_t> denseStrides() const;
   std::vector<int64_t> effectiveStrides() const { return strides.empty() ? denseStrides() : strides; }
   bool isDense() const;
-  std::string str() const;
+  std::string str() const;   // tensor<4x5xf32>, as values are typed in the printed program
+  std::string repr() const;  // 4x5xf32[, [5x1]]
   // Equality as plaidml_executable_run checks it: type, sizes and the strides vector.
   bool operator==(const TensorShape& rhs) const;
   bool operator!=(const TensorShape& rhs) const { return !(*this == rhs); }

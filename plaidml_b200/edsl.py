@@ -204,11 +204,35 @@ def intrinsic(fn, *args, name=""):
     return Tensor(expr=ffi_call(lib.plaidml_expr_intrinsic, fn.encode(), len(raw), raw, name.encode()))
 
 
+class TensorLens:
+    """Reorders dimensions and indexes written in a `source` layout (say 'NCHW') into the `target` layout
+    the code was written for ('NHWC'); position p of the result is taken from where target[p]'s letter
+    stands in source.  The empty lens is the identity.  (plaidml/edsl/__init__.py:292-309)"""
+
+    def __init__(self, source="", target=""):
+        if len(source) != len(target):
+            raise ValueError("source and target rank mismatch")
+        self.map = []
+        for letter in source:
+            pos = target.find(letter)
+            if pos < 0:
+                raise ValueError("source and target dims mismatch")
+            self.map.append(pos)
+
+    def apply(self, items):
+        if not self.map:
+            return list(items)
+        if len(items) != len(self.map):
+            raise ValueError("rank mismatch in TensorLens apply")
+        return [items[p] for p in self.map]
+
+
 class Tensor(ForeignObject):
     __ffi_del__ = lib.plaidml_expr_free
     __ffi_repr__ = lib.plaidml_expr_repr
 
-    def __init__(self, expr=None, value=None):
+    def __init__(self, expr=None, value=None, lens=None):
+        self._lens = lens if lens is not None else TensorLens()
         if expr is None:
             if value is None:
                 raise ValueError("a Tensor needs an expression or a literal value")
@@ -307,9 +331,13 @@ class Tensor(ForeignObject):
 
     def bind_dims(self, *dims):
         """Binds unbound ``TensorDim`` objects to this tensor's sizes and checks bound ones."""
-        dims = [d if isinstance(d, TensorDim) else _as_dim(d) for d in dims]
+        dims = self._lens.apply([d if isinstance(d, TensorDim) else _as_dim(d) for d in dims])
         handles = [d.as_ptr() for d in dims]
         ffi_call(lib.plaidml_expr_bind_dims, self.as_ptr(), len(handles), handles)
+
+    def use(self, lens: TensorLens) -> "Tensor":
+        """The same tensor seen through `lens` (its own handle, so both views can be freed independently)."""
+        return Tensor(expr=ffi_call(lib.plaidml_expr_clone, self.as_ptr()), lens=lens)
 
     def element(self, ordinal):
         return Tensor(expr=ffi_call(lib.plaidml_expr_element, self.as_ptr(), ordinal))
@@ -318,7 +346,10 @@ class Tensor(ForeignObject):
 class Contraction:
     """``Contraction().outShape(..).outAccess(..).sum(A[i, k] * B[k, j]).build()``"""
 
-    def __init__(self, name=""):
+    def __init__(self, lens=None, name=""):
+        if isinstance(lens, str):  # Contraction("name")
+            lens, name = None, lens
+        self._lens = lens if lens is not None else TensorLens()
         self._name = name
         self._dims = ()
         self._idxs = ()
@@ -373,8 +404,8 @@ class Contraction:
             rhs = IndexedTensor(lib.PLAIDML_COMBO_OP_NONE, ref=rhs, idxs=())
         elif not isinstance(rhs, IndexedTensor):
             rhs = IndexedTensor(lib.PLAIDML_COMBO_OP_NONE, ref=_as_tensor(rhs), idxs=())
-        dims = [_as_dim(d) for d in self._dims]
-        idxs = [_as_poly(i) for i in self._idxs]
+        dims = self._lens.apply([_as_dim(d) for d in self._dims])
+        idxs = self._lens.apply([_as_poly(i) for i in self._idxs])
         init = self._init.as_ptr() if self._init is not None else ffi.NULL
         tensor = Tensor(expr=ffi_call(lib.plaidml_expr_contraction, self._agg, rhs._op, len(idxs),
                                       [i.as_ptr() for i in idxs], [d.as_ptr() for d in dims], init,
@@ -383,7 +414,7 @@ class Contraction:
         for operand in operands:
             if not isinstance(operand, IndexedTensor) or operand._ref is None:
                 raise TypeError("contraction operands must be indexed tensors, e.g. A[i, k]")
-            polys = [_as_poly(i) for i in operand._idxs]
+            polys = operand._ref._lens.apply([_as_poly(i) for i in operand._idxs])
             ffi_call(lib.plaidml_contraction_add_operand, tensor.as_ptr(), operand._ref.as_ptr(), len(polys),
                      [p.as_ptr() for p in polys])
         for c in self._constraints:

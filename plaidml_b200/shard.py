@@ -1,0 +1,85 @@
+"""Data-parallel sharding of a contraction over one process per GPU.
+
+The Tile contraction path has no exchange step: independent rows of the output (the M dimension of a
+GEMM, the batch dimension of a convolution) are computed from independent rows of the first operand and a
+replicated second operand, like the reference's threading of the outermost parallel loop over output
+tiles (pmlc/target/x86/pipeline.cc:133-255 collapses scf.parallel for OpenMP, :374 converts it).  So
+ranks share nothing on the data path; the only collectives are the barrier and the max-over-ranks of the
+timed span, which use whatever process group is initialised (NCCL on GPUs, gloo in CPU tests).
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class RankInfo:
+    rank: int
+    local_rank: int
+    world: int
+
+    @staticmethod
+    def from_env(env=None) -> "RankInfo":
+        env = os.environ if env is None else env
+        return RankInfo(int(env.get("RANK", "0")), int(env.get("LOCAL_RANK", "0")), int(env.get("WORLD_SIZE", "1")))
+
+    @property
+    def device_id(self) -> str:
+        """The device string plaidml_jit takes for this rank (pattern name.N, pmlc/rt/device_id.cc:13-38)."""
+        return f"cuda.{self.local_rank}"
+
+
+def row_slice(total_rows: int, rank: int, world: int) -> tuple[int, int]:
+    """[begin, end) of the rows rank owns when `total_rows` are split as evenly as possible (strong scaling:
+    the first total_rows % world ranks get one row more).  Every row belongs to exactly one rank."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world of {world}")
+    if total_rows < 0:
+        raise ValueError("negative row count")
+    base, extra = divmod(total_rows, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def weak_rows(rows_per_rank: int, rank: int, world: int) -> tuple[int, int]:
+    """[begin, end) in the global row numbering when every rank holds `rows_per_rank` rows (weak scaling)."""
+    begin, end = row_slice(rows_per_rank * world, rank, world)
+    return begin, end
+
+
+def shard_seed(base_seed: int, rank: int) -> int:
+    """Seed of a rank's private operand; the replicated operand uses `base_seed` itself on every rank."""
+    return base_seed + 1000 * (rank + 1)
+
+
+def barrier(dist) -> None:
+    if dist is not None and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+
+
+def max_over_ranks(dist, value: float, device=None) -> float:
+    """The slowest rank's figure; `device` is where the one-element tensor lives (a CUDA device under NCCL)."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return float(value)
+    import torch
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device or "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(dist, value: float, device=None) -> float:
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return float(value)
+    import torch
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device or "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def job_throughput(dist, units_this_rank: float, seconds_this_rank: float, device=None) -> float:
+    """Whole-job rate: the units all ranks processed divided by the slowest rank's time."""
+    units = sum_over_ranks(dist, units_this_rank, device)
+    seconds = max_over_ranks(dist, seconds_this_rank, device)
+    return units / seconds
