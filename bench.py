@@ -39,6 +39,9 @@ WORKLOAD = "cfg2: int8 x int8 -> int32 Tile GEMM, N=K=4096, M=4096 rows per GPU 
 NCU_TRAFFIC_BYTES = 52.58e6
 
 
+emit = None  # set by main(): writes the result line
+
+
 def measured_peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -106,8 +109,10 @@ def seeded_inputs(rank: int):
 
 def cpu_baseline(rows: int, threads: int, repeats: int = 1) -> dict:
     """Times the oracle's int8 GEMM loop nest on `rows` rows of the workload."""
+    # The launcher of multi-process runs exports OMP_NUM_THREADS=1; the CPU arm is meant to use every core,
+    # so the variable is set here, before the OpenMP runtime of the checker library starts.
+    os.environ["OMP_NUM_THREADS"] = str(threads)
     import oracle
-    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
     a, b = seeded_inputs(0)
     a = np.ascontiguousarray(a[:rows])
     oracle.gemm_i8_i32(a[:8], b)  # load the library, warm the caches
@@ -145,7 +150,7 @@ def run_reference_arm(args) -> None:
         "cpu_baseline": {"value": value, "unit": "TOP/s", "cores": threads, "kind": "port", "sample": results[0]["sample"]},
         "e2e": {"value": value, "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 def build_gemm_runner(device: str):
@@ -208,6 +213,16 @@ def main() -> None:
     ap.add_argument("--extras", type=int, default=1)
     ap.add_argument("--cpu-baseline-rows", type=int, default=256)
     args = ap.parse_args()
+    # Exactly one line goes to standard output: libraries that print there (NCCL's version banner) are sent
+    # to standard error for the duration of the run and the result line is written to the saved descriptor.
+    sys.stdout.flush()
+    result_fd = os.dup(1)
+    os.dup2(2, 1)
+    global emit
+
+    def emit(line: dict) -> None:
+        os.write(result_fd, (json.dumps(line) + "\n").encode())
+
     if args.impl == "reference":
         run_reference_arm(args)
         return
@@ -294,7 +309,7 @@ def main() -> None:
                 line["other_configs"] = extras(device, max(5, args.steps // 2))
             except Exception as e:  # the headline line must still be printed
                 line["other_configs"] = {"error": str(e)}
-    print(json.dumps(line))
+    emit(line)
     if dist is not None:
         dist.destroy_process_group()
 

@@ -129,6 +129,9 @@ typedef struct {
 /* Take the epilogue that serves outputs whose rows are not 16-byte aligned even when the
  * staged TMA-store epilogue would apply (for testing that path). */
 #define PMLB_GEMM_PLAIN_STORES 2
+/* Keep the staged epilogue but read the residual with ordinary loads instead of fetching its
+ * rows by TMA ahead of each chunk (for testing that both routes round identically). */
+#define PMLB_GEMM_PLAIN_RESIDUAL 4
 
 pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* desc, pmlb_plan** plan);
 

@@ -343,6 +343,7 @@ pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream_v, const void* a, con
   L.status = plan->status;
   L.bn_override = d.tile_n;
   L.force_slow_epilogue = (d.flags & PMLB_GEMM_PLAIN_STORES) != 0;
+  L.residual_from_global = (d.flags & PMLB_GEMM_PLAIN_RESIDUAL) != 0;
   L.trace = g_trace_buffer;
 
   if (plan->split) {

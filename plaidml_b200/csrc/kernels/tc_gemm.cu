@@ -20,8 +20,7 @@ namespace pmlb {
 // every instance is compiled in one of the tc_inst_*.cu files
 #define PMLB_TC_EXTERN(EB, BN, NS, IM, MN, OB, G)                                              \
   extern template cudaError_t launch_cfg<TcCfg<EB, BN, NS, IM, MN, OB, G>>(                     \
-      const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,          \
-      const CUtensorMap&, const TcParams&, int, cudaStream_t);
+      const TcMaps&, const TcParams&, int, cudaStream_t);
 PMLB_TC_LIST_H16(PMLB_TC_EXTERN, 1)
 PMLB_TC_LIST_H16(PMLB_TC_EXTERN, 2)
 PMLB_TC_LIST_MISC(PMLB_TC_EXTERN)
@@ -224,12 +223,13 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   p.idesc = make_idesc(eb, L.is_f16, L.b_mn, bn);
 
   const CUtensorMapDataType dt = map_dtype(eb, L.is_f16);
-  CUtensorMap ta0, ta1, tb0, tb1, tc_map;
-  std::memset(&tc_map, 0, sizeof(tc_map));
-  std::memset(&ta0, 0, sizeof(ta0));
-  std::memset(&ta1, 0, sizeof(ta1));
-  std::memset(&tb0, 0, sizeof(tb0));
-  std::memset(&tb1, 0, sizeof(tb1));
+  TcMaps maps;
+  std::memset(&maps, 0, sizeof(maps));
+  CUtensorMap& ta0 = maps.a0;
+  CUtensorMap& ta1 = maps.a1;
+  CUtensorMap& tb0 = maps.b0;
+  CUtensorMap& tb1 = maps.b1;
+  CUtensorMap& tc_map = maps.c;
 
   if (L.conv) {
     const ConvGeom& g = *L.conv;
@@ -355,6 +355,16 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
       }
     }
     p.fast_epi = fast ? 1 : 0;
+    // Residual rows ride the same staging buffers: fetched by TMA ahead of their chunk.
+    if (fast && L.out != nullptr && (L.epi_flags & kEpiResidual) && !L.residual_from_global) {
+      const uint64_t r_bs = L.batch > 1 ? static_cast<uint64_t>(L.res_batch_stride) * ob
+                                        : static_cast<uint64_t>(L.ldr) * ob * L.m;
+      if (!encode3d(&maps.r, out_map_dtype(L.out_dtype), ob, L.residual, L.n, L.m, L.batch,
+                    static_cast<uint64_t>(L.ldr) * ob, r_bs, 128 / ob, 32, 1, err)) {
+        return 1;
+      }
+      p.res_tma = 1;
+    }
   }
 
   const long long total = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n;
@@ -376,8 +386,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
 #define PMLB_TC_CASE(EB, BN, NS, IM, MN, OB, G)                                                 \
   if (!launched && eb == EB && bn == BN && L.nsplit == NS && (L.conv != nullptr) == IM &&       \
       L.b_mn == MN && ob_tmpl == OB && groups == G) {                                           \
-    ce = launch_cfg<TcCfg<EB, BN, NS, IM, MN, OB, G>>(ta0, ta1, tb0, tb1, tc_map, p, grid,      \
-                                                     stream);                                   \
+    ce = launch_cfg<TcCfg<EB, BN, NS, IM, MN, OB, G>>(maps, p, grid, stream);                   \
     launched = true;                                                                            \
   }
   for (int attempt = 0; attempt < 2 && !launched; ++attempt) {

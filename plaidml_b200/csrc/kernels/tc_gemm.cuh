@@ -52,10 +52,16 @@ struct TcParams {
   float* rowmax;         // kEpiRowMax target, [batch * m]
 
   int fast_epi;          // 1: staged TMA-store epilogue (needs 16-byte aligned output rows)
+  int res_tma;           // 1: the staged epilogue fetches residual rows by TMA into its staging buffers
 
   uint32_t idesc;        // tcgen05 instruction descriptor
   int* status;           // device word: 0 = ok, otherwise the first error code seen
   long long* trace;      // debugging: CTA 0 logs (role, tile, event, clock64) records here, or null
+};
+
+// The tensor maps of one launch: A (hi / lo parts), B (hi / lo parts), output and residual tiles.
+struct TcMaps {
+  CUtensorMap a0, a1, b0, b1, c, r;
 };
 
 }  // namespace pmlb

@@ -48,7 +48,7 @@ struct TcCfg {
   static constexpr int B_TILE = BN * 128;   // bytes
   static constexpr int STAGE = NSPLIT * (A_TILE + B_TILE);
   static constexpr int STG_BYTES = EPI_GROUPS_ * 4 * 2 * 4096;  // per epilogue warp: two 32-row x 128-byte buffers
-  static constexpr int BAR_BYTES = 256;
+  static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_LIMIT = 232448;                     // 227 KB per CTA
   static constexpr int RING_BUDGET = SMEM_LIMIT - 1024 - STG_BYTES - BAR_BYTES;
   static constexpr int STAGES_RAW = RING_BUDGET / STAGE;
@@ -150,9 +150,15 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int t) {
 // a ragged N.
 template <bool FULL, bool IS_INT, int OB, int CW>
 __device__ __forceinline__ float epi_apply(const TcParams& p, uint32_t (&v)[CW], int col0, int row,
-                                           long long res_row, bool out_bf16) {
+                                           long long res_row, bool out_bf16, uint32_t res_smem,
+                                           int lane) {
+  // res_smem != 0: this warp's 32 x 128-byte residual rows lie in shared memory (swizzled like
+  // the staged output; rows and columns outside the matrix hold zeros), else they are read
+  // from global memory.
   const int nvalid = FULL ? CW : (p.n - col0);
-  const bool want_res = (p.epi_flags & kEpiResidual) && row < p.m;
+  const bool want_res = (p.epi_flags & kEpiResidual) && (row < p.m || res_smem != 0);
+  const uint32_t res_line = res_smem + static_cast<uint32_t>(lane) * 128u;
+  const uint32_t res_xor = static_cast<uint32_t>(lane & 7);
   float chunk_best = -INFINITY;
   if constexpr (IS_INT) {
     // 32-bit integer results (OB == 4)
@@ -176,10 +182,15 @@ __device__ __forceinline__ float epi_apply(const TcParams& p, uint32_t (&v)[CW],
     }
     if (want_res) {
       const int* rp = static_cast<const int*>(p.residual) + res_row + col0;
-      if constexpr (FULL) {
+      if (FULL || res_smem != 0) {
 #pragma unroll
         for (int i = 0; i < CW / 4; ++i) {
-          const int4 r4 = __ldg(reinterpret_cast<const int4*>(rp) + i);
+          uint4 r4;
+          if (res_smem != 0) {
+            r4 = ld_shared_v4(res_line + ((static_cast<uint32_t>(i) ^ res_xor) << 4));
+          } else {
+            r4 = __ldg(reinterpret_cast<const uint4*>(rp) + i);
+          }
           v[4 * i + 0] += static_cast<uint32_t>(r4.x);
           v[4 * i + 1] += static_cast<uint32_t>(r4.y);
           v[4 * i + 2] += static_cast<uint32_t>(r4.z);
@@ -216,12 +227,17 @@ __device__ __forceinline__ float epi_apply(const TcParams& p, uint32_t (&v)[CW],
       }
     }
     if (want_res) {
-      if constexpr (FULL) {
+      if (FULL || res_smem != 0) {
         const uint4* rp = reinterpret_cast<const uint4*>(
             static_cast<const char*>(p.residual) + (res_row + col0) * OB);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const uint4 r4 = __ldg(rp + i);
+          uint4 r4;
+          if (res_smem != 0) {
+            r4 = ld_shared_v4(res_line + ((static_cast<uint32_t>(i) ^ res_xor) << 4));
+          } else {
+            r4 = __ldg(rp + i);
+          }
           const uint32_t w[4] = {r4.x, r4.y, r4.z, r4.w};
           if constexpr (OB == 4) {
 #pragma unroll
@@ -292,12 +308,7 @@ __device__ __forceinline__ float epi_apply(const TcParams& p, uint32_t (&v)[CW],
 
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
-tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
-                   const __grid_constant__ CUtensorMap tm_a1,
-                   const __grid_constant__ CUtensorMap tm_b0,
-                   const __grid_constant__ CUtensorMap tm_b1,
-                   const __grid_constant__ CUtensorMap tm_c,
-                   const __grid_constant__ TcParams p) {
+tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ TcParams p) {
   constexpr int BN = Cfg::BN;
   constexpr int BK = Cfg::BK;
   constexpr int STAGES = Cfg::STAGES;
@@ -316,7 +327,9 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  // two residual-arrival barriers per epilogue warp (at most 8 warps)
+  auto res_bar = [&](int ew, uint32_t i) { return bar0 + 8u * (2 * STAGES + 4 + 2 * ew + i); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* abort_code = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
@@ -332,15 +345,21 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 4);
     }
+    for (int w = 0; w < 8; ++w) {
+      mbar_init(res_bar(w, 0), 1);
+      mbar_init(res_bar(w, 1), 1);
+    }
     *abort_flag = 0;
     *abort_code = 0;
     fence_mbar_init();
-    tma_prefetch_desc(&tm_a0);
-    tma_prefetch_desc(&tm_b0);
+    tma_prefetch_desc(&tm.a0);
+    tma_prefetch_desc(&tm.b0);
     if (NSPLIT == 2) {
-      tma_prefetch_desc(&tm_a1);
-      tma_prefetch_desc(&tm_b1);
+      tma_prefetch_desc(&tm.a1);
+      tma_prefetch_desc(&tm.b1);
     }
+    if (p.fast_epi && p.out != nullptr) tma_prefetch_desc(&tm.c);
+    if (p.res_tma) tma_prefetch_desc(&tm.r);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -389,26 +408,26 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
             const int cb = kb - tap * p.conv_cblocks;
             const int fr = tap / p.conv_s;
             const int fs = tap - fr * p.conv_s;
-            tma_load_im2col_4d(s_a, &tm_a0, fb, cb * BK, pix_w, pix_h, pix_n,
+            tma_load_im2col_4d(s_a, &tm.a0, fb, cb * BK, pix_w, pix_h, pix_n,
                                static_cast<uint16_t>(fs * p.conv_dil_w),
                                static_cast<uint16_t>(fr * p.conv_dil_h));
             // weights laid out [k_out][tap][c_in]: map dims (c_in, tap, k_out)
-            tma_load_3d(s_b, &tm_b0, fb, cb * BK, tap, tc.tn * BN);
+            tma_load_3d(s_b, &tm.b0, fb, cb * BK, tap, tc.tn * BN);
           } else {
-            tma_load_3d(s_a, &tm_a0, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
+            tma_load_3d(s_a, &tm.a0, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
             if constexpr (NSPLIT == 2) {
-              tma_load_3d(s_a + Cfg::A_TILE, &tm_a1, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
+              tma_load_3d(s_a + Cfg::A_TILE, &tm.a1, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
             }
             if constexpr (Cfg::B_MN) {
 #pragma unroll
               for (int ch = 0; ch < Cfg::B_CHUNKS; ++ch) {
-                tma_load_3d(s_b + ch * (BK * 128), &tm_b0, fb, tc.tn * BN + ch * BK, kb * BK,
+                tma_load_3d(s_b + ch * (BK * 128), &tm.b0, fb, tc.tn * BN + ch * BK, kb * BK,
                             tc.b * p.b_bz);
               }
             } else {
-              tma_load_3d(s_b, &tm_b0, fb, kb * BK, tc.tn * BN, tc.b * p.b_bz);
+              tma_load_3d(s_b, &tm.b0, fb, kb * BK, tc.tn * BN, tc.b * p.b_bz);
               if constexpr (NSPLIT == 2) {
-                tma_load_3d(s_b + Cfg::B_TILE, &tm_b1, fb, kb * BK, tc.tn * BN, tc.b * p.b_bz);
+                tma_load_3d(s_b + Cfg::B_TILE, &tm.b1, fb, kb * BK, tc.tn * BN, tc.b * p.b_bz);
               }
             }
           }
@@ -496,15 +515,42 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
       constexpr int OB = Cfg::OUT_BYTES;
       const uint32_t stage_buf = smem_u32(stg_all) + static_cast<uint32_t>(ew) * 8192u;
       uint32_t nbuf = 0;
+      // Residual rows fetched by TMA land in the staging buffer their chunk is later stored
+      // from: chunk number k of this warp (counted over all tiles) uses buffer k & 1 and
+      // arrival barrier k & 1 in phase (k >> 1) & 1.  `nreq` counts the chunks requested.
+      const bool res_tma = p.res_tma != 0;
+      uint32_t nreq = 0;
+      bool alive = true;
       const bool out_bf16 = p.out_dtype == kDtBF16;
       int it = 0;
       int ntrace = 0;
       const bool tracer = (q == 2) && lane == 0;   // first warp of each group (warps 2 and 6)
-      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, ++it) {
         if (G == 2 && (it & 1) != grp) continue;
         const int acc = it & 1;
         const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
         const TileCoord tc = tile_coord(p, t);
+        const int row0 = tc.tm * 128 + q * 32;
+        const int row = row0 + lane;
+        const int col_base = tc.tn * BN;
+        auto request_res = [&](int ch) {
+          const int c0 = col_base + ch * CW;
+          if (ch < Cfg::BN / CW && c0 < p.n) {       // warp-uniform
+            if (lane == 0) {
+              const uint32_t b = nreq & 1u;
+              mbar_arrive_expect_tx(res_bar(ew, b), 4096u);
+              tma_load_3d(stage_buf + b * 4096u, &tm.r, res_bar(ew, b), c0, row0, tc.b);
+            }
+            ++nreq;
+          }
+        };
+        if (res_tma) {
+          // Both buffers are free once the stores of the previous tile have read them; the
+          // first two chunks' residual rows then arrive while the main loop still runs.
+          if (lane == 0) bulk_wait_group_read<0>();
+          request_res(0);
+          request_res(1);
+        }
         if (tracer) trace_event(p, 2 + grp, ntrace, t, 0);
         if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
           if (*abort_code == 0) *abort_code = 4;
@@ -512,9 +558,6 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
         }
         if (tracer) trace_event(p, 2 + grp, ntrace, t, 1);
         tc_fence_after_sync();
-        const int row0 = tc.tm * 128 + q * 32;
-        const int row = row0 + lane;
-        const int col_base = tc.tn * BN;
         const uint32_t t_acc =
             tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(q * 32) << 16);
         const long long res_row =
@@ -543,13 +586,30 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
         };
         auto process = [&](uint32_t(&v)[CW], int ch) {
           const int col0 = col_base + ch * CW;
-          if (col0 >= p.n) return;                    // warp-uniform
+          if (col0 >= p.n || !alive) return;          // warp-uniform
+          uint32_t res_smem = 0;
+          if (res_tma) {
+            // Chunk ch + 1 takes the buffer chunk ch - 1 was stored from (chunks 0 and 1
+            // were requested at the start of the tile).
+            if (ch >= 1) {
+              if (lane == 0) bulk_wait_group_read<0>();
+              request_res(ch + 1);
+            }
+            if (!mbar_wait(res_bar(ew, nbuf & 1u), (nbuf >> 1) & 1u, abort_flag)) {
+              if (*abort_code == 0) *abort_code = 5;
+              alive = false;
+              return;
+            }
+            res_smem = stage_buf + (nbuf & 1u) * 4096u;
+          }
           const float chunk_best =
               (col0 + CW <= p.n)
-                  ? epi_apply<true, IS_INT, OB, CW>(p, v, col0, row, res_row, out_bf16)
-                  : epi_apply<false, IS_INT, OB, CW>(p, v, col0, row, res_row, out_bf16);
+                  ? epi_apply<true, IS_INT, OB, CW>(p, v, col0, row, res_row, out_bf16, res_smem, lane)
+                  : epi_apply<false, IS_INT, OB, CW>(p, v, col0, row, res_row, out_bf16, res_smem, lane);
           if (p.epi_flags & kEpiRowMax) row_best = fmaxf(row_best, chunk_best);
-          if (p.out == nullptr || row0 >= p.m) return;   // warp-uniform
+          // (with TMA-fetched residuals every chunk is stored, rows past M being clipped by
+          // the store, so that buffers and barriers stay in step with the requests)
+          if (!res_tma && (p.out == nullptr || row0 >= p.m)) return;   // warp-uniform
 
           uint4 o[8];
           if constexpr (OB == 4) {
@@ -574,8 +634,9 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
               o[i] = make_uint4(w[0], w[1], w[2], w[3]);
             }
           }
-          // the buffer used two chunks ago must have been read by its TMA store
-          if (lane == 0) bulk_wait_group_read<1>();
+          // the buffer used two chunks ago must have been read by its TMA store (already
+          // true when its residual rows were requested)
+          if (!res_tma && lane == 0) bulk_wait_group_read<1>();
           __syncwarp();
           const uint32_t buf = stage_buf + (nbuf & 1u) * 4096u;
 #pragma unroll
@@ -585,7 +646,7 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(&tm_c, buf, col0, row0, tc.b);
+            tma_store_3d(&tm.c, buf, col0, row0, tc.b);
             bulk_commit_group();
           }
           ++nbuf;
@@ -735,14 +796,12 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap tm_a0,
 }
 
 template <class Cfg>
-cudaError_t launch_cfg(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
-                       const CUtensorMap& b1, const CUtensorMap& c, const TcParams& p, int grid,
-                       cudaStream_t stream) {
+cudaError_t launch_cfg(const TcMaps& maps, const TcParams& p, int grid, cudaStream_t stream) {
   // The attribute is per device, so it is set on every call (a cheap host-side update).
   const cudaError_t attr_err = cudaFuncSetAttribute(
       tc_contract_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
   if (attr_err != cudaSuccess) return attr_err;
-  tc_contract_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(a0, a1, b0, b1, c, p);
+  tc_contract_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(maps, p);
   return cudaGetLastError();
 }
 

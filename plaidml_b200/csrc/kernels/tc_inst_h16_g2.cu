@@ -5,8 +5,7 @@
 namespace pmlb {
 #define PMLB_TC_DEFINE(EB, BN, NS, IM, MN, OB, G)                                              \
   template cudaError_t launch_cfg<TcCfg<EB, BN, NS, IM, MN, OB, G>>(                            \
-      const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,          \
-      const CUtensorMap&, const TcParams&, int, cudaStream_t);
+      const TcMaps&, const TcParams&, int, cudaStream_t);
 PMLB_TC_LIST_H16(PMLB_TC_DEFINE, 2)
 #undef PMLB_TC_DEFINE
 }  // namespace pmlb

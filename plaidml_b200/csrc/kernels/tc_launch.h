@@ -51,6 +51,7 @@ struct TcLaunch {
   int* status = nullptr;  // device word that receives a non-zero code if a wait times out
 
   bool force_slow_epilogue = false;  // testing: take the transpose-and-store epilogue
+  bool residual_from_global = false;  // testing: staged epilogue reads the residual with plain loads
   int bn_override = 0;    // 0 = choose; else 64, 128 or 256
   int epi_groups_override = 0;  // 0 = choose; else 1 or 2
   int grid_override = 0;  // 0 = one CTA per SM

@@ -20,6 +20,7 @@ COMBO_NONE, COMBO_MUL, COMBO_ADD, COMBO_EQ, COMBO_COND = range(5)
 EPI_BIAS, EPI_RESIDUAL, EPI_RELU, EPI_ROWMAX = 1, 2, 4, 8
 GEMM_TRANSPOSE_B = 1
 GEMM_PLAIN_STORES = 2
+GEMM_PLAIN_RESIDUAL = 4
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = range(5)
 
 MAX_IDX, MAX_RANK, MAX_CONS = 10, 8, 8

@@ -136,12 +136,35 @@ def test_bf16_residual_partial_chunk_and_plain_stores():
     ref = ref + bias.cpu().numpy()[None, None, :] + as_f32(res)
     ref = oracle.bf16_to_f32(oracle.f32_to_bf16(np.where(ref < 0, 0, ref)))
     outs = []
-    for flags in (0, K.GEMM_PLAIN_STORES):
+    for flags in (0, K.GEMM_PLAIN_STORES, K.GEMM_PLAIN_RESIDUAL):
         c, _, _ = run_gemm(K.BF16, K.BF16, a, b, m, n, k, batch=2, flags=flags,
                            epilogue=K.EPI_BIAS | K.EPI_RESIDUAL | K.EPI_RELU, bias=bias, residual=res)
         check_close(as_f32(c), ref, 1e-2)
         outs.append(bits16(c))
-    np.testing.assert_array_equal(outs[0], outs[1])   # both epilogues round identically
+    np.testing.assert_array_equal(outs[0], outs[1])   # all three epilogue routes round identically
+    np.testing.assert_array_equal(outs[0], outs[2])
+
+
+@pytest.mark.parametrize("k,tile_n", [(64, 0), (64, 128), (1664, 256), (192, 64)])
+def test_bf16_residual_many_tiles_per_sm(k, tile_n):
+    # more tiles than SMs (each CTA walks several, so the residual buffers and their barriers wrap many
+    # times), ragged M and N; short and long main loops take the two-group and one-group epilogues
+    g = rng(40 + k)
+    m, n = 128 * 150 + 40, 456
+    a = dev_bf16(g.standard_normal((1, m, k)))
+    b = dev_bf16(g.standard_normal((1, n, k)) * 0.1)
+    res = dev_bf16(g.standard_normal((1, m, n)))
+    bias = dev(g.standard_normal(n).astype(np.float32))
+    outs = []
+    for flags in (0, K.GEMM_PLAIN_RESIDUAL):
+        c, _, _ = run_gemm(K.BF16, K.BF16, a, b, m, n, k, flags=flags, tile_n=tile_n,
+                           epilogue=K.EPI_BIAS | K.EPI_RESIDUAL | K.EPI_RELU, bias=bias, residual=res)
+        outs.append(bits16(c))
+    np.testing.assert_array_equal(outs[0], outs[1])
+    ref = oracle.gemm_h16_f32(bits16(a), bits16(b), False, True)
+    ref = ref + bias.cpu().numpy()[None, None, :] + as_f32(res)
+    ref = oracle.bf16_to_f32(oracle.f32_to_bf16(np.where(ref < 0, 0, ref)))
+    check_close(oracle.bf16_to_f32(outs[0]), ref, 1e-2)
 
 
 def test_f32_out_residual_f32():
