@@ -184,7 +184,16 @@ typedef struct {
   int32_t dil_h, dil_w;
   int32_t epilogue;
   int32_t tile_n;
+  int32_t flags;                     /* PMLB_CONV_* */
 } pmlb_conv_desc;
+
+/* Thin inputs (c padded to a multiple of 8 is at most 32, s * that <= 64 elements, k <= 64,
+ * no dilation: the first layer of image networks) take the packed-row route: the activation
+ * is first copied into plan scratch with its rows zero-padded and its channels padded to a
+ * multiple of 8, and each filter row then costs one 64-element k-block instead of s of them.
+ * Such inputs may have any channel count; all others need c % 8 == 0.  This flag keeps an
+ * eligible convolution on the general im2col route (for testing one against the other). */
+#define PMLB_CONV_NO_PACKED_ROWS 1
 
 pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* desc, pmlb_plan** plan);
 

@@ -1,6 +1,8 @@
 // Planner and executor of the `cuda` device.
 #include "pml_exec.h"
 
+#include "../kernels/conv_route.h"
+
 #include <algorithm>
 #include <chrono>
 #include <cstring>
@@ -582,7 +584,6 @@ class Planner {
       int a, b, inDtype, outDtype;
       if (!tcTypes(opI, opF, outShape.dtype, &a, &b, &inDtype, &outDtype)) continue;
       if (inDtype != PMLB_BF16 && inDtype != PMLB_F16) continue;
-      if (is.sizes[3] % 8 != 0) continue;
       // plain 1x1 stride-1 convolutions are GEMMs; let that path take them
       if (fs.sizes[0] == 1 && fs.sizes[1] == 1 && stride[0] == 1 && stride[1] == 1 && pad[0] == 0 && pad[1] == 0) {
         return false;
@@ -606,6 +607,8 @@ class Planner {
       d.dil_h = static_cast<int32_t>(dil[0]);
       d.dil_w = static_cast<int32_t>(dil[1]);
       if (d.pad_h > 127 || d.pad_w > 127 || d.stride_h > 8 || d.stride_w > 8) continue;
+      // the im2col route needs whole 16-byte channel groups; thin inputs take the packed-row route
+      if (d.c % 8 != 0 && !pmlb::conv_takes_packed_rows(d)) continue;
       pd->kind = Pending::Conv;
       pd->a = a;
       pd->b = b;
@@ -860,7 +863,9 @@ class Planner {
         pmlbCheck(rc, "conv dispatch for '" + label + "'");
         pmlbCheck(pmlb_plan_share_status(plan, exe_->status_), "status word");
         st.plan = plan;
-        st.kernel = "tc_conv";
+        st.kernel = pmlb_plan_kind(plan);          // "tc_conv", or "tc_conv_rows" for the packed-row route
+        const int extra = std::string(st.kernel) == "tc_conv_rows" ? 1 : 0;   // its activation packing pass
+        st.launches = 1 + extra;
         std::ostringstream os;
         const pmlb_conv_desc& d = pd.conv;
         os << label << " n" << d.n << " " << d.h << "x" << d.w << "x" << d.c << " (*) " << d.r << "x" << d.s << "/"
@@ -879,7 +884,7 @@ class Planner {
           pmlbCheck(pmlb_conv_set_filter(plan, exe_->stream_, f, fdt), "filter layout");
           st.launch = [plan, x, out, bias, res](cudaStream_t s) { return pmlb_conv_invoke(plan, s, x, out, bias, res); };
         } else {
-          st.launches = 2;
+          st.launches = 2 + extra;
           st.launch = [plan, x, f, fdt, out, bias, res](cudaStream_t s) {
             pmlb_status r = pmlb_conv_set_filter(plan, s, f, fdt);
             if (r != PMLB_OK) return r;

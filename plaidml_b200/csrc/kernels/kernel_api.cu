@@ -11,6 +11,7 @@
 #include "prepass.h"
 #include "reduce.h"
 #include "tc_gemm.cuh"
+#include "conv_route.h"
 #include "tc_launch.h"
 
 namespace {
@@ -96,6 +97,8 @@ struct pmlb_plan {
 
   pmlb_conv_desc conv;
   bool filter_set = false;
+  bool packed_rows = false;      // conv: packed-row route (scratch = weights, then the padded activation)
+  size_t packed_input_off = 0;   // byte offset of the padded activation inside scratch
 
   pmlb_reduce_desc reduce;
   pmlb_pool_desc pool;
@@ -429,7 +432,8 @@ pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* d, pmlb_plan** out) {
       d->dil_w <= 0 || d->pad_h < 0 || d->pad_w < 0) {
     return fail(PMLB_ERR_INVALID, "conv: bad geometry");
   }
-  if (d->c % 8 != 0) {
+  const bool packed = pmlb::conv_takes_packed_rows(*d) && (d->flags & PMLB_CONV_NO_PACKED_ROWS) == 0;
+  if (!packed && d->c % 8 != 0) {
     return fail(PMLB_ERR_UNSUPPORTED, "conv: channel count must be a multiple of 8");
   }
   // every output pixel's first tap must lie inside the im2col bounding box
@@ -445,7 +449,16 @@ pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* d, pmlb_plan** out) {
   plan->kind = kPlanConv;
   plan->kind_name = "tc_conv";
   plan->conv = *d;
-  const size_t scratch = static_cast<size_t>(d->k) * d->r * d->s * d->c * 2;
+  size_t scratch = static_cast<size_t>(d->k) * d->r * d->s * d->c * 2;
+  if (packed) {
+    plan->packed_rows = true;
+    plan->kind_name = "tc_conv_rows";
+    const size_t wts = static_cast<size_t>(d->k) * d->r * 64 * 2;
+    plan->packed_input_off = (wts + 255) / 256 * 256;
+    scratch = plan->packed_input_off + static_cast<size_t>(d->n) * d->h *
+                                           pmlb::conv_packed_row_width(*d) *
+                                           pmlb::conv_padded_channels(*d) * 2;
+  }
   pmlb_status st = alloc_plan_memory(plan, scratch, true);
   if (st != PMLB_OK) {
     pmlb_plan_free(plan);
@@ -462,8 +475,15 @@ pmlb_status pmlb_conv_set_filter(pmlb_plan* plan, void* stream, const void* filt
     return fail(PMLB_ERR_UNSUPPORTED, "conv: filter must be f32, bf16 or f16");
   }
   const pmlb_conv_desc& d = plan->conv;
-  cudaError_t e = pmlb::launch_filter_relayout(filter, dtype, plan->scratch, d.in_dtype, d.r * d.s,
-                                               d.c, d.k, static_cast<cudaStream_t>(stream));
+  cudaError_t e;
+  if (plan->packed_rows) {
+    e = pmlb::launch_filter_pack_rows(filter, dtype, plan->scratch, d.in_dtype, d.r, d.s, d.c,
+                                      pmlb::conv_padded_channels(d), d.k,
+                                      static_cast<cudaStream_t>(stream));
+  } else {
+    e = pmlb::launch_filter_relayout(filter, dtype, plan->scratch, d.in_dtype, d.r * d.s, d.c, d.k,
+                                     static_cast<cudaStream_t>(stream));
+  }
   if (e != cudaSuccess) return cuda_fail(e, "filter relayout");
   plan->filter_set = true;
   return PMLB_OK;
@@ -477,6 +497,44 @@ pmlb_status pmlb_conv_invoke(pmlb_plan* plan, void* stream, const void* input, v
   const pmlb_conv_desc& d = plan->conv;
   if ((d.epilogue & PMLB_EPI_BIAS) && !bias) return fail(PMLB_ERR_INVALID, "conv: bias missing");
   if ((d.epilogue & PMLB_EPI_RESIDUAL) && !residual) return fail(PMLB_ERR_INVALID, "conv: residual missing");
+  if (plan->packed_rows) {
+    const int cp = pmlb::conv_padded_channels(d);
+    const int wp = pmlb::conv_packed_row_width(d);
+    void* padded = static_cast<char*>(plan->scratch) + plan->packed_input_off;
+    cudaError_t e = pmlb::launch_pack_rows(input, padded, d.n, d.h, d.w, d.c, wp, cp, d.pad_w,
+                                           static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, "activation row packing");
+    pmlb::WinGeom g;
+    g.n = d.n; g.h = d.h; g.wp = wp; g.cp = cp;
+    g.r = d.r; g.s = d.s; g.p = d.p; g.q = d.q;
+    g.stride_h = d.stride_h; g.stride_w = d.stride_w;
+    g.pad_h = d.pad_h;
+    pmlb::TcLaunch L;
+    L.elem_bytes = 2;
+    L.is_f16 = d.in_dtype == PMLB_F16;
+    L.m = d.q;
+    L.n = d.k;
+    L.k = d.r * 64;
+    L.batch = d.n * d.p;
+    L.a0 = padded;
+    L.b0 = plan->scratch;
+    L.window = &g;
+    L.out = output;
+    L.ldc = d.k;
+    L.out_batch_stride = static_cast<long long>(d.q) * d.k;
+    L.out_dtype = d.out_dtype;
+    L.epi_flags = d.epilogue;
+    L.bias = bias;
+    L.residual = residual;
+    L.ldr = d.k;
+    L.res_batch_stride = static_cast<long long>(d.q) * d.k;
+    L.status = plan->status;
+    L.trace = g_trace_buffer;
+    std::string err;
+    const int rc = pmlb::tc_launch(L, static_cast<cudaStream_t>(stream), &err);
+    if (rc != 0) return fail(static_cast<pmlb_status>(rc), "conv (packed rows): " + err);
+    return PMLB_OK;
+  }
   pmlb::ConvGeom g;
   g.n = d.n; g.h = d.h; g.w = d.w; g.c = d.c;
   g.r = d.r; g.s = d.s; g.p = d.p; g.q = d.q;

@@ -102,7 +102,80 @@ filter_relayout_kernel(const void* __restrict__ in, int in_dtype, void* __restri
   }
 }
 
+// One thread per group of 8 output channels of one output pixel (16 bytes).
+__global__ void __launch_bounds__(256)
+pack_rows_kernel(const uint16_t* __restrict__ in, uint4* __restrict__ out, long long rows, int w,
+                 int c, int wp, int cp8, int pad_w) {
+  const long long id = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long total = rows * wp * cp8;
+  if (id >= total) return;
+  const int g = static_cast<int>(id % cp8);
+  const long long pix = id / cp8;
+  const int x = static_cast<int>(pix % wp);
+  const long long row = pix / wp;     // n * h + hh
+  const int src_w = x - pad_w;
+  uint32_t words[4] = {0u, 0u, 0u, 0u};
+  if (src_w >= 0 && src_w < w) {
+    const uint16_t* src = in + (row * w + src_w) * c;
+    const int c0 = g * 8;
+    if (c0 + 8 <= c && (c % 8) == 0 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + c0));
+      words[0] = v.x; words[1] = v.y; words[2] = v.z; words[3] = v.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t e = (c0 + j < c) ? static_cast<uint32_t>(__ldg(src + c0 + j)) : 0u;
+        words[j >> 1] |= e << ((j & 1) * 16);
+      }
+    }
+  }
+  out[id] = make_uint4(words[0], words[1], words[2], words[3]);
+}
+
+__global__ void __launch_bounds__(256)
+filter_pack_rows_kernel(const void* __restrict__ in, int in_dtype, void* __restrict__ out,
+                        int out_dtype, int r, int s, int c, int cp, int k) {
+  const long long id = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long total = static_cast<long long>(k) * r * 64;
+  if (id >= total) return;
+  // id walks the output [k][r][64]
+  const int e = static_cast<int>(id % 64);
+  const long long rem = id / 64;
+  const int fr = static_cast<int>(rem % r);
+  const int ko = static_cast<int>(rem / r);
+  const int fs = e / cp;
+  const int ci = e - fs * cp;
+  float v = 0.f;
+  if (fs < s && ci < c) {
+    v = load_filter(in, in_dtype, ((static_cast<long long>(fr) * s + fs) * c + ci) * k + ko);
+  }
+  if (out_dtype == PMLB_BF16) {
+    static_cast<__nv_bfloat16*>(out)[id] = __float2bfloat16_rn(v);
+  } else {
+    static_cast<__half*>(out)[id] = __float2half_rn(v);
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_pack_rows(const void* in, void* out, int n, int h, int w, int c, int wp, int cp,
+                             int pad_w, cudaStream_t stream) {
+  const long long rows = static_cast<long long>(n) * h;
+  const long long total = rows * wp * (cp / 8);
+  if (total <= 0) return cudaSuccess;
+  pack_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      static_cast<const uint16_t*>(in), static_cast<uint4*>(out), rows, w, c, wp, cp / 8, pad_w);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_filter_pack_rows(const void* in, int in_dtype, void* out, int out_dtype, int r,
+                                    int s, int c, int cp, int k, cudaStream_t stream) {
+  const long long total = static_cast<long long>(k) * r * 64;
+  if (total <= 0) return cudaSuccess;
+  filter_pack_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      in, in_dtype, out, out_dtype, r, s, c, cp, k);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_split_tf32(const float* in, long long ld, long long in_batch, float* hi,
                               float* lo, long long out_ld, long long out_batch, int rows, int cols,

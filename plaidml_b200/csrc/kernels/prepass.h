@@ -23,4 +23,14 @@ cudaError_t launch_transpose(const void* in, long long ld, long long in_batch, v
 cudaError_t launch_filter_relayout(const void* in, int in_dtype, void* out, int out_dtype, int taps,
                                    int c, int k, cudaStream_t stream);
 
+// Packed-row convolution operands (16-bit elements).
+// Activation [n][h][w][c] -> [n][h][wp][cp]: `pad_w` zero pixels before every row, zeros after
+// it up to `wp` pixels, channels zero-padded from c to cp (a multiple of 8).
+cudaError_t launch_pack_rows(const void* in, void* out, int n, int h, int w, int c, int wp, int cp,
+                             int pad_w, cudaStream_t stream);
+// Filter [r][s][c][k] (f32, bf16 or f16) -> [k][r][64] in the 16-bit `out_dtype`, element
+// s * cp + ci of each 64-element row holding tap (r, s) of channel ci, zeros elsewhere.
+cudaError_t launch_filter_pack_rows(const void* in, int in_dtype, void* out, int out_dtype, int r,
+                                    int s, int c, int cp, int k, cudaStream_t stream);
+
 }  // namespace pmlb

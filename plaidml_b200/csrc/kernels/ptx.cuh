@@ -127,6 +127,18 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// Tiled 4-D load (coordinates innermost first; same alignment rule for x).  Coordinates other
+// than x may lie outside the tensor: those elements arrive as zeros.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
 // im2col 4-D load over an NHWC activation tensor described as (C, W, H, N):
 // (w, h, n) is the base pixel inside the bounding box, (off_w, off_h) the filter
 // tap offset added to every pixel; `pixelsPerColumn` pixels are walked W-then-H-

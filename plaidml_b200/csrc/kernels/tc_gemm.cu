@@ -231,7 +231,61 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   CUtensorMap& tb1 = maps.b1;
   CUtensorMap& tc_map = maps.c;
 
-  if (L.conv) {
+  if (L.window) {
+    const WinGeom& g = *L.window;
+    const int row_elems = g.s * g.cp;
+    if (eb != 2 || L.nsplit != 1 || L.b_mn || g.cp % 8 != 0 || row_elems > 64 || L.n > 64 ||
+        g.stride_h > g.r || g.r > 12 || L.m != g.q || L.batch != g.n * g.p) {
+      *err = "packed-row convolution: geometry outside what the kernel takes";
+      return 3;
+    }
+    bn = 64;
+    p.tiles_n = 1;
+    p.idesc = make_idesc(eb, L.is_f16, false, bn);
+    const int slot_rows = std::min(128, (g.q + 7) / 8 * 8);
+    p.win_r = g.r;
+    p.win_slot_bytes = slot_rows * 128;
+    // ring bytes of the 64-wide 16-bit instance with one epilogue group
+    const int ring_bytes = TcCfg<2, 64, 1, kAWindow, false, 2, 1>::STAGES *
+                           TcCfg<2, 64, 1, kAWindow, false, 2, 1>::STAGE;
+    p.win_slots = std::min(16, (ring_bytes - g.r * 64 * 128 - (128 - slot_rows) * 128) /
+                                   p.win_slot_bytes);
+    if (p.win_slots <= g.r) {
+      *err = "packed-row convolution: filter too tall for the row ring";
+      return 3;
+    }
+    p.conv_p = g.p;
+    p.conv_stride_h = g.stride_h;
+    p.conv_lower_h = -g.pad_h;
+    p.num_kb = g.r;
+    if ((reinterpret_cast<uintptr_t>(L.a0) & 15u) != 0 || (reinterpret_cast<uintptr_t>(L.b0) & 15u) != 0) {
+      *err = "operand base addresses must be 16-byte aligned";
+      return 1;
+    }
+    // activation seen as (row window of s * cp elements, q, h, n): windows of neighbouring
+    // output columns overlap, so the q stride is smaller than the window
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(row_elems), static_cast<cuuint64_t>(g.q),
+                          static_cast<cuuint64_t>(g.h), static_cast<cuuint64_t>(g.n)};
+    const cuuint64_t pitch = static_cast<cuuint64_t>(g.wp) * g.cp * eb;
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(g.stride_w) * g.cp * eb, pitch, pitch * g.h};
+    cuuint32_t box[4] = {64, static_cast<cuuint32_t>(slot_rows), 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = g_encode_tiled(&ta0, dt, 4, const_cast<void*>(L.a0), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      *err = "cuTensorMapEncodeTiled (row windows) failed with code " +
+             std::to_string(static_cast<int>(r));
+      return 2;
+    }
+    ta1 = ta0;
+    // weights [k_out][r][64]
+    if (!encode3d(&tb0, dt, eb, L.b0, 64, g.r, L.n, 64ull * eb, 64ull * g.r * eb, bk, 1, bn, err)) {
+      return 1;
+    }
+    tb1 = tb0;
+  } else if (L.conv) {
     const ConvGeom& g = *L.conv;
     if (g.c % 8 != 0) {
       *err = "im2col path needs the channel count to be a multiple of 8";
@@ -382,9 +436,11 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   if (const char* env = std::getenv("PMLB_TC_EPI_GROUPS")) {
     if (env[0] == '1' || env[0] == '2') groups = env[0] - '0';
   }
+  if (L.window) groups = 1;  // the row ring leaves room for one group's staging buffers only
+  const int a_mode = L.window ? kAWindow : (L.conv ? kAIm2col : kATiled);
   bool launched = false;
 #define PMLB_TC_CASE(EB, BN, NS, IM, MN, OB, G)                                                 \
-  if (!launched && eb == EB && bn == BN && L.nsplit == NS && (L.conv != nullptr) == IM &&       \
+  if (!launched && eb == EB && bn == BN && L.nsplit == NS && a_mode == static_cast<int>(IM) &&  \
       L.b_mn == MN && ob_tmpl == OB && groups == G) {                                           \
     ce = launch_cfg<TcCfg<EB, BN, NS, IM, MN, OB, G>>(maps, p, grid, stream);                   \
     launched = true;                                                                            \

@@ -38,6 +38,10 @@ struct TcParams {
   int conv_stride_h, conv_stride_w;
   int conv_lower_h, conv_lower_w;  // bounding-box lower corner (= -pad)
   int conv_dil_h, conv_dil_w;
+  // Packed-row convolution (A fetched as whole input rows into a ring of row slots).
+  int win_r;                   // filter rows = k-blocks per output row
+  int win_slots;               // row slots in the ring (> win_r, at most 16)
+  int win_slot_bytes;          // bytes per slot (rows of 128 bytes, a multiple of 1024)
 
   // Epilogue
   void* out;

@@ -27,7 +27,15 @@
 
 namespace pmlb {
 
-template <int EB, int BN_, int NSPLIT_, bool A_IM2COL_, bool B_MN_, int OUT_BYTES_ = 4,
+// How the A operand reaches shared memory.
+enum : int {
+  kATiled = 0,   // a [m][k] matrix, tiled TMA
+  kAIm2col = 1,  // an NHWC activation, im2col TMA: one k-block per filter tap and channel block
+  kAWindow = 2,  // a packed-row activation: one k-block per filter row, each input row fetched
+                 // once into a ring of row slots and reused by the output rows that overlap it
+};
+
+template <int EB, int BN_, int NSPLIT_, int A_MODE_, bool B_MN_, int OUT_BYTES_ = 4,
           int EPI_GROUPS_ = 1>
 struct TcCfg {
   // 1: four epilogue warps drain both TMEM accumulators in turn (TMEM loads software-
@@ -40,7 +48,9 @@ struct TcCfg {
   static constexpr int BM = 128;
   static constexpr int BN = BN_;
   static constexpr int NSPLIT = NSPLIT_;
-  static constexpr bool A_IM2COL = A_IM2COL_;
+  static constexpr int A_MODE = A_MODE_;
+  static constexpr bool A_IM2COL = A_MODE_ == kAIm2col;
+  static constexpr bool A_WINDOW = A_MODE_ == kAWindow;
   static constexpr bool B_MN = B_MN_;
   static constexpr int BK = 128 / EB;       // elements of K per stage
   static constexpr int UMMA_K = 32 / EB;    // elements of K per tcgen05.mma
@@ -48,7 +58,7 @@ struct TcCfg {
   static constexpr int B_TILE = BN * 128;   // bytes
   static constexpr int STAGE = NSPLIT * (A_TILE + B_TILE);
   static constexpr int STG_BYTES = EPI_GROUPS_ * 4 * 2 * 4096;  // per epilogue warp: two 32-row x 128-byte buffers
-  static constexpr int BAR_BYTES = 512;
+  static constexpr int BAR_BYTES = 1024;
   static constexpr int SMEM_LIMIT = 232448;                     // 227 KB per CTA
   static constexpr int RING_BUDGET = SMEM_LIMIT - 1024 - STG_BYTES - BAR_BYTES;
   static constexpr int STAGES_RAW = RING_BUDGET / STAGE;
@@ -142,6 +152,37 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int t) {
   c.tm = first_m + rr % gm;
   c.tn = rr / gm;
   return c;
+}
+
+// Packed-row convolution: tile t is output row `op` of strip (image `img`, segment `tm` of 128
+// output columns); tiles of a strip are consecutive so that a CTA walking a contiguous range
+// of tiles slides its window of input rows down the image.  As a batched problem the tile is
+// batch entry img * P + op.
+struct WinCoord {
+  int strip, img, op, tm;
+};
+
+__device__ __forceinline__ WinCoord win_coord(const TcParams& p, int t) {
+  WinCoord c;
+  c.strip = t / p.conv_p;
+  c.op = t - c.strip * p.conv_p;
+  c.img = c.strip / p.tiles_m;
+  c.tm = c.strip - c.img * p.tiles_m;
+  return c;
+}
+
+template <class Cfg>
+__device__ __forceinline__ TileCoord tile_coord_for(const TcParams& p, int t) {
+  if constexpr (Cfg::A_WINDOW) {
+    const WinCoord w = win_coord(p, t);
+    TileCoord c;
+    c.b = w.img * p.conv_p + w.op;
+    c.tm = w.tm;
+    c.tn = 0;
+    return c;
+  } else {
+    return tile_coord(p, t);
+  }
 }
 
 // Epilogue arithmetic on one staged chunk: CW accumulator columns of this thread's row.
@@ -329,7 +370,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
   // two residual-arrival barriers per epilogue warp (at most 8 warps)
   auto res_bar = [&](int ew, uint32_t i) { return bar0 + 8u * (2 * STAGES + 4 + 2 * ew + i); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + 16);
+  // packed-row mode: arrival / release barriers of up to 16 row slots, one for the weights
+  auto wfull_bar = [&](uint32_t i) { return bar0 + 8u * (2 * STAGES + 20 + i); };
+  auto wempty_bar = [&](uint32_t i) { return bar0 + 8u * (2 * STAGES + 36 + i); };
+  const uint32_t wts_bar = bar0 + 8u * (2 * STAGES + 52);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 53);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* abort_code = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
@@ -348,6 +393,13 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     for (int w = 0; w < 8; ++w) {
       mbar_init(res_bar(w, 0), 1);
       mbar_init(res_bar(w, 1), 1);
+    }
+    if constexpr (Cfg::A_WINDOW) {
+      for (uint32_t i = 0; i < 16; ++i) {
+        mbar_init(wfull_bar(i), 1);
+        mbar_init(wempty_bar(i), 1);
+      }
+      mbar_init(wts_bar, 1);
     }
     *abort_flag = 0;
     *abort_code = 0;
@@ -371,6 +423,16 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   const uint32_t tmem_base = *tmem_slot;
 
   const int total_tiles = p.batch * p.tiles_m * p.tiles_n;
+  // Tiles this CTA walks: every gridDim.x-th one, or (packed-row mode) a contiguous range.
+  int t_begin = blockIdx.x, t_end = total_tiles, t_step = gridDim.x;
+  if constexpr (Cfg::A_WINDOW) {
+    t_begin = static_cast<int>(static_cast<long long>(total_tiles) * blockIdx.x / gridDim.x);
+    t_end = static_cast<int>(static_cast<long long>(total_tiles) * (blockIdx.x + 1) / gridDim.x);
+    t_step = 1;
+  }
+  // packed-row mode: the weights of all filter rows stay in shared memory ahead of the row slots
+  const uint32_t win_wts = ring;
+  const uint32_t win_slots = ring + static_cast<uint32_t>(p.win_r) * Cfg::B_TILE;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -379,8 +441,43 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       uint32_t phase = 0;
       bool ok = true;
       int ntrace = 0;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const TileCoord tc = tile_coord(p, t);
+      if constexpr (Cfg::A_WINDOW) {
+        // Weights of every filter row, once.
+        mbar_arrive_expect_tx(wts_bar, static_cast<uint32_t>(p.win_r) * Cfg::B_TILE);
+        for (int r = 0; r < p.win_r; ++r) {
+          tma_load_3d(win_wts + r * Cfg::B_TILE, &tm.b0, wts_bar, 0, r, 0);
+        }
+        // Input rows in the order the output rows need them; `cnt` numbers them, row number
+        // cnt goes to slot cnt % slots.
+        uint32_t cnt = 0;
+        int cur_strip = -1, next_h = 0;
+        const uint32_t nslots = static_cast<uint32_t>(p.win_slots);
+        for (int t = t_begin; t < t_end && ok; ++t) {
+          const WinCoord wc = win_coord(p, t);
+          const int lo = wc.op * p.conv_stride_h + p.conv_lower_h;
+          if (wc.strip != cur_strip) {
+            cur_strip = wc.strip;
+            next_h = lo;
+          }
+          for (int h = next_h; h < lo + p.win_r; ++h) {
+            const uint32_t slot = cnt % nslots;
+            const uint32_t use = cnt / nslots;
+            if (use > 0 && !mbar_wait(wempty_bar(slot), (use - 1u) & 1u, abort_flag)) {
+              if (*abort_code == 0) *abort_code = 1;
+              ok = false;
+              break;
+            }
+            trace_event(p, 0, ntrace, t, h);
+            mbar_arrive_expect_tx(wfull_bar(slot), static_cast<uint32_t>(p.win_slot_bytes));
+            tma_load_4d(win_slots + slot * static_cast<uint32_t>(p.win_slot_bytes), &tm.a0,
+                        wfull_bar(slot), 0, wc.tm * 128, h, wc.img);
+            ++cnt;
+          }
+          next_h = lo + p.win_r;
+        }
+      }
+      for (int t = t_begin; t < t_end && ok && !Cfg::A_WINDOW; t += t_step) {
+        const TileCoord tc = tile_coord_for<Cfg>(p, t);
         int pix_w = 0, pix_h = 0, pix_n = 0;
         if constexpr (Cfg::A_IM2COL) {
           const int m0 = tc.tm * 128;
@@ -447,7 +544,64 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       uint32_t acc_phase = 0;
       bool ok = true;
       int ntrace = 0;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      if constexpr (Cfg::A_WINDOW) {
+        const uint32_t nslots = static_cast<uint32_t>(p.win_slots);
+        // Row h of the current strip has number h + delta; `cnt_end` rows have been numbered
+        // so far and the rows below number `waited` are known to have arrived.
+        uint32_t cnt_end = 0, waited = 0;
+        int cur_strip = -1, delta = 0;
+        if (t_begin < t_end && !mbar_wait(wts_bar, 0u, abort_flag)) {
+          if (*abort_code == 0) *abort_code = 3;
+          ok = false;
+        }
+        for (int t = t_begin; t < t_end && ok; ++t) {
+          if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+            if (*abort_code == 0) *abort_code = 2;
+            break;
+          }
+          const WinCoord wc = win_coord(p, t);
+          const int lo = wc.op * p.conv_stride_h + p.conv_lower_h;
+          if (wc.strip != cur_strip) {
+            cur_strip = wc.strip;
+            delta = static_cast<int>(cnt_end) - lo;
+          }
+          const uint32_t c0 = static_cast<uint32_t>(lo + delta);
+          for (uint32_t c = (waited > c0 ? waited : c0); c < c0 + p.win_r && ok; ++c) {
+            if (!mbar_wait(wfull_bar(c % nslots), (c / nslots) & 1u, abort_flag)) {
+              if (*abort_code == 0) *abort_code = 3;
+              ok = false;
+            }
+          }
+          if (!ok) break;
+          waited = c0 + p.win_r;
+          tc_fence_after_sync();
+          trace_event(p, 1, ntrace, t, 2);
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+          for (int r = 0; r < p.win_r; ++r) {
+            const uint32_t s_a =
+                win_slots + ((c0 + r) % nslots) * static_cast<uint32_t>(p.win_slot_bytes);
+            const uint32_t s_b = win_wts + r * Cfg::B_TILE;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint64_t a_d = make_smem_desc_sw128(s_a + j * 32, 16, 1024);
+              const uint64_t b_d = make_smem_desc_sw128(s_b + j * 32, 16, 1024);
+              tc_mma<Cfg::KIND>(d_tmem, a_d, b_d, p.idesc, (r > 0 || j > 0) ? 1u : 0u);
+            }
+          }
+          // Rows the next output row of this CTA does not read go back to the producer.
+          const bool slides = (t + 1 < t_end) && ((t + 1) / p.conv_p == wc.strip);
+          const int nrel = slides ? p.conv_stride_h : p.win_r;
+          for (int r = 0; r < nrel; ++r) tc_commit(wempty_bar((c0 + r) % nslots));
+          cnt_end = c0 + p.win_r;
+          tc_commit(tfull_bar(acc));
+          trace_event(p, 1, ntrace, t, 3);
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1u;
+          }
+        }
+      }
+      for (int t = t_begin; t < t_end && ok && !Cfg::A_WINDOW; t += t_step) {
         trace_event(p, 1, ntrace, t, 0);
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
           if (*abort_code == 0) *abort_code = 2;
@@ -525,11 +679,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       int it = 0;
       int ntrace = 0;
       const bool tracer = (q == 2) && lane == 0;   // first warp of each group (warps 2 and 6)
-      for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, ++it) {
+      for (int t = t_begin; t < t_end && alive; t += t_step, ++it) {
         if (G == 2 && (it & 1) != grp) continue;
         const int acc = it & 1;
         const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
-        const TileCoord tc = tile_coord(p, t);
+        const TileCoord tc = tile_coord_for<Cfg>(p, t);
         const int row0 = tc.tm * 128 + q * 32;
         const int row = row0 + lane;
         const int col_base = tc.tn * BN;
@@ -697,11 +851,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     } else {
       float* stg = stg_all + ew * 2048;          // this warp's 8 KB, used as a 32 x 33 pad
       int it = 0;
-      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      for (int t = t_begin; t < t_end; t += t_step, ++it) {
         if (G == 2 && (it & 1) != grp) continue;
         const int acc = it & 1;
         const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
-        const TileCoord tc = tile_coord(p, t);
+        const TileCoord tc = tile_coord_for<Cfg>(p, t);
         if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
           if (*abort_code == 0) *abort_code = 4;
           break;

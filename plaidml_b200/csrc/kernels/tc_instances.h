@@ -1,6 +1,7 @@
 // The instantiations of the tensor-core contraction kernel, as X-macro lists shared by the
 // files that compile them and the dispatcher that selects one.
-// X(element bytes, tile N, operand split, A by im2col, B stored [k][n], output bytes, epilogue groups)
+// X(element bytes, tile N, operand split, A mode (0 tiled, 1 im2col, 2 packed rows), B stored [k][n],
+//   output bytes, epilogue groups)
 #pragma once
 
 #define PMLB_TC_LIST_H16(X, G)      \
@@ -24,6 +25,8 @@
   X(2, 256, 1, true, false, 2, G)
 
 #define PMLB_TC_LIST_MISC(X)        \
+  X(2, 64, 1, 2, false, 2, 1)       \
+  X(2, 64, 1, 2, false, 4, 1)       \
   X(1, 64, 1, false, false, 4, 1)   \
   X(1, 128, 1, false, false, 4, 1)  \
   X(1, 256, 1, false, false, 4, 1)  \

@@ -17,6 +17,17 @@ struct ConvGeom {
   int dil_h, dil_w;
 };
 
+// Packed-row convolution: the activation has been copied to [n][h][wp][cp] with pad_w zero
+// pixels before every row (so output column q reads padded pixels q * stride_w ... + s - 1,
+// which are s * cp consecutive elements), the weights to [k_out][r][64].
+struct WinGeom {
+  int n, h, wp, cp;
+  int r, s;
+  int p, q;
+  int stride_h, stride_w;
+  int pad_h;
+};
+
 struct TcLaunch {
   int elem_bytes = 2;   // 1 (int8), 2 (bf16 / f16), 4 (fp32 pre-split into TF32 hi / lo)
   bool is_f16 = false;  // 2-byte operands are IEEE half instead of bfloat16
@@ -35,6 +46,9 @@ struct TcLaunch {
 
   const ConvGeom* conv = nullptr;  // non-null: A is an NHWC activation fetched by im2col TMA,
                                    // B holds the weights as [k_out][r*s][c]
+
+  const WinGeom* window = nullptr;  // non-null: packed-row convolution (a0 / b0 as described there);
+                                    // m, n, batch = q, k_out, n * p
 
   void* out = nullptr;
   long long ldc = 0;

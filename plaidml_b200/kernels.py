@@ -21,6 +21,7 @@ EPI_BIAS, EPI_RESIDUAL, EPI_RELU, EPI_ROWMAX = 1, 2, 4, 8
 GEMM_TRANSPOSE_B = 1
 GEMM_PLAIN_STORES = 2
 GEMM_PLAIN_RESIDUAL = 4
+CONV_NO_PACKED_ROWS = 1
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = range(5)
 
 MAX_IDX, MAX_RANK, MAX_CONS = 10, 8, 8
@@ -41,7 +42,7 @@ class GemmDesc(C.Structure):
 class ConvDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "in_dtype", "out_dtype", "n", "h", "w", "c", "r", "s", "k", "p", "q", "stride_h", "stride_w",
-        "pad_h", "pad_w", "dil_h", "dil_w", "epilogue", "tile_n")]
+        "pad_h", "pad_w", "dil_h", "dil_w", "epilogue", "tile_n", "flags")]
 
 
 class ReduceDesc(C.Structure):

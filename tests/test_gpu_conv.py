@@ -15,7 +15,7 @@ def out_size(i, f, s, pad_before, pad_after, d=1):
 
 
 def run_conv(seed, n, h, w, c, r, s, k, stride=1, pad=None, out_dtype=K.F32, epilogue=0, tile_n=0, dil=1,
-             same_upper=False):
+             same_upper=False, flags=0):
     g = rng(seed)
     if pad is None:
         pad = (r - 1) // 2
@@ -41,7 +41,7 @@ def run_conv(seed, n, h, w, c, r, s, k, stride=1, pad=None, out_dtype=K.F32, epi
     d.stride_h = d.stride_w = stride
     d.pad_h, d.pad_w = pad_h, pad_w
     d.dil_h = d.dil_w = dil
-    d.epilogue, d.tile_n = epilogue, tile_n
+    d.epilogue, d.tile_n, d.flags = epilogue, tile_n, flags
     plan = K.Plan("conv", d)
     f_dev = dev(f32)
     plan.set_filter(ptr(f_dev), K.F32)
@@ -120,9 +120,52 @@ def test_conv_dilated():
 def test_conv_rejects_odd_channels():
     d = K.ConvDesc()
     d.in_dtype, d.out_dtype = K.BF16, K.F32
-    d.n, d.h, d.w, d.c, d.r, d.s, d.k, d.p, d.q = 1, 8, 8, 3, 3, 3, 8, 8, 8
+    # 36 channels: not whole 16-byte groups, and too many for the packed-row route
+    d.n, d.h, d.w, d.c, d.r, d.s, d.k, d.p, d.q = 1, 8, 8, 36, 3, 3, 8, 8, 8
     d.stride_h = d.stride_w = d.dil_h = d.dil_w = 1
     d.pad_h = d.pad_w = 1
     with pytest.raises(K.KernelError) as e:
         K.Plan("conv", d)
     assert e.value.status == K.ERR_UNSUPPORTED
+
+
+# --- packed-row route (thin inputs: the first layer of image networks) -------------------------
+
+def test_stem_conv7x7_stride2_three_channels():
+    # ResNet's first layer at a small size: 3 input channels (no 16-byte channel groups), 7x7 / 2, pad 3
+    out, ref, plan = run_conv(30, 3, 40, 40, 3, 7, 7, 64, stride=2, pad=3, out_dtype=K.BF16,
+                              epilogue=K.EPI_BIAS | K.EPI_RELU)
+    assert plan.kernel == "tc_conv_rows"
+    check_close(out, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+
+
+def test_stem_conv_matches_im2col_route():
+    # 8 channels take either route; more tiles than SMs so that CTAs slide their row windows and wrap the ring
+    args = dict(n=5, h=70, w=36, c=8, r=7, s=7, k=64, stride=2, pad=3)
+    rows, ref, plan = run_conv(31, **args)
+    assert plan.kernel == "tc_conv_rows"
+    check_close(rows, ref, 1e-4)
+    im2col, _, plan2 = run_conv(31, flags=K.CONV_NO_PACKED_ROWS, **args)
+    assert plan2.kernel == "tc_conv"
+    check_close(rows, im2col, 1e-5)
+
+
+@pytest.mark.parametrize("case", [
+    dict(n=2, h=19, w=300, c=3, r=3, s=3, k=32, stride=1, pad=1),     # q = 300: three column segments per row
+    dict(n=2, h=33, w=45, c=4, r=5, s=5, k=48, stride=2, pad=2),      # q = 23 (not a multiple of 8), k < 64
+    dict(n=1, h=9, w=9, c=1, r=3, s=3, k=8, stride=1, pad=0),         # one channel, no padding, tiny
+    dict(n=2, h=30, w=30, c=16, r=3, s=4, k=64, stride=3, pad=1),     # 16 channels, stride = filter height
+    dict(n=3, h=24, w=24, c=3, r=7, s=7, k=64, stride=2, same_upper=True),
+], ids=["wide", "ragged", "tiny", "stride3", "same_upper"])
+def test_packed_row_geometries(case):
+    out, ref, plan = run_conv(32, **case)
+    assert plan.kernel == "tc_conv_rows"
+    check_close(out, ref, 1e-4)
+
+
+def test_packed_rows_residual_f32_and_bf16():
+    out, ref, plan = run_conv(33, 2, 20, 20, 3, 3, 3, 64, epilogue=K.EPI_RESIDUAL | K.EPI_RELU)
+    assert plan.kernel == "tc_conv_rows"
+    check_close(out, ref, 1e-4)
+    out, ref, _ = run_conv(34, 2, 20, 20, 3, 3, 3, 64, out_dtype=K.BF16, epilogue=K.EPI_BIAS | K.EPI_RESIDUAL)
+    check_close(out, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
