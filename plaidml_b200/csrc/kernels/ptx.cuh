@@ -95,6 +95,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// The same wait made by all 32 lanes of a warp, with one answer for the warp: false if any
+// lane gave up.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
+                                               volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
+}
+
 // ---------------------------------------------------------------- fences
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

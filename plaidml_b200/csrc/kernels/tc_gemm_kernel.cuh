@@ -378,7 +378,8 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* abort_code = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
-  const int warp = threadIdx.x >> 5;
+  // warp number through a shuffle: tells the compiler it is the same in all lanes
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -436,47 +437,56 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int ntrace = 0;
-      if constexpr (Cfg::A_WINDOW) {
-        // Weights of every filter row, once.
+    // The whole warp walks the loops (so that addresses and coordinates stay on the uniform
+    // datapath); one elected lane issues the copies.
+    const bool leader = elect_one();
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int ntrace = 0;
+    if constexpr (Cfg::A_WINDOW) {
+      // Weights of every filter row, once.
+      if (leader) {
         mbar_arrive_expect_tx(wts_bar, static_cast<uint32_t>(p.win_r) * Cfg::B_TILE);
         for (int r = 0; r < p.win_r; ++r) {
           tma_load_3d(win_wts + r * Cfg::B_TILE, &tm.b0, wts_bar, 0, r, 0);
         }
-        // Input rows in the order the output rows need them; `cnt` numbers them, row number
-        // cnt goes to slot cnt % slots.
-        uint32_t cnt = 0;
-        int cur_strip = -1, next_h = 0;
-        const uint32_t nslots = static_cast<uint32_t>(p.win_slots);
-        for (int t = t_begin; t < t_end && ok; ++t) {
-          const WinCoord wc = win_coord(p, t);
-          const int lo = wc.op * p.conv_stride_h + p.conv_lower_h;
-          if (wc.strip != cur_strip) {
-            cur_strip = wc.strip;
-            next_h = lo;
+      }
+      // Input rows in the order the output rows need them; `cnt` numbers them, row number
+      // cnt goes to slot cnt % slots.
+      uint32_t cnt = 0;
+      int cur_strip = -1, next_h = 0;
+      const uint32_t nslots = static_cast<uint32_t>(p.win_slots);
+      uint32_t slot = 0, use = 0;   // cnt % nslots, cnt / nslots
+      for (int t = t_begin; t < t_end && ok; ++t) {
+        const WinCoord wc = win_coord(p, t);
+        const int lo = wc.op * p.conv_stride_h + p.conv_lower_h;
+        if (wc.strip != cur_strip) {
+          cur_strip = wc.strip;
+          next_h = lo;
+        }
+        for (int h = next_h; h < lo + p.win_r; ++h) {
+          if (use > 0 && !mbar_wait_warp(wempty_bar(slot), (use - 1u) & 1u, abort_flag)) {
+            if (leader && *abort_code == 0) *abort_code = 1;
+            ok = false;
+            break;
           }
-          for (int h = next_h; h < lo + p.win_r; ++h) {
-            const uint32_t slot = cnt % nslots;
-            const uint32_t use = cnt / nslots;
-            if (use > 0 && !mbar_wait(wempty_bar(slot), (use - 1u) & 1u, abort_flag)) {
-              if (*abort_code == 0) *abort_code = 1;
-              ok = false;
-              break;
-            }
+          if (leader) {
             trace_event(p, 0, ntrace, t, h);
             mbar_arrive_expect_tx(wfull_bar(slot), static_cast<uint32_t>(p.win_slot_bytes));
             tma_load_4d(win_slots + slot * static_cast<uint32_t>(p.win_slot_bytes), &tm.a0,
                         wfull_bar(slot), 0, wc.tm * 128, h, wc.img);
-            ++cnt;
           }
-          next_h = lo + p.win_r;
+          ++cnt;
+          if (++slot == nslots) {
+            slot = 0;
+            ++use;
+          }
         }
+        next_h = lo + p.win_r;
       }
-      for (int t = t_begin; t < t_end && ok && !Cfg::A_WINDOW; t += t_step) {
+    } else {
+      for (int t = t_begin; t < t_end && ok; t += t_step) {
         const TileCoord tc = tile_coord_for<Cfg>(p, t);
         int pix_w = 0, pix_h = 0, pix_n = 0;
         if constexpr (Cfg::A_IM2COL) {
@@ -489,42 +499,51 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           pix_w = p.conv_lower_w + oq * p.conv_stride_w;
           pix_h = p.conv_lower_h + op * p.conv_stride_h;
         }
+        int tap = 0, cb = 0, fr = 0, fs = 0;   // im2col: k-block = (filter tap, channel block)
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
-            if (*abort_code == 0) *abort_code = 1;
+          if (!mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            if (leader && *abort_code == 0) *abort_code = 1;
             ok = false;
             break;
           }
-          trace_event(p, 0, ntrace, t, kb);
           const uint32_t fb = full_bar(stage);
-          mbar_arrive_expect_tx(fb, Cfg::STAGE);
           const uint32_t s_a = ring + stage * Cfg::STAGE;
           const uint32_t s_b = s_a + NSPLIT * Cfg::A_TILE;
-          if constexpr (Cfg::A_IM2COL) {
-            const int tap = kb / p.conv_cblocks;
-            const int cb = kb - tap * p.conv_cblocks;
-            const int fr = tap / p.conv_s;
-            const int fs = tap - fr * p.conv_s;
-            tma_load_im2col_4d(s_a, &tm.a0, fb, cb * BK, pix_w, pix_h, pix_n,
-                               static_cast<uint16_t>(fs * p.conv_dil_w),
-                               static_cast<uint16_t>(fr * p.conv_dil_h));
-            // weights laid out [k_out][tap][c_in]: map dims (c_in, tap, k_out)
-            tma_load_3d(s_b, &tm.b0, fb, cb * BK, tap, tc.tn * BN);
-          } else {
-            tma_load_3d(s_a, &tm.a0, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
-            if constexpr (NSPLIT == 2) {
-              tma_load_3d(s_a + Cfg::A_TILE, &tm.a1, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
-            }
-            if constexpr (Cfg::B_MN) {
-#pragma unroll
-              for (int ch = 0; ch < Cfg::B_CHUNKS; ++ch) {
-                tma_load_3d(s_b + ch * (BK * 128), &tm.b0, fb, tc.tn * BN + ch * BK, kb * BK,
-                            tc.b * p.b_bz);
-              }
+          if (leader) {
+            trace_event(p, 0, ntrace, t, kb);
+            mbar_arrive_expect_tx(fb, Cfg::STAGE);
+            if constexpr (Cfg::A_IM2COL) {
+              tma_load_im2col_4d(s_a, &tm.a0, fb, cb * BK, pix_w, pix_h, pix_n,
+                                 static_cast<uint16_t>(fs * p.conv_dil_w),
+                                 static_cast<uint16_t>(fr * p.conv_dil_h));
+              // weights laid out [k_out][tap][c_in]: map dims (c_in, tap, k_out)
+              tma_load_3d(s_b, &tm.b0, fb, cb * BK, tap, tc.tn * BN);
             } else {
-              tma_load_3d(s_b, &tm.b0, fb, kb * BK, tc.tn * BN, tc.b * p.b_bz);
+              tma_load_3d(s_a, &tm.a0, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
               if constexpr (NSPLIT == 2) {
-                tma_load_3d(s_b + Cfg::B_TILE, &tm.b1, fb, kb * BK, tc.tn * BN, tc.b * p.b_bz);
+                tma_load_3d(s_a + Cfg::A_TILE, &tm.a1, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
+              }
+              if constexpr (Cfg::B_MN) {
+#pragma unroll
+                for (int ch = 0; ch < Cfg::B_CHUNKS; ++ch) {
+                  tma_load_3d(s_b + ch * (BK * 128), &tm.b0, fb, tc.tn * BN + ch * BK, kb * BK,
+                              tc.b * p.b_bz);
+                }
+              } else {
+                tma_load_3d(s_b, &tm.b0, fb, kb * BK, tc.tn * BN, tc.b * p.b_bz);
+                if constexpr (NSPLIT == 2) {
+                  tma_load_3d(s_b + Cfg::B_TILE, &tm.b1, fb, kb * BK, tc.tn * BN, tc.b * p.b_bz);
+                }
+              }
+            }
+          }
+          if constexpr (Cfg::A_IM2COL) {
+            if (++cb == p.conv_cblocks) {
+              cb = 0;
+              ++tap;
+              if (++fs == p.conv_s) {
+                fs = 0;
+                ++fr;
               }
             }
           }
@@ -537,119 +556,144 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
-      int ntrace = 0;
-      if constexpr (Cfg::A_WINDOW) {
-        const uint32_t nslots = static_cast<uint32_t>(p.win_slots);
-        // Row h of the current strip has number h + delta; `cnt_end` rows have been numbered
-        // so far and the rows below number `waited` are known to have arrived.
-        uint32_t cnt_end = 0, waited = 0;
-        int cur_strip = -1, delta = 0;
-        if (t_begin < t_end && !mbar_wait(wts_bar, 0u, abort_flag)) {
-          if (*abort_code == 0) *abort_code = 3;
-          ok = false;
-        }
-        for (int t = t_begin; t < t_end && ok; ++t) {
-          if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
-            if (*abort_code == 0) *abort_code = 2;
-            break;
-          }
-          const WinCoord wc = win_coord(p, t);
-          const int lo = wc.op * p.conv_stride_h + p.conv_lower_h;
-          if (wc.strip != cur_strip) {
-            cur_strip = wc.strip;
-            delta = static_cast<int>(cnt_end) - lo;
-          }
-          const uint32_t c0 = static_cast<uint32_t>(lo + delta);
-          for (uint32_t c = (waited > c0 ? waited : c0); c < c0 + p.win_r && ok; ++c) {
-            if (!mbar_wait(wfull_bar(c % nslots), (c / nslots) & 1u, abort_flag)) {
-              if (*abort_code == 0) *abort_code = 3;
-              ok = false;
-            }
-          }
-          if (!ok) break;
-          waited = c0 + p.win_r;
-          tc_fence_after_sync();
-          trace_event(p, 1, ntrace, t, 2);
-          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-          for (int r = 0; r < p.win_r; ++r) {
-            const uint32_t s_a =
-                win_slots + ((c0 + r) % nslots) * static_cast<uint32_t>(p.win_slot_bytes);
-            const uint32_t s_b = win_wts + r * Cfg::B_TILE;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint64_t a_d = make_smem_desc_sw128(s_a + j * 32, 16, 1024);
-              const uint64_t b_d = make_smem_desc_sw128(s_b + j * 32, 16, 1024);
-              tc_mma<Cfg::KIND>(d_tmem, a_d, b_d, p.idesc, (r > 0 || j > 0) ? 1u : 0u);
-            }
-          }
-          // Rows the next output row of this CTA does not read go back to the producer.
-          const bool slides = (t + 1 < t_end) && ((t + 1) / p.conv_p == wc.strip);
-          const int nrel = slides ? p.conv_stride_h : p.win_r;
-          for (int r = 0; r < nrel; ++r) tc_commit(wempty_bar((c0 + r) % nslots));
-          cnt_end = c0 + p.win_r;
-          tc_commit(tfull_bar(acc));
-          trace_event(p, 1, ntrace, t, 3);
-          if (++acc == 2) {
-            acc = 0;
-            acc_phase ^= 1u;
-          }
-        }
+    // Same shape: the warp walks the loops and waits, one elected lane issues the MMAs and
+    // the commits (a commit covers the MMAs issued by the thread that executes it).
+    const bool leader = elect_one();
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    int ntrace = 0;
+    // operand descriptors differ from tile to tile only in the start-address field
+    const uint64_t desc_k = make_smem_desc_sw128(0, 16, 1024);           // K-major tile
+    const uint64_t desc_mn = make_smem_desc_sw128(0, BK * 128, 1024);    // MN-major B tile
+    auto desc_at = [](uint64_t base, uint32_t saddr) {
+      return base | static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+    };
+    if constexpr (Cfg::A_WINDOW) {
+      const uint32_t nslots = static_cast<uint32_t>(p.win_slots);
+      // Row h of the current strip has number h + delta; `cnt_end` rows have been numbered
+      // so far and the rows below number `waited` are known to have arrived.
+      uint32_t cnt_end = 0, waited = 0;
+      int cur_strip = -1, delta = 0;
+      if (t_begin < t_end && !mbar_wait_warp(wts_bar, 0u, abort_flag)) {
+        if (leader && *abort_code == 0) *abort_code = 3;
+        ok = false;
       }
-      for (int t = t_begin; t < t_end && ok && !Cfg::A_WINDOW; t += t_step) {
-        trace_event(p, 1, ntrace, t, 0);
-        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
-          if (*abort_code == 0) *abort_code = 2;
+      for (int t = t_begin; t < t_end && ok; ++t) {
+        if (!mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          if (leader && *abort_code == 0) *abort_code = 2;
           break;
         }
-        trace_event(p, 1, ntrace, t, 1);
+        const WinCoord wc = win_coord(p, t);
+        const int lo = wc.op * p.conv_stride_h + p.conv_lower_h;
+        if (wc.strip != cur_strip) {
+          cur_strip = wc.strip;
+          delta = static_cast<int>(cnt_end) - lo;
+        }
+        const uint32_t c0 = static_cast<uint32_t>(lo + delta);
+        for (uint32_t c = (waited > c0 ? waited : c0); c < c0 + p.win_r && ok; ++c) {
+          if (!mbar_wait_warp(wfull_bar(c % nslots), (c / nslots) & 1u, abort_flag)) {
+            if (leader && *abort_code == 0) *abort_code = 3;
+            ok = false;
+          }
+        }
+        if (!ok) break;
+        waited = c0 + p.win_r;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        // Rows the next output row of this CTA does not read go back to the producer.
+        const bool slides = (t + 1 < t_end) && ((t + 1) / p.conv_p == wc.strip);
+        const int nrel = slides ? p.conv_stride_h : p.win_r;
+        uint32_t slot = c0 % nslots;
+        for (int r = 0; r < p.win_r; ++r) {
+          const uint64_t a_d = desc_at(desc_k, win_slots + slot * static_cast<uint32_t>(p.win_slot_bytes));
+          const uint64_t b_d = desc_at(desc_k, win_wts + r * Cfg::B_TILE);
+          if (leader) {
+            if (r == 0) trace_event(p, 1, ntrace, t, 2);
+            tc_mma<Cfg::KIND>(d_tmem, a_d, b_d, p.idesc, r > 0 ? 1u : 0u);
+#pragma unroll
+            for (int j = 1; j < 4; ++j) {
+              tc_mma<Cfg::KIND>(d_tmem, a_d + 2u * j, b_d + 2u * j, p.idesc, 1u);
+            }
+          }
+          if (++slot == nslots) slot = 0;
+        }
+        if (leader) {
+          uint32_t rs = c0 % nslots;
+          for (int r = 0; r < nrel; ++r) {
+            tc_commit(wempty_bar(rs));
+            if (++rs == nslots) rs = 0;
+          }
+          tc_commit(tfull_bar(acc));
+          trace_event(p, 1, ntrace, t, 3);
+        }
+        cnt_end = c0 + p.win_r;
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    } else {
+      for (int t = t_begin; t < t_end && ok; t += t_step) {
+        if (leader) trace_event(p, 1, ntrace, t, 0);
+        if (!mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          if (leader && *abort_code == 0) *abort_code = 2;
+          break;
+        }
+        if (leader) trace_event(p, 1, ntrace, t, 1);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
-            if (*abort_code == 0) *abort_code = 3;
+          if (!mbar_wait_warp(full_bar(stage), phase, abort_flag)) {
+            if (leader && *abort_code == 0) *abort_code = 3;
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          if (kb == 0) trace_event(p, 1, ntrace, t, 2);
           const uint32_t s_a = ring + stage * Cfg::STAGE;
           const uint32_t s_b = s_a + NSPLIT * Cfg::A_TILE;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t accum = (kb > 0 || j > 0) ? 1u : 0u;
-            const uint64_t a_hi = make_smem_desc_sw128(s_a + j * 32, 16, 1024);
-            uint64_t b_hi;
-            if constexpr (Cfg::B_MN) {
-              b_hi = make_smem_desc_sw128(s_b + j * (Cfg::UMMA_K * 128), BK * 128, 1024);
-            } else {
-              b_hi = make_smem_desc_sw128(s_b + j * 32, 16, 1024);
-            }
+          const uint64_t a_hi = desc_at(desc_k, s_a);
+          const uint64_t b_hi = desc_at(Cfg::B_MN ? desc_mn : desc_k, s_b);
+          // descriptor step per 32 bytes of K: 32 bytes along a K-major row, UMMA_K rows of
+          // 128 bytes in an MN-major tile (address field counts 16-byte units)
+          constexpr uint32_t kStepA = 2u;
+          constexpr uint32_t kStepB = Cfg::B_MN ? (Cfg::UMMA_K * 128u) >> 4 : 2u;
+          if (leader) {
+            if (kb == 0) trace_event(p, 1, ntrace, t, 2);
             if constexpr (NSPLIT == 2) {
               // fp32 as three TF32 products; the two cross terms first.
-              const uint64_t a_lo = make_smem_desc_sw128(s_a + Cfg::A_TILE + j * 32, 16, 1024);
-              const uint64_t b_lo = make_smem_desc_sw128(s_b + Cfg::B_TILE + j * 32, 16, 1024);
-              tc_mma<Cfg::KIND>(d_tmem, a_lo, b_hi, p.idesc, accum);
+              const uint64_t a_lo = desc_at(desc_k, s_a + Cfg::A_TILE);
+              const uint64_t b_lo = desc_at(desc_k, s_b + Cfg::B_TILE);
+              tc_mma<Cfg::KIND>(d_tmem, a_lo, b_hi, p.idesc, kb > 0 ? 1u : 0u);
               tc_mma<Cfg::KIND>(d_tmem, a_hi, b_lo, p.idesc, 1u);
               tc_mma<Cfg::KIND>(d_tmem, a_hi, b_hi, p.idesc, 1u);
+#pragma unroll
+              for (int j = 1; j < 4; ++j) {
+                tc_mma<Cfg::KIND>(d_tmem, a_lo + kStepA * j, b_hi + kStepB * j, p.idesc, 1u);
+                tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_lo + kStepB * j, p.idesc, 1u);
+                tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, p.idesc, 1u);
+              }
             } else {
-              tc_mma<Cfg::KIND>(d_tmem, a_hi, b_hi, p.idesc, accum);
+              tc_mma<Cfg::KIND>(d_tmem, a_hi, b_hi, p.idesc, kb > 0 ? 1u : 0u);
+#pragma unroll
+              for (int j = 1; j < 4; ++j) {
+                tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, p.idesc, 1u);
+              }
             }
+            tc_commit(empty_bar(stage));
           }
-          tc_commit(empty_bar(stage));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        tc_commit(tfull_bar(acc));
-        trace_event(p, 1, ntrace, t, 3);
+        if (leader) {
+          tc_commit(tfull_bar(acc));
+          trace_event(p, 1, ntrace, t, 3);
+        }
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;

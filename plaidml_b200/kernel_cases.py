@@ -59,8 +59,7 @@ def main(argv) -> None:
         batch = int(argv[2]) if len(argv) > 2 else 32
         prog, _ = programs.resnet50(batch)
         r = Runner(prog, "cuda.0")
-        img = np.zeros((batch, 224, 224, 8), np.float32)
-        img[..., :3] = g.uniform(0, 1, (batch, 224, 224, 3))
+        img = g.uniform(0, 1, (batch, 224, 224, 3)).astype(np.float32)
         ins = [f32_to_bf16_bits(img)]
         passes = 1
     else:

@@ -67,8 +67,7 @@ def resnet50_weights(seed: int = 1234 + 4):
         w = g.standard_normal((r, s, cin, cout)).astype(np.float32) * np.sqrt(2.0 / (r * s * cin))
         weights[name] = (f32_to_bf16_bits(w), np.zeros(cout, dtype=np.float32))
 
-    conv("conv1", 7, 7, 8, 64)   # input channels padded 3 -> 8 (zero weights on the padding)
-    weights["conv1"][0][:, :, 3:, :] = 0
+    conv("conv1", 7, 7, 3, 64)
     cin = 64
     for si, (blocks, mid, out, _) in enumerate(RESNET_STAGES):
         for b in range(blocks):
@@ -87,10 +86,9 @@ def resnet50_weights(seed: int = 1234 + 4):
 def resnet50(batch: int, weights=None, with_softmax=False):
     """ResNet-50 v1.5 inference, NHWC, bf16 activations / weights with f32 accumulation.
 
-    The image input is [batch, 224, 224, 8]: RGB in channels 0..2, channels 3..7 zero (the
-    first convolution's weights are zero there), which gives the activation rows the 16-byte
-    alignment the tensor-core path needs.  Returns (program, weights); output 0 is the
-    [batch, 1000] float32 logits."""
+    The image input is [batch, 224, 224, 3]; the first convolution takes the packed-row route of
+    the kernel library, which needs no channel alignment.  Returns (program, weights); output 0
+    is the [batch, 1000] float32 logits."""
     if weights is None:
         weights = resnet50_weights()
     f32, bf16 = DType.FLOAT32, DType.BFLOAT16
@@ -110,7 +108,7 @@ def resnet50(batch: int, weights=None, with_softmax=False):
             y = op.relu(y)
         return cast(y, bf16)
 
-    I = Placeholder(bf16, [batch, 224, 224, 8], name="image")
+    I = Placeholder(bf16, [batch, 224, 224, 3], name="image")
     x = conv_block(I, "conv1", stride=2, pad=3)
     x = op.pool(x, op.PoolMode.MAX, [3, 3], [2, 2], op.AutoPadMode.EXPLICIT, [1, 1, 1, 1], op.TensorLayout.NXC, name="pool1")
     for si, (blocks, mid, out, stride) in enumerate(RESNET_STAGES):

@@ -52,12 +52,12 @@ def test_resnet50_logits_match_oracle():
     lines = plan.strip().splitlines()
     kinds = [ln.split()[0] for ln in lines]
     # 53 convolutions + the FC contraction on tensor cores; pooling and the average on their kernels
-    assert kinds.count("tc_conv") + kinds.count("tc_gemm") == 54, plan
+    assert kinds.count("tc_conv_rows") == 1, plan          # the 7x7 / 2 first layer on 3 channels
+    assert kinds.count("tc_conv_rows") + kinds.count("tc_conv") + kinds.count("tc_gemm") == 54, plan
     assert "nhwc_pool" in kinds and "strided_reduce" in kinds
     assert "generic_contract" not in kinds, plan
     g = rng(1234 + 4)
-    img = np.zeros((batch, 224, 224, 8), dtype=np.float32)
-    img[..., :3] = g.uniform(0, 1, size=(batch, 224, 224, 3))
+    img = g.uniform(0, 1, size=(batch, 224, 224, 3)).astype(np.float32)
     x_bits = f32_to_bf16_bits(img)
     logits = runner.run([x_bits])[0]
     ref = oracle_resnet50(bf16_bits_to_f32(x_bits), weights)
