@@ -64,11 +64,7 @@ struct TcCfg {
   static constexpr int STAGES_RAW = RING_BUDGET / STAGE;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE + STG_BYTES + BAR_BYTES;
-  // TMEM accumulators: two (the epilogue of one tile overlaps the main loop of the next); the
-  // packed-row mode streams image rows through the MMA and keeps every output row a row
-  // still contributes to open, so it takes all 512 columns.
-  static constexpr int NACC = A_MODE_ == kAWindow ? 512 / BN_ : 2;
-  static constexpr int TMEM_COLS = NACC * BN;         // 128, 256 or 512
+  static constexpr int TMEM_COLS = 2 * BN;            // 128, 256 or 512
   static constexpr int KIND = EB == 2 ? kMmaF16 : (EB == 4 ? kMmaTf32 : kMmaI8);
   static constexpr int B_CHUNKS = BN / BK;            // MN-major: chunks of 128 bytes of N
   static_assert(STAGES >= 2, "ring too small");
@@ -370,15 +366,15 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   // barrier index helpers (8 bytes each)
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };             // up to 8
-  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 8 + a); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
   // two residual-arrival barriers per epilogue warp (at most 8 warps)
-  auto res_bar = [&](int ew, uint32_t i) { return bar0 + 8u * (2 * STAGES + 16 + 2 * ew + i); };
+  auto res_bar = [&](int ew, uint32_t i) { return bar0 + 8u * (2 * STAGES + 4 + 2 * ew + i); };
   // packed-row mode: arrival / release barriers of up to 16 row slots, one for the weights
-  auto wfull_bar = [&](uint32_t i) { return bar0 + 8u * (2 * STAGES + 32 + i); };
-  auto wempty_bar = [&](uint32_t i) { return bar0 + 8u * (2 * STAGES + 48 + i); };
-  const uint32_t wts_bar = bar0 + 8u * (2 * STAGES + 64);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 65);
+  auto wfull_bar = [&](uint32_t i) { return bar0 + 8u * (2 * STAGES + 20 + i); };
+  auto wempty_bar = [&](uint32_t i) { return bar0 + 8u * (2 * STAGES + 36 + i); };
+  const uint32_t wts_bar = bar0 + 8u * (2 * STAGES + 52);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 53);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* abort_code = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
@@ -391,7 +387,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (int a = 0; a < Cfg::NACC; ++a) {
+    for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 4);
     }
@@ -576,73 +572,68 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       return base | static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
     };
     if constexpr (Cfg::A_WINDOW) {
-      // Image rows stream through in the order the producer fetches them.  Row h feeds every
-      // output row whose window covers it (filter row r = h - first row of that window), each
-      // into its own accumulator; an output row is complete after its last filter row.
       const uint32_t nslots = static_cast<uint32_t>(p.win_slots);
-      const uint32_t slot_bytes = static_cast<uint32_t>(p.win_slot_bytes);
-      const int sh = p.conv_stride_h, R = p.win_r, P = p.conv_p;
-      uint32_t slot = 0, sphase = 0;
+      // Row h of the current strip has number h + delta; `cnt_end` rows have been numbered
+      // so far and the rows below number `waited` are known to have arrived.
+      uint32_t cnt_end = 0, waited = 0;
+      int cur_strip = -1, delta = 0;
       if (t_begin < t_end && !mbar_wait_warp(wts_bar, 0u, abort_flag)) {
         if (leader && *abort_code == 0) *abort_code = 3;
         ok = false;
       }
-      int t = t_begin;
-      while (t < t_end && ok) {
-        // the output rows [pa, pb) of one strip that this CTA owns
+      for (int t = t_begin; t < t_end && ok; ++t) {
+        if (!mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          if (leader && *abort_code == 0) *abort_code = 2;
+          break;
+        }
         const WinCoord wc = win_coord(p, t);
-        const int pa = wc.op;
-        const int pb = min(P, pa + (t_end - t));
-        const int it0 = t - t_begin;                          // local tile number of row pa
-        const int x_end = (pb - 1) * sh + R;                  // rows as x = h - lower_h
-        for (int x = pa * sh; x < x_end && ok; ++x) {
-          if (!mbar_wait_warp(wfull_bar(slot), sphase, abort_flag)) {
+        const int lo = wc.op * p.conv_stride_h + p.conv_lower_h;
+        if (wc.strip != cur_strip) {
+          cur_strip = wc.strip;
+          delta = static_cast<int>(cnt_end) - lo;
+        }
+        const uint32_t c0 = static_cast<uint32_t>(lo + delta);
+        for (uint32_t c = (waited > c0 ? waited : c0); c < c0 + p.win_r && ok; ++c) {
+          if (!mbar_wait_warp(wfull_bar(c % nslots), (c / nslots) & 1u, abort_flag)) {
             if (leader && *abort_code == 0) *abort_code = 3;
             ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint64_t a_d = desc_at(desc_k, win_slots + slot * slot_bytes);
-          int p_lo = x - R + sh;                              // ceil((x - R + 1) / sh)
-          p_lo = p_lo > 0 ? p_lo / sh : 0;
-          if (p_lo < pa) p_lo = pa;
-          int p_hi = x / sh;
-          if (p_hi > pb - 1) p_hi = pb - 1;
-          for (int op = p_lo; op <= p_hi && ok; ++op) {
-            const int r = x - op * sh;
-            const int it = it0 + (op - pa);
-            const int acc = it % Cfg::NACC;
-            if (r == 0) {
-              const uint32_t ph = static_cast<uint32_t>(it / Cfg::NACC) & 1u;
-              if (!mbar_wait_warp(tempty_bar(acc), ph ^ 1u, abort_flag)) {
-                if (leader && *abort_code == 0) *abort_code = 2;
-                ok = false;
-                break;
-              }
-              tc_fence_after_sync();
-            }
-            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-            const uint64_t b_d = desc_at(desc_k, win_wts + r * Cfg::B_TILE);
-            if (leader) {
-              if (r == 0) trace_event(p, 1, ntrace, t + (op - pa), 2);
-              tc_mma<Cfg::KIND>(d_tmem, a_d, b_d, p.idesc, r > 0 ? 1u : 0u);
-#pragma unroll
-              for (int j = 1; j < 4; ++j) {
-                tc_mma<Cfg::KIND>(d_tmem, a_d + 2u * j, b_d + 2u * j, p.idesc, 1u);
-              }
-              if (r == R - 1) {
-                tc_commit(tfull_bar(acc));
-                trace_event(p, 1, ntrace, t + (op - pa), 3);
-              }
-            }
-          }
-          if (leader) tc_commit(wempty_bar(slot));            // the row is done with
-          if (++slot == nslots) {
-            slot = 0;
-            sphase ^= 1u;
           }
         }
-        t += pb - pa;
+        if (!ok) break;
+        waited = c0 + p.win_r;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        // Rows the next output row of this CTA does not read go back to the producer.
+        const bool slides = (t + 1 < t_end) && ((t + 1) / p.conv_p == wc.strip);
+        const int nrel = slides ? p.conv_stride_h : p.win_r;
+        uint32_t slot = c0 % nslots;
+        for (int r = 0; r < p.win_r; ++r) {
+          const uint64_t a_d = desc_at(desc_k, win_slots + slot * static_cast<uint32_t>(p.win_slot_bytes));
+          const uint64_t b_d = desc_at(desc_k, win_wts + r * Cfg::B_TILE);
+          if (leader) {
+            if (r == 0) trace_event(p, 1, ntrace, t, 2);
+            tc_mma<Cfg::KIND>(d_tmem, a_d, b_d, p.idesc, r > 0 ? 1u : 0u);
+#pragma unroll
+            for (int j = 1; j < 4; ++j) {
+              tc_mma<Cfg::KIND>(d_tmem, a_d + 2u * j, b_d + 2u * j, p.idesc, 1u);
+            }
+          }
+          if (++slot == nslots) slot = 0;
+        }
+        if (leader) {
+          uint32_t rs = c0 % nslots;
+          for (int r = 0; r < nrel; ++r) {
+            tc_commit(wempty_bar(rs));
+            if (++rs == nslots) rs = 0;
+          }
+          tc_commit(tfull_bar(acc));
+          trace_event(p, 1, ntrace, t, 3);
+        }
+        cnt_end = c0 + p.win_r;
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
       }
     } else {
       for (int t = t_begin; t < t_end && ok; t += t_step) {
@@ -715,8 +706,8 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     const int ew = warp - 2;                    // epilogue warp number
     const int grp = ew >> 2;                    // epilogue group (accumulator owner when two)
     constexpr int G = Cfg::EPI_GROUPS;
-    // Local tile number `it` selects the accumulator (it % NACC) and its barrier phase
-    // ((it / NACC) & 1); with two groups, group g takes the tiles with (it & 1) == g.
+    // Local tile number `it` selects the accumulator (it & 1) and its barrier phase
+    // ((it >> 1) & 1); with two groups, group g takes the tiles with (it & 1) == g.
     if (p.fast_epi) {
       constexpr int CW = Cfg::CW;
       constexpr int OB = Cfg::OUT_BYTES;
@@ -734,8 +725,8 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       const bool tracer = (q == 2) && lane == 0;   // first warp of each group (warps 2 and 6)
       for (int t = t_begin; t < t_end && alive; t += t_step, ++it) {
         if (G == 2 && (it & 1) != grp) continue;
-        const int acc = it % Cfg::NACC;
-        const uint32_t acc_phase = static_cast<uint32_t>(it / Cfg::NACC) & 1u;
+        const int acc = it & 1;
+        const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
         const TileCoord tc = tile_coord_for<Cfg>(p, t);
         const int row0 = tc.tm * 128 + q * 32;
         const int row = row0 + lane;
@@ -906,8 +897,8 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       int it = 0;
       for (int t = t_begin; t < t_end; t += t_step, ++it) {
         if (G == 2 && (it & 1) != grp) continue;
-        const int acc = it % Cfg::NACC;
-        const uint32_t acc_phase = static_cast<uint32_t>(it / Cfg::NACC) & 1u;
+        const int acc = it & 1;
+        const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
         const TileCoord tc = tile_coord_for<Cfg>(p, t);
         if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
           if (*abort_code == 0) *abort_code = 4;
