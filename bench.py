@@ -36,7 +36,7 @@ M_PER_GPU, N_DIM, K_DIM = 4096, 4096, 4096
 WORKLOAD = "cfg2: int8 x int8 -> int32 Tile GEMM, N=K=4096, M=4096 rows per GPU (rows of M sharded)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one tc_contract launch of this workload, from
 # the ncu capture summarised in profiles/tc_gemm_i8_4096.md
-NCU_TRAFFIC_BYTES = 52.58e6
+NCU_TRAFFIC_BYTES = 52.02e6
 
 
 emit = None  # set by main(): writes the result line
@@ -201,6 +201,13 @@ def extras(device: str, iters: int) -> dict:
     ms = r.executable.time_steps(iters, True)
     out["cfg5_qk_gemm_rowmax"] = {"ms": ms, "gemm_tflops_equiv": 2.0 * 1024 * 512 * 512 * 64 / ms / 1e9,
                                   "hbm_gbs": (1.208e9 + 1.076e9) / ms / 1e6, "plan": r.executable.describe().strip()}
+    # cfg4: ResNet-50 v1.5 inference, batch 256, 224x224x3 (device-resident kernel sequence)
+    prog, _ = progs.resnet50(256)
+    r = Runner(prog, device)
+    r.run([f32_to_bf16_bits(g.uniform(0, 1, (256, 224, 224, 3)).astype(np.float32))])
+    ms = r.executable.time_steps(max(3, iters // 2), True)
+    out["cfg4_resnet50_b256"] = {"ms": ms, "images_per_s": 256 / ms * 1e3,
+                                 "tflops": 256 * progs.RESNET50_GFLOP_PER_IMAGE / ms, "kernels": r.executable.launch_count}
     return out
 
 
