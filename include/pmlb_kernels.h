@@ -132,6 +132,10 @@ typedef struct {
 /* Keep the staged epilogue but read the residual with ordinary loads instead of fetching its
  * rows by TMA ahead of each chunk (for testing that both routes round identically). */
 #define PMLB_GEMM_PLAIN_RESIDUAL 4
+/* Large 8/16-bit GEMMs run two CTAs per 256 x 256 tile (a cluster of two with paired MMAs) when
+ * that fills the device; these flags force the choice for 256-wide tiles (for testing). */
+#define PMLB_GEMM_CTA_PAIRS 8
+#define PMLB_GEMM_NO_CTA_PAIRS 16
 
 pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* desc, pmlb_plan** plan);
 

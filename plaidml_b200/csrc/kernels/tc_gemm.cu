@@ -25,6 +25,12 @@ PMLB_TC_LIST_H16(PMLB_TC_EXTERN, 1)
 PMLB_TC_LIST_H16(PMLB_TC_EXTERN, 2)
 PMLB_TC_LIST_MISC(PMLB_TC_EXTERN)
 #undef PMLB_TC_EXTERN
+#define PMLB_TC_EXTERN(EB, BN, NS, IM, MN, OB, G)                                              \
+  extern template cudaError_t launch_cfg<TcCfg<EB, BN, NS, IM, MN, OB, G, 2>>(                  \
+      const TcMaps&, const TcParams&, int, cudaStream_t);
+PMLB_TC_LIST_PAIR(PMLB_TC_EXTERN)
+#undef PMLB_TC_EXTERN
+extern template int max_resident_pairs<TcCfg<2, 256, 1, 0, false, 2, 1, 2>>();
 
 namespace {
 
@@ -94,7 +100,7 @@ bool encode3d(CUtensorMap* map, CUtensorMapDataType dt, int eb, const void* base
   return true;
 }
 
-uint32_t make_idesc(int eb, bool is_f16, bool b_mn, int bn) {
+uint32_t make_idesc(int eb, bool is_f16, bool b_mn, int bn, int bm = 128) {
   // bits: [4,6) D format, [7,10) A format, [10,13) B format, 15 A major, 16 B major,
   //       [17,23) N >> 3, [24,29) M >> 4
   uint32_t cfmt, abfmt;
@@ -114,7 +120,7 @@ uint32_t make_idesc(int eb, bool is_f16, bool b_mn, int bn) {
   d |= abfmt << 10;
   d |= (b_mn ? 1u : 0u) << 16;
   d |= static_cast<uint32_t>(bn >> 3) << 17;
-  d |= static_cast<uint32_t>(128 >> 4) << 24;
+  d |= static_cast<uint32_t>(bm >> 4) << 24;
   return d;
 }
 
@@ -197,13 +203,38 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     return 1;
   }
 
+  // Two epilogue groups when the main loop of a tile is short next to its epilogue.
+  const int num_kb_plain = (L.k + bk - 1) / bk;
+  int groups = (L.conv ? 0 : num_kb_plain) <= 24 ? 2 : 1;
+  // CTA pairs: plain GEMMs whose 256-wide tiles have long main loops and fill the machine.
+  bool pair = false;
+  const bool pair_possible = !L.conv && !L.window && L.nsplit == 1 && bn == 256;
+  if (pair_possible && num_kb_plain > 24 && L.m >= 256) {
+    const long long pair_tiles =
+        static_cast<long long>(L.batch) * ((L.m + 255) / 256) * ((L.n + 255) / 256);
+    pair = pair_tiles * 2 >= num_sms;
+  }
+  if (L.pair_override == 0) pair = false;
+  if (L.pair_override == 1) pair = pair_possible;
+  if (const char* env = std::getenv("PMLB_TC_PAIR")) {
+    if (env[0] == '0') pair = false;
+  }
+  static int resident_pairs[64] = {0};
+  if (pair) {
+    if (dev >= 0 && dev < 64 && resident_pairs[dev] == 0) {
+      const int n = max_resident_pairs<TcCfg<2, 256, 1, 0, false, 2, 1, 2>>();
+      resident_pairs[dev] = n > 0 ? n : -1;
+    }
+    if (dev < 0 || dev >= 64 || resident_pairs[dev] <= 0) pair = false;
+  }
+
   TcParams p;
   std::memset(&p, 0, sizeof(p));
   p.m = L.m;
   p.n = L.n;
   p.k = L.k;
   p.batch = L.batch;
-  p.tiles_m = (L.m + 127) / 128;
+  p.tiles_m = pair ? (L.m + 255) / 256 : (L.m + 127) / 128;
   p.tiles_n = (L.n + bn - 1) / bn;
   p.group_m = 16;
   p.a_bz = L.a_batch_stride != 0 ? 1 : 0;
@@ -220,7 +251,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   p.rowmax = L.rowmax;
   p.status = L.status;
   p.trace = L.trace;
-  p.idesc = make_idesc(eb, L.is_f16, L.b_mn, bn);
+  p.idesc = make_idesc(eb, L.is_f16, L.b_mn, bn, pair ? 256 : 128);
 
   const CUtensorMapDataType dt = map_dtype(eb, L.is_f16);
   TcMaps maps;
@@ -372,7 +403,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
       const uint64_t b_bs = p.b_bz ? static_cast<uint64_t>(L.b_batch_stride) * eb
                                    : static_cast<uint64_t>(L.ldb) * eb * L.n;
       if (!encode3d(&tb0, dt, eb, L.b0, L.k, L.n, p.b_bz ? L.batch : 1,
-                    static_cast<uint64_t>(L.ldb) * eb, b_bs, bk, bn, 1, err)) {
+                    static_cast<uint64_t>(L.ldb) * eb, b_bs, bk, pair ? bn / 2 : bn, 1, err)) {
         return 1;
       }
       tb1 = tb0;
@@ -428,15 +459,19 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   }
   int grid = static_cast<int>(std::min<long long>(total, num_sms));
   if (L.grid_override > 0) grid = std::min<long long>(total, L.grid_override);
+  if (pair) {
+    long long pairs = std::min<long long>(total, resident_pairs[dev]);
+    if (L.grid_override > 0) pairs = std::min<long long>(pairs, std::max(1, L.grid_override / 2));
+    grid = static_cast<int>(2 * pairs);
+  }
 
   cudaError_t ce = cudaErrorInvalidValue;
-  // Two epilogue groups when the main loop of a tile is short next to its epilogue.
-  int groups = p.num_kb <= 24 ? 2 : 1;
+  if (L.conv) groups = p.num_kb <= 24 ? 2 : 1;
   if (L.epi_groups_override == 1 || L.epi_groups_override == 2) groups = L.epi_groups_override;
   if (const char* env = std::getenv("PMLB_TC_EPI_GROUPS")) {
     if (env[0] == '1' || env[0] == '2') groups = env[0] - '0';
   }
-  if (L.window) groups = 1;  // the row ring leaves room for one group's staging buffers only
+  if (L.window || pair) groups = 1;  // (the row ring leaves room for one group's staging buffers only)
   const int a_mode = L.window ? kAWindow : (L.conv ? kAIm2col : kATiled);
   bool launched = false;
 #define PMLB_TC_CASE(EB, BN, NS, IM, MN, OB, G)                                                 \
@@ -444,6 +479,17 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
       L.b_mn == MN && ob_tmpl == OB && groups == G) {                                           \
     ce = launch_cfg<TcCfg<EB, BN, NS, IM, MN, OB, G>>(maps, p, grid, stream);                   \
     launched = true;                                                                            \
+  }
+#define PMLB_TC_CASE_PAIR(EB, BN, NS, IM, MN, OB, G)                                            \
+  if (!launched && pair && eb == EB && bn == BN && L.b_mn == MN && ob_tmpl == OB) {             \
+    ce = launch_cfg<TcCfg<EB, BN, NS, IM, MN, OB, G, 2>>(maps, p, grid, stream);                \
+    launched = true;                                                                            \
+  }
+  PMLB_TC_LIST_PAIR(PMLB_TC_CASE_PAIR)
+#undef PMLB_TC_CASE_PAIR
+  if (pair && !launched) {
+    *err = "no CTA-pair instance for this configuration";
+    return 3;
   }
   for (int attempt = 0; attempt < 2 && !launched; ++attempt) {
     PMLB_TC_LIST_H16(PMLB_TC_CASE, 1)

@@ -36,8 +36,12 @@ enum : int {
 };
 
 template <int EB, int BN_, int NSPLIT_, int A_MODE_, bool B_MN_, int OUT_BYTES_ = 4,
-          int EPI_GROUPS_ = 1>
+          int EPI_GROUPS_ = 1, int CTAS_ = 1>
 struct TcCfg {
+  // 2: two CTAs (a cluster of two, on neighbouring SMs) work on one 256 x BN tile with
+  // cta_group::2 MMAs: each CTA holds 128 rows of A and of the accumulator and half of B's
+  // N rows, so that a B tile crosses from L2 to shared memory once per 256 output rows.
+  static constexpr int CTAS = CTAS_;
   // 1: four epilogue warps drain both TMEM accumulators in turn (TMEM loads software-
   //    pipelined); 2: eight warps, one group of four per accumulator, for shapes whose main
   //    loop per tile is shorter than the epilogue (small K).
@@ -55,7 +59,7 @@ struct TcCfg {
   static constexpr int BK = 128 / EB;       // elements of K per stage
   static constexpr int UMMA_K = 32 / EB;    // elements of K per tcgen05.mma
   static constexpr int A_TILE = BM * 128;   // bytes
-  static constexpr int B_TILE = BN * 128;   // bytes
+  static constexpr int B_TILE = (BN / CTAS_) * 128;   // bytes held by one CTA
   static constexpr int STAGE = NSPLIT * (A_TILE + B_TILE);
   static constexpr int STG_BYTES = EPI_GROUPS_ * 4 * 2 * 4096;  // per epilogue warp: two 32-row x 128-byte buffers
   static constexpr int BAR_BYTES = 1024;
@@ -66,9 +70,11 @@ struct TcCfg {
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE + STG_BYTES + BAR_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;            // 128, 256 or 512
   static constexpr int KIND = EB == 2 ? kMmaF16 : (EB == 4 ? kMmaTf32 : kMmaI8);
-  static constexpr int B_CHUNKS = BN / BK;            // MN-major: chunks of 128 bytes of N
+  static constexpr int B_CHUNKS = (BN / CTAS_) / BK;  // MN-major: chunks of 128 bytes of N per CTA
   static_assert(STAGES >= 2, "ring too small");
-  static_assert(!B_MN || (BN % BK == 0), "MN-major B needs BN to be whole chunks");
+  static_assert(!B_MN || ((BN / CTAS_) % BK == 0), "MN-major B needs whole chunks per CTA");
+  static_assert(CTAS_ == 1 || (CTAS_ == 2 && A_MODE_ == kATiled && NSPLIT_ == 1),
+                "CTA pairs serve plain 8/16-bit GEMMs");
 };
 
 __device__ __forceinline__ float atomic_max_float(float* addr, float v) {
@@ -183,6 +189,14 @@ __device__ __forceinline__ TileCoord tile_coord_for(const TcParams& p, int t) {
   } else {
     return tile_coord(p, t);
   }
+}
+
+// CTA pairs: the pair tile's coordinate with tm turned into this CTA's 128-row tile number.
+template <class Cfg>
+__device__ __forceinline__ TileCoord tile_coord_cta(const TcParams& p, int t, uint32_t cta_rank) {
+  TileCoord c = tile_coord_for<Cfg>(p, t);
+  if constexpr (Cfg::CTAS == 2) c.tm = 2 * c.tm + static_cast<int>(cta_rank);
+  return c;
 }
 
 // Epilogue arithmetic on one staged chunk: CW accumulator columns of this thread's row.
@@ -381,6 +395,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   // warp number through a shuffle: tells the compiler it is the same in all lanes
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
+  constexpr int CTAS = Cfg::CTAS;
+  // CTA pair: rank 0 issues the pair's MMAs and owns the barriers both producers and both
+  // epilogues report to (`full` and `tempty`); `empty` and `tfull` exist in both CTAs and are
+  // reached by multicast commits.
+  const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0u;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -389,7 +408,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), 4 * CTAS);
     }
     for (int w = 0; w < 8; ++w) {
       mbar_init(res_bar(w, 0), 1);
@@ -415,17 +434,28 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     if (p.res_tma) tma_prefetch_desc(&tm.r);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (CTAS == 2) {
+      tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (CTAS == 2) {
+    cluster_sync_all();   // the other CTA's barriers must exist before anything is sent to them
+  } else {
+    __syncthreads();
+  }
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // (pairs: p.tiles_m counts 256-row pair tiles; CTA `rank` takes rows 128 * rank .. of each)
   const int total_tiles = p.batch * p.tiles_m * p.tiles_n;
-  // Tiles this CTA walks: every gridDim.x-th one, or (packed-row mode) a contiguous range.
-  int t_begin = blockIdx.x, t_end = total_tiles, t_step = gridDim.x;
+  // Tiles this CTA walks: every gridDim.x-th one (pairs: every cluster-count-th one), or
+  // (packed-row mode) a contiguous range.
+  int t_begin = blockIdx.x / CTAS, t_end = total_tiles, t_step = gridDim.x / CTAS;
   if constexpr (Cfg::A_WINDOW) {
     t_begin = static_cast<int>(static_cast<long long>(total_tiles) * blockIdx.x / gridDim.x);
     t_end = static_cast<int>(static_cast<long long>(total_tiles) * (blockIdx.x + 1) / gridDim.x);
@@ -487,7 +517,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       }
     } else {
       for (int t = t_begin; t < t_end && ok; t += t_step) {
-        const TileCoord tc = tile_coord_for<Cfg>(p, t);
+        const TileCoord tc = tile_coord_cta<Cfg>(p, t, cta_rank);
         int pix_w = 0, pix_h = 0, pix_n = 0;
         if constexpr (Cfg::A_IM2COL) {
           const int m0 = tc.tm * 128;
@@ -511,13 +541,27 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           const uint32_t s_b = s_a + NSPLIT * Cfg::A_TILE;
           if (leader) {
             trace_event(p, 0, ntrace, t, kb);
-            mbar_arrive_expect_tx(fb, Cfg::STAGE);
+            if (CTAS == 1 || cta_rank == 0) mbar_arrive_expect_tx(fb, CTAS * Cfg::STAGE);
             if constexpr (Cfg::A_IM2COL) {
               tma_load_im2col_4d(s_a, &tm.a0, fb, cb * BK, pix_w, pix_h, pix_n,
                                  static_cast<uint16_t>(fs * p.conv_dil_w),
                                  static_cast<uint16_t>(fr * p.conv_dil_h));
               // weights laid out [k_out][tap][c_in]: map dims (c_in, tap, k_out)
               tma_load_3d(s_b, &tm.b0, fb, cb * BK, tap, tc.tn * BN);
+            } else if constexpr (CTAS == 2) {
+              // both CTAs count their bytes on the first CTA's barrier, which expects both
+              const uint32_t fb0 = mapa_rank(fb, 0);
+              const int n0 = tc.tn * BN + static_cast<int>(cta_rank) * (BN / 2);
+              tma_load_3d_pair(s_a, &tm.a0, fb0, kb * BK, tc.tm * 128, tc.b * p.a_bz);
+              if constexpr (Cfg::B_MN) {
+#pragma unroll
+                for (int ch = 0; ch < Cfg::B_CHUNKS; ++ch) {
+                  tma_load_3d_pair(s_b + ch * (BK * 128), &tm.b0, fb0, n0 + ch * BK, kb * BK,
+                                   tc.b * p.b_bz);
+                }
+              } else {
+                tma_load_3d_pair(s_b, &tm.b0, fb0, kb * BK, n0, tc.b * p.b_bz);
+              }
             } else {
               tma_load_3d(s_a, &tm.a0, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
               if constexpr (NSPLIT == 2) {
@@ -635,7 +679,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           acc_phase ^= 1u;
         }
       }
-    } else {
+    } else if (CTAS == 1 || cta_rank == 0) {
       for (int t = t_begin; t < t_end && ok; t += t_step) {
         if (leader) trace_event(p, 1, ntrace, t, 0);
         if (!mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
@@ -675,6 +719,12 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
                 tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_lo + kStepB * j, p.idesc, 1u);
                 tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, p.idesc, 1u);
               }
+            } else if constexpr (CTAS == 2) {
+              tc_mma_pair<Cfg::KIND>(d_tmem, a_hi, b_hi, p.idesc, kb > 0 ? 1u : 0u);
+#pragma unroll
+              for (int j = 1; j < 4; ++j) {
+                tc_mma_pair<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, p.idesc, 1u);
+              }
             } else {
               tc_mma<Cfg::KIND>(d_tmem, a_hi, b_hi, p.idesc, kb > 0 ? 1u : 0u);
 #pragma unroll
@@ -682,7 +732,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
                 tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, p.idesc, 1u);
               }
             }
-            tc_commit(empty_bar(stage));
+            if constexpr (CTAS == 2) {
+              tc_commit_pair(empty_bar(stage), 3);   // the stage is free in both CTAs
+            } else {
+              tc_commit(empty_bar(stage));
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -691,7 +745,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         }
         if (!ok) break;
         if (leader) {
-          tc_commit(tfull_bar(acc));
+          if constexpr (CTAS == 2) {
+            tc_commit_pair(tfull_bar(acc), 3);       // both CTAs' epilogues may read their half
+          } else {
+            tc_commit(tfull_bar(acc));
+          }
           trace_event(p, 1, ntrace, t, 3);
         }
         if (++acc == 2) {
@@ -727,7 +785,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         if (G == 2 && (it & 1) != grp) continue;
         const int acc = it & 1;
         const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
-        const TileCoord tc = tile_coord_for<Cfg>(p, t);
+        const TileCoord tc = tile_coord_cta<Cfg>(p, t, cta_rank);
         const int row0 = tc.tm * 128 + q * 32;
         const int row = row0 + lane;
         const int col_base = tc.tn * BN;
@@ -780,7 +838,13 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         auto release_acc = [&]() {
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(tempty_bar(acc));
+          if (lane == 0) {
+            if constexpr (CTAS == 2) {
+              mbar_arrive_cluster(mapa_rank(tempty_bar(acc), 0));
+            } else {
+              mbar_arrive(tempty_bar(acc));
+            }
+          }
         };
         auto process = [&](uint32_t(&v)[CW], int ch) {
           const int col0 = col_base + ch * CW;
@@ -899,7 +963,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         if (G == 2 && (it & 1) != grp) continue;
         const int acc = it & 1;
         const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
-        const TileCoord tc = tile_coord_for<Cfg>(p, t);
+        const TileCoord tc = tile_coord_cta<Cfg>(p, t, cta_rank);
         if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
           if (*abort_code == 0) *abort_code = 4;
           break;
@@ -923,7 +987,13 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
             // accumulator fully read: hand it back before finishing the stores
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (lane == 0) {
+            if constexpr (CTAS == 2) {
+              mbar_arrive_cluster(mapa_rank(tempty_bar(acc), 0));
+            } else {
+              mbar_arrive(tempty_bar(acc));
+            }
+          }
           }
           if (col0 >= p.n) continue;   // warp-uniform
           if ((p.epi_flags & kEpiRowMax) && p.out == nullptr) {
@@ -972,7 +1042,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
 
   // ---------------------------------------------------------------- teardown
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (CTAS == 2) {
+    cluster_sync_all();   // neither CTA's shared memory or barriers are touched by the other from here on
+  } else {
+    __syncthreads();
+  }
   if (*abort_flag != 0) {
     // A wait gave up.  Report, then give copies and MMAs still in flight a bounded
     // time to land before TMEM and shared memory are released.
@@ -986,10 +1060,15 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     }
     __syncthreads();
   }
+  if constexpr (CTAS == 2) cluster_sync_all();   // (a CTA that reported a time-out has waited above)
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if constexpr (CTAS == 2) {
+      tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    } else {
+      tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
   }
 }
 
@@ -999,8 +1078,47 @@ cudaError_t launch_cfg(const TcMaps& maps, const TcParams& p, int grid, cudaStre
   const cudaError_t attr_err = cudaFuncSetAttribute(
       tc_contract_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
   if (attr_err != cudaSuccess) return attr_err;
-  tc_contract_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(maps, p);
-  return cudaGetLastError();
+  if constexpr (Cfg::CTAS == 2) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, tc_contract_kernel<Cfg>, maps, p);
+  } else {
+    tc_contract_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(maps, p);
+    return cudaGetLastError();
+  }
+}
+
+// Clusters of two that the device can keep resident at once (0 if the query fails).
+template <class Cfg>
+int max_resident_pairs() {
+  if (cudaFuncSetAttribute(tc_contract_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           Cfg::SMEM_BYTES) != cudaSuccess) {
+    return 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, tc_contract_kernel<Cfg>, &cfg) != cudaSuccess) return 0;
+  return n;
 }
 
 }  // namespace pmlb

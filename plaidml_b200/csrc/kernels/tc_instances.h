@@ -38,3 +38,13 @@
   X(4, 64, 2, false, false, 4, 1)   \
   X(4, 128, 2, false, false, 4, 1)  \
   X(4, 64, 2, false, false, 4, 2)
+
+// CTA-pair instances (two CTAs per 256 x 256 tile, cta_group::2 MMAs): plain GEMMs with long
+// main loops; same columns, always one epilogue group per CTA.
+#define PMLB_TC_LIST_PAIR(X)        \
+  X(2, 256, 1, 0, false, 4, 1)      \
+  X(2, 256, 1, 0, false, 2, 1)      \
+  X(2, 256, 1, 0, true, 4, 1)       \
+  X(2, 256, 1, 0, true, 2, 1)       \
+  X(1, 256, 1, 0, false, 4, 1)      \
+  X(1, 256, 1, 0, true, 4, 1)

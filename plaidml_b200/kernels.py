@@ -21,6 +21,8 @@ EPI_BIAS, EPI_RESIDUAL, EPI_RELU, EPI_ROWMAX = 1, 2, 4, 8
 GEMM_TRANSPOSE_B = 1
 GEMM_PLAIN_STORES = 2
 GEMM_PLAIN_RESIDUAL = 4
+GEMM_CTA_PAIRS = 8
+GEMM_NO_CTA_PAIRS = 16
 CONV_NO_PACKED_ROWS = 1
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = range(5)
 

@@ -286,3 +286,58 @@ def test_f32_ragged():
     b = g.uniform(-1, 1, size=(1, k, n)).astype(np.float32)
     c, _, _ = run_gemm(K.F32, K.F32, dev(a), dev(b), m, n, k, 1, False)
     assert max_rel(c.cpu().numpy(), oracle.gemm_f32_acc64(a, b, False)) < 1e-5
+
+
+# --- CTA pairs (two CTAs per 256 x 256 tile) -----------------------------------------------------
+
+@pytest.mark.parametrize("b_is_nk", [True, False], ids=["B[n][k]", "B[k][n]"])
+def test_cta_pairs_bf16_matches_single_cta_and_oracle(b_is_nk):
+    # ragged in M (the second CTA of the last pair has no rows), N and K; more pair tiles than clusters
+    g = rng(50)
+    m, n, k = 128 * 5 + 24, 256 * 3 + 72, 2048 + 40
+    a = dev_bf16(g.standard_normal((1, m, k)))
+    b = dev_bf16(g.standard_normal((1, n, k) if b_is_nk else (1, k, n)))
+    outs = []
+    for flags in (K.GEMM_CTA_PAIRS, K.GEMM_NO_CTA_PAIRS):
+        c, _, _ = run_gemm(K.BF16, K.F32, a, b, m, n, k, b_is_nk=b_is_nk, tile_n=256, flags=flags)
+        outs.append(c.cpu().numpy())
+    ref = oracle.gemm_h16_f32(bits16(a), bits16(b), False, b_is_nk)
+    check_close(outs[0], ref, 1e-4)
+    np.testing.assert_array_equal(outs[0], outs[1])      # same products in the same order per element
+
+
+@pytest.mark.parametrize("b_is_nk", [True, False], ids=["B[n][k]", "B[k][n]"])
+def test_cta_pairs_int8_bit_exact(b_is_nk):
+    g = rng(51)
+    m, n, k = 1024 + 128, 512, 4096
+    a = g.integers(-128, 128, size=(1, m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(1, n, k) if b_is_nk else (1, k, n), dtype=np.int8)
+    c, _, _ = run_gemm(K.I8, K.I32, dev(a), dev(b), m, n, k, b_is_nk=b_is_nk, tile_n=256, flags=K.GEMM_CTA_PAIRS)
+    np.testing.assert_array_equal(c.cpu().numpy(), oracle.gemm_i8_i32(a, b, b_is_nk))
+
+
+def test_cta_pairs_batched_epilogue_bf16_out():
+    g = rng(52)
+    m, n, k = 384, 512, 1600
+    a = dev_bf16(g.standard_normal((3, m, k)))
+    b = dev_bf16(g.standard_normal((3, n, k)) * 0.05)
+    bias = dev(g.standard_normal(n).astype(np.float32))
+    res = dev_bf16(g.standard_normal((3, m, n)))
+    c, _, _ = run_gemm(K.BF16, K.BF16, a, b, m, n, k, batch=3, tile_n=256, flags=K.GEMM_CTA_PAIRS,
+                       epilogue=K.EPI_BIAS | K.EPI_RESIDUAL | K.EPI_RELU, bias=bias, residual=res)
+    ref = oracle.gemm_h16_f32(bits16(a), bits16(b), False, True)
+    ref = ref + bias.cpu().numpy()[None, None, :] + as_f32(res)
+    ref = oracle.bf16_to_f32(oracle.f32_to_bf16(np.where(ref < 0, 0, ref)))
+    check_close(as_f32(c), ref, 1e-2)
+
+
+def test_large_gemm_chooses_cta_pairs_and_is_exact():
+    # the headline shape takes the pair kernel by itself; int8 makes any slip visible
+    g = rng(53)
+    m = n = k = 4096
+    a = g.integers(-128, 128, size=(1, m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(1, k, n), dtype=np.int8)
+    c, _, _ = run_gemm(K.I8, K.I32, dev(a), dev(b), m, n, k, b_is_nk=False)
+    rows = np.concatenate([np.arange(0, 300), np.arange(4096 - 300, 4096)])
+    ref = oracle.gemm_i8_i32(np.ascontiguousarray(a[:, rows]), b, False)
+    np.testing.assert_array_equal(c.cpu().numpy()[:, rows], ref)
