@@ -186,13 +186,25 @@ class Planner {
     std::stable_sort(pending_.begin(), pending_.end(),
                      [](const Pending& x, const Pending& y) { return x.position < y.position; });
 
+    fuseRowMaxima();
+
     // ---- phase B: which steps are needed for the outputs
     std::vector<bool> needed(nv, false);
     for (int o : prog_.outputs) needed[root(o)] = true;
     std::vector<bool> keep(pending_.size(), false);
     for (size_t k = pending_.size(); k-- > 0;) {
       Pending& pd = pending_[k];
-      if (!needed[root(pd.result)]) continue;
+      if (pd.dropped) continue;
+      const bool mainNeeded = needed[root(pd.result)];
+      const bool sideNeeded = pd.rowmax >= 0 && needed[root(pd.rowmax)];
+      if (!mainNeeded && !sideNeeded) continue;
+      if (pd.rowmax >= 0) {
+        pd.storeMain = mainNeeded;
+        if (!sideNeeded) {
+          pd.rowmax = -1;
+          pd.gemm.epilogue &= ~PMLB_EPI_ROWMAX;
+        }
+      }
       keep[k] = true;
       for (int in : pd.inputs) needed[root(in)] = true;
     }
@@ -218,11 +230,40 @@ class Planner {
     pmlb_pool_desc pool;
     int a = -1, b = -1, bias = -1, residual = -1;  // value ids
     bool swapped = false;
+    int rowmax = -1;            // GEMM: value that receives the row maxima of the product (fused max-reduction)
+    bool storeMain = true;      // GEMM with fused row maxima: false if nothing else reads the product
+    bool dropped = false;       // folded into another step
   };
 
   int root(int v) const {
     while (alias_[v] >= 0) v = alias_[v];
     return v;
+  }
+
+  // R[b, i] = max_j S[b, i, j] right after the GEMM that produces S: the GEMM's epilogue folds
+  // each accumulator row into R (one atomic max per row and tile) and the separate pass over S
+  // goes away; S itself is still written if anything else reads it.  (The Q.K^T-then-row-max
+  // pattern of attention scores.)
+  void fuseRowMaxima() {
+    for (size_t r = 0; r < pending_.size(); ++r) {
+      Pending& red = pending_[r];
+      if (red.dropped || red.kind != Pending::Reduce) continue;
+      const pmlb_reduce_desc& rd = red.reduce;
+      if (rd.agg != PMLB_AGG_MAX || rd.dtype != PMLB_F32 || rd.out_dtype != PMLB_F32 || rd.inner != 1) continue;
+      for (size_t g = 0; g < r; ++g) {
+        Pending& gm = pending_[g];
+        if (gm.dropped || gm.kind != Pending::Gemm || gm.rowmax >= 0) continue;
+        if (root(gm.result) != root(red.a)) continue;
+        const pmlb_gemm_desc& gd = gm.gemm;
+        if (gd.out_dtype != PMLB_F32 || rd.reduce != gd.n || rd.outer != static_cast<int64_t>(gd.batch) * gd.m) continue;
+        if (gd.ldc != gd.n || (gd.batch > 1 && gd.stride_c != static_cast<int64_t>(gd.m) * gd.n)) continue;
+        gm.gemm.epilogue |= PMLB_EPI_ROWMAX;
+        gm.rowmax = red.result;
+        gm.fused += "+rowmax";
+        red.dropped = true;
+        break;
+      }
+    }
   }
 
   const PValue& val(int v) const { return prog_.values[v]; }
@@ -842,14 +883,15 @@ class Planner {
            << " in=" << dtypeName(static_cast<DType>(pd.gemm.in_dtype)) << " out=" << dtypeName(static_cast<DType>(pd.gemm.out_dtype))
            << (pd.gemm.b_is_nk ? " B[n][k]" : " B[k][n]") << pd.fused;
         st.detail = os.str();
-        st.launches = 1 + (pd.gemm.in_dtype == PMLB_F32 ? 2 : 0);
+        st.launches = 1 + (pd.gemm.in_dtype == PMLB_F32 ? 2 : 0) + (pd.rowmax >= 0 ? 1 : 0);
         const void* a = dev(pd.a);
         const void* b = dev(pd.b);
-        void* c = dev(pd.result);
+        void* c = pd.storeMain ? dev(pd.result) : nullptr;
         const void* bias = pd.bias >= 0 ? dev(pd.bias) : nullptr;
         const void* res = pd.residual >= 0 ? dev(pd.residual) : nullptr;
-        st.launch = [plan, a, b, c, bias, res](cudaStream_t s) {
-          return pmlb_gemm_invoke(plan, s, a, b, c, bias, res, nullptr);
+        float* rowmax = pd.rowmax >= 0 ? reinterpret_cast<float*>(dev(pd.rowmax)) : nullptr;
+        st.launch = [plan, a, b, c, bias, res, rowmax](cudaStream_t s) {
+          return pmlb_gemm_invoke(plan, s, a, b, c, bias, res, rowmax);
         };
         break;
       }

@@ -125,11 +125,22 @@ def test_qk_batched_gemm_then_row_max():
     R = Contraction(name="rowmax").outShape(b, m).outAccess(bb, i).max(S[bb, i, j]).build()
     runner = Runner(Program("qk_rowmax", [Q, Kt], [S, R]), "cuda.0")
     desc = runner.executable.describe()
-    assert "tc_gemm" in desc and "row_reduce" in desc, desc
+    # the row maximum rides in the GEMM's epilogue: one step, no second pass over S
+    assert "tc_gemm" in desc and "+rowmax" in desc and "row_reduce" not in desc, desc
     s_out, r_out = runner.run([q, kk])
     ref = oracle.gemm_h16_f32(q, kk, False, True)
     check_close(s_out, ref, 1e-2)
     np.testing.assert_array_equal(r_out, s_out.max(axis=2))   # exact given identical S
+    # the same maxima when only R is asked for (S is then never written) ...
+    only_r = Runner(Program("qk_rowmax_only", [Q, Kt], [R]), "cuda.0")
+    assert "+rowmax" in only_r.executable.describe()
+    np.testing.assert_array_equal(only_r.run([q, kk])[0], r_out)
+    # ... and from the separate reduction kernel when S comes from somewhere else
+    Sin = Placeholder(DType.FLOAT32, [b, m, m])
+    R2 = Contraction(name="rowmax").outShape(b, m).outAccess(bb, i).max(Sin[bb, i, j]).build()
+    plain = Runner(Program("rowmax_alone", [Sin], [R2]), "cuda.0")
+    assert "row_reduce" in plain.executable.describe()
+    np.testing.assert_array_equal(plain.run([s_out])[0], r_out)
 
 
 def test_maxpool_and_mean_and_softmax():
