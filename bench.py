@@ -36,7 +36,7 @@ M_PER_GPU, N_DIM, K_DIM = 4096, 4096, 4096
 WORKLOAD = "cfg2: int8 x int8 -> int32 Tile GEMM, N=K=4096, M=4096 rows per GPU (rows of M sharded)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one tc_contract launch of this workload, from
 # the ncu capture summarised in profiles/tc_gemm_i8_4096.md
-NCU_TRAFFIC_BYTES = 52.02e6
+NCU_TRAFFIC_BYTES = 52.58e6
 
 
 emit = None  # set by main(): writes the result line
@@ -309,7 +309,7 @@ def main() -> None:
                      "peak_source": ("2 x bf16_tflops of MEASURED_PEAKS.json (int8 dense peak derived from the measured "
                                      "bf16 burst figure; the file carries no int8 number)"
                                      if "_fallback" not in peaks else "2 x fallback bf16 figure"),
-                     "kernel": "tc_contract_kernel (int8, 128x256 tiles, B read as [k][n])",
+                     "kernel": "tc_contract_kernel (int8, CTA pairs on 256x256 tiles, cta_group::2 MMAs, B read as [k][n])",
                      "algorithmic_ops_per_launch": ops_per_step},
     }
     if args.gpus == 1 and world == 1:
