@@ -136,6 +136,9 @@ typedef struct {
  * that fills the device; these flags force the choice for 256-wide tiles (for testing). */
 #define PMLB_GEMM_CTA_PAIRS 8
 #define PMLB_GEMM_NO_CTA_PAIRS 16
+/* When the tiles left over after the last full wave occupy at most half of the SMs, 256-wide
+ * tiles of that tail are computed as two 128-wide halves; this flag keeps them whole (testing). */
+#define PMLB_GEMM_NO_TAIL_SPLIT 32
 
 pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* desc, pmlb_plan** plan);
 

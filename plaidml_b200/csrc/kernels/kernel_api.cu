@@ -349,6 +349,7 @@ pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream_v, const void* a, con
   L.residual_from_global = (d.flags & PMLB_GEMM_PLAIN_RESIDUAL) != 0;
   if (d.flags & PMLB_GEMM_CTA_PAIRS) L.pair_override = 1;
   if (d.flags & PMLB_GEMM_NO_CTA_PAIRS) L.pair_override = 0;
+  if (d.flags & PMLB_GEMM_NO_TAIL_SPLIT) L.split_tail = 0;
   L.trace = g_trace_buffer;
 
   if (plan->split) {

@@ -453,14 +453,27 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   }
 
   const long long total = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n;
-  if (total > 0x7fffffffLL) {
+  if (total > 0x3fffffffLL) {
     *err = "too many tiles";
     return 1;
   }
-  int grid = static_cast<int>(std::min<long long>(total, num_sms));
-  if (L.grid_override > 0) grid = std::min<long long>(total, L.grid_override);
+  // Tail of the last wave: when the tiles left over after the full waves occupy at most half of
+  // the CTAs (pairs), they are walked as two half-width tiles each and take half as long.
+  p.tiles_full = static_cast<int>(total);
+  p.idesc_half = p.idesc;
+  if (bn == 256 && !L.window && L.split_tail != 0) {
+    const long long workers = pair ? resident_pairs[dev] : num_sms;
+    const long long rem = total % workers;
+    if (total > workers && rem > 0 && 2 * rem <= workers) {
+      p.tiles_full = static_cast<int>(total - rem);
+      p.idesc_half = make_idesc(eb, L.is_f16, L.b_mn, bn / 2, pair ? 256 : 128);
+    }
+  }
+  const long long walked = 2 * total - p.tiles_full;
+  int grid = static_cast<int>(std::min<long long>(walked, num_sms));
+  if (L.grid_override > 0) grid = std::min<long long>(walked, L.grid_override);
   if (pair) {
-    long long pairs = std::min<long long>(total, resident_pairs[dev]);
+    long long pairs = std::min<long long>(walked, resident_pairs[dev]);
     if (L.grid_override > 0) pairs = std::min<long long>(pairs, std::max(1, L.grid_override / 2));
     grid = static_cast<int>(2 * pairs);
   }

@@ -27,6 +27,7 @@ struct TcParams {
   // Problem (per batch entry): C[m, n] = sum_k A[m, k] * B[n, k]
   int m, n, k, batch;
   int tiles_m, tiles_n;  // tiles per batch entry
+  int tiles_full;        // tiles walked whole; the rest (the tail of the last wave) as two half-width tiles each
   int num_kb;            // k-blocks (of 128 bytes of K) per tile
   int group_m;           // m-tiles per rasterisation group (L2 reuse of B panels)
   int a_bz, b_bz;        // 1: operand has a batch dimension, 0: one matrix shared by all entries
@@ -59,6 +60,7 @@ struct TcParams {
   int res_tma;           // 1: the staged epilogue fetches residual rows by TMA into its staging buffers
 
   uint32_t idesc;        // tcgen05 instruction descriptor
+  uint32_t idesc_half;   // the same for a half-width tile
   int* status;           // device word: 0 = ok, otherwise the first error code seen
   long long* trace;      // debugging: CTA 0 logs (role, tile, event, clock64) records here, or null
 };

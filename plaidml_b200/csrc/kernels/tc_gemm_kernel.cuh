@@ -143,6 +143,7 @@ __device__ __forceinline__ void trace_event(const TcParams& p, int role, int& n,
 
 struct TileCoord {
   int b, tm, tn;
+  int n0, bn;   // first output column and width of the tile (set by tile_coord_cta)
 };
 
 __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int t) {
@@ -191,10 +192,21 @@ __device__ __forceinline__ TileCoord tile_coord_for(const TcParams& p, int t) {
   }
 }
 
-// CTA pairs: the pair tile's coordinate with tm turned into this CTA's 128-row tile number.
+// Tile number t as the roles walk it -> coordinates for this CTA.  Tiles below p.tiles_full
+// are whole BN-wide tiles; above it every remaining tile appears twice, as its left and its
+// right half (the tail of the last wave, cut in two so that it takes half as long).  CTA pairs:
+// tm becomes this CTA's 128-row tile number.
 template <class Cfg>
 __device__ __forceinline__ TileCoord tile_coord_cta(const TcParams& p, int t, uint32_t cta_rank) {
-  TileCoord c = tile_coord_for<Cfg>(p, t);
+  int idx = t, half = -1;
+  if (t >= p.tiles_full) {
+    const int u = t - p.tiles_full;
+    idx = p.tiles_full + (u >> 1);
+    half = u & 1;
+  }
+  TileCoord c = tile_coord_for<Cfg>(p, idx);
+  c.bn = half < 0 ? Cfg::BN : Cfg::BN / 2;
+  c.n0 = c.tn * Cfg::BN + (half > 0 ? Cfg::BN / 2 : 0);
   if constexpr (Cfg::CTAS == 2) c.tm = 2 * c.tm + static_cast<int>(cta_rank);
   return c;
 }
@@ -452,7 +464,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   const uint32_t tmem_base = *tmem_slot;
 
   // (pairs: p.tiles_m counts 256-row pair tiles; CTA `rank` takes rows 128 * rank .. of each)
-  const int total_tiles = p.batch * p.tiles_m * p.tiles_n;
+  const int total_tiles = 2 * p.batch * p.tiles_m * p.tiles_n - p.tiles_full;   // halves count twice
   // Tiles this CTA walks: every gridDim.x-th one (pairs: every cluster-count-th one), or
   // (packed-row mode) a contiguous range.
   int t_begin = blockIdx.x / CTAS, t_end = total_tiles, t_step = gridDim.x / CTAS;
@@ -547,11 +559,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
                                  static_cast<uint16_t>(fs * p.conv_dil_w),
                                  static_cast<uint16_t>(fr * p.conv_dil_h));
               // weights laid out [k_out][tap][c_in]: map dims (c_in, tap, k_out)
-              tma_load_3d(s_b, &tm.b0, fb, cb * BK, tap, tc.tn * BN);
+              tma_load_3d(s_b, &tm.b0, fb, cb * BK, tap, tc.n0);
             } else if constexpr (CTAS == 2) {
               // both CTAs count their bytes on the first CTA's barrier, which expects both
               const uint32_t fb0 = mapa_rank(fb, 0);
-              const int n0 = tc.tn * BN + static_cast<int>(cta_rank) * (BN / 2);
+              const int n0 = tc.n0 + static_cast<int>(cta_rank) * (tc.bn / 2);
               tma_load_3d_pair(s_a, &tm.a0, fb0, kb * BK, tc.tm * 128, tc.b * p.a_bz);
               if constexpr (Cfg::B_MN) {
 #pragma unroll
@@ -570,13 +582,13 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
               if constexpr (Cfg::B_MN) {
 #pragma unroll
                 for (int ch = 0; ch < Cfg::B_CHUNKS; ++ch) {
-                  tma_load_3d(s_b + ch * (BK * 128), &tm.b0, fb, tc.tn * BN + ch * BK, kb * BK,
+                  tma_load_3d(s_b + ch * (BK * 128), &tm.b0, fb, tc.n0 + ch * BK, kb * BK,
                               tc.b * p.b_bz);
                 }
               } else {
-                tma_load_3d(s_b, &tm.b0, fb, kb * BK, tc.tn * BN, tc.b * p.b_bz);
+                tma_load_3d(s_b, &tm.b0, fb, kb * BK, tc.n0, tc.b * p.b_bz);
                 if constexpr (NSPLIT == 2) {
-                  tma_load_3d(s_b + Cfg::B_TILE, &tm.b1, fb, kb * BK, tc.tn * BN, tc.b * p.b_bz);
+                  tma_load_3d(s_b + Cfg::B_TILE, &tm.b1, fb, kb * BK, tc.n0, tc.b * p.b_bz);
                 }
               }
             }
@@ -689,6 +701,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         if (leader) trace_event(p, 1, ntrace, t, 1);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        const uint32_t idesc = t >= p.tiles_full ? p.idesc_half : p.idesc;   // half-width tail tiles
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait_warp(full_bar(stage), phase, abort_flag)) {
             if (leader && *abort_code == 0) *abort_code = 3;
@@ -710,26 +723,26 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
               // fp32 as three TF32 products; the two cross terms first.
               const uint64_t a_lo = desc_at(desc_k, s_a + Cfg::A_TILE);
               const uint64_t b_lo = desc_at(desc_k, s_b + Cfg::B_TILE);
-              tc_mma<Cfg::KIND>(d_tmem, a_lo, b_hi, p.idesc, kb > 0 ? 1u : 0u);
-              tc_mma<Cfg::KIND>(d_tmem, a_hi, b_lo, p.idesc, 1u);
-              tc_mma<Cfg::KIND>(d_tmem, a_hi, b_hi, p.idesc, 1u);
+              tc_mma<Cfg::KIND>(d_tmem, a_lo, b_hi, idesc, kb > 0 ? 1u : 0u);
+              tc_mma<Cfg::KIND>(d_tmem, a_hi, b_lo, idesc, 1u);
+              tc_mma<Cfg::KIND>(d_tmem, a_hi, b_hi, idesc, 1u);
 #pragma unroll
               for (int j = 1; j < 4; ++j) {
-                tc_mma<Cfg::KIND>(d_tmem, a_lo + kStepA * j, b_hi + kStepB * j, p.idesc, 1u);
-                tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_lo + kStepB * j, p.idesc, 1u);
-                tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, p.idesc, 1u);
+                tc_mma<Cfg::KIND>(d_tmem, a_lo + kStepA * j, b_hi + kStepB * j, idesc, 1u);
+                tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_lo + kStepB * j, idesc, 1u);
+                tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, idesc, 1u);
               }
             } else if constexpr (CTAS == 2) {
-              tc_mma_pair<Cfg::KIND>(d_tmem, a_hi, b_hi, p.idesc, kb > 0 ? 1u : 0u);
+              tc_mma_pair<Cfg::KIND>(d_tmem, a_hi, b_hi, idesc, kb > 0 ? 1u : 0u);
 #pragma unroll
               for (int j = 1; j < 4; ++j) {
-                tc_mma_pair<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, p.idesc, 1u);
+                tc_mma_pair<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, idesc, 1u);
               }
             } else {
-              tc_mma<Cfg::KIND>(d_tmem, a_hi, b_hi, p.idesc, kb > 0 ? 1u : 0u);
+              tc_mma<Cfg::KIND>(d_tmem, a_hi, b_hi, idesc, kb > 0 ? 1u : 0u);
 #pragma unroll
               for (int j = 1; j < 4; ++j) {
-                tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, p.idesc, 1u);
+                tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, idesc, 1u);
               }
             }
             if constexpr (CTAS == 2) {
@@ -788,10 +801,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         const TileCoord tc = tile_coord_cta<Cfg>(p, t, cta_rank);
         const int row0 = tc.tm * 128 + q * 32;
         const int row = row0 + lane;
-        const int col_base = tc.tn * BN;
+        const int col_base = tc.n0;
+        const int nch = tc.bn / CW;                 // chunks of this tile
         auto request_res = [&](int ch) {
           const int c0 = col_base + ch * CW;
-          if (ch < Cfg::BN / CW && c0 < p.n) {       // warp-uniform
+          if (ch < nch && c0 < p.n) {                // warp-uniform
             if (lane == 0) {
               const uint32_t b = nreq & 1u;
               mbar_arrive_expect_tx(res_bar(ew, b), 4096u);
@@ -820,7 +834,6 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
             static_cast<long long>(tc.b) * p.res_batch + static_cast<long long>(row) * p.ldr;
         float row_best = -INFINITY;
 
-        constexpr int NCH = BN / CW;
         auto issue_load = [&](uint32_t(&v)[CW], int ch) {
           uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&v[0]);
           tmem_ld_32x32(t_acc + ch * CW, lo);
@@ -919,17 +932,17 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           uint32_t va[CW], vb[CW];
           issue_load(va, 0);
 #pragma unroll 1
-          for (int ch = 0; ch < NCH; ch += 2) {
+          for (int ch = 0; ch < nch; ch += 2) {
             tmem_ld_wait();
             pin(va);
-            if (ch + 1 < NCH) issue_load(vb, ch + 1);
-            if (ch == NCH - 1) release_acc();
+            if (ch + 1 < nch) issue_load(vb, ch + 1);
+            if (ch == nch - 1) release_acc();
             process(va, ch);
-            if (ch + 1 < NCH) {
+            if (ch + 1 < nch) {
               tmem_ld_wait();
               pin(vb);
-              if (ch + 2 < NCH) issue_load(va, ch + 2);
-              if (ch + 1 == NCH - 1) release_acc();
+              if (ch + 2 < nch) issue_load(va, ch + 2);
+              if (ch + 1 == nch - 1) release_acc();
               process(vb, ch + 1);
             }
           }
@@ -937,12 +950,12 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           // two warps per scheduler hide each other's latencies; one register set suffices
           uint32_t va[CW];
 #pragma unroll 1
-          for (int ch = 0; ch < NCH; ++ch) {
+          for (int ch = 0; ch < nch; ++ch) {
             issue_load(va, ch);
             tmem_ld_wait();
             pin(va);
             if (tracer) trace_event(p, 2 + grp, ntrace, t, 10 + ch);
-            if (ch == NCH - 1) release_acc();
+            if (ch == nch - 1) release_acc();
             process(va, ch);
             if (tracer) trace_event(p, 2 + grp, ntrace, t, 30 + ch);
           }
@@ -970,7 +983,8 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         }
         tc_fence_after_sync();
         const int row0 = tc.tm * 128 + q * 32;     // first row of this warp
-        const int col_base = tc.tn * BN;
+        const int col_base = tc.n0;
+        const int nch32 = tc.bn / 32;
         const uint32_t t_acc =
             tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(q * 32) << 16);
         const long long out_b = static_cast<long long>(tc.b) * p.out_batch;
@@ -978,12 +992,12 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         float row_best = -INFINITY;
 
 #pragma unroll 1
-        for (int ch = 0; ch < BN / 32; ++ch) {
+        for (int ch = 0; ch < nch32; ++ch) {
           const int col0 = col_base + ch * 32;
           uint32_t v[32];
           tmem_ld_32x32(t_acc + ch * 32, v);
           tmem_ld_wait();
-          if (ch == BN / 32 - 1) {
+          if (ch == nch32 - 1) {
             // accumulator fully read: hand it back before finishing the stores
             tc_fence_before_sync();
             __syncwarp();

@@ -69,6 +69,7 @@ struct TcLaunch {
   int bn_override = 0;    // 0 = choose; else 64, 128 or 256
   int epi_groups_override = 0;  // 0 = choose; else 1 or 2
   int grid_override = 0;  // 0 = one CTA per SM
+  int split_tail = -1;    // -1 / 1 = halve the tiles of a short last wave; 0 = never
   int pair_override = -1; // -1 = choose; 0 = never pair CTAs on one tile; 1 = whenever the shape allows
 };
 

@@ -23,6 +23,7 @@ GEMM_PLAIN_STORES = 2
 GEMM_PLAIN_RESIDUAL = 4
 GEMM_CTA_PAIRS = 8
 GEMM_NO_CTA_PAIRS = 16
+GEMM_NO_TAIL_SPLIT = 32
 CONV_NO_PACKED_ROWS = 1
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = range(5)
 

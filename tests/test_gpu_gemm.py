@@ -341,3 +341,34 @@ def test_large_gemm_chooses_cta_pairs_and_is_exact():
     rows = np.concatenate([np.arange(0, 300), np.arange(4096 - 300, 4096)])
     ref = oracle.gemm_i8_i32(np.ascontiguousarray(a[:, rows]), b, False)
     np.testing.assert_array_equal(c.cpu().numpy()[:, rows], ref)
+
+
+# --- half-width tiles in a short last wave --------------------------------------------------------
+
+@pytest.mark.parametrize("pairs", [False, True], ids=["one CTA per tile", "CTA pairs"])
+@pytest.mark.parametrize("kind", ["bf16 B[n][k]", "bf16 B[k][n]", "int8 B[n][k]", "int8 B[k][n]"])
+def test_split_tail_matches_whole_tiles(kind, pairs):
+    # 168 tiles of 128 x 256 (84 pair tiles): one full wave on a 148-SM device plus a tail of 20 (10), which
+    # is walked as half-width tiles; the result must not depend on it
+    g = rng(60)
+    m, n, k = 1536, 3584, 320
+    b_is_nk = "[n][k]" in kind
+    if kind.startswith("bf16"):
+        a = dev_bf16(g.standard_normal((1, m, k)))
+        b = dev_bf16(g.standard_normal((1, n, k) if b_is_nk else (1, k, n)))
+        dt_in, dt_out = K.BF16, K.F32
+    else:
+        a = dev(g.integers(-128, 128, size=(1, m, k), dtype=np.int8))
+        b = dev(g.integers(-128, 128, size=(1, n, k) if b_is_nk else (1, k, n), dtype=np.int8))
+        dt_in, dt_out = K.I8, K.I32
+    base = K.GEMM_CTA_PAIRS if pairs else K.GEMM_NO_CTA_PAIRS
+    outs = []
+    for flags in (base, base | K.GEMM_NO_TAIL_SPLIT):
+        c, _, _ = run_gemm(dt_in, dt_out, a, b, m, n, k, b_is_nk=b_is_nk, tile_n=256, flags=flags)
+        outs.append(c.cpu().numpy())
+    np.testing.assert_array_equal(outs[0], outs[1])
+    if dt_in == K.I8:
+        ref = oracle.gemm_i8_i32(a.cpu().numpy(), b.cpu().numpy(), b_is_nk)
+        np.testing.assert_array_equal(outs[0], ref)
+    else:
+        check_close(outs[0], oracle.gemm_h16_f32(bits16(a), bits16(b), False, b_is_nk), 1e-4)
