@@ -201,6 +201,10 @@ typedef struct {
  * Such inputs may have any channel count; all others need c % 8 == 0.  This flag keeps an
  * eligible convolution on the general im2col route (for testing one against the other). */
 #define PMLB_CONV_NO_PACKED_ROWS 1
+/* Stride-1, undilated convolutions on whole 64-channel blocks into exactly 64 output channels
+ * take the halo route (weights resident in shared memory, each tile's padded pixels fetched
+ * once and every tap read as a shifted window).  This flag keeps them on the im2col route. */
+#define PMLB_CONV_NO_HALO 2
 
 pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* desc, pmlb_plan** plan);
 

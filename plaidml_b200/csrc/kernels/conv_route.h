@@ -28,4 +28,27 @@ inline int conv_packed_row_width(const pmlb_conv_desc& d) {
   return (wp + unit - 1) / unit * unit;
 }
 
+// Halo route: stride-1, undilated convolutions on whole 64-channel blocks into exactly 64 output
+// channels whose weights fit beside the pixel ring (the 3x3 convolutions of a network's first
+// stage): every tap is a row-shifted window of one fetched pixel buffer, so the activation
+// crosses from L2 to shared memory about 1.3 times instead of r * s times.
+// Shared memory the halo route has for weights plus pixel buffers (the kernel instance's operand
+// ring and its unused output staging area).
+constexpr int kHaloSmemBytes = 212992;
+
+inline bool conv_takes_halo(const pmlb_conv_desc& d) {
+  if (!(d.in_dtype == PMLB_BF16 || d.in_dtype == PMLB_F16)) return false;
+  if (d.stride_h != 1 || d.stride_w != 1 || d.dil_h != 1 || d.dil_w != 1) return false;
+  if (d.k != 64 || d.c % 64 != 0 || d.r * d.s < 2) return false;
+  const int wp = d.w + 2 * d.pad_w;
+  if (wp > 128 || d.q != wp - d.s + 1 || d.p != d.h + 2 * d.pad_h - d.r + 1) return false;
+  const int th = 128 / wp < d.p ? 128 / wp : d.p;
+  if (th < 1) return false;
+  // at least 3/4 of the 128 accumulator rows must be real outputs
+  if (th * d.q * 4 < 128 * 3) return false;
+  const int wts = d.r * d.s * (d.c / 64) * 64 * 128;
+  const int stage = (wp * (th + d.r - 1) * 128 + 1023) / 1024 * 1024;
+  return wts + 2 * stage + 8192 <= kHaloSmemBytes && (d.epilogue & PMLB_EPI_ROWMAX) == 0;
+}
+
 }  // namespace pmlb

@@ -97,6 +97,7 @@ struct pmlb_plan {
 
   pmlb_conv_desc conv;
   bool filter_set = false;
+  bool halo = false;             // conv: halo route (scratch = weights as for im2col)
   bool packed_rows = false;      // conv: packed-row route (scratch = weights, then the padded activation)
   size_t packed_input_off = 0;   // byte offset of the padded activation inside scratch
 
@@ -453,6 +454,10 @@ pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* d, pmlb_plan** out) {
   plan->kind_name = "tc_conv";
   plan->conv = *d;
   size_t scratch = static_cast<size_t>(d->k) * d->r * d->s * d->c * 2;
+  if (!packed && pmlb::conv_takes_halo(*d) && (d->flags & PMLB_CONV_NO_HALO) == 0) {
+    plan->halo = true;
+    plan->kind_name = "tc_conv_halo";
+  }
   if (packed) {
     plan->packed_rows = true;
     plan->kind_name = "tc_conv_rows";
@@ -553,7 +558,13 @@ pmlb_status pmlb_conv_invoke(pmlb_plan* plan, void* stream, const void* input, v
   L.batch = 1;
   L.a0 = input;
   L.b0 = plan->scratch;
-  L.conv = &g;
+  pmlb::HaloGeom hg;
+  if (plan->halo) {
+    hg.conv = g;
+    L.halo = &hg;
+  } else {
+    L.conv = &g;
+  }
   L.out = output;
   L.ldc = d.k;
   L.out_dtype = d.out_dtype;

@@ -13,6 +13,7 @@
 #include <string>
 
 #include "tc_gemm_kernel.cuh"
+#include "conv_route.h"
 #include "tc_instances.h"
 
 namespace pmlb {
@@ -262,7 +263,72 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   CUtensorMap& tb1 = maps.b1;
   CUtensorMap& tc_map = maps.c;
 
-  if (L.window) {
+  if (L.halo) {
+    const ConvGeom& g = L.halo->conv;
+    const int wp = g.w + 2 * g.pad_w;                     // = q + s - 1 for stride 1
+    const int th = wp > 0 ? std::min(128 / wp, g.p) : 0;
+    const int rows = th + g.r - 1;
+    const int cblocks = (g.c + bk - 1) / bk;
+    // operand ring plus the staging area this mode's epilogue does not use
+    using HaloCfg = TcCfg<2, 64, 1, kAHalo, false, 2, 2>;
+    static_assert(HaloCfg::STAGES * HaloCfg::STAGE + HaloCfg::STG_BYTES == kHaloSmemBytes, "halo budget");
+    const int ring_bytes = kHaloSmemBytes;
+    const int wts_bytes = g.r * g.s * cblocks * 64 * 128;
+    const int stage_bytes = (wp * rows * 128 + 1023) / 1024 * 1024;
+    // the last tap's window reaches (r - 1) * wp + s - 1 rows past the 128 it needs
+    const int overread = std::max(0, ((g.r - 1) * wp + g.s - 1 + 128) * 128 - stage_bytes);
+    const int stages = stage_bytes > 0 ? std::min(8, (ring_bytes - wts_bytes - overread) / stage_bytes) : 0;
+    if (eb != 2 || L.nsplit != 1 || L.b_mn || L.n != 64 || g.c % 64 != 0 || g.stride_h != 1 || g.stride_w != 1 ||
+        g.dil_h != 1 || g.dil_w != 1 || th < 1 || wp > 256 || rows > 256 || stages < 2 ||
+        g.q != wp - g.s + 1 || g.p != g.h + 2 * g.pad_h - g.r + 1 || L.m != g.n * g.p * g.q || L.batch != 1) {
+      *err = "halo convolution: geometry outside what the kernel takes";
+      return 3;
+    }
+    bn = 64;
+    p.conv_p = g.p;
+    p.conv_q = g.q;
+    p.conv_r = g.r;
+    p.conv_s = g.s;
+    p.conv_cblocks = cblocks;
+    p.conv_lower_h = -g.pad_h;
+    p.conv_lower_w = -g.pad_w;
+    p.halo_wp = wp;
+    p.halo_th = th;
+    p.halo_rows = rows;
+    p.halo_stage_bytes = stage_bytes;
+    p.halo_stages = stages;
+    p.halo_tiles_per_img = (g.p + th - 1) / th;
+    p.num_kb = g.r * g.s * cblocks;
+    p.batch = g.n * p.halo_tiles_per_img;     // tiles, one 128-position tile each
+    p.tiles_m = 1;
+    p.tiles_n = 1;
+    p.idesc = make_idesc(eb, L.is_f16, false, bn);
+    if ((reinterpret_cast<uintptr_t>(L.a0) & 15u) != 0) {
+      *err = "activation base address must be 16-byte aligned";
+      return 1;
+    }
+    // activation (C, W, H, N), box = 64 channels x padded width x fetched rows
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.c), static_cast<cuuint64_t>(g.w),
+                          static_cast<cuuint64_t>(g.h), static_cast<cuuint64_t>(g.n)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(g.c) * eb, static_cast<cuuint64_t>(g.c) * g.w * eb,
+                             static_cast<cuuint64_t>(g.c) * g.w * g.h * eb};
+    cuuint32_t box[4] = {64, static_cast<cuuint32_t>(wp), static_cast<cuuint32_t>(rows), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = g_encode_tiled(&ta0, dt, 4, const_cast<void*>(L.a0), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      *err = "cuTensorMapEncodeTiled (halo rows) failed with code " + std::to_string(static_cast<int>(r));
+      return 2;
+    }
+    ta1 = ta0;
+    const int taps = g.r * g.s;
+    if (!encode3d(&tb0, dt, eb, L.b0, g.c, taps, L.n, static_cast<uint64_t>(g.c) * eb,
+                  static_cast<uint64_t>(g.c) * taps * eb, bk, 1, bn, err)) {
+      return 1;
+    }
+    tb1 = tb0;
+  } else if (L.window) {
     const WinGeom& g = *L.window;
     const int row_elems = g.s * g.cp;
     if (eb != 2 || L.nsplit != 1 || L.b_mn || g.cp % 8 != 0 || row_elems > 64 || L.n > 64 ||
@@ -441,7 +507,11 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     }
     p.fast_epi = fast ? 1 : 0;
     // Residual rows ride the same staging buffers: fetched by TMA ahead of their chunk.
-    if (fast && L.out != nullptr && (L.epi_flags & kEpiResidual) && !L.residual_from_global) {
+    if (L.halo && (!fast || L.out == nullptr)) {
+      *err = "halo convolution: output rows must be 16-byte aligned";
+      return 3;
+    }
+    if (fast && L.out != nullptr && (L.epi_flags & kEpiResidual) && !L.residual_from_global && !L.halo) {
       const uint64_t r_bs = L.batch > 1 ? static_cast<uint64_t>(L.res_batch_stride) * ob
                                         : static_cast<uint64_t>(L.ldr) * ob * L.m;
       if (!encode3d(&maps.r, out_map_dtype(L.out_dtype), ob, L.residual, L.n, L.m, L.batch,
@@ -461,7 +531,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   // the CTAs (pairs), they are walked as two half-width tiles each and take half as long.
   p.tiles_full = static_cast<int>(total);
   p.idesc_half = p.idesc;
-  if (bn == 256 && !L.window && L.split_tail != 0) {
+  if (bn == 256 && !L.window && !L.halo && L.split_tail != 0) {
     const long long workers = pair ? resident_pairs[dev] : num_sms;
     const long long rem = total % workers;
     if (total > workers && rem > 0 && 2 * rem <= workers) {
@@ -484,8 +554,9 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   if (const char* env = std::getenv("PMLB_TC_EPI_GROUPS")) {
     if (env[0] == '1' || env[0] == '2') groups = env[0] - '0';
   }
+  if (L.halo) groups = 2;
   if (L.window || pair) groups = 1;  // (the row ring leaves room for one group's staging buffers only)
-  const int a_mode = L.window ? kAWindow : (L.conv ? kAIm2col : kATiled);
+  const int a_mode = L.halo ? kAHalo : (L.window ? kAWindow : (L.conv ? kAIm2col : kATiled));
   bool launched = false;
 #define PMLB_TC_CASE(EB, BN, NS, IM, MN, OB, G)                                                 \
   if (!launched && eb == EB && bn == BN && L.nsplit == NS && a_mode == static_cast<int>(IM) &&  \

@@ -44,6 +44,16 @@ struct TcParams {
   int win_slots;               // row slots in the ring (> win_r, at most 16)
   int win_slot_bytes;          // bytes per slot (rows of 128 bytes, a multiple of 1024)
 
+  // Halo convolution (stride 1: the padded pixels of a few image rows fetched once per tile,
+  // every filter tap read as a row-shifted window of that buffer, weights resident).
+  int halo_wp;                 // padded row width in pixels = output positions per image row
+  int halo_th;                 // output image rows per tile (halo_th * halo_wp <= 128)
+  int halo_rows;               // image rows fetched per tile = halo_th + r - 1
+  int halo_stage_bytes;        // bytes per fetched buffer (a multiple of 1024)
+  int halo_stages;             // buffers in the ring
+  int halo_tiles_per_img;      // ceil(p / halo_th)
+  int conv_r;                  // filter taps along H
+
   // Epilogue
   void* out;
   long long ldc;         // elements between output rows

@@ -33,6 +33,10 @@ enum : int {
   kAIm2col = 1,  // an NHWC activation, im2col TMA: one k-block per filter tap and channel block
   kAWindow = 2,  // a packed-row activation: one k-block per filter row, each input row fetched
                  // once into a ring of row slots and reused by the output rows that overlap it
+  kAHalo = 3,    // an NHWC activation, stride-1 convolution: the zero-padded pixels of a few
+                 // image rows are fetched once per tile (tiled TMA, padding = out-of-bounds
+                 // fill) and every filter tap is read as a row-shifted window of that buffer;
+                 // output positions in the padding columns are computed and discarded
 };
 
 template <int EB, int BN_, int NSPLIT_, int A_MODE_, bool B_MN_, int OUT_BYTES_ = 4,
@@ -55,6 +59,7 @@ struct TcCfg {
   static constexpr int A_MODE = A_MODE_;
   static constexpr bool A_IM2COL = A_MODE_ == kAIm2col;
   static constexpr bool A_WINDOW = A_MODE_ == kAWindow;
+  static constexpr bool A_HALO = A_MODE_ == kAHalo;
   static constexpr bool B_MN = B_MN_;
   static constexpr int BK = 128 / EB;       // elements of K per stage
   static constexpr int UMMA_K = 32 / EB;    // elements of K per tcgen05.mma
@@ -433,6 +438,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       }
       mbar_init(wts_bar, 1);
     }
+    if constexpr (Cfg::A_HALO) mbar_init(wts_bar, 1);
     *abort_flag = 0;
     *abort_code = 0;
     fence_mbar_init();
@@ -477,6 +483,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   const uint32_t win_wts = ring;
   const uint32_t win_slots = ring + static_cast<uint32_t>(p.win_r) * Cfg::B_TILE;
 
+  // halo mode: the weights of every (tap, channel block) stay in shared memory ahead of the ring
+  // of fetched pixel buffers; halo_nb = k-blocks (taps x channel blocks) per tile
+  const int halo_taps = p.conv_r * p.conv_s;
+  const uint32_t halo_ring = ring + static_cast<uint32_t>(halo_taps * p.conv_cblocks) * Cfg::B_TILE;
+
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     // The whole warp walks the loops (so that addresses and coordinates stay on the uniform
@@ -486,7 +497,42 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     uint32_t phase = 0;
     bool ok = true;
     int ntrace = 0;
-    if constexpr (Cfg::A_WINDOW) {
+    if constexpr (Cfg::A_HALO) {
+      // Weights of every tap and channel block, once: block (tap, cb) at wts + (tap * cblocks + cb).
+      if (leader) {
+        mbar_arrive_expect_tx(wts_bar, static_cast<uint32_t>(halo_taps * p.conv_cblocks) * Cfg::B_TILE);
+        for (int tap = 0; tap < halo_taps; ++tap) {
+          for (int cb = 0; cb < p.conv_cblocks; ++cb) {
+            tma_load_3d(ring + static_cast<uint32_t>(tap * p.conv_cblocks + cb) * Cfg::B_TILE, &tm.b0,
+                        wts_bar, cb * BK, tap, 0);
+          }
+        }
+      }
+      // One buffer per tile and channel block: image rows p0 - pad .. of the padded width.
+      const uint32_t nst = static_cast<uint32_t>(p.halo_stages);
+      uint32_t hs = 0, hphase = 0;
+      for (int t = t_begin; t < t_end && ok; t += t_step) {
+        const int img = t / p.halo_tiles_per_img;
+        const int p0 = (t - img * p.halo_tiles_per_img) * p.halo_th;
+        for (int cb = 0; cb < p.conv_cblocks; ++cb) {
+          if (!mbar_wait_warp(empty_bar(hs), hphase ^ 1u, abort_flag)) {
+            if (leader && *abort_code == 0) *abort_code = 1;
+            ok = false;
+            break;
+          }
+          if (leader) {
+            trace_event(p, 0, ntrace, t, cb);
+            mbar_arrive_expect_tx(full_bar(hs), static_cast<uint32_t>(p.halo_wp * p.halo_rows) * 128u);
+            tma_load_4d(halo_ring + hs * static_cast<uint32_t>(p.halo_stage_bytes), &tm.a0, full_bar(hs),
+                        cb * BK, p.conv_lower_w, p0 + p.conv_lower_h, img);
+          }
+          if (++hs == nst) {
+            hs = 0;
+            hphase ^= 1u;
+          }
+        }
+      }
+    } else if constexpr (Cfg::A_WINDOW) {
       // Weights of every filter row, once.
       if (leader) {
         mbar_arrive_expect_tx(wts_bar, static_cast<uint32_t>(p.win_r) * Cfg::B_TILE);
@@ -627,7 +673,67 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     auto desc_at = [](uint64_t base, uint32_t saddr) {
       return base | static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
     };
-    if constexpr (Cfg::A_WINDOW) {
+    if constexpr (Cfg::A_HALO) {
+      const uint32_t nst = static_cast<uint32_t>(p.halo_stages);
+      uint32_t hs = 0, hphase = 0;
+      if (t_begin < t_end && !mbar_wait_warp(wts_bar, 0u, abort_flag)) {
+        if (leader && *abort_code == 0) *abort_code = 3;
+        ok = false;
+      }
+      // A window that starts a whole number of 128-byte rows into a fetched buffer takes the
+      // plain descriptor of its start address: TMA and the tensor core both derive the swizzle
+      // phase of a row from its shared-memory address (measured: with the row phase also put
+      // into the descriptor's base-offset field the results are wrong).
+      auto win_desc = [&](uint32_t saddr) { return desc_at(desc_k, saddr); };
+      for (int t = t_begin; t < t_end && ok; t += t_step) {
+        if (!mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          if (leader && *abort_code == 0) *abort_code = 2;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int cb = 0; cb < p.conv_cblocks && ok; ++cb) {
+          if (!mbar_wait_warp(full_bar(hs), hphase, abort_flag)) {
+            if (leader && *abort_code == 0) *abort_code = 3;
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t buf = halo_ring + hs * static_cast<uint32_t>(p.halo_stage_bytes);
+          int tap = 0;
+          for (int fr = 0; fr < p.conv_r; ++fr) {
+            for (int fs = 0; fs < p.conv_s; ++fs, ++tap) {
+              // output position j reads padded pixel j + fr * wp + fs of the buffer
+              const uint64_t a_d = win_desc(buf + static_cast<uint32_t>(fr * p.halo_wp + fs) * 128u);
+              const uint64_t b_d =
+                  desc_at(desc_k, ring + static_cast<uint32_t>(tap * p.conv_cblocks + cb) * Cfg::B_TILE);
+              if (leader) {
+                if (tap == 0 && cb == 0) trace_event(p, 1, ntrace, t, 2);
+                tc_mma<Cfg::KIND>(d_tmem, a_d, b_d, p.idesc, (cb > 0 || tap > 0) ? 1u : 0u);
+#pragma unroll
+                for (int j = 1; j < 4; ++j) {
+                  tc_mma<Cfg::KIND>(d_tmem, a_d + 2u * j, b_d + 2u * j, p.idesc, 1u);
+                }
+              }
+            }
+          }
+          if (leader) tc_commit(empty_bar(hs));
+          if (++hs == nst) {
+            hs = 0;
+            hphase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        if (leader) {
+          tc_commit(tfull_bar(acc));
+          trace_event(p, 1, ntrace, t, 3);
+        }
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    } else if constexpr (Cfg::A_WINDOW) {
       const uint32_t nslots = static_cast<uint32_t>(p.win_slots);
       // Row h of the current strip has number h + delta; `cnt_end` rows have been numbered
       // so far and the rows below number `waited` are known to have arrived.
@@ -799,8 +905,20 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         const int acc = it & 1;
         const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
         const TileCoord tc = tile_coord_cta<Cfg>(p, t, cta_rank);
-        const int row0 = tc.tm * 128 + q * 32;
-        const int row = row0 + lane;
+        int row0 = tc.tm * 128 + q * 32;
+        int row = row0 + lane;
+        if constexpr (Cfg::A_HALO) {
+          // accumulator row j = output position j of the tile: image row j / wp, column j % wp;
+          // columns past q (the padding columns) and rows past the image are not outputs
+          const int img = t / p.halo_tiles_per_img;
+          const int p0 = (t - img * p.halo_tiles_per_img) * p.halo_th;
+          const int j = q * 32 + lane;
+          const int pr = j / p.halo_wp;
+          const int qq = j - pr * p.halo_wp;
+          const bool valid = pr < p.halo_th && qq < p.conv_q && p0 + pr < p.conv_p;
+          row0 = 0;
+          row = valid ? (img * p.conv_p + p0 + pr) * p.conv_q + qq : p.m;
+        }
         const int col_base = tc.n0;
         const int nch = tc.bn / CW;                 // chunks of this tile
         auto request_res = [&](int ch) {
@@ -908,6 +1026,17 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
               }
               o[i] = make_uint4(w[0], w[1], w[2], w[3]);
             }
+          }
+          if constexpr (Cfg::A_HALO) {
+            // output pixels of a tile are not a box of the output tensor: each lane writes its
+            // own pixel's 128 bytes
+            if (row < p.m) {
+              uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(p.out) +
+                                                    (static_cast<long long>(row) * p.ldc + col0) * OB);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) dst[i] = o[i];
+            }
+            return;
           }
           // the buffer used two chunks ago must have been read by its TMA store (already
           // true when its residual rows were requested)

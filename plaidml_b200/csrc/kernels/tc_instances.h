@@ -2,6 +2,7 @@
 // files that compile them and the dispatcher that selects one.
 // X(element bytes, tile N, operand split, A mode (0 tiled, 1 im2col, 2 packed rows), B stored [k][n],
 //   output bytes, epilogue groups)
+// A modes: 0 tiled, 1 im2col, 2 packed rows, 3 halo rows
 #pragma once
 
 #define PMLB_TC_LIST_H16(X, G)      \
@@ -25,6 +26,8 @@
   X(2, 256, 1, true, false, 2, G)
 
 #define PMLB_TC_LIST_MISC(X)        \
+  X(2, 64, 1, 3, false, 2, 2)       \
+  X(2, 64, 1, 3, false, 4, 2)       \
   X(2, 64, 1, 2, false, 2, 1)       \
   X(2, 64, 1, 2, false, 4, 1)       \
   X(1, 64, 1, false, false, 4, 1)   \

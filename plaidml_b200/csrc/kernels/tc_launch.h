@@ -28,6 +28,12 @@ struct WinGeom {
   int pad_h;
 };
 
+// Halo convolution: a stride-1, undilated ConvGeom whose weights ([k_out][r*s][c], k_out = 64)
+// stay in shared memory; a0 is the activation, b0 the weights.
+struct HaloGeom {
+  ConvGeom conv;
+};
+
 struct TcLaunch {
   int elem_bytes = 2;   // 1 (int8), 2 (bf16 / f16), 4 (fp32 pre-split into TF32 hi / lo)
   bool is_f16 = false;  // 2-byte operands are IEEE half instead of bfloat16
@@ -47,6 +53,7 @@ struct TcLaunch {
   const ConvGeom* conv = nullptr;  // non-null: A is an NHWC activation fetched by im2col TMA,
                                    // B holds the weights as [k_out][r*s][c]
 
+  const HaloGeom* halo = nullptr;   // non-null: halo convolution; m, n, batch = n*p*q, k_out, 1
   const WinGeom* window = nullptr;  // non-null: packed-row convolution (a0 / b0 as described there);
                                     // m, n, batch = q, k_out, n * p
 

@@ -169,3 +169,29 @@ def test_packed_rows_residual_f32_and_bf16():
     check_close(out, ref, 1e-4)
     out, ref, _ = run_conv(34, 2, 20, 20, 3, 3, 3, 64, out_dtype=K.BF16, epilogue=K.EPI_BIAS | K.EPI_RESIDUAL)
     check_close(out, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+
+
+# --- halo route (stride 1, 64 output channels, weights resident) ----------------------------------
+
+@pytest.mark.parametrize("case", [
+    dict(n=3, h=56, w=56, c=64, r=3, s=3, k=64),                      # the first-stage layer: 2 image rows per tile
+    dict(n=2, h=15, w=20, c=64, r=3, s=3, k=64),                      # 5 rows per tile, 15 rows: exact; 22-wide rows
+    dict(n=2, h=17, w=36, c=64, r=3, s=5, k=64, pad=2),               # 3x5 taps, over-padded rows, ragged last tile
+    dict(n=70, h=14, w=14, c=64, r=3, s=3, k=64),                     # more tiles than SMs
+], ids=["56x56", "15x20", "3x5", "many"])
+def test_halo_route_matches_oracle_and_im2col(case):
+    halo, ref, plan = run_conv(70, **case)
+    assert plan.kernel == "tc_conv_halo"
+    check_close(halo, ref, 1e-4)
+    im2col, _, plan2 = run_conv(70, flags=K.CONV_NO_HALO, **case)
+    assert plan2.kernel == "tc_conv"
+    check_close(halo, im2col, 1e-5)
+
+
+def test_halo_route_epilogues():
+    out, ref, plan = run_conv(71, 2, 28, 28, 64, 3, 3, 64, out_dtype=K.BF16, epilogue=K.EPI_BIAS | K.EPI_RESIDUAL | K.EPI_RELU)
+    assert plan.kernel == "tc_conv_halo"
+    check_close(out, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+    out, ref, plan = run_conv(72, 2, 28, 28, 64, 3, 3, 64, epilogue=K.EPI_BIAS | K.EPI_RESIDUAL)
+    assert plan.kernel == "tc_conv_halo"
+    check_close(out, ref, 1e-4)
