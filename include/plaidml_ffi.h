@@ -275,6 +275,9 @@ double plaidml_executable_run(plaidml_error* err, plaidml_executable* exec, size
 plaidml_string* pmlb_exec_describe(plaidml_error* err, plaidml_executable* exec);
 /* Number of kernel launches one run enqueues. */
 size_t pmlb_exec_launch_count(plaidml_error* err, plaidml_executable* exec);
+/* 1 once the kernel sequence has been captured into a CUDA graph and passes replay it (from the
+ * second pass on, for programs of two or more steps, unless PLAIDML_CUDA_GRAPH=0), else 0. */
+int pmlb_exec_uses_graph(plaidml_error* err, plaidml_executable* exec);
 /* Re-runs the kernel sequence `iters` times on the inputs already resident on the device from
  * the last plaidml_executable_run (no host copies) and returns the mean milliseconds per
  * iteration measured with CUDA events on the executable's stream. */

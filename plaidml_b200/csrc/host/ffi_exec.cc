@@ -54,6 +54,10 @@ size_t pmlb_exec_launch_count(plaidml_error* err, plaidml_executable* exec) {
   return ffiWrap<size_t>(err, 0, [&] { return exec->exec->launchCount(); });
 }
 
+int pmlb_exec_uses_graph(plaidml_error* err, plaidml_executable* exec) {
+  return ffiWrap<int>(err, 0, [&] { return exec->exec->usesGraph() ? 1 : 0; });
+}
+
 double pmlb_exec_run_resident(plaidml_error* err, plaidml_executable* exec, size_t iters) {
   return ffiWrap<double>(err, 0.0, [&] { return exec->exec->runResident(iters); });
 }

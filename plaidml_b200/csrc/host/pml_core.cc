@@ -250,6 +250,15 @@ std::string Settings::get(const std::string& key) {
   throw std::runtime_error("Unknown setting: " + key);
 }
 
+std::string Settings::getOr(const std::string& key, const std::string& fallback) {
+  const char* env = std::getenv(key.c_str());
+  if (env) return env;
+  for (const auto& kv : kvs_) {
+    if (kv.first == key) return kv.second;
+  }
+  return fallback;
+}
+
 void Settings::set(const std::string& key, const std::string& value) {
   bool found = false;
   for (auto& kv : kvs_) {

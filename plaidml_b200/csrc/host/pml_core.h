@@ -93,6 +93,7 @@ class Settings {
  public:
   static Settings& instance();
   std::string get(const std::string& key);  // throws if unset
+  std::string getOr(const std::string& key, const std::string& fallback);
   void set(const std::string& key, const std::string& value);
   std::vector<std::pair<std::string, std::string>> all();
   void load();

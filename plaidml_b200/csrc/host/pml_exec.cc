@@ -1200,6 +1200,8 @@ Executable::Executable(std::shared_ptr<Program> program, int device) : prog_(std
 Executable::~Executable() {
   cudaSetDevice(device_);
   if (stream_) cudaStreamSynchronize(stream_);
+  if (graphExec_) cudaGraphExecDestroy(graphExec_);
+  if (graph_) cudaGraphDestroy(graph_);
   for (Step& s : steps_) pmlb_plan_free(s.plan);
   if (arena_) cudaFree(arena_);
   if (flush_) cudaFree(flush_);
@@ -1209,11 +1211,62 @@ Executable::~Executable() {
   if (stream_) cudaStreamDestroy(stream_);
 }
 
-void Executable::enqueueSteps() {
+void Executable::launchStepsDirect() {
   for (Step& s : steps_) {
     const pmlb_status rc = s.launch(stream_);
     if (rc != PMLB_OK) throw std::runtime_error("Kernel step '" + s.kernel + " " + s.detail + "' failed: " + pmlb_last_error());
   }
+}
+
+// Records the kernel sequence once; the same launches, replayed by the driver without the
+// per-launch host work (tensor-map encoding, attribute calls, argument marshalling).  Any
+// failure leaves the executable on direct launches.
+void Executable::captureGraph() {
+  graphState_ = 2;
+  if (cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  bool ok = true;
+  for (Step& s : steps_) {
+    if (s.launch(stream_) != PMLB_OK) {
+      ok = false;
+      break;
+    }
+  }
+  cudaGraph_t g = nullptr;
+  const cudaError_t endErr = cudaStreamEndCapture(stream_, &g);
+  if (!ok || endErr != cudaSuccess || g == nullptr) {
+    if (g) cudaGraphDestroy(g);
+    cudaGetLastError();
+    return;
+  }
+  cudaGraphExec_t exec = nullptr;
+  if (cudaGraphInstantiate(&exec, g, 0) != cudaSuccess || exec == nullptr) {
+    cudaGraphDestroy(g);
+    cudaGetLastError();
+    return;
+  }
+  graph_ = g;
+  graphExec_ = exec;
+  graphState_ = 1;
+}
+
+void Executable::enqueueSteps() {
+  ++passes_;
+  if (graphState_ == 0 && passes_ >= 2) {
+    const bool wanted = steps_.size() >= 2 && Settings::instance().getOr("PLAIDML_CUDA_GRAPH", "1") != "0";
+    if (wanted) {
+      captureGraph();
+    } else {
+      graphState_ = 2;
+    }
+  }
+  if (graphState_ == 1) {
+    cudaCheck(cudaGraphLaunch(graphExec_, stream_), "cudaGraphLaunch");
+    return;
+  }
+  launchStepsDirect();
 }
 
 void Executable::checkStatus() {

@@ -46,6 +46,7 @@ class Executable {
   double timeSteps(size_t iters, bool flushL2);
   std::string describe() const;
   size_t launchCount() const;
+  bool usesGraph() const { return graphState_ == 1; }
   void* outputDevicePtr(size_t index, size_t* nbytes) const;
   cudaStream_t stream() const { return stream_; }
   const Program& program() const { return *prog_; }
@@ -53,6 +54,8 @@ class Executable {
  private:
   friend class Planner;
   void enqueueSteps();
+  void launchStepsDirect();
+  void captureGraph();
   void checkStatus();
 
   std::shared_ptr<Program> prog_;
@@ -66,6 +69,12 @@ class Executable {
   std::vector<Step> steps_;
   int* status_ = nullptr;          // device word shared by all tensor-core plans
   bool inputsResident_ = false;
+  // The kernel sequence as a CUDA graph: captured on the second pass (the first one has done every
+  // one-time host-side set-up), launched as one node list afterwards.  0 = not tried, 1 = in use, 2 = off.
+  int graphState_ = 0;
+  size_t passes_ = 0;
+  cudaGraph_t graph_ = nullptr;
+  cudaGraphExec_t graphExec_ = nullptr;
 };
 
 // Device ids follow the reference's pattern name(-name)*.N (pmlc/rt/device_id.cc:13-38).

@@ -33,6 +33,11 @@ class Executable(ForeignObject):
     def launch_count(self) -> int:
         return ffi_call(lib.pmlb_exec_launch_count, self.as_ptr())
 
+    @property
+    def uses_graph(self) -> bool:
+        """True once passes replay a captured CUDA graph of the kernel sequence."""
+        return bool(ffi_call(lib.pmlb_exec_uses_graph, self.as_ptr()))
+
     def run_resident(self, iters: int = 1) -> float:
         """Mean milliseconds per iteration of the kernel sequence on device-resident inputs."""
         return ffi_call(lib.pmlb_exec_run_resident, self.as_ptr(), iters)

@@ -83,3 +83,46 @@ def job_throughput(dist, units_this_rank: float, seconds_this_rank: float, devic
     units = sum_over_ranks(dist, units_this_rank, device)
     seconds = max_over_ranks(dist, seconds_this_rank, device)
     return units / seconds
+
+
+# ---------------------------------------------------------------------------- gathered outputs
+#
+# Outputs stay sharded unless the caller asks for the whole tensor: then one all-gather of equal
+# row slices puts every rank's rows on every rank (NCCL over NVLink when the tensors are on GPUs).
+
+def all_gather_rows(dist, local):
+    """`local` = this rank's [rows, ...] torch tensor (every rank the same shape); returns the
+    [world * rows, ...] tensor holding rank 0's rows, then rank 1's, ...  One collective."""
+    import torch
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return local.clone()
+    world = dist.get_world_size()
+    out = torch.empty((world * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, local.contiguous())
+    return out
+
+
+class _DeviceSpan:
+    """A device address range as an object torch can adopt (CUDA array interface, version 3)."""
+
+    def __init__(self, ptr: int, nbytes: int, stream: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "stream": stream or 1}
+
+
+def output_tensor(executable, index: int = 0):
+    """Output `index` of an executable as a flat uint8 torch tensor over the executable's own device
+    memory (no copy; valid while the executable lives and until its next run overwrites it)."""
+    import torch
+    ptr, nbytes = executable.output_device_ptr(index)
+    return torch.as_tensor(_DeviceSpan(ptr, nbytes, executable.stream), device="cuda")
+
+
+def gather_output(dist, executable, index: int = 0):
+    """All ranks' copies of output `index` (sharded along its first dimension), concatenated in rank
+    order on every rank: a uint8 tensor of world x nbytes.  The caller views it with the output's
+    element type.  The executable's stream is synchronised first."""
+    import torch
+    local = output_tensor(executable, index)
+    torch.cuda.current_stream().synchronize()
+    return all_gather_rows(dist, local.reshape(1, -1)).reshape(-1)

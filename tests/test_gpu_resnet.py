@@ -61,6 +61,10 @@ def test_resnet50_logits_match_oracle():
     img = g.uniform(0, 1, size=(batch, 224, 224, 3)).astype(np.float32)
     x_bits = f32_to_bf16_bits(img)
     logits = runner.run([x_bits])[0]
+    assert not runner.executable.uses_graph                 # first pass: direct launches
+    again = runner.run([x_bits])[0]                          # second pass: captured and replayed as a CUDA graph
+    assert runner.executable.uses_graph
+    np.testing.assert_array_equal(again, logits)
     ref = oracle_resnet50(bf16_bits_to_f32(x_bits), weights)
     err = max_rel(logits, ref)
     print("resnet50 logits max-rel error:", err, "steps:", len(lines))

@@ -59,6 +59,10 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         units = shard.sum_over_ranks(dist, float(hi - lo))
         rate = shard.job_throughput(dist, float(hi - lo), 1.0 + rank)
         np.save(os.path.join(out_dir, f"t{rank}.npy"), np.array([slowest, units, rate, lo, hi]))
+        # gathered output: equal slices only (pad the ragged last shard as the caller would)
+        mine = torch.full((3, 4), float(rank), dtype=torch.float32)
+        whole = shard.all_gather_rows(dist, mine)
+        np.save(os.path.join(out_dir, f"g{rank}.npy"), whole.numpy())
     finally:
         dist.destroy_process_group()
 
@@ -77,6 +81,8 @@ def test_two_gloo_ranks_tile_the_unsharded_result(tmp_path):
         slowest, units, rate, lo, hi = np.load(tmp_path / f"t{r}.npy")
         assert slowest == 2.0 and units == m and rate == m / 2.0
         assert (lo, hi) == shard.row_slice(m, r, world)
+        gathered = np.load(tmp_path / f"g{r}.npy")
+        assert gathered.shape == (6, 4) and (gathered[:3] == 0).all() and (gathered[3:] == 1).all()
 
 
 def test_single_process_reductions_are_identities():
@@ -84,4 +90,6 @@ def test_single_process_reductions_are_identities():
     assert shard.sum_over_ranks(None, 3.5) == 3.5
     assert shard.job_throughput(None, 10.0, 2.0) == 5.0
     shard.barrier(None)
+    t = torch.arange(6.0).reshape(2, 3)
+    assert torch.equal(shard.all_gather_rows(None, t), t)
     assert isinstance(torch.__version__, str)
