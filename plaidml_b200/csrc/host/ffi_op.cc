@@ -738,9 +738,506 @@ VarPtr opElu(const VarPtr& value) {
   return exprValue(intrinsic("select", {intrinsic("cmp_lt", {I, litFloat(0.0)}), castTo(neg, shapeOf(I).dtype), I}));
 }
 
+// ------------------------------------------------------------------ small value builders
+
+VarPtr intVar(int64_t v) {
+  auto n = std::make_shared<VarNode>();
+  n->kind = VarNode::Int;
+  n->i = v;
+  return n;
+}
+
+VarPtr noneVar() { return std::make_shared<VarNode>(); }
+
+VarPtr tupleVar(std::vector<VarPtr> elts) {
+  auto n = std::make_shared<VarNode>();
+  n->kind = VarNode::Tuple;
+  n->tuple = std::move(elts);
+  return n;
+}
+
+VarPtr intTupleVar(const std::vector<int64_t>& v) {
+  std::vector<VarPtr> e;
+  for (int64_t x : v) e.push_back(intVar(x));
+  return tupleVar(std::move(e));
+}
+
+ExprPtr binary(const char* fn, const ExprPtr& a, const ExprPtr& b) { return intrinsic(fn, {a, b}); }
+
+// 0 / 1 in the tensor's own type: select(I == 0, 0, 1) (plaidml/op/lib/ops.cc:459-461)
+ExprPtr asZeroOne(const ExprPtr& I, pml::DType dt) {
+  return intrinsic("select", {binary("cmp_eq", I, litInt(0)), castTo(litInt(0), dt), castTo(litInt(1), dt)});
+}
+
+// plaidml/op/lib/ops.cc:450-503: all = product of the 0/1 image, any = its sum compared with 0; u8 results
+VarPtr opAllAny(const VarPtr& value, bool all) {
+  const char* name = all ? "all" : "any";
+  const auto& args = asTuple(value, name);
+  if (args.size() != 3) throw std::runtime_error(std::string(name) + " expects 3 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const pml::TensorShape shape = shapeOf(I);
+  ExprPtr B = asZeroOne(I, shape.dtype);
+  if (shape.rank() == 0 || (args[1]->kind == VarNode::Tuple && args[1]->tuple.empty())) {
+    return exprValue(castTo(B, pml::DType::ui8));
+  }
+  AggAxes ax(shape, args[1], asBool(args[2]));
+  ExprPtr R = contraction(all ? pml::AggKind::mul : pml::AggKind::add, pml::ComboKind::none, ax.dstDims, ax.dstIdxs,
+                          {{B, ax.srcIdxs}}, {}, name);
+  if (!all) R = asZeroOne(R, shape.dtype);
+  return exprValue(castTo(R, pml::DType::ui8));
+}
+
+// plaidml/op/lib/ops.cc:505-521: the maximum, then the largest flattened index whose element equals it
+VarPtr opArgmax(const VarPtr& value) {
+  const auto& args = asTuple(value, "argmax");
+  if (args.size() != 2) throw std::runtime_error("argmax expects 2 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const pml::TensorShape shape = shapeOf(I);
+  AggAxes ax(shape, args[1], false);
+  ExprPtr M = contraction(pml::AggKind::max, pml::ComboKind::none, ax.dstDims, ax.dstIdxs, {{I, ax.srcIdxs}}, {}, "argmax");
+  std::vector<ExprPtr> ixArgs;
+  std::vector<PolyPtr> redIdxs;
+  std::vector<int64_t> redDims;
+  for (size_t a : ax.axes) {
+    redIdxs.push_back(ax.srcIdxs[a]);
+    redDims.push_back(shape.sizes[a]);
+  }
+  // index(dims, 0): a tensor of shape `reduce dims` whose elements are their own coordinate along axis 0
+  ixArgs.push_back(litInt(0));
+  for (int64_t d : redDims) ixArgs.push_back(litInt(d));
+  ExprPtr IX = intrinsic("index", ixArgs);
+  ExprPtr AM = contraction(pml::AggKind::max, pml::ComboKind::cond, ax.dstDims, ax.dstIdxs,
+                           {{I, ax.srcIdxs}, {M, ax.dstIdxs}, {IX, redIdxs}}, {}, "argmax");
+  return exprValue(castTo(AM, pml::DType::ui32));
+}
+
+// plaidml/op/lib/ops.cc:523-544
+VarPtr opBinaryCrossentropy(const VarPtr& value) {
+  const auto& args = asTuple(value, "binary_crossentropy");
+  if (args.size() != 3) throw std::runtime_error("binary_crossentropy expects 3 arguments");
+  ExprPtr T = asTensor(args[0]);
+  if (args[2]->kind != VarNode::Float && args[2]->kind != VarNode::Int) throw std::runtime_error("Expected a float argument");
+  const double eps = args[2]->kind == VarNode::Float ? args[2]->f : static_cast<double>(args[2]->i);
+  if (eps < 0. || eps >= 0.5) {
+    throw std::runtime_error("The epsilon used in binary_crossentropy must be between 0 and 0.5, received " + std::to_string(eps));
+  }
+  auto lo = std::make_shared<VarNode>();
+  lo->kind = VarNode::Float;
+  lo->f = eps;
+  auto hi = std::make_shared<VarNode>();
+  hi->kind = VarNode::Float;
+  hi->f = 1. - eps;
+  ExprPtr P = opClip(tupleVar({args[1], lo, hi}))->expr;
+  // -T * log(P) - (1 - T) * log(1 - P)
+  ExprPtr a = binary("mul", intrinsic("neg", {T}), intrinsic("log", {P}));
+  ExprPtr b = binary("mul", binary("sub", litInt(1), T), intrinsic("log", {binary("sub", litInt(1), P)}));
+  return exprValue(binary("sub", a, b));
+}
+
+// plaidml/op/lib/ops.cc:546-584: input dim i feeds output dim axes[i]; size-1 input dims repeat
+VarPtr opBroadcast(const VarPtr& value) {
+  const auto& args = asTuple(value, "broadcast");
+  if (args.size() != 3) throw std::runtime_error("PlaidML broadcast op expects 3 arguments (received " + std::to_string(args.size()) + ")");
+  ExprPtr I = asTensor(args[0]);
+  const pml::TensorShape shape = shapeOf(I);
+  const std::vector<int64_t> target = asIntTuple(args[1]);
+  const std::vector<int64_t> axes = asIntTuple(args[2]);
+  if (shape.rank() != axes.size()) {
+    throw std::runtime_error("Mismatched broadcast axes (received " + std::to_string(axes.size()) +
+                             " broadcast axes for input tensor of rank " + std::to_string(shape.rank()) + ")");
+  }
+  std::vector<PolyPtr> oIdx, iIdx;
+  for (size_t i = 0; i < target.size(); ++i) oIdx.push_back(newIndex());
+  for (size_t i = 0; i < axes.size(); ++i) {
+    if (shape.sizes[i] == 1) {
+      iIdx.push_back(polyLit(0));
+    } else {
+      if (axes[i] < 0 || axes[i] >= static_cast<int64_t>(target.size())) throw std::runtime_error("broadcast axis out of range");
+      iIdx.push_back(oIdx[axes[i]]);
+    }
+  }
+  return exprValue(contraction(pml::AggKind::assign, pml::ComboKind::none, target, oIdx, {{I, iIdx}}, {}, "broadcast"));
+}
+
+// plaidml/op/lib/ops.cc:608-668: each input assigned into its span of a zero-filled result, results added
+ExprPtr concatExprs(const std::vector<ExprPtr>& tensors, int64_t rawAxis) {
+  if (tensors.empty()) throw std::runtime_error("The concatenate op requires at least one input tensor");
+  const pml::TensorShape first = shapeOf(tensors[0]);
+  const size_t nd = first.rank();
+  const size_t axis = static_cast<size_t>(normalizeAxis(rawAxis, nd, "concatenate"));
+  std::vector<int64_t> dims = first.sizes;
+  std::vector<int64_t> offsets;
+  int64_t total = 0;
+  for (const ExprPtr& t : tensors) {
+    const pml::TensorShape ts = shapeOf(t);
+    if (ts.rank() != nd) throw std::runtime_error("concatenate: ranks differ");
+    for (size_t d = 0; d < nd; ++d) {
+      if (d != axis && ts.sizes[d] != first.sizes[d]) throw std::runtime_error("concatenate: bind dims mismatch off the axis");
+    }
+    offsets.push_back(total);
+    total += ts.sizes[axis];
+  }
+  dims[axis] = total;
+  ExprPtr result;
+  for (size_t t = 0; t < tensors.size(); ++t) {
+    std::vector<PolyPtr> iIdx, oIdx;
+    for (size_t d = 0; d < nd; ++d) iIdx.push_back(newIndex(d == axis ? "a" : "n" + std::to_string(d)));
+    oIdx = iIdx;
+    oIdx[axis] = iIdx[axis] + offsets[t];
+    ExprPtr R = contraction(pml::AggKind::assign, pml::ComboKind::none, dims, oIdx, {{tensors[t], iIdx}}, {}, "concatenate");
+    result = result ? binary("add", result, R) : R;
+  }
+  return result;
+}
+
+VarPtr opConcatenate(const VarPtr& value) {
+  const auto& args = asTuple(value, "concatenate");
+  if (args.size() != 2) throw std::runtime_error("concatenate expects 2 arguments");
+  std::vector<ExprPtr> tensors;
+  for (const VarPtr& v : asTuple(args[0], "concatenate tensors")) tensors.push_back(asTensor(v));
+  return exprValue(concatExprs(tensors, asInt(args[1])));
+}
+
+// plaidml/op/lib/ops.cc:1469-1488
+VarPtr opCumprod(const VarPtr& value) {
+  const auto& args = asTuple(value, "cumprod");
+  if (args.size() != 2) throw std::runtime_error("cumprod expects 2 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const pml::TensorShape shape = shapeOf(I);
+  const int64_t axis = normalizeAxis(asInt(args[1]), shape.rank(), "cumprod");
+  std::vector<PolyPtr> oIdx, iIdx;
+  for (size_t i = 0; i < shape.rank(); ++i) oIdx.push_back(newIndex());
+  iIdx = oIdx;
+  PolyPtr k = newIndex("k");
+  iIdx[axis] = oIdx[axis] - k;
+  return exprValue(contraction(pml::AggKind::mul, pml::ComboKind::none, shape.sizes, oIdx, {{I, iIdx}},
+                               {{k, shape.sizes[axis]}}, "cumprod"));
+}
+
+double asFloat(const VarPtr& v) {
+  if (v->kind == VarNode::Float) return v->f;
+  if (v->kind == VarNode::Int) return static_cast<double>(v->i);
+  throw std::runtime_error("Expected a float argument");
+}
+
+// plaidml/op/lib/ops.cc:1586-1685: CONSTANT (0) pads with a value through the contraction's
+// initial tensor, EDGE (1) repeats the border by concatenating slices; SYMMETRIC / REFLECT are
+// unimplemented there too
+VarPtr opExplicitPadding(const VarPtr& value) {
+  const auto& args = asTuple(value, "explicit_padding");
+  if (args.size() < 5) throw std::runtime_error("explicit_padding expects 5 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const pml::TensorShape shape = shapeOf(I);
+  const std::vector<int64_t> lo = asIntTuple(args[1]), hi = asIntTuple(args[2]);
+  const int64_t mode = asInt(args[3]);
+  const size_t nd = shape.rank();
+  if (lo.size() != nd) {
+    throw std::runtime_error("Inconsistent shapes in explicit_padding op (received an input tensor with " + std::to_string(nd) +
+                             " dims, but received lower padding for " + std::to_string(lo.size()) + " dims.)");
+  }
+  if (hi.size() != nd) {
+    throw std::runtime_error("Inconsistent shapes in explicit_padding op (received an input tensor with " + std::to_string(nd) +
+                             " dims, but received higher padding for " + std::to_string(hi.size()) + " dims.)");
+  }
+  if (mode == 0) {
+    std::vector<PolyPtr> iIdx, oIdx;
+    std::vector<int64_t> oDims;
+    for (size_t d = 0; d < nd; ++d) {
+      iIdx.push_back(newIndex("x" + std::to_string(d)));
+      oIdx.push_back(iIdx[d] + lo[d]);
+      oDims.push_back(shape.sizes[d] + lo[d] + hi[d]);
+    }
+    ExprPtr O = contraction(pml::AggKind::assign, pml::ComboKind::none, oDims, oIdx, {{I, iIdx}}, {}, "explicit_padding");
+    O->init = asTensor(args[4]);
+    pml::Evaluator local;
+    local.verify(O);
+    return exprValue(O);
+  }
+  if (mode == 1) {
+    ExprPtr O = I;
+    for (size_t d = 0; d < nd; ++d) {
+      const pml::TensorShape cur = shapeOf(O);
+      std::vector<ExprPtr> parts;
+      for (int side = 0; side < 2; ++side) {
+        const int64_t width = side == 0 ? lo[d] : hi[d];
+        if (side == 1) parts.push_back(O);
+        if (width <= 0) continue;
+        std::vector<PolyPtr> dst, src;
+        std::vector<int64_t> dims = cur.sizes;
+        for (size_t e = 0; e < nd; ++e) dst.push_back(newIndex());
+        src = dst;
+        src[d] = polyLit(side == 0 ? 0 : cur.sizes[d] - 1);
+        dims[d] = width;
+        parts.push_back(contraction(pml::AggKind::assign, pml::ComboKind::none, dims, dst, {{O, src}}, {}, "explicit_padding"));
+      }
+      O = parts.size() == 1 ? parts[0] : concatExprs(parts, static_cast<int64_t>(d));
+    }
+    return exprValue(O);
+  }
+  if (mode == 2 || mode == 3) throw std::runtime_error("Unimplemented padding mode: " + std::string(mode == 2 ? "SYMMETRIC" : "REFLECT"));
+  throw std::runtime_error("Unrecognized padding mode");
+}
+
+// plaidml/op/lib/ops.cc:1803-1820
+VarPtr opHardSigmoid(const VarPtr& value) {
+  const auto& args = asTuple(value, "hard_sigmoid");
+  if (args.size() != 2) throw std::runtime_error("hard_sigmoid expects 2 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const double slope = asFloat(args[1]);
+  if (slope <= 0) throw std::runtime_error("hard_sigmoid expects positive slope, received " + std::to_string(slope));
+  const double hiCusp = 1. / (2. * slope);
+  const pml::DType dt = shapeOf(I).dtype;
+  ExprPtr mid = binary("add", binary("mul", litFloat(slope), I), litFloat(0.5));
+  ExprPtr upper = intrinsic("select", {binary("cmp_gt", I, litFloat(hiCusp)), castTo(litFloat(1.), dt), mid});
+  return exprValue(intrinsic("select", {binary("cmp_lt", I, litFloat(-hiCusp)), castTo(litFloat(0.), dt), upper}));
+}
+
+// plaidml/op/lib/ops.cc:129-160,1920-1940: I / (alpha * windowed sum of squares + epsilon) ^ beta
+VarPtr opLrn(const VarPtr& value) {
+  const auto& args = asTuple(value, "lrn");
+  if (args.size() != 6) throw std::runtime_error("lrn expects 6 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const pml::TensorShape shape = shapeOf(I);
+  const std::vector<int64_t> widths = asIntTuple(args[1]);
+  std::set<int64_t> axes;
+  for (int64_t a : asIntTuple(args[2])) axes.insert(normalizeAxis(a, shape.rank(), "lrn"));
+  if (axes.size() != widths.size()) {
+    throw std::runtime_error("Inconsistent axis count and window width count in LRN (" + std::to_string(axes.size()) + " vs " +
+                             std::to_string(widths.size()) + ")");
+  }
+  const double alpha = asFloat(args[3]), beta = asFloat(args[4]), eps = asFloat(args[5]);
+  std::vector<PolyPtr> dst, src;
+  for (size_t d = 0; d < shape.rank(); ++d) dst.push_back(newIndex());
+  src = dst;
+  std::vector<Cons> cons;
+  size_t w = 0;
+  for (int64_t a : axes) {
+    PolyPtr win = newIndex();
+    cons.push_back({win, widths[w]});
+    src[a] = dst[a] + win - (widths[w] / 2);
+    ++w;
+  }
+  ExprPtr sq = binary("mul", I, I);
+  ExprPtr sum = contraction(pml::AggKind::add, pml::ComboKind::none, shape.sizes, dst, {{sq, src}}, cons, "lrn");
+  ExprPtr denom = binary("pow", binary("add", binary("mul", litFloat(alpha), sum), litFloat(eps)), litFloat(beta));
+  return exprValue(binary("div", I, denom));
+}
+
+// plaidml/op/lib/ops.cc:2469-2503
+VarPtr opMvn(const VarPtr& value) {
+  const auto& args = asTuple(value, "mvn");
+  if (args.size() != 6) throw std::runtime_error("mvn expects 6 arguments");
+  ExprPtr I = asTensor(args[0]);
+  VarPtr axes = args[1];
+  const bool normVar = asBool(args[2]);
+  const double eps = asFloat(args[3]);
+  const bool acrossChannels = asBool(args[4]);
+  const std::string layout = asStr(args[5]);
+  if (axes->kind == VarNode::None) {
+    if (layout.empty()) throw std::runtime_error("Either axes or layout must be specified for MVN");
+    std::vector<int64_t> raw;
+    for (size_t i = 0; i < layout.size(); ++i) {
+      if (layout[i] == 'N') continue;
+      if (layout[i] == 'C' && !acrossChannels) continue;
+      raw.push_back(static_cast<int64_t>(i));
+    }
+    axes = intTupleVar(raw);
+  }
+  ExprPtr R = binary("sub", I, opMean(tupleVar({args[0], axes, intVar(1)}))->expr);
+  if (normVar) {
+    ExprPtr stdev = intrinsic("sqrt", {opVariance(tupleVar({args[0], axes, intVar(1)}))->expr});
+    ExprPtr floor = castTo(litFloat(eps), shapeOf(I).dtype);
+    R = binary("div", R, intrinsic("select", {binary("cmp_lt", stdev, floor), floor, stdev}));
+  }
+  return exprValue(R);
+}
+
+// plaidml/op/lib/ops.cc:2505-2530: sqrt(sum(I^2, axes, keepdims) (+ | max) epsilon); eps_mode 0 = ADD, 1 = MAX
+VarPtr opL2norm(const VarPtr& value) {
+  const auto& args = asTuple(value, "l2norm");
+  if (args.size() != 4) throw std::runtime_error("norm expects 4 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const double eps = asFloat(args[2]);
+  const int64_t mode = asInt(args[3]);
+  ExprPtr X = reduceOp(tupleVar({exprValue(binary("mul", I, I)), intTupleVar(asIntTuple(args[1])), intVar(1)}),
+                       pml::AggKind::add, "sum")->expr;
+  if (mode == 0) {
+    X = binary("add", X, litFloat(eps));
+  } else if (mode == 1) {
+    ExprPtr e = castTo(litFloat(eps), shapeOf(X).dtype);
+    X = intrinsic("select", {binary("cmp_lt", X, e), e, X});
+  } else {
+    throw std::runtime_error("Unrecognized eps_mode in l2norm op");
+  }
+  return exprValue(intrinsic("sqrt", {X}));
+}
+
+// plaidml/op/lib/ops.cc:2782-2816: numpy-style repeat of every element along one axis
+VarPtr opRepeat(const VarPtr& value) {
+  const auto& args = asTuple(value, "repeat");
+  if (args.size() != 3) throw std::runtime_error("PlaidML repeat op expects 3 arguments (received " + std::to_string(args.size()) + ")");
+  ExprPtr I = asTensor(args[0]);
+  if (args[1]->kind != VarNode::Int && args[1]->kind != VarNode::Dim) {
+    throw std::runtime_error("Repeat only accepts int or TensorDim for repeats parameter");
+  }
+  const int64_t reps = asInt(args[1]);
+  const pml::TensorShape shape = shapeOf(I);
+  const size_t axis = static_cast<size_t>(normalizeAxis(asInt(args[2]), shape.rank(), "repeat"));
+  std::vector<PolyPtr> iIdx, oIdx;
+  for (size_t d = 0; d < shape.rank(); ++d) iIdx.push_back(newIndex());
+  oIdx = iIdx;
+  PolyPtr inner = newIndex();
+  oIdx[axis] = reps * iIdx[axis] + inner;
+  std::vector<int64_t> dims = shape.sizes;
+  dims[axis] *= reps;
+  return exprValue(contraction(pml::AggKind::assign, pml::ComboKind::none, dims, oIdx, {{I, iIdx}}, {{inner, reps}}, "repeat"));
+}
+
+// plaidml/op/lib/ops.cc:3454-3487: numpy-style tile
+VarPtr opTile(const VarPtr& value) {
+  const auto& args = asTuple(value, "tile");
+  if (args.size() != 2) throw std::runtime_error("Tile expects 2 arguments");
+  ExprPtr I = asTensor(args[0]);
+  std::vector<int64_t> reps = asIntTuple(args[1]);
+  const pml::TensorShape shape = shapeOf(I);
+  if (reps.empty()) throw std::runtime_error("No tiling factors provided to tile operation");
+  while (reps.size() < shape.rank()) reps.push_back(1);
+  if (reps.size() > shape.rank()) throw std::runtime_error("More tiling factors provided to tile operation than tensor dimensions");
+  std::vector<PolyPtr> iIdx, oIdx;
+  std::vector<int64_t> dims;
+  for (size_t d = 0; d < shape.rank(); ++d) {
+    iIdx.push_back(newIndex());
+    oIdx.push_back(shape.sizes[d] * newIndex() + iIdx[d]);
+    dims.push_back(shape.sizes[d] * reps[d]);
+  }
+  return exprValue(contraction(pml::AggKind::assign, pml::ComboKind::none, dims, oIdx, {{I, iIdx}}, {}, "tile"));
+}
+
+// plaidml/op/lib/ops.cc:2888-2903: the forward pass is the identity
+VarPtr opScaleGradient(const VarPtr& value) {
+  const auto& args = asTuple(value, "scale_gradient");
+  if (args.size() != 2) throw std::runtime_error("scale_gradient expects 2 arguments");
+  return exprValue(asTensor(args[0]));
+}
+
+// plaidml/op/lib/ops.cc:2917-3042: per axis an integer (the axis disappears) or (start, stop, step)
+// with None defaults and negative values counted from the end
+VarPtr opSlice(const VarPtr& value) {
+  const auto& args = asTuple(value, "slice");
+  if (args.size() != 2) throw std::runtime_error("slice expects 2 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const pml::TensorShape shape = shapeOf(I);
+  const size_t nd = shape.rank();
+  if (nd == 0) return exprValue(I);
+  const auto& slices = asTuple(args[1], "slices");
+  if (slices.size() != nd) {
+    throw std::runtime_error(std::to_string(slices.size()) + " slice axes provided to slice " + std::to_string(nd) + "-dimensional tensor");
+  }
+  std::vector<PolyPtr> oIdx, iIdx;
+  std::vector<int64_t> oDims;
+  for (size_t d = 0; d < nd; ++d) {
+    const VarPtr& sl = slices[d];
+    const int64_t size = shape.sizes[d];
+    if (sl->kind == VarNode::Int) {
+      iIdx.push_back(polyLit(sl->i < 0 ? sl->i + size : sl->i));
+      continue;
+    }
+    if (sl->kind != VarNode::Tuple) throw std::runtime_error("Attempted to define slice with invalid type");
+    if (sl->tuple.size() != 3) {
+      throw std::runtime_error("Attempted to slice with " + std::to_string(sl->tuple.size()) + " entries, 3 required");
+    }
+    const int64_t step = sl->tuple[2]->kind == VarNode::None ? 1 : asInt(sl->tuple[2]);
+    if (step == 0) throw std::runtime_error("Cannot slice with step size 0");
+    int64_t start, stop;
+    if (sl->tuple[0]->kind == VarNode::None) {
+      start = step > 0 ? 0 : size - 1;
+    } else {
+      start = asInt(sl->tuple[0]);
+      if (start < 0) start += size;
+    }
+    if (sl->tuple[1]->kind == VarNode::None) {
+      stop = step > 0 ? size : -1;
+    } else {
+      stop = asInt(sl->tuple[1]);
+      if (stop < 0) stop += size;
+    }
+    const int64_t toCeil = step > 0 ? step - 1 : step + 1;
+    const int64_t count = (stop - start + toCeil) / step;    // truncating division, as the dimension arithmetic does
+    PolyPtr o = newIndex();
+    oIdx.push_back(o);
+    oDims.push_back(count);
+    iIdx.push_back(step * o + start);
+  }
+  return exprValue(contraction(pml::AggKind::assign, pml::ComboKind::none, oDims, oIdx, {{I, iIdx}}, {}, "slice"));
+}
+
+// plaidml/op/lib/ops.cc:2730-2780: YOLO's space-to-depth shuffle (and its inverse) on a 4-d tensor given in
+// `layout` (a permutation of NCHW)
+VarPtr opReorgYolo(const VarPtr& value) {
+  const auto& args = asTuple(value, "reorg_yolo");
+  if (args.size() != 4) throw std::runtime_error("PlaidML reorg_yolo op expects 4 arguments (received " + std::to_string(args.size()) + ")");
+  ExprPtr I = asTensor(args[0]);
+  const int64_t stride = asInt(args[1]);
+  const bool decrease = asBool(args[2]);
+  const std::string layout = asStr(args[3]);
+  const pml::TensorShape shape = shapeOf(I);
+  if (shape.rank() != 4) throw std::runtime_error("PlaidML reorg_yolo op expects I to have 4 dimensions (received " + std::to_string(shape.rank()) + ")");
+  if (layout.size() != 4) throw std::runtime_error("source and target rank mismatch");
+  // position of each of N, C, H, W in the given layout
+  size_t pos[4];
+  const std::string canon = "NCHW";
+  for (size_t i = 0; i < 4; ++i) {
+    const size_t at = layout.find(canon[i]);
+    if (at == std::string::npos) throw std::runtime_error("source and target dims mismatch");
+    pos[i] = at;
+  }
+  const int64_t N = shape.sizes[pos[0]], C = shape.sizes[pos[1]], H = shape.sizes[pos[2]], W = shape.sizes[pos[3]];
+  if (stride <= 0) throw std::runtime_error("reorg_yolo expects a positive stride");
+  PolyPtr b = newIndex("b"), i = newIndex("i"), j = newIndex("j"), k = newIndex("k"), x = newIndex("x"), y = newIndex("y");
+  PolyPtr h = stride * j + y, w = stride * i + x;
+  auto place = [&](PolyPtr n_, PolyPtr c_, PolyPtr h_, PolyPtr w_) {
+    std::vector<PolyPtr> v(4);
+    v[pos[0]] = n_; v[pos[1]] = c_; v[pos[2]] = h_; v[pos[3]] = w_;
+    return v;
+  };
+  auto placeDims = [&](int64_t n_, int64_t c_, int64_t h_, int64_t w_) {
+    std::vector<int64_t> v(4);
+    v[pos[0]] = n_; v[pos[1]] = c_; v[pos[2]] = h_; v[pos[3]] = w_;
+    return v;
+  };
+  const std::vector<Cons> cons = {{y, stride}, {x, stride}};
+  if (decrease) {
+    const int64_t cOut = C / (stride * stride);
+    PolyPtr c = k + cOut * (x + stride * y);
+    return exprValue(contraction(pml::AggKind::assign, pml::ComboKind::none, placeDims(N, cOut, H * stride, W * stride),
+                                 place(b, k, h, w), {{I, place(b, c, j, i)}}, cons, "reorg_yolo"));
+  }
+  const int64_t cOut = C * stride * stride;
+  PolyPtr c = k + C * (x + stride * y);
+  return exprValue(contraction(pml::AggKind::assign, pml::ComboKind::none, placeDims(N, cOut, H / stride, W / stride),
+                               place(b, c, j, i), {{I, place(b, k, h, w)}}, cons, "reorg_yolo"));
+}
+
 const std::map<std::string, std::function<VarPtr(const VarPtr&)>>& registry() {
   static const std::map<std::string, std::function<VarPtr(const VarPtr&)>> ops = {
       {"abs", [](const VarPtr& v) { return unary(v, "abs"); }},
+      {"all", [](const VarPtr& v) { return opAllAny(v, true); }},
+      {"any", [](const VarPtr& v) { return opAllAny(v, false); }},
+      {"argmax", opArgmax},
+      {"binary_crossentropy", opBinaryCrossentropy},
+      {"broadcast", opBroadcast},
+      {"concatenate", opConcatenate},
+      {"cumprod", opCumprod},
+      {"explicit_padding", opExplicitPadding},
+      {"hard_sigmoid", opHardSigmoid},
+      {"l2norm", opL2norm},
+      {"lrn", opLrn},
+      {"mvn", opMvn},
+      {"reorg_yolo", opReorgYolo},
+      {"repeat", opRepeat},
+      {"scale_gradient", opScaleGradient},
+      {"slice", opSlice},
+      {"tile", opTile},
       {"clip", opClip},
       {"convolution", opConvolution},
       {"cumsum", opCumsum},

@@ -166,3 +166,95 @@ def elu(x, alpha):
 
 def spatial_padding(x, lo_pads, hi_pads, data_layout=TensorLayout.NXC):
     return op("spatial_padding", [x, list(lo_pads), list(hi_pads), int(data_layout)]).as_tensor()
+
+
+# ---- the rest of the contraction-built operations of plaidml/op/__init__.py (same names and arguments)
+
+class EpsMode(enum.IntEnum):
+    ADD = 0
+    MAX = 1
+
+
+class PadMode(enum.IntEnum):
+    CONSTANT = 0
+    EDGE = 1
+    REFLECT = 2
+    SYMMETRIC = 3
+
+
+def all(x, axis=None, keepdims=False):
+    return op("all", [x, axis, keepdims]).as_tensor()
+
+
+def any(x, axis=None, keepdims=False):
+    return op("any", [x, axis, keepdims]).as_tensor()
+
+
+def argmax(x, axis=-1):
+    return op("argmax", [x, axis]).as_tensor()
+
+
+def binary_crossentropy(targets, preds, epsilon):
+    return op("binary_crossentropy", [targets, preds, float(epsilon)]).as_tensor()
+
+
+def broadcast(x, result_shape, bcast_axes):
+    return op("broadcast", [x, list(result_shape), list(bcast_axes)]).as_tensor()
+
+
+def concatenate(tensors, axis=-1):
+    return op("concatenate", [list(tensors), axis]).as_tensor()
+
+
+def cumprod(x, axis):
+    return op("cumprod", [x, axis]).as_tensor()
+
+
+def explicit_padding(x, lo_pads, hi_pads, mode=PadMode.CONSTANT, padval=0.0):
+    return op("explicit_padding", [x, list(lo_pads), list(hi_pads), int(mode), padval]).as_tensor()
+
+
+def hard_sigmoid(x, slope):
+    return op("hard_sigmoid", [x, float(slope)]).as_tensor()
+
+
+def l2norm(x, axes, epsilon, eps_mode=EpsMode.ADD):
+    return op("l2norm", [x, list(axes), float(epsilon), int(eps_mode)]).as_tensor()
+
+
+def lrn(x, window_size, axes=(-1,), alpha=1.0, beta=0.5, epsilon=1.0):
+    return op("lrn", [x, list(window_size), list(axes), float(alpha), float(beta), float(epsilon)]).as_tensor()
+
+
+def mvn(x, axes=None, normalize_variance=True, epsilon=1e-9, across_channels=True, layout=""):
+    return op("mvn", [x, None if axes is None else list(axes), normalize_variance, float(epsilon), across_channels,
+                      layout]).as_tensor()
+
+
+def reorg_yolo(x, stride, decrease, layout="NCHW"):
+    return op("reorg_yolo", [x, stride, decrease, layout]).as_tensor()
+
+
+def repeat(x, repeats, axis):
+    return op("repeat", [x, repeats, axis]).as_tensor()
+
+
+def scale_gradient(x, scale=-1.0):
+    return op("scale_gradient", [x, float(scale)]).as_tensor()
+
+
+def slice_of(x, slices):
+    """`slices`: one entry per axis, an int (the axis disappears) or a Python slice."""
+    packed = []
+    for s in slices:
+        if isinstance(s, int):
+            packed.append(s)
+        elif isinstance(s, slice):
+            packed.append([s.start, s.stop, s.step])
+        else:
+            raise ValueError("Unexpected type {} used to slice tensor".format(type(s)))
+    return op("slice", [x, packed]).as_tensor()
+
+
+def tile(x, n):
+    return op("tile", [x, list(n)]).as_tensor()

@@ -1,0 +1,118 @@
+"""The contraction-built operations of the op library (plaidml/op/lib/ops.cc) run on the GPU and are
+compared with numpy restatements of their definitions."""
+
+import numpy as np
+import pytest
+
+from plaidml_b200 import op
+from plaidml_b200.core import DType, Program
+from plaidml_b200.edsl import Placeholder
+from plaidml_b200.exec import Runner
+from gpu_util import rng
+
+pytestmark = pytest.mark.gpu
+
+
+def run(build, *arrays, dtype=DType.FLOAT32):
+    ins = [Placeholder(dtype, list(a.shape)) for a in arrays]
+    out = build(*ins)
+    outs = out if isinstance(out, (list, tuple)) else [out]
+    res = Runner(Program("op", ins, list(outs)), "cuda.0").run(list(arrays))
+    return res if isinstance(out, (list, tuple)) else res[0]
+
+
+def test_all_any():
+    x = (rng(1).integers(0, 3, size=(3, 4, 5)) > 0).astype(np.float32) * rng(2).standard_normal((3, 4, 5)).astype(np.float32)
+    x[1, :, 2] = 1.0
+    x[2, :, 3] = 0.0
+    np.testing.assert_array_equal(run(lambda X: op.all(X, axis=1), x), np.all(x != 0, axis=1).astype(np.uint8))
+    np.testing.assert_array_equal(run(lambda X: op.any(X, axis=1, keepdims=True), x),
+                                  np.any(x != 0, axis=1, keepdims=True).astype(np.uint8))
+    np.testing.assert_array_equal(run(lambda X: op.any(X), x), np.uint8(1))
+
+
+def test_argmax_takes_the_position_of_the_maximum():
+    x = rng(3).standard_normal((4, 7, 5)).astype(np.float32)
+    np.testing.assert_array_equal(run(lambda X: op.argmax(X, axis=1), x), np.argmax(x, axis=1).astype(np.uint32))
+    np.testing.assert_array_equal(run(lambda X: op.argmax(X), x), np.argmax(x, axis=-1).astype(np.uint32))
+
+
+def test_binary_crossentropy_and_hard_sigmoid():
+    g = rng(4)
+    t = g.integers(0, 2, size=(6, 9)).astype(np.float32)
+    p = g.uniform(0, 1, size=(6, 9)).astype(np.float32)
+    p[0, 0], p[0, 1] = 0.0, 1.0
+    eps = 1e-3
+    pc = np.clip(p, eps, 1 - eps)
+    ref = -t * np.log(pc) - (1 - t) * np.log(1 - pc)
+    np.testing.assert_allclose(run(lambda T, P: op.binary_crossentropy(T, P, eps), t, p), ref, rtol=2e-5, atol=1e-6)
+    x = g.uniform(-5, 5, size=(50,)).astype(np.float32)
+    np.testing.assert_allclose(run(lambda X: op.hard_sigmoid(X, 0.2), x), np.clip(0.2 * x + 0.5, 0, 1), rtol=1e-6, atol=1e-7)
+
+
+def test_broadcast_concatenate_repeat_tile():
+    g = rng(5)
+    a = g.standard_normal((3, 1)).astype(np.float32)
+    np.testing.assert_array_equal(run(lambda A: op.broadcast(A, [2, 3, 5], [1, 2]), a), np.broadcast_to(a, (2, 3, 5)))
+    x = g.standard_normal((2, 3, 4)).astype(np.float32)
+    y = g.standard_normal((2, 5, 4)).astype(np.float32)
+    np.testing.assert_array_equal(run(lambda X, Y: op.concatenate([X, Y, X], axis=1), x, y), np.concatenate([x, y, x], axis=1))
+    np.testing.assert_array_equal(run(lambda X: op.repeat(X, 3, 1), x), np.repeat(x, 3, axis=1))
+    np.testing.assert_array_equal(run(lambda X: op.tile(X, [2, 1, 3]), x), np.tile(x, (2, 1, 3)))
+
+
+def test_cumprod():
+    x = rng(6).uniform(0.5, 1.5, size=(3, 6, 2)).astype(np.float32)
+    np.testing.assert_allclose(run(lambda X: op.cumprod(X, 1), x), np.cumprod(x, axis=1), rtol=1e-5)
+
+
+def test_explicit_padding_constant_and_edge():
+    x = rng(7).standard_normal((2, 3, 4)).astype(np.float32)
+    lo, hi = [0, 1, 2], [1, 0, 3]
+    pads = list(zip(lo, hi))
+    np.testing.assert_array_equal(run(lambda X: op.explicit_padding(X, lo, hi, op.PadMode.CONSTANT, -1.5), x),
+                                  np.pad(x, pads, mode="constant", constant_values=-1.5))
+    np.testing.assert_array_equal(run(lambda X: op.explicit_padding(X, lo, hi, op.PadMode.EDGE), x), np.pad(x, pads, mode="edge"))
+
+
+def test_l2norm_lrn_mvn():
+    g = rng(8)
+    x = g.standard_normal((2, 6, 5, 4)).astype(np.float32)
+    ss = (x * x).sum(axis=(1, 2), keepdims=True)
+    np.testing.assert_allclose(run(lambda X: op.l2norm(X, [1, 2], 1e-2, op.EpsMode.ADD), x), np.sqrt(ss + 1e-2), rtol=1e-5)
+    np.testing.assert_allclose(run(lambda X: op.l2norm(X, [1, 2], 50.0, op.EpsMode.MAX), x), np.sqrt(np.maximum(ss, 50.0)), rtol=1e-5)
+    # local response normalisation over a 3-wide window of the last axis
+    sq = np.pad(x * x, [(0, 0), (0, 0), (0, 0), (1, 1)])
+    win = sq[..., 0:4] + sq[..., 1:5] + sq[..., 2:6]
+    np.testing.assert_allclose(run(lambda X: op.lrn(X, [3], [-1], alpha=0.1, beta=0.75, epsilon=2.0), x),
+                               x / (0.1 * win + 2.0) ** 0.75, rtol=2e-5)
+    mean = x.mean(axis=(2, 3), keepdims=True)
+    std = np.sqrt(((x - mean) ** 2).mean(axis=(2, 3), keepdims=True))
+    np.testing.assert_allclose(run(lambda X: op.mvn(X, across_channels=False, layout="NCHW"), x),
+                               (x - mean) / np.maximum(std, 1e-9), rtol=1e-4, atol=1e-5)
+
+
+def test_reorg_yolo_and_its_inverse():
+    x = rng(9).standard_normal((2, 4, 6, 6)).astype(np.float32)
+    s = 2
+    n, c, h, w = x.shape
+    ref = np.zeros((n, c * s * s, h // s, w // s), np.float32)
+    for yy in range(s):
+        for xx in range(s):
+            ref[:, (xx + yy * s) * c:(xx + yy * s + 1) * c] = x[:, :, yy::s, xx::s]
+    got = run(lambda X: op.reorg_yolo(X, s, False), x)
+    np.testing.assert_array_equal(got, ref)
+    np.testing.assert_array_equal(run(lambda X: op.reorg_yolo(X, s, True), ref), x)
+
+
+def test_slice_of():
+    x = rng(10).standard_normal((5, 6, 7, 8)).astype(np.float32)
+    sl = [slice(None), 1, slice(None, None, -1), slice(1, 7, 2)]
+    np.testing.assert_array_equal(run(lambda X: op.slice_of(X, sl), x), x[:, 1, ::-1, 1:7:2])
+    sl = [slice(-3, None), -1, slice(5, 1, -2), slice(None, -2)]
+    np.testing.assert_array_equal(run(lambda X: op.slice_of(X, sl), x), x[-3:, -1, 5:1:-2, :-2])
+
+
+def test_scale_gradient_is_the_identity_forward():
+    x = rng(11).standard_normal((3, 3)).astype(np.float32)
+    np.testing.assert_array_equal(run(lambda X: op.scale_gradient(X, 0.5) + 0.0, x), x)

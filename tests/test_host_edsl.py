@@ -321,3 +321,26 @@ def test_resnet50_program_builds_with_the_expected_layer_count():
     text = str(prog)
     assert prog.outputs[0].sizes == [2, 1000]
     assert text.count("tile.contract add, mul") >= 53 + 1     # 53 convolutions and the classifier
+
+
+def test_more_op_library_shapes_and_errors():
+    X = Placeholder(DType.FLOAT32, [2, 3, 4, 5])
+    assert shape_str(op.all(X, axis=1)) == "2x4x5xui8"
+    assert shape_str(op.argmax(X, axis=-1)) == "2x3x4xui32"
+    assert op.concatenate([X, X], axis=2).compute_shape().sizes == [2, 3, 8, 5]
+    assert op.explicit_padding(X, [0, 1, 2, 0], [0, 1, 0, 3]).compute_shape().sizes == [2, 5, 6, 8]
+    assert op.slice_of(X, [slice(None), 1, slice(None, None, -1), slice(1, 4, 2)]).compute_shape().sizes == [2, 4, 2]
+    assert op.tile(X, [2, 1, 3]).compute_shape().sizes == [4, 3, 12, 5]
+    assert op.repeat(X, 3, 2).compute_shape().sizes == [2, 3, 12, 5]
+    assert op.reorg_yolo(Placeholder(DType.FLOAT32, [1, 4, 6, 6]), 2, False).compute_shape().sizes == [1, 16, 3, 3]
+    assert op.broadcast(Placeholder(DType.FLOAT32, [3, 1]), [2, 3, 5], [1, 2]).compute_shape().sizes == [2, 3, 5]
+    with pytest.raises(Error, match="0 and 0.5"):
+        op.binary_crossentropy(X, X, 0.7)
+    with pytest.raises(Error, match="positive slope"):
+        op.hard_sigmoid(X, 0.0)
+    with pytest.raises(Error, match="step size 0"):
+        op.slice_of(X, [slice(None, None, 0), 0, 0, 0])
+    with pytest.raises(Error, match="Unimplemented padding mode"):
+        op.explicit_padding(X, [0, 0, 0, 0], [0, 0, 0, 0], op.PadMode.REFLECT)
+    with pytest.raises(Error, match="tiling factors"):
+        op.tile(X, [])
