@@ -974,7 +974,7 @@ VarPtr opExplicitPadding(const VarPtr& value) {
     }
     return exprValue(O);
   }
-  if (mode == 2 || mode == 3) throw std::runtime_error("Unimplemented padding mode: " + std::string(mode == 2 ? "SYMMETRIC" : "REFLECT"));
+  if (mode == 2 || mode == 3) throw std::runtime_error("Unimplemented padding mode: " + std::string(mode == 2 ? "REFLECT" : "SYMMETRIC"));
   throw std::runtime_error("Unrecognized padding mode");
 }
 
