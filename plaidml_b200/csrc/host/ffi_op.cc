@@ -321,13 +321,22 @@ VarPtr opConvolution(const VarPtr& value) {
   std::string name = asStr(args[13]);
   const int64_t derivMode = asInt(args[15]);
   if (name.empty()) name = "conv";
-  if (groups != 1) throw std::runtime_error("Grouped convolutions are not offered by the cuda target's op library");
+  const int groupLayout = static_cast<int>(asInt(args[11]));     // 0 none, 1 separate, 2 in C, 3 in K
+  const int autogroup = static_cast<int>(asInt(args[14]));       // 0 ungrouped, 1 explicit, 2 auto, 3 depthwise
   if (derivMode != 0) throw std::runtime_error("Only the forward convolution is offered by the cuda target's op library");
-  if (!(inputLayout == kNXC && filterLayout == kXCK) && !(inputLayout == kNCX && filterLayout == kKCX)) {
-    throw std::runtime_error("Convolution layouts must be NXC with XCK or NCX with KCX");
+  enum { kGKCX = 4, kXGCK = 5 };
+  const bool nxc = inputLayout == kNXC;
+  if (inputLayout != kNXC && inputLayout != kNCX) throw std::runtime_error("Invalid input_layout");
+  if (filterLayout != kKCX && filterLayout != kXCK && filterLayout != kGKCX && filterLayout != kXGCK) {
+    throw std::runtime_error("Invalid filter_layout");
+  }
+  const bool filterHasG = filterLayout == kGKCX || filterLayout == kXGCK;
+  const bool filterSpatialFirst = filterLayout == kXCK || filterLayout == kXGCK;
+  if (filterHasG != (groupLayout == 1)) {
+    throw std::runtime_error("Filter layouts with a group dimension go with the SEPARATE group layout, and only with it");
   }
   const pml::TensorShape is = shapeOf(I), fs = shapeOf(F);
-  if (is.rank() < 3 || fs.rank() != is.rank()) {
+  if (is.rank() < 3 || fs.rank() != is.rank() + (filterHasG ? 1 : 0)) {
     throw std::runtime_error("Convolution input and filter ranks are inconsistent");
   }
   const size_t sr = is.rank() - 2;  // spatial rank
@@ -337,76 +346,150 @@ VarPtr opConvolution(const VarPtr& value) {
   if (strides.size() != sr || dilations.size() != sr || dataDilations.size() != sr) {
     throw std::runtime_error("Convolution strides / dilations do not match the spatial rank");
   }
-  for (int64_t d : dataDilations) {
-    if (d != 1) throw std::runtime_error("Data dilation is not offered by the cuda target's op library");
+  for (size_t i = 0; i < sr; ++i) {
+    if (strides[i] <= 0 || dilations[i] <= 0 || dataDilations[i] <= 0) {
+      throw std::runtime_error("Convolution strides and dilations must be positive");
+    }
   }
   if (!manualPadding.empty() && autopad != kPadExplicit) {
     throw std::runtime_error("Autopadding and manual padding both requested for single conv operation");
   }
   std::vector<int64_t> padLo, padHi;
   splitManualPadding(manualPadding, sr, &padLo, &padHi);
-  const bool nxc = inputLayout == kNXC;
   const int64_t N = is.sizes[0];
   const int64_t CI = nxc ? is.sizes.back() : is.sizes[1];
+  // filter dims: [G] K C x...   or   x... [G] C K
   std::vector<int64_t> X(sr), K(sr);
-  for (size_t i = 0; i < sr; ++i) {
-    X[i] = nxc ? is.sizes[1 + i] : is.sizes[2 + i];
-    K[i] = nxc ? fs.sizes[i] : fs.sizes[2 + i];
+  int64_t FG = 1, FCI, FCO;
+  if (filterSpatialFirst) {
+    for (size_t i = 0; i < sr; ++i) K[i] = fs.sizes[i];
+    size_t at = sr;
+    if (filterHasG) FG = fs.sizes[at++];
+    FCI = fs.sizes[at];
+    FCO = fs.sizes[at + 1];
+  } else {
+    size_t at = 0;
+    if (filterHasG) FG = fs.sizes[at++];
+    FCO = fs.sizes[at];
+    FCI = fs.sizes[at + 1];
+    for (size_t i = 0; i < sr; ++i) K[i] = fs.sizes[at + 2 + i];
   }
-  const int64_t FCI = nxc ? fs.sizes[sr] : fs.sizes[1];
-  const int64_t CO = nxc ? fs.sizes[sr + 1] : fs.sizes[0];
-  if (FCI != CI) throw std::runtime_error("Convolution input channels do not match the filter");
+  for (size_t i = 0; i < sr; ++i) X[i] = nxc ? is.sizes[1 + i] : is.sizes[2 + i];
+  // group count (plaidml/op/lib/ops.cc:1029-1056)
+  int64_t G = groups;
+  switch (autogroup) {
+    case 0:
+    case 1: break;
+    case 3:
+      G = CI;
+      if ((groupLayout == 3 || groupLayout == 1) && FCI != 1) {
+        throw std::runtime_error("Depthwise convolutions take filters with one input channel per group");
+      }
+      if (groupLayout == 0) throw std::runtime_error("Unsupported group layout 'GroupLayout::NONE' used with autogroup mode DEPTHWISE");
+      break;
+    case 2:
+      if (groupLayout == 1) {
+        G = FG;
+      } else if (groupLayout == 3) {
+        if (FCI <= 0 || CI % FCI != 0) throw std::runtime_error("Cannot infer the group count: input channels are not a multiple of the filter's");
+        G = CI / FCI;
+      } else {
+        throw std::runtime_error("Unsupported group layout used with autogroup mode AUTO");
+      }
+      break;
+    default: throw std::runtime_error("Unrecognized AutoGroupMode");
+  }
+  if (G < 1) throw std::runtime_error("Convolution group count must be positive");
+  int64_t CO = FCO;
+  switch (groupLayout) {
+    case 0:
+      if (G != 1) throw std::runtime_error("Grouped convolutions need a group layout");
+      if (FCI != CI) throw std::runtime_error("Convolution input channels do not match the filter");
+      break;
+    case 2:  // groups inside the filter's input-channel dimension
+      if (FCI != CI) throw std::runtime_error("Convolution input channels do not match the filter");
+      CO = FCO * G;
+      break;
+    case 3:  // groups inside the filter's output-channel dimension
+      if (FCI * G != CI) throw std::runtime_error("Convolution input channels do not match the filter");
+      break;
+    case 1:
+      if (FG != G) throw std::runtime_error("Convolution group count does not match the filter");
+      if (FCI * G != CI) throw std::runtime_error("Convolution input channels do not match the filter");
+      CO = FCO * G;
+      break;
+    default: throw std::runtime_error("Invalid group_layout");
+  }
+  if (CI % G != 0 || CO % G != 0) throw std::runtime_error("Channel counts must be multiples of the group count");
   if (!filterShape.empty()) {
     if (filterShape.size() != sr) throw std::runtime_error("Filter shape does not match the spatial rank");
     for (size_t i = 0; i < sr; ++i) {
       if (filterShape[i] != K[i]) throw std::runtime_error("Filter shape does not match the filter tensor");
     }
   }
-  PolyPtr n = newIndex("n"), ci = newIndex("ci"), co = newIndex("co");
+  PolyPtr n = newIndex("n"), ci = newIndex("ci"), co = newIndex("co"), g = newIndex("g");
   std::vector<PolyPtr> x, k, inSpatial;
   std::vector<int64_t> outSpatial;
   for (size_t i = 0; i < sr; ++i) {
     x.push_back(newIndex("x" + std::to_string(i)));
     k.push_back(newIndex("k" + std::to_string(i)));
     int64_t padBefore = 0, outSize = 0;
-    paddingAndOutput(X[i], K[i], strides[i], autopad, padLo[i], padHi[i], dilations[i], 1, false, &padBefore, &outSize);
+    paddingAndOutput(X[i], K[i], strides[i], autopad, padLo[i], padHi[i], dilations[i], dataDilations[i], false, &padBefore,
+                     &outSize);
     outSpatial.push_back(outSize);
-    inSpatial.push_back(strides[i] * x[i] + dilations[i] * k[i] - padBefore);
+    PolyPtr pos = strides[i] * x[i] + dilations[i] * k[i] - padBefore;
+    // data dilation: only positions that fall on an input element (an integral quotient) contribute
+    if (dataDilations[i] != 1) pos = polyOp(pml::AffineOp::Div, pos, polyLit(dataDilations[i]));
+    inSpatial.push_back(pos);
+  }
+  const bool grouped = groupLayout != 0;
+  PolyPtr iChan = grouped ? (CI / G) * g + ci : ci;
+  PolyPtr oChan = grouped ? (CO / G) * g + co : co;
+  PolyPtr fCo = co, fCi = ci;
+  std::vector<Cons> cons;
+  if (groupLayout == 2) {
+    fCi = (CI / G) * g + ci;
+    cons.push_back({ci, CI / G});
+  } else if (groupLayout == 3) {
+    fCo = (CO / G) * g + co;
+    cons.push_back({co, CO / G});
   }
   std::vector<PolyPtr> iIdx, fIdx, oIdx;
   std::vector<int64_t> oDims;
+  iIdx.push_back(n);
+  oIdx.push_back(n);
+  oDims.push_back(N);
   if (nxc) {
-    iIdx.push_back(n);
     for (auto& p : inSpatial) iIdx.push_back(p);
-    iIdx.push_back(ci);
-    for (auto& p : k) fIdx.push_back(p);
-    fIdx.push_back(ci);
-    fIdx.push_back(co);
-    oIdx.push_back(n);
-    oDims.push_back(N);
+    iIdx.push_back(iChan);
     for (size_t i = 0; i < sr; ++i) {
       oIdx.push_back(x[i]);
       oDims.push_back(outSpatial[i]);
     }
-    oIdx.push_back(co);
+    oIdx.push_back(oChan);
     oDims.push_back(CO);
   } else {
-    iIdx.push_back(n);
-    iIdx.push_back(ci);
+    iIdx.push_back(iChan);
     for (auto& p : inSpatial) iIdx.push_back(p);
-    fIdx.push_back(co);
-    fIdx.push_back(ci);
-    for (auto& p : k) fIdx.push_back(p);
-    oIdx.push_back(n);
-    oDims.push_back(N);
-    oIdx.push_back(co);
+    oIdx.push_back(oChan);
     oDims.push_back(CO);
     for (size_t i = 0; i < sr; ++i) {
       oIdx.push_back(x[i]);
       oDims.push_back(outSpatial[i]);
     }
   }
-  return exprValue(contraction(pml::AggKind::add, pml::ComboKind::mul, oDims, oIdx, {{I, iIdx}, {F, fIdx}}, {}, name));
+  if (filterSpatialFirst) {
+    for (auto& p : k) fIdx.push_back(p);
+    if (filterHasG) fIdx.push_back(g);
+    fIdx.push_back(fCi);
+    fIdx.push_back(fCo);
+  } else {
+    if (filterHasG) fIdx.push_back(g);
+    fIdx.push_back(fCo);
+    fIdx.push_back(fCi);
+    for (auto& p : k) fIdx.push_back(p);
+  }
+  return exprValue(contraction(pml::AggKind::add, pml::ComboKind::mul, oDims, oIdx, {{I, iIdx}, {F, fIdx}}, cons, name));
 }
 
 // plaidml/op/lib/ops.cc:2562-2703

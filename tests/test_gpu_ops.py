@@ -116,3 +116,73 @@ def test_slice_of():
 def test_scale_gradient_is_the_identity_forward():
     x = rng(11).standard_normal((3, 3)).astype(np.float32)
     np.testing.assert_array_equal(run(lambda X: op.scale_gradient(X, 0.5) + 0.0, x), x)
+
+
+# ---- convolution variants that run on the general contraction kernel --------------------------------
+
+def conv_ref(x, f, groups=1, stride=1, dil=1, ddil=1, pad=0):
+    """x [n,h,w,ci], f [kh,kw,ci/groups,co] with output channel block g = co // (co_total/groups) reading input
+    channel block g; data dilation inserts ddil-1 zeros between input elements."""
+    n, h, w, ci = x.shape
+    if ddil > 1:
+        xd = np.zeros((n, (h - 1) * ddil + 1, (w - 1) * ddil + 1, ci), x.dtype)
+        xd[:, ::ddil, ::ddil] = x
+        x, h, w = xd, xd.shape[1], xd.shape[2]
+    kh, kw, cig, co = f.shape
+    xp = np.pad(x, [(0, 0), (pad, pad), (pad, pad), (0, 0)])
+    p = (h + 2 * pad - dil * (kh - 1) - 1) // stride + 1
+    q = (w + 2 * pad - dil * (kw - 1) - 1) // stride + 1
+    out = np.zeros((n, p, q, co), np.float64)
+    cog = co // groups
+    for g in range(groups):
+        for r in range(kh):
+            for s in range(kw):
+                patch = xp[:, r * dil:r * dil + (p - 1) * stride + 1:stride, s * dil:s * dil + (q - 1) * stride + 1:stride,
+                           g * cig:(g + 1) * cig]
+                out[..., g * cog:(g + 1) * cog] += patch.astype(np.float64) @ f[r, s, :, g * cog:(g + 1) * cog].astype(np.float64)
+    return out.astype(np.float32)
+
+
+def test_grouped_convolution_group_layouts():
+    g = rng(20)
+    x = g.standard_normal((2, 9, 9, 8)).astype(np.float32)
+    groups = 2
+    f = g.standard_normal((3, 3, 4, 6)).astype(np.float32)          # [kh, kw, ci/groups, co]: the IN_K layout
+    ref = conv_ref(x, f, groups=groups, pad=1)
+    got = run(lambda X, F: op.convolution(X, F, groups=groups, autopad_mode=op.AutoPadMode.EXPLICIT, manual_padding=[1, 1],
+                                          group_layout=op.GroupLayout.IN_K, autogroup_mode=op.AutoGroupMode.EXPLICIT), x, f)
+    np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-5)
+    # the same filter with an explicit group dimension: [kh, kw, g, ci/g, co/g]
+    f_sep = np.stack([f[:, :, :, :3], f[:, :, :, 3:]], axis=2)
+    got = run(lambda X, F: op.convolution(X, F, groups=groups, autopad_mode=op.AutoPadMode.EXPLICIT, manual_padding=[1, 1],
+                                          filter_layout=op.TensorLayout.XGCK, group_layout=op.GroupLayout.SEPARATE,
+                                          autogroup_mode=op.AutoGroupMode.AUTO), x, f_sep)
+    np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-5)
+    # groups folded into the filter's input-channel dimension: [kh, kw, ci, co/g], block g of ci belongs to group g
+    f_inc = np.concatenate([f[:, :, :, :3], f[:, :, :, 3:]], axis=2)
+    got = run(lambda X, F: op.convolution(X, F, groups=groups, autopad_mode=op.AutoPadMode.EXPLICIT, manual_padding=[1, 1],
+                                          group_layout=op.GroupLayout.IN_C, autogroup_mode=op.AutoGroupMode.EXPLICIT), x, f_inc)
+    np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-5)
+
+
+def test_depthwise_convolution():
+    g = rng(21)
+    x = g.standard_normal((2, 10, 10, 6)).astype(np.float32)
+    f = g.standard_normal((3, 3, 1, 12)).astype(np.float32)         # channel multiplier 2
+    ref = conv_ref(x, f, groups=6, pad=1)
+    got = run(lambda X, F: op.convolution(X, F, autopad_mode=op.AutoPadMode.EXPLICIT, manual_padding=[1, 1],
+                                          group_layout=op.GroupLayout.IN_K, autogroup_mode=op.AutoGroupMode.DEPTHWISE), x, f)
+    np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-5)
+
+
+def test_dilated_strided_and_data_dilated_convolutions():
+    g = rng(22)
+    x = g.standard_normal((1, 12, 12, 4)).astype(np.float32)
+    f = g.standard_normal((3, 3, 4, 5)).astype(np.float32)
+    got = run(lambda X, F: op.convolution(X, F, strides=[2, 2], dilations=[2, 2], autopad_mode=op.AutoPadMode.EXPLICIT,
+                                          manual_padding=[2, 2]), x, f)
+    np.testing.assert_allclose(got, conv_ref(x, f, stride=2, dil=2, pad=2), rtol=1e-4, atol=1e-5)
+    # data dilation (the forward form of a transposed convolution): only taps that land on an input element count
+    got = run(lambda X, F: op.convolution(X, F, data_dilations=[2, 2], autopad_mode=op.AutoPadMode.EXPLICIT,
+                                          manual_padding=[1, 1]), x, f)
+    np.testing.assert_allclose(got, conv_ref(x, f, ddil=2, pad=1), rtol=1e-4, atol=1e-5)
