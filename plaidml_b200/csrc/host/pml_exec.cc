@@ -893,6 +893,23 @@ class Planner {
         st.launch = [plan, a, b, c, bias, res, rowmax](cudaStream_t s) {
           return pmlb_gemm_invoke(plan, s, a, b, c, bias, res, rowmax);
         };
+        // row-sliceable: plain 8/16-bit GEMM from a program input to a program output
+        if (pd.gemm.batch == 1 && pd.gemm.in_dtype != PMLB_F32 && pd.rowmax < 0 && pd.residual < 0 && pd.storeMain &&
+            pd.gemm.lda == pd.gemm.k && pd.gemm.ldc == pd.gemm.n) {
+          const int aRoot = root(pd.a), cRoot = root(pd.result);
+          for (size_t i = 0; i < prog_.inputs.size(); ++i) {
+            if (prog_.inputs[i] == aRoot) st.aInput = static_cast<int>(i);
+          }
+          for (size_t i = 0; i < prog_.outputs.size(); ++i) {
+            if (root(prog_.outputs[i]) == cRoot) st.cOutput = static_cast<int>(i);
+          }
+          if (st.aInput >= 0 && st.cOutput >= 0 && aRoot != root(pd.b)) {
+            st.rowSliceable = true;
+            st.gemm = pd.gemm;
+            st.bPtr = b;
+            st.biasPtr = bias;
+          }
+        }
         break;
       }
       case Pending::Conv: {
@@ -1200,6 +1217,9 @@ Executable::Executable(std::shared_ptr<Program> program, int device) : prog_(std
 Executable::~Executable() {
   cudaSetDevice(device_);
   if (stream_) cudaStreamSynchronize(stream_);
+  for (pmlb_plan* q : slicePlans_) pmlb_plan_free(q);
+  for (cudaEvent_t ev : sliceDone_) cudaEventDestroy(ev);
+  if (copyStream_) cudaStreamDestroy(copyStream_);
   if (graphExec_) cudaGraphExecDestroy(graphExec_);
   if (graph_) cudaGraphDestroy(graph_);
   for (Step& s : steps_) pmlb_plan_free(s.plan);
@@ -1304,6 +1324,8 @@ double Executable::run(const std::vector<BufferPtr>& inputs, const std::vector<B
     }
   }
   cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  if (slicedState_ == 0) slicedState_ = prepareSlicedRun() ? 1 : 2;
+  if (slicedState_ == 1) return runSliced(inputs, outputs);
   const auto t0 = std::chrono::steady_clock::now();
   for (size_t i = 0; i < inputs.size(); ++i) {
     const int id = prog_->inputs[i];
@@ -1321,6 +1343,73 @@ double Executable::run(const std::vector<BufferPtr>& inputs, const std::vector<B
       cudaCheck(cudaMemcpyAsync(outputs[i]->data(), dev_[id], bytes, cudaMemcpyDeviceToHost, stream_), "output download");
     }
   }
+  checkStatus();
+  const auto t1 = std::chrono::steady_clock::now();
+  return std::chrono::duration<double, std::milli>(t1 - t0).count();
+}
+
+// A program that is one large GEMM from a host input to a host output is bound by the host link,
+// not by the kernel.  Its rows are then processed in four slices: while slice i's rows of C travel
+// device -> host on a second stream, slice i + 1's rows of A travel host -> device, so the two
+// directions of the link overlap instead of taking turns.  Same kernels, same results.
+bool Executable::prepareSlicedRun() {
+  constexpr int kSlices = 4;
+  if (steps_.size() != 1 || !steps_[0].rowSliceable || prog_->outputs.size() != 1) return false;
+  if (Settings::instance().getOr("PLAIDML_CUDA_SLICED_RUN", "1") == "0") return false;
+  const Step& st = steps_[0];
+  const pmlb_gemm_desc& d = st.gemm;
+  const size_t outBytes = prog_->values[prog_->outputs[0]].shape.byteSize();
+  if (d.m % (kSlices * 256) != 0 || outBytes < (16u << 20)) return false;
+  for (int i = 0; i < kSlices; ++i) {
+    pmlb_gemm_desc sd = d;
+    sd.m = d.m / kSlices;
+    pmlb_plan* plan = nullptr;
+    if (pmlb_gemm_dispatch(&sd, &plan) != PMLB_OK || pmlb_plan_share_status(plan, status_) != PMLB_OK) {
+      if (plan) pmlb_plan_free(plan);
+      for (pmlb_plan* q : slicePlans_) pmlb_plan_free(q);
+      slicePlans_.clear();
+      return false;
+    }
+    slicePlans_.push_back(plan);
+  }
+  if (cudaStreamCreateWithFlags(&copyStream_, cudaStreamNonBlocking) != cudaSuccess) return false;
+  for (int i = 0; i < kSlices; ++i) {
+    cudaEvent_t ev = nullptr;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return false;
+    sliceDone_.push_back(ev);
+  }
+  return true;
+}
+
+double Executable::runSliced(const std::vector<BufferPtr>& inputs, const std::vector<BufferPtr>& outputs) {
+  const Step& st = steps_[0];
+  const pmlb_gemm_desc& d = st.gemm;
+  const int slices = static_cast<int>(slicePlans_.size());
+  const auto t0 = std::chrono::steady_clock::now();
+  for (size_t i = 0; i < inputs.size(); ++i) {
+    if (static_cast<int>(i) == st.aInput) continue;
+    const int id = prog_->inputs[i];
+    const size_t bytes = prog_->values[id].shape.byteSize();
+    if (bytes) cudaCheck(cudaMemcpyAsync(dev_[id], inputs[i]->data(), bytes, cudaMemcpyHostToDevice, stream_), "input upload");
+  }
+  const int aId = prog_->inputs[st.aInput], cId = prog_->outputs[st.cOutput];
+  const size_t aBytes = prog_->values[aId].shape.byteSize() / slices;
+  const size_t cBytes = prog_->values[cId].shape.byteSize() / slices;
+  for (int i = 0; i < slices; ++i) {
+    char* aDev = dev_[aId] + aBytes * i;
+    char* cDev = dev_[cId] + cBytes * i;
+    cudaCheck(cudaMemcpyAsync(aDev, static_cast<const char*>(inputs[st.aInput]->data()) + aBytes * i, aBytes,
+                              cudaMemcpyHostToDevice, stream_), "input upload");
+    const pmlb_status rc = pmlb_gemm_invoke(slicePlans_[i], stream_, aDev, st.bPtr, cDev, st.biasPtr, nullptr, nullptr);
+    if (rc != PMLB_OK) throw std::runtime_error("Kernel step '" + st.kernel + " " + st.detail + "' failed: " + pmlb_last_error());
+    cudaCheck(cudaEventRecord(sliceDone_[i], stream_), "cudaEventRecord");
+    cudaCheck(cudaStreamWaitEvent(copyStream_, sliceDone_[i], 0), "cudaStreamWaitEvent");
+    cudaCheck(cudaMemcpyAsync(static_cast<char*>(outputs[st.cOutput]->data()) + cBytes * i, cDev, cBytes,
+                              cudaMemcpyDeviceToHost, copyStream_), "output download");
+  }
+  inputsResident_ = true;
+  (void)d;
+  cudaCheck(cudaStreamSynchronize(copyStream_), "run");
   checkStatus();
   const auto t1 = std::chrono::steady_clock::now();
   return std::chrono::duration<double, std::milli>(t1 - t0).count();

@@ -30,6 +30,14 @@ struct Step {
   pmlb_plan* plan = nullptr;
   int launches = 1;     // kernel launches this step enqueues
   std::function<pmlb_status(cudaStream_t)> launch;
+  // GEMM steps whose A operand is a program input and whose product is a program output, with
+  // nothing else reading or feeding them: rows of A / C can be processed in slices.
+  bool rowSliceable = false;
+  pmlb_gemm_desc gemm{};
+  int aInput = -1;      // index into the program's inputs
+  int cOutput = -1;     // index into the program's outputs
+  const void* bPtr = nullptr;
+  const void* biasPtr = nullptr;
 };
 
 class Executable {
@@ -56,6 +64,8 @@ class Executable {
   void enqueueSteps();
   void launchStepsDirect();
   void captureGraph();
+  bool prepareSlicedRun();
+  double runSliced(const std::vector<BufferPtr>& inputs, const std::vector<BufferPtr>& outputs);
   void checkStatus();
 
   std::shared_ptr<Program> prog_;
@@ -75,6 +85,11 @@ class Executable {
   size_t passes_ = 0;
   cudaGraph_t graph_ = nullptr;
   cudaGraphExec_t graphExec_ = nullptr;
+  // Sliced run of a single-GEMM program (see Executable::runSliced): 0 = not tried, 1 = in use, 2 = off.
+  int slicedState_ = 0;
+  std::vector<pmlb_plan*> slicePlans_;
+  std::vector<cudaEvent_t> sliceDone_;
+  cudaStream_t copyStream_ = nullptr;
 };
 
 // Device ids follow the reference's pattern name(-name)*.N (pmlc/rt/device_id.cc:13-38).

@@ -88,6 +88,27 @@ def test_int8_tile_gemm_bit_exact():
     np.testing.assert_array_equal(runner.run([a, b])[0], oracle.gemm_i8_i32(a, b))
 
 
+def test_full_size_int8_gemm_through_the_sliced_run():
+    # configuration 2 at full size: plaidml_executable_run moves the rows of A and C in four slices so that
+    # upload and download overlap; the result must equal the single-pass run bit for bit, and a checksum of
+    # row sums pins both against the operands (sum_j C[i, j] = A[i, :] . rowsum(B))
+    g = rng(1240)
+    m = n = k = 4096
+    a = g.integers(-128, 128, size=(m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(k, n), dtype=np.int8)
+    A, B, C = P.tile_gemm(DType.INT8, m, n, k, acc=DType.INT32)
+    sliced = Runner(Program("gemm_i8_full", [A, B], [C]), "cuda.0").run([a, b])[0]
+    core.settings_set("PLAIDML_CUDA_SLICED_RUN", "0")
+    try:
+        whole = Runner(Program("gemm_i8_full", [A, B], [C]), "cuda.0").run([a, b])[0]
+    finally:
+        core.settings_set("PLAIDML_CUDA_SLICED_RUN", "1")
+    np.testing.assert_array_equal(sliced, whole)
+    np.testing.assert_array_equal(sliced.astype(np.int64).sum(axis=1), a.astype(np.int64) @ b.astype(np.int64).sum(axis=1))
+    rows = [0, 1023, 1024, 2047, 3072, 4095]
+    np.testing.assert_array_equal(sliced[rows], oracle.gemm_i8_i32(np.ascontiguousarray(a[rows]), b))
+
+
 def test_int8_without_casts_wraps_like_the_reference():
     g = rng(1236)
     a = g.integers(-128, 128, size=(64, 48), dtype=np.int8)
