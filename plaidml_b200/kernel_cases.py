@@ -4,7 +4,7 @@
 
 Each case builds its program through the EDSL, runs it once through ``plaidml_executable_run``
 (inputs seeded, uploaded from host buffers) and then repeats the device-resident kernel
-sequence ``passes`` times (default 3) without L2 flushing, so that a profiler sees a handful of
+sequence once untimed and then ``passes`` times (default 3) without L2 flushing, so that a profiler sees a handful of
 launches of the kernel of interest:
 
     i8_4k      int8 -> int32 Tile GEMM 4096^3            (tc_contract_kernel, int8, B as [k][n])
@@ -12,7 +12,10 @@ launches of the kernel of interest:
     f32_1k     fp32 Tile GEMM 1024^3 via three TF32 products
     conv3      conv 3x3 56x56 64->64 + bias + ReLU, batch 16
     conv3_full the same at batch 128
-    qk         batched Q.K^T 128 x (512x512x64) + row max
+    qk         batched Q.K^T 128 x (512x512x64) + row max (folded into the GEMM's epilogue)
+    rowmax     row max alone over a 256 x 512 x 512 f32 tensor (row_reduce_kernel, 256 MiB)
+    stem       the first two layers of ResNet-50 at batch 32: 7x7 / 2 convolution on 3 channels
+               (pack_rows_kernel + tc_contract_kernel, packed rows) and the 3x3 / 2 max pool (pool_kernel)
     resnet N   ResNet-50 v1.5 at batch N
 """
 
@@ -29,6 +32,10 @@ from .exec import Runner
 
 
 def main(argv) -> None:
+    from .core import settings_set
+    # one launch per GEMM, as in the device-resident timing of bench.py (plaidml_executable_run would
+    # otherwise cut a large single GEMM into four row slices to overlap its host copies)
+    settings_set("PLAIDML_CUDA_SLICED_RUN", "0")
     case = argv[1] if len(argv) > 1 else "i8_4k"
     g = np.random.Generator(np.random.PCG64(7))
     passes = 3
@@ -55,6 +62,25 @@ def main(argv) -> None:
         R = Contraction(name="rowmax").outShape(128, 512).outAccess(bb, i).max(S[bb, i, j]).build()
         r = Runner(Program(case, [Q, Kt], [S, R]), "cuda.0")
         ins = [f32_to_bf16_bits(g.standard_normal((128, 512, 64))) for _ in range(2)]
+    elif case == "rowmax":
+        from .edsl import Placeholder
+        S = Placeholder(DType.FLOAT32, [256, 512, 512])
+        bb, i, j = TensorIndexes(3)
+        R = Contraction(name="rowmax").outShape(256, 512).outAccess(bb, i).max(S[bb, i, j]).build()
+        r = Runner(Program(case, [S], [R]), "cuda.0")
+        ins = [g.standard_normal((256, 512, 512)).astype(np.float32)]
+    elif case == "stem":
+        from . import edsl, op
+        from .edsl import Placeholder, cast
+        w = f32_to_bf16_bits(g.standard_normal((7, 7, 3, 64)) * np.sqrt(2.0 / 147))
+        I = Placeholder(DType.BFLOAT16, [32, 224, 224, 3])
+        F = cast(edsl.Constant(w, name="w", dtype=DType.BFLOAT16), DType.FLOAT32)
+        y = op.convolution(cast(I, DType.FLOAT32), F, strides=[2, 2], autopad_mode=op.AutoPadMode.EXPLICIT,
+                           manual_padding=[3, 3, 3, 3]) + edsl.Constant(np.zeros(64, np.float32), name="b")
+        y = cast(op.relu(y), DType.BFLOAT16)
+        y = op.pool(y, op.PoolMode.MAX, [3, 3], [2, 2], op.AutoPadMode.EXPLICIT, [1, 1, 1, 1], op.TensorLayout.NXC)
+        r = Runner(Program(case, [I], [y]), "cuda.0")
+        ins = [f32_to_bf16_bits(g.uniform(0, 1, (32, 224, 224, 3)).astype(np.float32))]
     elif case == "resnet":
         batch = int(argv[2]) if len(argv) > 2 else 32
         prog, _ = programs.resnet50(batch)
@@ -67,6 +93,7 @@ def main(argv) -> None:
     if len(argv) > 2 and case != "resnet":
         passes = int(argv[2])
     r.run(ins)
+    r.executable.time_steps(1, False)      # first use of the kernels of the resident path (module loading)
     ms = r.executable.time_steps(passes, False)
     print(f"{case}: {ms:.4f} ms per pass over {passes} passes; {r.executable.launch_count} launches per pass")
     print(r.executable.describe())
