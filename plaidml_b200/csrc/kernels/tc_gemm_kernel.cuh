@@ -50,7 +50,6 @@ struct TcCfg {
   //    pipelined); 2: eight warps, one group of four per accumulator, for shapes whose main
   //    loop per tile is shorter than the epilogue (small K).
   static constexpr int EPI_GROUPS = EPI_GROUPS_;
-  static constexpr int THREADS = 64 + 128 * EPI_GROUPS_;
   static constexpr int OUT_BYTES = OUT_BYTES_;  // element size the staged epilogue packs to
   static constexpr int CW = 128 / OUT_BYTES_;   // output columns per 128-byte staged row
   static constexpr int BM = 128;
@@ -73,7 +72,15 @@ struct TcCfg {
   static constexpr int STAGES_RAW = RING_BUDGET / STAGE;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE + STG_BYTES + BAR_BYTES;
-  static constexpr int TMEM_COLS = 2 * BN;            // 128, 256 or 512
+  // MMA-issuing warps.  The tensor pipe queues only three or four MMAs; a 64- or 128-wide MMA
+  // lasts 48 / 64 cycles, so the issuing thread's per-tile bookkeeping (barrier waits, commits:
+  // several hundred cycles) leaves the pipe idle.  Narrow tiles therefore get two issuers that
+  // take alternate tiles, each with its own pair of accumulators.
+  static constexpr int ISSUERS = (BN_ <= 64 && CTAS_ == 1 && NSPLIT_ == 1 && A_MODE_ != kAWindow) ? 2 : 1;
+  static constexpr int NACC = 2 * ISSUERS;            // TMEM accumulators
+  static constexpr int FIRST_EPI_WARP = 1 + ISSUERS;
+  static constexpr int THREADS = 32 * FIRST_EPI_WARP + 128 * EPI_GROUPS_;
+  static constexpr int TMEM_COLS = NACC * BN;         // 128, 256 or 512
   static constexpr int KIND = EB == 2 ? kMmaF16 : (EB == 4 ? kMmaTf32 : kMmaI8);
   static constexpr int B_CHUNKS = (BN / CTAS_) / BK;  // MN-major: chunks of 128 bytes of N per CTA
   static_assert(STAGES >= 2, "ring too small");
@@ -397,15 +404,15 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   // barrier index helpers (8 bytes each)
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
-  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };             // up to 4
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 4 + a); };
   // two residual-arrival barriers per epilogue warp (at most 8 warps)
-  auto res_bar = [&](int ew, uint32_t i) { return bar0 + 8u * (2 * STAGES + 4 + 2 * ew + i); };
+  auto res_bar = [&](int ew, uint32_t i) { return bar0 + 8u * (2 * STAGES + 8 + 2 * ew + i); };
   // packed-row mode: arrival / release barriers of up to 16 row slots, one for the weights
-  auto wfull_bar = [&](uint32_t i) { return bar0 + 8u * (2 * STAGES + 20 + i); };
-  auto wempty_bar = [&](uint32_t i) { return bar0 + 8u * (2 * STAGES + 36 + i); };
-  const uint32_t wts_bar = bar0 + 8u * (2 * STAGES + 52);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 53);
+  auto wfull_bar = [&](uint32_t i) { return bar0 + 8u * (2 * STAGES + 24 + i); };
+  auto wempty_bar = [&](uint32_t i) { return bar0 + 8u * (2 * STAGES + 40 + i); };
+  const uint32_t wts_bar = bar0 + 8u * (2 * STAGES + 56);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 57);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* abort_code = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
@@ -423,7 +430,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < Cfg::NACC; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 4 * CTAS);
     }
@@ -656,8 +663,12 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp < Cfg::FIRST_EPI_WARP) {
+    // ------------------------------------------------------------ MMA issuer(s)
+    // With two issuers, issuer iw takes the tiles whose local number is iw modulo 2; local tile
+    // number `it` uses accumulator it % NACC in barrier phase (it / NACC) & 1, and the ring
+    // stages go to tiles in order, so an issuer also walks the stages of the other's tiles.
+    const int iw = warp - 1;
     // Same shape: the warp walks the loops and waits, one elected lane issues the MMAs and
     // the commits (a commit covers the MMAs issued by the thread that executes it).
     const bool leader = elect_one();
@@ -673,6 +684,10 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     auto desc_at = [](uint64_t base, uint32_t saddr) {
       return base | static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
     };
+    // the same split into words: low word = leading-offset field | start address >> 4
+    const uint32_t dk_lo = static_cast<uint32_t>(desc_k), dk_hi = static_cast<uint32_t>(desc_k >> 32);
+    const uint32_t dmn_lo = static_cast<uint32_t>(desc_mn), dmn_hi = static_cast<uint32_t>(desc_mn >> 32);
+    auto lo_at = [](uint32_t base_lo, uint32_t saddr) { return base_lo | ((saddr & 0x3FFFFu) >> 4); };
     if constexpr (Cfg::A_HALO) {
       const uint32_t nst = static_cast<uint32_t>(p.halo_stages);
       uint32_t hs = 0, hphase = 0;
@@ -685,11 +700,34 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       // phase of a row from its shared-memory address (measured: with the row phase also put
       // into the descriptor's base-offset field the results are wrong).
       auto win_desc = [&](uint32_t saddr) { return desc_at(desc_k, saddr); };
-      for (int t = t_begin; t < t_end && ok; t += t_step) {
+      int hsi = 0;
+      int it = 0;
+      for (int t = t_begin; t < t_end && ok; t += t_step, ++it) {
+        if (it % Cfg::ISSUERS != iw) {
+          // The other issuer's tile: walk its buffers too, waiting for each to arrive.  A parity
+          // wait tells "this phase" from "the one before" only, so an issuer must never run
+          // more than one ring revolution ahead of the data.
+          for (int cb = 0; cb < p.conv_cblocks && ok; ++cb) {
+            if (!mbar_wait_warp(full_bar(static_cast<uint32_t>(hsi)), hphase, abort_flag)) {
+              if (leader && *abort_code == 0) *abort_code = 3;
+              ok = false;
+            }
+            if (++hsi == static_cast<int>(nst)) {
+              hsi = 0;
+              hphase ^= 1u;
+            }
+          }
+          continue;
+        }
+        hs = static_cast<uint32_t>(hsi);
+        acc = it % Cfg::NACC;
+        acc_phase = static_cast<uint32_t>(it / Cfg::NACC) & 1u;
+        if (leader && iw == 0) trace_event(p, 1, ntrace, t, 0);
         if (!mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
           if (leader && *abort_code == 0) *abort_code = 2;
           break;
         }
+        if (leader && iw == 0) trace_event(p, 1, ntrace, t, 1);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int cb = 0; cb < p.conv_cblocks && ok; ++cb) {
@@ -700,22 +738,24 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           }
           tc_fence_after_sync();
           const uint32_t buf = halo_ring + hs * static_cast<uint32_t>(p.halo_stage_bytes);
-          int tap = 0;
+          // output position j reads padded pixel j + fr * wp + fs of the buffer: descriptor low
+          // words advance by 8 (one 128-byte row) per filter column, wp * 8 per filter row, and
+          // the weights' by one B tile per tap (all in 16-byte units)
+          uint32_t a_row = lo_at(dk_lo, buf);
+          uint32_t b_lo = lo_at(dk_lo, ring + static_cast<uint32_t>(cb) * Cfg::B_TILE);
+          const uint32_t b_step = static_cast<uint32_t>(p.conv_cblocks) * (Cfg::B_TILE >> 4);
+          const uint32_t a_row_step = static_cast<uint32_t>(p.halo_wp) * 8u;
+          uint32_t first = cb > 0 ? 1u : 0u;
+          if (leader && iw == 0 && cb == 0) trace_event(p, 1, ntrace, t, 2);
           for (int fr = 0; fr < p.conv_r; ++fr) {
-            for (int fs = 0; fs < p.conv_s; ++fs, ++tap) {
-              // output position j reads padded pixel j + fr * wp + fs of the buffer
-              const uint64_t a_d = win_desc(buf + static_cast<uint32_t>(fr * p.halo_wp + fs) * 128u);
-              const uint64_t b_d =
-                  desc_at(desc_k, ring + static_cast<uint32_t>(tap * p.conv_cblocks + cb) * Cfg::B_TILE);
-              if (leader) {
-                if (tap == 0 && cb == 0) trace_event(p, 1, ntrace, t, 2);
-                tc_mma<Cfg::KIND>(d_tmem, a_d, b_d, p.idesc, (cb > 0 || tap > 0) ? 1u : 0u);
-#pragma unroll
-                for (int j = 1; j < 4; ++j) {
-                  tc_mma<Cfg::KIND>(d_tmem, a_d + 2u * j, b_d + 2u * j, p.idesc, 1u);
-                }
-              }
+            uint32_t a_lo = a_row;
+            for (int fs = 0; fs < p.conv_s; ++fs) {
+              if (leader) tc_mma_x4<Cfg::KIND, 1>(d_tmem, a_lo, b_lo, dk_hi, dk_hi, p.idesc, first, 2u, 2u);
+              first = 1u;
+              a_lo += 8u;
+              b_lo += b_step;
             }
+            a_row += a_row_step;
           }
           if (leader) tc_commit(empty_bar(hs));
           if (++hs == nst) {
@@ -723,14 +763,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
             hphase ^= 1u;
           }
         }
+        hsi = static_cast<int>(hs);
         if (!ok) break;
         if (leader) {
           tc_commit(tfull_bar(acc));
-          trace_event(p, 1, ntrace, t, 3);
-        }
-        if (++acc == 2) {
-          acc = 0;
-          acc_phase ^= 1u;
+          if (iw == 0) trace_event(p, 1, ntrace, t, 3);
         }
       }
     } else if constexpr (Cfg::A_WINDOW) {
@@ -770,15 +807,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         const int nrel = slides ? p.conv_stride_h : p.win_r;
         uint32_t slot = c0 % nslots;
         for (int r = 0; r < p.win_r; ++r) {
-          const uint64_t a_d = desc_at(desc_k, win_slots + slot * static_cast<uint32_t>(p.win_slot_bytes));
-          const uint64_t b_d = desc_at(desc_k, win_wts + r * Cfg::B_TILE);
+          const uint32_t a_lo = lo_at(dk_lo, win_slots + slot * static_cast<uint32_t>(p.win_slot_bytes));
+          const uint32_t b_lo = lo_at(dk_lo, win_wts + r * Cfg::B_TILE);
           if (leader) {
             if (r == 0) trace_event(p, 1, ntrace, t, 2);
-            tc_mma<Cfg::KIND>(d_tmem, a_d, b_d, p.idesc, r > 0 ? 1u : 0u);
-#pragma unroll
-            for (int j = 1; j < 4; ++j) {
-              tc_mma<Cfg::KIND>(d_tmem, a_d + 2u * j, b_d + 2u * j, p.idesc, 1u);
-            }
+            tc_mma_x4<Cfg::KIND, 1>(d_tmem, a_lo, b_lo, dk_hi, dk_hi, p.idesc, r > 0 ? 1u : 0u, 2u, 2u);
           }
           if (++slot == nslots) slot = 0;
         }
@@ -798,13 +831,30 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         }
       }
     } else if (CTAS == 1 || cta_rank == 0) {
-      for (int t = t_begin; t < t_end && ok; t += t_step) {
-        if (leader) trace_event(p, 1, ntrace, t, 0);
+      int it = 0;
+      for (int t = t_begin; t < t_end && ok; t += t_step, ++it) {
+        if (it % Cfg::ISSUERS != iw) {
+          // the other issuer's tile: walk its stages too, waiting for each to arrive (see above)
+          for (int kb = 0; kb < p.num_kb && ok; ++kb) {
+            if (!mbar_wait_warp(full_bar(stage), phase, abort_flag)) {
+              if (leader && *abort_code == 0) *abort_code = 3;
+              ok = false;
+            }
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          continue;
+        }
+        acc = it % Cfg::NACC;
+        acc_phase = static_cast<uint32_t>(it / Cfg::NACC) & 1u;
+        if (leader && iw == 0) trace_event(p, 1, ntrace, t, 0);
         if (!mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
           if (leader && *abort_code == 0) *abort_code = 2;
           break;
         }
-        if (leader) trace_event(p, 1, ntrace, t, 1);
+        if (leader && iw == 0) trace_event(p, 1, ntrace, t, 1);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         const uint32_t idesc = t >= p.tiles_full ? p.idesc_half : p.idesc;   // half-width tail tiles
@@ -824,7 +874,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           constexpr uint32_t kStepA = 2u;
           constexpr uint32_t kStepB = Cfg::B_MN ? (Cfg::UMMA_K * 128u) >> 4 : 2u;
           if (leader) {
-            if (kb == 0) trace_event(p, 1, ntrace, t, 2);
+            if (kb == 0 && iw == 0) trace_event(p, 1, ntrace, t, 2);
             if constexpr (NSPLIT == 2) {
               // fp32 as three TF32 products; the two cross terms first.
               const uint64_t a_lo = desc_at(desc_k, s_a + Cfg::A_TILE);
@@ -838,18 +888,9 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
                 tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_lo + kStepB * j, idesc, 1u);
                 tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, idesc, 1u);
               }
-            } else if constexpr (CTAS == 2) {
-              tc_mma_pair<Cfg::KIND>(d_tmem, a_hi, b_hi, idesc, kb > 0 ? 1u : 0u);
-#pragma unroll
-              for (int j = 1; j < 4; ++j) {
-                tc_mma_pair<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, idesc, 1u);
-              }
             } else {
-              tc_mma<Cfg::KIND>(d_tmem, a_hi, b_hi, idesc, kb > 0 ? 1u : 0u);
-#pragma unroll
-              for (int j = 1; j < 4; ++j) {
-                tc_mma<Cfg::KIND>(d_tmem, a_hi + kStepA * j, b_hi + kStepB * j, idesc, 1u);
-              }
+              tc_mma_x4<Cfg::KIND, CTAS>(d_tmem, lo_at(dk_lo, s_a), lo_at(Cfg::B_MN ? dmn_lo : dk_lo, s_b), dk_hi,
+                                         Cfg::B_MN ? dmn_hi : dk_hi, idesc, kb > 0 ? 1u : 0u, kStepA, kStepB);
             }
             if constexpr (CTAS == 2) {
               tc_commit_pair(empty_bar(stage), 3);   // the stage is free in both CTAs
@@ -869,22 +910,18 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           } else {
             tc_commit(tfull_bar(acc));
           }
-          trace_event(p, 1, ntrace, t, 3);
-        }
-        if (++acc == 2) {
-          acc = 0;
-          acc_phase ^= 1u;
+          if (iw == 0) trace_event(p, 1, ntrace, t, 3);
         }
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;                     // TMEM lane quarter this warp may read
-    const int ew = warp - 2;                    // epilogue warp number
+    const int ew = warp - Cfg::FIRST_EPI_WARP;  // epilogue warp number
     const int grp = ew >> 2;                    // epilogue group (accumulator owner when two)
     constexpr int G = Cfg::EPI_GROUPS;
-    // Local tile number `it` selects the accumulator (it & 1) and its barrier phase
-    // ((it >> 1) & 1); with two groups, group g takes the tiles with (it & 1) == g.
+    // Local tile number `it` selects the accumulator (it % NACC) and its barrier phase
+    // ((it / NACC) & 1); with two groups, group g takes the tiles with (it & 1) == g.
     if (p.fast_epi) {
       constexpr int CW = Cfg::CW;
       constexpr int OB = Cfg::OUT_BYTES;
@@ -899,11 +936,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       const bool out_bf16 = p.out_dtype == kDtBF16;
       int it = 0;
       int ntrace = 0;
-      const bool tracer = (q == 2) && lane == 0;   // first warp of each group (warps 2 and 6)
+      const bool tracer = (ew & 3) == 0 && lane == 0;   // first warp of each group
       for (int t = t_begin; t < t_end && alive; t += t_step, ++it) {
         if (G == 2 && (it & 1) != grp) continue;
-        const int acc = it & 1;
-        const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
+        const int acc = it % Cfg::NACC;
+        const uint32_t acc_phase = static_cast<uint32_t>(it / Cfg::NACC) & 1u;
         const TileCoord tc = tile_coord_cta<Cfg>(p, t, cta_rank);
         int row0 = tc.tm * 128 + q * 32;
         int row = row0 + lane;
@@ -1103,8 +1140,8 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       int it = 0;
       for (int t = t_begin; t < t_end; t += t_step, ++it) {
         if (G == 2 && (it & 1) != grp) continue;
-        const int acc = it & 1;
-        const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
+        const int acc = it % Cfg::NACC;
+        const uint32_t acc_phase = static_cast<uint32_t>(it / Cfg::NACC) & 1u;
         const TileCoord tc = tile_coord_cta<Cfg>(p, t, cta_rank);
         if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
           if (*abort_code == 0) *abort_code = 4;
