@@ -205,6 +205,11 @@ typedef struct {
  * take the halo route (weights resident in shared memory, each tile's padded pixels fetched
  * once and every tap read as a shifted window).  This flag keeps them on the im2col route. */
 #define PMLB_CONV_NO_HALO 2
+/* Stride-2 convolutions of inputs with at most 4 channels into at most 64 output channels take
+ * the space-to-depth route (a pre-pass packs the 2 x 2 pixel phases as channels; the kernel then
+ * runs the stride-1 form with resident weights).  This flag sends them down the next route that
+ * accepts them (packed rows, else im2col). */
+#define PMLB_CONV_NO_S2D 4
 
 pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* desc, pmlb_plan** plan);
 

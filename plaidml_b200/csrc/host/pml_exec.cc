@@ -649,7 +649,7 @@ class Planner {
       d.dil_w = static_cast<int32_t>(dil[1]);
       if (d.pad_h > 127 || d.pad_w > 127 || d.stride_h > 8 || d.stride_w > 8) continue;
       // the im2col route needs whole 16-byte channel groups; thin inputs take the packed-row route
-      if (d.c % 8 != 0 && !pmlb::conv_takes_packed_rows(d)) continue;
+      if (d.c % 8 != 0 && !pmlb::conv_takes_packed_rows(d) && !pmlb::conv_takes_s2d(d)) continue;
       pd->kind = Pending::Conv;
       pd->a = a;
       pd->b = b;
@@ -922,8 +922,9 @@ class Planner {
         pmlbCheck(rc, "conv dispatch for '" + label + "'");
         pmlbCheck(pmlb_plan_share_status(plan, exe_->status_), "status word");
         st.plan = plan;
-        st.kernel = pmlb_plan_kind(plan);          // "tc_conv", or "tc_conv_rows" for the packed-row route
-        const int extra = std::string(st.kernel) == "tc_conv_rows" ? 1 : 0;   // its activation packing pass
+        st.kernel = pmlb_plan_kind(plan);          // "tc_conv", "tc_conv_halo", "tc_conv_rows" or "tc_conv_s2d"
+        const std::string route = st.kernel;
+        const int extra = (route == "tc_conv_rows" || route == "tc_conv_s2d") ? 1 : 0;   // their activation packing pass
         st.launches = 1 + extra;
         std::ostringstream os;
         const pmlb_conv_desc& d = pd.conv;

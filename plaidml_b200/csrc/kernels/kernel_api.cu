@@ -99,6 +99,7 @@ struct pmlb_plan {
   bool filter_set = false;
   bool halo = false;             // conv: halo route (scratch = weights as for im2col)
   bool packed_rows = false;      // conv: packed-row route (scratch = weights, then the padded activation)
+  bool s2d = false;              // conv: space-to-depth route (scratch = weights, then the packed activation)
   size_t packed_input_off = 0;   // byte offset of the padded activation inside scratch
 
   pmlb_reduce_desc reduce;
@@ -436,8 +437,10 @@ pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* d, pmlb_plan** out) {
       d->dil_w <= 0 || d->pad_h < 0 || d->pad_w < 0) {
     return fail(PMLB_ERR_INVALID, "conv: bad geometry");
   }
-  const bool packed = pmlb::conv_takes_packed_rows(*d) && (d->flags & PMLB_CONV_NO_PACKED_ROWS) == 0;
-  if (!packed && d->c % 8 != 0) {
+  const bool s2d = pmlb::conv_takes_s2d(*d) && (d->flags & PMLB_CONV_NO_S2D) == 0;
+  const bool packed =
+      !s2d && pmlb::conv_takes_packed_rows(*d) && (d->flags & PMLB_CONV_NO_PACKED_ROWS) == 0;
+  if (!packed && !s2d && d->c % 8 != 0) {
     return fail(PMLB_ERR_UNSUPPORTED, "conv: channel count must be a multiple of 8");
   }
   // every output pixel's first tap must lie inside the im2col bounding box
@@ -454,7 +457,17 @@ pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* d, pmlb_plan** out) {
   plan->kind_name = "tc_conv";
   plan->conv = *d;
   size_t scratch = static_cast<size_t>(d->k) * d->r * d->s * d->c * 2;
-  if (!packed && pmlb::conv_takes_halo(*d) && (d->flags & PMLB_CONV_NO_HALO) == 0) {
+  if (s2d) {
+    const pmlb::S2dShape g = pmlb::conv_s2d_shape(*d);
+    plan->s2d = true;
+    plan->kind_name = "tc_conv_s2d";
+    const size_t wts = static_cast<size_t>(g.r2) * g.s2 * 2048;
+    plan->packed_input_off = (wts + 255) / 256 * 256;
+    // (a tile's copy may run past the last image: keep that much readable behind it)
+    scratch = plan->packed_input_off + static_cast<size_t>(d->n) * g.h2 * g.wp * 32 +
+              static_cast<size_t>(g.stage_px) * 32;
+  }
+  if (!packed && !s2d && pmlb::conv_takes_halo(*d) && (d->flags & PMLB_CONV_NO_HALO) == 0) {
     plan->halo = true;
     plan->kind_name = "tc_conv_halo";
   }
@@ -484,7 +497,11 @@ pmlb_status pmlb_conv_set_filter(pmlb_plan* plan, void* stream, const void* filt
   }
   const pmlb_conv_desc& d = plan->conv;
   cudaError_t e;
-  if (plan->packed_rows) {
+  if (plan->s2d) {
+    const pmlb::S2dShape g = pmlb::conv_s2d_shape(d);
+    e = pmlb::launch_filter_s2d(filter, dtype, plan->scratch, d.in_dtype, d.r, d.s, d.c, d.k, g.r2,
+                                g.s2, g.dh, g.dw, static_cast<cudaStream_t>(stream));
+  } else if (plan->packed_rows) {
     e = pmlb::launch_filter_pack_rows(filter, dtype, plan->scratch, d.in_dtype, d.r, d.s, d.c,
                                       pmlb::conv_padded_channels(d), d.k,
                                       static_cast<cudaStream_t>(stream));
@@ -505,6 +522,37 @@ pmlb_status pmlb_conv_invoke(pmlb_plan* plan, void* stream, const void* input, v
   const pmlb_conv_desc& d = plan->conv;
   if ((d.epilogue & PMLB_EPI_BIAS) && !bias) return fail(PMLB_ERR_INVALID, "conv: bias missing");
   if ((d.epilogue & PMLB_EPI_RESIDUAL) && !residual) return fail(PMLB_ERR_INVALID, "conv: residual missing");
+  if (plan->s2d) {
+    const pmlb::S2dShape sh = pmlb::conv_s2d_shape(d);
+    void* packed = static_cast<char*>(plan->scratch) + plan->packed_input_off;
+    cudaError_t e = pmlb::launch_s2d_pack(input, packed, d.n, d.h, d.w, d.c, sh.h2, sh.wp, sh.pe_h,
+                                          sh.pe_w, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, "activation space-to-depth packing");
+    pmlb::S2dGeom g;
+    g.n = d.n; g.p = d.p; g.q = d.q;
+    g.r2 = sh.r2; g.s2 = sh.s2; g.h2 = sh.h2; g.wp = sh.wp; g.stage_px = sh.stage_px;
+    pmlb::TcLaunch L;
+    L.elem_bytes = 2;
+    L.is_f16 = d.in_dtype == PMLB_F16;
+    L.m = d.n * d.p * d.q;
+    L.n = d.k;
+    L.k = sh.r2 * sh.s2 * 16;
+    L.batch = 1;
+    L.a0 = packed;
+    L.b0 = plan->scratch;
+    L.s2d = &g;
+    L.out = output;
+    L.ldc = d.k;
+    L.out_dtype = d.out_dtype;
+    L.epi_flags = d.epilogue;
+    L.bias = bias;
+    L.status = plan->status;
+    L.trace = g_trace_buffer;
+    std::string err;
+    const int rc = pmlb::tc_launch(L, static_cast<cudaStream_t>(stream), &err);
+    if (rc != 0) return fail(static_cast<pmlb_status>(rc), "conv (space to depth): " + err);
+    return PMLB_OK;
+  }
   if (plan->packed_rows) {
     const int cp = pmlb::conv_padded_channels(d);
     const int wp = pmlb::conv_packed_row_width(d);

@@ -156,7 +156,93 @@ filter_pack_rows_kernel(const void* __restrict__ in, int in_dtype, void* __restr
   }
 }
 
+template <int C>
+__global__ void __launch_bounds__(256)
+s2d_pack_kernel(const uint16_t* __restrict__ in, uint4* __restrict__ out, long long total_px, int h,
+                int w, int h2, int wp, int pe_h, int pe_w) {
+  const long long id = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (id >= total_px) return;
+  const int x2 = static_cast<int>(id % wp);
+  const long long rem = id / wp;
+  const int y2 = static_cast<int>(rem % h2);
+  const long long img = rem / h2;
+  uint32_t words[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+  for (int py = 0; py < 2; ++py) {
+    const int y = 2 * y2 + py - pe_h;
+#pragma unroll
+    for (int px = 0; px < 2; ++px) {
+      const int x = 2 * x2 + px - pe_w;
+      if (y >= 0 && y < h && x >= 0 && x < w) {
+        const uint16_t* src = in + ((img * h + y) * w + x) * C;
+#pragma unroll
+        for (int ci = 0; ci < C; ++ci) {
+          const int ch = (py * 2 + px) * C + ci;
+          words[ch >> 1] |= static_cast<uint32_t>(__ldg(src + ci)) << ((ch & 1) * 16);
+        }
+      }
+    }
+  }
+  const int swap = static_cast<int>(((static_cast<long long>(y2) * wp + x2) >> 2) & 1);
+  out[id * 2 + swap] = make_uint4(words[0], words[1], words[2], words[3]);
+  out[id * 2 + (swap ^ 1)] = make_uint4(words[4], words[5], words[6], words[7]);
+}
+
+__global__ void __launch_bounds__(256)
+filter_s2d_kernel(const void* __restrict__ in, int in_dtype, void* __restrict__ out, int out_dtype,
+                  int r, int s, int c, int k, int r2, int s2, int dh, int dw) {
+  const int id = blockIdx.x * blockDim.x + threadIdx.x;
+  const int total = r2 * s2 * 64 * 16;
+  if (id >= total) return;
+  // id walks the logical output [tap][ko][16]
+  const int ch = id & 15;
+  const int ko = (id >> 4) & 63;
+  const int tap = id >> 10;
+  const int tr = tap / s2, ts = tap - tr * s2;
+  float v = 0.f;
+  if (ch < 4 * c && ko < k) {
+    const int phase = ch / c, ci = ch - phase * c;
+    const int fr = 2 * tr + (phase >> 1) - dh, fs = 2 * ts + (phase & 1) - dw;
+    if (fr >= 0 && fr < r && fs >= 0 && fs < s) {
+      v = load_filter(in, in_dtype, ((static_cast<long long>(fr) * s + fs) * c + ci) * k + ko);
+    }
+  }
+  // exchange the 16-byte halves (8 elements each) of rows whose number has bit 2 set
+  const int o = (id & ~15) | (ch ^ (((ko >> 2) & 1) << 3));
+  if (out_dtype == PMLB_BF16) {
+    static_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
+  } else {
+    static_cast<__half*>(out)[o] = __float2half_rn(v);
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_s2d_pack(const void* in, void* out, int n, int h, int w, int c, int h2, int wp,
+                            int pe_h, int pe_w, cudaStream_t stream) {
+  const long long total = static_cast<long long>(n) * h2 * wp;
+  if (total <= 0) return cudaSuccess;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  const uint16_t* src = static_cast<const uint16_t*>(in);
+  uint4* dst = static_cast<uint4*>(out);
+  switch (c) {
+    case 1: s2d_pack_kernel<1><<<blocks, 256, 0, stream>>>(src, dst, total, h, w, h2, wp, pe_h, pe_w); break;
+    case 2: s2d_pack_kernel<2><<<blocks, 256, 0, stream>>>(src, dst, total, h, w, h2, wp, pe_h, pe_w); break;
+    case 3: s2d_pack_kernel<3><<<blocks, 256, 0, stream>>>(src, dst, total, h, w, h2, wp, pe_h, pe_w); break;
+    case 4: s2d_pack_kernel<4><<<blocks, 256, 0, stream>>>(src, dst, total, h, w, h2, wp, pe_h, pe_w); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_filter_s2d(const void* in, int in_dtype, void* out, int out_dtype, int r, int s,
+                              int c, int k, int r2, int s2, int dh, int dw, cudaStream_t stream) {
+  const int total = r2 * s2 * 64 * 16;
+  if (total <= 0) return cudaSuccess;
+  filter_s2d_kernel<<<(total + 255) / 256, 256, 0, stream>>>(in, in_dtype, out, out_dtype, r, s, c, k,
+                                                             r2, s2, dh, dw);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_pack_rows(const void* in, void* out, int n, int h, int w, int c, int wp, int cp,
                              int pad_w, cudaStream_t stream) {

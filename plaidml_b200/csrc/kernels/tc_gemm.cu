@@ -209,7 +209,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   int groups = (L.conv ? 0 : num_kb_plain) <= 24 ? 2 : 1;
   // CTA pairs: plain GEMMs whose 256-wide tiles have long main loops and fill the machine.
   bool pair = false;
-  const bool pair_possible = !L.conv && !L.window && L.nsplit == 1 && bn == 256;
+  const bool pair_possible = !L.conv && !L.window && !L.halo && !L.s2d && L.nsplit == 1 && bn == 256;
   if (pair_possible && num_kb_plain > 24 && L.m >= 256) {
     const long long pair_tiles =
         static_cast<long long>(L.batch) * ((L.m + 255) / 256) * ((L.n + 255) / 256);
@@ -263,7 +263,46 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   CUtensorMap& tb1 = maps.b1;
   CUtensorMap& tc_map = maps.c;
 
-  if (L.halo) {
+  if (L.s2d) {
+    const S2dGeom& g = *L.s2d;
+    using S2dCfg = TcCfg<2, 64, 1, kAS2d, false, 2, 2>;
+    static_assert(S2dCfg::STAGES * S2dCfg::STAGE == kS2dSmemBytes, "space-to-depth budget");
+    const int taps = g.r2 * g.s2;
+    const int wts_bytes = taps * 2048;
+    const int stage_bytes = (g.stage_px * 32 + 1023) / 1024 * 1024;
+    // (the kernel has one pair of barriers per operand-ring stage of its instance)
+    const int stages = std::min(S2dCfg::STAGES, (kS2dSmemBytes - wts_bytes) / stage_bytes);
+    if (eb != 2 || L.nsplit != 1 || L.b_mn || L.n > 64 || L.n % 8 != 0 || g.wp % 8 != 0 || g.stage_px % 8 != 0 ||
+        g.stage_px < 128 + (g.r2 - 1) * g.wp + g.s2 - 1 || g.wp < g.q + g.s2 - 1 || g.h2 < g.p + g.r2 - 1 ||
+        stages < 3 || L.m != g.n * g.p * g.q || L.batch != 1 ||
+        (L.epi_flags & (kEpiResidual | kEpiRowMax)) != 0) {
+      *err = "space-to-depth convolution: geometry outside what the kernel takes";
+      return 3;
+    }
+    if ((reinterpret_cast<uintptr_t>(L.a0) & 255u) != 0 || (reinterpret_cast<uintptr_t>(L.b0) & 15u) != 0) {
+      *err = "space-to-depth convolution: packed operands must be 256- / 16-byte aligned";
+      return 1;
+    }
+    bn = 64;
+    p.conv_p = g.p;
+    p.conv_q = g.q;
+    p.conv_r = g.r2;
+    p.conv_s = g.s2;
+    p.conv_cblocks = 1;
+    p.halo_wp = g.wp;
+    p.halo_stage_bytes = stage_bytes;
+    p.halo_stages = stages;
+    p.halo_tiles_per_img = (g.p * g.wp + 127) / 128;
+    p.s2d_px = L.a0;
+    p.s2d_wts = L.b0;
+    p.s2d_img_px = g.h2 * g.wp;
+    p.s2d_stage_load = g.stage_px * 32;
+    p.num_kb = taps;
+    p.batch = g.n * p.halo_tiles_per_img;     // tiles of 128 positions
+    p.tiles_m = 1;
+    p.tiles_n = 1;
+    p.idesc = make_idesc(eb, L.is_f16, false, bn);
+  } else if (L.halo) {
     const ConvGeom& g = L.halo->conv;
     const int wp = g.w + 2 * g.pad_w;                     // = q + s - 1 for stride 1
     const int th = wp > 0 ? std::min(128 / wp, g.p) : 0;
@@ -277,7 +316,9 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     const int stage_bytes = (wp * rows * 128 + 1023) / 1024 * 1024;
     // the last tap's window reaches (r - 1) * wp + s - 1 rows past the 128 it needs
     const int overread = std::max(0, ((g.r - 1) * wp + g.s - 1 + 128) * 128 - stage_bytes);
-    const int stages = stage_bytes > 0 ? std::min(8, (ring_bytes - wts_bytes - overread) / stage_bytes) : 0;
+    // (the kernel has one pair of barriers per operand-ring stage of its instance)
+    const int stages =
+        stage_bytes > 0 ? std::min(HaloCfg::STAGES, (ring_bytes - wts_bytes - overread) / stage_bytes) : 0;
     if (eb != 2 || L.nsplit != 1 || L.b_mn || L.n != 64 || g.c % 64 != 0 || g.stride_h != 1 || g.stride_w != 1 ||
         g.dil_h != 1 || g.dil_w != 1 || th < 1 || wp > 256 || rows > 256 || stages < 2 ||
         g.q != wp - g.s + 1 || g.p != g.h + 2 * g.pad_h - g.r + 1 || L.m != g.n * g.p * g.q || L.batch != 1) {
@@ -500,15 +541,23 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     if (fast && L.out != nullptr) {
       const uint64_t c_bs = L.batch > 1 ? static_cast<uint64_t>(L.out_batch_stride) * ob
                                         : static_cast<uint64_t>(L.ldc) * ob * L.m;
-      if (!encode3d(&tc_map, out_map_dtype(L.out_dtype), ob, L.out, L.n, L.m, L.batch,
-                    static_cast<uint64_t>(L.ldc) * ob, c_bs, 128 / ob, 32, 1, err)) {
+      if (L.s2d) {
+        // (channels, q, n * p); boxes of 8 output columns
+        const S2dGeom& g = *L.s2d;
+        if (!encode3d(&tc_map, out_map_dtype(L.out_dtype), ob, L.out, L.n, g.q, static_cast<uint64_t>(g.n) * g.p,
+                      static_cast<uint64_t>(L.ldc) * ob, static_cast<uint64_t>(L.ldc) * ob * g.q, 128 / ob, 8, 1,
+                      err)) {
+          return 1;
+        }
+      } else if (!encode3d(&tc_map, out_map_dtype(L.out_dtype), ob, L.out, L.n, L.m, L.batch,
+                           static_cast<uint64_t>(L.ldc) * ob, c_bs, 128 / ob, 32, 1, err)) {
         return 1;
       }
     }
     p.fast_epi = fast ? 1 : 0;
     // Residual rows ride the same staging buffers: fetched by TMA ahead of their chunk.
-    if (L.halo && (!fast || L.out == nullptr)) {
-      *err = "halo convolution: output rows must be 16-byte aligned";
+    if ((L.halo || L.s2d) && (!fast || L.out == nullptr)) {
+      *err = "halo / space-to-depth convolution: output rows must be 16-byte aligned";
       return 3;
     }
     if (fast && L.out != nullptr && (L.epi_flags & kEpiResidual) && !L.residual_from_global && !L.halo) {
@@ -531,7 +580,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   // the CTAs (pairs), they are walked as two half-width tiles each and take half as long.
   p.tiles_full = static_cast<int>(total);
   p.idesc_half = p.idesc;
-  if (bn == 256 && !L.window && !L.halo && L.split_tail != 0) {
+  if (bn == 256 && !L.window && !L.halo && !L.s2d && L.split_tail != 0) {
     const long long workers = pair ? resident_pairs[dev] : num_sms;
     const long long rem = total % workers;
     if (total > workers && rem > 0 && 2 * rem <= workers) {
@@ -554,9 +603,9 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   if (const char* env = std::getenv("PMLB_TC_EPI_GROUPS")) {
     if (env[0] == '1' || env[0] == '2') groups = env[0] - '0';
   }
-  if (L.halo) groups = 2;
+  if (L.halo || L.s2d) groups = 2;
   if (L.window || pair) groups = 1;  // (the row ring leaves room for one group's staging buffers only)
-  const int a_mode = L.halo ? kAHalo : (L.window ? kAWindow : (L.conv ? kAIm2col : kATiled));
+  const int a_mode = L.s2d ? kAS2d : (L.halo ? kAHalo : (L.window ? kAWindow : (L.conv ? kAIm2col : kATiled)));
   bool launched = false;
 #define PMLB_TC_CASE(EB, BN, NS, IM, MN, OB, G)                                                 \
   if (!launched && eb == EB && bn == BN && L.nsplit == NS && a_mode == static_cast<int>(IM) &&  \

@@ -53,6 +53,14 @@ struct TcParams {
   int halo_stages;             // buffers in the ring
   int halo_tiles_per_img;      // ceil(p / halo_th)
   int conv_r;                  // filter taps along H
+  // Space-to-depth convolution (stride 2, thin input): as the halo convolution, on a packed
+  // activation of 32-byte pixels whose tiles are 128 consecutive pixel positions; conv_r / conv_s
+  // count the taps of the stride-1 form, halo_wp / halo_stage_bytes / halo_stages /
+  // halo_tiles_per_img keep their meaning.
+  const void* s2d_px;          // packed activation [n][h2][wp][16], pre-swizzled
+  const void* s2d_wts;         // packed weights [taps][64][16], pre-swizzled
+  int s2d_img_px;              // pixels per packed image = h2 * wp
+  int s2d_stage_load;          // bytes copied per tile
 
   // Epilogue
   void* out;

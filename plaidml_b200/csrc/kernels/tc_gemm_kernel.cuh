@@ -37,6 +37,10 @@ enum : int {
                  // image rows are fetched once per tile (tiled TMA, padding = out-of-bounds
                  // fill) and every filter tap is read as a row-shifted window of that buffer;
                  // output positions in the padding columns are computed and discarded
+  kAS2d = 4,     // a thin NHWC activation, stride-2 convolution, repacked by a pre-pass to 32-byte
+                 // pixels holding the 2 x 2 phases as channels (and already in the 32-byte
+                 // swizzle): a tile is 128 consecutive pixel positions, fetched with the pixels
+                 // its taps reach by one untiled bulk copy; taps are row-shifted windows as above
 };
 
 template <int EB, int BN_, int NSPLIT_, int A_MODE_, bool B_MN_, int OUT_BYTES_ = 4,
@@ -59,6 +63,7 @@ struct TcCfg {
   static constexpr bool A_IM2COL = A_MODE_ == kAIm2col;
   static constexpr bool A_WINDOW = A_MODE_ == kAWindow;
   static constexpr bool A_HALO = A_MODE_ == kAHalo;
+  static constexpr bool A_S2D = A_MODE_ == kAS2d;
   static constexpr bool B_MN = B_MN_;
   static constexpr int BK = 128 / EB;       // elements of K per stage
   static constexpr int UMMA_K = 32 / EB;    // elements of K per tcgen05.mma
@@ -445,7 +450,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       }
       mbar_init(wts_bar, 1);
     }
-    if constexpr (Cfg::A_HALO) mbar_init(wts_bar, 1);
+    if constexpr (Cfg::A_HALO || Cfg::A_S2D) mbar_init(wts_bar, 1);
     *abort_flag = 0;
     *abort_code = 0;
     fence_mbar_init();
@@ -493,7 +498,9 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   // halo mode: the weights of every (tap, channel block) stay in shared memory ahead of the ring
   // of fetched pixel buffers; halo_nb = k-blocks (taps x channel blocks) per tile
   const int halo_taps = p.conv_r * p.conv_s;
-  const uint32_t halo_ring = ring + static_cast<uint32_t>(halo_taps * p.conv_cblocks) * Cfg::B_TILE;
+  const uint32_t halo_ring =
+      ring + (Cfg::A_S2D ? static_cast<uint32_t>(halo_taps) * 2048u
+                         : static_cast<uint32_t>(halo_taps * p.conv_cblocks) * Cfg::B_TILE);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -504,7 +511,39 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     uint32_t phase = 0;
     bool ok = true;
     int ntrace = 0;
-    if constexpr (Cfg::A_HALO) {
+    if constexpr (Cfg::A_S2D) {
+      // Weights of every tap, once: 64 rows of 32 bytes each.
+      const uint32_t wts_bytes = static_cast<uint32_t>(halo_taps) * 2048u;
+      if (leader) {
+        mbar_arrive_expect_tx(wts_bar, wts_bytes);
+        bulk_load_1d(ring, p.s2d_wts, wts_bytes, wts_bar);
+      }
+      // One buffer per tile: the tile's 128 pixel positions and the pixels its taps reach are
+      // consecutive in the packed activation.
+      const uint32_t nst = static_cast<uint32_t>(p.halo_stages);
+      uint32_t hs = 0, hphase = 0;
+      for (int t = t_begin; t < t_end && ok; t += t_step) {
+        const int img = t / p.halo_tiles_per_img;
+        const int tt = t - img * p.halo_tiles_per_img;
+        if (!mbar_wait_warp(empty_bar(hs), hphase ^ 1u, abort_flag)) {
+          if (leader && *abort_code == 0) *abort_code = 1;
+          ok = false;
+          break;
+        }
+        if (leader) {
+          trace_event(p, 0, ntrace, t, 0);
+          const char* src = static_cast<const char*>(p.s2d_px) +
+                            (static_cast<long long>(img) * p.s2d_img_px + tt * 128) * 32;
+          mbar_arrive_expect_tx(full_bar(hs), static_cast<uint32_t>(p.s2d_stage_load));
+          bulk_load_1d(halo_ring + hs * static_cast<uint32_t>(p.halo_stage_bytes), src,
+                       static_cast<uint32_t>(p.s2d_stage_load), full_bar(hs));
+        }
+        if (++hs == nst) {
+          hs = 0;
+          hphase ^= 1u;
+        }
+      }
+    } else if constexpr (Cfg::A_HALO) {
       // Weights of every tap and channel block, once: block (tap, cb) at wts + (tap * cblocks + cb).
       if (leader) {
         mbar_arrive_expect_tx(wts_bar, static_cast<uint32_t>(halo_taps * p.conv_cblocks) * Cfg::B_TILE);
@@ -688,7 +727,86 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     const uint32_t dk_lo = static_cast<uint32_t>(desc_k), dk_hi = static_cast<uint32_t>(desc_k >> 32);
     const uint32_t dmn_lo = static_cast<uint32_t>(desc_mn), dmn_hi = static_cast<uint32_t>(desc_mn >> 32);
     auto lo_at = [](uint32_t base_lo, uint32_t saddr) { return base_lo | ((saddr & 0x3FFFFu) >> 4); };
-    if constexpr (Cfg::A_HALO) {
+    if constexpr (Cfg::A_S2D) {
+      const uint32_t nst = static_cast<uint32_t>(p.halo_stages);
+      uint32_t hs = 0, hphase = 0;
+      if (t_begin < t_end && !mbar_wait_warp(wts_bar, 0u, abort_flag)) {
+        if (leader && *abort_code == 0) *abort_code = 3;
+        ok = false;
+      }
+      // 32-byte rows in the 32-byte swizzle, eight rows every 256 bytes; one MMA (K = 16
+      // elements = one pixel's channels) per tap.  As in the halo mode a window that starts a
+      // whole number of rows into the buffer takes the plain descriptor of its start address.
+      const uint64_t d32 = make_smem_desc_sw32(0, 16, 256);
+      const uint32_t d32_lo = static_cast<uint32_t>(d32), d32_hi = static_cast<uint32_t>(d32 >> 32);
+      int it = 0;
+      for (int t = t_begin; t < t_end && ok; t += t_step, ++it) {
+        if (it % Cfg::ISSUERS != iw) {
+          // the other issuer's tile: wait for its buffer too, so that the parity of later waits
+          // stays unambiguous
+          if (!mbar_wait_warp(full_bar(hs), hphase, abort_flag)) {
+            if (leader && *abort_code == 0) *abort_code = 3;
+            ok = false;
+          }
+          if (++hs == nst) {
+            hs = 0;
+            hphase ^= 1u;
+          }
+          continue;
+        }
+        acc = it % Cfg::NACC;
+        acc_phase = static_cast<uint32_t>(it / Cfg::NACC) & 1u;
+        if (leader && iw == 0) trace_event(p, 1, ntrace, t, 0);
+        if (!mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          if (leader && *abort_code == 0) *abort_code = 2;
+          break;
+        }
+        if (!mbar_wait_warp(full_bar(hs), hphase, abort_flag)) {
+          if (leader && *abort_code == 0) *abort_code = 3;
+          ok = false;
+          break;
+        }
+        if (leader && iw == 0) trace_event(p, 1, ntrace, t, 1);
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        const uint32_t buf = halo_ring + hs * static_cast<uint32_t>(p.halo_stage_bytes);
+        // output position j reads packed pixel j + tr * wp + ts: descriptor low words advance by
+        // 2 (one 32-byte row) per tap column, wp * 2 per tap row, the weights' by 128 per tap
+        uint32_t a_row = lo_at(d32_lo, buf);
+        uint32_t b_lo = lo_at(d32_lo, ring);
+        const uint32_t a_row_step = static_cast<uint32_t>(p.halo_wp) * 2u;
+        uint32_t first = 0u;
+        for (int tr = 0; tr < p.conv_r; ++tr) {
+          uint32_t a_lo = a_row;
+          int ts = 0;
+          for (; ts + 4 <= p.conv_s; ts += 4) {
+            if (leader) tc_mma_x4<Cfg::KIND, 1>(d_tmem, a_lo, b_lo, d32_hi, d32_hi, p.idesc, first, 2u, 128u);
+            first = 1u;
+            a_lo += 8u;
+            b_lo += 512u;
+          }
+          for (; ts < p.conv_s; ++ts) {
+            if (leader) {
+              tc_mma<Cfg::KIND>(d_tmem, (static_cast<uint64_t>(d32_hi) << 32) | a_lo,
+                                (static_cast<uint64_t>(d32_hi) << 32) | b_lo, p.idesc, first);
+            }
+            first = 1u;
+            a_lo += 2u;
+            b_lo += 128u;
+          }
+          a_row += a_row_step;
+        }
+        if (leader) {
+          tc_commit(empty_bar(hs));
+          tc_commit(tfull_bar(acc));
+          if (iw == 0) trace_event(p, 1, ntrace, t, 3);
+        }
+        if (++hs == nst) {
+          hs = 0;
+          hphase ^= 1u;
+        }
+      }
+    } else if constexpr (Cfg::A_HALO) {
       const uint32_t nst = static_cast<uint32_t>(p.halo_stages);
       uint32_t hs = 0, hphase = 0;
       if (t_begin < t_end && !mbar_wait_warp(wts_bar, 0u, abort_flag)) {
@@ -944,6 +1062,10 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         const TileCoord tc = tile_coord_cta<Cfg>(p, t, cta_rank);
         int row0 = tc.tm * 128 + q * 32;
         int row = row0 + lane;
+        if constexpr (Cfg::A_S2D) {
+          row0 = 0;   // (no per-row epilogue inputs in this mode; the store maps rows itself)
+          row = 0;
+        }
         if constexpr (Cfg::A_HALO) {
           // accumulator row j = output position j of the tile: image row j / wp, column j % wp;
           // columns past q (the padding columns) and rows past the image are not outputs
@@ -1087,7 +1209,26 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(&tm.c, buf, col0, row0, tc.b);
+            if constexpr (Cfg::A_S2D) {
+              // The warp's 32 rows are positions g0 .. g0 + 31 of the image's padded position
+              // grid (wp a multiple of 8 per image row): every run of 8 lies in one image row
+              // and goes out as one box of the (channels, q, n * p) output map, which clips
+              // the columns from q on; runs in the padding columns or below the image are
+              // skipped.
+              const int img = t / p.halo_tiles_per_img;
+              const int g0 = (t - img * p.halo_tiles_per_img) * 128 + q * 32;
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const int g = g0 + 8 * b;
+                const int op = g / p.halo_wp;
+                const int oq = g - op * p.halo_wp;
+                if (op < p.conv_p && oq < p.conv_q) {
+                  tma_store_3d(&tm.c, buf + static_cast<uint32_t>(b) * 1024u, col0, oq, img * p.conv_p + op);
+                }
+              }
+            } else {
+              tma_store_3d(&tm.c, buf, col0, row0, tc.b);
+            }
             bulk_commit_group();
           }
           ++nbuf;

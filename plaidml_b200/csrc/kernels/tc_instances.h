@@ -28,6 +28,8 @@
 #define PMLB_TC_LIST_MISC(X)        \
   X(2, 64, 1, 3, false, 2, 2)       \
   X(2, 64, 1, 3, false, 4, 2)       \
+  X(2, 64, 1, 4, false, 2, 2)       \
+  X(2, 64, 1, 4, false, 4, 2)       \
   X(2, 64, 1, 2, false, 2, 1)       \
   X(2, 64, 1, 2, false, 4, 1)       \
   X(1, 64, 1, false, false, 4, 1)   \

@@ -34,6 +34,16 @@ struct HaloGeom {
   ConvGeom conv;
 };
 
+// Space-to-depth convolution (stride 2, thin input): a0 is the packed activation [n][h2][wp][16]
+// (followed by at least stage_px * 32 readable bytes), b0 the packed weights [r2 * s2][64][16],
+// both already in the 32-byte swizzle; the output is [n][p][q][k_out].
+struct S2dGeom {
+  int n, p, q;
+  int r2, s2;     // taps of the stride-1 form
+  int h2, wp;     // rows per packed image, pixels per row (a multiple of 8)
+  int stage_px;   // pixels a 128-position tile reads (a multiple of 8)
+};
+
 struct TcLaunch {
   int elem_bytes = 2;   // 1 (int8), 2 (bf16 / f16), 4 (fp32 pre-split into TF32 hi / lo)
   bool is_f16 = false;  // 2-byte operands are IEEE half instead of bfloat16
@@ -54,6 +64,7 @@ struct TcLaunch {
                                    // B holds the weights as [k_out][r*s][c]
 
   const HaloGeom* halo = nullptr;   // non-null: halo convolution; m, n, batch = n*p*q, k_out, 1
+  const S2dGeom* s2d = nullptr;     // non-null: space-to-depth convolution; m, n, batch = n*p*q, k_out, 1
   const WinGeom* window = nullptr;  // non-null: packed-row convolution (a0 / b0 as described there);
                                     // m, n, batch = q, k_out, n * p
 

@@ -134,7 +134,7 @@ def test_conv_rejects_odd_channels():
 def test_stem_conv7x7_stride2_three_channels():
     # ResNet's first layer at a small size: 3 input channels (no 16-byte channel groups), 7x7 / 2, pad 3
     out, ref, plan = run_conv(30, 3, 40, 40, 3, 7, 7, 64, stride=2, pad=3, out_dtype=K.BF16,
-                              epilogue=K.EPI_BIAS | K.EPI_RELU)
+                              epilogue=K.EPI_BIAS | K.EPI_RELU, flags=K.CONV_NO_S2D)
     assert plan.kernel == "tc_conv_rows"
     check_close(out, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
 
@@ -158,7 +158,7 @@ def test_stem_conv_matches_im2col_route():
     dict(n=3, h=24, w=24, c=3, r=7, s=7, k=64, stride=2, same_upper=True),
 ], ids=["wide", "ragged", "tiny", "stride3", "same_upper"])
 def test_packed_row_geometries(case):
-    out, ref, plan = run_conv(32, **case)
+    out, ref, plan = run_conv(32, flags=K.CONV_NO_S2D, **case)
     assert plan.kernel == "tc_conv_rows"
     check_close(out, ref, 1e-4)
 
@@ -169,6 +169,35 @@ def test_packed_rows_residual_f32_and_bf16():
     check_close(out, ref, 1e-4)
     out, ref, _ = run_conv(34, 2, 20, 20, 3, 3, 3, 64, out_dtype=K.BF16, epilogue=K.EPI_BIAS | K.EPI_RESIDUAL)
     check_close(out, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+
+
+# --- space-to-depth route (stride 2, at most 4 input channels: 2 x 2 phases packed as channels) ---
+
+@pytest.mark.parametrize("case", [
+    dict(n=3, h=40, w=40, c=3, r=7, s=7, k=64, stride=2, pad=3),      # ResNet's first layer at a small size
+    dict(n=2, h=33, w=45, c=4, r=5, s=5, k=48, stride=2, pad=2),      # odd extents, k < 64, even padding
+    dict(n=3, h=24, w=24, c=3, r=7, s=7, k=64, stride=2, same_upper=True),   # more padding after than before
+    dict(n=2, h=31, w=50, c=1, r=3, s=3, k=8, stride=2, pad=0),       # one channel, no padding
+    dict(n=2, h=20, w=22, c=2, r=4, s=2, k=16, stride=2, pad=1),      # even filter extents, odd padding
+    dict(n=40, h=64, w=64, c=3, r=7, s=7, k=64, stride=2, pad=3),     # 440 tiles: the ring wraps, both issuers work
+], ids=["stem", "ragged", "same_upper", "one_channel", "even_filter", "many"])
+def test_s2d_route_matches_oracle_and_packed_rows(case):
+    out, ref, plan = run_conv(80, **case)
+    assert plan.kernel == "tc_conv_s2d"
+    check_close(out, ref, 1e-4)
+    rows, _, plan2 = run_conv(80, flags=K.CONV_NO_S2D, **case)
+    assert plan2.kernel == "tc_conv_rows"
+    check_close(out, rows, 1e-5)
+
+
+def test_s2d_route_bias_relu_bf16_out():
+    out, ref, plan = run_conv(81, 3, 40, 40, 3, 7, 7, 64, stride=2, pad=3, out_dtype=K.BF16,
+                              epilogue=K.EPI_BIAS | K.EPI_RELU)
+    assert plan.kernel == "tc_conv_s2d"
+    check_close(out, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+    # a residual input is outside the route: the layer falls through to packed rows
+    _, _, plan = run_conv(82, 2, 20, 20, 3, 3, 3, 64, stride=2, epilogue=K.EPI_RESIDUAL)
+    assert plan.kernel == "tc_conv_rows"
 
 
 # --- halo route (stride 1, 64 output channels, weights resident) ----------------------------------
