@@ -75,7 +75,9 @@ int pmlb_device_count(void);
 
 /* Debugging aid: while `device_buffer` (4 * 2048 * 3 int64, zero-filled by the caller) is
  * set, CTA 0 of every tensor-core launch logs {tile, event, clock64} records of its producer,
- * MMA and epilogue warps to it.  NULL (the default) turns logging off. */
+ * MMA and epilogue warps to it.  NULL (the default) turns logging off.  The records exist only
+ * in a library built with -DPMLB_TC_TRACE (they slow the kernel's roles by several per cent even
+ * when unused); otherwise the call is accepted and nothing is logged. */
 void pmlb_debug_set_trace(void* device_buffer);
 
 typedef struct pmlb_plan pmlb_plan;

@@ -55,6 +55,8 @@ def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> None:
     ]
     if src.suffix == ".cc":
         cmd += ["-x", "cu"]  # host files include cuda_runtime.h; one toolchain for everything
+    if os.environ.get("PMLB_TC_TRACE"):
+        cmd += ["-DPMLB_TC_TRACE"]   # the kernel's timeline records (see pmlb_debug_set_trace)
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-c", str(src), "-o", str(obj)]

@@ -54,13 +54,14 @@ inline bool conv_takes_halo(const pmlb_conv_desc& d) {
 // Space-to-depth route: stride-2 convolutions of thin inputs (at most 4 channels: the first layer
 // of an image network) into at most 64 channels.  The 2 x 2 pixel phases become channels, which
 // turns the r x s / 2 convolution into a stride-1 one with ceil(r / 2) x ceil(s / 2) taps over
-// 16-channel (32-byte) pixels; the kernel then works as the halo route does, on 32-byte rows.
+// 16-channel (32-byte) pixels; the kernel then works as the halo route does, with the 32-byte
+// k-steps of its 128-byte operand rows being four neighbouring pixels.
 struct S2dShape {
   int pe_h, pe_w;   // padding before the first row / column, rounded up to even
   int dh, dw;       // pe - pad: filter tap fr sits at row fr + dh of the 2 x 2 phase grid
   int r2, s2;       // taps of the stride-1 convolution
-  int h2, wp;       // rows and (padded to a multiple of 8) pixels per row of the packed activation
-  int stage_px;     // pixels a 128-position tile reads
+  int h2, wp;       // rows and (padded to a multiple of 32) pixels per row of the packed activation
+  int stage_px;     // pixels a 512-position tile reads (a multiple of 32)
 };
 
 inline S2dShape conv_s2d_shape(const pmlb_conv_desc& d) {
@@ -72,8 +73,8 @@ inline S2dShape conv_s2d_shape(const pmlb_conv_desc& d) {
   g.r2 = (d.r + g.dh + 1) / 2;
   g.s2 = (d.s + g.dw + 1) / 2;
   g.h2 = d.p + g.r2 - 1;
-  g.wp = (d.q + g.s2 - 1 + 7) / 8 * 8;
-  g.stage_px = (128 + (g.r2 - 1) * g.wp + g.s2 - 1 + 7) / 8 * 8;
+  g.wp = (d.q + g.s2 - 1 + 31) / 32 * 32;
+  g.stage_px = (512 + (g.r2 - 1) * g.wp + g.s2 - 1 + 31) / 32 * 32;
   return g;
 }
 
@@ -81,15 +82,19 @@ inline S2dShape conv_s2d_shape(const pmlb_conv_desc& d) {
 // instance with two epilogue groups).
 constexpr int kS2dSmemBytes = 147456;
 
-inline int conv_s2d_stage_bytes(const S2dShape& g) { return (g.stage_px * 32 + 1023) / 1024 * 1024; }
+// packed weights: one 64-row block of 128-byte rows per tap row and four tap columns
+inline int conv_s2d_weight_bytes(const S2dShape& g) { return g.r2 * ((g.s2 + 3) / 4) * 8192; }
+
+inline int conv_s2d_stage_bytes(const S2dShape& g) { return g.stage_px * 32; }
 
 inline bool conv_takes_s2d(const pmlb_conv_desc& d) {
   if (!(d.in_dtype == PMLB_BF16 || d.in_dtype == PMLB_F16)) return false;
   if (d.stride_h != 2 || d.stride_w != 2 || d.dil_h != 1 || d.dil_w != 1) return false;
-  if (d.c > 4 || d.k > 64 || d.k % 8 != 0 || d.r * d.s < 2) return false;
+  // (the output map addresses columns as (column % 4, column / 4): whole groups of four only)
+  if (d.c > 4 || d.k > 64 || d.k % 8 != 0 || d.q % 4 != 0 || d.r * d.s < 2) return false;
   if (d.epilogue & (PMLB_EPI_ROWMAX | PMLB_EPI_RESIDUAL)) return false;
   const S2dShape g = conv_s2d_shape(d);
-  return g.r2 * g.s2 * 2048 + 3 * conv_s2d_stage_bytes(g) <= kS2dSmemBytes;
+  return conv_s2d_weight_bytes(g) + 2 * conv_s2d_stage_bytes(g) <= kS2dSmemBytes;
 }
 
 }  // namespace pmlb

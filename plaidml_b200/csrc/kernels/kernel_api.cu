@@ -461,7 +461,7 @@ pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* d, pmlb_plan** out) {
     const pmlb::S2dShape g = pmlb::conv_s2d_shape(*d);
     plan->s2d = true;
     plan->kind_name = "tc_conv_s2d";
-    const size_t wts = static_cast<size_t>(g.r2) * g.s2 * 2048;
+    const size_t wts = static_cast<size_t>(pmlb::conv_s2d_weight_bytes(g));
     plan->packed_input_off = (wts + 255) / 256 * 256;
     // (a tile's copy may run past the last image: keep that much readable behind it)
     scratch = plan->packed_input_off + static_cast<size_t>(d->n) * g.h2 * g.wp * 32 +

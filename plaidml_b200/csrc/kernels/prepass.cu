@@ -183,32 +183,38 @@ s2d_pack_kernel(const uint16_t* __restrict__ in, uint4* __restrict__ out, long l
       }
     }
   }
-  const int swap = static_cast<int>(((static_cast<long long>(y2) * wp + x2) >> 2) & 1);
-  out[id * 2 + swap] = make_uint4(words[0], words[1], words[2], words[3]);
-  out[id * 2 + (swap ^ 1)] = make_uint4(words[4], words[5], words[6], words[7]);
+  // 128-byte swizzle over rows of four pixels: 16-byte chunk c of row number `row` goes to
+  // chunk c ^ (row & 7) (wp is a multiple of 32, so images start on whole 8-row groups)
+  const long long row = id >> 2;
+  const int c0 = static_cast<int>(id & 3) * 2;
+  const int x = static_cast<int>(row & 7);
+  out[row * 8 + (c0 ^ x)] = make_uint4(words[0], words[1], words[2], words[3]);
+  out[row * 8 + ((c0 + 1) ^ x)] = make_uint4(words[4], words[5], words[6], words[7]);
 }
 
 __global__ void __launch_bounds__(256)
 filter_s2d_kernel(const void* __restrict__ in, int in_dtype, void* __restrict__ out, int out_dtype,
                   int r, int s, int c, int k, int r2, int s2, int dh, int dw) {
   const int id = blockIdx.x * blockDim.x + threadIdx.x;
-  const int total = r2 * s2 * 64 * 16;
+  const int sg = (s2 + 3) / 4;                 // groups of four tap columns
+  const int total = r2 * sg * 64 * 64;
   if (id >= total) return;
-  // id walks the logical output [tap][ko][16]
-  const int ch = id & 15;
-  const int ko = (id >> 4) & 63;
-  const int tap = id >> 10;
-  const int tr = tap / s2, ts = tap - tr * s2;
+  // id walks the logical output [tr][tap-column group][ko][4 tap columns x 16 channels]
+  const int e = id & 63;
+  const int ko = (id >> 6) & 63;
+  const int blk = id >> 12;
+  const int tr = blk / sg, ts = (blk - tr * sg) * 4 + (e >> 4);
+  const int ch = e & 15;
   float v = 0.f;
-  if (ch < 4 * c && ko < k) {
+  if (ch < 4 * c && ko < k && ts < s2) {
     const int phase = ch / c, ci = ch - phase * c;
     const int fr = 2 * tr + (phase >> 1) - dh, fs = 2 * ts + (phase & 1) - dw;
     if (fr >= 0 && fr < r && fs >= 0 && fs < s) {
       v = load_filter(in, in_dtype, ((static_cast<long long>(fr) * s + fs) * c + ci) * k + ko);
     }
   }
-  // exchange the 16-byte halves (8 elements each) of rows whose number has bit 2 set
-  const int o = (id & ~15) | (ch ^ (((ko >> 2) & 1) << 3));
+  // 128-byte swizzle: 16-byte chunk number (e >> 3) exchanged with chunk ^ (row & 7)
+  const int o = (id & ~63) | ((((e >> 3) ^ (ko & 7)) << 3) | (e & 7));
   if (out_dtype == PMLB_BF16) {
     static_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
   } else {
@@ -237,7 +243,7 @@ cudaError_t launch_s2d_pack(const void* in, void* out, int n, int h, int w, int 
 
 cudaError_t launch_filter_s2d(const void* in, int in_dtype, void* out, int out_dtype, int r, int s,
                               int c, int k, int r2, int s2, int dh, int dw, cudaStream_t stream) {
-  const int total = r2 * s2 * 64 * 16;
+  const int total = r2 * ((s2 + 3) / 4) * 64 * 64;
   if (total <= 0) return cudaSuccess;
   filter_s2d_kernel<<<(total + 255) / 256, 256, 0, stream>>>(in, in_dtype, out, out_dtype, r, s, c, k,
                                                              r2, s2, dh, dw);

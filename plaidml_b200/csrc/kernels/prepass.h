@@ -36,15 +36,16 @@ cudaError_t launch_filter_pack_rows(const void* in, int in_dtype, void* out, int
 // Space-to-depth operands (16-bit elements) of the stride-2 route for thin inputs (c <= 4).
 // Activation [n][h][w][c] -> [n][h2][wp][16]: channel (py * 2 + px) * c + ci of pixel (y2, x2)
 // is input pixel (2 * y2 + py - pe_h, 2 * x2 + px - pe_w), zero outside the image and in the
-// unused channels.  Pixel number g = y2 * wp + x2 (wp a multiple of 8) has its two 16-byte
-// halves exchanged when bit 2 of g is set, which is the 32-byte shared-memory swizzle: an
-// untiled copy of whole pixels that starts at a multiple of eight pixels lands in operand layout.
+// unused channels.  wp is a multiple of 32; the result is stored in the 128-byte shared-memory
+// swizzle (rows of four pixels, 16-byte chunk c of row number j at chunk c ^ (j & 7)), so that an
+// untiled copy that starts at a multiple of 32 pixels lands in operand layout.
 cudaError_t launch_s2d_pack(const void* in, void* out, int n, int h, int w, int c, int h2, int wp,
                             int pe_h, int pe_w, cudaStream_t stream);
-// Filter [r][s][c][k] (f32, bf16 or f16) -> [r2 * s2][64][16] in the 16-bit `out_dtype`: row ko
-// of tap (tr, ts) holds, at channel (py * 2 + px) * c + ci, the weight of filter tap
-// (2 * tr + py - dh, 2 * ts + px - dw) (zero outside the filter, in the unused channels and in
-// rows ko >= k); rows are swizzled like the activation's pixels.
+// Filter [r][s][c][k] (f32, bf16 or f16) -> [r2][ceil(s2 / 4)][64][4][16] in the 16-bit
+// `out_dtype`: row ko of block (tr, group) holds, for tap column ts = 4 * group + j at channel
+// (py * 2 + px) * c + ci, the weight of filter tap (2 * tr + py - dh, 2 * ts + px - dw) (zero
+// outside the filter, in the unused channels and in rows ko >= k); every 64 x 128-byte block is
+// stored in the 128-byte shared-memory swizzle.
 cudaError_t launch_filter_s2d(const void* in, int in_dtype, void* out, int out_dtype, int r, int s,
                               int c, int k, int r2, int s2, int dh, int dw, cudaStream_t stream);
 

@@ -212,6 +212,15 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sr
       : "memory");
 }
 
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int x, int y,
+                                             int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      :
+      : "l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
 // Untiled copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) from global to
 // shared memory, completing on an mbarrier.
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes,
@@ -332,6 +341,34 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw32(uint32_t saddr, uint32_t
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= static_cast<uint64_t>(1) << 46;
   d |= static_cast<uint64_t>(6) << 61;
+  return d;
+}
+
+// Two floats -> packed 16-bit pair (lo in the low half), round to nearest even; the RELU forms
+// turn negative values into +0 in the same instruction (NaN stays NaN).
+template <bool BF16, bool RELU>
+__device__ __forceinline__ uint32_t cvt_pack16(float lo, float hi) {
+  uint32_t d;
+  if constexpr (BF16) {
+    if constexpr (RELU) {
+      asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    } else {
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    }
+  } else {
+    if constexpr (RELU) {
+      asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    } else {
+      asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    }
+  }
+  return d;
+}
+
+// max(x, 0) that keeps NaN (one instruction; -0 becomes +0)
+__device__ __forceinline__ float relu_keep_nan(float x) {
+  float d;
+  asm("max.NaN.f32 %0, %1, 0f00000000;" : "=f"(d) : "f"(x));
   return d;
 }
 

@@ -268,19 +268,19 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     using S2dCfg = TcCfg<2, 64, 1, kAS2d, false, 2, 2>;
     static_assert(S2dCfg::STAGES * S2dCfg::STAGE == kS2dSmemBytes, "space-to-depth budget");
     const int taps = g.r2 * g.s2;
-    const int wts_bytes = taps * 2048;
-    const int stage_bytes = (g.stage_px * 32 + 1023) / 1024 * 1024;
+    const int wts_bytes = g.r2 * ((g.s2 + 3) / 4) * 8192;
+    const int stage_bytes = g.stage_px * 32;
     // (the kernel has one pair of barriers per operand-ring stage of its instance)
-    const int stages = std::min(S2dCfg::STAGES, (kS2dSmemBytes - wts_bytes) / stage_bytes);
-    if (eb != 2 || L.nsplit != 1 || L.b_mn || L.n > 64 || L.n % 8 != 0 || g.wp % 8 != 0 || g.stage_px % 8 != 0 ||
-        g.stage_px < 128 + (g.r2 - 1) * g.wp + g.s2 - 1 || g.wp < g.q + g.s2 - 1 || g.h2 < g.p + g.r2 - 1 ||
-        stages < 3 || L.m != g.n * g.p * g.q || L.batch != 1 ||
+    const int stages = stage_bytes > 0 ? std::min(S2dCfg::STAGES, (kS2dSmemBytes - wts_bytes) / stage_bytes) : 0;
+    if (eb != 2 || L.nsplit != 1 || L.b_mn || L.n > 64 || L.n % 8 != 0 || g.wp % 32 != 0 || g.stage_px % 32 != 0 ||
+        g.stage_px < 512 + (g.r2 - 1) * g.wp + g.s2 - 1 || g.wp < g.q + g.s2 - 1 || g.h2 < g.p + g.r2 - 1 ||
+        g.q % 4 != 0 || stages < 2 || L.m != g.n * g.p * g.q || L.batch != 1 ||
         (L.epi_flags & (kEpiResidual | kEpiRowMax)) != 0) {
       *err = "space-to-depth convolution: geometry outside what the kernel takes";
       return 3;
     }
-    if ((reinterpret_cast<uintptr_t>(L.a0) & 255u) != 0 || (reinterpret_cast<uintptr_t>(L.b0) & 15u) != 0) {
-      *err = "space-to-depth convolution: packed operands must be 256- / 16-byte aligned";
+    if ((reinterpret_cast<uintptr_t>(L.a0) & 15u) != 0 || (reinterpret_cast<uintptr_t>(L.b0) & 15u) != 0) {
+      *err = "space-to-depth convolution: packed operands must be 16-byte aligned";
       return 1;
     }
     bn = 64;
@@ -292,13 +292,13 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     p.halo_wp = g.wp;
     p.halo_stage_bytes = stage_bytes;
     p.halo_stages = stages;
-    p.halo_tiles_per_img = (g.p * g.wp + 127) / 128;
+    p.halo_tiles_per_img = (g.p * g.wp + 511) / 512;
     p.s2d_px = L.a0;
     p.s2d_wts = L.b0;
     p.s2d_img_px = g.h2 * g.wp;
     p.s2d_stage_load = g.stage_px * 32;
     p.num_kb = taps;
-    p.batch = g.n * p.halo_tiles_per_img;     // tiles of 128 positions
+    p.batch = g.n * p.halo_tiles_per_img;     // tiles of 512 positions
     p.tiles_m = 1;
     p.tiles_n = 1;
     p.idesc = make_idesc(eb, L.is_f16, false, bn);
@@ -542,12 +542,21 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
       const uint64_t c_bs = L.batch > 1 ? static_cast<uint64_t>(L.out_batch_stride) * ob
                                         : static_cast<uint64_t>(L.ldc) * ob * L.m;
       if (L.s2d) {
-        // (channels, q, n * p); boxes of 8 output columns
+        // (channels, column % 4, column / 4, n * p); boxes of 8 columns that are 4 apart
         const S2dGeom& g = *L.s2d;
-        if (!encode3d(&tc_map, out_map_dtype(L.out_dtype), ob, L.out, L.n, g.q, static_cast<uint64_t>(g.n) * g.p,
-                      static_cast<uint64_t>(L.ldc) * ob, static_cast<uint64_t>(L.ldc) * ob * g.q, 128 / ob, 8, 1,
-                      err)) {
-          return 1;
+        const cuuint64_t pix = static_cast<cuuint64_t>(L.ldc) * ob;
+        cuuint64_t dims[4] = {static_cast<cuuint64_t>(L.n), 4, static_cast<cuuint64_t>(g.q / 4),
+                              static_cast<cuuint64_t>(g.n) * g.p};
+        cuuint64_t strides[3] = {pix, 4 * pix, pix * g.q};
+        cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / ob), 1, 8, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult r = g_encode_tiled(&tc_map, out_map_dtype(L.out_dtype), 4, L.out, dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+          *err = "cuTensorMapEncodeTiled (strided output columns) failed with code " +
+                 std::to_string(static_cast<int>(r));
+          return 2;
         }
       } else if (!encode3d(&tc_map, out_map_dtype(L.out_dtype), ob, L.out, L.n, L.m, L.batch,
                            static_cast<uint64_t>(L.ldc) * ob, c_bs, 128 / ob, 32, 1, err)) {

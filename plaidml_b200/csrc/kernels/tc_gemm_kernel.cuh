@@ -22,6 +22,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "ptx.cuh"
 #include "tc_gemm.cuh"
 
@@ -38,9 +40,14 @@ enum : int {
                  // fill) and every filter tap is read as a row-shifted window of that buffer;
                  // output positions in the padding columns are computed and discarded
   kAS2d = 4,     // a thin NHWC activation, stride-2 convolution, repacked by a pre-pass to 32-byte
-                 // pixels holding the 2 x 2 phases as channels (and already in the 32-byte
-                 // swizzle): a tile is 128 consecutive pixel positions, fetched with the pixels
-                 // its taps reach by one untiled bulk copy; taps are row-shifted windows as above
+                 // pixels holding the 2 x 2 phases as channels, four pixels to a 128-byte row
+                 // and already in the 128-byte swizzle.  A tile is 512 consecutive pixel
+                 // positions, fetched with the pixels its taps reach by one untiled bulk copy,
+                 // and has four accumulators: row i of accumulator a is position 4 * i + a, so
+                 // that the operand of a tap is the buffer read from byte 32 * (a + tap shift)
+                 // on, one 32-byte k-step of every 128-byte row (operand rows in any other
+                 // layout than 128-byte rows in the 128-byte swizzle were measured to feed the
+                 // tensor core at well under half the rate)
 };
 
 template <int EB, int BN_, int NSPLIT_, int A_MODE_, bool B_MN_, int OUT_BYTES_ = 4,
@@ -158,6 +165,14 @@ __device__ __forceinline__ void trace_event(const TcParams& p, int role, int& n,
   }
 }
 
+// The timeline records cost the roles several per cent even when no buffer is given (each is a
+// divergent branch): they are compiled in only with -DPMLB_TC_TRACE.
+#ifdef PMLB_TC_TRACE
+#define PMLB_TRACE_EVENT(...) trace_event(__VA_ARGS__)
+#else
+#define PMLB_TRACE_EVENT(...) ((void)0)
+#endif
+
 struct TileCoord {
   int b, tm, tn;
   int n0, bn;   // first output column and width of the tile (set by tile_coord_cta)
@@ -235,7 +250,7 @@ __device__ __forceinline__ TileCoord tile_coord_cta(const TcParams& p, int t, ui
 template <bool FULL, bool IS_INT, int OB, int CW>
 __device__ __forceinline__ float epi_apply(const TcParams& p, uint32_t (&v)[CW], int col0, int row,
                                            long long res_row, bool out_bf16, uint32_t res_smem,
-                                           int lane) {
+                                           int lane, bool relu_later) {
   // res_smem != 0: this warp's 32 x 128-byte residual rows lie in shared memory (swizzled like
   // the staged output; rows and columns outside the matrix hold zeros), else they are read
   // from global memory.
@@ -363,12 +378,10 @@ __device__ __forceinline__ float epi_apply(const TcParams& p, uint32_t (&v)[CW],
         }
       }
     }
-    if (p.epi_flags & kEpiRelu) {
+    // (16-bit outputs without a row maximum get their ReLU from the packing conversion)
+    if ((p.epi_flags & kEpiRelu) && !relu_later) {
 #pragma unroll
-      for (int j = 0; j < CW; ++j) {
-        const float x = __uint_as_float(v[j]);
-        v[j] = __float_as_uint(x < 0.f ? 0.f : x);
-      }
+      for (int j = 0; j < CW; ++j) v[j] = __float_as_uint(relu_keep_nan(__uint_as_float(v[j])));
     }
     if (p.epi_flags & kEpiRowMax) {
       // Balanced tree of hardware max operations.  For non-NaN values this equals the
@@ -433,7 +446,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
+      mbar_init(empty_bar(s), Cfg::A_S2D ? Cfg::ISSUERS : 1);   // (both issuers read a space-to-depth buffer)
     }
     for (int a = 0; a < Cfg::NACC; ++a) {
       mbar_init(tfull_bar(a), 1);
@@ -499,7 +512,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   // of fetched pixel buffers; halo_nb = k-blocks (taps x channel blocks) per tile
   const int halo_taps = p.conv_r * p.conv_s;
   const uint32_t halo_ring =
-      ring + (Cfg::A_S2D ? static_cast<uint32_t>(halo_taps) * 2048u
+      ring + (Cfg::A_S2D ? static_cast<uint32_t>(p.conv_r * ((p.conv_s + 3) / 4)) * 8192u
                          : static_cast<uint32_t>(halo_taps * p.conv_cblocks) * Cfg::B_TILE);
 
   if (warp == 0) {
@@ -512,13 +525,13 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     bool ok = true;
     int ntrace = 0;
     if constexpr (Cfg::A_S2D) {
-      // Weights of every tap, once: 64 rows of 32 bytes each.
-      const uint32_t wts_bytes = static_cast<uint32_t>(halo_taps) * 2048u;
+      // Weights of every tap, once: a 64-row block of 128-byte rows per four tap columns.
+      const uint32_t wts_bytes = static_cast<uint32_t>(p.conv_r * ((p.conv_s + 3) / 4)) * 8192u;
       if (leader) {
         mbar_arrive_expect_tx(wts_bar, wts_bytes);
         bulk_load_1d(ring, p.s2d_wts, wts_bytes, wts_bar);
       }
-      // One buffer per tile: the tile's 128 pixel positions and the pixels its taps reach are
+      // One buffer per tile: the tile's 512 pixel positions and the pixels its taps reach are
       // consecutive in the packed activation.
       const uint32_t nst = static_cast<uint32_t>(p.halo_stages);
       uint32_t hs = 0, hphase = 0;
@@ -531,9 +544,9 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           break;
         }
         if (leader) {
-          trace_event(p, 0, ntrace, t, 0);
+          PMLB_TRACE_EVENT(p, 0, ntrace, t, 0);
           const char* src = static_cast<const char*>(p.s2d_px) +
-                            (static_cast<long long>(img) * p.s2d_img_px + tt * 128) * 32;
+                            (static_cast<long long>(img) * p.s2d_img_px + tt * 512) * 32;
           mbar_arrive_expect_tx(full_bar(hs), static_cast<uint32_t>(p.s2d_stage_load));
           bulk_load_1d(halo_ring + hs * static_cast<uint32_t>(p.halo_stage_bytes), src,
                        static_cast<uint32_t>(p.s2d_stage_load), full_bar(hs));
@@ -567,7 +580,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
             break;
           }
           if (leader) {
-            trace_event(p, 0, ntrace, t, cb);
+            PMLB_TRACE_EVENT(p, 0, ntrace, t, cb);
             mbar_arrive_expect_tx(full_bar(hs), static_cast<uint32_t>(p.halo_wp * p.halo_rows) * 128u);
             tma_load_4d(halo_ring + hs * static_cast<uint32_t>(p.halo_stage_bytes), &tm.a0, full_bar(hs),
                         cb * BK, p.conv_lower_w, p0 + p.conv_lower_h, img);
@@ -606,7 +619,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
             break;
           }
           if (leader) {
-            trace_event(p, 0, ntrace, t, h);
+            PMLB_TRACE_EVENT(p, 0, ntrace, t, h);
             mbar_arrive_expect_tx(wfull_bar(slot), static_cast<uint32_t>(p.win_slot_bytes));
             tma_load_4d(win_slots + slot * static_cast<uint32_t>(p.win_slot_bytes), &tm.a0,
                         wfull_bar(slot), 0, wc.tm * 128, h, wc.img);
@@ -644,7 +657,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           const uint32_t s_a = ring + stage * Cfg::STAGE;
           const uint32_t s_b = s_a + NSPLIT * Cfg::A_TILE;
           if (leader) {
-            trace_event(p, 0, ntrace, t, kb);
+            PMLB_TRACE_EVENT(p, 0, ntrace, t, kb);
             if (CTAS == 1 || cta_rank == 0) mbar_arrive_expect_tx(fb, CTAS * Cfg::STAGE);
             if constexpr (Cfg::A_IM2COL) {
               tma_load_im2col_4d(s_a, &tm.a0, fb, cb * BK, pix_w, pix_h, pix_n,
@@ -734,73 +747,67 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         if (leader && *abort_code == 0) *abort_code = 3;
         ok = false;
       }
-      // 32-byte rows in the 32-byte swizzle, eight rows every 256 bytes; one MMA (K = 16
-      // elements = one pixel's channels) per tap.  As in the halo mode a window that starts a
-      // whole number of rows into the buffer takes the plain descriptor of its start address.
-      const uint64_t d32 = make_smem_desc_sw32(0, 16, 256);
-      const uint32_t d32_lo = static_cast<uint32_t>(d32), d32_hi = static_cast<uint32_t>(d32 >> 32);
-      int it = 0;
-      for (int t = t_begin; t < t_end && ok; t += t_step, ++it) {
-        if (it % Cfg::ISSUERS != iw) {
-          // the other issuer's tile: wait for its buffer too, so that the parity of later waits
-          // stays unambiguous
-          if (!mbar_wait_warp(full_bar(hs), hphase, abort_flag)) {
-            if (leader && *abort_code == 0) *abort_code = 3;
-            ok = false;
-          }
-          if (++hs == nst) {
-            hs = 0;
-            hphase ^= 1u;
-          }
-          continue;
-        }
-        acc = it % Cfg::NACC;
-        acc_phase = static_cast<uint32_t>(it / Cfg::NACC) & 1u;
-        if (leader && iw == 0) trace_event(p, 1, ntrace, t, 0);
-        if (!mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
-          if (leader && *abort_code == 0) *abort_code = 2;
-          break;
-        }
+      // Every issuer walks all tiles and issues the accumulators a = iw, iw + ISSUERS, ... of each:
+      // sub-tile number it = 4 * (tiles so far) + a uses accumulator a.  One MMA (K = 16 elements
+      // = one pixel's channels) per tap; the weights are ordinary K-major blocks, tap column ts
+      // being k-step ts % 4 of block ts / 4 of its tap row.
+      int itile = 0;
+      for (int t = t_begin; t < t_end && ok; t += t_step, ++itile) {
         if (!mbar_wait_warp(full_bar(hs), hphase, abort_flag)) {
           if (leader && *abort_code == 0) *abort_code = 3;
           ok = false;
           break;
         }
-        if (leader && iw == 0) trace_event(p, 1, ntrace, t, 1);
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         const uint32_t buf = halo_ring + hs * static_cast<uint32_t>(p.halo_stage_bytes);
-        // output position j reads packed pixel j + tr * wp + ts: descriptor low words advance by
-        // 2 (one 32-byte row) per tap column, wp * 2 per tap row, the weights' by 128 per tap
-        uint32_t a_row = lo_at(d32_lo, buf);
-        uint32_t b_lo = lo_at(d32_lo, ring);
         const uint32_t a_row_step = static_cast<uint32_t>(p.halo_wp) * 2u;
-        uint32_t first = 0u;
-        for (int tr = 0; tr < p.conv_r; ++tr) {
-          uint32_t a_lo = a_row;
-          int ts = 0;
-          for (; ts + 4 <= p.conv_s; ts += 4) {
-            if (leader) tc_mma_x4<Cfg::KIND, 1>(d_tmem, a_lo, b_lo, d32_hi, d32_hi, p.idesc, first, 2u, 128u);
-            first = 1u;
-            a_lo += 8u;
-            b_lo += 512u;
+        for (int a = iw; a < 4 && ok; a += Cfg::ISSUERS) {
+          acc_phase = static_cast<uint32_t>(itile) & 1u;
+          if (leader && iw == 0) PMLB_TRACE_EVENT(p, 1, ntrace, t, 0);
+          if (!mbar_wait_warp(tempty_bar(a), acc_phase ^ 1u, abort_flag)) {
+            if (leader && *abort_code == 0) *abort_code = 2;
+            ok = false;
+            break;
           }
-          for (; ts < p.conv_s; ++ts) {
-            if (leader) {
-              tc_mma<Cfg::KIND>(d_tmem, (static_cast<uint64_t>(d32_hi) << 32) | a_lo,
-                                (static_cast<uint64_t>(d32_hi) << 32) | b_lo, p.idesc, first);
+          if (leader && iw == 0) PMLB_TRACE_EVENT(p, 1, ntrace, t, 1);
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(a * BN);
+          // position 4 * i + a reads packed pixel 4 * i + a + tr * wp + ts: descriptor low words
+          // (16-byte units) start 2 * a into the buffer and advance by 2 per tap column, wp * 2
+          // per tap row
+          uint32_t a_row = lo_at(dk_lo, buf) + 2u * static_cast<uint32_t>(a);
+          uint32_t b_blk = lo_at(dk_lo, ring);
+          uint32_t first = 0u;
+          for (int tr = 0; tr < p.conv_r; ++tr) {
+            uint32_t a_lo = a_row;
+            int ts = 0;
+            for (; ts + 4 <= p.conv_s; ts += 4) {
+              if (leader) tc_mma_x4<Cfg::KIND, 1>(d_tmem, a_lo, b_blk, dk_hi, dk_hi, p.idesc, first, 2u, 2u);
+              first = 1u;
+              a_lo += 8u;
+              b_blk += 512u;
             }
-            first = 1u;
-            a_lo += 2u;
-            b_lo += 128u;
+            if (ts < p.conv_s) {
+              uint32_t b_lo = b_blk;
+              for (; ts < p.conv_s; ++ts) {
+                if (leader) {
+                  tc_mma<Cfg::KIND>(d_tmem, (static_cast<uint64_t>(dk_hi) << 32) | a_lo,
+                                    (static_cast<uint64_t>(dk_hi) << 32) | b_lo, p.idesc, first);
+                }
+                first = 1u;
+                a_lo += 2u;
+                b_lo += 2u;
+              }
+              b_blk += 512u;
+            }
+            a_row += a_row_step;
           }
-          a_row += a_row_step;
+          if (leader) {
+            tc_commit(tfull_bar(a));
+            if (iw == 0) PMLB_TRACE_EVENT(p, 1, ntrace, t, 3);
+          }
         }
-        if (leader) {
-          tc_commit(empty_bar(hs));
-          tc_commit(tfull_bar(acc));
-          if (iw == 0) trace_event(p, 1, ntrace, t, 3);
-        }
+        if (!ok) break;
+        if (leader) tc_commit(empty_bar(hs));
         if (++hs == nst) {
           hs = 0;
           hphase ^= 1u;
@@ -840,12 +847,12 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         hs = static_cast<uint32_t>(hsi);
         acc = it % Cfg::NACC;
         acc_phase = static_cast<uint32_t>(it / Cfg::NACC) & 1u;
-        if (leader && iw == 0) trace_event(p, 1, ntrace, t, 0);
+        if (leader && iw == 0) PMLB_TRACE_EVENT(p, 1, ntrace, t, 0);
         if (!mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
           if (leader && *abort_code == 0) *abort_code = 2;
           break;
         }
-        if (leader && iw == 0) trace_event(p, 1, ntrace, t, 1);
+        if (leader && iw == 0) PMLB_TRACE_EVENT(p, 1, ntrace, t, 1);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int cb = 0; cb < p.conv_cblocks && ok; ++cb) {
@@ -864,7 +871,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           const uint32_t b_step = static_cast<uint32_t>(p.conv_cblocks) * (Cfg::B_TILE >> 4);
           const uint32_t a_row_step = static_cast<uint32_t>(p.halo_wp) * 8u;
           uint32_t first = cb > 0 ? 1u : 0u;
-          if (leader && iw == 0 && cb == 0) trace_event(p, 1, ntrace, t, 2);
+          if (leader && iw == 0 && cb == 0) PMLB_TRACE_EVENT(p, 1, ntrace, t, 2);
           for (int fr = 0; fr < p.conv_r; ++fr) {
             uint32_t a_lo = a_row;
             for (int fs = 0; fs < p.conv_s; ++fs) {
@@ -885,7 +892,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         if (!ok) break;
         if (leader) {
           tc_commit(tfull_bar(acc));
-          if (iw == 0) trace_event(p, 1, ntrace, t, 3);
+          if (iw == 0) PMLB_TRACE_EVENT(p, 1, ntrace, t, 3);
         }
       }
     } else if constexpr (Cfg::A_WINDOW) {
@@ -928,7 +935,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           const uint32_t a_lo = lo_at(dk_lo, win_slots + slot * static_cast<uint32_t>(p.win_slot_bytes));
           const uint32_t b_lo = lo_at(dk_lo, win_wts + r * Cfg::B_TILE);
           if (leader) {
-            if (r == 0) trace_event(p, 1, ntrace, t, 2);
+            if (r == 0) PMLB_TRACE_EVENT(p, 1, ntrace, t, 2);
             tc_mma_x4<Cfg::KIND, 1>(d_tmem, a_lo, b_lo, dk_hi, dk_hi, p.idesc, r > 0 ? 1u : 0u, 2u, 2u);
           }
           if (++slot == nslots) slot = 0;
@@ -940,7 +947,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
             if (++rs == nslots) rs = 0;
           }
           tc_commit(tfull_bar(acc));
-          trace_event(p, 1, ntrace, t, 3);
+          PMLB_TRACE_EVENT(p, 1, ntrace, t, 3);
         }
         cnt_end = c0 + p.win_r;
         if (++acc == 2) {
@@ -967,12 +974,12 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         }
         acc = it % Cfg::NACC;
         acc_phase = static_cast<uint32_t>(it / Cfg::NACC) & 1u;
-        if (leader && iw == 0) trace_event(p, 1, ntrace, t, 0);
+        if (leader && iw == 0) PMLB_TRACE_EVENT(p, 1, ntrace, t, 0);
         if (!mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
           if (leader && *abort_code == 0) *abort_code = 2;
           break;
         }
-        if (leader && iw == 0) trace_event(p, 1, ntrace, t, 1);
+        if (leader && iw == 0) PMLB_TRACE_EVENT(p, 1, ntrace, t, 1);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         const uint32_t idesc = t >= p.tiles_full ? p.idesc_half : p.idesc;   // half-width tail tiles
@@ -992,7 +999,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           constexpr uint32_t kStepA = 2u;
           constexpr uint32_t kStepB = Cfg::B_MN ? (Cfg::UMMA_K * 128u) >> 4 : 2u;
           if (leader) {
-            if (kb == 0 && iw == 0) trace_event(p, 1, ntrace, t, 2);
+            if (kb == 0 && iw == 0) PMLB_TRACE_EVENT(p, 1, ntrace, t, 2);
             if constexpr (NSPLIT == 2) {
               // fp32 as three TF32 products; the two cross terms first.
               const uint64_t a_lo = desc_at(desc_k, s_a + Cfg::A_TILE);
@@ -1028,7 +1035,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           } else {
             tc_commit(tfull_bar(acc));
           }
-          if (iw == 0) trace_event(p, 1, ntrace, t, 3);
+          if (iw == 0) PMLB_TRACE_EVENT(p, 1, ntrace, t, 3);
         }
       }
     }
@@ -1052,19 +1059,38 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       uint32_t nreq = 0;
       bool alive = true;
       const bool out_bf16 = p.out_dtype == kDtBF16;
+      const bool relu_in_cvt = OB == 2 && !IS_INT && (p.epi_flags & kEpiRelu) && !(p.epi_flags & kEpiRowMax);
       int it = 0;
       int ntrace = 0;
       const bool tracer = (ew & 3) == 0 && lane == 0;   // first warp of each group
-      for (int t = t_begin; t < t_end && alive; t += t_step, ++it) {
+      // (space-to-depth tiles have four accumulators each: `it` then counts those)
+      constexpr int SUBS = Cfg::A_S2D ? 4 : 1;
+      for (;; ++it) {
+        const int t = t_begin + (it / SUBS) * t_step;
+        if (t >= t_end || !alive) break;
         if (G == 2 && (it & 1) != grp) continue;
         const int acc = it % Cfg::NACC;
         const uint32_t acc_phase = static_cast<uint32_t>(it / Cfg::NACC) & 1u;
-        const TileCoord tc = tile_coord_cta<Cfg>(p, t, cta_rank);
+        TileCoord tc;
+        if constexpr (Cfg::A_S2D || Cfg::A_HALO) {
+          tc.b = t;
+          tc.tm = tc.tn = tc.n0 = 0;
+          tc.bn = BN;
+        } else {
+          tc = tile_coord_cta<Cfg>(p, t, cta_rank);
+        }
         int row0 = tc.tm * 128 + q * 32;
         int row = row0 + lane;
+        // space-to-depth: image row / column of this warp's first position, first output row of the image
+        int s2d_op0 = 0, s2d_oq0 = 0, s2d_row0 = 0;
         if constexpr (Cfg::A_S2D) {
           row0 = 0;   // (no per-row epilogue inputs in this mode; the store maps rows itself)
           row = 0;
+          const int img = t / p.halo_tiles_per_img;
+          const int g0 = (t - img * p.halo_tiles_per_img) * 512 + q * 128;
+          s2d_op0 = g0 / p.halo_wp;
+          s2d_oq0 = g0 - s2d_op0 * p.halo_wp;
+          s2d_row0 = img * p.conv_p;
         }
         if constexpr (Cfg::A_HALO) {
           // accumulator row j = output position j of the tile: image row j / wp, column j % wp;
@@ -1098,12 +1124,12 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           request_res(0);
           request_res(1);
         }
-        if (tracer) trace_event(p, 2 + grp, ntrace, t, 0);
+        if (tracer) PMLB_TRACE_EVENT(p, 2 + grp, ntrace, t, 0);
         if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
           if (*abort_code == 0) *abort_code = 4;
           break;
         }
-        if (tracer) trace_event(p, 2 + grp, ntrace, t, 1);
+        if (tracer) PMLB_TRACE_EVENT(p, 2 + grp, ntrace, t, 1);
         tc_fence_after_sync();
         const uint32_t t_acc =
             tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(q * 32) << 16);
@@ -1156,8 +1182,8 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           }
           const float chunk_best =
               (col0 + CW <= p.n)
-                  ? epi_apply<true, IS_INT, OB, CW>(p, v, col0, row, res_row, out_bf16, res_smem, lane)
-                  : epi_apply<false, IS_INT, OB, CW>(p, v, col0, row, res_row, out_bf16, res_smem, lane);
+                  ? epi_apply<true, IS_INT, OB, CW>(p, v, col0, row, res_row, out_bf16, res_smem, lane, relu_in_cvt)
+                  : epi_apply<false, IS_INT, OB, CW>(p, v, col0, row, res_row, out_bf16, res_smem, lane, relu_in_cvt);
           if (p.epi_flags & kEpiRowMax) row_best = fmaxf(row_best, chunk_best);
           // (with TMA-fetched residuals every chunk is stored, rows past M being clipped by
           // the store, so that buffers and barriers stay in step with the requests)
@@ -1169,21 +1195,24 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
             for (int i = 0; i < 8; ++i) o[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
           } else {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              uint32_t w[4];
+            auto pack_all = [&](auto bf16, auto relu) {
 #pragma unroll
-              for (int h = 0; h < 4; ++h) {
-                const float x0 = __uint_as_float(v[8 * i + 2 * h]);
-                const float x1 = __uint_as_float(v[8 * i + 2 * h + 1]);
-                if (out_bf16) {
-                  const __nv_bfloat162 pk = __floats2bfloat162_rn(x0, x1);
-                  w[h] = *reinterpret_cast<const uint32_t*>(&pk);
-                } else {
-                  const __half2 pk = __floats2half2_rn(x0, x1);
-                  w[h] = *reinterpret_cast<const uint32_t*>(&pk);
+              for (int i = 0; i < 8; ++i) {
+                uint32_t w[4];
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                  w[h] = cvt_pack16<decltype(bf16)::value, decltype(relu)::value>(
+                      __uint_as_float(v[8 * i + 2 * h]), __uint_as_float(v[8 * i + 2 * h + 1]));
                 }
+                o[i] = make_uint4(w[0], w[1], w[2], w[3]);
               }
-              o[i] = make_uint4(w[0], w[1], w[2], w[3]);
+            };
+            using T = std::true_type;
+            using F = std::false_type;
+            if (out_bf16) {
+              if (relu_in_cvt) pack_all(T{}, T{}); else pack_all(T{}, F{});
+            } else {
+              if (relu_in_cvt) pack_all(F{}, T{}); else pack_all(F{}, F{});
             }
           }
           if constexpr (Cfg::A_HALO) {
@@ -1210,20 +1239,23 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           __syncwarp();
           if (lane == 0) {
             if constexpr (Cfg::A_S2D) {
-              // The warp's 32 rows are positions g0 .. g0 + 31 of the image's padded position
-              // grid (wp a multiple of 8 per image row): every run of 8 lies in one image row
-              // and goes out as one box of the (channels, q, n * p) output map, which clips
-              // the columns from q on; runs in the padding columns or below the image are
-              // skipped.
-              const int img = t / p.halo_tiles_per_img;
-              const int g0 = (t - img * p.halo_tiles_per_img) * 128 + q * 32;
+              // Row i of accumulator a is position 512 * tile + 4 * i + a of the image's padded
+              // position grid (wp a multiple of 32 per image row).  The output map is
+              // (channels, 4, q / 4, n * p) with output column 4 * c2 + c1 at (c1, c2): the
+              // warp's rows 8 * b .. 8 * b + 7 are one box at c1 = a, c2 = column / 4 of one
+              // image row; boxes in the padding columns or below the image are skipped, the
+              // map clips the rest.
+              const int a = it & 3;
+              int op = s2d_op0, oq = s2d_oq0;
 #pragma unroll
               for (int b = 0; b < 4; ++b) {
-                const int g = g0 + 8 * b;
-                const int op = g / p.halo_wp;
-                const int oq = g - op * p.halo_wp;
                 if (op < p.conv_p && oq < p.conv_q) {
-                  tma_store_3d(&tm.c, buf + static_cast<uint32_t>(b) * 1024u, col0, oq, img * p.conv_p + op);
+                  tma_store_4d(&tm.c, buf + static_cast<uint32_t>(b) * 1024u, col0, a, oq >> 2, s2d_row0 + op);
+                }
+                oq += 32;
+                if (oq >= p.halo_wp) {
+                  oq -= p.halo_wp;
+                  ++op;
                 }
               }
             } else {
@@ -1261,10 +1293,10 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
             issue_load(va, ch);
             tmem_ld_wait();
             pin(va);
-            if (tracer) trace_event(p, 2 + grp, ntrace, t, 10 + ch);
+            if (tracer) PMLB_TRACE_EVENT(p, 2 + grp, ntrace, t, 10 + ch);
             if (ch == nch - 1) release_acc();
             process(va, ch);
-            if (tracer) trace_event(p, 2 + grp, ntrace, t, 30 + ch);
+            if (tracer) PMLB_TRACE_EVENT(p, 2 + grp, ntrace, t, 30 + ch);
           }
         }
         if (p.epi_flags & kEpiRowMax) {

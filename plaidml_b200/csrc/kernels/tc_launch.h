@@ -35,13 +35,13 @@ struct HaloGeom {
 };
 
 // Space-to-depth convolution (stride 2, thin input): a0 is the packed activation [n][h2][wp][16]
-// (followed by at least stage_px * 32 readable bytes), b0 the packed weights [r2 * s2][64][16],
-// both already in the 32-byte swizzle; the output is [n][p][q][k_out].
+// (followed by at least stage_px * 32 readable bytes), b0 the packed weights [r2][ceil(s2 / 4)][64][64],
+// both already in the 128-byte swizzle; the output is [n][p][q][k_out], q a multiple of 4.
 struct S2dGeom {
   int n, p, q;
   int r2, s2;     // taps of the stride-1 form
-  int h2, wp;     // rows per packed image, pixels per row (a multiple of 8)
-  int stage_px;   // pixels a 128-position tile reads (a multiple of 8)
+  int h2, wp;     // rows per packed image, pixels per row (a multiple of 32)
+  int stage_px;   // pixels a 512-position tile reads (a multiple of 32)
 };
 
 struct TcLaunch {

@@ -175,11 +175,11 @@ def test_packed_rows_residual_f32_and_bf16():
 
 @pytest.mark.parametrize("case", [
     dict(n=3, h=40, w=40, c=3, r=7, s=7, k=64, stride=2, pad=3),      # ResNet's first layer at a small size
-    dict(n=2, h=33, w=45, c=4, r=5, s=5, k=48, stride=2, pad=2),      # odd extents, k < 64, even padding
+    dict(n=2, h=33, w=47, c=4, r=5, s=5, k=48, stride=2, pad=2),      # odd extents, k < 64, even padding
     dict(n=3, h=24, w=24, c=3, r=7, s=7, k=64, stride=2, same_upper=True),   # more padding after than before
     dict(n=2, h=31, w=50, c=1, r=3, s=3, k=8, stride=2, pad=0),       # one channel, no padding
     dict(n=2, h=20, w=22, c=2, r=4, s=2, k=16, stride=2, pad=1),      # even filter extents, odd padding
-    dict(n=40, h=64, w=64, c=3, r=7, s=7, k=64, stride=2, pad=3),     # 440 tiles: the ring wraps, both issuers work
+    dict(n=160, h=64, w=64, c=3, r=7, s=7, k=64, stride=2, pad=3),    # 640 tiles: the ring wraps several times
 ], ids=["stem", "ragged", "same_upper", "one_channel", "even_filter", "many"])
 def test_s2d_route_matches_oracle_and_packed_rows(case):
     out, ref, plan = run_conv(80, **case)
@@ -195,9 +195,13 @@ def test_s2d_route_bias_relu_bf16_out():
                               epilogue=K.EPI_BIAS | K.EPI_RELU)
     assert plan.kernel == "tc_conv_s2d"
     check_close(out, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
-    # a residual input is outside the route: the layer falls through to packed rows
+    # a residual input, or an output width that is not a multiple of 4, is outside the route: the layer falls
+    # through to packed rows
     _, _, plan = run_conv(82, 2, 20, 20, 3, 3, 3, 64, stride=2, epilogue=K.EPI_RESIDUAL)
     assert plan.kernel == "tc_conv_rows"
+    out, ref, plan = run_conv(83, 2, 33, 45, 4, 5, 5, 48, stride=2, pad=2)
+    assert plan.kernel == "tc_conv_rows"
+    check_close(out, ref, 1e-4)
 
 
 # --- halo route (stride 1, 64 output channels, weights resident) ----------------------------------
