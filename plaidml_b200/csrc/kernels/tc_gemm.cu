@@ -580,6 +580,17 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     }
   }
 
+  {
+    auto fd = [](long long d) { return make_fastdiv(static_cast<uint32_t>(std::max<long long>(1, d))); };
+    p.fd_per_batch = fd(static_cast<long long>(p.tiles_m) * p.tiles_n);
+    p.fd_group = fd(static_cast<long long>(p.group_m) * p.tiles_n);
+    p.fd_gm_full = fd(p.group_m);
+    p.fd_gm_tail = fd(p.tiles_m % p.group_m);
+    p.fd_per_img = fd(static_cast<long long>(p.conv_p) * p.conv_q);
+    p.fd_q = fd(p.conv_q);
+    p.fd_tiles_per_img = fd(p.halo_tiles_per_img);
+    p.fd_wp = fd(p.halo_wp);
+  }
   const long long total = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n;
   if (total > 0x3fffffffLL) {
     *err = "too many tiles";

@@ -23,6 +23,28 @@ enum : int {
   kEpiRowMax = 8,    // do not store the tile; fold it into rowmax[row] with atomic max
 };
 
+// Division by a launch-time constant as a multiplication: n / d for 0 <= n < 2^31.  (A runtime
+// integer division is a chain of some thirty dependent instructions; the roles of the kernel run
+// as single warps whose dependent instructions issue several cycles apart.)
+struct FastDiv {
+  uint32_t mul, shift;
+};
+
+inline FastDiv make_fastdiv(uint32_t d) {
+  uint32_t s = 0;
+  while ((1ull << s) < d) ++s;
+  FastDiv f;
+  f.shift = 31 + s;
+  f.mul = static_cast<uint32_t>(((1ull << f.shift) + d - 1) / d);
+  return f;
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ int fast_div(int n, FastDiv f) {
+  return static_cast<int>((static_cast<unsigned long long>(static_cast<uint32_t>(n)) * f.mul) >> f.shift);
+}
+#endif
+
 struct TcParams {
   // Problem (per batch entry): C[m, n] = sum_k A[m, k] * B[n, k]
   int m, n, k, batch;
@@ -30,6 +52,10 @@ struct TcParams {
   int tiles_full;        // tiles walked whole; the rest (the tail of the last wave) as two half-width tiles each
   int num_kb;            // k-blocks (of 128 bytes of K) per tile
   int group_m;           // m-tiles per rasterisation group (L2 reuse of B panels)
+  // divisors of the tile-number arithmetic: tiles per batch entry, tiles per rasterisation group,
+  // m-tiles of a full group and of the last (shorter) one, output pixels per image, output
+  // columns, halo / space-to-depth tiles per image and positions per padded image row
+  FastDiv fd_per_batch, fd_group, fd_gm_full, fd_gm_tail, fd_per_img, fd_q, fd_tiles_per_img, fd_wp;
   int a_bz, b_bz;        // 1: operand has a batch dimension, 0: one matrix shared by all entries
 
   // Implicit-GEMM convolution (A fetched by im2col TMA); unused for plain GEMM.

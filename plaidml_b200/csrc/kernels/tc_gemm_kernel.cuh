@@ -181,15 +181,17 @@ struct TileCoord {
 __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int t) {
   const int per_batch = p.tiles_m * p.tiles_n;
   TileCoord c;
-  c.b = t / per_batch;
+  c.b = fast_div(t, p.fd_per_batch);
   const int r = t - c.b * per_batch;
   const int group = p.group_m * p.tiles_n;
-  const int g = r / group;
+  const int g = fast_div(r, p.fd_group);
   const int first_m = g * p.group_m;
-  const int gm = min(p.group_m, p.tiles_m - first_m);
   const int rr = r - g * group;
-  c.tm = first_m + rr % gm;
-  c.tn = rr / gm;
+  // a full group has group_m m-tiles, the last one of a batch entry the remainder
+  const bool full = first_m + p.group_m <= p.tiles_m;
+  const int gm = full ? p.group_m : p.tiles_m - first_m;
+  c.tn = fast_div(rr, full ? p.fd_gm_full : p.fd_gm_tail);
+  c.tm = first_m + rr - c.tn * gm;
   return c;
 }
 
@@ -536,7 +538,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       const uint32_t nst = static_cast<uint32_t>(p.halo_stages);
       uint32_t hs = 0, hphase = 0;
       for (int t = t_begin; t < t_end && ok; t += t_step) {
-        const int img = t / p.halo_tiles_per_img;
+        const int img = fast_div(t, p.fd_tiles_per_img);
         const int tt = t - img * p.halo_tiles_per_img;
         if (!mbar_wait_warp(empty_bar(hs), hphase ^ 1u, abort_flag)) {
           if (leader && *abort_code == 0) *abort_code = 1;
@@ -571,7 +573,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       const uint32_t nst = static_cast<uint32_t>(p.halo_stages);
       uint32_t hs = 0, hphase = 0;
       for (int t = t_begin; t < t_end && ok; t += t_step) {
-        const int img = t / p.halo_tiles_per_img;
+        const int img = fast_div(t, p.fd_tiles_per_img);
         const int p0 = (t - img * p.halo_tiles_per_img) * p.halo_th;
         for (int cb = 0; cb < p.conv_cblocks; ++cb) {
           if (!mbar_wait_warp(empty_bar(hs), hphase ^ 1u, abort_flag)) {
@@ -639,9 +641,9 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         if constexpr (Cfg::A_IM2COL) {
           const int m0 = tc.tm * 128;
           const int per_img = p.conv_p * p.conv_q;
-          pix_n = m0 / per_img;
+          pix_n = fast_div(m0, p.fd_per_img);
           const int rem = m0 - pix_n * per_img;
-          const int op = rem / p.conv_q;
+          const int op = fast_div(rem, p.fd_q);
           const int oq = rem - op * p.conv_q;
           pix_w = p.conv_lower_w + oq * p.conv_stride_w;
           pix_h = p.conv_lower_h + op * p.conv_stride_h;
@@ -1086,19 +1088,19 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         if constexpr (Cfg::A_S2D) {
           row0 = 0;   // (no per-row epilogue inputs in this mode; the store maps rows itself)
           row = 0;
-          const int img = t / p.halo_tiles_per_img;
+          const int img = fast_div(t, p.fd_tiles_per_img);
           const int g0 = (t - img * p.halo_tiles_per_img) * 512 + q * 128;
-          s2d_op0 = g0 / p.halo_wp;
+          s2d_op0 = fast_div(g0, p.fd_wp);
           s2d_oq0 = g0 - s2d_op0 * p.halo_wp;
           s2d_row0 = img * p.conv_p;
         }
         if constexpr (Cfg::A_HALO) {
           // accumulator row j = output position j of the tile: image row j / wp, column j % wp;
           // columns past q (the padding columns) and rows past the image are not outputs
-          const int img = t / p.halo_tiles_per_img;
+          const int img = fast_div(t, p.fd_tiles_per_img);
           const int p0 = (t - img * p.halo_tiles_per_img) * p.halo_th;
           const int j = q * 32 + lane;
-          const int pr = j / p.halo_wp;
+          const int pr = fast_div(j, p.fd_wp);
           const int qq = j - pr * p.halo_wp;
           const bool valid = pr < p.halo_th && qq < p.conv_q && p0 + pr < p.conv_p;
           row0 = 0;
@@ -1185,6 +1187,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
                   ? epi_apply<true, IS_INT, OB, CW>(p, v, col0, row, res_row, out_bf16, res_smem, lane, relu_in_cvt)
                   : epi_apply<false, IS_INT, OB, CW>(p, v, col0, row, res_row, out_bf16, res_smem, lane, relu_in_cvt);
           if (p.epi_flags & kEpiRowMax) row_best = fmaxf(row_best, chunk_best);
+          if (tracer) PMLB_TRACE_EVENT(p, 2 + grp, ntrace, t, 40);
           // (with TMA-fetched residuals every chunk is stored, rows past M being clipped by
           // the store, so that buffers and barriers stay in step with the requests)
           if (!res_tma && (p.out == nullptr || row0 >= p.m)) return;   // warp-uniform
@@ -1228,8 +1231,10 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           }
           // the buffer used two chunks ago must have been read by its TMA store (already
           // true when its residual rows were requested)
+          if (tracer) PMLB_TRACE_EVENT(p, 2 + grp, ntrace, t, 41);
           if (!res_tma && lane == 0) bulk_wait_group_read<1>();
           __syncwarp();
+          if (tracer) PMLB_TRACE_EVENT(p, 2 + grp, ntrace, t, 42);
           const uint32_t buf = stage_buf + (nbuf & 1u) * 4096u;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -1237,6 +1242,7 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           }
           fence_proxy_async_smem();
           __syncwarp();
+          if (tracer) PMLB_TRACE_EVENT(p, 2 + grp, ntrace, t, 43);
           if (lane == 0) {
             if constexpr (Cfg::A_S2D) {
               // Row i of accumulator a is position 512 * tile + 4 * i + a of the image's padded
