@@ -4,6 +4,10 @@
 // with warp shuffles; none of them touches the tensor cores.
 #include "reduce.h"
 
+#include <type_traits>
+
+#include "tc_gemm.cuh"
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
@@ -200,6 +204,76 @@ pool_kernel(const T* __restrict__ in, T* __restrict__ out, PoolGeom g) {
   }
 }
 
+// Max / min pooling of 16-bit floats on packed pairs: the window's 16-byte groups are combined
+// with two-wide max / min instructions in the storage type (no conversion: max and min are
+// exact), a quarter of the instructions of the generic kernel, which is bound by instruction
+// issue.  One block row (blockIdx.x) per output image row, so that only the position inside
+// the row needs a division.  For NaN-free inputs the result equals the compare-and-select
+// chain of the definition; a NaN operand is skipped rather than propagated in visiting order.
+template <class T2, int AGG>
+__device__ __forceinline__ uint32_t combine16x2(uint32_t acc, uint32_t v) {
+  const T2 a = *reinterpret_cast<const T2*>(&acc);
+  const T2 b = *reinterpret_cast<const T2*>(&v);
+  const T2 r = (AGG == PMLB_AGG_MAX) ? __hmax2(a, b) : __hmin2(a, b);
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+template <class T2, int AGG, bool K3X3>
+__global__ void __launch_bounds__(256)
+pool16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, PoolGeom g, FastDiv fd_cv,
+              FastDiv fd_p, uint32_t identity2) {
+  const int cv = g.c / 8;
+  const int pos = blockIdx.y * 256 + threadIdx.x;       // (x, channel group) inside the output row
+  if (pos >= g.q * cv) return;
+  const int x = fast_div(pos, fd_cv);
+  const int cg = pos - x * cv;
+  const int row = blockIdx.x;                           // n * p + y
+  const int n = fast_div(row, fd_p);
+  const int y = row - n * g.p;
+  uint32_t acc[4] = {identity2, identity2, identity2, identity2};
+  const int iy0 = y * g.stride_h - g.pad_h, ix0 = x * g.stride_w - g.pad_w;
+  const uint4* base = in + (static_cast<long long>(n) * g.h * g.w) * cv + cg;
+  const int r = K3X3 ? 3 : g.r, s = K3X3 ? 3 : g.s;
+#pragma unroll
+  for (int fr = 0; fr < r; ++fr) {
+    const int iy = iy0 + fr;
+    if (iy < 0 || iy >= g.h) continue;
+#pragma unroll
+    for (int fs = 0; fs < s; ++fs) {
+      const int ix = ix0 + fs;
+      if (ix < 0 || ix >= g.w) continue;
+      const uint4 a = __ldg(base + (static_cast<long long>(iy) * g.w + ix) * cv);
+      acc[0] = combine16x2<T2, AGG>(acc[0], a.x);
+      acc[1] = combine16x2<T2, AGG>(acc[1], a.y);
+      acc[2] = combine16x2<T2, AGG>(acc[2], a.z);
+      acc[3] = combine16x2<T2, AGG>(acc[3], a.w);
+    }
+  }
+  out[(static_cast<long long>(row) * g.q + x) * cv + cg] = make_uint4(acc[0], acc[1], acc[2], acc[3]);
+}
+
+template <class T2>
+cudaError_t launch_pool16(const PoolGeom& g, const void* in, void* out, uint32_t neg_inf2,
+                          uint32_t pos_inf2, cudaStream_t stream) {
+  const int cv = g.c / 8;
+  const long long rows = static_cast<long long>(g.n) * g.p;
+  const long long per_row = static_cast<long long>(g.q) * cv;
+  if (rows > 0x7fffffffLL || (per_row + 255) / 256 > 65535) return cudaErrorInvalidValue;
+  dim3 grid(static_cast<unsigned>(rows), static_cast<unsigned>((per_row + 255) / 256));
+  const FastDiv fc = make_fastdiv(static_cast<uint32_t>(cv)), fp = make_fastdiv(static_cast<uint32_t>(g.p));
+  const uint4* ip = static_cast<const uint4*>(in);
+  uint4* op = static_cast<uint4*>(out);
+  const bool k3 = g.r == 3 && g.s == 3;
+  if (g.agg == PMLB_AGG_MAX) {
+    if (k3) pool16_kernel<T2, PMLB_AGG_MAX, true><<<grid, 256, 0, stream>>>(ip, op, g, fc, fp, neg_inf2);
+    else pool16_kernel<T2, PMLB_AGG_MAX, false><<<grid, 256, 0, stream>>>(ip, op, g, fc, fp, neg_inf2);
+  } else {
+    if (k3) pool16_kernel<T2, PMLB_AGG_MIN, true><<<grid, 256, 0, stream>>>(ip, op, g, fc, fp, pos_inf2);
+    else pool16_kernel<T2, PMLB_AGG_MIN, false><<<grid, 256, 0, stream>>>(ip, op, g, fc, fp, pos_inf2);
+  }
+  return cudaGetLastError();
+}
+
 template <class T, class TO, bool VEC>
 cudaError_t launch_reduce_t(int agg, const void* in, void* out, long long outer, long long red,
                             long long inner, float scale, cudaStream_t stream) {
@@ -255,6 +329,18 @@ cudaError_t launch_pool_v(const PoolGeom& g, const void* in, void* out, cudaStre
   constexpr int N = 16 / sizeof(T);
   const bool vec = (g.c % N == 0) && (reinterpret_cast<uintptr_t>(in) & 15u) == 0 &&
                    (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
+  if constexpr (sizeof(T) == 2) {
+    // 16-bit floats, max / min: packed-pair kernel (falls through if the grid would not fit)
+    if (vec && (g.agg == PMLB_AGG_MAX || g.agg == PMLB_AGG_MIN)) {
+      cudaError_t e;
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        e = launch_pool16<__nv_bfloat162>(g, in, out, 0xFF80FF80u, 0x7F807F80u, stream);
+      } else {
+        e = launch_pool16<__half2>(g, in, out, 0xFC00FC00u, 0x7C007C00u, stream);
+      }
+      if (e != cudaErrorInvalidValue) return e;
+    }
+  }
   return vec ? launch_pool_t<T, true>(g, in, out, stream) : launch_pool_t<T, false>(g, in, out, stream);
 }
 

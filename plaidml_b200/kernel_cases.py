@@ -12,6 +12,7 @@ launches of the kernel of interest:
     f32_1k     fp32 Tile GEMM 1024^3 via three TF32 products
     conv3      conv 3x3 56x56 64->64 + bias + ReLU, batch 16
     conv3_full the same at batch 128
+    conv1x1    conv 1x1 56x56 64->256 + bias + ReLU, batch 64 (HBM-bound: 26 MB in, 103 MB out)
     qk         batched Q.K^T 128 x (512x512x64) + row max (folded into the GEMM's epilogue)
     rowmax     row max alone over a 256 x 512 x 512 f32 tensor (row_reduce_kernel, 256 MiB)
     stem       the first two layers of ResNet-50 at batch 32: 7x7 / 2 convolution on 3 channels
@@ -56,6 +57,11 @@ def main(argv) -> None:
         f = f32_to_bf16_bits(g.standard_normal((3, 3, 64, 64)) * np.sqrt(2.0 / 576))
         r = Runner(programs.conv_bias_relu(n, 56, 56, 64, 64, filt=f, bias=np.zeros(64, np.float32)), "cuda.0")
         ins = [f32_to_bf16_bits(g.uniform(0, 1, (n, 56, 56, 64)))]
+    elif case == "conv1x1":
+        f = f32_to_bf16_bits(g.standard_normal((1, 1, 64, 256)) * np.sqrt(2.0 / 64))
+        r = Runner(programs.conv_bias_relu(64, 56, 56, 64, 256, r=1, s=1, filt=f, bias=np.zeros(256, np.float32)),
+                   "cuda.0")
+        ins = [f32_to_bf16_bits(g.uniform(0, 1, (64, 56, 56, 64)))]
     elif case == "qk":
         Q, Kt, S = programs.tile_gemm(DType.BFLOAT16, 512, 512, 64, acc=DType.FLOAT32, batch=128, b_transposed=True)
         bb, i, j = TensorIndexes(3)
