@@ -212,6 +212,10 @@ typedef struct {
  * runs the stride-1 form with resident weights).  This flag sends them down the next route that
  * accepts them (packed rows, else im2col). */
 #define PMLB_CONV_NO_S2D 4
+/* im2col route: CTA pairs (two CTAs on one 256-pixel tile, each fetching half of the tile's
+ * weights) always where the shape allows / never; without either flag the library chooses. */
+#define PMLB_CONV_CTA_PAIRS 8
+#define PMLB_CONV_NO_CTA_PAIRS 16
 
 pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* desc, pmlb_plan** plan);
 

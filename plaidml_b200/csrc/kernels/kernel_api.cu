@@ -622,6 +622,8 @@ pmlb_status pmlb_conv_invoke(pmlb_plan* plan, void* stream, const void* input, v
   L.ldr = d.k;
   L.status = plan->status;
   L.bn_override = d.tile_n;
+  if (d.flags & PMLB_CONV_CTA_PAIRS) L.pair_override = 1;
+  if (d.flags & PMLB_CONV_NO_CTA_PAIRS) L.pair_override = 0;
   L.trace = g_trace_buffer;
   std::string err;
   const int rc = pmlb::tc_launch(L, static_cast<cudaStream_t>(stream), &err);

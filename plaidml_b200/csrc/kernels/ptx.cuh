@@ -201,6 +201,20 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorM
       : "memory");
 }
 
+// The same from either CTA of a pair, completing on a barrier of the cluster (an address made
+// with mapa): both CTAs' loads count on the first CTA's barrier.
+__device__ __forceinline__ void tma_load_im2col_4d_pair(uint32_t dst, const CUtensorMap* map,
+                                                        uint32_t bar_cluster, int c, int w, int h,
+                                                        int n, uint16_t off_w, uint16_t off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(c), "r"(w), "r"(h),
+        "r"(n), "h"(off_w), "h"(off_h)
+      : "memory");
+}
+
 // Tiled 3-D store from shared memory (bulk async-group completion).  Elements outside the
 // tensor are not written.  Coordinates must not be negative.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y,

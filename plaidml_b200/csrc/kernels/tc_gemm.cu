@@ -209,10 +209,18 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   int groups = (L.conv ? 0 : num_kb_plain) <= 24 ? 2 : 1;
   // CTA pairs: plain GEMMs whose 256-wide tiles have long main loops and fill the machine.
   bool pair = false;
-  const bool pair_possible = !L.conv && !L.window && !L.halo && !L.s2d && L.nsplit == 1 && bn == 256;
-  if (pair_possible && num_kb_plain > 24 && L.m >= 256) {
+  const bool pair_possible = !L.window && !L.halo && !L.s2d && L.nsplit == 1 && !(L.conv && L.b_mn) &&
+                             (bn == 256 || (L.conv && bn == 128 && eb == 2));
+  if (pair_possible && !L.conv && num_kb_plain > 24 && L.m >= 256) {
     const long long pair_tiles =
         static_cast<long long>(L.batch) * ((L.m + 255) / 256) * ((L.n + 255) / 256);
+    pair = pair_tiles * 2 >= num_sms;
+  }
+  // Convolutions with several taps are bound by the operand traffic from L2 to shared memory
+  // (A and B tiles of every tap and channel block): a pair fetches each weight tile once per
+  // 256 pixels.  Their main loops are long enough for the single epilogue group of a pair.
+  if (pair_possible && L.conv && L.conv->r * L.conv->s > 1 && num_kb_plain >= 9 && L.m >= 256) {
+    const long long pair_tiles = static_cast<long long>((L.m + 255) / 256) * ((L.n + bn - 1) / bn);
     pair = pair_tiles * 2 >= num_sms;
   }
   if (L.pair_override == 0) pair = false;
@@ -480,7 +488,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     // weights [k_out][taps][c]
     const int taps = g.r * g.s;
     if (!encode3d(&tb0, dt, eb, L.b0, g.c, taps, L.n, static_cast<uint64_t>(g.c) * eb,
-                  static_cast<uint64_t>(g.c) * taps * eb, bk, 1, bn, err)) {
+                  static_cast<uint64_t>(g.c) * taps * eb, bk, 1, pair ? bn / 2 : bn, err)) {
       return 1;
     }
     tb1 = tb0;
@@ -634,7 +642,8 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     launched = true;                                                                            \
   }
 #define PMLB_TC_CASE_PAIR(EB, BN, NS, IM, MN, OB, G)                                            \
-  if (!launched && pair && eb == EB && bn == BN && L.b_mn == MN && ob_tmpl == OB) {             \
+  if (!launched && pair && eb == EB && bn == BN && a_mode == static_cast<int>(IM) &&            \
+      L.b_mn == MN && ob_tmpl == OB) {                                                          \
     ce = launch_cfg<TcCfg<EB, BN, NS, IM, MN, OB, G, 2>>(maps, p, grid, stream);                \
     launched = true;                                                                            \
   }

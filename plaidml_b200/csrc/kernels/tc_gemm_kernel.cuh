@@ -97,8 +97,8 @@ struct TcCfg {
   static constexpr int B_CHUNKS = (BN / CTAS_) / BK;  // MN-major: chunks of 128 bytes of N per CTA
   static_assert(STAGES >= 2, "ring too small");
   static_assert(!B_MN || ((BN / CTAS_) % BK == 0), "MN-major B needs whole chunks per CTA");
-  static_assert(CTAS_ == 1 || (CTAS_ == 2 && A_MODE_ == kATiled && NSPLIT_ == 1),
-                "CTA pairs serve plain 8/16-bit GEMMs");
+  static_assert(CTAS_ == 1 || (CTAS_ == 2 && (A_MODE_ == kATiled || A_MODE_ == kAIm2col) && NSPLIT_ == 1),
+                "CTA pairs serve plain 8/16-bit GEMMs and im2col convolutions");
 };
 
 __device__ __forceinline__ float atomic_max_float(float* addr, float v) {
@@ -661,7 +661,15 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           if (leader) {
             PMLB_TRACE_EVENT(p, 0, ntrace, t, kb);
             if (CTAS == 1 || cta_rank == 0) mbar_arrive_expect_tx(fb, CTAS * Cfg::STAGE);
-            if constexpr (Cfg::A_IM2COL) {
+            if constexpr (Cfg::A_IM2COL && CTAS == 2) {
+              // this CTA's 128 pixels and its half of the tile's output channels
+              const uint32_t fb0 = mapa_rank(fb, 0);
+              tma_load_im2col_4d_pair(s_a, &tm.a0, fb0, cb * BK, pix_w, pix_h, pix_n,
+                                      static_cast<uint16_t>(fs * p.conv_dil_w),
+                                      static_cast<uint16_t>(fr * p.conv_dil_h));
+              tma_load_3d_pair(s_b, &tm.b0, fb0, cb * BK, tap,
+                               tc.n0 + static_cast<int>(cta_rank) * (tc.bn / 2));
+            } else if constexpr (Cfg::A_IM2COL) {
               tma_load_im2col_4d(s_a, &tm.a0, fb, cb * BK, pix_w, pix_h, pix_n,
                                  static_cast<uint16_t>(fs * p.conv_dil_w),
                                  static_cast<uint16_t>(fr * p.conv_dil_h));

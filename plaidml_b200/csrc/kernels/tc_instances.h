@@ -52,4 +52,8 @@
   X(2, 256, 1, 0, true, 4, 1)       \
   X(2, 256, 1, 0, true, 2, 1)       \
   X(1, 256, 1, 0, false, 4, 1)      \
-  X(1, 256, 1, 0, true, 4, 1)
+  X(1, 256, 1, 0, true, 4, 1)       \
+  X(2, 256, 1, 1, false, 4, 1)      \
+  X(2, 256, 1, 1, false, 2, 1)      \
+  X(2, 128, 1, 1, false, 4, 1)      \
+  X(2, 128, 1, 1, false, 2, 1)

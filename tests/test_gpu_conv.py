@@ -129,6 +129,30 @@ def test_conv_rejects_odd_channels():
     assert e.value.status == K.ERR_UNSUPPORTED
 
 
+# --- CTA pairs on the im2col route (two CTAs per 256-pixel tile, each fetching half of the weights) ---
+
+@pytest.mark.parametrize("case", [
+    dict(n=3, h=20, w=20, c=128, r=3, s=3, k=128),                    # 128-wide tiles; 1200 pixels: ragged last pair
+    dict(n=5, h=14, w=14, c=256, r=3, s=3, k=256),                    # 256-wide tiles
+    dict(n=2, h=9, w=11, c=64, r=3, s=3, k=512, stride=2),            # two column tiles, stride 2, 60 pixels (one CTA idle)
+    dict(n=40, h=14, w=14, c=128, r=3, s=3, k=384),                   # 31 pair tiles x 2 column tiles, last one half-width
+], ids=["n128", "n256", "stride2", "ragged_n"])
+def test_conv_cta_pairs_match_oracle_and_single_ctas(case):
+    pairs, ref, _ = run_conv(95, flags=K.CONV_CTA_PAIRS, **case)
+    check_close(pairs, ref, 1e-4)
+    single, _, _ = run_conv(95, flags=K.CONV_NO_CTA_PAIRS, **case)
+    check_close(pairs, single, 1e-5)
+
+
+def test_conv_cta_pairs_bf16_epilogue_and_default_choice():
+    out, ref, _ = run_conv(96, 7, 7, 7, 512, 3, 3, 512, out_dtype=K.BF16, epilogue=K.EPI_BIAS | K.EPI_RELU,
+                           flags=K.CONV_CTA_PAIRS)
+    check_close(out, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+    # large enough for the library to pair CTAs by itself (74 pair tiles and more)
+    out, ref, _ = run_conv(97, 24, 28, 28, 128, 3, 3, 128, out_dtype=K.BF16, epilogue=K.EPI_BIAS | K.EPI_RESIDUAL | K.EPI_RELU)
+    check_close(out, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+
+
 # --- packed-row route (thin inputs: the first layer of image networks) -------------------------
 
 def test_stem_conv7x7_stride2_three_channels():
