@@ -211,7 +211,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   bool pair = false;
   const bool pair_possible = !L.window && !L.halo && !L.s2d && L.nsplit == 1 && !(L.conv && L.b_mn) &&
                              (bn == 256 || (L.conv && bn == 128 && eb == 2));
-  if (pair_possible && !L.conv && num_kb_plain > 24 && L.m >= 256) {
+  if (pair_possible && !L.conv && num_kb_plain >= 16 && L.m >= 256) {
     const long long pair_tiles =
         static_cast<long long>(L.batch) * ((L.m + 255) / 256) * ((L.n + 255) / 256);
     pair = pair_tiles * 2 >= num_sms;
