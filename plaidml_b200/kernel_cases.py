@@ -16,7 +16,7 @@ launches of the kernel of interest:
     qk         batched Q.K^T 128 x (512x512x64) + row max (folded into the GEMM's epilogue)
     rowmax     row max alone over a 256 x 512 x 512 f32 tensor (row_reduce_kernel, 256 MiB)
     stem       the first two layers of ResNet-50 at batch 32: 7x7 / 2 convolution on 3 channels
-               (pack_rows_kernel + tc_contract_kernel, packed rows) and the 3x3 / 2 max pool (pool_kernel)
+               (s2d_pack_kernel + tc_contract_kernel, space-to-depth route) and the 3x3 / 2 max pool (pool16_kernel)
     resnet N   ResNet-50 v1.5 at batch N
 """
 
