@@ -1219,6 +1219,7 @@ Executable::~Executable() {
   cudaSetDevice(device_);
   if (stream_) cudaStreamSynchronize(stream_);
   for (pmlb_plan* q : slicePlans_) pmlb_plan_free(q);
+  for (pmlb_plan* q : blockPlans_) pmlb_plan_free(q);
   for (cudaEvent_t ev : sliceDone_) cudaEventDestroy(ev);
   if (copyStream_) cudaStreamDestroy(copyStream_);
   if (graphExec_) cudaGraphExecDestroy(graphExec_);
@@ -1352,7 +1353,10 @@ double Executable::run(const std::vector<BufferPtr>& inputs, const std::vector<B
 // A program that is one large GEMM from a host input to a host output is bound by the host link,
 // not by the kernel.  Its rows are then processed in four slices: while slice i's rows of C travel
 // device -> host on a second stream, slice i + 1's rows of A travel host -> device, so the two
-// directions of the link overlap instead of taking turns.  Same kernels, same results.
+// directions of the link overlap instead of taking turns.  When B comes from the host as well, the
+// first row slice is further cut into four column blocks, each computed as soon as its quarter of
+// B has arrived: the download (the longer direction) then starts after a quarter of A and a quarter
+// of B instead of after a quarter of A and all of B.  Same kernels, same results.
 bool Executable::prepareSlicedRun() {
   constexpr int kSlices = 4;
   if (steps_.size() != 1 || !steps_[0].rowSliceable || prog_->outputs.size() != 1) return false;
@@ -1373,8 +1377,28 @@ bool Executable::prepareSlicedRun() {
     }
     slicePlans_.push_back(plan);
   }
+  // column blocks of the first slice, if B is a program input
+  for (size_t i = 0; i < prog_->inputs.size(); ++i) {
+    if (static_cast<int>(i) != st.aInput && dev_[prog_->inputs[i]] == st.bPtr) bInput_ = static_cast<int>(i);
+  }
+  if (bInput_ >= 0 && d.n % (kSlices * 256) == 0 && d.ldc == d.n && d.ldb == (d.b_is_nk ? d.k : d.n)) {
+    for (int j = 0; j < kSlices; ++j) {
+      pmlb_gemm_desc bd = d;
+      bd.m = d.m / kSlices;
+      bd.n = d.n / kSlices;
+      pmlb_plan* plan = nullptr;
+      if (pmlb_gemm_dispatch(&bd, &plan) != PMLB_OK || pmlb_plan_share_status(plan, status_) != PMLB_OK) {
+        if (plan) pmlb_plan_free(plan);
+        for (pmlb_plan* q : blockPlans_) pmlb_plan_free(q);
+        blockPlans_.clear();
+        break;
+      }
+      blockPlans_.push_back(plan);
+    }
+  }
+  if (blockPlans_.empty()) bInput_ = -1;
   if (cudaStreamCreateWithFlags(&copyStream_, cudaStreamNonBlocking) != cudaSuccess) return false;
-  for (int i = 0; i < kSlices; ++i) {
+  for (int i = 0; i < 2 * kSlices; ++i) {
     cudaEvent_t ev = nullptr;
     if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return false;
     sliceDone_.push_back(ev);
@@ -1388,7 +1412,7 @@ double Executable::runSliced(const std::vector<BufferPtr>& inputs, const std::ve
   const int slices = static_cast<int>(slicePlans_.size());
   const auto t0 = std::chrono::steady_clock::now();
   for (size_t i = 0; i < inputs.size(); ++i) {
-    if (static_cast<int>(i) == st.aInput) continue;
+    if (static_cast<int>(i) == st.aInput || static_cast<int>(i) == bInput_) continue;
     const int id = prog_->inputs[i];
     const size_t bytes = prog_->values[id].shape.byteSize();
     if (bytes) cudaCheck(cudaMemcpyAsync(dev_[id], inputs[i]->data(), bytes, cudaMemcpyHostToDevice, stream_), "input upload");
@@ -1396,7 +1420,40 @@ double Executable::runSliced(const std::vector<BufferPtr>& inputs, const std::ve
   const int aId = prog_->inputs[st.aInput], cId = prog_->outputs[st.cOutput];
   const size_t aBytes = prog_->values[aId].shape.byteSize() / slices;
   const size_t cBytes = prog_->values[cId].shape.byteSize() / slices;
-  for (int i = 0; i < slices; ++i) {
+  int first = 0;
+  if (bInput_ >= 0) {
+    // first row slice by column blocks: A's rows, then a quarter of B at a time
+    const int blocks = static_cast<int>(blockPlans_.size());
+    const int bId = prog_->inputs[bInput_];
+    const size_t eb = prog_->values[bId].shape.byteSize() / (static_cast<size_t>(d.n) * d.k);
+    const size_t ob = prog_->values[cId].shape.byteSize() / (static_cast<size_t>(d.m) * d.n);
+    const size_t nb = static_cast<size_t>(d.n) / blocks;          // columns per block
+    const char* bHost = static_cast<const char*>(inputs[bInput_]->data());
+    char* cHost = static_cast<char*>(outputs[st.cOutput]->data());
+    cudaCheck(cudaMemcpyAsync(dev_[aId], inputs[st.aInput]->data(), aBytes, cudaMemcpyHostToDevice, stream_), "input upload");
+    for (int j = 0; j < blocks; ++j) {
+      size_t bOff;
+      if (d.b_is_nk) {   // B stored [n][k]: a block of columns is a run of whole rows
+        bOff = nb * j * d.k * eb;
+        cudaCheck(cudaMemcpyAsync(dev_[bId] + bOff, bHost + bOff, nb * d.k * eb, cudaMemcpyHostToDevice, stream_), "input upload");
+      } else {           // B stored [k][n]: a block of columns is a pitched rectangle
+        bOff = nb * j * eb;
+        cudaCheck(cudaMemcpy2DAsync(dev_[bId] + bOff, d.n * eb, bHost + bOff, d.n * eb, nb * eb, d.k,
+                                    cudaMemcpyHostToDevice, stream_), "input upload");
+      }
+      char* cDev = dev_[cId] + nb * j * ob;
+      const void* bias = st.biasPtr ? static_cast<const char*>(st.biasPtr) + nb * j * 4 : nullptr;
+      const pmlb_status rc = pmlb_gemm_invoke(blockPlans_[j], stream_, dev_[aId], dev_[bId] + bOff, cDev, bias, nullptr, nullptr);
+      if (rc != PMLB_OK) throw std::runtime_error("Kernel step '" + st.kernel + " " + st.detail + "' failed: " + pmlb_last_error());
+      cudaEvent_t ev = sliceDone_[slices + j];
+      cudaCheck(cudaEventRecord(ev, stream_), "cudaEventRecord");
+      cudaCheck(cudaStreamWaitEvent(copyStream_, ev, 0), "cudaStreamWaitEvent");
+      cudaCheck(cudaMemcpy2DAsync(cHost + nb * j * ob, d.n * ob, cDev, d.n * ob, nb * ob, d.m / slices,
+                                  cudaMemcpyDeviceToHost, copyStream_), "output download");
+    }
+    first = 1;
+  }
+  for (int i = first; i < slices; ++i) {
     char* aDev = dev_[aId] + aBytes * i;
     char* cDev = dev_[cId] + cBytes * i;
     cudaCheck(cudaMemcpyAsync(aDev, static_cast<const char*>(inputs[st.aInput]->data()) + aBytes * i, aBytes,
@@ -1409,7 +1466,6 @@ double Executable::runSliced(const std::vector<BufferPtr>& inputs, const std::ve
                               cudaMemcpyDeviceToHost, copyStream_), "output download");
   }
   inputsResident_ = true;
-  (void)d;
   cudaCheck(cudaStreamSynchronize(copyStream_), "run");
   checkStatus();
   const auto t1 = std::chrono::steady_clock::now();

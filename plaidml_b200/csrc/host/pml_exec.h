@@ -88,6 +88,8 @@ class Executable {
   // Sliced run of a single-GEMM program (see Executable::runSliced): 0 = not tried, 1 = in use, 2 = off.
   int slicedState_ = 0;
   std::vector<pmlb_plan*> slicePlans_;
+  std::vector<pmlb_plan*> blockPlans_;   // column blocks of the first row slice (B is a host input too)
+  int bInput_ = -1;                      // index of B among the program's inputs, or -1
   std::vector<cudaEvent_t> sliceDone_;
   cudaStream_t copyStream_ = nullptr;
 };

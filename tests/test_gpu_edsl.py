@@ -109,6 +109,27 @@ def test_full_size_int8_gemm_through_the_sliced_run():
     np.testing.assert_array_equal(sliced[rows], oracle.gemm_i8_i32(np.ascontiguousarray(a[rows]), b))
 
 
+@pytest.mark.parametrize("b_transposed", [False, True], ids=["B_kn", "B_nk"])
+def test_bf16_gemm_sliced_run_with_column_blocks(b_transposed):
+    # B is a host input as well: the first row slice is computed in four column blocks, each after its quarter of B
+    # (a pitched rectangle of B[k][n], a run of rows of B[n][k]); results must equal the single-pass run exactly
+    g = rng(1241)
+    m, n, k = 4096, 4096, 192
+    a = f32_to_bf16_bits(g.standard_normal((m, k)))
+    b = f32_to_bf16_bits(g.standard_normal((n, k) if b_transposed else (k, n)))
+    A, B, C = P.tile_gemm(DType.BFLOAT16, m, n, k, acc=DType.FLOAT32, out_bf16=True, b_transposed=b_transposed)
+    sliced = Runner(Program("gemm_bf16_blocks", [A, B], [C]), "cuda.0").run([a, b])[0]
+    core.settings_set("PLAIDML_CUDA_SLICED_RUN", "0")
+    try:
+        whole = Runner(Program("gemm_bf16_blocks", [A, B], [C]), "cuda.0").run([a, b])[0]
+    finally:
+        core.settings_set("PLAIDML_CUDA_SLICED_RUN", "1")
+    np.testing.assert_array_equal(sliced, whole)
+    af, bf = oracle.bf16_to_f32(a[:8]), oracle.bf16_to_f32(b)
+    ref = af @ (bf.T if b_transposed else bf)
+    check_close(oracle.bf16_to_f32(sliced[:8]), oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+
+
 def test_int8_without_casts_wraps_like_the_reference():
     g = rng(1236)
     a = g.integers(-128, 128, size=(64, 48), dtype=np.int8)
