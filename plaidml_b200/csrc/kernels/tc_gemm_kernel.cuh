@@ -1067,6 +1067,33 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       // arrival barrier k & 1 in phase (k >> 1) & 1.  `nreq` counts the chunks requested.
       const bool res_tma = p.res_tma != 0;
       uint32_t nreq = 0;
+      // The requests run ahead of the processing across tile boundaries: a cursor walks this
+      // group's tiles and their chunks in processing order, and before a chunk is processed the
+      // one after it (the next tile's first chunk after a tile's last) is requested, so that
+      // every chunk's rows have about one chunk's processing time to arrive.
+      int rq_t = t_begin + (G == 2 ? grp : 0) * t_step, rq_ch = 0;
+      bool rq_valid = res_tma && rq_t < t_end;
+      TileCoord rq_tc;
+      if (rq_valid) rq_tc = tile_coord_cta<Cfg>(p, rq_t, cta_rank);
+      auto request_ahead = [&](uint32_t upto) {       // until `upto` chunks have been requested
+        while (nreq < upto && rq_valid) {
+          const int c0 = rq_tc.n0 + rq_ch * CW;
+          if (c0 < p.n) {                            // warp-uniform
+            if (lane == 0) {
+              const uint32_t b = nreq & 1u;
+              mbar_arrive_expect_tx(res_bar(ew, b), 4096u);
+              tma_load_3d(stage_buf + b * 4096u, &tm.r, res_bar(ew, b), c0, rq_tc.tm * 128 + q * 32, rq_tc.b);
+            }
+            ++nreq;
+          }
+          if (++rq_ch >= rq_tc.bn / CW || c0 + CW >= p.n) {
+            rq_ch = 0;
+            rq_t += G * t_step;
+            rq_valid = rq_t < t_end;
+            if (rq_valid) rq_tc = tile_coord_cta<Cfg>(p, rq_t, cta_rank);
+          }
+        }
+      };
       bool alive = true;
       const bool out_bf16 = p.out_dtype == kDtBF16;
       const bool relu_in_cvt = OB == 2 && !IS_INT && (p.epi_flags & kEpiRelu) && !(p.epi_flags & kEpiRowMax);
@@ -1116,23 +1143,12 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
         }
         const int col_base = tc.n0;
         const int nch = tc.bn / CW;                 // chunks of this tile
-        auto request_res = [&](int ch) {
-          const int c0 = col_base + ch * CW;
-          if (ch < nch && c0 < p.n) {                // warp-uniform
-            if (lane == 0) {
-              const uint32_t b = nreq & 1u;
-              mbar_arrive_expect_tx(res_bar(ew, b), 4096u);
-              tma_load_3d(stage_buf + b * 4096u, &tm.r, res_bar(ew, b), c0, row0, tc.b);
-            }
-            ++nreq;
-          }
-        };
-        if (res_tma) {
+        if (res_tma && nreq < nbuf + 2 && rq_valid) {
           // Both buffers are free once the stores of the previous tile have read them; the
-          // first two chunks' residual rows then arrive while the main loop still runs.
+          // first two chunks' residual rows then arrive while the main loop still runs (in
+          // the steady state the first was requested during the previous tile's last chunk).
           if (lane == 0) bulk_wait_group_read<0>();
-          request_res(0);
-          request_res(1);
+          request_ahead(nbuf + 2);
         }
         if (tracer) PMLB_TRACE_EVENT(p, 2 + grp, ntrace, t, 0);
         if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
@@ -1177,11 +1193,10 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           if (col0 >= p.n || !alive) return;          // warp-uniform
           uint32_t res_smem = 0;
           if (res_tma) {
-            // Chunk ch + 1 takes the buffer chunk ch - 1 was stored from (chunks 0 and 1
-            // were requested at the start of the tile).
-            if (ch >= 1) {
+            // The chunk after this one takes the buffer the chunk before this one was stored from.
+            if (nreq < nbuf + 2 && rq_valid) {
               if (lane == 0) bulk_wait_group_read<0>();
-              request_res(ch + 1);
+              request_ahead(nbuf + 2);
             }
             if (!mbar_wait(res_bar(ew, nbuf & 1u), (nbuf >> 1) & 1u, abort_flag)) {
               if (*abort_code == 0) *abort_code = 5;
