@@ -883,7 +883,7 @@ class Planner {
            << " in=" << dtypeName(static_cast<DType>(pd.gemm.in_dtype)) << " out=" << dtypeName(static_cast<DType>(pd.gemm.out_dtype))
            << (pd.gemm.b_is_nk ? " B[n][k]" : " B[k][n]") << pd.fused;
         st.detail = os.str();
-        st.launches = 1 + (pd.gemm.in_dtype == PMLB_F32 ? 2 : 0) + (pd.rowmax >= 0 ? 1 : 0);
+        st.launches = 1 + (pd.gemm.in_dtype == PMLB_F32 ? 1 : 0) + (pd.rowmax >= 0 ? 1 : 0);   // (+ the TF32 split of both operands, + the row-max fill)
         const void* a = dev(pd.a);
         const void* b = dev(pd.b);
         void* c = pd.storeMain ? dev(pd.result) : nullptr;

@@ -362,20 +362,13 @@ pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream_v, const void* a, con
     float* a_lo = a_hi + a_mats * d.m * kp;
     float* b_hi = a_lo + a_mats * d.m * kp;
     float* b_lo = b_hi + b_mats * d.n * kp;
-    cudaError_t e = pmlb::launch_split_tf32(static_cast<const float*>(a), d.lda, d.stride_a, a_hi,
-                                            a_lo, kp, static_cast<long long>(d.m) * kp, d.m, d.k,
-                                            static_cast<int>(a_mats), false, stream);
-    if (e != cudaSuccess) return cuda_fail(e, "split(A)");
-    if (d.b_is_nk) {
-      e = pmlb::launch_split_tf32(static_cast<const float*>(b), d.ldb, d.stride_b, b_hi, b_lo, kp,
-                                  static_cast<long long>(d.n) * kp, d.n, d.k,
-                                  static_cast<int>(b_mats), false, stream);
-    } else {
-      e = pmlb::launch_split_tf32(static_cast<const float*>(b), d.ldb, d.stride_b, b_hi, b_lo, kp,
-                                  static_cast<long long>(d.n) * kp, d.k, d.n,
-                                  static_cast<int>(b_mats), true, stream);
-    }
-    if (e != cudaSuccess) return cuda_fail(e, "split(B)");
+    pmlb::SplitTf32Args sa{static_cast<const float*>(a), d.lda, d.stride_a, a_hi, a_lo, kp,
+                           static_cast<long long>(d.m) * kp, d.m, d.k, static_cast<int>(a_mats), false};
+    pmlb::SplitTf32Args sb{static_cast<const float*>(b), d.ldb, d.stride_b, b_hi, b_lo, kp,
+                           static_cast<long long>(d.n) * kp, d.b_is_nk ? d.n : d.k, d.b_is_nk ? d.k : d.n,
+                           static_cast<int>(b_mats), !d.b_is_nk};
+    cudaError_t e = pmlb::launch_split_tf32_pair(sa, sb, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "split(A, B)");
     L.nsplit = 2;
     L.a0 = a_hi;
     L.a1 = a_lo;

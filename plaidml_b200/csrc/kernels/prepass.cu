@@ -18,16 +18,42 @@ __device__ __forceinline__ float tf32_round(float x) {
 
 // 32x32 tiles through shared memory so that both the read and the (possibly transposed)
 // write are row-contiguous.
+__device__ __forceinline__ void split_tf32_tile(float (&tile)[32][33], int b, int bx, int by,
+                                                const float* __restrict__ in, long long ld,
+                                                long long in_batch, float* __restrict__ hi,
+                                                float* __restrict__ lo, long long out_ld,
+                                                long long out_batch, int rows, int cols, bool transpose);
+
 __global__ void __launch_bounds__(256)
 split_tf32_kernel(const float* __restrict__ in, long long ld, long long in_batch,
                   float* __restrict__ hi, float* __restrict__ lo, long long out_ld,
                   long long out_batch, int rows, int cols, bool transpose) {
   __shared__ float tile[32][33];
-  const int b = blockIdx.z;
+  split_tf32_tile(tile, blockIdx.z, blockIdx.x, blockIdx.y, in, ld, in_batch, hi, lo, out_ld, out_batch, rows,
+                  cols, transpose);
+}
+
+// blockIdx.z < a.batch: a tile of operand a, else of operand b; tiles outside an operand's
+// (padded) extent return at once.
+__global__ void __launch_bounds__(256)
+split_tf32_pair_kernel(SplitTf32Args a, SplitTf32Args b, int a_gx, int a_gy, int b_gx, int b_gy) {
+  __shared__ float tile[32][33];
+  const bool first = static_cast<int>(blockIdx.z) < a.batch;
+  const SplitTf32Args& s = first ? a : b;
+  if (static_cast<int>(blockIdx.x) >= (first ? a_gx : b_gx) || static_cast<int>(blockIdx.y) >= (first ? a_gy : b_gy)) return;
+  split_tf32_tile(tile, first ? blockIdx.z : blockIdx.z - a.batch, blockIdx.x, blockIdx.y, s.in, s.ld, s.in_batch,
+                  s.hi, s.lo, s.out_ld, s.out_batch, s.rows, s.cols, s.transpose);
+}
+
+__device__ __forceinline__ void split_tf32_tile(float (&tile)[32][33], int b, int bx, int by,
+                                                const float* __restrict__ in, long long ld,
+                                                long long in_batch, float* __restrict__ hi,
+                                                float* __restrict__ lo, long long out_ld,
+                                                long long out_batch, int rows, int cols, bool transpose) {
   const float* src = in + static_cast<long long>(b) * in_batch;
   float* dhi = hi + static_cast<long long>(b) * out_batch;
   float* dlo = lo + static_cast<long long>(b) * out_batch;
-  const int r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+  const int r0 = by * 32, c0 = bx * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
   for (int i = ty; i < 32; i += 8) {
     const int r = r0 + i, c = c0 + tx;
@@ -280,6 +306,34 @@ cudaError_t launch_split_tf32(const float* in, long long ld, long long in_batch,
   dim3 grid((cover_cols + 31) / 32, (cover_rows + 31) / 32, batch);
   split_tf32_kernel<<<grid, 256, 0, stream>>>(in, ld, in_batch, hi, lo, out_ld, out_batch, rows,
                                               cols, transpose);
+  return cudaGetLastError();
+}
+
+namespace {
+void split_grid(const SplitTf32Args& s, int* gx, int* gy) {
+  // cover the padded output extent so that the pad is written (as zeros)
+  const int out_rows = s.transpose ? s.cols : s.rows;
+  const int out_cols = static_cast<int>(s.out_ld);
+  const int cover_rows = s.transpose ? out_cols : out_rows;  // in input-row units
+  const int cover_cols = s.transpose ? out_rows : out_cols;  // in input-col units
+  *gx = (cover_cols + 31) / 32;
+  *gy = (cover_rows + 31) / 32;
+}
+}  // namespace
+
+cudaError_t launch_split_tf32_pair(const SplitTf32Args& a, const SplitTf32Args& b, cudaStream_t stream) {
+  int agx, agy, bgx, bgy;
+  split_grid(a, &agx, &agy);
+  split_grid(b, &bgx, &bgy);
+  dim3 grid(agx > bgx ? agx : bgx, agy > bgy ? agy : bgy, a.batch + b.batch);
+  if (grid.y > 65535u || grid.z > 65535u) {
+    cudaError_t e = launch_split_tf32(a.in, a.ld, a.in_batch, a.hi, a.lo, a.out_ld, a.out_batch, a.rows, a.cols,
+                                      a.batch, a.transpose, stream);
+    if (e != cudaSuccess) return e;
+    return launch_split_tf32(b.in, b.ld, b.in_batch, b.hi, b.lo, b.out_ld, b.out_batch, b.rows, b.cols, b.batch,
+                             b.transpose, stream);
+  }
+  split_tf32_pair_kernel<<<grid, 256, 0, stream>>>(a, b, agx, agy, bgx, bgy);
   return cudaGetLastError();
 }
 

@@ -13,6 +13,19 @@ cudaError_t launch_split_tf32(const float* in, long long ld, long long in_batch,
                               float* lo, long long out_ld, long long out_batch, int rows, int cols,
                               int batch, bool transpose, cudaStream_t stream);
 
+// The same for two operands in one launch (the A and the B of an fp32 GEMM): the launch gap between two
+// small kernels is of the order of their run time.
+struct SplitTf32Args {
+  const float* in;
+  long long ld, in_batch;
+  float* hi;
+  float* lo;
+  long long out_ld, out_batch;
+  int rows, cols, batch;
+  bool transpose;
+};
+cudaError_t launch_split_tf32_pair(const SplitTf32Args& a, const SplitTf32Args& b, cudaStream_t stream);
+
 // Generic 2-D transpose of `elem_bytes`-sized elements: in [rows][cols] -> out [cols][out_ld].
 cudaError_t launch_transpose(const void* in, long long ld, long long in_batch, void* out,
                              long long out_ld, long long out_batch, int rows, int cols, int batch,

@@ -151,7 +151,13 @@ int pick_bn(const TcLaunch& L, int num_sms) {
   const int max_bn = (L.nsplit == 2) ? 128 : 256;
   if (L.n <= 64) return 64;
   if (L.n <= 128) return 128;
-  if (max_bn == 128) return 128;
+  if (max_bn == 128) {
+    // fp32 (three TF32 products per k-step, all tensor-bound): 64-wide tiles when the 128-wide ones
+    // would leave SMs without a tile
+    const long long tiles128 =
+        static_cast<long long>(L.batch) * ((L.m + 127) / 128) * ((L.n + 127) / 128);
+    return tiles128 < num_sms ? 64 : 128;
+  }
   // 256-wide tiles halve the A re-reads; use them once they still fill the machine.
   const long long tiles256 =
       static_cast<long long>(L.batch) * ((L.m + 127) / 128) * ((L.n + 255) / 256);
