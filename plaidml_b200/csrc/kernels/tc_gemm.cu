@@ -311,6 +311,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     p.s2d_wts = L.b0;
     p.s2d_img_px = g.h2 * g.wp;
     p.s2d_stage_load = g.stage_px * 32;
+    p.s2d_box_rows = g.wp % 128 == 0 ? 32 : (g.wp % 64 == 0 ? 16 : 8);
     p.num_kb = taps;
     p.batch = g.n * p.halo_tiles_per_img;     // tiles of 512 positions
     p.tiles_m = 1;
@@ -562,7 +563,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
         cuuint64_t dims[4] = {static_cast<cuuint64_t>(L.n), 4, static_cast<cuuint64_t>(g.q / 4),
                               static_cast<cuuint64_t>(g.n) * g.p};
         cuuint64_t strides[3] = {pix, 4 * pix, pix * g.q};
-        cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / ob), 1, 8, 1};
+        cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / ob), 1, static_cast<cuuint32_t>(p.s2d_box_rows), 1};
         cuuint32_t estr[4] = {1, 1, 1, 1};
         CUresult r = g_encode_tiled(&tc_map, out_map_dtype(L.out_dtype), 4, L.out, dims, strides, box, estr,
                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,

@@ -87,6 +87,7 @@ struct TcParams {
   const void* s2d_wts;         // packed weights [taps][64][16], pre-swizzled
   int s2d_img_px;              // pixels per packed image = h2 * wp
   int s2d_stage_load;          // bytes copied per tile
+  int s2d_box_rows;            // accumulator rows per output store box: 8, 16 or 32 (4 * box rows divides wp)
 
   // Epilogue
   void* out;

@@ -1270,18 +1270,18 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
             if constexpr (Cfg::A_S2D) {
               // Row i of accumulator a is position 512 * tile + 4 * i + a of the image's padded
               // position grid (wp a multiple of 32 per image row).  The output map is
-              // (channels, 4, q / 4, n * p) with output column 4 * c2 + c1 at (c1, c2): the
-              // warp's rows 8 * b .. 8 * b + 7 are one box at c1 = a, c2 = column / 4 of one
-              // image row; boxes in the padding columns or below the image are skipped, the
-              // map clips the rest.
+              // (channels, 4, q / 4, n * p) with output column 4 * c2 + c1 at (c1, c2): every
+              // run of p.s2d_box_rows of the warp's rows (32 when an image row holds the whole
+              // warp) is one box at c1 = a, c2 = column / 4 of one image row; boxes in the
+              // padding columns or below the image are skipped, the map clips the rest.
               const int a = it & 3;
               int op = s2d_op0, oq = s2d_oq0;
-#pragma unroll
-              for (int b = 0; b < 4; ++b) {
+              const int box = p.s2d_box_rows;
+              for (int r = 0; r < 32; r += box) {
                 if (op < p.conv_p && oq < p.conv_q) {
-                  tma_store_4d(&tm.c, buf + static_cast<uint32_t>(b) * 1024u, col0, a, oq >> 2, s2d_row0 + op);
+                  tma_store_4d(&tm.c, buf + static_cast<uint32_t>(r) * 128u, col0, a, oq >> 2, s2d_row0 + op);
                 }
-                oq += 32;
+                oq += 4 * box;
                 if (oq >= p.halo_wp) {
                   oq -= p.halo_wp;
                   ++op;
