@@ -248,6 +248,13 @@ def extras(device: str, iters: int) -> dict:
                                   # the GEMM's epilogue, S is not read back)
                                   "hbm_gbs": (2 * 1024 * 512 * 64 * 2 + 1024 * 512 * 512 * 4 + 1024 * 512 * 4) / ms / 1e6,
                                   "plan": r.executable.describe().strip()}
+    # the same contractions when only R is asked for: S is an intermediate, never written
+    r = Runner(Program("cfg5_r_only", [Q, Kt], [R]), device)
+    r.run([q, q])
+    ms = r.executable.time_steps(iters, True)
+    out["cfg5_qk_rowmax_only"] = {"ms": ms, "gemm_tflops_equiv": 2.0 * 1024 * 512 * 512 * 64 / ms / 1e9,
+                                  "hbm_gbs": (2 * 1024 * 512 * 64 * 2 + 1024 * 512 * 4) / ms / 1e6,
+                                  "plan": r.executable.describe().strip()}
     # cfg4: ResNet-50 v1.5 inference, batch 256, 224x224x3 (device-resident kernel sequence)
     prog, _ = progs.resnet50(256)
     r = Runner(prog, device)

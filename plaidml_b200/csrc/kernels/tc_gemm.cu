@@ -540,9 +540,13 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   // Staged TMA-store epilogue when every output (and residual) row starts on a 16-byte
   // boundary; otherwise the kernel's transpose-and-store path.
   const int ob = out_bytes_of(L.out_dtype);
-  const int ob_tmpl = (eb == 2 && ob == 2) ? 2 : 4;
+  // A launch that stores nothing (row maxima only) takes the 16-bit-output instance whatever the
+  // declared output type: its chunks are 64 accumulator columns instead of 32, i.e. half as many
+  // TMEM round trips per tile, and nothing of it depends on the output element size.
+  const bool no_store = L.out == nullptr && !(L.epi_flags & kEpiResidual);
+  const int ob_tmpl = (eb == 2 && (ob == 2 || no_store)) ? 2 : 4;
   {
-    bool fast = (ob == 2 || ob == 4) && ob == ob_tmpl;
+    bool fast = (ob == 2 || ob == 4) && (ob == ob_tmpl || no_store);
     if (L.out != nullptr) {
       fast = fast && aligned16(L.out) && (L.ldc * ob) % 16 == 0 &&
              (L.batch == 1 || (L.out_batch_stride * ob) % 16 == 0);
