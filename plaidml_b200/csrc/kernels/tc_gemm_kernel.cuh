@@ -1314,6 +1314,35 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
               process(vb, ch + 1);
             }
           }
+        } else if (p.out == nullptr && p.epi_flags == kEpiRowMax && !IS_INT) {
+          // Row maxima only (nothing stored, no other epilogue term): a lean loop, since this
+          // launch is nothing but its epilogue.  Each chunk is reduced by a balanced tree of
+          // hardware max operations, as in the general path.
+          uint32_t va[CW];
+          const int span = p.n - col_base;                         // valid columns from the tile's first on
+          const int chunks = span >= nch * CW ? nch : (span + CW - 1) / CW;
+#pragma unroll 1
+          for (int ch = 0; ch < chunks; ++ch) {
+            issue_load(va, ch);
+            tmem_ld_wait();
+            pin(va);
+            if (ch == chunks - 1) release_acc();
+            const int nvalid = span - ch * CW;                     // >= 1
+            float mx[CW];
+            if (nvalid >= CW) {
+#pragma unroll
+              for (int j = 0; j < CW; ++j) mx[j] = __uint_as_float(va[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < CW; ++j) mx[j] = j < nvalid ? __uint_as_float(va[j]) : -INFINITY;
+            }
+#pragma unroll
+            for (int w = CW / 2; w > 0; w >>= 1) {
+#pragma unroll
+              for (int j = 0; j < w; ++j) mx[j] = fmaxf(mx[j], mx[j + w]);
+            }
+            row_best = fmaxf(row_best, mx[0]);
+          }
         } else {
           // two warps per scheduler hide each other's latencies; one register set suffices
           uint32_t va[CW];
