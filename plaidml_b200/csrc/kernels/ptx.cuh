@@ -386,6 +386,14 @@ __device__ __forceinline__ float relu_keep_nan(float x) {
   return d;
 }
 
+// 32-byte global store (one whole sector per lane); the address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint4& lo, const uint4& hi) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               :
+               : "l"(ptr), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+               : "memory");
+}
+
 enum : int { kMmaF16 = 0, kMmaTf32 = 1, kMmaI8 = 2 };
 
 // D[tmem] (+)= A[smem] * B[smem]; `accumulate` == 0 overwrites D.

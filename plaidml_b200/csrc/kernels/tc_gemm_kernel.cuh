@@ -1244,11 +1244,17 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           if constexpr (Cfg::A_HALO) {
             // output pixels of a tile are not a box of the output tensor: each lane writes its
             // own pixel's 128 bytes
+            // (32-byte stores: whole sectors; output rows of this mode are 128 or 256 bytes on a
+            // 16-byte aligned base, so the 32-byte form needs the base checked once)
             if (row < p.m) {
-              uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(p.out) +
-                                                    (static_cast<long long>(row) * p.ldc + col0) * OB);
+              char* dst = static_cast<char*>(p.out) + (static_cast<long long>(row) * p.ldc + col0) * OB;
+              if ((reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) dst[i] = o[i];
+                for (int i = 0; i < 4; ++i) st_global_v8(dst + 32 * i, o[2 * i], o[2 * i + 1]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) reinterpret_cast<uint4*>(dst)[i] = o[i];
+              }
             }
             return;
           }
