@@ -214,8 +214,18 @@ s2d_pack_kernel(const uint16_t* __restrict__ in, uint4* __restrict__ out, long l
   const long long row = id >> 2;
   const int c0 = static_cast<int>(id & 3) * 2;
   const int x = static_cast<int>(row & 7);
-  out[row * 8 + (c0 ^ x)] = make_uint4(words[0], words[1], words[2], words[3]);
-  out[row * 8 + ((c0 + 1) ^ x)] = make_uint4(words[4], words[5], words[6], words[7]);
+  // (c0 is even, so the pixel's two chunks stay one 32-byte sector, in swapped order when the row
+  // number is odd: one 32-byte store)
+  const uint4 first = make_uint4(words[0], words[1], words[2], words[3]);
+  const uint4 second = make_uint4(words[4], words[5], words[6], words[7]);
+  uint4* sector = out + row * 8 + ((c0 ^ x) & ~1);
+  const bool swapped = (x & 1) != 0;
+  const uint4& a = swapped ? second : first;
+  const uint4& b = swapped ? first : second;
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               :
+               : "l"(sector), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+               : "memory");
 }
 
 __global__ void __launch_bounds__(256)
