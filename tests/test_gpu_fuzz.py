@@ -1,0 +1,129 @@
+"""Seeded random shapes through the kernel C ABI against the CPU oracle: GEMMs (all element types,
+both B layouts, every epilogue combination, forced tile widths and CTA pairs) and convolutions (every
+route the planner can pick, thin and wide inputs, strides, paddings, epilogues).  The shapes are small
+enough for the oracle's loop nests; the seeds are fixed, so a failure names a reproducible case."""
+
+import numpy as np
+import pytest
+
+import oracle
+from plaidml_b200 import kernels as K
+from gpu_util import as_f32, bits16, check_close, dev, dev_bf16, rng
+
+from test_gpu_conv import run_conv
+from test_gpu_gemm import run_gemm
+
+pytestmark = pytest.mark.gpu
+
+
+def random_gemm_case(g):
+    kind = ["bf16", "bf16", "bf16", "i8", "f32"][int(g.integers(0, 5))]
+    m = int(g.integers(1, 700))
+    n = int(g.integers(1, 90)) * 8            # output rows 16-byte aligned (other widths: the ragged tests)
+    k = int(g.integers(1, 60)) * 16
+    batch = int(g.choice([1, 1, 1, 3]))
+    b_is_nk = bool(g.integers(0, 2))
+    tile_n = int(g.choice([0, 0, 64, 128, 256]))
+    flags = int(g.choice([0, 0, K.GEMM_CTA_PAIRS, K.GEMM_NO_CTA_PAIRS, K.GEMM_NO_TAIL_SPLIT]))
+    epi = int(g.integers(0, 8))               # any subset of bias, residual, relu
+    return dict(kind=kind, m=m, n=n, k=k, batch=batch, b_is_nk=b_is_nk, tile_n=tile_n, flags=flags, epi=epi)
+
+
+@pytest.mark.parametrize("seed", range(100))
+def test_random_gemm(seed):
+    g = rng(9000 + seed)
+    c = random_gemm_case(g)
+    m, n, k, batch = c["m"], c["n"], c["k"], c["batch"]
+    if c["kind"] == "f32":
+        c["tile_n"] = c["tile_n"] if c["tile_n"] in (0, 64, 128) else 0
+        c["flags"] = 0
+    if c["tile_n"] == 64 and not c["b_is_nk"] and c["kind"] != "f32":
+        c["tile_n"] = 0                       # (B stored [k][n] is fetched in whole 128-byte chunks of N)
+    bshape = (batch, n, k) if c["b_is_nk"] else (batch, k, n)
+    epi = c["epi"]
+    if c["kind"] == "i8":
+        a = g.integers(-128, 128, size=(batch, m, k), dtype=np.int8)
+        b = g.integers(-128, 128, size=bshape, dtype=np.int8)
+        bias = g.integers(-1000, 1000, size=n, dtype=np.int32) if epi & K.EPI_BIAS else None
+        res = g.integers(-1000, 1000, size=(batch, m, n), dtype=np.int32) if epi & K.EPI_RESIDUAL else None
+        out, _, _ = run_gemm(K.I8, K.I32, dev(a), dev(b), m, n, k, batch, c["b_is_nk"], epilogue=epi,
+                             bias=None if bias is None else dev(bias), residual=None if res is None else dev(res),
+                             tile_n=c["tile_n"], flags=c["flags"])
+        ref = np.stack([oracle.gemm_i8_i32(a[i], b[i], c["b_is_nk"]) for i in range(batch)])
+        if bias is not None:
+            ref = ref + bias[None, None, :]
+        if res is not None:
+            ref = ref + res
+        if epi & K.EPI_RELU:
+            ref = np.maximum(ref, 0)
+        np.testing.assert_array_equal(out.cpu().numpy(), ref.astype(np.int32), err_msg=str(c))
+        return
+    if c["kind"] == "f32":
+        a = g.uniform(-1, 1, size=(batch, m, k)).astype(np.float32)
+        b = g.uniform(-1, 1, size=bshape).astype(np.float32)
+        bias = g.standard_normal(n).astype(np.float32) if epi & K.EPI_BIAS else None
+        res = g.standard_normal((batch, m, n)).astype(np.float32) if epi & K.EPI_RESIDUAL else None
+        out, _, _ = run_gemm(K.F32, K.F32, dev(a), dev(b), m, n, k, batch, c["b_is_nk"], epilogue=epi,
+                             bias=None if bias is None else dev(bias), residual=None if res is None else dev(res),
+                             tile_n=c["tile_n"], flags=c["flags"])
+        ref = np.stack([oracle.gemm_f32_acc64(a[i], b[i], c["b_is_nk"]) for i in range(batch)]).astype(np.float64)
+        tol = 1e-5
+    else:
+        a_t = dev_bf16(g.standard_normal((batch, m, k)))
+        b_t = dev_bf16(g.standard_normal(bshape))
+        out_dt = K.BF16 if g.integers(0, 2) else K.F32
+        bias = g.standard_normal(n).astype(np.float32) if epi & K.EPI_BIAS else None
+        res = None
+        if epi & K.EPI_RESIDUAL:
+            res = dev_bf16(g.standard_normal((batch, m, n))) if out_dt == K.BF16 else dev(
+                g.standard_normal((batch, m, n)).astype(np.float32))
+        out, _, _ = run_gemm(K.BF16, out_dt, a_t, b_t, m, n, k, batch, c["b_is_nk"], epilogue=epi,
+                             bias=None if bias is None else dev(bias), residual=res, tile_n=c["tile_n"], flags=c["flags"])
+        ref = oracle.gemm_h16_f32(bits16(a_t), bits16(b_t), False, c["b_is_nk"]).astype(np.float64)
+        res = None if res is None else as_f32(res)
+        tol = 1e-2 if out_dt == K.BF16 else 1e-4
+    if bias is not None:
+        ref = ref + bias[None, None, :]
+    if res is not None:
+        ref = ref + res
+    if epi & K.EPI_RELU:
+        ref = np.maximum(ref, 0)
+    ref = ref.astype(np.float32)
+    if c["kind"] == "bf16" and tol == 1e-2:
+        ref = oracle.bf16_to_f32(oracle.f32_to_bf16(ref))
+    try:
+        check_close(as_f32(out), ref, tol)
+    except AssertionError as e:
+        raise AssertionError(f"{c}: {e}") from None
+
+
+@pytest.mark.parametrize("seed", range(100))
+def test_random_conv(seed):
+    g = rng(9500 + seed)
+    thin = bool(g.integers(0, 3) == 0)
+    c = int(g.choice([1, 2, 3, 4])) if thin else int(g.choice([8, 16, 32, 64, 64, 128]))
+    r = int(g.choice([1, 3, 3, 5, 7]))
+    s = int(g.choice([3, 5, 7])) if thin else int(g.choice([1, 3, 3, 5]))
+    if thin:
+        r = max(r, 2)
+        while s * 8 > 64:                      # a filter row of a thin input is one 64-element k-block
+            s -= 2
+    stride = int(g.choice([1, 1, 2]))
+    pad = int(g.integers(0, (min(r, s) + 1) // 2 + 1))
+    h = int(g.integers(max(r, 6), 30))
+    w = int(g.integers(max(s, 6), 34))
+    n = int(g.integers(1, 5))
+    k = int(g.choice([8, 16, 64, 64, 96, 128])) if not thin else int(g.choice([8, 32, 64]))
+    out_dtype = K.BF16 if g.integers(0, 2) else K.F32
+    epi = int(g.integers(0, 8))
+    flags = int(g.choice([0, 0, 0, K.CONV_NO_HALO, K.CONV_NO_S2D, K.CONV_CTA_PAIRS]))
+    case = dict(n=n, h=h, w=w, c=c, r=r, s=s, k=k, stride=stride, pad=pad, out_dtype=out_dtype, epilogue=epi, flags=flags)
+    out, ref, plan = run_conv(9500 + seed, **case)
+    tol = 1e-4
+    if out_dtype == K.BF16:
+        ref = oracle.bf16_to_f32(oracle.f32_to_bf16(ref))
+        tol = 1e-2
+    try:
+        check_close(out, ref, tol)
+    except AssertionError as e:
+        raise AssertionError(f"{case} on {plan.kernel}: {e}") from None
