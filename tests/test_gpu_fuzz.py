@@ -127,3 +127,41 @@ def test_random_conv(seed):
         check_close(out, ref, tol)
     except AssertionError as e:
         raise AssertionError(f"{case} on {plan.kernel}: {e}") from None
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_gemm_many_tiles_per_cta(seed):
+    # several tiles per CTA: ring wrap-around, accumulator hand-over between tiles, residual requests running ahead
+    # across tile boundaries, the half-width tail, CTA pairs walking more than one tile
+    g = rng(9800 + seed)
+    m = int(g.integers(150, 420)) * 128 + int(g.integers(0, 128))
+    n = int(g.choice([64, 128, 192, 256, 512, 768, 1024]))
+    k = int(g.choice([64, 128, 256, 512, 1024, 1088]))
+    b_is_nk = bool(g.integers(0, 2))
+    out_dt = K.BF16 if g.integers(0, 3) else K.F32
+    epi = int(g.integers(0, 8))
+    flags = int(g.choice([0, 0, K.GEMM_CTA_PAIRS, K.GEMM_NO_CTA_PAIRS]))
+    a_t = dev_bf16(g.standard_normal((1, m, k)))
+    b_t = dev_bf16(g.standard_normal((1, n, k) if b_is_nk else (1, k, n)))
+    bias = g.standard_normal(n).astype(np.float32) if epi & K.EPI_BIAS else None
+    res = None
+    if epi & K.EPI_RESIDUAL:
+        res = dev_bf16(g.standard_normal((1, m, n))) if out_dt == K.BF16 else dev(g.standard_normal((1, m, n)).astype(np.float32))
+    out, _, _ = run_gemm(K.BF16, out_dt, a_t, b_t, m, n, k, 1, b_is_nk, epilogue=epi,
+                         bias=None if bias is None else dev(bias), residual=res, flags=flags)
+    ref = oracle.gemm_h16_f32(bits16(a_t), bits16(b_t), False, b_is_nk).astype(np.float64)
+    if bias is not None:
+        ref = ref + bias[None, None, :]
+    if res is not None:
+        ref = ref + as_f32(res)
+    if epi & K.EPI_RELU:
+        ref = np.maximum(ref, 0)
+    ref = ref.astype(np.float32)
+    tol = 1e-4
+    if out_dt == K.BF16:
+        ref, tol = oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2
+    case = dict(m=m, n=n, k=k, b_is_nk=b_is_nk, out=out_dt, epi=epi, flags=flags)
+    try:
+        check_close(as_f32(out), ref, tol)
+    except AssertionError as e:
+        raise AssertionError(f"{case}: {e}") from None
