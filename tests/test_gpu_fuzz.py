@@ -165,3 +165,56 @@ def test_random_gemm_many_tiles_per_cta(seed):
         check_close(as_f32(out), ref, tol)
     except AssertionError as e:
         raise AssertionError(f"{case}: {e}") from None
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_pool(seed):
+    # NHWC pooling: the packed two-wide max / min kernel for 16-bit floats and the generic kernel (f32, sums,
+    # averages, channel counts that are not a multiple of 8), windows, strides and paddings at random
+    import torch
+    from gpu_util import empty, ptr
+    g = rng(9900 + seed)
+    dt = [K.BF16, K.BF16, K.F16, K.F32][int(g.integers(0, 4))]
+    mode = ["max", "max", "min", "sum", "avg"][int(g.integers(0, 5))]
+    c = int(g.choice([8, 16, 24, 64, 5, 12]))
+    r, s = int(g.integers(1, 5)), int(g.integers(1, 5))
+    stride = int(g.integers(1, 4))
+    pad = int(g.integers(0, min(r, s)))
+    n, h, w = int(g.integers(1, 4)), int(g.integers(max(r, 4), 20)), int(g.integers(max(s, 4), 24))
+    p, q = (h + 2 * pad - r) // stride + 1, (w + 2 * pad - s) // stride + 1
+    x = g.standard_normal((n, h, w, c)).astype(np.float32)
+    if dt == K.F32:
+        xd = dev(x)
+    elif dt == K.BF16:
+        xd = dev_bf16(x)
+    else:
+        xd = dev(x.astype(np.float16))
+    d = K.PoolDesc()
+    d.agg = {"max": K.AGG_MAX, "min": K.AGG_MIN, "sum": K.AGG_SUM, "avg": K.AGG_SUM}[mode]
+    d.dtype = dt
+    d.n, d.h, d.w, d.c, d.r, d.s, d.p, d.q = n, h, w, c, r, s, p, q
+    d.stride_h = d.stride_w = stride
+    d.pad_h = d.pad_w = pad
+    d.average = int(mode == "avg")
+    d.include_padding = int(g.integers(0, 2)) if mode == "avg" else 0
+    plan = K.Plan("pool", d)
+    out = empty((n, p, q, c), dt)
+    plan.pool(ptr(xd), ptr(out))
+    torch.cuda.synchronize()
+    ref = oracle.pool2d_nhwc_f32(as_f32(xd), "sum" if mode == "avg" else mode, (r, s), (stride, stride), (pad, pad), (p, q),
+                                 average=mode == "avg", include_padding=bool(d.include_padding))
+    case = dict(dt=dt, mode=mode, n=n, h=h, w=w, c=c, r=r, s=s, stride=stride, pad=pad)
+    got = as_f32(out)
+    # a window that lies wholly in the padding has no tap: both sides leave the aggregation's identity there
+    finite = np.isfinite(ref)
+    assert np.array_equal(np.isfinite(got), finite), case
+    if mode in ("max", "min"):
+        np.testing.assert_array_equal(got[finite], ref[finite], err_msg=str(case))      # exact: no arithmetic
+    else:
+        tol = 1e-5 if dt == K.F32 else 1e-2
+        if dt != K.F32:
+            ref = oracle.bf16_to_f32(oracle.f32_to_bf16(ref)) if dt == K.BF16 else ref.astype(np.float16).astype(np.float32)
+        try:
+            check_close(got, ref, tol)
+        except AssertionError as e:
+            raise AssertionError(f"{case}: {e}") from None
