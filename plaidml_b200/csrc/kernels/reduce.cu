@@ -218,11 +218,13 @@ __device__ __forceinline__ uint32_t combine16x2(uint32_t acc, uint32_t v) {
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-template <class T2, int AGG, bool K3X3>
+// W = 16-byte groups per thread: 1, or 2 (32-byte loads and stores: 16 channels per thread, half as
+// many threads and memory instructions; needs c % 16 == 0 and 32-byte aligned tensors).
+template <class T2, int AGG, bool K3X3, int W>
 __global__ void __launch_bounds__(256)
 pool16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, PoolGeom g, FastDiv fd_cv,
               FastDiv fd_p, uint32_t identity2) {
-  const int cv = g.c / 8;
+  const int cv = g.c / (8 * W);                         // channel groups of one thread's width
   const int pos = blockIdx.y * 256 + threadIdx.x;       // (x, channel group) inside the output row
   if (pos >= g.q * cv) return;
   const int x = fast_div(pos, fd_cv);
@@ -230,9 +232,11 @@ pool16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, PoolGeom g,
   const int row = blockIdx.x;                           // n * p + y
   const int n = fast_div(row, fd_p);
   const int y = row - n * g.p;
-  uint32_t acc[4] = {identity2, identity2, identity2, identity2};
+  uint32_t acc[4 * W];
+#pragma unroll
+  for (int j = 0; j < 4 * W; ++j) acc[j] = identity2;
   const int iy0 = y * g.stride_h - g.pad_h, ix0 = x * g.stride_w - g.pad_w;
-  const uint4* base = in + (static_cast<long long>(n) * g.h * g.w) * cv + cg;
+  const uint4* base = in + ((static_cast<long long>(n) * g.h * g.w) * cv + cg) * W;
   const int r = K3X3 ? 3 : g.r, s = K3X3 ? 3 : g.s;
 #pragma unroll
   for (int fr = 0; fr < r; ++fr) {
@@ -242,20 +246,35 @@ pool16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, PoolGeom g,
     for (int fs = 0; fs < s; ++fs) {
       const int ix = ix0 + fs;
       if (ix < 0 || ix >= g.w) continue;
-      const uint4 a = __ldg(base + (static_cast<long long>(iy) * g.w + ix) * cv);
-      acc[0] = combine16x2<T2, AGG>(acc[0], a.x);
-      acc[1] = combine16x2<T2, AGG>(acc[1], a.y);
-      acc[2] = combine16x2<T2, AGG>(acc[2], a.z);
-      acc[3] = combine16x2<T2, AGG>(acc[3], a.w);
+      const uint4* src = base + (static_cast<long long>(iy) * g.w + ix) * cv * W;
+      uint32_t v[4 * W];
+      if constexpr (W == 2) {
+        asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                     : "l"(src));
+      } else {
+        const uint4 a = __ldg(src);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 4 * W; ++j) acc[j] = combine16x2<T2, AGG>(acc[j], v[j]);
     }
   }
-  out[(static_cast<long long>(row) * g.q + x) * cv + cg] = make_uint4(acc[0], acc[1], acc[2], acc[3]);
+  uint4* dst = out + ((static_cast<long long>(row) * g.q + x) * cv + cg) * W;
+  if constexpr (W == 2) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 :
+                 : "l"(dst), "r"(acc[0]), "r"(acc[1]), "r"(acc[2]), "r"(acc[3]), "r"(acc[4]), "r"(acc[5]), "r"(acc[6]), "r"(acc[7])
+                 : "memory");
+  } else {
+    dst[0] = make_uint4(acc[0], acc[1], acc[2], acc[3]);
+  }
 }
 
-template <class T2>
-cudaError_t launch_pool16(const PoolGeom& g, const void* in, void* out, uint32_t neg_inf2,
-                          uint32_t pos_inf2, cudaStream_t stream) {
-  const int cv = g.c / 8;
+template <class T2, int W>
+cudaError_t launch_pool16_w(const PoolGeom& g, const void* in, void* out, uint32_t neg_inf2,
+                            uint32_t pos_inf2, cudaStream_t stream) {
+  const int cv = g.c / (8 * W);
   const long long rows = static_cast<long long>(g.n) * g.p;
   const long long per_row = static_cast<long long>(g.q) * cv;
   if (rows > 0x7fffffffLL || (per_row + 255) / 256 > 65535) return cudaErrorInvalidValue;
@@ -265,13 +284,22 @@ cudaError_t launch_pool16(const PoolGeom& g, const void* in, void* out, uint32_t
   uint4* op = static_cast<uint4*>(out);
   const bool k3 = g.r == 3 && g.s == 3;
   if (g.agg == PMLB_AGG_MAX) {
-    if (k3) pool16_kernel<T2, PMLB_AGG_MAX, true><<<grid, 256, 0, stream>>>(ip, op, g, fc, fp, neg_inf2);
-    else pool16_kernel<T2, PMLB_AGG_MAX, false><<<grid, 256, 0, stream>>>(ip, op, g, fc, fp, neg_inf2);
+    if (k3) pool16_kernel<T2, PMLB_AGG_MAX, true, W><<<grid, 256, 0, stream>>>(ip, op, g, fc, fp, neg_inf2);
+    else pool16_kernel<T2, PMLB_AGG_MAX, false, W><<<grid, 256, 0, stream>>>(ip, op, g, fc, fp, neg_inf2);
   } else {
-    if (k3) pool16_kernel<T2, PMLB_AGG_MIN, true><<<grid, 256, 0, stream>>>(ip, op, g, fc, fp, pos_inf2);
-    else pool16_kernel<T2, PMLB_AGG_MIN, false><<<grid, 256, 0, stream>>>(ip, op, g, fc, fp, pos_inf2);
+    if (k3) pool16_kernel<T2, PMLB_AGG_MIN, true, W><<<grid, 256, 0, stream>>>(ip, op, g, fc, fp, pos_inf2);
+    else pool16_kernel<T2, PMLB_AGG_MIN, false, W><<<grid, 256, 0, stream>>>(ip, op, g, fc, fp, pos_inf2);
   }
   return cudaGetLastError();
+}
+
+template <class T2>
+cudaError_t launch_pool16(const PoolGeom& g, const void* in, void* out, uint32_t neg_inf2,
+                          uint32_t pos_inf2, cudaStream_t stream) {
+  const bool wide = g.c % 16 == 0 && (reinterpret_cast<uintptr_t>(in) & 31u) == 0 &&
+                    (reinterpret_cast<uintptr_t>(out) & 31u) == 0;
+  return wide ? launch_pool16_w<T2, 2>(g, in, out, neg_inf2, pos_inf2, stream)
+              : launch_pool16_w<T2, 1>(g, in, out, neg_inf2, pos_inf2, stream);
 }
 
 template <class T, class TO, bool VEC>
