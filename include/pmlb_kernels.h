@@ -234,13 +234,15 @@ pmlb_status pmlb_conv_invoke(pmlb_plan* plan, void* stream, const void* input, v
  * max"), inner > 1 the strided one (global average pooling sums).  These are the
  * contractions the x86 target leaves as plain loops (pmlc/dialect/pxa/transforms/
  * stencil_gemm.cc:60-75 matches add-of-mul only).  out_dtype == dtype, or F32 for a
- * BF16/F16 input summed in f32.  `scale` multiplies the result (1/count for a mean).
+ * BF16/F16 input summed in f32.  `scale` (0 = none) multiplies a float sum, or with `divide`
+ * != 0 divides it (the count of a mean: sum / count is what the reference's `mean` computes,
+ * plaidml/op/lib/ops.cc:1970-2003; a positive divisor).
  */
 typedef struct {
   int32_t agg;
   int32_t dtype;
   int32_t out_dtype;
-  int32_t reserved;
+  int32_t divide;
   int64_t outer, reduce, inner;
   double scale;
 } pmlb_reduce_desc;

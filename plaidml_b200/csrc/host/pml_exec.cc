@@ -728,7 +728,51 @@ class Planner {
     pd->reduce = d;
     pd->a = src;
     pd->inputs = {src};
+    fuseMeanTail(pd);
     return true;
+  }
+
+  // sum -> div by a literal -> (cast back to the 16-bit input type): the tail of `mean`
+  // (plaidml/op/lib/ops.cc:1970-2003) folds into the reduction kernel, which divides its f32
+  // sum by the count and rounds once.
+  void fuseMeanTail(Pending* pd) {
+    pmlb_reduce_desc& d = pd->reduce;
+    if (d.agg != PMLB_AGG_SUM || d.out_dtype != PMLB_F32) return;
+    int cur = pd->result;
+    auto soleUser = [&](int v) -> int {
+      if (uses_[v] != 1 || isOutput_[v] || users_[v].size() != 1) return -1;
+      return users_[v][0];
+    };
+    const int di = soleUser(cur);
+    if (di < 0) return;
+    const POp& dv = prog_.ops[di];
+    if (dv.kind != POp::Eltwise || dv.mnemonic != "div" || dv.operands.size() != 2 || dv.operands[0] != cur) return;
+    // (a literal operand of an element-wise operation is a rank-0 internal constant of the other operand's type)
+    const PValue& lit = val(dv.operands[1]);
+    if (lit.kind != PValue::InternalConstant || !lit.constant || lit.shape.elements() != 1 ||
+        lit.shape.dtype != DType::f32) {
+      return;
+    }
+    const double count = static_cast<double>(*reinterpret_cast<const float*>(lit.constant->data()));
+    const TensorShape& rs = val(dv.result).shape;
+    if (!(count > 0) || rs.sizes != val(cur).shape.sizes || rs.dtype != DType::f32) return;
+    d.scale = count;
+    d.divide = 1;
+    absorbed_[di] = true;
+    pd->position = std::max(pd->position, di);
+    pd->result = dv.result;
+    pd->fused = "+div";
+    // ... -> cast to the type the input has: the kernel's same-type form (f32 sum, one rounding)
+    const int ci = soleUser(dv.result);
+    if (ci < 0) return;
+    const POp& cs = prog_.ops[ci];
+    const DType ct = val(cs.result).shape.dtype;
+    if (cs.kind != POp::Cast || static_cast<int>(ct) != d.dtype || !(ct == DType::bf16 || ct == DType::f16)) return;
+    d.out_dtype = d.dtype;
+    absorbed_[ci] = true;
+    pd->position = std::max(pd->position, ci);
+    pd->result = cs.result;
+    pd->fused += "+cast";
   }
 
   // sum(cast(x: 16-bit float -> f32)) can read x directly (the widening is exact); for
@@ -964,7 +1008,7 @@ class Planner {
         st.plan = plan;
         st.kernel = pmlb_plan_kind(plan);
         std::ostringstream os;
-        os << label << " outer" << pd.reduce.outer << " reduce" << pd.reduce.reduce << " inner" << pd.reduce.inner;
+        os << label << " outer" << pd.reduce.outer << " reduce" << pd.reduce.reduce << " inner" << pd.reduce.inner << pd.fused;
         st.detail = os.str();
         const void* in = dev(pd.a);
         void* out = dev(pd.result);

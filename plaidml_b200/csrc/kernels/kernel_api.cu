@@ -649,7 +649,11 @@ pmlb_status pmlb_reduce_invoke(pmlb_plan* plan, void* stream, const void* in, vo
   if (!plan || plan->kind != kPlanReduce) return fail(PMLB_ERR_INVALID, "not a reduce plan");
   if (!in || !outp) return fail(PMLB_ERR_INVALID, "reduce: null tensor");
   const pmlb_reduce_desc& d = plan->reduce;
-  const float scale = d.scale == 0.0 ? 1.f : static_cast<float>(d.scale);
+  float scale = d.scale == 0.0 ? 1.f : static_cast<float>(d.scale);
+  if (d.divide != 0) {
+    if (!(scale > 0.f)) return fail(PMLB_ERR_INVALID, "reduce: a divisor must be positive");
+    scale = -scale;   // (the kernels' encoding of a divisor)
+  }
   cudaError_t e = pmlb::launch_reduce(d.agg, d.dtype, d.out_dtype, in, outp, d.outer, d.reduce,
                                       d.inner, scale, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "reduce launch");

@@ -102,7 +102,7 @@ row_reduce_kernel(const T* __restrict__ in, TO* __restrict__ out, long long rows
   }
   if (lane == 0) {
     if constexpr (AGG == PMLB_AGG_SUM && sizeof(A) == 4 && static_cast<A>(0.5) != A(0)) {
-      if (scale != 1.f) acc = acc * scale;
+      if (scale != 1.f) acc = scale < 0.f ? acc / -scale : acc * scale;   // (negative: a divisor)
     }
     out[row] = from_acc<TO, A>(acc);
   }
@@ -138,7 +138,7 @@ strided_reduce_kernel(const T* __restrict__ in, TO* __restrict__ out, long long 
   for (int j = 0; j < N; ++j) {
     A v = acc[j];
     if constexpr (AGG == PMLB_AGG_SUM && sizeof(A) == 4 && static_cast<A>(0.5) != A(0)) {
-      if (scale != 1.f) v = v * scale;
+      if (scale != 1.f) v = scale < 0.f ? v / -scale : v * scale;   // (negative: a divisor)
     }
     out[o * inner + iv * N + j] = from_acc<TO, A>(v);
   }

@@ -19,6 +19,7 @@ struct PoolGeom {
 };
 
 bool reduce_supported(int agg, int dtype, int out_dtype);
+// `scale` applies to float sums only: positive = factor, negative = minus the divisor, 1 = none.
 cudaError_t launch_reduce(int agg, int dtype, int out_dtype, const void* in, void* out,
                           long long outer, long long red, long long inner, float scale,
                           cudaStream_t stream);

@@ -54,7 +54,7 @@ class ConvDesc(C.Structure):
 
 class ReduceDesc(C.Structure):
     _fields_ = [
-        ("agg", C.c_int32), ("dtype", C.c_int32), ("out_dtype", C.c_int32), ("reserved", C.c_int32),
+        ("agg", C.c_int32), ("dtype", C.c_int32), ("out_dtype", C.c_int32), ("divide", C.c_int32),
         ("outer", C.c_int64), ("reduce", C.c_int64), ("inner", C.c_int64), ("scale", C.c_double),
     ]
 

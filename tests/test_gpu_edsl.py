@@ -204,6 +204,28 @@ def test_maxpool_and_mean_and_softmax():
     np.testing.assert_allclose(got_sm, e / e.sum(axis=1, keepdims=True), rtol=1e-5, atol=1e-7)
 
 
+def test_mean_tail_folds_into_the_reduction():
+    # sum -> / count -> cast back to bf16 (the global average pool of a bf16 network): one kernel that divides its
+    # f32 sum by the count and rounds once; the same values as the three separate steps (general kernels)
+    g = rng(1242)
+    x = f32_to_bf16_bits(g.standard_normal((3, 7, 7, 32)))
+    I = Placeholder(DType.BFLOAT16, x.shape)
+    mean = op.mean(cast(I, DType.FLOAT32), axes=[1, 2])
+    O = cast(mean, DType.BFLOAT16)
+    runner = Runner(Program("gap", [I], [O]), "cuda.0")
+    desc = runner.executable.describe()
+    assert desc.count("\n") == 1 and "strided_reduce" in desc and "+div+cast" in desc, desc
+    got = runner.run([x])[0]
+    sums = bf16_bits_to_f32(x).astype(np.float32).sum(axis=(1, 2), dtype=np.float64)
+    ref = f32_to_bf16_bits((sums.astype(np.float32) / np.float32(49)).astype(np.float32))
+    # (the f32 sum's rounding depends on the summation order: allow one bf16 ulp)
+    assert np.abs(got.astype(np.int32) - ref.astype(np.int32)).max() <= 1
+    # a mean that stays f32 folds the division only, and a mean that is itself an output is not folded past
+    runner = Runner(Program("gap32", [I], [mean]), "cuda.0")
+    assert "+div" in runner.executable.describe() and "+cast" not in runner.executable.describe()
+    np.testing.assert_allclose(runner.run([x])[0], sums / 49.0, rtol=1e-5, atol=1e-6)
+
+
 def test_avgpool_counts_only_in_range_taps():
     g = rng(1240)
     x = g.standard_normal((1, 7, 7, 4)).astype(np.float32)
