@@ -164,6 +164,11 @@ int pick_bn(const TcLaunch& L, int num_sms) {
   if (L.n % 256 == 0 || L.n > 512) {
     if (tiles256 >= num_sms) return 256;
   }
+  // small problems (few rows): 64-wide tiles put a tile on more SMs, and a tile's serial walk over
+  // K is shorter per k-block (a 64-wide MMA lasts 48 cycles, a 128-wide one 64)
+  const long long tiles128 =
+      static_cast<long long>(L.batch) * ((L.m + 127) / 128) * ((L.n + 127) / 128);
+  if (tiles128 * 2 <= num_sms) return 64;
   return 128;
 }
 
