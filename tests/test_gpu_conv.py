@@ -252,3 +252,43 @@ def test_halo_route_epilogues():
     out, ref, plan = run_conv(72, 2, 28, 28, 64, 3, 3, 64, epilogue=K.EPI_BIAS | K.EPI_RESIDUAL)
     assert plan.kernel == "tc_conv_halo"
     check_close(out, ref, 1e-4)
+
+
+# --- IEEE half operands (PLAIDML_DATA_FLOAT16 programs): every route, f16 output packed with and without ReLU ---
+
+@pytest.mark.parametrize("case", [
+    dict(n=2, h=20, w=20, c=64, r=3, s=3, k=64, stride=1, pad=1, route="tc_conv_halo"),
+    dict(n=2, h=18, w=18, c=32, r=3, s=3, k=96, stride=1, pad=1, route="tc_conv"),
+    dict(n=2, h=40, w=40, c=3, r=7, s=7, k=64, stride=2, pad=3, route="tc_conv_s2d"),
+    dict(n=2, h=19, w=30, c=3, r=3, s=3, k=32, stride=1, pad=1, route="tc_conv_rows"),
+], ids=["halo", "im2col", "s2d", "rows"])
+@pytest.mark.parametrize("relu", [False, True], ids=["linear", "relu"])
+def test_conv_f16_operands_and_output(case, relu):
+    import torch
+    g = rng(60)
+    n, h, w, c, r, s, k, stride, pad = (case[x] for x in ("n", "h", "w", "c", "r", "s", "k", "stride", "pad"))
+    p, q = out_size(h, r, stride, pad, pad), out_size(w, s, stride, pad, pad)
+    x16 = g.uniform(-1, 1, size=(n, h, w, c)).astype(np.float16)
+    f16 = (g.standard_normal((r, s, c, k)) * np.sqrt(2.0 / (r * s * c))).astype(np.float16)
+    bias = g.standard_normal(k).astype(np.float32)
+    d = K.ConvDesc()
+    d.in_dtype, d.out_dtype = K.F16, K.F16
+    d.n, d.h, d.w, d.c, d.r, d.s, d.k, d.p, d.q = n, h, w, c, r, s, k, p, q
+    d.stride_h = d.stride_w = stride
+    d.pad_h = d.pad_w = pad
+    d.dil_h = d.dil_w = 1
+    d.epilogue = K.EPI_BIAS | (K.EPI_RELU if relu else 0)
+    plan = K.Plan("conv", d)
+    assert plan.kernel == case["route"]
+    f_dev = dev(f16)
+    plan.set_filter(ptr(f_dev), K.F16)
+    x_dev, b_dev = dev(x16), dev(bias)
+    out = empty((n, p, q, k), K.F16)
+    plan.conv(ptr(x_dev), ptr(out), ptr(b_dev), None)
+    plan.check()
+    ref = oracle.conv2d_nhwc_f32(x16.astype(np.float32), f16.astype(np.float32), bias, None, (stride, stride), (pad, pad),
+                                 (1, 1), relu, out_hw=(p, q))
+    got = out.cpu().numpy().astype(np.float32)
+    if relu:
+        assert (got >= 0).all()
+    check_close(got, ref.astype(np.float16).astype(np.float32), 2e-3)
