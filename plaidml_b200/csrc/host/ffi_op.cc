@@ -1177,6 +1177,65 @@ VarPtr opRepeat(const VarPtr& value) {
 }
 
 // plaidml/op/lib/ops.cc:3454-3487: numpy-style tile
+// Resize the two spatial dimensions of an image tensor by positive integer factors: nearest (two repeats) or
+// bilinear with corners aligned to 0 and factor * (dim - 1) over zero padding, as a contraction with a
+// (2 fh - 1) x (2 fw - 1) triangular kernel built by contractions (plaidml/op/lib/ops.cc:1822-1917).
+VarPtr opImageResize(const VarPtr& value) {
+  const auto& args = asTuple(value, "image_resize");
+  if (args.size() != 4) throw std::runtime_error("image_resize expects 4 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const std::vector<int64_t> factors = asIntTuple(args[1]);
+  const int64_t interp = asInt(args[2]);
+  const int64_t layout = asInt(args[3]);
+  if (interp < 0 || interp > 1) throw std::runtime_error("Invalid enumeration value: " + std::to_string(interp));
+  for (int64_t f : factors) {
+    if (f <= 0) {
+      throw std::runtime_error("All scaling factors in image_resize must be positive (received " + std::to_string(f) + ")");
+    }
+  }
+  const pml::TensorShape shape = shapeOf(I);
+  const size_t nd = shape.rank();
+  size_t pre;
+  if (layout == 1) pre = 2;        // NCX
+  else if (layout == 0) pre = 1;   // NXC
+  else throw std::runtime_error("Unable to apply image_resize to a tensor with layout '" + std::to_string(layout) + "'");
+  if (nd < 2 || nd - 2 != 2) {
+    throw std::runtime_error("Expected 2 spatial dims for resize_images, received " + std::to_string(static_cast<int64_t>(nd) - 2));
+  }
+  if (factors.size() != 2) {
+    throw std::runtime_error("Cannot resize a 2D image using " + std::to_string(factors.size()) + " spatial scaling factors");
+  }
+  if (interp == 0) {
+    VarPtr rows = opRepeat(tupleVar({args[0], intVar(factors[0]), intVar(static_cast<int64_t>(pre))}));
+    return opRepeat(tupleVar({rows, intVar(factors[1]), intVar(static_cast<int64_t>(pre) + 1)}));
+  }
+  // one axis of the kernel: ramp[y] = sum over j < f of (1/f)[j + y - f + 1], a triangle of height 1 at y = f - 1
+  auto ramp = [](int64_t f) {
+    ExprPtr coeff = castTo(litFloat(1.0 / static_cast<double>(f)), pml::DType::f32);
+    PolyPtr y = newIndex("y");
+    ExprPtr vec = contraction(pml::AggKind::assign, pml::ComboKind::none, {f}, {y}, {{coeff, {}}}, {}, "image_resize");
+    PolyPtr j = newIndex("j"), y2 = newIndex("y");
+    return contraction(pml::AggKind::add, pml::ComboKind::none, {2 * f - 1}, {y2}, {{vec, {j + y2 - f + 1}}}, {{j, f}},
+                       "image_resize");
+  };
+  const int64_t fh = factors[0], fw = factors[1];
+  ExprPtr hk = ramp(fh), wk = ramp(fw);
+  PolyPtr ky = newIndex("y"), kx = newIndex("x");
+  ExprPtr kernel = contraction(pml::AggKind::assign, pml::ComboKind::mul, {2 * fh - 1, 2 * fw - 1}, {ky, kx},
+                               {{hk, {ky}}, {wk, {kx}}}, {}, "image_resize");
+  std::vector<PolyPtr> iIdx, oIdx;
+  for (size_t d = 0; d < nd; ++d) iIdx.push_back(newIndex());
+  oIdx = iIdx;
+  PolyPtr j = newIndex("j"), i = newIndex("i");
+  std::vector<int64_t> oDims = shape.sizes;
+  oDims[pre] *= fh;
+  oDims[pre + 1] *= fw;
+  oIdx[pre] = fh * iIdx[pre] + j - fh + 1;
+  oIdx[pre + 1] = fw * iIdx[pre + 1] + i - fw + 1;
+  return exprValue(contraction(pml::AggKind::add, pml::ComboKind::mul, oDims, oIdx, {{I, iIdx}, {kernel, {j, i}}}, {},
+                               "image_resize"));
+}
+
 VarPtr opTile(const VarPtr& value) {
   const auto& args = asTuple(value, "tile");
   if (args.size() != 2) throw std::runtime_error("Tile expects 2 arguments");
@@ -1313,6 +1372,7 @@ const std::map<std::string, std::function<VarPtr(const VarPtr&)>>& registry() {
       {"cumprod", opCumprod},
       {"explicit_padding", opExplicitPadding},
       {"hard_sigmoid", opHardSigmoid},
+      {"image_resize", opImageResize},
       {"l2norm", opL2norm},
       {"lrn", opLrn},
       {"mvn", opMvn},

@@ -175,6 +175,11 @@ class EpsMode(enum.IntEnum):
     MAX = 1
 
 
+class InterpolationMode(enum.IntEnum):
+    NEAREST = 0
+    BILINEAR = 1
+
+
 class PadMode(enum.IntEnum):
     CONSTANT = 0
     EDGE = 1
@@ -220,6 +225,10 @@ def hard_sigmoid(x, slope):
 
 def l2norm(x, axes, epsilon, eps_mode=EpsMode.ADD):
     return op("l2norm", [x, list(axes), float(epsilon), int(eps_mode)]).as_tensor()
+
+
+def image_resize(x, factors, interp, layout):
+    return op("image_resize", [x, list(factors), int(interp), int(layout)]).as_tensor()
 
 
 def lrn(x, window_size, axes=(-1,), alpha=1.0, beta=0.5, epsilon=1.0):

@@ -186,3 +186,44 @@ def test_dilated_strided_and_data_dilated_convolutions():
     got = run(lambda X, F: op.convolution(X, F, data_dilations=[2, 2], autopad_mode=op.AutoPadMode.EXPLICIT,
                                           manual_padding=[1, 1]), x, f)
     np.testing.assert_allclose(got, conv_ref(x, f, ddil=2, pad=1), rtol=1e-4, atol=1e-5)
+
+
+def resize_ref(x, fh, fw, h_axis):
+    """Bilinear image_resize as the op library defines it (plaidml/op/lib/ops.cc:1873-1912): every input
+    pixel spreads a (2 fh - 1) x (2 fw - 1) triangle, centred on output position (fh * y, fw * x), over a zero background."""
+    def ramp(f):
+        return np.array([min(y + 1, 2 * f - 1 - y) for y in range(2 * f - 1)], np.float64) * np.float64(np.float32(1.0 / f))
+    kern = np.float32(ramp(fh))[:, None].astype(np.float64) * np.float32(ramp(fw))[None, :].astype(np.float64)
+    kern = kern.astype(np.float32).astype(np.float64)
+    x = np.moveaxis(x.astype(np.float64), (h_axis, h_axis + 1), (-2, -1))
+    h, w = x.shape[-2:]
+    out = np.zeros(x.shape[:-2] + (fh * h, fw * w))
+    for y in range(h):
+        for xx in range(w):
+            for j in range(2 * fh - 1):
+                for i in range(2 * fw - 1):
+                    oy, ox = fh * y + j - fh + 1, fw * xx + i - fw + 1
+                    if 0 <= oy < fh * h and 0 <= ox < fw * w:
+                        out[..., oy, ox] += x[..., y, xx] * kern[j, i]
+    return np.moveaxis(out, (-2, -1), (h_axis, h_axis + 1)).astype(np.float32)
+
+
+def test_image_resize_nearest_and_bilinear_in_both_layouts():
+    g = rng(31)
+    x = g.standard_normal((2, 5, 7, 3)).astype(np.float32)
+    got = run(lambda X: op.image_resize(X, [2, 3], op.InterpolationMode.NEAREST, op.TensorLayout.NXC), x)
+    np.testing.assert_array_equal(got, np.repeat(np.repeat(x, 2, axis=1), 3, axis=2))
+    got = run(lambda X: op.image_resize(X, [3, 2], op.InterpolationMode.NEAREST, op.TensorLayout.NCX), x)
+    np.testing.assert_array_equal(got, np.repeat(np.repeat(x, 3, axis=2), 2, axis=3))
+    for fh, fw in ((2, 2), (2, 3), (1, 4), (3, 1)):
+        got = run(lambda X: op.image_resize(X, [fh, fw], op.InterpolationMode.BILINEAR, op.TensorLayout.NXC), x)
+        assert got.shape == (2, 5 * fh, 7 * fw, 3)
+        np.testing.assert_allclose(got, resize_ref(x, fh, fw, 1), rtol=1e-5, atol=1e-6)
+        got = run(lambda X: op.image_resize(X, [fh, fw], op.InterpolationMode.BILINEAR, op.TensorLayout.NCX), x)
+        assert got.shape == (2, 5, 7 * fh, 3 * fw)
+        np.testing.assert_allclose(got, resize_ref(x, fh, fw, 2), rtol=1e-5, atol=1e-6)
+    # a constant image stays constant away from the zero-padded far edge (the triangles sum to one)
+    ones = np.ones((1, 4, 4, 1), np.float32)
+    got = run(lambda X: op.image_resize(X, [2, 2], op.InterpolationMode.BILINEAR, op.TensorLayout.NXC), ones)
+    np.testing.assert_allclose(got[0, :7, :7, 0], 1.0, rtol=1e-6)
+    np.testing.assert_allclose(got[0, 7, :7, 0], 0.5, rtol=1e-6)

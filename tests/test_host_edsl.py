@@ -344,3 +344,22 @@ def test_more_op_library_shapes_and_errors():
         op.explicit_padding(X, [0, 0, 0, 0], [0, 0, 0, 0], op.PadMode.REFLECT)
     with pytest.raises(Error, match="tiling factors"):
         op.tile(X, [])
+
+
+def test_image_resize_shapes_and_argument_errors():
+    # plaidml/op/lib/ops.cc:1822-1866: positive factors, two of them, two spatial dimensions, NXC or NCX
+    x = Placeholder(DType.FLOAT32, [2, 5, 7, 3])
+    near = op.image_resize(x, [2, 3], op.InterpolationMode.NEAREST, op.TensorLayout.NXC)
+    assert near.compute_shape().sizes == [2, 10, 21, 3]
+    bil = op.image_resize(x, [2, 3], op.InterpolationMode.BILINEAR, op.TensorLayout.NCX)
+    assert bil.compute_shape().sizes == [2, 5, 14, 9] and bil.compute_shape().dtype == DType.FLOAT32
+    text = str(Program("resize", [x], [bil]))
+    assert text.count('name="image_resize"') == 6 and "tensor<3x5xf32>" in text     # two ramps, their vectors, kernel, resize
+    with pytest.raises(Error, match="must be positive"):
+        op.image_resize(x, [0, 2], op.InterpolationMode.BILINEAR, op.TensorLayout.NXC)
+    with pytest.raises(Error, match="spatial scaling factors"):
+        op.image_resize(x, [2], op.InterpolationMode.BILINEAR, op.TensorLayout.NXC)
+    with pytest.raises(Error, match="layout"):
+        op.image_resize(x, [2, 2], op.InterpolationMode.BILINEAR, op.TensorLayout.KCX)
+    with pytest.raises(Error, match="2 spatial dims"):
+        op.image_resize(Placeholder(DType.FLOAT32, [2, 5, 3]), [2, 2], op.InterpolationMode.NEAREST, op.TensorLayout.NXC)
