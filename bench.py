@@ -326,13 +326,16 @@ def main() -> None:
     e2e_value = world * ops_per_step * args.steps / e2e_s / 1e12
 
     # ---- device-resident: the kernel sequence alone, CUDA events per pass, L2 flushed between passes
-    exe.time_steps(warm, True)
+    # Warm-up: at least 30 passes, because the phase before this one leaves the GPU waiting on PCIe copies
+    # (at 8 ranks most of the time) and its clocks take a few milliseconds of work to come back up.
+    exe.time_steps(max(warm, 30), True)
     sampler = ClockSampler(local_rank)
     barrier()
     sampler.start()
-    ms = exe.time_steps(args.steps, True)
+    ms = exe.time_steps(args.steps, True)   # one CUDA-event pair per pass, passes enqueued ahead of the host's wait
     clocks = sampler.stop()
     barrier()
+    rank_ms = shard.gather_floats(dist, ms, f"cuda:{local_rank}")
     # The timed region lasts a few milliseconds, less than most clock queries take; so the same kernel
     # sequence is also run back to back for about 0.3 s (untimed) under a second sampler: the clock and the
     # throttle reasons the kernel settles at under sustained load.
@@ -364,6 +367,7 @@ def main() -> None:
         "e2e": {"value": e2e_value, "unit": "TOP/s", "h2d_bytes_per_step": int(a.nbytes + b.nbytes),
                 "d2h_bytes_per_step": int(M_PER_GPU * N_DIM * 4), "ms_per_step": 1e3 * e2e_s / args.steps},
         "gpu_launches": int(exe.launch_count * args.steps),
+        "ms_per_step_by_rank": [round(x, 5) for x in rank_ms],
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": int8_peak, "unit": "TOP/s",
                      "frac": per_gpu / int8_peak, "traffic": NCU_TRAFFIC_BYTES,

@@ -284,7 +284,8 @@ int pmlb_exec_uses_graph(plaidml_error* err, plaidml_executable* exec);
 double pmlb_exec_run_resident(plaidml_error* err, plaidml_executable* exec, size_t iters);
 /* Like pmlb_exec_run_resident, but every pass is bracketed by its own CUDA event pair and,
  * with `flush_l2`, preceded by an untimed overwrite of a 256 MiB device buffer so that no
- * pass finds its operands in the 126 MB L2. */
+ * pass finds its operands in the 126 MB L2.  Passes are enqueued up to 64 ahead of the host's
+ * wait, so an interval holds device time only; returns the mean interval in milliseconds. */
 double pmlb_exec_time_steps(plaidml_error* err, plaidml_executable* exec, size_t iters, bool flush_l2);
 /* Device address and byte size of output `index` (valid until the executable is freed). */
 void* pmlb_exec_output_device_ptr(plaidml_error* err, plaidml_executable* exec, size_t index, size_t* nbytes);

@@ -72,6 +72,7 @@ class Executable {
   int device_ = 0;
   cudaStream_t stream_ = nullptr;
   cudaEvent_t evStart_ = nullptr, evStop_ = nullptr;
+  std::vector<cudaEvent_t> timingEvents_;   // start / stop pairs of timeSteps
   char* arena_ = nullptr;
   char* flush_ = nullptr;
   size_t arenaBytes_ = 0;

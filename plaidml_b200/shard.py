@@ -78,6 +78,17 @@ def sum_over_ranks(dist, value: float, device=None) -> float:
     return float(t.item())
 
 
+def gather_floats(dist, value: float, device=None) -> list:
+    """Every rank's figure, in rank order, on every rank (one all-gather of one element)."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return [float(value)]
+    import torch
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device or "cpu")
+    out = torch.empty(dist.get_world_size(), dtype=torch.float64, device=device or "cpu")
+    dist.all_gather_into_tensor(out, t)
+    return [float(x) for x in out.tolist()]
+
+
 def job_throughput(dist, units_this_rank: float, seconds_this_rank: float, device=None) -> float:
     """Whole-job rate: the units all ranks processed divided by the slowest rank's time."""
     units = sum_over_ranks(dist, units_this_rank, device)

@@ -57,6 +57,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         shard.barrier(dist)
         slowest = shard.max_over_ranks(dist, 1.0 + rank)
         units = shard.sum_over_ranks(dist, float(hi - lo))
+        assert shard.gather_floats(dist, 1.0 + rank) == [1.0 + r for r in range(world)]
         rate = shard.job_throughput(dist, float(hi - lo), 1.0 + rank)
         np.save(os.path.join(out_dir, f"t{rank}.npy"), np.array([slowest, units, rate, lo, hi]))
         # gathered output: equal slices only (pad the ragged last shard as the caller would)
@@ -88,6 +89,7 @@ def test_two_gloo_ranks_tile_the_unsharded_result(tmp_path):
 def test_single_process_reductions_are_identities():
     assert shard.max_over_ranks(None, 3.5) == 3.5
     assert shard.sum_over_ranks(None, 3.5) == 3.5
+    assert shard.gather_floats(None, 3.5) == [3.5]
     assert shard.job_throughput(None, 10.0, 2.0) == 5.0
     shard.barrier(None)
     t = torch.arange(6.0).reshape(2, 3)
