@@ -183,7 +183,7 @@ void plaidml_program_free(plaidml_error* err, plaidml_program* program) {
 }
 
 plaidml_string* plaidml_program_repr(plaidml_error* err, plaidml_program* program) {
-  return ffiWrap<plaidml_string*>(err, nullptr, [&] { return new plaidml_string{program->program->str()}; });
+  return ffiWrap<plaidml_string*>(err, nullptr, [&] { return new plaidml_string{program->program->mlir()}; });
 }
 
 plaidml_shapes* plaidml_program_get_inputs(plaidml_error* err, plaidml_program* program) {
@@ -204,9 +204,11 @@ plaidml_shapes* plaidml_program_get_outputs(plaidml_error* err, plaidml_program*
 
 plaidml_kvps* plaidml_program_get_passes(plaidml_error* err, plaidml_program* program) {
   return ffiWrap<plaidml_kvps*>(err, nullptr, [&] {
-    // one "pass": the bounded tile program, the form the planner consumes
+    // two "passes": the program as built (tile-dialect spelling) and after bounds inference, the form
+    // the planner consumes
     std::vector<std::pair<std::string, std::string>> passes;
-    passes.emplace_back("tile", program->program->str());
+    passes.emplace_back("tile", program->program->mlir());
+    passes.emplace_back("bounds", program->program->str());
     return makeKvps(passes);
   });
 }

@@ -7,6 +7,7 @@
 #include <cmath>
 #include <cstring>
 #include <limits>
+#include <map>
 #include <numeric>
 #include <sstream>
 
@@ -222,6 +223,19 @@ static uint16_t f32ToF16(float f) {
   return u;
 }
 
+static float bf16ToF32(uint16_t h) {
+  const uint32_t u = static_cast<uint32_t>(h) << 16;
+  float f;
+  std::memcpy(&f, &u, 4);
+  return f;
+}
+
+static float f16ToF32(uint16_t u) {
+  __half h;
+  std::memcpy(&h, &u, 2);
+  return __half2float(h);
+}
+
 BufferPtr makeScalarConstant(DType dtype, const Literal& lit) {
   DType dt = dtype;
   if (dt == DType::six) dt = DType::si32;
@@ -316,6 +330,232 @@ std::string Program::str() const {
   for (size_t i = 0; i < outputs.size(); ++i) os << (i ? ", %" : " %") << outputs[i];
   os << "\n}\n";
   return os.str();
+}
+
+// ------------------------------------------------------------------ tile-dialect spelling
+//
+// The text plaidml_program_repr returns in the reference is the printed MLIR module of the `tile`
+// dialect (plaidml/core/ffi.cc: program repr -> module print); its tests match that text with
+// FileCheck patterns (plaidml/edsl/tests/edsl_test.cc).  This printer spells the bounded program
+// the same way: module / func @main, one `tile.constant` per distinct scalar literal, eltwise ops as
+// `tile.<op> %a, %b : (types) -> type`, contractions with their initial value as first operand and
+// the accesses as affine maps (constraints as an affine set).
+
+namespace {
+
+std::string mlirFloat(double v) {
+  if (std::isinf(v)) return v < 0 ? "0xFFF0000000000000" : "0x7FF0000000000000";
+  if (std::isnan(v)) return "0x7FF8000000000000";
+  char buf[64];
+  std::snprintf(buf, sizeof buf, "%e", v);
+  if (std::strtod(buf, nullptr) == v) return buf;
+  // shortest digits that read back exactly, as d.dddE-x
+  for (int prec = 1; prec <= 17; ++prec) {
+    std::snprintf(buf, sizeof buf, "%.*E", prec, v);
+    if (std::strtod(buf, nullptr) == v) break;
+  }
+  std::string t(buf);
+  const size_t e = t.find('E');
+  std::string mant = t.substr(0, e), ex = t.substr(e + 1);
+  int exponent = std::atoi(ex.c_str());
+  return mant + "E" + std::to_string(exponent);
+}
+
+std::string mlirAffine(const Affine& a) {
+  // common denominator d: (sum of integer terms) floordiv d
+  int64_t den = a.constant.den;
+  auto lcm = [](int64_t x, int64_t y) {
+    int64_t g = x, h = y;
+    while (h) { const int64_t t = g % h; g = h; h = t; }
+    return x / g * y;
+  };
+  for (const Rational& c : a.coef) if (!c.isZero()) den = lcm(den, c.den);
+  std::ostringstream os;
+  bool any = false;
+  for (size_t i = 0; i < a.coef.size(); ++i) {
+    if (a.coef[i].isZero()) continue;
+    int64_t k = a.coef[i].num * (den / a.coef[i].den);
+    if (any) os << (k < 0 ? " - " : " + ");
+    else if (k < 0) os << "-";
+    const int64_t mag = k < 0 ? -k : k;
+    os << "d" << i;
+    if (mag != 1) os << " * " << mag;
+    any = true;
+  }
+  const int64_t k0 = a.constant.num * (den / a.constant.den);
+  if (k0 != 0 || !any) {
+    if (any) os << (k0 < 0 ? " - " : " + ") << (k0 < 0 ? -k0 : k0);
+    else os << k0;
+  }
+  if (den == 1) return os.str();
+  return "(" + os.str() + ") floordiv " + std::to_string(den);
+}
+
+std::string mlirDims(size_t n) {
+  std::string out = "(";
+  for (size_t i = 0; i < n; ++i) out += (i ? ", d" : "d") + std::to_string(i);
+  return out + ")";
+}
+
+std::string mlirMap(const std::vector<Affine>& exprs, size_t n) {
+  std::string out = "affine_map<" + mlirDims(n) + " -> (";
+  for (size_t d = 0; d < exprs.size(); ++d) out += (d ? ", " : "") + mlirAffine(exprs[d]);
+  return out + ")>";
+}
+
+// value of a rank-0 constant buffer / literal as (is float, f, i)
+struct Scalar {
+  bool isFloat = false;
+  double f = 0;
+  int64_t i = 0;
+};
+
+Scalar scalarOf(const PValue& v) {
+  Scalar out;
+  if (v.kind == PValue::LiteralValue) {
+    out.isFloat = v.literal.kind == Literal::Float;
+    out.f = v.literal.f;
+    out.i = v.literal.kind == Literal::Unsigned ? static_cast<int64_t>(v.literal.u) : v.literal.i;
+    return out;
+  }
+  const char* p = v.constant->data();
+  switch (v.shape.dtype) {
+    case DType::f16: { uint16_t h; std::memcpy(&h, p, 2); out.isFloat = true; out.f = f16ToF32(h); break; }
+    case DType::bf16: { uint16_t h; std::memcpy(&h, p, 2); out.isFloat = true; out.f = bf16ToF32(h); break; }
+    case DType::f32: { float f; std::memcpy(&f, p, 4); out.isFloat = true; out.f = f; break; }
+    case DType::f64: { std::memcpy(&out.f, p, 8); out.isFloat = true; break; }
+    case DType::i1: case DType::ui8: { uint8_t x; std::memcpy(&x, p, 1); out.i = x; break; }
+    case DType::si8: { int8_t x; std::memcpy(&x, p, 1); out.i = x; break; }
+    case DType::si16: { int16_t x; std::memcpy(&x, p, 2); out.i = x; break; }
+    case DType::ui16: { uint16_t x; std::memcpy(&x, p, 2); out.i = x; break; }
+    case DType::si32: { int32_t x; std::memcpy(&x, p, 4); out.i = x; break; }
+    case DType::ui32: { uint32_t x; std::memcpy(&x, p, 4); out.i = x; break; }
+    default: { std::memcpy(&out.i, p, 8); break; }
+  }
+  return out;
+}
+
+}  // namespace
+
+std::string Program::mlir() const {
+  static const char* aggNames[] = {"assign", "add", "max", "min", "mul"};
+  static const char* comboNames[] = {"none", "add", "cond", "eq", "mul"};
+  std::vector<std::string> names(values.size());
+  std::ostringstream head, csts, body;
+  size_t nargs = 0;
+  head << "module @" << name << " {\n  func @main(";
+  for (int id : inputs) {
+    names[id] = "%arg" + std::to_string(nargs);
+    head << (nargs ? ", " : "") << names[id] << ": " << values[id].shape.str();
+    ++nargs;
+  }
+  for (int id : constants) {
+    const PValue& v = values[id];
+    if (v.kind == PValue::InternalConstant && v.shape.sizes.empty()) continue;   // a literal: tile.constant below
+    names[id] = "%arg" + std::to_string(nargs);
+    head << (nargs ? ", " : "") << names[id] << ": " << v.shape.str() << " {stdx.const}";
+    ++nargs;
+  }
+  head << ") -> ";
+  if (outputs.size() != 1) head << "(";
+  for (size_t i = 0; i < outputs.size(); ++i) head << (i ? ", " : "") << values[outputs[i]].shape.str();
+  if (outputs.size() != 1) head << ")";
+  head << " {\n";
+
+  // scalar constants, one per distinct (value, type), all defined before the first op
+  std::map<std::string, std::string> cstByText;
+  size_t ncst = 0;
+  auto constantName = [&](const std::string& text) {
+    auto it = cstByText.find(text);
+    if (it != cstByText.end()) return it->second;
+    const std::string nm = ncst == 0 ? "%cst" : "%cst_" + std::to_string(ncst - 1);
+    ++ncst;
+    cstByText.emplace(text, nm);
+    csts << "    " << nm << " = " << text << "\n";
+    return nm;
+  };
+  auto scalarText = [&](const Scalar& sc, DType dt) {
+    std::string t = "tile.constant(";
+    if (sc.isFloat || isFloat(dt)) t += mlirFloat(sc.isFloat ? sc.f : static_cast<double>(sc.i)) + " : f64";
+    else t += std::to_string(sc.i) + " : i64";
+    return t + ") : " + TensorShape(dt).str();
+  };
+  auto use = [&](int id) -> std::string {
+    if (!names[id].empty()) return names[id];
+    const PValue& v = values[id];
+    if (v.kind == PValue::LiteralValue || (v.kind == PValue::InternalConstant && v.shape.sizes.empty())) {
+      names[id] = constantName(scalarText(scalarOf(v), v.shape.dtype));
+    } else {
+      names[id] = "%v" + std::to_string(id);   // not reached for a well-formed program
+    }
+    return names[id];
+  };
+  auto identity = [&](AggKind agg, DType dt) {
+    Scalar sc;
+    sc.isFloat = isFloat(dt);
+    const size_t bits = dtypeBytes(dt) * 8;
+    const bool sgn = isSignedInt(dt);
+    switch (agg) {
+      case AggKind::mul: sc.f = 1.0; sc.i = 1; break;
+      case AggKind::max:
+        sc.f = -std::numeric_limits<double>::infinity();
+        sc.i = sgn ? (bits >= 64 ? std::numeric_limits<int64_t>::min() : -(int64_t{1} << (bits - 1))) : 0;
+        break;
+      case AggKind::min:
+        sc.f = std::numeric_limits<double>::infinity();
+        sc.i = bits >= 64 ? std::numeric_limits<int64_t>::max()
+                          : (sgn ? (int64_t{1} << (bits - 1)) - 1 : (int64_t{1} << bits) - 1);
+        break;
+      default: break;
+    }
+    return constantName(scalarText(sc, dt));
+  };
+
+  size_t nres = 0;
+  for (const POp& op : ops) {
+    std::vector<std::string> args;
+    if (op.kind == POp::Contraction) {
+      const BoundedContraction& c = *op.c;
+      const size_t nsrc = op.operands.size() - (c.hasInit ? 1 : 0);
+      const std::string init = c.hasInit ? use(op.operands.back()) : identity(c.agg, values[op.result].shape.dtype);
+      for (size_t i = 0; i < nsrc; ++i) args.push_back(use(op.operands[i]));
+      names[op.result] = "%" + std::to_string(nres++);
+      body << "    " << names[op.result] << " = tile.contract " << aggNames[static_cast<int>(c.agg)] << ", "
+           << comboNames[static_cast<int>(c.combo)] << ", " << init;
+      for (const std::string& a : args) body << ", " << a;
+      body << " {";
+      if (!c.cons.empty()) {
+        body << "cons = affine_set<" << mlirDims(c.nIdx()) << " : (";
+        for (size_t k = 0; k < c.cons.size(); ++k) {
+          Affine hi = c.cons[k].first;
+          for (Rational& r : hi.coef) r = Rational(0) - r;
+          hi.constant = Rational(c.cons[k].second - 1) - hi.constant;
+          body << (k ? ", " : "") << mlirAffine(c.cons[k].first) << " >= 0, " << mlirAffine(hi) << " >= 0";
+        }
+        body << ")>, ";
+      }
+      if (!op.label.empty()) body << "name = \"" << op.label << "\", ";
+      body << "sink = " << mlirMap(c.sink, c.nIdx()) << ", srcs = [";
+      for (size_t i = 0; i < nsrc; ++i) body << (i ? ", " : "") << mlirMap(c.srcs[i], c.nIdx());
+      body << "]} : " << (c.hasInit ? values[op.operands.back()].shape.str() : TensorShape(values[op.result].shape.dtype).str());
+      for (size_t i = 0; i < nsrc; ++i) body << ", " << values[op.operands[i]].shape.str();
+      body << " -> " << values[op.result].shape.str() << "\n";
+      continue;
+    }
+    for (int id : op.operands) args.push_back(use(id));
+    names[op.result] = "%" + std::to_string(nres++);
+    body << "    " << names[op.result] << " = tile." << op.mnemonic;
+    for (size_t i = 0; i < args.size(); ++i) body << (i ? ", " : " ") << args[i];
+    body << " : (";
+    for (size_t i = 0; i < op.operands.size(); ++i) body << (i ? ", " : "") << values[op.operands[i]].shape.str();
+    body << ") -> " << values[op.result].shape.str() << "\n";
+  }
+  body << "    return";
+  for (size_t i = 0; i < outputs.size(); ++i) body << (i ? ", " : " ") << use(outputs[i]);
+  if (!outputs.empty()) body << " : ";
+  for (size_t i = 0; i < outputs.size(); ++i) body << (i ? ", " : "") << values[outputs[i]].shape.str();
+  body << "\n  }\n}\n";
+  return head.str() + csts.str() + body.str();
 }
 
 // ------------------------------------------------------------------ builder

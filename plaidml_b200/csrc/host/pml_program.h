@@ -85,7 +85,8 @@ struct Program {
   std::vector<int> outputs;    // value ids
   std::string target;          // set by plaidml_program_compile
   bool compiled = false;
-  std::string str() const;
+  std::string str() const;    // the bounded form the planner consumes: index ranges, rational accesses
+  std::string mlir() const;   // the same program spelled like the reference's printed `tile` module
 };
 
 std::shared_ptr<Program> buildProgram(const std::string& name, const std::vector<ExprPtr>& inputs,

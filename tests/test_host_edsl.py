@@ -65,6 +65,11 @@ def flatten(X):
     return reshape(X, (1, functools.reduce(lambda a, b: a * b, dims[1:])))
 
 
+def bounds_text(prog) -> str:
+    """The program after bounds inference (index ranges, rational accesses): the second entry of the passes list."""
+    return dict(prog.passes)["bounds"]
+
+
 def shape_str(t) -> str:
     return str(t.compute_shape())
 
@@ -104,7 +109,8 @@ def test_dot_program_text_has_the_bounded_contraction():
     A = Placeholder(DType.FLOAT32, [4, 5])
     B = Placeholder(DType.FLOAT32, [5, 6])
     prog = Program("g", [A, B], [dot(A, B)])
-    text = str(prog)
+    assert "tile.contract add, mul, %cst, %arg0, %arg1" in str(prog)
+    text = bounds_text(prog)
     assert "tile.contract add, mul" in text
     assert "x0 in [0, 4)" in text and "x1 in [0, 6)" in text and "x2 in [0, 5)" in text
     assert [s.sizes for s in prog.inputs] == [[4, 5], [5, 6]]
@@ -195,7 +201,8 @@ def test_collect_passes_starts_with_tile():
     prog = Program("collect_passes", [A, B], [dot(A, B)])
     core.settings_set("PLAIDML_TARGET", "cuda")     # an empty target means "the PLAIDML_TARGET setting"
     prog.compile(debug=True)
-    assert prog.passes[0][0] == "tile"
+    assert prog.passes[0][0] == "tile" and prog.passes[0][1] == str(prog)
+    assert prog.passes[1][0] == "bounds" and "x0 in [0, 10)" in prog.passes[1][1]
 
 
 def test_trace_builds():
@@ -236,7 +243,7 @@ def test_bounds_of_a_strided_window_and_a_fractional_index():
     K = Placeholder(DType.FLOAT32, [3], name="K")
     i, j = TensorIndexes(2)
     O = Contraction().outShape(5).outAccess(i).sum(I[(i - j + 1) // 2] * K[j]).build()
-    text = str(Program("defract", [I, K], [O]))
+    text = bounds_text(Program("defract", [I, K], [O]))
     assert "x0 in [0, 5)" in text and "x1 in [0, 3)" in text
     # a pooling window: the window index is bounded by its constraint only
     P = Placeholder(DType.FLOAT32, [1, 7, 7, 2])
@@ -257,7 +264,7 @@ def test_an_index_no_access_bounds_is_an_error():
     A = Placeholder(DType.FLOAT32, [4])
     i, j = TensorIndexes(2)
     ok = Contraction().outShape(4).outAccess(i).sum(A[i + j]).add_constraint(j < 2).build()
-    text = str(Program("window", [A], [ok]))       # j is held to [0, 2) by the constraint and by A's range
+    text = bounds_text(Program("window", [A], [ok]))       # j is held to [0, 2) by the constraint and by A's range
     assert "x1 in [0, 2)" in text
     free = Contraction().outShape(4).outAccess(i).sum(A[i] * A[i + 0 * j]).build()
     with pytest.raises(Error):
@@ -354,7 +361,7 @@ def test_image_resize_shapes_and_argument_errors():
     bil = op.image_resize(x, [2, 3], op.InterpolationMode.BILINEAR, op.TensorLayout.NCX)
     assert bil.compute_shape().sizes == [2, 5, 14, 9] and bil.compute_shape().dtype == DType.FLOAT32
     text = str(Program("resize", [x], [bil]))
-    assert text.count('name="image_resize"') == 6 and "tensor<3x5xf32>" in text     # two ramps, their vectors, kernel, resize
+    assert text.count('name = "image_resize"') == 6 and "tensor<3x5xf32>" in text     # two ramps, their vectors, kernel, resize
     with pytest.raises(Error, match="must be positive"):
         op.image_resize(x, [0, 2], op.InterpolationMode.BILINEAR, op.TensorLayout.NXC)
     with pytest.raises(Error, match="spatial scaling factors"):
