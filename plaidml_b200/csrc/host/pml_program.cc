@@ -346,19 +346,27 @@ namespace {
 std::string mlirFloat(double v) {
   if (std::isinf(v)) return v < 0 ? "0xFFF0000000000000" : "0x7FF0000000000000";
   if (std::isnan(v)) return "0x7FF8000000000000";
+  // MLIR's spelling: six decimals when the value has at most six significant digits, else the shortest
+  // digits that read back exactly (scientific, capital E, for small and large exponents)
   char buf[64];
-  std::snprintf(buf, sizeof buf, "%e", v);
-  if (std::strtod(buf, nullptr) == v) return buf;
-  // shortest digits that read back exactly, as d.dddE-x
-  for (int prec = 1; prec <= 17; ++prec) {
+  std::snprintf(buf, sizeof buf, "%.5e", v);
+  if (std::strtod(buf, nullptr) == v) {
+    std::snprintf(buf, sizeof buf, "%e", v);
+    return buf;
+  }
+  for (int prec = 6; prec <= 17; ++prec) {
     std::snprintf(buf, sizeof buf, "%.*E", prec, v);
     if (std::strtod(buf, nullptr) == v) break;
   }
   std::string t(buf);
   const size_t e = t.find('E');
-  std::string mant = t.substr(0, e), ex = t.substr(e + 1);
-  int exponent = std::atoi(ex.c_str());
-  return mant + "E" + std::to_string(exponent);
+  const std::string mant = t.substr(0, e);
+  const int exponent = std::atoi(t.substr(e + 1).c_str());
+  if (exponent >= -3 && exponent <= 15) {
+    std::snprintf(buf, sizeof buf, "%.*f", std::max(0, static_cast<int>(mant.size()) - 2 - (mant[0] == '-' ? 1 : 0) - exponent), v);
+    if (std::strtod(buf, nullptr) == v) return buf;
+  }
+  return mant + "E" + (exponent >= 0 ? "+" : "") + std::to_string(exponent);
 }
 
 std::string mlirAffine(const Affine& a) {
@@ -486,7 +494,10 @@ std::string Program::mlir() const {
     if (v.kind == PValue::LiteralValue || (v.kind == PValue::InternalConstant && v.shape.sizes.empty())) {
       names[id] = constantName(scalarText(scalarOf(v), v.shape.dtype));
     } else {
-      names[id] = "%v" + std::to_string(id);   // not reached for a well-formed program
+      // a tensor the builder computed from shapes alone (index, shape): a dense constant
+      std::string t = "tile.constant(dense<" + std::string(v.name.empty() ? "..." : v.name) + "> : " + v.shape.str() + ") : " +
+                      v.shape.str();
+      names[id] = constantName(t);
     }
     return names[id];
   };
@@ -785,6 +796,8 @@ class Builder {
       if (prog_->values[src].shape.elements() != shape.elements()) {
         throw std::runtime_error("'reshape' changes the number of elements");
       }
+      // reshape(x, x.shape) is x (pmlc/dialect/tile/ir/ops.cc:88-94)
+      if (prog_->values[src].shape.sizes == shape.sizes && prog_->values[src].shape.dtype == shape.dtype) return src;
       POp op;
       op.kind = POp::Reshape;
       op.mnemonic = "reshape";
@@ -808,6 +821,17 @@ class Builder {
       ids[2] = materialise(ids[2], promoted);
     } else {
       for (int& id : ids) id = materialise(id, promoted);
+    }
+    // commutative operations keep a scalar constant on the right, as MLIR's folder leaves them in the
+    // reference (pmlc/dialect/tile/ir/eltwise.td: the ops marked Commutative)
+    static const char* const kCommutative[] = {"add", "mul", "max", "min", "cmp_eq", "cmp_ne", "bit_and", "bit_or",
+                                               "bit_xor", "logical_and", "logical_or", "logical_xor"};
+    if (ids.size() == 2 && std::find(std::begin(kCommutative), std::end(kCommutative), name) != std::end(kCommutative)) {
+      auto scalarConstant = [&](int id) {
+        const PValue& v = prog_->values[id];
+        return v.kind == PValue::LiteralValue || (v.kind == PValue::InternalConstant && v.shape.sizes.empty());
+      };
+      if (scalarConstant(ids[0]) && !scalarConstant(ids[1])) std::swap(ids[0], ids[1]);
     }
     POp op;
     op.kind = POp::Eltwise;
@@ -840,8 +864,11 @@ std::shared_ptr<Program> buildProgram(const std::string& name, const std::vector
     const PValue::Kind kind = prog->values[id].kind;
     if (kind == PValue::LiteralValue) id = b.materialise(id, prog->values[id].shape.dtype);
     const bool dup = std::find(seen.begin(), seen.end(), id) != seen.end();
-    if (prog->values[id].kind != PValue::Temp || dup) {
-      // outputs are distinct buffers written by the program (pmlc/ast/builder.cc:560-590)
+    const int def = prog->values[id].def;
+    const bool view = def >= 0 && prog->ops[def].kind == POp::Reshape;
+    if (prog->values[id].kind != PValue::Temp || dup || view) {
+      // outputs are distinct buffers written by the program: an argument, a reshaped view or a value returned
+      // twice is copied by an ident (pmlc/ast/builder.cc:580-593)
       POp op;
       op.kind = POp::Eltwise;
       op.mnemonic = "ident";

@@ -276,3 +276,23 @@ def test_run_argument_checks_and_timing():
     with pytest.raises(core.Error, match="Shape mismatch"):
         exe.run([a, wrong], [c])
     assert exe.run_resident(3) > 0 and exe.launch_count >= 1
+
+
+def test_reshaped_outputs_and_constants_on_either_side():
+    # an output that is a reshaped view (or a reshape that changes nothing) is copied through tile.ident, and a
+    # commutative operation keeps its scalar constant on the right whichever way it was written
+    g = rng(77)
+    a = g.standard_normal((4, 6)).astype(np.float32)
+    A = Placeholder(DType.FLOAT32, [4, 6])
+    outs = [edsl.reshape(A, [3, 8]), edsl.reshape(A, [4, 6]), 2.0 * A, A * 2.0, 1.0 - A, edsl.reshape(A + 1.0, [24])]
+    prog = Program("views", [A], outs)
+    text = str(prog)
+    assert text.count("tile.ident") == 3 and text.count("tile.reshape") == 2
+    assert text.count("tile.mul %arg0, %cst") == 2
+    got = Runner(prog, "cuda.0").run([a])
+    np.testing.assert_array_equal(got[0], a.reshape(3, 8))
+    np.testing.assert_array_equal(got[1], a)
+    np.testing.assert_array_equal(got[2], 2.0 * a)
+    np.testing.assert_array_equal(got[3], 2.0 * a)
+    np.testing.assert_array_equal(got[4], 1.0 - a)
+    np.testing.assert_array_equal(got[5], (a + 1.0).reshape(24))
