@@ -448,7 +448,11 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), Cfg::A_S2D ? Cfg::ISSUERS : 1);   // (both issuers read a space-to-depth buffer)
+      // Every MMA-issuing warp reports on a stage before it is refilled: the tile's owner when its MMAs
+      // have read it (a commit), the other issuer when it has seen the stage arrive (a plain arrive).
+      // A parity wait cannot tell a phase from the one two later, so a warp that only watched the
+      // stages go by could, if it fell one ring revolution behind, wait for ever.
+      mbar_init(empty_bar(s), Cfg::ISSUERS);
     }
     for (int a = 0; a < Cfg::NACC; ++a) {
       mbar_init(tfull_bar(a), 1);
@@ -839,13 +843,14 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       int it = 0;
       for (int t = t_begin; t < t_end && ok; t += t_step, ++it) {
         if (it % Cfg::ISSUERS != iw) {
-          // The other issuer's tile: walk its buffers too, waiting for each to arrive.  A parity
-          // wait tells "this phase" from "the one before" only, so an issuer must never run
-          // more than one ring revolution ahead of the data.
+          // The other issuer's tile: walk its buffers too, waiting for each to arrive and reporting
+          // it seen (the producer refills a buffer only after both issuers have reported on it).
           for (int cb = 0; cb < p.conv_cblocks && ok; ++cb) {
             if (!mbar_wait_warp(full_bar(static_cast<uint32_t>(hsi)), hphase, abort_flag)) {
               if (leader && *abort_code == 0) *abort_code = 3;
               ok = false;
+            } else if (leader) {
+              mbar_arrive(empty_bar(static_cast<uint32_t>(hsi)));
             }
             if (++hsi == static_cast<int>(nst)) {
               hsi = 0;
@@ -969,11 +974,13 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
       int it = 0;
       for (int t = t_begin; t < t_end && ok; t += t_step, ++it) {
         if (it % Cfg::ISSUERS != iw) {
-          // the other issuer's tile: walk its stages too, waiting for each to arrive (see above)
+          // the other issuer's tile: walk its stages too, waiting for each to arrive and saying so
           for (int kb = 0; kb < p.num_kb && ok; ++kb) {
             if (!mbar_wait_warp(full_bar(stage), phase, abort_flag)) {
               if (leader && *abort_code == 0) *abort_code = 3;
               ok = false;
+            } else if (leader) {
+              mbar_arrive(empty_bar(stage));
             }
             if (++stage == STAGES) {
               stage = 0;
