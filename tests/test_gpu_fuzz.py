@@ -129,7 +129,7 @@ def test_random_conv(seed):
         raise AssertionError(f"{case} on {plan.kernel}: {e}") from None
 
 
-@pytest.mark.parametrize("seed", range(12))
+@pytest.mark.parametrize("seed", range(24))
 def test_random_gemm_many_tiles_per_cta(seed):
     # several tiles per CTA: ring wrap-around, accumulator hand-over between tiles, residual requests running ahead
     # across tile boundaries, the half-width tail, CTA pairs walking more than one tile
@@ -141,6 +141,8 @@ def test_random_gemm_many_tiles_per_cta(seed):
     out_dt = K.BF16 if g.integers(0, 3) else K.F32
     epi = int(g.integers(0, 8))
     flags = int(g.choice([0, 0, K.GEMM_CTA_PAIRS, K.GEMM_NO_CTA_PAIRS]))
+    # forced widths: 64-wide tiles (two MMA-issuing warps on alternate tiles) with main loops longer than the ring
+    tile_n = int(g.choice([0, 0, 64, 64, 128])) if seed >= 12 else 0
     a_t = dev_bf16(g.standard_normal((1, m, k)))
     b_t = dev_bf16(g.standard_normal((1, n, k) if b_is_nk else (1, k, n)))
     bias = g.standard_normal(n).astype(np.float32) if epi & K.EPI_BIAS else None
@@ -148,7 +150,7 @@ def test_random_gemm_many_tiles_per_cta(seed):
     if epi & K.EPI_RESIDUAL:
         res = dev_bf16(g.standard_normal((1, m, n))) if out_dt == K.BF16 else dev(g.standard_normal((1, m, n)).astype(np.float32))
     out, _, _ = run_gemm(K.BF16, out_dt, a_t, b_t, m, n, k, 1, b_is_nk, epilogue=epi,
-                         bias=None if bias is None else dev(bias), residual=res, flags=flags)
+                         bias=None if bias is None else dev(bias), residual=res, flags=flags, tile_n=tile_n)
     ref = oracle.gemm_h16_f32(bits16(a_t), bits16(b_t), False, b_is_nk).astype(np.float64)
     if bias is not None:
         ref = ref + bias[None, None, :]
@@ -160,7 +162,7 @@ def test_random_gemm_many_tiles_per_cta(seed):
     tol = 1e-4
     if out_dt == K.BF16:
         ref, tol = oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2
-    case = dict(m=m, n=n, k=k, b_is_nk=b_is_nk, out=out_dt, epi=epi, flags=flags)
+    case = dict(m=m, n=n, k=k, b_is_nk=b_is_nk, out=out_dt, epi=epi, flags=flags, tile_n=tile_n)
     try:
         check_close(as_f32(out), ref, tol)
     except AssertionError as e:
