@@ -124,7 +124,12 @@ size_t plaidml_buffer_size(plaidml_error* err, plaidml_buffer* buffer);
  * plaidml/core/ffi.h:249-284.  plaidml_program_compile("" target) resolves PLAIDML_TARGET
  * (plaidml/core/ffi.cc:376-389); the only target is "cuda" (options in braces are accepted
  * and ignored, as in pmlc/compiler/program.cc:176-188).  plaidml_program_save reports that
- * the target has no save support, like the x86 target (pmlc/target/x86/register.cc:26-33). */
+ * the target has no save support, like the x86 target (pmlc/target/x86/register.cc:26-33).
+ * plaidml_program_repr returns the program spelled like the reference's printed `tile` module
+ * (module @name { func @main(...) { tile.constant / tile.<eltwise> / tile.contract ... } }), the text
+ * the FileCheck lines of plaidml/edsl/tests/edsl_test.cc match.  plaidml_program_get_passes returns
+ * two entries: "tile" (that text) and "bounds" (every contraction with its index ranges and
+ * rational access forms, the form the planner consumes). */
 void plaidml_program_free(plaidml_error* err, plaidml_program* program);
 plaidml_string* plaidml_program_repr(plaidml_error* err, plaidml_program* program);
 plaidml_shapes* plaidml_program_get_inputs(plaidml_error* err, plaidml_program* program);
