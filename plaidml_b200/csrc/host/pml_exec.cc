@@ -161,6 +161,8 @@ class Planner {
     for (size_t i = 0; i < prog_.ops.size(); ++i) {
       if (absorbed_[i]) continue;
       const POp& op = prog_.ops[i];
+      // an operation whose value the builder already computed from shapes alone (tile.shape): nothing to run
+      if (prog_.values[op.result].kind == PValue::InternalConstant) continue;
       Pending pd;
       pd.op = static_cast<int>(i);
       pd.position = static_cast<int>(i);
@@ -1180,7 +1182,7 @@ class Planner {
     if (op.operands.size() > 3) throw std::runtime_error("Element-wise '" + op.mnemonic + "' takes more than three operands");
     pmlb_eltwise_desc d;
     std::memset(&d, 0, sizeof(d));
-    std::strncpy(d.op, op.mnemonic.c_str(), sizeof(d.op) - 1);
+    std::strncpy(d.op, op.mnemonic == "pragma" ? "ident" : op.mnemonic.c_str(), sizeof(d.op) - 1);   // a pragma copies its operand
     d.n_in = static_cast<int32_t>(op.operands.size());
     d.rank = static_cast<int32_t>(outShape.rank());
     d.out_dtype = static_cast<int32_t>(outShape.dtype);

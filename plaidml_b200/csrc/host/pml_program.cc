@@ -555,6 +555,11 @@ std::string Program::mlir() const {
     }
     for (int id : op.operands) args.push_back(use(id));
     names[op.result] = "%" + std::to_string(nres++);
+    if (op.mnemonic == "pragma") {
+      body << "    " << names[op.result] << " = tile.pragma " << args[0] << " \"" << op.label << "\" {" << op.attrs
+           << "} : " << values[op.result].shape.str() << "\n";
+      continue;
+    }
     body << "    " << names[op.result] << " = tile." << op.mnemonic;
     for (size_t i = 0; i < args.size(); ++i) body << (i ? ", " : " ") << args[i];
     body << " : (";
@@ -676,7 +681,26 @@ class Builder {
         l.i = ev.evaluate(e->dim);
         return literal(e, l, DType::six);
       }
-      case ExprNode::Pragma: return lower(e->expr);
+      case ExprNode::Pragma: {
+        // kept as an operation (tile.pragma), run as a copy of its operand (pmlc/ast/builder.cc:768-780)
+        const int src = lower(e->expr);
+        POp op;
+        op.kind = POp::Eltwise;
+        op.mnemonic = "pragma";
+        op.label = e->op;
+        bool first = true;
+        for (const auto& kv : e->attrs) {
+          op.attrs += (first ? "" : ", ") + kv.first + " = ";
+          const VarPtr& v = kv.second;
+          if (v && v->kind == VarNode::Str) op.attrs += "\"" + v->s + "\"";
+          else if (v && v->kind == VarNode::Int) op.attrs += std::to_string(v->i) + " : i64";
+          else if (v && v->kind == VarNode::Float) op.attrs += std::to_string(v->f) + " : f64";
+          else op.attrs += v ? v->str() : "unit";
+          first = false;
+        }
+        op.operands = {materialise(src, prog_->values[src].shape.dtype)};
+        return emit(op, prog_->values[op.operands[0]].shape);
+      }
       case ExprNode::Element: {
         const ExprPtr& src = e->expr;
         if (src->kind == ExprNode::Layer) {
@@ -789,7 +813,16 @@ class Builder {
       v.constant = buf;
       v.shape = shape;
       v.name = "shape";
-      return addValue(v);
+      const int id = addValue(v);
+      // kept as an operation of the printed program (tile.shape); its value is known here, so nothing runs for it
+      POp op;
+      op.kind = POp::Eltwise;
+      op.mnemonic = "shape";
+      op.operands = {lower(e->operands[0])};
+      op.result = id;
+      prog_->values[id].def = static_cast<int>(prog_->ops.size());
+      prog_->ops.push_back(op);
+      return id;
     }
     if (name == "reshape") {
       const int src = lower(e->operands[0]);

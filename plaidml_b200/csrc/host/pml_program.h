@@ -70,7 +70,8 @@ struct PValue {
 struct POp {
   enum Kind { Contraction, Eltwise, Cast, Reshape } kind = Eltwise;
   std::string mnemonic;  // eltwise op name ("add", "relu", ...), "cast", "reshape", "contract"
-  std::string label;     // user-given name (contraction / layer name)
+  std::string label;     // user-given name (contraction / layer name); the pragma's name for "pragma"
+  std::string attrs;     // "pragma": its attributes as printed, e.g. msg = "text"
   std::vector<int> operands;  // value ids; for contractions: sources then the init (if any)
   int result = -1;
   std::shared_ptr<BoundedContraction> c;

@@ -509,9 +509,21 @@ def shape(x):
     return intrinsic("shape", x)
 
 
+def pragma(x, op, attrs):
+    """``tile.pragma``: `x` annotated with an operation name and attributes (plaidml/edsl/__init__.py:1159-1171).
+    The cuda target runs it as a copy of `x`."""
+    t = _as_tensor(x)
+    keys, values, raw = [], [], []
+    for key, value in attrs.items():
+        keys.append(ffi.new("char[]", key.encode()))
+        values.append(Value(value))
+        raw.append(ffi.new("plaidml_attr*", {"key": keys[-1], "value": values[-1].as_ptr()}))
+    return Tensor(expr=ffi_call(lib.plaidml_expr_pragma, t.as_ptr(), op.encode(), len(raw), raw))
+
+
 def trace(x, msg):
-    """Accepted for compatibility; the cuda target records no host-side trace points."""
-    return x
+    """A trace point: ``pragma(x, "trace", msg=...)``; the cuda target records no host-side trace."""
+    return pragma(x, "trace", dict(msg=msg))
 
 
 # ---------------------------------------------------------------------- values (op-library arguments)

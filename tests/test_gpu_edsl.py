@@ -296,3 +296,17 @@ def test_reshaped_outputs_and_constants_on_either_side():
     np.testing.assert_array_equal(got[3], 2.0 * a)
     np.testing.assert_array_equal(got[4], 1.0 - a)
     np.testing.assert_array_equal(got[5], (a + 1.0).reshape(24))
+
+
+def test_shape_and_trace_run():
+    # tile.shape is known when the program is built (nothing runs for it); tile.pragma runs as a copy of its operand
+    g = rng(78)
+    a = g.standard_normal((2, 3)).astype(np.float32)
+    A = Placeholder(DType.FLOAT32, [2, 3])
+    prog = Program("shape_trace", [A], [edsl.shape(A), edsl.trace(A * 2.0, "after doubling"), edsl.trace(A, "input")])
+    text = str(prog)
+    assert "tile.shape %arg0" in text and text.count("tile.pragma") == 2 and 'msg = "input"' in text
+    got = Runner(prog, "cuda.0").run([a])
+    np.testing.assert_array_equal(got[0], np.array([2, 3], np.int32))
+    np.testing.assert_array_equal(got[1], a * 2.0)
+    np.testing.assert_array_equal(got[2], a)

@@ -12,7 +12,7 @@ import pytest
 import filecheck
 from plaidml_b200.core import DType, Program
 from plaidml_b200.edsl import (Constant, Contraction, Placeholder, TensorDims, TensorIndexes, cast, exp, reshape, select,
-                               sqrt)
+                               shape, sqrt, trace)
 
 with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "edsl_filecheck.json")) as f:
     CHECKS = json.load(f)
@@ -244,7 +244,18 @@ def build_reshape(name, src_dims, dst_dims):
     return Program(name, [A], [reshape(A, dst_dims)])
 
 
+def build_shape():
+    I = f32(2, 3)
+    return Program("shape", [I], [shape(I)])
+
+
+def build_trace():
+    I = f32(3, 3)
+    return Program("trace", [I], [trace(I, "msg")])
+
+
 BUILDERS = {
+    "Shape": build_shape, "Trace": build_trace,
     "HigherPrecisionConstants": build_higher_precision_constants, "LarsMomentum4d": build_lars_momentum_4d,
     "ReshapeFold": lambda: build_reshape("reshape_fold", [3, 3], [3, 3]),
     "ReshapeScalar": lambda: build_reshape("reshape_scalar", [], []),
