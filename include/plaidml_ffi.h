@@ -292,10 +292,41 @@ double pmlb_exec_run_resident(plaidml_error* err, plaidml_executable* exec, size
  * pass finds its operands in the 126 MB L2.  Passes are enqueued up to 64 ahead of the host's
  * wait, so an interval holds device time only; returns the mean interval in milliseconds. */
 double pmlb_exec_time_steps(plaidml_error* err, plaidml_executable* exec, size_t iters, bool flush_l2);
+/* The same, with every pass's interval written to ms_out[0 .. iters) (milliseconds). */
+void pmlb_exec_time_passes(plaidml_error* err, plaidml_executable* exec, size_t iters, bool flush_l2, double* ms_out);
 /* Device address and byte size of output `index` (valid until the executable is freed). */
 void* pmlb_exec_output_device_ptr(plaidml_error* err, plaidml_executable* exec, size_t index, size_t* nbytes);
 /* CUDA stream (cudaStream_t) the executable enqueues on. */
 void* pmlb_exec_stream(plaidml_error* err, plaidml_executable* exec);
+
+
+/* ------------------------------------------------------------------ sharded mode (no reference counterpart)
+ * One process per GPU, each compiling the same program for its slice of the independent dimension
+ * (rows of M, images of a batch); the reference splits one fixed problem over threads that share one
+ * memory instead (pmlc/dialect/pxa/transforms/cpu_thread.cc:49-92).  The data path has no exchange
+ * step.  Two collectives exist around it, each one NCCL all-gather over NVLink on buffers the
+ * executable owns; NCCL (libnccl.so.2) is bound with dlopen at the first of these calls.
+ *
+ * pmlb_shard_unique_id: called on rank 0; the caller carries the 128 bytes to the other ranks.
+ * pmlb_shard_init: collective; makes `device` ("cuda.N", or PLAIDML_DEVICE when empty) current and
+ *   joins the process to the communicator.  world == 1 needs no id and loads nothing.
+ * pmlb_exec_set_input_replicated: marks a program input as holding the same data on every rank (the
+ *   B matrix of a row-sharded GEMM).  plaidml_executable_run then uploads only bytes / world of it
+ *   from this rank's host buffer and completes it with an all-gather, so that the operand crosses the
+ *   host link once per box, not once per rank.  Every rank must mark the same inputs.
+ * pmlb_exec_gather_output: all ranks' copies of output `index` concatenated in rank order, in device
+ *   memory the executable owns (valid until the next gather or until it is freed); *nbytes receives
+ *   world x the output's size.  Complete on return.  iters > 1 repeats the collective and *mean_ms
+ *   (may be NULL) receives the mean device time of one, by CUDA events on the executable's stream. */
+#define PMLB_SHARD_ID_BYTES 128
+void pmlb_shard_unique_id(plaidml_error* err, char* id);
+void pmlb_shard_init(plaidml_error* err, int rank, int world, const char* id, const char* device);
+void pmlb_shard_shutdown(plaidml_error* err);
+int pmlb_shard_rank(plaidml_error* err);
+int pmlb_shard_world(plaidml_error* err);
+void pmlb_exec_set_input_replicated(plaidml_error* err, plaidml_executable* exec, size_t index, int replicated);
+void* pmlb_exec_gather_output(plaidml_error* err, plaidml_executable* exec, size_t index, size_t* nbytes, size_t iters,
+                              double* mean_ms);
 
 #ifdef __cplusplus
 }

@@ -2,6 +2,7 @@
 #include <mutex>
 
 #include "pml_exec.h"
+#include "pml_shard.h"
 
 using pml::ffiWrap;
 using pml::ffiWrapVoid;
@@ -68,6 +69,52 @@ double pmlb_exec_time_steps(plaidml_error* err, plaidml_executable* exec, size_t
 
 void* pmlb_exec_output_device_ptr(plaidml_error* err, plaidml_executable* exec, size_t index, size_t* nbytes) {
   return ffiWrap<void*>(err, nullptr, [&] { return exec->exec->outputDevicePtr(index, nbytes); });
+}
+
+void pmlb_exec_time_passes(plaidml_error* err, plaidml_executable* exec, size_t iters, bool flush_l2, double* ms_out) {
+  ffiWrapVoid(err, [&] {
+    if (!ms_out) throw std::runtime_error("null result array");
+    exec->exec->timeSteps(iters, flush_l2, ms_out);
+  });
+}
+
+void pmlb_shard_unique_id(plaidml_error* err, char* id) {
+  ffiWrapVoid(err, [&] {
+    if (!id) throw std::runtime_error("null id");
+    pml::ShardComm::instance().makeUniqueId(id);
+  });
+}
+
+void pmlb_shard_init(plaidml_error* err, int rank, int world, const char* id, const char* raw_device) {
+  ffiWrapVoid(err, [&] {
+    if (world > 1 && !id) throw std::runtime_error("null id");
+    std::string device(raw_device ? raw_device : "");
+    if (device.empty()) device = pml::Settings::instance().get("PLAIDML_DEVICE");
+    const int index = pml::parseDeviceId(device);
+    if (cudaSetDevice(index) != cudaSuccess) throw std::runtime_error("No such device: " + device);
+    pml::ShardComm::instance().init(rank, world, id);
+  });
+}
+
+void pmlb_shard_shutdown(plaidml_error* err) {
+  ffiWrapVoid(err, [&] { pml::ShardComm::instance().shutdown(); });
+}
+
+int pmlb_shard_rank(plaidml_error* err) {
+  return ffiWrap<int>(err, 0, [&] { return pml::ShardComm::instance().rank(); });
+}
+
+int pmlb_shard_world(plaidml_error* err) {
+  return ffiWrap<int>(err, 1, [&] { return pml::ShardComm::instance().world(); });
+}
+
+void pmlb_exec_set_input_replicated(plaidml_error* err, plaidml_executable* exec, size_t index, int replicated) {
+  ffiWrapVoid(err, [&] { exec->exec->setInputReplicated(index, replicated != 0); });
+}
+
+void* pmlb_exec_gather_output(plaidml_error* err, plaidml_executable* exec, size_t index, size_t* nbytes, size_t iters,
+                              double* mean_ms) {
+  return ffiWrap<void*>(err, nullptr, [&] { return exec->exec->gatherOutput(index, nbytes, iters, mean_ms); });
 }
 
 void* pmlb_exec_stream(plaidml_error* err, plaidml_executable* exec) {

@@ -1,6 +1,8 @@
 // Planner and executor of the `cuda` device.
 #include "pml_exec.h"
 
+#include "pml_shard.h"
+
 #include "../kernels/conv_route.h"
 
 #include <algorithm>
@@ -259,6 +261,19 @@ class Planner {
         const pmlb_gemm_desc& gd = gm.gemm;
         if (gd.out_dtype != PMLB_F32 || rd.reduce != gd.n || rd.outer != static_cast<int64_t>(gd.batch) * gd.m) continue;
         if (gd.ldc != gd.n || (gd.batch > 1 && gd.stride_c != static_cast<int64_t>(gd.m) * gd.n)) continue;
+        // The kernel folds row maxima only into a product with no other epilogue term (a bias, residual or
+        // ReLU already fused into this GEMM keeps the reduction a separate step), and the fusion is kept only
+        // if the library accepts the combined descriptor: a refusal after this point could not be undone,
+        // since the reduction step is gone and the product may not even be stored.
+        if (gd.epilogue != 0) continue;
+        {
+          pmlb_gemm_desc trial = gd;
+          trial.epilogue |= PMLB_EPI_ROWMAX;
+          pmlb_plan* probe = nullptr;
+          const pmlb_status rc = pmlb_gemm_dispatch(&trial, &probe);
+          if (probe) pmlb_plan_free(probe);
+          if (rc != PMLB_OK) continue;
+        }
         gm.gemm.epilogue |= PMLB_EPI_ROWMAX;
         gm.rowmax = red.result;
         gm.fused += "+rowmax";
@@ -513,6 +528,16 @@ class Planner {
           !pureStrides(s, tB, val(opB).shape, &ub)) {
         return false;
       }
+      // The index ranges must cover the whole output: a dim the contraction writes only partly (a range
+      // shorter than the dim, or index 0 of a longer dim) keeps the aggregation's identity elsewhere, which
+      // the general kernel initialises and this one would leave unwritten.
+      bool covers = true;
+      for (size_t d = 0; d < outShape.rank(); ++d) {
+        const int v = pureVar(s, 0, d);
+        const int64_t span = v >= 0 ? s.extent[v] : 1;
+        if (span != outShape.sizes[d]) covers = false;
+      }
+      if (!covers) return false;
       std::vector<int> mv, nv, kv, bv;
       bool bad = false;
       for (size_t i = 0; i < s.n; ++i) {
@@ -1049,6 +1074,10 @@ class Planner {
   // then the fused element-wise operations, on the general kernels.
   void emitGenericFallback(const Pending& pd, const std::string& why) {
     const POp& op = prog_.ops[pd.op];
+    if (pd.rowmax >= 0) {
+      // (fuseRowMaxima dispatches the combined descriptor before it drops the reduction step)
+      throw std::runtime_error("Contraction '" + op.label + "': " + why + " (after a row maximum was folded into it)");
+    }
     if (pd.result != op.result) {
       throw std::runtime_error("Contraction '" + op.label + "': " + why +
                                " (after its consumers were fused; re-run with PLAIDML_CUDA_GENERIC_ONLY=1)");
@@ -1273,6 +1302,7 @@ Executable::~Executable() {
   for (Step& s : steps_) pmlb_plan_free(s.plan);
   if (arena_) cudaFree(arena_);
   if (flush_) cudaFree(flush_);
+  if (gathered_) cudaFree(gathered_);
   if (status_) cudaFree(status_);
   if (evStart_) cudaEventDestroy(evStart_);
   if (evStop_) cudaEventDestroy(evStop_);
@@ -1376,13 +1406,7 @@ double Executable::run(const std::vector<BufferPtr>& inputs, const std::vector<B
   if (slicedState_ == 0) slicedState_ = prepareSlicedRun() ? 1 : 2;
   if (slicedState_ == 1) return runSliced(inputs, outputs);
   const auto t0 = std::chrono::steady_clock::now();
-  for (size_t i = 0; i < inputs.size(); ++i) {
-    const int id = prog_->inputs[i];
-    const size_t bytes = prog_->values[id].shape.byteSize();
-    if (bytes) {
-      cudaCheck(cudaMemcpyAsync(dev_[id], inputs[i]->data(), bytes, cudaMemcpyHostToDevice, stream_), "input upload");
-    }
-  }
+  for (size_t i = 0; i < inputs.size(); ++i) uploadInput(i, inputs[i]);
   inputsResident_ = true;
   enqueueSteps();
   for (size_t i = 0; i < outputs.size(); ++i) {
@@ -1395,6 +1419,61 @@ double Executable::run(const std::vector<BufferPtr>& inputs, const std::vector<B
   checkStatus();
   const auto t1 = std::chrono::steady_clock::now();
   return std::chrono::duration<double, std::milli>(t1 - t0).count();
+}
+
+// Host -> device copy of one program input on the executable's stream.  In the sharded mode a
+// replicated input travels as this rank's slice only; the all-gather behind it fills in the rest.
+void Executable::uploadInput(size_t i, const BufferPtr& buf) {
+  const int id = prog_->inputs[i];
+  const size_t bytes = prog_->values[id].shape.byteSize();
+  if (!bytes) return;
+  ShardComm& comm = ShardComm::instance();
+  const size_t world = static_cast<size_t>(comm.world());
+  // (slices of whole 16-byte units keep every rank's part aligned for the collective)
+  if (world > 1 && i < replicated_.size() && replicated_[i] && bytes % (16 * world) == 0) {
+    const size_t part = bytes / world;
+    const size_t off = part * static_cast<size_t>(comm.rank());
+    cudaCheck(cudaMemcpyAsync(dev_[id] + off, static_cast<const char*>(buf->data()) + off, part, cudaMemcpyHostToDevice,
+                              stream_), "input upload");
+    comm.allGatherBytes(dev_[id] + off, dev_[id], part, stream_);
+    return;
+  }
+  cudaCheck(cudaMemcpyAsync(dev_[id], buf->data(), bytes, cudaMemcpyHostToDevice, stream_), "input upload");
+}
+
+void Executable::setInputReplicated(size_t index, bool on) {
+  if (index >= prog_->inputs.size()) throw std::runtime_error("No such input");
+  if (replicated_.size() < prog_->inputs.size()) replicated_.assign(prog_->inputs.size(), false);
+  replicated_[index] = on;
+}
+
+void* Executable::gatherOutput(size_t index, size_t* nbytes, size_t iters, double* meanMs) {
+  if (index >= prog_->outputs.size()) throw std::runtime_error("No such output");
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  ShardComm& comm = ShardComm::instance();
+  const int id = prog_->outputs[index];
+  const size_t bytes = prog_->values[id].shape.byteSize();
+  const size_t total = bytes * static_cast<size_t>(comm.world());
+  if (gatheredBytes_ < total) {
+    cudaCheck(cudaStreamSynchronize(stream_), "gather");
+    if (gathered_) cudaFree(gathered_);
+    gathered_ = nullptr;
+    gatheredBytes_ = 0;
+    cudaCheck(cudaMalloc(reinterpret_cast<void**>(&gathered_), total ? total : 256), "cudaMalloc(gathered output)");
+    gatheredBytes_ = total;
+  }
+  if (iters == 0) iters = 1;
+  cudaCheck(cudaEventRecord(evStart_, stream_), "cudaEventRecord");
+  for (size_t i = 0; i < iters; ++i) comm.allGatherBytes(dev_[id], gathered_, bytes, stream_);
+  cudaCheck(cudaEventRecord(evStop_, stream_), "cudaEventRecord");
+  cudaCheck(cudaStreamSynchronize(stream_), "gather");
+  if (meanMs) {
+    float ms = 0.f;
+    cudaCheck(cudaEventElapsedTime(&ms, evStart_, evStop_), "cudaEventElapsedTime");
+    *meanMs = static_cast<double>(ms) / static_cast<double>(iters);
+  }
+  if (nbytes) *nbytes = total;
+  return gathered_;
 }
 
 // A program that is one large GEMM from a host input to a host output is bound by the host link,
@@ -1458,24 +1537,26 @@ double Executable::runSliced(const std::vector<BufferPtr>& inputs, const std::ve
   const pmlb_gemm_desc& d = st.gemm;
   const int slices = static_cast<int>(slicePlans_.size());
   const auto t0 = std::chrono::steady_clock::now();
+  // (a replicated B arrives by slice upload + all-gather, as a whole, before the first block)
+  const bool bGathered = bInput_ >= 0 && ShardComm::instance().world() > 1 &&
+                         static_cast<size_t>(bInput_) < replicated_.size() && replicated_[bInput_];
+  const int bInput = bGathered ? -1 : bInput_;
   for (size_t i = 0; i < inputs.size(); ++i) {
-    if (static_cast<int>(i) == st.aInput || static_cast<int>(i) == bInput_) continue;
-    const int id = prog_->inputs[i];
-    const size_t bytes = prog_->values[id].shape.byteSize();
-    if (bytes) cudaCheck(cudaMemcpyAsync(dev_[id], inputs[i]->data(), bytes, cudaMemcpyHostToDevice, stream_), "input upload");
+    if (static_cast<int>(i) == st.aInput || static_cast<int>(i) == bInput) continue;
+    uploadInput(i, inputs[i]);
   }
   const int aId = prog_->inputs[st.aInput], cId = prog_->outputs[st.cOutput];
   const size_t aBytes = prog_->values[aId].shape.byteSize() / slices;
   const size_t cBytes = prog_->values[cId].shape.byteSize() / slices;
   int first = 0;
-  if (bInput_ >= 0) {
+  if (bInput >= 0) {
     // first row slice by column blocks: A's rows, then a quarter of B at a time
     const int blocks = static_cast<int>(blockPlans_.size());
-    const int bId = prog_->inputs[bInput_];
+    const int bId = prog_->inputs[bInput];
     const size_t eb = prog_->values[bId].shape.byteSize() / (static_cast<size_t>(d.n) * d.k);
     const size_t ob = prog_->values[cId].shape.byteSize() / (static_cast<size_t>(d.m) * d.n);
     const size_t nb = static_cast<size_t>(d.n) / blocks;          // columns per block
-    const char* bHost = static_cast<const char*>(inputs[bInput_]->data());
+    const char* bHost = static_cast<const char*>(inputs[bInput]->data());
     char* cHost = static_cast<char*>(outputs[st.cOutput]->data());
     cudaCheck(cudaMemcpyAsync(dev_[aId], inputs[st.aInput]->data(), aBytes, cudaMemcpyHostToDevice, stream_), "input upload");
     for (int j = 0; j < blocks; ++j) {
@@ -1532,7 +1613,7 @@ double Executable::runResident(size_t iters) {
   return static_cast<double>(ms) / static_cast<double>(iters);
 }
 
-double Executable::timeSteps(size_t iters, bool flushL2) {
+double Executable::timeSteps(size_t iters, bool flushL2, double* perPassMs) {
   if (!inputsResident_) throw std::runtime_error("run the executable once before timing it on resident inputs");
   if (iters == 0) return 0.0;
   cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
@@ -1564,6 +1645,7 @@ double Executable::timeSteps(size_t iters, bool flushL2) {
       float ms = 0.f;
       cudaCheck(cudaEventElapsedTime(&ms, timingEvents_[2 * i], timingEvents_[2 * i + 1]), "cudaEventElapsedTime");
       total += ms;
+      if (perPassMs) perPassMs[done + i] = ms;
     }
   }
   checkStatus();

@@ -51,7 +51,15 @@ class Executable {
   double runResident(size_t iters);
   // Mean milliseconds of one pass of the kernel sequence, each pass timed by its own event pair;
   // with flushL2 a 256 MiB buffer is overwritten before every pass (outside the timed span).
-  double timeSteps(size_t iters, bool flushL2);
+  double timeSteps(size_t iters, bool flushL2, double* perPassMs = nullptr);
+  // Sharded mode (pml_shard.h).  A replicated input is uploaded as this rank's 1 / world slice and
+  // completed by one all-gather on the executable's stream; inputs whose byte size does not divide by
+  // the world size are uploaded whole.
+  void setInputReplicated(size_t index, bool on);
+  // All ranks' copies of output `index`, concatenated in rank order in a buffer the executable owns
+  // (world x nbytes, allocated at the first call): one all-gather on the executable's stream, complete
+  // on return.  With iters > 1 the gather is repeated and *meanMs receives the mean device time of one.
+  void* gatherOutput(size_t index, size_t* nbytes, size_t iters = 1, double* meanMs = nullptr);
   std::string describe() const;
   size_t launchCount() const;
   bool usesGraph() const { return graphState_ == 1; }
@@ -67,6 +75,7 @@ class Executable {
   bool prepareSlicedRun();
   double runSliced(const std::vector<BufferPtr>& inputs, const std::vector<BufferPtr>& outputs);
   void checkStatus();
+  void uploadInput(size_t i, const BufferPtr& buf);
 
   std::shared_ptr<Program> prog_;
   int device_ = 0;
@@ -93,6 +102,9 @@ class Executable {
   int bInput_ = -1;                      // index of B among the program's inputs, or -1
   std::vector<cudaEvent_t> sliceDone_;
   cudaStream_t copyStream_ = nullptr;
+  std::vector<bool> replicated_;         // per program input (sharded mode)
+  char* gathered_ = nullptr;             // world x the largest gathered output
+  size_t gatheredBytes_ = 0;
 };
 
 // Device ids follow the reference's pattern name(-name)*.N (pmlc/rt/device_id.cc:13-38).

@@ -102,8 +102,10 @@ struct TcCfg {
 };
 
 __device__ __forceinline__ float atomic_max_float(float* addr, float v) {
-  // Ordered for all non-NaN values, including -inf as the initial content.
-  if (v >= 0.f) {
+  // Ordered for all non-NaN values, including -inf as the initial content.  The branch is on the sign
+  // bit, not on v >= 0: -0.0 has the bit pattern of the most negative integer and belongs with the
+  // negative values (where, as the smallest unsigned pattern of them, it wins as it should).
+  if (__float_as_int(v) >= 0) {
     return __int_as_float(atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v)));
   }
   return __uint_as_float(atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v)));
@@ -122,11 +124,14 @@ __device__ __forceinline__ void epilogue_store(const TcParams& p, long long out_
         x += static_cast<const int8_t*>(p.residual)[res_off];
       }
     }
+    // An int8 result is the sum wrapped to 8 bits (two's complement) and the ReLU acts on that value:
+    // narrowing comes first, as when every step of the chain is computed in the result type.
+    if (p.out_dtype != kDtI32) x = static_cast<int8_t>(x);
     if (p.epi_flags & kEpiRelu) x = x < 0 ? 0 : x;
     if (p.out_dtype == kDtI32) {
       static_cast<int*>(p.out)[out_off] = x;
     } else {
-      static_cast<int8_t*>(p.out)[out_off] = static_cast<int8_t>(x);  // two's-complement wrap
+      static_cast<int8_t*>(p.out)[out_off] = static_cast<int8_t>(x);
     }
   } else {
     float x = __uint_as_float(raw);

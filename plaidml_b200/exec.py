@@ -46,6 +46,25 @@ class Executable(ForeignObject):
         """Mean milliseconds per pass, each pass timed alone (CUDA events), L2 flushed before it."""
         return ffi_call(lib.pmlb_exec_time_steps, self.as_ptr(), iters, flush_l2)
 
+    def time_passes(self, iters: int, flush_l2: bool = True) -> np.ndarray:
+        """Milliseconds of each of ``iters`` passes, each timed alone (CUDA events), L2 flushed before it."""
+        out = ffi.new("double[]", max(1, iters))
+        ffi_call(lib.pmlb_exec_time_passes, self.as_ptr(), iters, flush_l2, out)
+        return np.array([out[i] for i in range(iters)], dtype=np.float64)
+
+    def set_input_replicated(self, index: int, replicated: bool = True) -> None:
+        """Sharded mode: input ``index`` holds the same data on every rank; a run uploads this rank's
+        1 / world slice and one all-gather over NVLink completes it on every GPU."""
+        ffi_call(lib.pmlb_exec_set_input_replicated, self.as_ptr(), index, int(replicated))
+
+    def gather_output(self, index: int = 0, iters: int = 1) -> tuple[int, int, float]:
+        """Sharded mode: all ranks' copies of output ``index`` in rank order, in device memory the
+        executable owns.  Returns (device address, bytes, mean milliseconds of one all-gather)."""
+        nbytes = ffi.new("size_t*")
+        ms = ffi.new("double*")
+        ptr = ffi_call(lib.pmlb_exec_gather_output, self.as_ptr(), index, nbytes, iters, ms)
+        return int(ffi.cast("uintptr_t", ptr)), int(nbytes[0]), float(ms[0])
+
     def output_device_ptr(self, index: int = 0) -> tuple[int, int]:
         nbytes = ffi.new("size_t*")
         ptr = ffi_call(lib.pmlb_exec_output_device_ptr, self.as_ptr(), index, nbytes)

@@ -96,6 +96,41 @@ def job_throughput(dist, units_this_rank: float, seconds_this_rank: float, devic
     return units / seconds
 
 
+# ---------------------------------------------------------------------------- the library's own communicator
+#
+# libplaidml.so carries the two collectives of the sharded mode itself (a replicated input completed by
+# an all-gather, a gathered output), so that a C or C++ host needs no Python for them.  Its NCCL
+# communicator is set up from a 128-byte id made on rank 0; here torch.distributed carries the id.
+
+def exchange_id(dist, make_id, id_bytes: int = 128) -> bytes:
+    """Rank 0 calls ``make_id()`` (-> bytes); every rank returns rank 0's id.  Works on any backend."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return bytes(id_bytes)
+    box = [make_id() if dist.get_rank() == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    if not isinstance(box[0], (bytes, bytearray)) or len(box[0]) != id_bytes:
+        raise RuntimeError("rank 0 did not deliver a communicator id")
+    return bytes(box[0])
+
+
+def init_library(dist, info: "RankInfo") -> None:
+    """Joins this process to the library's communicator (collective over all ranks)."""
+    from .ffi import ffi, ffi_call, lib
+
+    def make_id() -> bytes:
+        buf = ffi.new("char[128]")
+        ffi_call(lib.pmlb_shard_unique_id, buf)
+        return bytes(ffi.buffer(buf, 128))
+
+    ident = exchange_id(dist, make_id) if info.world > 1 else bytes(128)
+    ffi_call(lib.pmlb_shard_init, info.rank, info.world, ident, info.device_id.encode())
+
+
+def shutdown_library() -> None:
+    from .ffi import ffi_call, lib
+    ffi_call(lib.pmlb_shard_shutdown)
+
+
 # ---------------------------------------------------------------------------- gathered outputs
 #
 # Outputs stay sharded unless the caller asks for the whole tensor: then one all-gather of equal

@@ -185,6 +185,63 @@ def test_qk_batched_gemm_then_row_max():
     np.testing.assert_array_equal(plain.run([s_out])[0], r_out)
 
 
+def test_dense_bias_then_softmax():
+    # a GEMM that already carries a bias keeps its softmax's max-reduction as a separate step (the kernel
+    # folds row maxima only into a product without other epilogue terms); the program must still plan and
+    # its numbers follow the definition
+    g = rng(1250)
+    m, k, n = 96, 160, 200
+    x = g.standard_normal((m, k)).astype(np.float32)
+    w = g.standard_normal((k, n)).astype(np.float32) * 0.1
+    bias = g.standard_normal(n).astype(np.float32)
+    X = Placeholder(DType.FLOAT32, [m, k])
+    logits = op.dot(X, edsl.Constant(w, name="w")) + edsl.Constant(bias, name="b")
+    sm = op.softmax(logits, axis=1)
+    runner = Runner(Program("dense_softmax", [X], [logits, sm]), "cuda.0")
+    desc = runner.executable.describe()
+    assert "tc_gemm" in desc and "+bias" in desc and "+rowmax" not in desc, desc
+    got_logits, got_sm = runner.run([x])
+    ref = oracle.gemm_f32_acc64(x, w) + bias
+    assert max_rel(got_logits, ref) < 1e-5
+    e = np.exp(ref - ref.max(axis=1, keepdims=True))
+    np.testing.assert_allclose(got_sm, e / e.sum(axis=1, keepdims=True), rtol=2e-4, atol=1e-7)
+    # the same with a ReLU between them and only the softmax asked for
+    sm2 = op.softmax(op.relu(logits), axis=1)
+    only = Runner(Program("dense_relu_softmax", [X], [sm2]), "cuda.0")
+    r = np.maximum(ref, 0)
+    e = np.exp(r - r.max(axis=1, keepdims=True))
+    np.testing.assert_allclose(only.run([x])[0], e / e.sum(axis=1, keepdims=True), rtol=2e-4, atol=1e-7)
+
+
+def test_gemm_that_covers_part_of_its_output_leaves_zeros():
+    # the index ranges span 48 of the output's 64 rows (and only column block 0..31 of 40): the rest keeps
+    # the aggregation's identity, 0, which rules out the tensor-core route (it writes only what it covers)
+    g = rng(1251)
+    a = g.standard_normal((48, 64)).astype(np.float32)
+    b = g.standard_normal((64, 32)).astype(np.float32)
+    A = Placeholder(DType.FLOAT32, [48, 64])
+    B = Placeholder(DType.FLOAT32, [64, 32])
+    i, j, k = TensorIndexes(3)
+    C = Contraction().outShape(64, 40).outAccess(i, j).sum(A[i, k] * B[k, j]).build()
+    runner = Runner(Program("partial_cover", [A, B], [C]), "cuda.0")
+    assert "generic_contract" in runner.executable.describe()
+    got = runner.run([a, b])[0]
+    want = np.zeros((64, 40), dtype=np.float32)
+    want[:48, :32] = oracle.gemm_f32_acc64(a, b)
+    assert max_rel(got, want) < 1e-5
+    assert not got[48:].any() and not got[:, 32:].any()
+
+
+def test_int8_gemm_relu_without_casts_wraps_first():
+    g = rng(1252)
+    m, n, k = 64, 32, 256
+    a = g.integers(-128, 128, size=(m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(k, n), dtype=np.int8)
+    A, B, C = P.tile_gemm(DType.INT8, m, n, k)
+    got = Runner(Program("gemm_i8_relu", [A, B], [op.relu(C)]), "cuda.0").run([a, b])[0]
+    np.testing.assert_array_equal(got, np.maximum(oracle.gemm_i8_i32(a, b).astype(np.int8), 0))
+
+
 def test_maxpool_and_mean_and_softmax():
     g = rng(1239)
     x = g.standard_normal((2, 12, 12, 16)).astype(np.float32)

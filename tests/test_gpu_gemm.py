@@ -259,6 +259,35 @@ def test_int8_wraps_to_int8():
     np.testing.assert_array_equal(c.cpu().numpy(), ref)
 
 
+def test_int8_to_int8_relu_acts_on_the_wrapped_value():
+    # sums far outside int8: the result is the sum wrapped to 8 bits, and the ReLU sees that value
+    # (acc = 200 wraps to -56, then ReLU gives 0; a ReLU taken on the 32-bit sum would store -56)
+    g = rng(25)
+    m = n = 128
+    k = 256
+    a = g.integers(-128, 128, size=(1, m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(1, n, k), dtype=np.int8)
+    c, _, _ = run_gemm(K.I8, K.I8, dev(a), dev(b), m, n, k, epilogue=K.EPI_RELU)
+    wrapped = oracle.gemm_i8_i32(a, b, True).astype(np.int8)
+    assert (wrapped < 0).mean() > 0.3 and (np.abs(oracle.gemm_i8_i32(a, b, True)) > 127).mean() > 0.9
+    np.testing.assert_array_equal(c.cpu().numpy(), np.maximum(wrapped, 0))
+
+
+def test_row_max_of_negative_zero():
+    # a row whose largest element is -0.0: the atomic fold must rank it above every negative value
+    m, n, k = 128, 512, 64
+    a = np.zeros((1, m, k), dtype=np.float32)
+    a[:, :, 0] = 1.0
+    b = np.full((1, n, k), 0.0, dtype=np.float32)
+    b[:, :, 0] = -1.0          # every product is -1 ...
+    b[:, 300, :] = -0.0        # ... except one column whose products are all -0.0 (a sum of them stays -0.0)
+    at, bt = dev_bf16(a), dev_bf16(b)
+    c, rowmax, _ = run_gemm(K.BF16, K.F32, at, bt, m, n, k, epilogue=K.EPI_ROWMAX, want_rowmax=True)
+    got = rowmax.cpu().numpy()
+    assert np.all(got == 0.0) and np.all(c.cpu().numpy()[0, :, 300] == 0.0)
+    assert np.all(c.cpu().numpy()[0, :, 299] == -1.0)
+
+
 # --- fp32 as 3xTF32 ---------------------------------------------------------------------------
 
 @pytest.mark.parametrize("b_is_nk", [True, False])

@@ -31,6 +31,26 @@ def _worker(rank, world, port, out_dir):
         whole = shard.gather_output(dist, runner.executable, 0).view(torch.int32).reshape(world * rows, n)
         np.save(os.path.join(out_dir, f"whole{rank}.npy"), whole.cpu().numpy())
         np.save(os.path.join(out_dir, f"local{rank}.npy"), c_local)
+        # the same two collectives inside the library (its own NCCL communicator): B is marked replicated and
+        # every rank's host copy holds only its own 1 / world of the bytes (the rest is poisoned), so a
+        # correct product proves that the all-gather completed the operand; the output is gathered by
+        # pmlb_exec_gather_output into memory the executable owns
+        shard.init_library(dist, info)
+        runner2 = Runner(Program("shard_lib", [A, B], [C]), info.device_id)
+        runner2.executable.set_input_replicated(1, True)
+        flat = b.reshape(-1).copy()
+        part = flat.size // world
+        poisoned = np.full_like(flat, 77)
+        poisoned[rank * part:(rank + 1) * part] = flat[rank * part:(rank + 1) * part]
+        c_lib = runner2.run([a, poisoned.reshape(b.shape)])[0]
+        ptr, nbytes, _ = runner2.executable.gather_output(0)
+        assert nbytes == world * rows * n * 4
+        span = shard._DeviceSpan(ptr, nbytes, runner2.executable.stream)
+        whole2 = torch.as_tensor(span, device="cuda").view(torch.int32).reshape(world * rows, n)
+        np.save(os.path.join(out_dir, f"libwhole{rank}.npy"), whole2.cpu().numpy())
+        np.save(os.path.join(out_dir, f"liblocal{rank}.npy"), c_lib)
+        del runner2
+        shard.shutdown_library()
     finally:
         dist.destroy_process_group()
 
@@ -54,3 +74,5 @@ def test_two_gpus_gather_the_sharded_product(tmp_path):
     for r in range(2):
         np.testing.assert_array_equal(np.load(tmp_path / f"whole{r}.npy"), ref)
         np.testing.assert_array_equal(np.load(tmp_path / f"local{r}.npy"), parts[r])
+        np.testing.assert_array_equal(np.load(tmp_path / f"libwhole{r}.npy"), ref)
+        np.testing.assert_array_equal(np.load(tmp_path / f"liblocal{r}.npy"), parts[r])

@@ -70,3 +70,18 @@ def test_resnet50_logits_match_oracle():
     print("resnet50 logits max-rel error:", err, "steps:", len(lines))
     # 2e-2 relative: the stated tolerance for the network's logits in bf16
     assert err < 2e-2
+
+
+def test_resnet50_with_softmax_output_plans_and_sums_to_one():
+    # fc + bias feeding a softmax: the fc GEMM already has an epilogue term, so the softmax's row maximum
+    # stays a reduction step of its own
+    batch = 2
+    program, _ = programs.resnet50(batch, with_softmax=True)
+    runner = Runner(program, "cuda.0")
+    assert "+rowmax" not in runner.executable.describe()
+    g = rng(1234 + 4)
+    x_bits = f32_to_bf16_bits(g.uniform(0, 1, size=(batch, 224, 224, 3)).astype(np.float32))
+    logits, probs = runner.run([x_bits])
+    e = np.exp(logits - logits.max(axis=1, keepdims=True))
+    np.testing.assert_allclose(probs, e / e.sum(axis=1, keepdims=True), rtol=1e-4, atol=1e-7)
+    np.testing.assert_allclose(probs.sum(axis=1), 1.0, rtol=1e-5)

@@ -60,6 +60,9 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         assert shard.gather_floats(dist, 1.0 + rank) == [1.0 + r for r in range(world)]
         rate = shard.job_throughput(dist, float(hi - lo), 1.0 + rank)
         np.save(os.path.join(out_dir, f"t{rank}.npy"), np.array([slowest, units, rate, lo, hi]))
+        # the communicator id of the library's own collectives travels from rank 0 to everyone
+        ident = shard.exchange_id(dist, lambda: bytes(range(128)))
+        assert ident == bytes(range(128))
         # gathered output: equal slices only (pad the ragged last shard as the caller would)
         mine = torch.full((3, 4), float(rank), dtype=torch.float32)
         whole = shard.all_gather_rows(dist, mine)
@@ -92,6 +95,7 @@ def test_single_process_reductions_are_identities():
     assert shard.gather_floats(None, 3.5) == [3.5]
     assert shard.job_throughput(None, 10.0, 2.0) == 5.0
     shard.barrier(None)
+    assert shard.exchange_id(None, lambda: b"x" * 128) == bytes(128)   # a world of one needs no id
     t = torch.arange(6.0).reshape(2, 3)
     assert torch.equal(shard.all_gather_rows(None, t), t)
     assert isinstance(torch.__version__, str)
