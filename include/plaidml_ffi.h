@@ -294,6 +294,11 @@ double pmlb_exec_run_resident(plaidml_error* err, plaidml_executable* exec, size
 double pmlb_exec_time_steps(plaidml_error* err, plaidml_executable* exec, size_t iters, bool flush_l2);
 /* The same, with every pass's interval written to ms_out[0 .. iters) (milliseconds). */
 void pmlb_exec_time_passes(plaidml_error* err, plaidml_executable* exec, size_t iters, bool flush_l2, double* ms_out);
+/* Every kernel step on its own: ms_out[i] (i < the returned step count, line i of pmlb_exec_describe) receives the
+ * mean milliseconds of step i over `iters` direct launches, each between its own event pair.  Nothing is run when
+ * ms_out is NULL or `capacity` is below the step count; the count is returned either way. */
+size_t pmlb_exec_time_each_step(plaidml_error* err, plaidml_executable* exec, size_t iters, bool flush_l2, double* ms_out,
+                                size_t capacity);
 /* Device address and byte size of output `index` (valid until the executable is freed). */
 void* pmlb_exec_output_device_ptr(plaidml_error* err, plaidml_executable* exec, size_t index, size_t* nbytes);
 /* CUDA stream (cudaStream_t) the executable enqueues on. */

@@ -78,6 +78,15 @@ void pmlb_exec_time_passes(plaidml_error* err, plaidml_executable* exec, size_t 
   });
 }
 
+size_t pmlb_exec_time_each_step(plaidml_error* err, plaidml_executable* exec, size_t iters, bool flush_l2, double* ms_out,
+                                size_t capacity) {
+  return ffiWrap<size_t>(err, 0, [&] {
+    const size_t n = exec->exec->stepCount();
+    if (ms_out && capacity >= n) exec->exec->timeEachStep(iters, flush_l2, ms_out);
+    return n;
+  });
+}
+
 void pmlb_shard_unique_id(plaidml_error* err, char* id) {
   ffiWrapVoid(err, [&] {
     if (!id) throw std::runtime_error("null id");

@@ -1652,6 +1652,30 @@ double Executable::timeSteps(size_t iters, bool flushL2, double* perPassMs) {
   return total / static_cast<double>(iters);
 }
 
+void Executable::timeEachStep(size_t iters, bool flushL2, double* out) {
+  if (!inputsResident_) throw std::runtime_error("run the executable once before timing it on resident inputs");
+  if (iters == 0) iters = 1;
+  cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+  constexpr size_t kFlushBytes = 256u << 20;
+  if (flushL2 && !flush_) cudaCheck(cudaMalloc(reinterpret_cast<void**>(&flush_), kFlushBytes), "cudaMalloc(L2 flush)");
+  for (size_t k = 0; k < steps_.size(); ++k) out[k] = 0.0;
+  for (size_t it = 0; it < iters; ++it) {
+    for (size_t k = 0; k < steps_.size(); ++k) {
+      if (flushL2) cudaCheck(cudaMemsetAsync(flush_, static_cast<int>(it & 0xff), kFlushBytes, stream_), "L2 flush");
+      cudaCheck(cudaEventRecord(evStart_, stream_), "cudaEventRecord");
+      const pmlb_status rc = steps_[k].launch(stream_);
+      if (rc != PMLB_OK) throw std::runtime_error("Kernel step '" + steps_[k].kernel + "' failed: " + pmlb_last_error());
+      cudaCheck(cudaEventRecord(evStop_, stream_), "cudaEventRecord");
+      cudaCheck(cudaEventSynchronize(evStop_), "cudaEventSynchronize");
+      float ms = 0.f;
+      cudaCheck(cudaEventElapsedTime(&ms, evStart_, evStop_), "cudaEventElapsedTime");
+      out[k] += ms;
+    }
+  }
+  for (size_t k = 0; k < steps_.size(); ++k) out[k] /= static_cast<double>(iters);
+  checkStatus();
+}
+
 std::string Executable::describe() const {
   std::ostringstream os;
   for (const Step& s : steps_) os << s.kernel << " " << s.detail << "\n";

@@ -52,6 +52,13 @@ class Executable(ForeignObject):
         ffi_call(lib.pmlb_exec_time_passes, self.as_ptr(), iters, flush_l2, out)
         return np.array([out[i] for i in range(iters)], dtype=np.float64)
 
+    def time_each_step(self, iters: int = 3, flush_l2: bool = False) -> list[tuple[str, float]]:
+        """(plan line, mean milliseconds) of every kernel step launched on its own."""
+        n = ffi_call(lib.pmlb_exec_time_each_step, self.as_ptr(), iters, flush_l2, ffi.NULL, 0)
+        out = ffi.new("double[]", max(1, n))
+        ffi_call(lib.pmlb_exec_time_each_step, self.as_ptr(), iters, flush_l2, out, n)
+        return list(zip(self.describe().strip().splitlines(), [out[i] for i in range(n)]))
+
     def set_input_replicated(self, index: int, replicated: bool = True) -> None:
         """Sharded mode: input ``index`` holds the same data on every rank; a run uploads this rank's
         1 / world slice and one all-gather over NVLink completes it on every GPU."""
