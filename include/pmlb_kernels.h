@@ -216,6 +216,11 @@ typedef struct {
  * weights) always where the shape allows / never; without either flag the library chooses. */
 #define PMLB_CONV_CTA_PAIRS 8
 #define PMLB_CONV_NO_CTA_PAIRS 16
+/* Halo route with three filter columns on 64 input channels: normally one 128 x 192 MMA per filter row
+ * computes the three columns' products side by side and the epilogue adds them with their shifts (the
+ * pixels are read from shared memory once per filter row instead of once per tap).  This flag keeps one
+ * MMA per tap (the form every other halo shape takes). */
+#define PMLB_CONV_NO_COLUMN_MERGE 32
 
 pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* desc, pmlb_plan** plan);
 

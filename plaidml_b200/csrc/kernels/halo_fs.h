@@ -1,0 +1,18 @@
+// Host-side entry of the filter-column-merged halo convolution (halo_fs_kernel.cuh).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "tc_gemm.cuh"
+
+namespace pmlb {
+
+// Pixel buffers that fit beside `weight_bytes` of resident weights (at most 8).
+int halo_fs_stages(int weight_bytes, int stage_bytes);
+// Bytes of shared memory behind the last pixel buffer (what a tap window may read past its buffer).
+int halo_fs_tail_bytes();
+// p: the halo fields of TcParams filled as for the general kernel, halo_stages from halo_fs_stages,
+// idesc for a 128 x 128 MMA, idesc_half for a 128 x 64 one.
+cudaError_t launch_halo_fs(const TcMaps& maps, const TcParams& p, int grid, int out_bytes, cudaStream_t stream);
+
+}  // namespace pmlb

@@ -617,6 +617,7 @@ pmlb_status pmlb_conv_invoke(pmlb_plan* plan, void* stream, const void* input, v
   L.bn_override = d.tile_n;
   if (d.flags & PMLB_CONV_CTA_PAIRS) L.pair_override = 1;
   if (d.flags & PMLB_CONV_NO_CTA_PAIRS) L.pair_override = 0;
+  if (d.flags & PMLB_CONV_NO_COLUMN_MERGE) L.halo_merge_columns = 0;
   L.trace = g_trace_buffer;
   std::string err;
   const int rc = pmlb::tc_launch(L, static_cast<cudaStream_t>(stream), &err);

@@ -89,6 +89,8 @@ struct TcLaunch {
   int grid_override = 0;  // 0 = one CTA per SM
   int split_tail = -1;    // -1 / 1 = halve the tiles of a short last wave; 0 = never
   int pair_override = -1; // -1 = choose; 0 = never pair CTAs on one tile; 1 = whenever the shape allows
+  int halo_merge_columns = 1;  // halo route, 3 filter columns on 64 channels: 1 = one 128 x 192 MMA per filter row
+                               // (columns merged into N, shifted adds in the epilogue); 0 = one MMA per tap
 };
 
 // Returns 0 on success; otherwise 1 (invalid argument), 2 (CUDA error) or

@@ -254,6 +254,30 @@ def test_halo_route_epilogues():
     check_close(out, ref, 1e-4)
 
 
+@pytest.mark.parametrize("out_dtype", [K.BF16, K.F32], ids=["bf16_out", "f32_out"])
+@pytest.mark.parametrize("case", [
+    dict(n=5, h=56, w=56, c=64, r=3, s=3, k=64),        # two image rows per tile, more tiles than one per SM for some
+    dict(n=2, h=13, w=30, c=64, r=3, s=3, k=64),        # four rows per tile, ragged last tile of an image
+    dict(n=3, h=9, w=126, c=64, r=1, s=3, k=64, pad=1), # one filter row; a single image row fills a tile
+    dict(n=40, h=28, w=28, c=64, r=5, s=3, k=64, pad=1),# five filter rows (rows shrink: p = 26), many tiles per CTA
+], ids=["56x56", "13x30", "1x3", "5x3"])
+def test_halo_columns_merged_into_n_matches_one_mma_per_tap(case, out_dtype):
+    # three filter columns side by side in one 128 x 192 MMA per filter row, the shifted adds in the epilogue:
+    # same numbers as one MMA per tap up to the order of three additions, and both match the oracle
+    epi = K.EPI_BIAS | K.EPI_RELU
+    merged, ref, plan = run_conv(74, out_dtype=out_dtype, epilogue=epi, **case)
+    assert plan.kernel == "tc_conv_halo"
+    per_tap, _, plan2 = run_conv(74, out_dtype=out_dtype, epilogue=epi, flags=K.CONV_NO_COLUMN_MERGE, **case)
+    assert plan2.kernel == "tc_conv_halo"
+    if out_dtype == K.F32:
+        check_close(merged, ref, 1e-4)
+        check_close(merged, per_tap, 1e-5)
+    else:
+        check_close(merged, oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+        # at most one bf16 step apart where the f32 sums straddle a rounding boundary
+        assert np.max(np.abs(merged - per_tap)) <= np.max(np.abs(ref)) * 2.0 ** -7
+
+
 # --- IEEE half operands (PLAIDML_DATA_FLOAT16 programs): every route, f16 output packed with and without ReLU ---
 
 @pytest.mark.parametrize("case", [
