@@ -295,7 +295,8 @@ double pmlb_exec_time_steps(plaidml_error* err, plaidml_executable* exec, size_t
 /* The same, with every pass's interval written to ms_out[0 .. iters) (milliseconds). */
 void pmlb_exec_time_passes(plaidml_error* err, plaidml_executable* exec, size_t iters, bool flush_l2, double* ms_out);
 /* Every kernel step on its own: ms_out[i] (i < the returned step count, line i of pmlb_exec_describe) receives the
- * mean milliseconds of step i over `iters` direct launches, each between its own event pair.  Nothing is run when
+ * mean milliseconds of step i over `iters` launches back to back, replayed from a CUDA graph between one event pair
+ * (so the host cost of launching is not in the figure, as in a replayed program).  Nothing is run when
  * ms_out is NULL or `capacity` is below the step count; the count is returned either way. */
 size_t pmlb_exec_time_each_step(plaidml_error* err, plaidml_executable* exec, size_t iters, bool flush_l2, double* ms_out,
                                 size_t capacity);

@@ -98,6 +98,8 @@ pmlb_status pmlb_plan_share_status(pmlb_plan* plan, int* device_word);
 
 /* Name of the kernel family a plan resolved to ("tc_gemm", "tc_conv", "row_reduce", ...). */
 const char* pmlb_plan_kind(const pmlb_plan* plan);
+/* Parts the K range of a GEMM plan is split into (1 = a single pass). */
+int pmlb_plan_split_k(const pmlb_plan* plan);
 
 /* ---------------------------------------------------------------- GEMM
  * C[b, i, j] = sum_k A[b, i, k] * B[b, k, j]   (b_is_nk == 0, B stored [k][n])
@@ -141,6 +143,13 @@ typedef struct {
 /* When the tiles left over after the last full wave occupy at most half of the SMs, 256-wide
  * tiles of that tail are computed as two 128-wide halves; this flag keeps them whole (testing). */
 #define PMLB_GEMM_NO_TAIL_SPLIT 32
+/* Few output tiles and a long K (fewer tiles than half the SMs, eight k-blocks or more, batch 1): the K
+ * range is split over 2..8 CTAs per tile as a batch of partial products into plan scratch (f32 / i32),
+ * and a second small kernel sums the parts in order and applies bias / residual / ReLU / cast.  The
+ * result does not depend on timing (no atomics).  NO_SPLIT_K keeps one pass; SPLIT_K splits whenever
+ * the k-blocks divide evenly, whatever the tile count (for testing). */
+#define PMLB_GEMM_NO_SPLIT_K 64
+#define PMLB_GEMM_SPLIT_K 128
 
 pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* desc, pmlb_plan** plan);
 

@@ -60,8 +60,9 @@ class Executable {
   // (world x nbytes, allocated at the first call): one all-gather on the executable's stream, complete
   // on return.  With iters > 1 the gather is repeated and *meanMs receives the mean device time of one.
   void* gatherOutput(size_t index, size_t* nbytes, size_t iters = 1, double* meanMs = nullptr);
-  // Mean milliseconds of every kernel step on its own (direct launches, one event pair per launch of a
-  // step, L2 optionally flushed before each): out[i] belongs to line i of describe().
+  // Mean milliseconds of every kernel step on its own (`iters` launches of a step back to back, replayed
+  // from a CUDA graph between one event pair, L2 optionally flushed before the first): out[i] belongs to
+  // line i of describe().
   void timeEachStep(size_t iters, bool flushL2, double* out);
   size_t stepCount() const { return steps_.size(); }
   std::string describe() const;

@@ -596,6 +596,18 @@ class Builder {
   }
 
   void bindInput(const ExprPtr& e, const TensorShape* shape) {
+    if (e->kind == ExprNode::ConstTensor && shape == nullptr) {
+      // A constant tensor listed among the inputs (networks/oplib/resnet50.cc:317-319 of the reference passes
+      // its weight constants that way): it takes an argument slot of its shape, which plaidml_executable_run
+      // expects a buffer for, but the program computes with the constant's own data -- in the reference the
+      // constant's second registration as a constant argument replaces the first (pmlc/ast/builder.cc:495-542).
+      PValue v;
+      v.kind = PValue::Input;
+      v.shape = e->buffer->shape();
+      v.name = e->name;
+      prog_->inputs.push_back(addValue(v));
+      return;
+    }
     if (e->kind != ExprNode::Input) throw std::runtime_error("Program inputs must be input placeholders");
     if (shape && *shape != e->shape) e->shape = *shape;
     PValue v;

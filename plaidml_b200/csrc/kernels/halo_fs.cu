@@ -14,18 +14,31 @@ int halo_fs_stages(int weight_bytes, int stage_bytes) {
 
 int halo_fs_tail_bytes() { return kFsTailBytes; }
 
-cudaError_t launch_halo_fs(const TcMaps& maps, const TcParams& p, int grid, int out_bytes, cudaStream_t stream) {
+cudaError_t launch_halo_fs(const TcMaps& maps, const TcParams& p, int grid, int out_bytes, bool dependent_launch,
+                           cudaStream_t stream) {
   const int smem = 1024 + p.conv_r * 3 * 8192 + p.halo_stages * p.halo_stage_bytes + kFsTailBytes;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kFsThreads, 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int na = 0;
+  if (dependent_launch) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
   if (out_bytes == 2) {
     cudaError_t e = cudaFuncSetAttribute(conv_halo_fs_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    conv_halo_fs_kernel<2><<<grid, kFsThreads, smem, stream>>>(maps, p);
-  } else {
-    cudaError_t e = cudaFuncSetAttribute(conv_halo_fs_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    conv_halo_fs_kernel<4><<<grid, kFsThreads, smem, stream>>>(maps, p);
+    return cudaLaunchKernelEx(&cfg, conv_halo_fs_kernel<2>, maps, p);
   }
-  return cudaGetLastError();
+  cudaError_t e = cudaFuncSetAttribute(conv_halo_fs_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  return cudaLaunchKernelEx(&cfg, conv_halo_fs_kernel<4>, maps, p);
 }
 
 }  // namespace pmlb

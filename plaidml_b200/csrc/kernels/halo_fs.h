@@ -13,6 +13,8 @@ int halo_fs_stages(int weight_bytes, int stage_bytes);
 int halo_fs_tail_bytes();
 // p: the halo fields of TcParams filled as for the general kernel, halo_stages from halo_fs_stages,
 // idesc for a 128 x 128 MMA, idesc_half for a 128 x 64 one.
-cudaError_t launch_halo_fs(const TcMaps& maps, const TcParams& p, int grid, int out_bytes, cudaStream_t stream);
+// dependent_launch: the kernel's set-up may overlap the tail of the kernel before it in the stream.
+cudaError_t launch_halo_fs(const TcMaps& maps, const TcParams& p, int grid, int out_bytes, bool dependent_launch,
+                           cudaStream_t stream);
 
 }  // namespace pmlb

@@ -56,6 +56,7 @@ __device__ __forceinline__ void tmem_ld_32x32_x16(uint32_t taddr, uint32_t (&v)[
 template <int OB>
 __global__ void __launch_bounds__(kFsThreads, 1)
 conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ TcParams p) {
+  grid_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t ring = (raw_addr + 1023u) & ~1023u;
@@ -107,14 +108,17 @@ conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ T
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
-  if (warp >= 2 && warp < 4) {
-    const int ch = (warp - 2) * 32 + lane;
-    bias_s[ch] = (p.epi_flags & kEpiBias) ? __ldg(static_cast<const float*>(p.bias) + ch) : 0.f;
-  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // set-up done: from here on the kernel reads and writes tensors, so the kernel before it must be complete
+  grid_dependency_wait();
+  if (warp >= 2 && warp < 4) {
+    const int ch = (warp - 2) * 32 + lane;
+    bias_s[ch] = (p.epi_flags & kEpiBias) ? __ldg(static_cast<const float*>(p.bias) + ch) : 0.f;
+  }
+  __syncthreads();   // (the staged bias, for the epilogue warps)
 
   const int total_tiles = p.batch;   // tiles of one 128-position block each
   const int t_begin = blockIdx.x, t_step = gridDim.x;

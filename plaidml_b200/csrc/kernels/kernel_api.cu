@@ -94,6 +94,8 @@ struct pmlb_plan {
   long long kpad = 0;       // fp32 path: padded K of the split copies
   bool transpose_b = false; // 8/16-bit path: B goes through [n][k] scratch
   bool split = false;
+  int ksplit = 1;           // parts of the K range (two-pass split-K), each of kslice elements
+  long long kslice = 0;
 
   pmlb_conv_desc conv;
   bool filter_set = false;
@@ -219,6 +221,8 @@ size_t pmlb_plan_scratch_bytes(const pmlb_plan* plan) { return plan ? plan->scra
 
 const char* pmlb_plan_kind(const pmlb_plan* plan) { return plan ? plan->kind_name : ""; }
 
+int pmlb_plan_split_k(const pmlb_plan* plan) { return plan ? plan->ksplit : 1; }
+
 pmlb_status pmlb_plan_check(pmlb_plan* plan, void* stream) {
   if (!plan) return fail(PMLB_ERR_INVALID, "null plan");
   cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
@@ -302,6 +306,30 @@ pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* d, pmlb_plan** out) {
       plan->kpad = round_up(d->k, 16 / eb);
       const long long b_mats = d->stride_b != 0 ? d->batch : 1;
       scratch = static_cast<size_t>(b_mats * d->n * plan->kpad * eb);
+    }
+  }
+  // Split K?  (8/16-bit inputs read in place, one matrix, no row maxima: see PMLB_GEMM_NO_SPLIT_K)
+  if (!f32 && !plan->transpose_b && d->batch == 1 && !(d->epilogue & PMLB_EPI_ROWMAX) &&
+      !(d->flags & PMLB_GEMM_NO_SPLIT_K)) {
+    const int bk = 128 / eb;
+    int dev = 0, num_sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long bn = d->n <= 64 ? 64 : 128;
+    const long long tiles = static_cast<long long>((d->m + 127) / 128) * ((d->n + bn - 1) / bn);
+    const int num_kb = d->k / bk;
+    const bool forced = (d->flags & PMLB_GEMM_SPLIT_K) != 0;
+    if (d->k % bk == 0 && ((tiles * 2 <= num_sms && num_kb >= 8) || forced)) {
+      const long long room = forced ? 8 : num_sms / tiles;            // CTAs per tile that still fit one wave
+      int parts = 1;
+      for (int s = 2; s <= 8; ++s) {
+        if (s <= room && num_kb % s == 0 && (forced || num_kb / s >= 4)) parts = s;
+      }
+      if (parts > 1) {
+        plan->ksplit = parts;
+        plan->kslice = static_cast<long long>(num_kb / parts) * bk;
+        scratch = static_cast<size_t>(parts) * d->m * d->n * 4;
+      }
     }
   }
   pmlb_status st = alloc_plan_memory(plan, scratch, true);
@@ -405,6 +433,30 @@ pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream_v, const void* a, con
     cudaError_t e = pmlb::launch_fill_f32(rowmax, static_cast<long long>(d.batch) * d.m,
                                           -__builtin_inff(), stream);
     if (e != cudaSuccess) return cuda_fail(e, "fill(rowmax)");
+  }
+  if (plan->ksplit > 1) {
+    // pass 1: part s multiplies columns [s * kslice, (s + 1) * kslice) of A with the matching rows of B,
+    // as entry s of a batch, into partial products in plan scratch; no epilogue
+    const bool is_int = d.in_dtype == PMLB_I8;
+    L.batch = plan->ksplit;
+    L.k = static_cast<int>(plan->kslice);
+    L.a_batch_stride = plan->kslice;
+    L.b_batch_stride = d.b_is_nk ? plan->kslice : plan->kslice * d.ldb;
+    L.out = plan->scratch;
+    L.ldc = d.n;
+    L.out_batch_stride = static_cast<long long>(d.m) * d.n;
+    L.out_dtype = is_int ? PMLB_I32 : PMLB_F32;
+    L.epi_flags = 0;
+    L.bias = nullptr;
+    L.residual = nullptr;
+    std::string err1;
+    const int rc1 = pmlb::tc_launch(L, stream, &err1);
+    if (rc1 != 0) return fail(static_cast<pmlb_status>(rc1), "gemm (split K): " + err1);
+    // pass 2: the parts summed in order, then the epilogue
+    cudaError_t e = pmlb::launch_splitk_combine(plan->scratch, is_int, plan->ksplit, d.m, d.n, c, d.out_dtype, d.ldc,
+                                                d.epilogue, bias, residual, d.ldr, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "split-K combine");
+    return PMLB_OK;
   }
   std::string err;
   const int rc = pmlb::tc_launch(L, stream, &err);

@@ -381,4 +381,112 @@ cudaError_t launch_filter_relayout(const void* in, int in_dtype, void* out, int 
   return cudaGetLastError();
 }
 
+namespace {
+
+// One thread per four consecutive output columns (n % 4 == 0) or per column.
+template <bool IS_INT, int V>
+__global__ void __launch_bounds__(256)
+splitk_combine_kernel(const void* __restrict__ partials, int parts, int m, int n, void* __restrict__ out, int out_dtype,
+                      long long ldc, int epi_flags, const void* __restrict__ bias, const void* __restrict__ residual,
+                      long long ldr) {
+  const long long per_row = n / V;
+  const long long id = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (id >= static_cast<long long>(m) * per_row) return;
+  const long long row = id / per_row;
+  const int col = static_cast<int>(id - row * per_row) * V;
+  const long long plane = static_cast<long long>(m) * n;
+  const long long off = row * n + col;
+  if constexpr (IS_INT) {
+    int acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0;
+    const int* src = static_cast<const int*>(partials) + off;
+    for (int s = 0; s < parts; ++s) {
+      if constexpr (V == 4) {
+        const int4 v = *reinterpret_cast<const int4*>(src + s * plane);
+        acc[0] += v.x, acc[1] += v.y, acc[2] += v.z, acc[3] += v.w;
+      } else {
+        acc[0] += src[s * plane];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      int x = acc[j];
+      if (epi_flags & PMLB_EPI_BIAS) x += static_cast<const int*>(bias)[col + j];
+      if (epi_flags & PMLB_EPI_RESIDUAL) {
+        x += out_dtype == PMLB_I32 ? static_cast<const int*>(residual)[row * ldr + col + j]
+                                   : static_cast<const int8_t*>(residual)[row * ldr + col + j];
+      }
+      if (out_dtype != PMLB_I32) x = static_cast<int8_t>(x);   // wrap first: the ReLU acts on the int8 value
+      if (epi_flags & PMLB_EPI_RELU) x = x < 0 ? 0 : x;
+      if (out_dtype == PMLB_I32) {
+        static_cast<int*>(out)[row * ldc + col + j] = x;
+      } else {
+        static_cast<int8_t*>(out)[row * ldc + col + j] = static_cast<int8_t>(x);
+      }
+    }
+  } else {
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.f;
+    const float* src = static_cast<const float*>(partials) + off;
+    for (int s = 0; s < parts; ++s) {
+      if constexpr (V == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(src + s * plane);
+        acc[0] += v.x, acc[1] += v.y, acc[2] += v.z, acc[3] += v.w;
+      } else {
+        acc[0] += src[s * plane];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      float x = acc[j];
+      if (epi_flags & PMLB_EPI_BIAS) x += static_cast<const float*>(bias)[col + j];
+      if (epi_flags & PMLB_EPI_RESIDUAL) {
+        const long long r = row * ldr + col + j;
+        if (out_dtype == PMLB_F32) {
+          x += static_cast<const float*>(residual)[r];
+        } else if (out_dtype == PMLB_BF16) {
+          x += __bfloat162float(static_cast<const __nv_bfloat16*>(residual)[r]);
+        } else {
+          x += __half2float(static_cast<const __half*>(residual)[r]);
+        }
+      }
+      if (epi_flags & PMLB_EPI_RELU) x = x < 0.f ? 0.f : x;   // (ordered compare: NaN passes through)
+      const long long o = row * ldc + col + j;
+      if (out_dtype == PMLB_F32) {
+        static_cast<float*>(out)[o] = x;
+      } else if (out_dtype == PMLB_BF16) {
+        static_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(x);
+      } else {
+        static_cast<__half*>(out)[o] = __float2half_rn(x);
+      }
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_splitk_combine(const void* partials, bool is_int, int parts, int m, int n, void* out, int out_dtype,
+                                  long long ldc, int epi_flags, const void* bias, const void* residual, long long ldr,
+                                  cudaStream_t stream) {
+  const bool vec = n % 4 == 0 && (reinterpret_cast<uintptr_t>(partials) & 15u) == 0;
+  const long long threads = static_cast<long long>(m) * (vec ? n / 4 : n);
+  const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+  if (is_int) {
+    if (vec) {
+      splitk_combine_kernel<true, 4><<<grid, 256, 0, stream>>>(partials, parts, m, n, out, out_dtype, ldc, epi_flags, bias, residual, ldr);
+    } else {
+      splitk_combine_kernel<true, 1><<<grid, 256, 0, stream>>>(partials, parts, m, n, out, out_dtype, ldc, epi_flags, bias, residual, ldr);
+    }
+  } else {
+    if (vec) {
+      splitk_combine_kernel<false, 4><<<grid, 256, 0, stream>>>(partials, parts, m, n, out, out_dtype, ldc, epi_flags, bias, residual, ldr);
+    } else {
+      splitk_combine_kernel<false, 1><<<grid, 256, 0, stream>>>(partials, parts, m, n, out, out_dtype, ldc, epi_flags, bias, residual, ldr);
+    }
+  }
+  return cudaGetLastError();
+}
+
 }  // namespace pmlb

@@ -62,4 +62,12 @@ cudaError_t launch_s2d_pack(const void* in, void* out, int n, int h, int w, int 
 cudaError_t launch_filter_s2d(const void* in, int in_dtype, void* out, int out_dtype, int r, int s,
                               int c, int k, int r2, int s2, int dh, int dw, cudaStream_t stream);
 
+// Second pass of a GEMM whose K range was split over `parts` CTAs per output tile: sums the partial
+// products (f32 or i32, [parts][m][n] dense) in part order and applies the epilogue the single-pass kernel
+// would have applied -- bias[n], residual[m][n] (element type of the output, row stride ldr), ReLU, cast
+// to out_dtype (row stride ldc).  Integer partials: out_dtype I32 or I8 (wrap, then ReLU).
+cudaError_t launch_splitk_combine(const void* partials, bool is_int, int parts, int m, int n, void* out, int out_dtype,
+                                  long long ldc, int epi_flags, const void* bias, const void* residual, long long ldr,
+                                  cudaStream_t stream);
+
 }  // namespace pmlb

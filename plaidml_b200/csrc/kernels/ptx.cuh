@@ -36,6 +36,23 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+//
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel
+// before it in the stream is still running, once every CTA of that kernel has executed
+// `launch_dependents` (or exited).  Its CTAs then run their set-up (barriers, TMEM, descriptor prefetch)
+// on SMs the earlier kernel has already left and block in `grid_dependency_wait` until the earlier kernel
+// has completed and its memory operations are visible.  Nothing that depends on, or could disturb, the
+// earlier kernel's data may happen before that wait.  Without the launch attribute both are no-ops.
+
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

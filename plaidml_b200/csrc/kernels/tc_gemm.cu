@@ -405,7 +405,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
       p.fd_tiles_per_img = make_fastdiv(static_cast<uint32_t>(std::max(1, p.halo_tiles_per_img)));
       p.fd_wp = make_fastdiv(static_cast<uint32_t>(std::max(1, p.halo_wp)));
       const int fs_grid = std::min(p.batch, L.grid_override > 0 ? L.grid_override : num_sms);
-      const cudaError_t fe = launch_halo_fs(maps, p, fs_grid, ob_out, stream);
+      const cudaError_t fe = launch_halo_fs(maps, p, fs_grid, ob_out, dependent_launch_enabled(), stream);
       if (fe != cudaSuccess) {
         *err = std::string("kernel launch failed: ") + cudaGetErrorString(fe);
         return 2;

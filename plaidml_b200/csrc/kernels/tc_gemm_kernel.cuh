@@ -22,6 +22,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <type_traits>
 
 #include "ptx.cuh"
@@ -410,6 +411,15 @@ __device__ __forceinline__ float epi_apply(const TcParams& p, uint32_t (&v)[CW],
   return chunk_best;
 }
 
+// PMLB_TC_DEPENDENT_LAUNCH=0 in the environment launches every kernel fully serialised.
+inline bool dependent_launch_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("PMLB_TC_DEPENDENT_LAUNCH");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ TcParams p) {
@@ -419,6 +429,9 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   constexpr int NSPLIT = Cfg::NSPLIT;
   constexpr bool IS_INT = (Cfg::KIND == kMmaI8);
 
+  // (the next kernel of the stream may be scheduled onto SMs as this one leaves them; it waits for this
+  // kernel's completion before it touches memory)
+  grid_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t ring = (raw_addr + 1023u) & ~1023u;           // shared-space address
@@ -504,6 +517,8 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
   }
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // set-up done: from here on the kernel reads and writes tensors, so the kernel before it must be complete
+  grid_dependency_wait();
 
   // (pairs: p.tiles_m counts 256-row pair tiles; CTA `rank` takes rows 128 * rank .. of each)
   const int total_tiles = 2 * p.batch * p.tiles_m * p.tiles_n - p.tiles_full;   // halves count twice
@@ -1507,24 +1522,29 @@ cudaError_t launch_cfg(const TcMaps& maps, const TcParams& p, int grid, cudaStre
   const cudaError_t attr_err = cudaFuncSetAttribute(
       tc_contract_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
   if (attr_err != cudaSuccess) return attr_err;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
   if constexpr (Cfg::CTAS == 2) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-    cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
-    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, tc_contract_kernel<Cfg>, maps, p);
-  } else {
-    tc_contract_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(maps, p);
-    return cudaGetLastError();
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 2;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
   }
+  if (dependent_launch_enabled()) {
+    // the kernel's set-up may overlap the tail of the kernel before it (see grid_dependency_wait)
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, tc_contract_kernel<Cfg>, maps, p);
 }
 
 // Clusters of two that the device can keep resident at once (0 if the query fails).

@@ -24,6 +24,8 @@ GEMM_PLAIN_RESIDUAL = 4
 GEMM_CTA_PAIRS = 8
 GEMM_NO_CTA_PAIRS = 16
 GEMM_NO_TAIL_SPLIT = 32
+GEMM_NO_SPLIT_K = 64
+GEMM_SPLIT_K = 128
 CONV_NO_PACKED_ROWS = 1
 CONV_NO_HALO = 2
 CONV_NO_S2D = 4
@@ -127,6 +129,8 @@ def load() -> C.CDLL:
     lib.pmlb_version.restype = C.c_char_p
     lib.pmlb_plan_kind.restype = C.c_char_p
     lib.pmlb_plan_kind.argtypes = [vp]
+    lib.pmlb_plan_split_k.restype = C.c_int
+    lib.pmlb_plan_split_k.argtypes = [vp]
     lib.pmlb_plan_free.argtypes = [vp]
     lib.pmlb_plan_free.restype = None
     lib.pmlb_plan_scratch_bytes.argtypes = [vp]
@@ -175,6 +179,10 @@ class Plan:
     @property
     def kernel(self) -> str:
         return self.lib.pmlb_plan_kind(self.handle).decode()
+
+    @property
+    def split_k(self) -> int:
+        return self.lib.pmlb_plan_split_k(self.handle)
 
     def check(self, stream: int = 0) -> None:
         check(self.lib.pmlb_plan_check(self.handle, stream))

@@ -316,3 +316,34 @@ def test_conv_f16_operands_and_output(case, relu):
     if relu:
         assert (got >= 0).all()
     check_close(got, ref.astype(np.float16).astype(np.float32), 2e-3)
+
+
+def test_reference_microkernel_convolution_on_the_tensor_core_routes():
+    # the reference's only printed convolution result (1x6x5x7 (*) 1x1x7x11, pmlc/target/x86/tests/xsmm_call.mlir):
+    # all values are small integers, exact in bf16, so the bf16 kernels must reproduce it exactly -- as a 1x1
+    # convolution, and as a 3x3 one whose centre tap is that filter (zero padding and eight zero taps); the seven
+    # channels are padded to eight with a zero channel (the im2col route takes whole 16-byte channel groups)
+    import json
+    from pathlib import Path
+    kat = {k["name"]: k for k in json.loads((Path(__file__).parent / "golden" / "reference_xsmm_kats.json").read_text())}["xsmm_conv_1x1"]
+    x, f = (np.array(v, dtype=np.float32) for v in kat["inputs"])
+    want = np.array(kat["outputs"][0], dtype=np.float32).reshape(1, 6, 5, 11)
+    x8 = np.zeros((1, 6, 5, 8), dtype=np.float32)
+    x8[..., :7] = x
+    for r in (1, 3):
+        f8 = np.zeros((r, r, 8, 11), dtype=np.float32)
+        f8[r // 2, r // 2, :7] = f[0, 0]
+        d = K.ConvDesc()
+        d.in_dtype, d.out_dtype = K.BF16, K.F32
+        d.n, d.h, d.w, d.c, d.r, d.s, d.k, d.p, d.q = 1, 6, 5, 8, r, r, 11, 6, 5
+        d.stride_h = d.stride_w = d.dil_h = d.dil_w = 1
+        d.pad_h = d.pad_w = r // 2
+        plan = K.Plan("conv", d)
+        assert plan.kernel == "tc_conv"
+        f_dev = dev(f8)
+        plan.set_filter(ptr(f_dev), K.F32)
+        x_dev = dev_bf16(x8)
+        out = empty((1, 6, 5, 11), K.F32)
+        plan.conv(ptr(x_dev), ptr(out), None, None)
+        plan.check()
+        np.testing.assert_array_equal(out.cpu().numpy(), want)

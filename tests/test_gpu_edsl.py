@@ -44,6 +44,52 @@ def test_reference_known_answers(kat):
             np.testing.assert_array_equal(got, want.astype(got.dtype))
 
 
+XSMM = {k["name"]: k for k in json.loads((Path(__file__).parent / "golden" / "reference_xsmm_kats.json").read_text())}
+
+
+@pytest.mark.parametrize("generic", [False, True], ids=["tensor_core", "general_kernel"])
+def test_reference_microkernel_known_answers(generic, monkeypatch):
+    # the 8 x 8 dot product and the 1x1 convolution 1x6x5x7 (*) 1x1x7x11 printed by the reference's x86
+    # microkernel test: integer-valued, so the result is exact whatever the route (three TF32 products per
+    # term on the tensor cores, or the general contraction kernel)
+    if generic:
+        monkeypatch.setenv("PLAIDML_CUDA_GENERIC_ONLY", "1")
+    kat = XSMM["xsmm_dot_8x8"]
+    a, b = (np.array(v, dtype=np.float32) for v in kat["inputs"])
+    A, B, C = P.tile_gemm(DType.FLOAT32, 8, 8, 8)
+    runner = Runner(Program("xsmm_dot", [A, B], [C]), "cuda.0")
+    assert ("generic_contract" if generic else "tc_gemm") in runner.executable.describe()
+    np.testing.assert_array_equal(runner.run([a, b])[0], np.array(kat["outputs"][0], dtype=np.float32))
+    kat = XSMM["xsmm_conv_1x1"]
+    x, f = (np.array(v, dtype=np.float32) for v in kat["inputs"])
+    I = Placeholder(DType.FLOAT32, [1, 6, 5, 7])
+    F = Placeholder(DType.FLOAT32, [1, 1, 7, 11])
+    O = op.convolution(I, F, strides=[1, 1], autopad_mode=op.AutoPadMode.VALID)
+    runner = Runner(Program("xsmm_conv", [I, F], [O]), "cuda.0")
+    assert ("generic_contract" if generic else "tc_gemm") in runner.executable.describe()
+    np.testing.assert_array_equal(runner.run([x, f])[0], np.array(kat["outputs"][0], dtype=np.float32).reshape(1, 6, 5, 11))
+
+
+def test_run_on_adopted_caller_memory():
+    # buffers that borrow the caller's (pageable) numpy memory, as the reference's C++ Buffer(ptr, shape) does:
+    # inputs are read from it and outputs land in it
+    g = rng(1260)
+    a = g.integers(-128, 128, size=(96, 64), dtype=np.int8)
+    b = g.integers(-128, 128, size=(64, 80), dtype=np.int8)
+    c = np.full((96, 80), -7, dtype=np.int32)
+    A, B, C = P.tile_gemm(DType.INT8, 96, 80, 64, acc=DType.INT32)
+    program = Program("adopted", [A, B], [C])
+    program.compile("cuda")
+    exe = Executable(program, "cuda.0")
+    ins = [Buffer.adopt(a), Buffer.adopt(b)]
+    outs = [Buffer.adopt(c)]
+    exe.run(ins, outs)
+    np.testing.assert_array_equal(c, oracle.gemm_i8_i32(a, b))
+    a[:] = 1                                   # the buffer is the array: a second run sees the new contents
+    exe.run(ins, outs)
+    np.testing.assert_array_equal(c, np.broadcast_to(b.astype(np.int32).sum(axis=0), (96, 80)))
+
+
 def test_known_answers_also_on_the_general_kernel(monkeypatch):
     monkeypatch.setenv("PLAIDML_CUDA_GENERIC_ONLY", "1")
     for kat in KATS:

@@ -288,6 +288,66 @@ def test_row_max_of_negative_zero():
     assert np.all(c.cpu().numpy()[0, :, 299] == -1.0)
 
 
+# --- K split over several CTAs per tile (two passes: partial products, then sum + epilogue) -------------
+
+@pytest.mark.parametrize("b_is_nk", [True, False], ids=["B[n][k]", "B[k][n]"])
+@pytest.mark.parametrize("out_dtype", [K.F32, K.BF16], ids=["f32_out", "bf16_out"])
+def test_split_k_bf16_with_every_epilogue_term(b_is_nk, out_dtype):
+    g = rng(40)
+    m, n, k = 200, 328, 1024                      # ragged M and N; 16 k-blocks -> 8 parts when forced
+    a = dev_bf16(g.standard_normal((1, m, k)))
+    b = dev_bf16(g.standard_normal((1, n, k) if b_is_nk else (1, k, n)))
+    bias = g.standard_normal(n).astype(np.float32)
+    res_f32 = g.standard_normal((1, m, n)).astype(np.float32) * 8
+    res = dev(res_f32) if out_dtype == K.F32 else dev_bf16(res_f32)
+    epi = K.EPI_BIAS | K.EPI_RESIDUAL | K.EPI_RELU
+    outs = {}
+    for name, flags in (("split", K.GEMM_SPLIT_K), ("single", K.GEMM_NO_SPLIT_K)):
+        c, _, plan = run_gemm(K.BF16, out_dtype, a, b, m, n, k, 1, b_is_nk, epilogue=epi, bias=dev(bias), residual=res, flags=flags)
+        assert plan.split_k == (8 if name == "split" else 1)
+        outs[name] = as_f32(c)
+    ref = oracle.gemm_h16_f32(bits16(a), bits16(b), False, b_is_nk) + bias + as_f32(res)
+    ref = np.maximum(ref, 0)
+    if out_dtype == K.F32:
+        check_close(outs["split"], ref, 1e-4)
+        check_close(outs["split"], outs["single"], 1e-5)
+    else:
+        check_close(outs["split"], oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+
+
+def test_split_k_int8_is_bit_exact_and_chosen_for_few_tiles():
+    g = rng(41)
+    m, n, k = 256, 256, 4096                      # four 128-wide tiles, 32 k-blocks: the library splits by itself
+    a = g.integers(-128, 128, size=(1, m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(1, k, n), dtype=np.int8)
+    bias = g.integers(-1000, 1000, size=n).astype(np.int32)
+    c, _, plan = run_gemm(K.I8, K.I32, dev(a), dev(b), m, n, k, 1, False, epilogue=K.EPI_BIAS | K.EPI_RELU, bias=dev(bias))
+    assert plan.split_k == 8 and plan.scratch_bytes == 8 * m * n * 4
+    ref = np.maximum(oracle.gemm_i8_i32(a, b, False) + bias, 0)
+    np.testing.assert_array_equal(c.cpu().numpy(), ref)
+    # int8 result: the wrapped sum, then the ReLU
+    c8, _, plan8 = run_gemm(K.I8, K.I8, dev(a), dev(b), m, n, k, 1, False, epilogue=K.EPI_RELU)
+    assert plan8.split_k == 8
+    np.testing.assert_array_equal(c8.cpu().numpy(), np.maximum(oracle.gemm_i8_i32(a, b, False).astype(np.int8), 0))
+    # many tiles: one pass
+    _, _, big = run_gemm(K.I8, K.I32, dev(g.integers(-128, 128, size=(1, 4096, 512), dtype=np.int8)),
+                         dev(g.integers(-128, 128, size=(1, 512, 2048), dtype=np.int8)), 4096, 2048, 512, 1, False)
+    assert big.split_k == 1
+
+
+def test_split_k_f16_skinny_fc_shape():
+    # the shape of a classifier head at a small batch: 32 x 1000 x 2048, B stored [k][n]
+    g = rng(42)
+    m, n, k = 32, 1000, 2048
+    a16 = g.standard_normal((1, m, k)).astype(np.float16)
+    b16 = (g.standard_normal((1, k, n)) * 0.03).astype(np.float16)
+    bias = g.standard_normal(n).astype(np.float32)
+    c, _, plan = run_gemm(K.F16, K.F32, dev(a16), dev(b16), m, n, k, 1, False, epilogue=K.EPI_BIAS, bias=dev(bias))
+    assert plan.split_k == 8
+    ref = a16[0].astype(np.float64) @ b16[0].astype(np.float64) + bias
+    assert max_rel(c.cpu().numpy()[0], ref) < 1e-5
+
+
 # --- fp32 as 3xTF32 ---------------------------------------------------------------------------
 
 @pytest.mark.parametrize("b_is_nk", [True, False])

@@ -14,6 +14,7 @@ import oracle
 from plaidml_b200 import kernels as K
 
 KATS = {k["name"]: k for k in json.loads((Path(__file__).parent / "golden" / "reference_kats.json").read_text())}
+XSMM = {k["name"]: k for k in json.loads((Path(__file__).parent / "golden" / "reference_xsmm_kats.json").read_text())}
 
 NP = {"INT64": (np.int64, K.I64), "UINT64": (np.uint64, K.U64), "INT32": (np.int32, K.I32), "INT8": (np.int8, K.I8),
       "FLOAT32": (np.float32, K.F32)}
@@ -125,3 +126,46 @@ def test_oracle_fast_paths_agree_with_walker():
     xm = np.pad(x, ((0, 0), (1, 1), (1, 1), (0, 0)), constant_values=-np.inf)
     want = np.stack([[xm[:, 2 * y:2 * y + 3, 2 * xx:2 * xx + 3, :].max(axis=(1, 2)) for xx in range(3)] for y in range(4)])
     np.testing.assert_array_equal(pooled, np.transpose(want, (2, 0, 1, 3)))
+
+
+def test_microkernel_dot_known_answer():
+    # the 8 x 8 product printed by the reference's x86 microkernel test (integer-valued: exact in f32)
+    kat = XSMM["xsmm_dot_8x8"]
+    a, b = (np.array(v, dtype=np.float32) for v in kat["inputs"])
+    want = np.array(kat["outputs"][0], dtype=np.float32)
+    np.testing.assert_array_equal(oracle.gemm_f32(a, b), want)
+    np.testing.assert_array_equal(oracle.gemm_f32_acc64(a, b), want)
+    np.testing.assert_array_equal(oracle.gemm_i8_i32(a.astype(np.int8), np.clip(b, -128, 127).astype(np.int8))[:, :5],
+                                  (a.astype(np.int32) @ np.clip(b, -128, 127).astype(np.int32))[:, :5])
+    d = K.ContractDesc()
+    d.agg, d.combo, d.n_idx, d.n_src = K.AGG_SUM, K.COMBO_MUL, 3, 2
+    d.range[0] = d.range[1] = d.range[2] = 8
+    d.out = K.make_access(K.F32, [8, 8], [{0: 1}, {1: 1}])
+    d.src[0] = K.make_access(K.F32, [8, 8], [{0: 1}, {2: 1}])
+    d.src[1] = K.make_access(K.F32, [8, 8], [{2: 1}, {1: 1}])
+    np.testing.assert_array_equal(contract(d, [a, b], (8, 8), np.float32), want)
+
+
+def test_microkernel_convolution_known_answer():
+    # the only convolution numbers the reference's tests hold: 1x6x5x7 (*) 1x1x7x11, printed by the same test.
+    # Both the convolution loop nest (which checks every convolution, pooling and ResNet test) and the index-box
+    # walker must reproduce them exactly; so must the loop nest when the same filter sits in the centre of a
+    # zero 3x3 one (padding 1), which exercises its out-of-range taps.
+    kat = XSMM["xsmm_conv_1x1"]
+    x, f = (np.array(v, dtype=np.float32) for v in kat["inputs"])
+    want = np.array(kat["outputs"][0], dtype=np.float32).reshape(1, 6, 5, 11)
+    assert x.shape == (1, 6, 5, 7) and f.shape == (1, 1, 7, 11)
+    np.testing.assert_array_equal(oracle.conv2d_nhwc_f32(x, f), want)
+    f3 = np.zeros((3, 3, 7, 11), dtype=np.float32)
+    f3[1, 1] = f[0, 0]
+    np.testing.assert_array_equal(oracle.conv2d_nhwc_f32(x, f3, pad=(1, 1)), want)
+    bias = np.arange(11, dtype=np.float32) - 400
+    np.testing.assert_array_equal(oracle.conv2d_nhwc_f32(x, f, bias, None, relu=True), np.maximum(want + bias, 0))
+    d = K.ContractDesc()
+    d.agg, d.combo, d.n_idx, d.n_src = K.AGG_SUM, K.COMBO_MUL, 4, 2
+    for v, r in enumerate([6, 5, 7, 11]):          # x, y, ci, co
+        d.range[v] = r
+    d.out = K.make_access(K.F32, [1, 6, 5, 11], [{}, {0: 1}, {1: 1}, {3: 1}])
+    d.src[0] = K.make_access(K.F32, [1, 6, 5, 7], [{}, {0: 1}, {1: 1}, {2: 1}])
+    d.src[1] = K.make_access(K.F32, [1, 1, 7, 11], [{}, {}, {2: 1}, {3: 1}])
+    np.testing.assert_array_equal(contract(d, [x, f], (1, 6, 5, 11), np.float32), want)

@@ -1,0 +1,76 @@
+"""Test sources of the reference checkout, compiled UNMODIFIED against the reference's own C++ headers and
+linked with this repository's libplaidml.so (tests/host/ref_driver.cc and the stand-in headers under
+tests/host/refshim/ replace googletest, gflags and three LLVM ADT headers, nothing of plaidml):
+
+  * plaidml/edsl/examples/gemm.cc: five GEMM tests with exact expected outputs;
+  * networks/oplib/resnet50.cc: the reference's ResNet-50 builder, built at batch 1.
+
+The CPU half needs the checkout (``PLAIDML_REFERENCE_DIR``; skipped when unset) and g++: it compiles both
+binaries into tests/host/_build/ and runs them with --build-only (programs are built, printed and compiled
+for the `cuda` target; no device).  The GPU half runs whatever binaries tests/host/_build/ already holds --
+they link libplaidml.so dynamically, so they always exercise the current library -- on cuda.0 and applies
+the tests' own expectations; it never reads the checkout.
+"""
+
+import os
+import shutil
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+HOST = ROOT / "tests" / "host"
+OUT = HOST / "_build"
+LIB_DIR = ROOT / "plaidml_b200"
+
+BINARIES = {
+    "ref_gemm": (["plaidml/edsl/examples/gemm.cc"], []),
+    "ref_resnet": (["networks/oplib/resnet50.cc"], ["-DPMLB_REF_RESNET"]),
+}
+
+
+def build_binaries(ref_dir: Path) -> list:
+    """Compiles the reference's sources where they lie; outputs only under tests/host/_build/."""
+    OUT.mkdir(parents=True, exist_ok=True)
+    built = []
+    for name, (sources, defines) in BINARIES.items():
+        cmd = ["g++", "-std=c++17", "-O1", "-w", *defines, "-I", str(HOST / "refshim"), "-I", str(ref_dir), "-o", str(OUT / name),
+               str(HOST / "ref_driver.cc"), *[str(ref_dir / s) for s in sources], "-L", str(LIB_DIR), "-l:libplaidml.so",
+               "-Wl,-rpath,$ORIGIN/../../../plaidml_b200"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr[-4000:]
+        built.append(OUT / name)
+    return built
+
+
+def _run(binary: Path, *args) -> str:
+    res = subprocess.run([str(binary), *args], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, (res.stdout[-3000:], res.stderr[-2000:])
+    return res.stdout
+
+
+def test_reference_sources_compile_and_build_their_programs():
+    ref = os.environ.get("PLAIDML_REFERENCE_DIR")
+    if not ref or not (Path(ref) / "plaidml/edsl/edsl.h").exists():
+        pytest.skip("PLAIDML_REFERENCE_DIR does not point at a checkout of the reference")
+    if shutil.which("g++") is None or not (LIB_DIR / "libplaidml.so").exists():
+        pytest.skip("needs g++ and a built libplaidml.so")
+    gemm, resnet = build_binaries(Path(ref))
+    out = _run(gemm, "--build-only")
+    assert "5 tests, 0 failures" in out
+    # the printed programs are the tile module of the reference's own FileCheck expectations
+    assert out.count("tile.contract add, mul") == 5 and "tensor<3x3xsi8>" in out and "tensor<3x3xui64>" in out
+    out = _run(resnet, "--build-only")
+    assert "1 tests, 0 failures" in out and "109 inputs, 1 output" in out
+
+
+@pytest.mark.gpu
+def test_reference_sources_run_on_the_cuda_device():
+    if not (OUT / "ref_gemm").exists():
+        pytest.skip("tests/host/_build/ holds no binaries (built by the CPU half where the checkout is mounted)")
+    out = _run(OUT / "ref_gemm", "--device", "cuda.0")
+    assert "5 tests, 0 failures" in out and "build only" not in out
+    if (OUT / "ref_resnet").exists():
+        out = _run(OUT / "ref_resnet", "--device", "cuda.0")
+        assert "1 tests, 0 failures" in out
