@@ -146,8 +146,11 @@ typedef struct {
 /* Few output tiles and a long K (fewer tiles than half the SMs, eight k-blocks or more, batch 1): the K
  * range is split over 2..8 CTAs per tile as a batch of partial products into plan scratch (f32 / i32),
  * and a second small kernel sums the parts in order and applies bias / residual / ReLU / cast.  The
- * result does not depend on timing (no atomics).  NO_SPLIT_K keeps one pass; SPLIT_K splits whenever
- * the k-blocks divide evenly, whatever the tile count (for testing). */
+ * result does not depend on timing (no atomics), but the order of the f32 additions differs from the
+ * single pass, so a problem that is split at one size and not at another (the tile count decides) can
+ * differ in the last bits between the two.  NO_SPLIT_K keeps one pass; SPLIT_K splits whenever the
+ * k-blocks divide evenly, whatever the tile count (for testing); PMLB_SPLIT_K=0 in the environment turns
+ * the library's own choice off for a whole process. */
 #define PMLB_GEMM_NO_SPLIT_K 64
 #define PMLB_GEMM_SPLIT_K 128
 
@@ -172,15 +175,25 @@ pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream, const void* a, const
  *   - Limit: 8 * (m + n) * round_up(k, 4) + 256 bytes must fit in the array (1024^3 needs
  *     16 MiB); larger problems return PMLB_ERR_UNSUPPORTED with the sizes in the message.
  *   - The first call on each device looks the array's address up (with that device current);
- *     make that first call before starting any stream capture.
+ *     make that first call before starting any stream capture.  With CUDA's default lazy module
+ *     loading the array comes into being at that first call, not when the library is loaded: a
+ *     host that sizes its own pool to what the card has left must make the first call (any small
+ *     problem) on every device BEFORE it measures free memory and builds the pool; afterwards a
+ *     call leaves the amount of free device memory unchanged.
  *   - All calls share the one array per device and each call overwrites it: two calls whose
  *     kernels can overlap on the GPU (different streams, no dependency) race.  Serialise them.
  *   - `wait` != 0 synchronises the stream before returning and reports a device-side pipeline
- *     time-out as PMLB_ERR_TIMEOUT; with `wait` == 0 the call only enqueues.
+ *     time-out as PMLB_ERR_TIMEOUT; with `wait` == 0 the call only enqueues, and a time-out of that
+ *     launch stays in the array's status word until pmlb_gemm_f32_noalloc_status is asked or the
+ *     next call clears the word: a caller that enqueues must ask before it trusts the results.
  * a, b, c are device pointers; lda / ldb / ldc count elements between rows. */
 #define PMLB_NOALLOC_SCRATCH_BYTES (32u << 20)
 pmlb_status pmlb_gemm_f32_noalloc(void* stream, const float* a, const float* b, float* c, int32_t m, int32_t n,
                                   int32_t k, int64_t lda, int64_t ldb, int64_t ldc, int32_t b_is_nk, int32_t wait);
+/* (no counterpart in the reference)  Synchronises `stream` and reports what the launches enqueued by
+ * pmlb_gemm_f32_noalloc(..., wait = 0) on the current device left in the status word: PMLB_OK, or
+ * PMLB_ERR_TIMEOUT (and clears the word).  Allocates nothing. */
+pmlb_status pmlb_gemm_f32_noalloc_status(void* stream);
 
 /* ---------------------------------------------------------------- convolution
  * NHWC activation [n, h, w, c] (*) filter [r, s, c, k] -> [n, p, q, k]:

@@ -564,6 +564,10 @@ class Planner {
       if (M.extent > INT32_MAX || N.extent > INT32_MAX || K.extent > INT32_MAX || B.extent > INT32_MAX) continue;
       // batch must be outermost in the output
       if (B.any && M.any && B.strideOut < M.strideOut * M.extent) continue;
+      // A tiny fp32 product gains nothing from the tensor cores (the launch dominates) and would lose the
+      // last bits to the three-TF32-product form; the general kernel computes it in plain f32, which is what
+      // the reference's exact small-matrix expectations (plaidml/edsl/examples/gemm.cc:79-90) were written for.
+      if (inDtype == PMLB_F32 && M.extent * N.extent * K.extent * B.extent <= 32768) return false;
       pmlb_gemm_desc d;
       std::memset(&d, 0, sizeof(d));
       d.in_dtype = inDtype;

@@ -2,6 +2,7 @@
 // sequences the preparation kernels and the main kernel of each plan.
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -309,8 +310,10 @@ pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* d, pmlb_plan** out) {
     }
   }
   // Split K?  (8/16-bit inputs read in place, one matrix, no row maxima: see PMLB_GEMM_NO_SPLIT_K)
+  const char* split_env = std::getenv("PMLB_SPLIT_K");   // "0": never split (sums then never depend on the tile count)
+  const bool split_allowed = !(split_env && split_env[0] == '0') || (d->flags & PMLB_GEMM_SPLIT_K);
   if (!f32 && !plan->transpose_b && d->batch == 1 && !(d->epilogue & PMLB_EPI_ROWMAX) &&
-      !(d->flags & PMLB_GEMM_NO_SPLIT_K)) {
+      !(d->flags & PMLB_GEMM_NO_SPLIT_K) && split_allowed) {
     const int bk = 128 / eb;
     int dev = 0, num_sms = 0;
     cudaGetDevice(&dev);

@@ -142,3 +142,32 @@ extern "C" pmlb_status pmlb_gemm_f32_noalloc(void* stream_v, const float* a, con
   }
   return PMLB_OK;
 }
+
+extern "C" pmlb_status pmlb_gemm_f32_noalloc_status(void* stream_v) {
+  auto fail = [](pmlb_status code, const std::string& msg) {
+    pmlb_set_last_error_message(msg);
+    return code;
+  };
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    return fail(PMLB_ERR_CUDA, std::string("gemm_f32_noalloc_status: cudaGetDevice: ") + cudaGetErrorString(e));
+  }
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    base = g_scratch_addr[dev];
+  }
+  e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(PMLB_ERR_CUDA, std::string("gemm_f32_noalloc_status: ") + cudaGetErrorString(e));
+  if (base == nullptr) return PMLB_OK;   // no call has run on this device yet
+  int code = 0;
+  e = cudaMemcpy(&code, base, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail(PMLB_ERR_CUDA, std::string("gemm_f32_noalloc_status: ") + cudaGetErrorString(e));
+  if (code != 0) {
+    cudaMemset(base, 0, sizeof(int));
+    return fail(PMLB_ERR_TIMEOUT,
+                "gemm_f32_noalloc: a device-side pipeline wait gave up (role code " + std::to_string(code) + ")");
+  }
+  return PMLB_OK;
+}

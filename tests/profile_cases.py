@@ -1,6 +1,6 @@
 """Small, self-contained runs of single hot-path configurations, for profilers.
 
-    python -m plaidml_b200.kernel_cases <case> [passes]
+    python tests/profile_cases.py <case> [passes]
 
 Each case builds its program through the EDSL, runs it once through ``plaidml_executable_run``
 (inputs seeded, uploaded from host buffers) and then repeats the device-resident kernel
@@ -25,17 +25,20 @@ launches of the kernel of interest:
 from __future__ import annotations
 
 import sys
+from pathlib import Path
 
 import numpy as np
 
-from . import programs
-from .core import DType, Program, f32_to_bf16_bits
-from .edsl import Contraction, TensorIndexes
-from .exec import Runner
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+from plaidml_b200 import programs  # noqa: E402
+from plaidml_b200.core import DType, Program, f32_to_bf16_bits  # noqa: E402
+from plaidml_b200.edsl import Contraction, TensorIndexes  # noqa: E402
+from plaidml_b200.exec import Runner  # noqa: E402
 
 
 def main(argv) -> None:
-    from .core import settings_set
+    from plaidml_b200.core import settings_set
     # one launch per GEMM, as in the device-resident timing of bench.py (plaidml_executable_run would
     # otherwise cut a large single GEMM into four row slices to overlap its host copies)
     settings_set("PLAIDML_CUDA_SLICED_RUN", "0")
@@ -72,15 +75,15 @@ def main(argv) -> None:
         r = Runner(Program(case, [Q, Kt], [S, R] if case == "qk" else [R]), "cuda.0")
         ins = [f32_to_bf16_bits(g.standard_normal((nb, 512, 64))) for _ in range(2)]
     elif case == "rowmax":
-        from .edsl import Placeholder
+        from plaidml_b200.edsl import Placeholder
         S = Placeholder(DType.FLOAT32, [256, 512, 512])
         bb, i, j = TensorIndexes(3)
         R = Contraction(name="rowmax").outShape(256, 512).outAccess(bb, i).max(S[bb, i, j]).build()
         r = Runner(Program(case, [S], [R]), "cuda.0")
         ins = [g.standard_normal((256, 512, 512)).astype(np.float32)]
     elif case == "stem":
-        from . import edsl, op
-        from .edsl import Placeholder, cast
+        from plaidml_b200 import edsl, op
+        from plaidml_b200.edsl import Placeholder, cast
         w = f32_to_bf16_bits(g.standard_normal((7, 7, 3, 64)) * np.sqrt(2.0 / 147))
         I = Placeholder(DType.BFLOAT16, [32, 224, 224, 3])
         F = cast(edsl.Constant(w, name="w", dtype=DType.BFLOAT16), DType.FLOAT32)

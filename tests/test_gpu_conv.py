@@ -321,28 +321,31 @@ def test_conv_f16_operands_and_output(case, relu):
 def test_reference_microkernel_convolution_on_the_tensor_core_routes():
     # the reference's only printed convolution result (1x6x5x7 (*) 1x1x7x11, pmlc/target/x86/tests/xsmm_call.mlir):
     # all values are small integers, exact in bf16, so the bf16 kernels must reproduce it exactly -- as a 1x1
-    # convolution, and as a 3x3 one whose centre tap is that filter (zero padding and eight zero taps); the seven
-    # channels are padded to eight with a zero channel (the im2col route takes whole 16-byte channel groups)
+    # convolution, and as a 3x3 one whose centre tap is that filter (zero padding and eight zero taps) on the
+    # packed-row route (which takes the seven channels as they are) and on the im2col route (whole 16-byte channel
+    # groups: a zero eighth channel)
     import json
     from pathlib import Path
     kat = {k["name"]: k for k in json.loads((Path(__file__).parent / "golden" / "reference_xsmm_kats.json").read_text())}["xsmm_conv_1x1"]
     x, f = (np.array(v, dtype=np.float32) for v in kat["inputs"])
     want = np.array(kat["outputs"][0], dtype=np.float32).reshape(1, 6, 5, 11)
-    x8 = np.zeros((1, 6, 5, 8), dtype=np.float32)
-    x8[..., :7] = x
-    for r in (1, 3):
-        f8 = np.zeros((r, r, 8, 11), dtype=np.float32)
-        f8[r // 2, r // 2, :7] = f[0, 0]
+    for r, c, flags, route in [(1, 8, 0, "tc_conv"), (3, 7, 0, "tc_conv_rows"), (3, 8, 0, "tc_conv_rows"),
+                               (3, 8, K.CONV_NO_PACKED_ROWS, "tc_conv")]:
+        xc = np.zeros((1, 6, 5, c), dtype=np.float32)
+        xc[..., :7] = x
+        fc = np.zeros((r, r, c, 11), dtype=np.float32)
+        fc[r // 2, r // 2, :7] = f[0, 0]
         d = K.ConvDesc()
         d.in_dtype, d.out_dtype = K.BF16, K.F32
-        d.n, d.h, d.w, d.c, d.r, d.s, d.k, d.p, d.q = 1, 6, 5, 8, r, r, 11, 6, 5
+        d.n, d.h, d.w, d.c, d.r, d.s, d.k, d.p, d.q = 1, 6, 5, c, r, r, 11, 6, 5
         d.stride_h = d.stride_w = d.dil_h = d.dil_w = 1
         d.pad_h = d.pad_w = r // 2
+        d.flags = flags
         plan = K.Plan("conv", d)
-        assert plan.kernel == "tc_conv"
-        f_dev = dev(f8)
+        assert plan.kernel == route
+        f_dev = dev(fc)
         plan.set_filter(ptr(f_dev), K.F32)
-        x_dev = dev_bf16(x8)
+        x_dev = dev_bf16(xc)
         out = empty((1, 6, 5, 11), K.F32)
         plan.conv(ptr(x_dev), ptr(out), None, None)
         plan.check()

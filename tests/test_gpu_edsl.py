@@ -47,18 +47,14 @@ def test_reference_known_answers(kat):
 XSMM = {k["name"]: k for k in json.loads((Path(__file__).parent / "golden" / "reference_xsmm_kats.json").read_text())}
 
 
-@pytest.mark.parametrize("generic", [False, True], ids=["tensor_core", "general_kernel"])
-def test_reference_microkernel_known_answers(generic, monkeypatch):
+def test_reference_microkernel_known_answers():
     # the 8 x 8 dot product and the 1x1 convolution 1x6x5x7 (*) 1x1x7x11 printed by the reference's x86
-    # microkernel test: integer-valued, so the result is exact whatever the route (three TF32 products per
-    # term on the tensor cores, or the general contraction kernel)
-    if generic:
-        monkeypatch.setenv("PLAIDML_CUDA_GENERIC_ONLY", "1")
+    # microkernel test, through the EDSL (fp32 products this small run on the general kernel, in plain f32)
     kat = XSMM["xsmm_dot_8x8"]
     a, b = (np.array(v, dtype=np.float32) for v in kat["inputs"])
     A, B, C = P.tile_gemm(DType.FLOAT32, 8, 8, 8)
     runner = Runner(Program("xsmm_dot", [A, B], [C]), "cuda.0")
-    assert ("generic_contract" if generic else "tc_gemm") in runner.executable.describe()
+    assert "generic_contract" in runner.executable.describe()
     np.testing.assert_array_equal(runner.run([a, b])[0], np.array(kat["outputs"][0], dtype=np.float32))
     kat = XSMM["xsmm_conv_1x1"]
     x, f = (np.array(v, dtype=np.float32) for v in kat["inputs"])
@@ -66,8 +62,17 @@ def test_reference_microkernel_known_answers(generic, monkeypatch):
     F = Placeholder(DType.FLOAT32, [1, 1, 7, 11])
     O = op.convolution(I, F, strides=[1, 1], autopad_mode=op.AutoPadMode.VALID)
     runner = Runner(Program("xsmm_conv", [I, F], [O]), "cuda.0")
-    assert ("generic_contract" if generic else "tc_gemm") in runner.executable.describe()
     np.testing.assert_array_equal(runner.run([x, f])[0], np.array(kat["outputs"][0], dtype=np.float32).reshape(1, 6, 5, 11))
+
+
+def test_small_fp32_gemm_is_exact_like_the_reference_expects():
+    # plaidml/edsl/examples/gemm.cc GEMM_FLOAT32 is checked with checkExact in the reference: any true f32
+    # arithmetic reproduces it bit for bit (three TF32 products per term would not)
+    kat = next(k for k in KATS if k["name"] == "GEMM_FLOAT32")
+    program = P.GOLDEN_BUILDERS["GEMM_FLOAT32"]()
+    ins = [np.array(v, dtype=np.float32).reshape(3, 3) for v in kat["inputs"]]
+    got = Runner(program, "cuda.0").run(ins)[0]
+    np.testing.assert_array_equal(got, np.array(kat["outputs"][0], dtype=np.float32).reshape(3, 3))
 
 
 def test_run_on_adopted_caller_memory():

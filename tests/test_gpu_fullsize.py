@@ -91,10 +91,15 @@ def test_cfg5_full_size_row_max_equals_max_of_stored_product():
         check_close(s_out[e:e + 1], ref, 1e-2)
 
 
-def test_cfg4_resnet50_batch_256_entries_do_not_depend_on_the_batch():
+@pytest.mark.parametrize("split_k", [False, True], ids=["one_pass", "split_k"])
+def test_cfg4_resnet50_batch_256_entries_do_not_depend_on_the_batch(split_k, monkeypatch):
     # configuration 4 at its full batch: an image's logits must be the ones it gets in a batch of two (the
-    # oracle-checked size of test_gpu_resnet.py); every kernel route differs between the two batch sizes only in
-    # tiling, never in the order in which a sum is accumulated
+    # oracle-checked size of test_gpu_resnet.py).  With every GEMM in one pass the kernel routes differ between
+    # the two batch sizes only in tiling, never in the order in which a sum is accumulated; with the library's
+    # default, the few-tile layers of the batch of two sum a long K range in parts, which moves f32 sums by a
+    # last bit and, after bf16 rounding of the activations layer after layer, the logits by a few 1e-3
+    if not split_k:
+        monkeypatch.setenv("PMLB_SPLIT_K", "0")
     g = rng(1234 + 4)
     img = g.uniform(0, 1, size=(256, 224, 224, 3)).astype(np.float32)
     bits = f32_to_bf16_bits(img)
@@ -110,6 +115,6 @@ def test_cfg4_resnet50_batch_256_entries_do_not_depend_on_the_batch():
         pair = small.run([np.ascontiguousarray(bits[first:first + 2])])[0]
         err = max_rel(logits[first:first + 2], pair)
         print("batch 256 vs batch 2, images", first, first + 1, "max-rel", err)
-        assert err < 1e-3
+        assert err < (8e-3 if split_k else 1e-3)
     # images differ, so do their logits (guards against a stuck or broadcast batch index)
     assert np.abs(logits[0] - logits[255]).max() > 1e-3

@@ -368,6 +368,18 @@ def test_f32_3xtf32(b_is_nk):
     check_close(c.cpu().numpy(), ref32, 1e-5)
 
 
+def test_f32_reference_microkernel_dot_on_the_tensor_cores():
+    # the 8 x 8 product printed by the reference's x86 microkernel test (pmlc/target/x86/tests/xsmm_call.mlir):
+    # integer-valued operands, so three TF32 products per term reproduce it exactly
+    import json
+    from pathlib import Path
+    kat = {k["name"]: k for k in json.loads((Path(__file__).parent / "golden" / "reference_xsmm_kats.json").read_text())}["xsmm_dot_8x8"]
+    a, b = (np.array(v, dtype=np.float32).reshape(1, 8, 8) for v in kat["inputs"])
+    c, _, plan = run_gemm(K.F32, K.F32, dev(a), dev(b), 8, 8, 8, 1, False)
+    assert plan.kernel == "tc_gemm"
+    np.testing.assert_array_equal(c.cpu().numpy()[0], np.array(kat["outputs"][0], dtype=np.float32))
+
+
 def test_f32_ragged():
     g = rng(31)
     m, n, k = 70, 50, 37

@@ -61,6 +61,32 @@ def test_two_calls_in_a_row_match_the_allocating_path():
         assert max_rel(got, oracle.gemm_f32_acc64(a, b, b_is_nk)) < 1e-5
 
 
+def test_calls_leave_free_device_memory_unchanged_and_enqueued_launches_report_through_status():
+    # the property the entry point exists for: once the first call on the device has happened (it is what brings
+    # the static array into being under lazy module loading), further calls take no device memory at all
+    lib, fn = _noalloc()
+    status = lib.pmlb_gemm_f32_noalloc_status
+    status.argtypes = [C.c_void_p]
+    status.restype = C.c_int
+    g = rng(4243)
+    m, n, k = 192, 160, 96
+    a = g.uniform(-1, 1, size=(m, k)).astype(np.float32)
+    b = g.uniform(-1, 1, size=(k, n)).astype(np.float32)
+    a_t, b_t = dev(a), dev(b)
+    c_t = empty((m, n), K.F32)
+    assert fn(None, ptr(a_t), ptr(b_t), ptr(c_t), m, n, k, k, n, n, 0, 1) == K.OK   # first call (or a later one)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        c_t.fill_(float("nan"))
+        # enqueue only; the status query synchronises and would report a device-side time-out
+        assert fn(None, ptr(a_t), ptr(b_t), ptr(c_t), m, n, k, k, n, n, 0, 0) == K.OK
+        assert status(None) == K.OK, lib.pmlb_last_error().decode()
+        assert max_rel(c_t.cpu().numpy(), oracle.gemm_f32_acc64(a, b, False)) < 1e-5
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+
+
 def test_oversized_problem_is_refused_without_touching_the_device():
     lib, fn = _noalloc()
     t = empty((16,), K.F32)
