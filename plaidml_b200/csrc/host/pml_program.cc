@@ -195,6 +195,84 @@ void computeBounds(BoundedContraction* c, const TensorShape& out, const std::vec
       }
     }
   }
+  // Indices that only constraints on sums or differences limit (0 <= i + j < 5 together with
+  // 0 <= i - j < 5 bounds both, but neither condition alone bounds either): the propagation above needs a
+  // finite range of the other variable to start from.  For those the bounding box of the rational polytope
+  // is computed by Fourier-Motzkin elimination and rounded inwards.  The reference solves an integer
+  // program per index instead (pmlc/dialect/tile/transforms/contraction.cc:576-655,
+  // pmlc/util/bilp/ilp_solver.h:26-100); a box that is a little larger costs only idle iterations here,
+  // because the kernels test every condition at every point.
+  auto unbounded = [&](size_t i) { return lo[i] <= -kInf || hi[i] >= kInf; };
+  bool anyUnbounded = false;
+  for (size_t i = 0; i < n; ++i) anyUnbounded = anyUnbounded || unbounded(i);
+  if (anyUnbounded) {
+    struct Ineq {   // constant + sum coef * x >= 0
+      std::vector<Rational> coef;
+      Rational constant;
+    };
+    std::vector<Ineq> base;
+    for (const Cond& cd : conds) {
+      Ineq ge{cd.f.coef, cd.f.constant};                       // f >= 0
+      Ineq le{std::vector<Rational>(n), Rational(cd.bound - 1) - cd.f.constant};   // bound - 1 - f >= 0
+      for (size_t i = 0; i < n; ++i) le.coef[i] = Rational(0) - cd.f.coef[i];
+      base.push_back(std::move(ge));
+      base.push_back(std::move(le));
+    }
+    for (size_t i = 0; i < n; ++i) {   // what the propagation already knows
+      if (lo[i] > -kInf) {
+        Ineq q{std::vector<Rational>(n), Rational(-lo[i])};
+        q.coef[i] = Rational(1);
+        base.push_back(std::move(q));
+      }
+      if (hi[i] < kInf) {
+        Ineq q{std::vector<Rational>(n), Rational(hi[i])};
+        q.coef[i] = Rational(-1);
+        base.push_back(std::move(q));
+      }
+    }
+    constexpr size_t kMaxIneq = 4000;
+    for (size_t target = 0; target < n; ++target) {
+      if (!unbounded(target)) continue;
+      std::vector<Ineq> sys = base;
+      bool gaveUp = false;
+      for (size_t v = 0; v < n && !gaveUp; ++v) {
+        if (v == target) continue;
+        std::vector<Ineq> pos, neg, rest;
+        for (Ineq& q : sys) {
+          if (q.coef[v].isZero()) rest.push_back(std::move(q));
+          else if (q.coef[v].num > 0) pos.push_back(std::move(q));
+          else neg.push_back(std::move(q));
+        }
+        if (rest.size() + pos.size() * neg.size() > kMaxIneq) {
+          gaveUp = true;
+          break;
+        }
+        for (const Ineq& a : pos) {
+          for (const Ineq& b : neg) {
+            // a / a_v + b / (-b_v) has no x_v
+            const Rational fa = Rational(1) / a.coef[v], fb = Rational(1) / (Rational(0) - b.coef[v]);
+            Ineq q{std::vector<Rational>(n), a.constant * fa + b.constant * fb};
+            bool trivial = true;
+            for (size_t i = 0; i < n; ++i) {
+              if (i == v) continue;
+              q.coef[i] = a.coef[i] * fa + b.coef[i] * fb;
+              if (!q.coef[i].isZero()) trivial = false;
+            }
+            if (!trivial) rest.push_back(std::move(q));
+          }
+        }
+        sys = std::move(rest);
+      }
+      if (gaveUp) continue;
+      for (const Ineq& q : sys) {
+        const Rational a = q.coef[target];
+        if (a.isZero()) continue;
+        const Rational v = (Rational(0) - q.constant) / a;   // a x + c >= 0
+        if (a.num > 0) lo[target] = std::max(lo[target], ceilR(v));
+        else hi[target] = std::min(hi[target], floorR(v));
+      }
+    }
+  }
   c->lower.assign(n, 0);
   c->extent.assign(n, 0);
   for (size_t i = 0; i < n; ++i) {

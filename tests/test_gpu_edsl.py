@@ -75,6 +75,34 @@ def test_small_fp32_gemm_is_exact_like_the_reference_expects():
     np.testing.assert_array_equal(got, np.array(kat["outputs"][0], dtype=np.float32).reshape(3, 3))
 
 
+def test_funky_sum_of_the_reference():
+    # plaidml/edsl/tests/edsl_test.cc:2709-2719 (CppEdsl.FunkySum), checked exactly there
+    I = Placeholder(DType.FLOAT32, [3])
+    Kt = Placeholder(DType.FLOAT32, [3])
+    i, j = TensorIndexes(2)
+    O = Contraction().outShape(5).outAccess(i).sum(I[(i - j + 1) // 2] * Kt[j]).build()
+    got = Runner(Program("funky_sum", [I, Kt], [O]), "cuda.0").run([np.array([1, 2, 3], np.float32), np.array([1, 2, 3], np.float32)])[0]
+    np.testing.assert_array_equal(got, np.array([2, 5, 4, 9, 6], np.float32))
+
+
+def test_contraction_whose_indices_only_sums_and_differences_bound():
+    # O[i + j] += A[i + j, i - j + 4]: the index box comes from Fourier-Motzkin elimination, a little larger than
+    # the set of feasible points; the kernel's per-point range checks make the result the definition's
+    g = rng(1261)
+    a = g.standard_normal((9, 9)).astype(np.float32)
+    A = Placeholder(DType.FLOAT32, [9, 9])
+    i, j = TensorIndexes(2)
+    O = Contraction().outShape(9).outAccess(i + j).sum(A[i + j, i - j + 4]).build()
+    got = Runner(Program("skew", [A], [O]), "cuda.0").run([a])[0]
+    want = np.zeros(9, dtype=np.float64)
+    for ii in range(-10, 20):
+        for jj in range(-10, 20):
+            r, c = ii + jj, ii - jj + 4
+            if 0 <= r < 9 and 0 <= c < 9:
+                want[r] += a[r, c]
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
+
+
 def test_run_on_adopted_caller_memory():
     # buffers that borrow the caller's (pageable) numpy memory, as the reference's C++ Buffer(ptr, shape) does:
     # inputs are read from it and outputs land in it

@@ -251,6 +251,43 @@ def test_bounds_of_a_strided_window_and_a_fractional_index():
     assert "max" in text and "tensor<1x4x4x2xf32>" in text
 
 
+def test_bounds_of_the_reference_compute_bounds_cases():
+    # pmlc/dialect/tile/tests/compute-bounds.mlir:7-25 (@dot: sink (j, k), srcs (j, i) and (i, k) over tensors
+    # 1x784 and 784x512): the pass annotates lowerBounds (0, 0, 0) and upperBounds (783, 0, 511) for (i, j, k)
+    A = Placeholder(DType.FLOAT32, [1, 784])
+    B = Placeholder(DType.FLOAT32, [784, 512])
+    i, j, k = TensorIndexes(3)
+    O = Contraction().outShape(1, 512).outAccess(j, k).sum(A[j, i] * B[i, k]).build()
+    text = bounds_text(Program("dot", [A, B], [O]))
+    # indices are numbered in order of first appearance (sink first): x0 = j, x1 = k, x2 = i
+    assert "x0 in [0, 1)" in text and "x1 in [0, 512)" in text and "x2 in [0, 784)" in text
+    # :29-47 (@no_reduce: sink d0 * 10 + d1 with both indices held to [0, 9] by constraints; an assignment)
+    T = Placeholder(DType.FLOAT32, [10, 10])
+    a, b = TensorIndexes(2)
+    flat = Contraction().outShape(100).outAccess(a * 10 + b).assign(T[a, b]).build()
+    text = bounds_text(Program("no_reduce", [T], [flat]))
+    assert "x0 in [0, 10)" in text and "x1 in [0, 10)" in text
+
+
+def test_bounds_of_indices_limited_only_by_sums_and_differences():
+    # neither 0 <= i + j < 9 nor 0 <= i - j + 4 < 9 bounds i or j alone; together they do (the reference finds
+    # the box with an integer program per index, pmlc/dialect/tile/transforms/contraction.cc:576-655): the
+    # hull is i, j in [-2, 6]
+    A = Placeholder(DType.FLOAT32, [9, 9])
+    i, j = TensorIndexes(2)
+    O = Contraction().outShape(9).outAccess(i + j).sum(A[i + j, i - j + 4]).build()
+    text = bounds_text(Program("skew", [A], [O]))
+    assert "x0 in [-2, 7)" in text and "x1 in [-2, 7)" in text
+    # three coupled indices: 0 <= i + j < 4, 0 <= j + k < 4, 0 <= i + k < 4 and 0 <= i - j + 3 < 7
+    B = Placeholder(DType.FLOAT32, [4, 4, 4, 7])
+    i, j, k = TensorIndexes(3)
+    O = Contraction().outShape(4).outAccess(i + j).sum(B[i + j, j + k, i + k, i - j + 3]).build()
+    text = bounds_text(Program("skew3", [B], [O]))
+    for v in ("x0", "x1", "x2"):
+        lo, hi = (int(t) for t in text.split(v + " in [")[1].split(")")[0].split(", "))
+        assert -4 <= lo <= 0 and 3 < hi <= 8, text     # finite, and wide enough for every feasible point
+
+
 def test_bind_dims_mismatch_is_an_error():
     A = Placeholder(DType.FLOAT32, [5, 1])
     B = Placeholder(DType.FLOAT32, [2, 5])
