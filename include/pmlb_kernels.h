@@ -100,6 +100,15 @@ pmlb_status pmlb_plan_share_status(pmlb_plan* plan, int* device_word);
 const char* pmlb_plan_kind(const pmlb_plan* plan);
 /* Parts the K range of a GEMM plan is split into (1 = a single pass). */
 int pmlb_plan_split_k(const pmlb_plan* plan);
+/* Test hook for the bounded waits of the tensor-core kernel (no counterpart in the reference).  Every
+ * device-side wait (on an operand stage, an accumulator, a residual row) gives up after a wall-clock limit,
+ * normally two seconds; the CTA then raises an abort flag, all its roles leave their loops, it waits a
+ * bounded time for copies still in flight, frees its TMEM, writes a role code to the plan's status word and
+ * returns -- the launch ends, the context stays usable, and pmlb_plan_check reports PMLB_ERR_TIMEOUT.
+ * This call arms the NEXT pmlb_gemm_invoke of a single-pass 8/16-bit GEMM plan so that exactly this
+ * happens: the first CTA's producer never issues its first operand load (nothing is in flight for that
+ * stage, nothing faults) and waits give up after `wait_limit_ms` (1..100).  The launch after it is normal. */
+pmlb_status pmlb_plan_arm_timeout_test(pmlb_plan* plan, int wait_limit_ms);
 
 /* ---------------------------------------------------------------- GEMM
  * C[b, i, j] = sum_k A[b, i, k] * B[b, k, j]   (b_is_nk == 0, B stored [k][n])

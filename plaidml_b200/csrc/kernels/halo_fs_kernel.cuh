@@ -100,6 +100,7 @@ conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ T
     mbar_init(wts_bar, 1);
     *abort_flag = 0;
     *abort_code = 0;
+    abort_flag[2] = p.wait_limit_us;
     fence_mbar_init();
     tma_prefetch_desc(&tm.a0);
     tma_prefetch_desc(&tm.b0);

@@ -95,6 +95,7 @@ struct pmlb_plan {
   long long kpad = 0;       // fp32 path: padded K of the split copies
   bool transpose_b = false; // 8/16-bit path: B goes through [n][k] scratch
   bool split = false;
+  int armed_wait_us = 0;    // > 0: the next invoke runs the time-out test (see pmlb_plan_arm_timeout_test)
   int ksplit = 1;           // parts of the K range (two-pass split-K), each of kslice elements
   long long kslice = 0;
 
@@ -223,6 +224,16 @@ size_t pmlb_plan_scratch_bytes(const pmlb_plan* plan) { return plan ? plan->scra
 const char* pmlb_plan_kind(const pmlb_plan* plan) { return plan ? plan->kind_name : ""; }
 
 int pmlb_plan_split_k(const pmlb_plan* plan) { return plan ? plan->ksplit : 1; }
+
+pmlb_status pmlb_plan_arm_timeout_test(pmlb_plan* plan, int wait_limit_ms) {
+  if (!plan || plan->kind != kPlanGemm) return fail(PMLB_ERR_INVALID, "the time-out test takes a gemm plan");
+  if (wait_limit_ms < 1 || wait_limit_ms > 100) return fail(PMLB_ERR_INVALID, "wait limit must be 1..100 ms");
+  if (plan->gemm.in_dtype == PMLB_F32 || plan->ksplit > 1) {
+    return fail(PMLB_ERR_UNSUPPORTED, "the time-out test takes a single-pass 8/16-bit gemm plan");
+  }
+  plan->armed_wait_us = wait_limit_ms * 1000;
+  return PMLB_OK;
+}
 
 pmlb_status pmlb_plan_check(pmlb_plan* plan, void* stream) {
   if (!plan) return fail(PMLB_ERR_INVALID, "null plan");
@@ -384,6 +395,14 @@ pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream_v, const void* a, con
   if (d.flags & PMLB_GEMM_NO_CTA_PAIRS) L.pair_override = 0;
   if (d.flags & PMLB_GEMM_NO_TAIL_SPLIT) L.split_tail = 0;
   L.trace = g_trace_buffer;
+  if (plan->armed_wait_us > 0) {
+    // one launch whose first operand load of CTA 0 never happens: the wait for it gives up after the armed
+    // limit, every role of that CTA leaves through the tear-down and the status word reports it
+    L.wait_limit_us = plan->armed_wait_us;
+    L.test_drop_load = true;
+    L.pair_override = 0;
+    plan->armed_wait_us = 0;
+  }
 
   if (plan->split) {
     const long long kp = plan->kpad;

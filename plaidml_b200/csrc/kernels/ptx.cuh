@@ -107,7 +107,9 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Waits for the phase with the given parity.  Returns false when the CTA-wide
 // abort flag is up or when the wait ran out of time (in which case it raises the
-// flag itself).  `abort_flag` lives in shared memory.
+// flag itself).  `abort_flag` lives in shared memory: word 0 is the flag, word 1 the code of
+// the role that gave up first (written by the callers), word 2 the wait limit of this launch in
+// microseconds (0 = kWaitLimitNs).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
 #pragma unroll 1
   for (int i = 0; i < 128; ++i) {
@@ -121,7 +123,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (mbar_try_wait(bar, parity)) return true;
     }
     if (*abort_flag != 0) return false;
-    if (global_timer_ns() - t0 > kWaitLimitNs) {
+    const uint64_t limit_us = static_cast<uint64_t>(abort_flag[2]);
+    if (global_timer_ns() - t0 > (limit_us != 0 ? limit_us * 1000ull : kWaitLimitNs)) {
       *abort_flag = 1;
       return false;
     }

@@ -271,6 +271,8 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   p.res_batch = L.res_batch_stride;
   p.rowmax = L.rowmax;
   p.status = L.status;
+  p.wait_limit_us = L.wait_limit_us;
+  p.test_drop_load = L.test_drop_load ? 1 : 0;
   p.trace = L.trace;
   p.idesc = make_idesc(eb, L.is_f16, L.b_mn, bn, pair ? 256 : 128);
 

@@ -81,6 +81,8 @@ struct TcLaunch {
 
   long long* trace = nullptr;  // debugging: device buffer of 4 * 2048 * 3 int64 for CTA 0's timeline
   int* status = nullptr;  // device word that receives a non-zero code if a wait times out
+  int wait_limit_us = 0;  // limit of every device-side wait in microseconds; 0 = two seconds
+  bool test_drop_load = false;  // testing: CTA 0's producer skips its first load, so that a wait runs out
 
   bool force_slow_epilogue = false;  // testing: take the transpose-and-store epilogue
   bool residual_from_global = false;  // testing: staged epilogue reads the residual with plain loads

@@ -131,6 +131,8 @@ def load() -> C.CDLL:
     lib.pmlb_plan_kind.argtypes = [vp]
     lib.pmlb_plan_split_k.restype = C.c_int
     lib.pmlb_plan_split_k.argtypes = [vp]
+    lib.pmlb_plan_arm_timeout_test.restype = C.c_int
+    lib.pmlb_plan_arm_timeout_test.argtypes = [vp, C.c_int]
     lib.pmlb_plan_free.argtypes = [vp]
     lib.pmlb_plan_free.restype = None
     lib.pmlb_plan_scratch_bytes.argtypes = [vp]
@@ -183,6 +185,9 @@ class Plan:
     @property
     def split_k(self) -> int:
         return self.lib.pmlb_plan_split_k(self.handle)
+
+    def arm_timeout_test(self, wait_limit_ms: int = 5) -> None:
+        check(self.lib.pmlb_plan_arm_timeout_test(self.handle, wait_limit_ms))
 
     def check(self, stream: int = 0) -> None:
         check(self.lib.pmlb_plan_check(self.handle, stream))

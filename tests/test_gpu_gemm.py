@@ -348,6 +348,41 @@ def test_split_k_f16_skinny_fc_shape():
     assert max_rel(c.cpu().numpy()[0], ref) < 1e-5
 
 
+# --- bounded waits -------------------------------------------------------------------------------------
+
+def test_a_wait_that_runs_out_ends_the_launch_with_a_status_and_the_plan_stays_usable():
+    # Every device-side wait of the kernel is bounded.  The plan is armed so that, in its next launch, the first
+    # CTA's producer never issues its first operand load and waits give up after 5 ms: the issuer's wait for
+    # that stage runs out, the CTA's roles leave through the tear-down (no trap, nothing left spinning), the
+    # launch returns and the status word says so.  The launch after it is an ordinary one and must be correct.
+    import time
+    g = rng(45)
+    m, n, k = 512, 256, 512
+    a = g.integers(-128, 128, size=(1, m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(1, n, k), dtype=np.int8)
+    d = K.GemmDesc()
+    d.in_dtype, d.out_dtype = K.I8, K.I32
+    d.m, d.n, d.k, d.batch = m, n, k, 1
+    d.lda, d.ldb, d.ldc = k, k, n
+    d.b_is_nk = 1
+    d.flags = K.GEMM_NO_SPLIT_K | K.GEMM_NO_CTA_PAIRS
+    plan = K.Plan("gemm", d)
+    a_t, b_t = dev(a), dev(b)
+    c = empty((1, m, n), K.I32)
+    plan.arm_timeout_test(5)
+    t0 = time.perf_counter()
+    plan.gemm(ptr(a_t), ptr(b_t), ptr(c))
+    with pytest.raises(K.KernelError) as err:
+        plan.check()
+    assert err.value.status == K.ERR_TIMEOUT and "gave up" in str(err.value)
+    assert time.perf_counter() - t0 < 2.0            # milliseconds, not the two-second default
+    # the context is intact and the same plan computes the right product
+    c.fill_(0)
+    plan.gemm(ptr(a_t), ptr(b_t), ptr(c))
+    plan.check()
+    np.testing.assert_array_equal(c.cpu().numpy(), oracle.gemm_i8_i32(a, b, True))
+
+
 # --- fp32 as 3xTF32 ---------------------------------------------------------------------------
 
 @pytest.mark.parametrize("b_is_nk", [True, False])
