@@ -205,6 +205,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
 
   int bn = pick_bn(L, num_sms);
+  bool prefer_pair = false;   // set where the operand-traffic estimate below prefers CTA pairs
   const int bk = 128 / eb;
   if (L.b_mn && bn < bk) bn = bk;           // MN-major B tiles are whole 128-byte chunks of N
   if (L.b_mn && L.nsplit == 2) {
@@ -216,8 +217,29 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     return 1;
   }
 
-  // Two epilogue groups when the main loop of a tile is short next to its epilogue.
   const int num_kb_plain = (L.k + bk - 1) / bk;
+  // Few-tile GEMMs with a long K: 128-wide tiles were chosen above because 256-wide ones would not fill the
+  // device.  Such launches run at the pace operands reach an SM, not at the tensor cores': measured on
+  // 4096-deep int8 and bf16 GEMMs, a CTA ingests ~48 B/clk with 128 x 128 tiles (32 KB per k-block: ~680
+  // cycles where the MMAs need 256) and ~34 B/clk as half of a CTA pair on a 256 x 256 tile (32 KB per
+  // k-block too, ~960 cycles for twice the work), whatever the number of CTAs.  So a wave of pair tiles does a
+  // quarter more per cycle but is coarser: estimate both (waves x cycles per k-block) and take pairs when
+  // they win (1024 x 4096 x 4096: two waves of 128-wide tiles 25.4 us, one wave of pairs 22.7 us; 512 rows:
+  // one wave either way, 17.3 against 22.6 us, pairs lose).
+  if (bn == 128 && L.bn_override == 0 && L.pair_override != 0 && !L.conv && !L.window && !L.halo && !L.s2d &&
+      L.nsplit == 1 && num_kb_plain >= 16 && L.m >= 256 && L.n >= 256) {
+    const long long tiles128 = static_cast<long long>(L.batch) * ((L.m + 127) / 128) * ((L.n + 127) / 128);
+    const long long pairs256 = static_cast<long long>(L.batch) * ((L.m + 255) / 256) * ((L.n + 255) / 256);
+    const long long waves128 = (tiles128 + num_sms - 1) / num_sms;
+    const long long waves_pair = (pairs256 + num_sms / 2 - 1) / (num_sms / 2);
+    const double t128 = static_cast<double>(waves128) * std::max(256.0, 32768.0 / 48.0);
+    const double tpair = static_cast<double>(waves_pair) * std::max(512.0, 32768.0 / 34.0);
+    if (tpair < 0.95 * t128) {
+      bn = 256;
+      prefer_pair = true;
+    }
+  }
+  // Two epilogue groups when the main loop of a tile is short next to its epilogue.
   int groups = (L.conv ? 0 : num_kb_plain) <= 24 ? 2 : 1;
   // CTA pairs: plain GEMMs whose 256-wide tiles have long main loops and fill the machine.
   bool pair = false;
@@ -226,7 +248,7 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
   if (pair_possible && !L.conv && num_kb_plain >= 16 && L.m >= 256) {
     const long long pair_tiles =
         static_cast<long long>(L.batch) * ((L.m + 255) / 256) * ((L.n + 255) / 256);
-    pair = pair_tiles * 2 >= num_sms;
+    pair = pair_tiles * 2 >= num_sms || prefer_pair;
   }
   // Convolutions with several taps are bound by the operand traffic from L2 to shared memory
   // (A and B tiles of every tap and channel block): a pair fetches each weight tile once per

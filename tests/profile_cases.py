@@ -20,6 +20,9 @@ launches of the kernel of interest:
     stem       the first two layers of ResNet-50 at batch 32: 7x7 / 2 convolution on 3 channels
                (s2d_pack_kernel + tc_contract_kernel, space-to-depth route) and the 3x3 / 2 max pool (pool16_kernel)
     resnet N   ResNet-50 v1.5 at batch N
+    resnet_steps N   the same, followed by a table of every kernel step on its own (CUDA events around 20 launches
+               of the step replayed from a CUDA graph: device time without the host's launch cost) beside the time of
+               the whole pass replayed as one graph
 """
 
 from __future__ import annotations
@@ -93,7 +96,7 @@ def main(argv) -> None:
         y = op.pool(y, op.PoolMode.MAX, [3, 3], [2, 2], op.AutoPadMode.EXPLICIT, [1, 1, 1, 1], op.TensorLayout.NXC)
         r = Runner(Program(case, [I], [y]), "cuda.0")
         ins = [f32_to_bf16_bits(g.uniform(0, 1, (32, 224, 224, 3)).astype(np.float32))]
-    elif case == "resnet":
+    elif case in ("resnet", "resnet_steps"):
         batch = int(argv[2]) if len(argv) > 2 else 32
         prog, _ = programs.resnet50(batch)
         r = Runner(prog, "cuda.0")
@@ -102,13 +105,21 @@ def main(argv) -> None:
         passes = 1
     else:
         raise SystemExit(__doc__)
-    if len(argv) > 2 and case != "resnet":
+    if len(argv) > 2 and case not in ("resnet", "resnet_steps"):
         passes = int(argv[2])
     r.run(ins)
     r.executable.time_steps(1, False)      # first use of the kernels of the resident path (module loading)
     ms = r.executable.time_steps(passes, False)
     print(f"{case}: {ms:.4f} ms per pass over {passes} passes; {r.executable.launch_count} launches per pass")
-    print(r.executable.describe())
+    if case == "resnet_steps":
+        r.executable.time_steps(5, False)
+        whole = np.median(r.executable.time_passes(30, False))
+        rows = r.executable.time_each_step(20, False)
+        print(f"whole pass (one graph, L2 not flushed): {whole * 1e3:.1f} us; sum of the steps: {sum(t for _, t in rows) * 1e3:.1f} us")
+        for line, t in rows:
+            print(f"{t * 1e3:8.1f} us  {line}")
+    else:
+        print(r.executable.describe())
 
 
 if __name__ == "__main__":
