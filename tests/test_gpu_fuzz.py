@@ -8,7 +8,7 @@ import pytest
 
 import oracle
 from plaidml_b200 import kernels as K
-from gpu_util import as_f32, bits16, check_close, dev, dev_bf16, rng
+from gpu_util import as_f32, bits16, check_close, dev, dev_bf16, ptr, rng
 
 from test_gpu_conv import run_conv
 from test_gpu_gemm import run_gemm
@@ -165,6 +165,149 @@ def test_random_gemm_many_tiles_per_cta(seed):
     case = dict(m=m, n=n, k=k, b_is_nk=b_is_nk, out=out_dt, epi=epi, flags=flags, tile_n=tile_n)
     try:
         check_close(as_f32(out), ref, tol)
+    except AssertionError as e:
+        raise AssertionError(f"{case}: {e}") from None
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_random_gemm_with_k_split_over_ctas(seed):
+    # two passes: partial products of 2..8 slices of K as a batch, then the parts summed in order with the epilogue;
+    # int8 must stay bit-exact, 16-bit inputs within the one-pass tolerances; forced on arbitrary shapes, and the
+    # library's own choice on few-tile shapes
+    g = rng(9700 + seed)
+    kind = ["i8", "bf16", "bf16"][int(g.integers(0, 3))]
+    bk = 128 if kind == "i8" else 64
+    m = int(g.integers(1, 600))
+    n = int(g.integers(1, 60)) * 8
+    k = bk * int(g.choice([2, 3, 4, 6, 8, 12, 16, 24]))
+    b_is_nk = bool(g.integers(0, 2))
+    epi = int(g.integers(0, 8))
+    forced = bool(g.integers(0, 3))
+    flags = K.GEMM_SPLIT_K if forced else 0
+    bshape = (1, n, k) if b_is_nk else (1, k, n)
+    case = dict(kind=kind, m=m, n=n, k=k, b_is_nk=b_is_nk, epi=epi, forced=forced)
+    if kind == "i8":
+        out_dt = K.I32 if g.integers(0, 3) else K.I8
+        a = g.integers(-128, 128, size=(1, m, k), dtype=np.int8)
+        b = g.integers(-128, 128, size=bshape, dtype=np.int8)
+        if out_dt == K.I8:
+            epi &= K.EPI_RELU | K.EPI_RESIDUAL      # (a bias is 32-bit: the result would be, too)
+        bias = g.integers(-1000, 1000, size=n, dtype=np.int32) if epi & K.EPI_BIAS else None
+        res = None
+        if epi & K.EPI_RESIDUAL:
+            res = g.integers(-1000, 1000, size=(1, m, n), dtype=np.int32) if out_dt == K.I32 else g.integers(
+                -128, 128, size=(1, m, n), dtype=np.int8)
+        out, _, plan = run_gemm(K.I8, out_dt, dev(a), dev(b), m, n, k, 1, b_is_nk, epilogue=epi,
+                                bias=None if bias is None else dev(bias), residual=None if res is None else dev(res), flags=flags)
+        ref = oracle.gemm_i8_i32(a[0], b[0], b_is_nk)[None].astype(np.int64)
+        if bias is not None:
+            ref = ref + bias[None, None, :]
+        if res is not None:
+            ref = ref + res
+        if out_dt == K.I8:
+            ref = ref.astype(np.int8)                # wrap, then the ReLU
+        if epi & K.EPI_RELU:
+            ref = np.maximum(ref, 0)
+        if forced and (b_is_nk or n % 16 == 0):      # (a [k][n] B whose rows are not 16-byte multiples is copied
+            assert plan.split_k > 1, case            #  transposed first and keeps the one-pass route)
+        np.testing.assert_array_equal(out.cpu().numpy(), ref.astype(np.int32 if out_dt == K.I32 else np.int8), err_msg=str(case))
+        return
+    a_t = dev_bf16(g.standard_normal((1, m, k)))
+    b_t = dev_bf16(g.standard_normal(bshape))
+    out_dt = K.BF16 if g.integers(0, 2) else K.F32
+    bias = g.standard_normal(n).astype(np.float32) if epi & K.EPI_BIAS else None
+    res = None
+    if epi & K.EPI_RESIDUAL:
+        res = dev_bf16(g.standard_normal((1, m, n))) if out_dt == K.BF16 else dev(g.standard_normal((1, m, n)).astype(np.float32))
+    out, _, plan = run_gemm(K.BF16, out_dt, a_t, b_t, m, n, k, 1, b_is_nk, epilogue=epi,
+                            bias=None if bias is None else dev(bias), residual=res, flags=flags)
+    if forced:
+        assert plan.split_k > 1, case
+    ref = oracle.gemm_h16_f32(bits16(a_t), bits16(b_t), False, b_is_nk).astype(np.float64)
+    if bias is not None:
+        ref = ref + bias[None, None, :]
+    if res is not None:
+        ref = ref + as_f32(res)
+    if epi & K.EPI_RELU:
+        ref = np.maximum(ref, 0)
+    ref = ref.astype(np.float32)
+    tol = 1e-4
+    if out_dt == K.BF16:
+        ref, tol = oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2
+    try:
+        check_close(as_f32(out), ref, tol)
+    except AssertionError as e:
+        raise AssertionError(f"{case} split_k={plan.split_k}: {e}") from None
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_few_tile_long_k_gemm(seed):
+    # the shapes of a sharded GEMM (a few hundred rows against a wide, deep B): the library picks 128-wide tiles or CTA
+    # pairs on 256-wide ones from an operand-traffic estimate; int8 bit-exact either way
+    g = rng(9750 + seed)
+    m = int(g.choice([256, 384, 512, 640, 1024, 1152]))
+    n = int(g.choice([1024, 2048, 4096]))
+    k = int(g.choice([2048, 4096]))
+    a = g.integers(-128, 128, size=(1, m, k), dtype=np.int8)
+    b = g.integers(-128, 128, size=(1, k, n), dtype=np.int8)
+    out, _, _ = run_gemm(K.I8, K.I32, dev(a), dev(b), m, n, k, 1, False, flags=K.GEMM_NO_SPLIT_K)
+    rows = np.sort(g.choice(m, size=24, replace=False))
+    np.testing.assert_array_equal(out.cpu().numpy()[0][rows], oracle.gemm_i8_i32(np.ascontiguousarray(a[0][rows]), b[0], False))
+    # every row through the row-sum identity
+    np.testing.assert_array_equal(out.cpu().numpy()[0].astype(np.int64).sum(axis=1),
+                                  a[0].astype(np.int64) @ b[0].astype(np.int64).sum(axis=1))
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_random_halo_conv_with_merged_filter_columns(seed):
+    # three filter columns on 64 channels into 64: two columns side by side in one MMA, the third from a shifted
+    # window, the shifted add in the epilogue; image sizes, filter heights and paddings at random (row widths from
+    # 6 to 126 padded positions: one to many image rows per tile, ragged last tiles, more tiles than SMs)
+    g = rng(9600 + seed)
+    r = int(g.choice([1, 3, 3, 3, 5]))
+    pad_w = 1
+    while True:     # the route wants three quarters of a tile's 128 rows to be outputs
+        w = int(g.integers(4, 125))
+        h = int(g.integers(max(r, 3), 40))
+        pad_h = int(g.integers(0, r // 2 + 1))
+        if min(128 // (w + 2), h + 2 * pad_h - r + 1) * w >= 96:
+            break
+    n = int(g.integers(1, 7)) if w * h < 1500 else int(g.integers(1, 3))
+    out_dtype = K.BF16 if g.integers(0, 2) else K.F32
+    epi = int(g.choice([0, K.EPI_BIAS, K.EPI_RELU, K.EPI_BIAS | K.EPI_RELU]))
+    g2 = rng(9600 + seed)
+    p, q = h + 2 * pad_h - r + 1, w + 2 * pad_w - 3 + 1
+    x = dev_bf16(g2.uniform(-1, 1, size=(n, h, w, 64)))
+    f32 = (g2.standard_normal((r, 3, 64, 64)) * np.sqrt(2.0 / (r * 3 * 64))).astype(np.float32)
+    bias = g2.standard_normal(64).astype(np.float32) if epi & K.EPI_BIAS else None
+    outs = []
+    for flags in (0, K.CONV_NO_COLUMN_MERGE):
+        d = K.ConvDesc()
+        d.in_dtype, d.out_dtype = K.BF16, out_dtype
+        d.n, d.h, d.w, d.c, d.r, d.s, d.k, d.p, d.q = n, h, w, 64, r, 3, 64, p, q
+        d.stride_h = d.stride_w = d.dil_h = d.dil_w = 1
+        d.pad_h, d.pad_w = pad_h, pad_w
+        d.epilogue, d.flags = epi, flags
+        plan = K.Plan("conv", d)
+        if plan.kernel != "tc_conv_halo":
+            pytest.skip(f"shape takes {plan.kernel}")
+        f_dev = dev(f32)
+        plan.set_filter(ptr(f_dev), K.F32)
+        from gpu_util import empty
+        out = empty((n, p, q, 64), out_dtype)
+        out.fill_(float("nan"))
+        plan.conv(ptr(x), ptr(out), ptr(dev(bias)) if bias is not None else None, None)
+        plan.check()
+        outs.append(as_f32(out))
+    ref = oracle.conv2d_nhwc_f32(as_f32(x), oracle.bf16_to_f32(oracle.f32_to_bf16(f32)), bias, None, (1, 1), (pad_h, pad_w),
+                                 (1, 1), bool(epi & K.EPI_RELU), out_hw=(p, q))
+    case = dict(n=n, h=h, w=w, r=r, pad_h=pad_h, out=out_dtype, epi=epi)
+    try:
+        if out_dtype == K.F32:
+            check_close(outs[0], ref, 1e-4)
+            check_close(outs[0], outs[1], 1e-5)
+        else:
+            check_close(outs[0], oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
     except AssertionError as e:
         raise AssertionError(f"{case}: {e}") from None
 
