@@ -247,11 +247,18 @@ typedef struct {
  * weights) always where the shape allows / never; without either flag the library chooses. */
 #define PMLB_CONV_CTA_PAIRS 8
 #define PMLB_CONV_NO_CTA_PAIRS 16
-/* Halo route with three filter columns on 64 input channels: normally one 128 x 192 MMA per filter row
- * computes the three columns' products side by side and the epilogue adds them with their shifts (the
- * pixels are read from shared memory once per filter row instead of once per tap).  This flag keeps one
- * MMA per tap (the form every other halo shape takes). */
+/* Halo route with three filter columns on 64 input channels: normally one 128 x 128 MMA per filter row
+ * computes two columns' products side by side, one 128 x 64 MMA the third, and the epilogue adds the second
+ * block one position late (the pixels are read from shared memory twice per filter row instead of once
+ * per tap).  This flag keeps one MMA per tap (the form every other halo shape takes). */
 #define PMLB_CONV_NO_COLUMN_MERGE 32
+/* The convolution is followed by a 3 x 3 max pool of stride 2 with one pixel of padding on each side, and
+ * the plan computes both: `output` of pmlb_conv_invoke is then [n][p / 2][q / 2][k] and the convolution's
+ * own output is never written.  Accepted (else pmlb_conv_dispatch returns PMLB_ERR_UNSUPPORTED and the
+ * caller plans the two steps separately) for the space-to-depth route with a 7-wide filter, k = 64, a
+ * 16-bit output, p a multiple of 4 and q at most 124, bias and ReLU as the only epilogue terms: the first
+ * layer of image networks.  No counterpart in the reference, whose stencil pass fuses no pooling. */
+#define PMLB_CONV_MAX_POOL_3X3_S2 64
 
 pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* desc, pmlb_plan** plan);
 

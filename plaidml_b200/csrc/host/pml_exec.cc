@@ -191,6 +191,7 @@ class Planner {
                      [](const Pending& x, const Pending& y) { return x.position < y.position; });
 
     fuseRowMaxima();
+    fuseConvMaxPool();
 
     // ---- phase B: which steps are needed for the outputs
     std::vector<bool> needed(nv, false);
@@ -278,6 +279,52 @@ class Planner {
         gm.rowmax = red.result;
         gm.fused += "+rowmax";
         red.dropped = true;
+        break;
+      }
+    }
+  }
+
+  // A 3 x 3 / 2 max pool (one pixel of padding) right behind a convolution that nothing else reads, where
+  // the library has a kernel for the pair (the first layer of image networks: the convolution's output, four
+  // times the pooled tensor, is then never written).  Kept only if the library accepts the combined descriptor.
+  void fuseConvMaxPool() {
+    if (getenvFlag("PLAIDML_CUDA_NO_POOL_FUSION")) return;
+    for (size_t r = 0; r < pending_.size(); ++r) {
+      Pending& pl = pending_[r];
+      if (pl.dropped || pl.kind != Pending::Pool) continue;
+      const pmlb_pool_desc& pd = pl.pool;
+      if (pd.agg != PMLB_AGG_MAX || pd.r != 3 || pd.s != 3 || pd.stride_h != 2 || pd.stride_w != 2 || pd.pad_h != 1 ||
+          pd.pad_w != 1) {
+        continue;
+      }
+      const int mid = root(pl.a);
+      for (size_t g = 0; g < r; ++g) {
+        Pending& cv = pending_[g];
+        if (cv.dropped || cv.kind != Pending::Conv || root(cv.result) != mid) continue;
+        const pmlb_conv_desc& cd = cv.conv;
+        if (cd.n != pd.n || cd.p != pd.h || cd.q != pd.w || cd.k != pd.c || cd.out_dtype != pd.dtype ||
+            pd.p * 2 != cd.p || pd.q * 2 != cd.q || cv.residual >= 0) {
+          break;
+        }
+        // the convolution's output has no other reader and is not a program output
+        bool shared = false;
+        for (int o : prog_.outputs) shared = shared || root(o) == mid;
+        for (size_t k = 0; k < pending_.size() && !shared; ++k) {
+          if (k == r || pending_[k].dropped) continue;
+          for (int in : pending_[k].inputs) shared = shared || root(in) == mid;
+        }
+        if (shared) break;
+        pmlb_conv_desc trial = cd;
+        trial.flags |= PMLB_CONV_MAX_POOL_3X3_S2;
+        pmlb_plan* probe = nullptr;
+        const pmlb_status rc = pmlb_conv_dispatch(&trial, &probe);
+        if (probe) pmlb_plan_free(probe);
+        if (rc != PMLB_OK) break;
+        cv.conv = trial;
+        cv.result = pl.result;
+        cv.position = pl.position;
+        cv.fused += "+maxpool3x3/2 -> " + std::to_string(pd.p) + "x" + std::to_string(pd.q);
+        pl.dropped = true;
         break;
       }
     }
@@ -999,9 +1046,9 @@ class Planner {
         pmlbCheck(rc, "conv dispatch for '" + label + "'");
         pmlbCheck(pmlb_plan_share_status(plan, exe_->status_), "status word");
         st.plan = plan;
-        st.kernel = pmlb_plan_kind(plan);          // "tc_conv", "tc_conv_halo", "tc_conv_rows" or "tc_conv_s2d"
+        st.kernel = pmlb_plan_kind(plan);          // "tc_conv", "tc_conv_halo", "tc_conv_rows", "tc_conv_s2d" or "tc_conv_s2d_pool"
         const std::string route = st.kernel;
-        const int extra = (route == "tc_conv_rows" || route == "tc_conv_s2d") ? 1 : 0;   // their activation packing pass
+        const int extra = (route == "tc_conv_rows" || route == "tc_conv_s2d" || route == "tc_conv_s2d_pool") ? 1 : 0;   // their activation packing pass
         st.launches = 1 + extra;
         std::ostringstream os;
         const pmlb_conv_desc& d = pd.conv;

@@ -97,4 +97,16 @@ inline bool conv_takes_s2d(const pmlb_conv_desc& d) {
   return conv_s2d_weight_bytes(g) + 2 * conv_s2d_stage_bytes(g) <= kS2dSmemBytes;
 }
 
+// The space-to-depth route fused with the 3 x 3 / 2 max pool (one pixel of padding) that follows the layer:
+// a 7-wide filter (four tap columns in the stride-1 form) on rows of exactly 128 packed positions, 64
+// output channels, a 16-bit output, whole tiles of four output rows.  The output tensor is then
+// [n][p / 2][q / 2][64].
+inline bool conv_takes_s2d_pool(const pmlb_conv_desc& d) {
+  if (!conv_takes_s2d(d)) return false;
+  if (d.k != 64 || d.p % 4 != 0 || !(d.out_dtype == PMLB_BF16 || d.out_dtype == PMLB_F16)) return false;
+  if (d.epilogue & ~(PMLB_EPI_BIAS | PMLB_EPI_RELU)) return false;
+  const S2dShape g = conv_s2d_shape(d);
+  return g.s2 == 4 && g.r2 <= 4 && g.wp == 128;
+}
+
 }  // namespace pmlb

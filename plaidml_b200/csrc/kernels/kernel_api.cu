@@ -2,6 +2,7 @@
 // sequences the preparation kernels and the main kernel of each plan.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -11,6 +12,7 @@
 #include "pmlb_kernels.h"
 #include "prepass.h"
 #include "reduce.h"
+#include "s2d_pool.h"
 #include "tc_gemm.cuh"
 #include "conv_route.h"
 #include "tc_launch.h"
@@ -104,6 +106,7 @@ struct pmlb_plan {
   bool halo = false;             // conv: halo route (scratch = weights as for im2col)
   bool packed_rows = false;      // conv: packed-row route (scratch = weights, then the padded activation)
   bool s2d = false;              // conv: space-to-depth route (scratch = weights, then the packed activation)
+  bool s2d_pool = false;         // ... fused with the 3 x 3 / 2 max pool behind it
   size_t packed_input_off = 0;   // byte offset of the padded activation inside scratch
 
   pmlb_reduce_desc reduce;
@@ -505,6 +508,10 @@ pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* d, pmlb_plan** out) {
     return fail(PMLB_ERR_INVALID, "conv: bad geometry");
   }
   const bool s2d = pmlb::conv_takes_s2d(*d) && (d->flags & PMLB_CONV_NO_S2D) == 0;
+  const bool pooled = (d->flags & PMLB_CONV_MAX_POOL_3X3_S2) != 0;
+  if (pooled && !(s2d && pmlb::conv_takes_s2d_pool(*d))) {
+    return fail(PMLB_ERR_UNSUPPORTED, "conv: this shape does not take the fused max pool");
+  }
   const bool packed =
       !s2d && pmlb::conv_takes_packed_rows(*d) && (d->flags & PMLB_CONV_NO_PACKED_ROWS) == 0;
   if (!packed && !s2d && d->c % 8 != 0) {
@@ -527,7 +534,8 @@ pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* d, pmlb_plan** out) {
   if (s2d) {
     const pmlb::S2dShape g = pmlb::conv_s2d_shape(*d);
     plan->s2d = true;
-    plan->kind_name = "tc_conv_s2d";
+    plan->s2d_pool = pooled;
+    plan->kind_name = pooled ? "tc_conv_s2d_pool" : "tc_conv_s2d";
     const size_t wts = static_cast<size_t>(pmlb::conv_s2d_weight_bytes(g));
     plan->packed_input_off = (wts + 255) / 256 * 256;
     // (a tile's copy may run past the last image: keep that much readable behind it)
@@ -566,8 +574,10 @@ pmlb_status pmlb_conv_set_filter(pmlb_plan* plan, void* stream, const void* filt
   cudaError_t e;
   if (plan->s2d) {
     const pmlb::S2dShape g = pmlb::conv_s2d_shape(d);
-    e = pmlb::launch_filter_s2d(filter, dtype, plan->scratch, d.in_dtype, d.r, d.s, d.c, d.k, g.r2,
-                                g.s2, g.dh, g.dw, static_cast<cudaStream_t>(stream));
+    e = plan->s2d_pool ? pmlb::launch_filter_s2d_merged(filter, dtype, plan->scratch, d.in_dtype, d.r, d.s, d.c, d.k,
+                                                        g.r2, g.s2, g.dh, g.dw, static_cast<cudaStream_t>(stream))
+                       : pmlb::launch_filter_s2d(filter, dtype, plan->scratch, d.in_dtype, d.r, d.s, d.c, d.k, g.r2,
+                                                 g.s2, g.dh, g.dw, static_cast<cudaStream_t>(stream));
   } else if (plan->packed_rows) {
     e = pmlb::launch_filter_pack_rows(filter, dtype, plan->scratch, d.in_dtype, d.r, d.s, d.c,
                                       pmlb::conv_padded_channels(d), d.k,
@@ -595,6 +605,34 @@ pmlb_status pmlb_conv_invoke(pmlb_plan* plan, void* stream, const void* input, v
     cudaError_t e = pmlb::launch_s2d_pack(input, packed, d.n, d.h, d.w, d.c, sh.h2, sh.wp, sh.pe_h,
                                           sh.pe_w, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e, "activation space-to-depth packing");
+    if (plan->s2d_pool) {
+      pmlb::S2dPoolParams sp = {};
+      sp.px = packed;
+      sp.wts = plan->scratch;
+      sp.bias = (d.epilogue & PMLB_EPI_BIAS) ? static_cast<const float*>(bias) : nullptr;
+      sp.out = output;
+      sp.status = plan->status;
+      sp.tiles_per_img = d.p / 4;
+      sp.total_tiles = d.n * sp.tiles_per_img;
+      sp.img_px = sh.h2 * sh.wp;
+      sp.stage_load = sh.stage_px * 32;
+      sp.stage_bytes = (sp.stage_load + 1023) / 1024 * 1024;
+      sp.stages = pmlb::s2d_pool_stages(sp.stage_bytes);
+      sp.r2 = sh.r2;
+      sp.conv_q = d.q;
+      sp.pool_p = d.p / 2;
+      sp.pool_q = d.q / 2;
+      sp.relu = (d.epilogue & PMLB_EPI_RELU) ? 1 : 0;
+      sp.wait_limit_us = 0;
+      if (sp.stages < 2) return fail(PMLB_ERR_UNSUPPORTED, "conv (space to depth + pool): pixel buffers do not fit");
+      int dev = 0, num_sms = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+      const int grid = std::min(num_sms, sp.total_tiles);
+      e = pmlb::launch_s2d_pool(sp, grid, d.in_dtype == PMLB_F16, d.out_dtype == PMLB_BF16, static_cast<cudaStream_t>(stream));
+      if (e != cudaSuccess) return cuda_fail(e, "conv (space to depth + pool)");
+      return PMLB_OK;
+    }
     pmlb::S2dGeom g;
     g.n = d.n; g.p = d.p; g.q = d.q;
     g.r2 = sh.r2; g.s2 = sh.s2; g.h2 = sh.h2; g.wp = sh.wp; g.stage_px = sh.stage_px;

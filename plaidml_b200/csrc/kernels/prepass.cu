@@ -258,7 +258,41 @@ filter_s2d_kernel(const void* __restrict__ in, int in_dtype, void* __restrict__ 
   }
 }
 
+// The same weights for the kernel that merges tap columns into the N dimension of its MMAs: logical
+// output [3 - tap column][ko][tap row][16 channels] (four blocks of 64 rows of 128 bytes), 128-byte swizzle.
+__global__ void __launch_bounds__(256)
+filter_s2d_merged_kernel(const void* __restrict__ in, int in_dtype, void* __restrict__ out, int out_dtype,
+                         int r, int s, int c, int k, int r2, int s2, int dh, int dw) {
+  const int id = blockIdx.x * blockDim.x + threadIdx.x;
+  if (id >= 4 * 64 * 64) return;
+  const int e = id & 63;
+  const int ko = (id >> 6) & 63;
+  const int ts = 3 - (id >> 12);
+  const int tr = e >> 4;
+  const int ch = e & 15;
+  float v = 0.f;
+  if (ch < 4 * c && ko < k && ts < s2 && tr < r2) {
+    const int phase = ch / c, ci = ch - phase * c;
+    const int fr = 2 * tr + (phase >> 1) - dh, fs = 2 * ts + (phase & 1) - dw;
+    if (fr >= 0 && fr < r && fs >= 0 && fs < s) {
+      v = load_filter(in, in_dtype, ((static_cast<long long>(fr) * s + fs) * c + ci) * k + ko);
+    }
+  }
+  const int o = (id & ~63) | ((((e >> 3) ^ (ko & 7)) << 3) | (e & 7));
+  if (out_dtype == PMLB_BF16) {
+    static_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
+  } else {
+    static_cast<__half*>(out)[o] = __float2half_rn(v);
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_filter_s2d_merged(const void* in, int in_dtype, void* out, int out_dtype, int r, int s,
+                                     int c, int k, int r2, int s2, int dh, int dw, cudaStream_t stream) {
+  filter_s2d_merged_kernel<<<64, 256, 0, stream>>>(in, in_dtype, out, out_dtype, r, s, c, k, r2, s2, dh, dw);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_s2d_pack(const void* in, void* out, int n, int h, int w, int c, int h2, int wp,
                             int pe_h, int pe_w, cudaStream_t stream) {

@@ -62,6 +62,11 @@ cudaError_t launch_s2d_pack(const void* in, void* out, int n, int h, int w, int 
 cudaError_t launch_filter_s2d(const void* in, int in_dtype, void* out, int out_dtype, int r, int s,
                               int c, int k, int r2, int s2, int dh, int dw, cudaStream_t stream);
 
+// The same weights as [3 - tap column][64][tap row][16] (four blocks of 64 rows of 128 bytes, 32 KB):
+// the layout of the kernel that fuses the layer with the max pool behind it (s2 = 4, r2 <= 4).
+cudaError_t launch_filter_s2d_merged(const void* in, int in_dtype, void* out, int out_dtype, int r, int s,
+                                     int c, int k, int r2, int s2, int dh, int dw, cudaStream_t stream);
+
 // Second pass of a GEMM whose K range was split over `parts` CTAs per output tile: sums the partial
 // products (f32 or i32, [parts][m][n] dense) in part order and applies the epilogue the single-pass kernel
 // would have applied -- bias[n], residual[m][n] (element type of the output, row stride ldr), ReLU, cast

@@ -32,6 +32,7 @@ CONV_NO_S2D = 4
 CONV_CTA_PAIRS = 8
 CONV_NO_CTA_PAIRS = 16
 CONV_NO_COLUMN_MERGE = 32
+CONV_MAX_POOL_3X3_S2 = 64
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = range(5)
 
 MAX_IDX, MAX_RANK, MAX_CONS = 10, 8, 8

@@ -350,3 +350,66 @@ def test_reference_microkernel_convolution_on_the_tensor_core_routes():
         plan.conv(ptr(x_dev), ptr(out), None, None)
         plan.check()
         np.testing.assert_array_equal(out.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("n,h,w,c,r,pad,epi", [
+    (2, 32, 200, 3, 7, 3, K.EPI_BIAS | K.EPI_RELU),         # fewer tiles than SMs: one tile per CTA and lead-in tiles
+    (3, 224, 224, 3, 7, 3, K.EPI_BIAS | K.EPI_RELU),        # ResNet's first layer: 84 tiles
+    (200, 64, 200, 3, 7, 3, K.EPI_BIAS | K.EPI_RELU),       # 1600 tiles: runs of ~11 tiles that start inside images
+    (37, 48, 208, 4, 7, 3, K.EPI_RELU),                     # four channels, no bias, 222 tiles of 104 columns
+    (5, 122, 250, 1, 7, 2, K.EPI_BIAS),                     # one channel, pad 2, no ReLU (negative maxima), 124 columns
+    (4, 62, 222, 3, 8, 4, K.EPI_BIAS | K.EPI_RELU),         # 8 x 8 filter
+    (2, 30, 224, 3, 7, 3, 0),                               # 15 output rows: refused
+    (2, 32, 32, 3, 7, 3, 0),                                # rows of 32 packed positions: refused
+])
+def test_first_layer_fused_with_its_max_pool(n, h, w, c, r, pad, epi):
+    # the convolution's output is never written: conv + bias + ReLU + 3x3/2 max pool (pad 1) in one kernel,
+    # against the oracle's convolution followed by the oracle's pool, and against the two-kernel route
+    g = rng(4100 + n + h)
+    s = 7 if r != 8 else 8
+    p, q = out_size(h, r, 2, pad, pad, 1), out_size(w, s, 2, pad, pad, 1)
+    x = dev_bf16(g.uniform(-1, 1, size=(n, h, w, c)))
+    f32 = (g.standard_normal((r, s, c, 64)) * np.sqrt(2.0 / (r * s * c))).astype(np.float32)
+    bias = g.standard_normal(64).astype(np.float32) if epi & K.EPI_BIAS else None
+    d = K.ConvDesc()
+    d.in_dtype, d.out_dtype = K.BF16, K.BF16
+    d.n, d.h, d.w, d.c, d.r, d.s, d.k, d.p, d.q = n, h, w, c, r, s, 64, p, q
+    d.stride_h = d.stride_w = 2
+    d.pad_h = d.pad_w = pad
+    d.dil_h = d.dil_w = 1
+    d.epilogue, d.flags = epi, K.CONV_MAX_POOL_3X3_S2
+    if p % 4 != 0 or not 96 < q + 3 <= 128:
+        with pytest.raises(K.KernelError):
+            K.Plan("conv", d)
+        return
+    plan = K.Plan("conv", d)
+    assert plan.kernel == "tc_conv_s2d_pool"
+    f_dev = dev(f32)
+    plan.set_filter(ptr(f_dev), K.F32)
+    out = empty((n, p // 2, q // 2, 64), K.BF16)
+    out.fill_(float("nan"))
+    bias_dev = dev(bias) if bias is not None else None
+    for _ in range(2):      # (a second launch: barriers and buffers start clean every time)
+        plan.conv(ptr(x), ptr(out), ptr(bias_dev), None)
+        plan.check()
+    conv_ref = oracle.conv2d_nhwc_f32(as_f32(x), oracle.bf16_to_f32(oracle.f32_to_bf16(f32)), bias, None, (2, 2), (pad, pad),
+                                      (1, 1), bool(epi & K.EPI_RELU), out_hw=(p, q))
+    conv_ref = oracle.bf16_to_f32(oracle.f32_to_bf16(conv_ref))
+    ref = oracle.pool2d_nhwc_f32(conv_ref, "max", (3, 3), (2, 2), (1, 1), (p // 2, q // 2))
+    got = as_f32(out)
+    assert np.isfinite(got).all()
+    check_close(got, ref, 1e-2)
+    # the unfused route: the same convolution kernel family, then the pooling kernel; equal up to the
+    # summation order of the taps (the fused kernel walks the tap columns in another order)
+    d2 = K.ConvDesc()
+    for fld in ("in_dtype", "out_dtype", "n", "h", "w", "c", "r", "s", "k", "p", "q", "stride_h", "stride_w", "pad_h",
+                "pad_w", "dil_h", "dil_w", "epilogue"):
+        setattr(d2, fld, getattr(d, fld))
+    plan2 = K.Plan("conv", d2)
+    plan2.set_filter(ptr(f_dev), K.F32)
+    mid = empty((n, p, q, 64), K.BF16)
+    plan2.conv(ptr(x), ptr(mid), ptr(bias_dev), None)
+    plan2.check()
+    two = oracle.pool2d_nhwc_f32(as_f32(mid), "max", (3, 3), (2, 2), (1, 1), (p // 2, q // 2))
+    check_close(got, two, 1e-2)
+    assert (got != two).mean() < 0.02

@@ -340,6 +340,52 @@ def test_maxpool_and_mean_and_softmax():
     np.testing.assert_allclose(got_sm, e / e.sum(axis=1, keepdims=True), rtol=1e-5, atol=1e-7)
 
 
+def _stem_program(n, h, with_side_output=False, w_img=224):
+    g = rng(1251)
+    w = f32_to_bf16_bits(g.standard_normal((7, 7, 3, 64)) * np.sqrt(2.0 / 147))
+    b = (g.standard_normal(64) * 0.1).astype(np.float32)
+    I = Placeholder(DType.BFLOAT16, [n, h, w_img, 3])
+    F = cast(edsl.Constant(w, name="w", dtype=DType.BFLOAT16), DType.FLOAT32)
+    y = op.convolution(cast(I, DType.FLOAT32), F, strides=[2, 2], autopad_mode=op.AutoPadMode.EXPLICIT,
+                       manual_padding=[3, 3, 3, 3]) + edsl.Constant(b, name="b")
+    y = cast(op.relu(y), DType.BFLOAT16)
+    pooled = op.pool(y, op.PoolMode.MAX, [3, 3], [2, 2], op.AutoPadMode.EXPLICIT, [1, 1, 1, 1], op.TensorLayout.NXC)
+    x = f32_to_bf16_bits(g.uniform(-1, 1, (n, h, w_img, 3)).astype(np.float32))
+    return Program("stem", [I], [pooled, y] if with_side_output else [pooled]), x, w, b
+
+
+def test_first_convolution_and_its_max_pool_run_as_one_kernel(monkeypatch):
+    # conv 7x7/2 + bias + ReLU + cast -> max pool 3x3/2 pad 1: one step whose output is the pooled tensor;
+    # same values as the two separate steps, and as the oracle's convolution followed by its pool
+    prog, x, w, b = _stem_program(5, 96)
+    runner = Runner(prog, "cuda.0")
+    desc = runner.executable.describe()
+    assert "tc_conv_s2d_pool" in desc and "+maxpool3x3/2" in desc and "nhwc_pool" not in desc, desc
+    got = bf16_bits_to_f32(runner.run([x])[0])
+    conv = oracle.conv2d_nhwc_f32(bf16_bits_to_f32(x), bf16_bits_to_f32(w), b, None, (2, 2), (3, 3), (1, 1), True, out_hw=(48, 112))
+    conv = oracle.bf16_to_f32(oracle.f32_to_bf16(conv))
+    ref = oracle.pool2d_nhwc_f32(conv, "max", (3, 3), (2, 2), (1, 1), (24, 56))
+    check_close(got, ref, 1e-2)
+    monkeypatch.setenv("PLAIDML_CUDA_NO_POOL_FUSION", "1")
+    two = Runner(_stem_program(5, 96)[0], "cuda.0")
+    desc2 = two.executable.describe()
+    assert "tc_conv_s2d " in desc2 and "nhwc_pool" in desc2, desc2
+    got2 = bf16_bits_to_f32(two.run([x])[0])
+    check_close(got, got2, 1e-2)
+    assert (got != got2).mean() < 0.02
+    monkeypatch.delenv("PLAIDML_CUDA_NO_POOL_FUSION")
+    # the convolution's output read by anything else (here: a program output) keeps the two steps
+    prog, x, _, _ = _stem_program(2, 64, with_side_output=True)
+    both = Runner(prog, "cuda.0")
+    assert "nhwc_pool" in both.executable.describe() and "tc_conv_s2d_pool" not in both.executable.describe()
+    pooled, y = both.run([x])
+    ref = oracle.pool2d_nhwc_f32(bf16_bits_to_f32(y), "max", (3, 3), (2, 2), (1, 1), (16, 56))
+    np.testing.assert_array_equal(bf16_bits_to_f32(pooled), ref)
+    # rows of the packed activation that are not 128 positions wide (a 96-wide image) keep the two steps, too
+    narrow = Runner(_stem_program(2, 64, w_img=96)[0], "cuda.0")
+    assert "nhwc_pool" in narrow.executable.describe() and "tc_conv_s2d_pool" not in narrow.executable.describe()
+
+
 def test_mean_tail_folds_into_the_reduction():
     # sum -> / count -> cast back to bf16 (the global average pool of a bf16 network): one kernel that divides its
     # f32 sum by the count and rounds once; the same values as the three separate steps (general kernels)
