@@ -10,6 +10,8 @@ launches of the kernel of interest:
     i8_4k      int8 -> int32 Tile GEMM 4096^3            (tc_contract_kernel, int8, B as [k][n])
     bf16_4k    bf16 Tile GEMM 4096^3, f32 accumulate     (tc_contract_kernel, bf16)
     f32_1k     fp32 Tile GEMM 1024^3 via three TF32 products
+    bf16_2a    bf16 GEMM 50176 x 256 x 1024 (the shape of ResNet-50's res4x_2a layers at 256 images: A streamed once)
+    bf16_2c    bf16 GEMM 50176 x 1024 x 256 (res4x_2c: short K, 103 MB of output)
     conv3      conv 3x3 56x56 64->64 + bias + ReLU, batch 16
     conv3_full the same at batch 128
     conv1x1    conv 1x1 56x56 64->256 + bias + ReLU, batch 64 (HBM-bound: 26 MB in, 103 MB out)
@@ -17,8 +19,11 @@ launches of the kernel of interest:
     qk_r       the same at the full batch of 1024 with only the row maxima as output (the product is never written:
                134 MB read, 2 MB written)
     rowmax     row max alone over a 256 x 512 x 512 f32 tensor (row_reduce_kernel, 256 MiB)
-    stem       the first two layers of ResNet-50 at batch 32: 7x7 / 2 convolution on 3 channels
-               (s2d_pack_kernel + tc_contract_kernel, space-to-depth route) and the 3x3 / 2 max pool (pool16_kernel)
+    stem       the first two layers of ResNet-50 at batch 32: 7x7 / 2 convolution on 3 channels + bias + ReLU and the
+               3x3 / 2 max pool as one kernel (s2d_pack_kernel, then conv_s2d_pool_kernel); with
+               PLAIDML_CUDA_NO_POOL_FUSION=1 in the environment the two-kernel form (tc_contract_kernel on the
+               space-to-depth route, pool16_kernel)
+    stem_full  the same at batch 256 (120 MB of packed pixels in, 103 MB out)
     resnet N   ResNet-50 v1.5 at batch N
     resnet_steps N   the same, followed by a table of every kernel step on its own (CUDA events around 20 launches
                of the step replayed from a CUDA graph: device time without the host's launch cost) beside the time of
@@ -56,6 +61,11 @@ def main(argv) -> None:
         A, B, C = programs.tile_gemm(DType.BFLOAT16, 4096, 4096, 4096, acc=DType.FLOAT32, out_bf16=True)
         r = Runner(Program(case, [A, B], [C]), "cuda.0")
         ins = [f32_to_bf16_bits(g.standard_normal((4096, 4096))) for _ in range(2)]
+    elif case in ("bf16_2a", "bf16_2c"):
+        m, n, k = (50176, 256, 1024) if case == "bf16_2a" else (50176, 1024, 256)
+        A, B, C = programs.tile_gemm(DType.BFLOAT16, m, n, k, acc=DType.FLOAT32, out_bf16=True)
+        r = Runner(Program(case, [A, B], [C]), "cuda.0")
+        ins = [f32_to_bf16_bits(g.standard_normal((m, k))), f32_to_bf16_bits(g.standard_normal((k, n)))]
     elif case == "f32_1k":
         A, B, C = programs.tile_gemm(DType.FLOAT32, 1024, 1024, 1024)
         r = Runner(Program(case, [A, B], [C]), "cuda.0")
@@ -84,18 +94,19 @@ def main(argv) -> None:
         R = Contraction(name="rowmax").outShape(256, 512).outAccess(bb, i).max(S[bb, i, j]).build()
         r = Runner(Program(case, [S], [R]), "cuda.0")
         ins = [g.standard_normal((256, 512, 512)).astype(np.float32)]
-    elif case == "stem":
+    elif case in ("stem", "stem_full"):
         from plaidml_b200 import edsl, op
         from plaidml_b200.edsl import Placeholder, cast
         w = f32_to_bf16_bits(g.standard_normal((7, 7, 3, 64)) * np.sqrt(2.0 / 147))
-        I = Placeholder(DType.BFLOAT16, [32, 224, 224, 3])
+        nimg = 32 if case == "stem" else 256
+        I = Placeholder(DType.BFLOAT16, [nimg, 224, 224, 3])
         F = cast(edsl.Constant(w, name="w", dtype=DType.BFLOAT16), DType.FLOAT32)
         y = op.convolution(cast(I, DType.FLOAT32), F, strides=[2, 2], autopad_mode=op.AutoPadMode.EXPLICIT,
                            manual_padding=[3, 3, 3, 3]) + edsl.Constant(np.zeros(64, np.float32), name="b")
         y = cast(op.relu(y), DType.BFLOAT16)
         y = op.pool(y, op.PoolMode.MAX, [3, 3], [2, 2], op.AutoPadMode.EXPLICIT, [1, 1, 1, 1], op.TensorLayout.NXC)
         r = Runner(Program(case, [I], [y]), "cuda.0")
-        ins = [f32_to_bf16_bits(g.uniform(0, 1, (32, 224, 224, 3)).astype(np.float32))]
+        ins = [f32_to_bf16_bits(g.uniform(0, 1, (nimg, 224, 224, 3)).astype(np.float32))]
     elif case in ("resnet", "resnet_steps"):
         batch = int(argv[2]) if len(argv) > 2 else 32
         prog, _ = programs.resnet50(batch)
