@@ -295,6 +295,7 @@ plaidml_expr* plaidml_expr_layer_begin(plaidml_error* err, const char* op, size_
     for (size_t i = 0; i < nattrs; ++i) node->attrs[attrs[i]->key] = attrs[i]->value->node;
     LayerContext::get()->addNode(node);
     LayerContext::get()->stack.push_front(node);
+    ExprNode::openLayer() = node;
     return new plaidml_expr{node};
   });
 }
@@ -304,6 +305,7 @@ plaidml_exprs* plaidml_expr_layer_end(plaidml_error* err, plaidml_expr* expr, si
     if (expr->node->kind != ExprNode::Layer) throw std::bad_cast();
     auto& stack = LayerContext::get()->stack;
     if (!stack.empty()) stack.pop_front();
+    ExprNode::openLayer() = stack.empty() ? ExprPtr() : stack.front();
     expr->node->results.clear();
     std::vector<plaidml_expr*> outer;
     for (size_t i = 0; i < noutputs; ++i) {

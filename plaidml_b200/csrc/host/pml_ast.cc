@@ -77,6 +77,11 @@ std::string VarNode::str() const {
   return "?";
 }
 
+ExprPtr& ExprNode::openLayer() {
+  thread_local ExprPtr layer;
+  return layer;
+}
+
 std::string ExprNode::str() const {
   switch (kind) {
     case Cast: return std::string("cast(") + dtypeName(dtype) + ")";

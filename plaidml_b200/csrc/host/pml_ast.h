@@ -109,8 +109,13 @@ struct ExprNode {
   std::vector<ExprPtr> results;                 // Layer
   std::map<std::string, VarPtr> attrs;          // Layer / Pragma
 
-  explicit ExprNode(Kind k) : kind(k) {}
+  // A node made while a layer is open on this thread belongs to it (plaidml/edsl/ffi.cc:95-113), whichever
+  // entry point made it (the EDSL calls or the operation library).
+  explicit ExprNode(Kind k) : kind(k), parent(openLayer()) {}
   std::string str() const;
+
+  // Innermost layer open on this thread (null outside layers); set by plaidml_expr_layer_begin / _end.
+  static ExprPtr& openLayer();
 };
 
 // ---------------------------------------------------------------- evaluator

@@ -7,6 +7,7 @@
 #include <cmath>
 #include <cstring>
 #include <limits>
+#include <functional>
 #include <map>
 #include <numeric>
 #include <sstream>
@@ -526,20 +527,31 @@ Scalar scalarOf(const PValue& v) {
 std::string Program::mlir() const {
   static const char* aggNames[] = {"assign", "add", "max", "min", "mul"};
   static const char* comboNames[] = {"none", "add", "cond", "eq", "mul"};
-  std::vector<std::string> names(values.size());
-  std::ostringstream head, csts, body;
-  size_t nargs = 0;
+  std::ostringstream head;
+  size_t nargs = 0, nres = 0, ncst = 0;
+
+  // One region of the printed program: the function body or the body of a layer.  Names are per region
+  // (a layer's body sees only its block arguments and what it defines itself).
+  struct Region {
+    std::map<int, std::string> local;              // value id -> SSA name inside this region
+    std::map<std::string, std::string> cstByText;  // scalar constants defined at the top of this region
+    std::ostringstream csts, body;
+    std::string indent;
+  };
+
+  Region top;
+  top.indent = "    ";
   head << "module @" << name << " {\n  func @main(";
   for (int id : inputs) {
-    names[id] = "%arg" + std::to_string(nargs);
-    head << (nargs ? ", " : "") << names[id] << ": " << values[id].shape.str();
+    top.local[id] = "%arg" + std::to_string(nargs);
+    head << (nargs ? ", " : "") << top.local[id] << ": " << values[id].shape.str();
     ++nargs;
   }
   for (int id : constants) {
     const PValue& v = values[id];
     if (v.kind == PValue::InternalConstant && v.shape.sizes.empty()) continue;   // a literal: tile.constant below
-    names[id] = "%arg" + std::to_string(nargs);
-    head << (nargs ? ", " : "") << names[id] << ": " << v.shape.str() << " {stdx.const}";
+    top.local[id] = "%arg" + std::to_string(nargs);
+    head << (nargs ? ", " : "") << top.local[id] << ": " << v.shape.str() << " {stdx.const}";
     ++nargs;
   }
   head << ") -> ";
@@ -548,16 +560,14 @@ std::string Program::mlir() const {
   if (outputs.size() != 1) head << ")";
   head << " {\n";
 
-  // scalar constants, one per distinct (value, type), all defined before the first op
-  std::map<std::string, std::string> cstByText;
-  size_t ncst = 0;
-  auto constantName = [&](const std::string& text) {
-    auto it = cstByText.find(text);
-    if (it != cstByText.end()) return it->second;
+  // scalar constants: one per distinct (value, type) and region, all defined before the region's first op
+  auto constantName = [&](Region& rg, const std::string& text) {
+    auto it = rg.cstByText.find(text);
+    if (it != rg.cstByText.end()) return it->second;
     const std::string nm = ncst == 0 ? "%cst" : "%cst_" + std::to_string(ncst - 1);
     ++ncst;
-    cstByText.emplace(text, nm);
-    csts << "    " << nm << " = " << text << "\n";
+    rg.cstByText.emplace(text, nm);
+    rg.csts << rg.indent << nm << " = " << text << "\n";
     return nm;
   };
   auto scalarText = [&](const Scalar& sc, DType dt) {
@@ -566,20 +576,25 @@ std::string Program::mlir() const {
     else t += std::to_string(sc.i) + " : i64";
     return t + ") : " + TensorShape(dt).str();
   };
-  auto use = [&](int id) -> std::string {
-    if (!names[id].empty()) return names[id];
+  auto use = [&](Region& rg, int id) -> std::string {
+    auto it = rg.local.find(id);
+    if (it != rg.local.end()) return it->second;
     const PValue& v = values[id];
+    std::string nm;
     if (v.kind == PValue::LiteralValue || (v.kind == PValue::InternalConstant && v.shape.sizes.empty())) {
-      names[id] = constantName(scalarText(scalarOf(v), v.shape.dtype));
-    } else {
+      nm = constantName(rg, scalarText(scalarOf(v), v.shape.dtype));
+    } else if (v.kind == PValue::InternalConstant) {
       // a tensor the builder computed from shapes alone (index, shape): a dense constant
       std::string t = "tile.constant(dense<" + std::string(v.name.empty() ? "..." : v.name) + "> : " + v.shape.str() + ") : " +
                       v.shape.str();
-      names[id] = constantName(t);
+      nm = constantName(rg, t);
+    } else {
+      nm = "%<undefined " + std::to_string(id) + ">";   // (the builder rejects programs that would get here)
     }
-    return names[id];
+    rg.local[id] = nm;
+    return nm;
   };
-  auto identity = [&](AggKind agg, DType dt) {
+  auto identity = [&](Region& rg, AggKind agg, DType dt) {
     Scalar sc;
     sc.isFloat = isFloat(dt);
     const size_t bits = dtypeBytes(dt) * 8;
@@ -597,19 +612,19 @@ std::string Program::mlir() const {
         break;
       default: break;
     }
-    return constantName(scalarText(sc, dt));
+    return constantName(rg, scalarText(sc, dt));
   };
 
-  size_t nres = 0;
-  for (const POp& op : ops) {
+  auto printOp = [&](Region& rg, const POp& op) {
+    std::ostringstream& body = rg.body;
     std::vector<std::string> args;
     if (op.kind == POp::Contraction) {
       const BoundedContraction& c = *op.c;
       const size_t nsrc = op.operands.size() - (c.hasInit ? 1 : 0);
-      const std::string init = c.hasInit ? use(op.operands.back()) : identity(c.agg, values[op.result].shape.dtype);
-      for (size_t i = 0; i < nsrc; ++i) args.push_back(use(op.operands[i]));
-      names[op.result] = "%" + std::to_string(nres++);
-      body << "    " << names[op.result] << " = tile.contract " << aggNames[static_cast<int>(c.agg)] << ", "
+      const std::string init = c.hasInit ? use(rg, op.operands.back()) : identity(rg, c.agg, values[op.result].shape.dtype);
+      for (size_t i = 0; i < nsrc; ++i) args.push_back(use(rg, op.operands[i]));
+      rg.local[op.result] = "%" + std::to_string(nres++);
+      body << rg.indent << rg.local[op.result] << " = tile.contract " << aggNames[static_cast<int>(c.agg)] << ", "
            << comboNames[static_cast<int>(c.combo)] << ", " << init;
       for (const std::string& a : args) body << ", " << a;
       body << " {";
@@ -629,27 +644,118 @@ std::string Program::mlir() const {
       body << "]} : " << (c.hasInit ? values[op.operands.back()].shape.str() : TensorShape(values[op.result].shape.dtype).str());
       for (size_t i = 0; i < nsrc; ++i) body << ", " << values[op.operands[i]].shape.str();
       body << " -> " << values[op.result].shape.str() << "\n";
-      continue;
+      return;
     }
-    for (int id : op.operands) args.push_back(use(id));
-    names[op.result] = "%" + std::to_string(nres++);
+    for (int id : op.operands) args.push_back(use(rg, id));
+    rg.local[op.result] = "%" + std::to_string(nres++);
     if (op.mnemonic == "pragma") {
-      body << "    " << names[op.result] << " = tile.pragma " << args[0] << " \"" << op.label << "\" {" << op.attrs
+      body << rg.indent << rg.local[op.result] << " = tile.pragma " << args[0] << " \"" << op.label << "\" {" << op.attrs
            << "} : " << values[op.result].shape.str() << "\n";
-      continue;
+      return;
     }
-    body << "    " << names[op.result] << " = tile." << op.mnemonic;
+    body << rg.indent << rg.local[op.result] << " = tile." << op.mnemonic;
     for (size_t i = 0; i < args.size(); ++i) body << (i ? ", " : " ") << args[i];
     body << " : (";
     for (size_t i = 0; i < op.operands.size(); ++i) body << (i ? ", " : "") << values[op.operands[i]].shape.str();
     body << ") -> " << values[op.result].shape.str() << "\n";
+  };
+
+  // first operation (in list order) inside a layer or anything nested in it; ops.size() if it has none
+  std::vector<size_t> firstOp(layers.size(), ops.size());
+  for (size_t i = ops.size(); i-- > 0;) {
+    for (int l = ops[i].layer; l >= 0; l = layers[l].parent) firstOp[l] = i;
   }
-  body << "    return";
-  for (size_t i = 0; i < outputs.size(); ++i) body << (i ? ", " : " ") << use(outputs[i]);
-  if (!outputs.empty()) body << " : ";
-  for (size_t i = 0; i < outputs.size(); ++i) body << (i ? ", " : "") << values[outputs[i]].shape.str();
-  body << "\n  }\n}\n";
-  return head.str() + csts.str() + body.str();
+
+  // Prints the operations and child layers of region `level` (-1: the function body) in an order in which every
+  // value is defined before its use: list order, except that a layer (one item, placed at its first operation)
+  // waits for all of its operands.
+  std::function<void(Region&, int)> printRegion = [&](Region& rg, int level) {
+    struct Item {
+      size_t key;
+      int op = -1, layer = -1;
+      std::vector<int> needs;
+      bool done = false;
+    };
+    std::vector<Item> items;
+    std::map<int, size_t> producer;   // value id -> item
+    for (size_t i = 0; i < ops.size(); ++i) {
+      if (ops[i].layer != level) continue;
+      Item it;
+      it.key = i;
+      it.op = static_cast<int>(i);
+      it.needs = ops[i].operands;
+      producer[ops[i].result] = items.size();
+      items.push_back(std::move(it));
+    }
+    for (size_t l = 0; l < layers.size(); ++l) {
+      if (layers[l].parent != level) continue;
+      Item it;
+      it.key = firstOp[l];
+      it.layer = static_cast<int>(l);
+      it.needs = layers[l].operands;
+      for (int r : layers[l].results) producer[r] = items.size();
+      items.push_back(std::move(it));
+    }
+    for (size_t printed = 0; printed < items.size(); ++printed) {
+      size_t best = items.size();
+      for (size_t k = 0; k < items.size(); ++k) {
+        if (items[k].done) continue;
+        bool ready = true;
+        for (int v : items[k].needs) {
+          auto pr = producer.find(v);
+          if (pr != producer.end() && pr->second != k && !items[pr->second].done) ready = false;
+        }
+        if (ready && (best == items.size() || items[k].key < items[best].key)) best = k;
+      }
+      if (best == items.size()) break;   // (a cycle cannot happen in a program the builder made)
+      Item& it = items[best];
+      it.done = true;
+      if (it.op >= 0) {
+        printOp(rg, ops[it.op]);
+        continue;
+      }
+      const PLayer& ly = layers[it.layer];
+      std::vector<std::string> args;
+      for (int v : ly.operands) args.push_back(use(rg, v));
+      const std::string box = "%" + std::to_string(nres++);
+      Region inner;
+      inner.indent = rg.indent + "  ";
+      std::ostringstream blockArgs;
+      for (size_t k = 0; k < ly.operands.size(); ++k) {
+        const std::string an = "%arg" + std::to_string(nargs++);
+        if (!inner.local.count(ly.operands[k])) inner.local[ly.operands[k]] = an;
+        blockArgs << (k ? ", " : "") << an << ": " << values[ly.operands[k]].shape.str();
+      }
+      printRegion(inner, it.layer);
+      rg.body << rg.indent << box;
+      if (ly.results.size() != 1) rg.body << ":" << ly.results.size();
+      rg.body << " = layer.box \"" << ly.name << "\"(";
+      for (size_t k = 0; k < args.size(); ++k) rg.body << (k ? ", " : "") << args[k];
+      rg.body << ") {attrs = {" << ly.attrs << "}} : ";
+      for (size_t k = 0; k < ly.operands.size(); ++k) rg.body << (k ? ", " : "") << values[ly.operands[k]].shape.str();
+      rg.body << " -> ";
+      for (size_t k = 0; k < ly.results.size(); ++k) rg.body << (k ? ", " : "") << values[ly.results[k]].shape.str();
+      rg.body << " {\n" << rg.indent << "^bb0(" << blockArgs.str() << "):\n";
+      std::ostringstream ret;
+      ret << inner.indent << "layer.return";
+      for (size_t k = 0; k < ly.results.size(); ++k) ret << (k ? ", " : " ") << use(inner, ly.results[k]);
+      if (!ly.results.empty()) ret << " : ";
+      for (size_t k = 0; k < ly.results.size(); ++k) ret << (k ? ", " : "") << values[ly.results[k]].shape.str();
+      rg.body << inner.csts.str() << inner.body.str() << ret.str() << "\n" << rg.indent << "}\n";
+      for (size_t k = 0; k < ly.results.size(); ++k) {
+        rg.local[ly.results[k]] = ly.results.size() == 1 ? box : box + "#" + std::to_string(k);
+      }
+    }
+  };
+  printRegion(top, -1);
+
+  std::ostringstream tail;
+  tail << "    return";
+  for (size_t i = 0; i < outputs.size(); ++i) tail << (i ? ", " : " ") << use(top, outputs[i]);
+  if (!outputs.empty()) tail << " : ";
+  for (size_t i = 0; i < outputs.size(); ++i) tail << (i ? ", " : "") << values[outputs[i]].shape.str();
+  tail << "\n  }\n}\n";
+  return head.str() + top.csts.str() + top.body.str() + tail.str();
 }
 
 // ------------------------------------------------------------------ builder
@@ -668,9 +774,98 @@ class Builder {
   int lower(const ExprPtr& e) {
     auto it = memo_.find(e.get());
     if (it != memo_.end()) return it->second;
+    // operations emitted for this node belong to the layer that was open when the node was made
+    const int saved = layer_;
+    layer_ = e->parent ? layerOf(e->parent) : -1;
     const int id = lowerNode(e);
+    layer_ = saved;
     memo_[e.get()] = id;
     return id;
+  }
+
+  // Index of the layer record of a Layer node (made on first use, enclosing layers first).
+  int layerOf(const ExprPtr& node) {
+    auto it = layerIds_.find(node.get());
+    if (it != layerIds_.end()) return it->second;
+    const int parent = node->parent ? layerOf(node->parent) : -1;
+    const int id = static_cast<int>(prog_->layers.size());
+    layerIds_[node.get()] = id;
+    layerNodes_.push_back(node);
+    PLayer rec;
+    rec.name = node->op;
+    rec.parent = parent;
+    bool first = true;
+    for (const auto& kv : node->attrs) {
+      rec.attrs += (first ? "" : ", ") + kv.first + " = ";
+      const VarPtr& v = kv.second;
+      if (v && v->kind == VarNode::Str) rec.attrs += "\"" + v->s + "\"";
+      else if (v && v->kind == VarNode::Int) rec.attrs += std::to_string(v->i) + " : i64";
+      else if (v && v->kind == VarNode::Float) rec.attrs += std::to_string(v->f) + " : f64";
+      else rec.attrs += v ? v->str() : "unit";
+      first = false;
+    }
+    prog_->layers.push_back(std::move(rec));
+    // operands are values of the enclosing region (lowered there), literals become tensors of their own
+    std::vector<int> operands;
+    for (const ExprPtr& o : node->operands) {
+      int v = lower(o);
+      if (prog_->values[v].kind == PValue::LiteralValue) v = materialise(v, prog_->values[v].shape.dtype);
+      operands.push_back(v);
+    }
+    prog_->layers[id].operands = std::move(operands);
+    return id;
+  }
+
+  // After all outputs are lowered: the layers' result values, and the check that a layer's body reads nothing
+  // of the regions around it except through its operands (the reference's layer.box is isolated from above;
+  // a body that uses a tensor not listed as an operand is rejected when the program is built).
+  void finishLayers() {
+    for (size_t l = 0; l < layerNodes_.size(); ++l) {
+      std::vector<int> results;
+      for (const ExprPtr& r : layerNodes_[l]->results) results.push_back(lower(r));
+      prog_->layers[l].results = std::move(results);
+    }
+    auto inside = [&](int inner, int outer) {   // is region `inner` the region `outer` or nested in it
+      for (int l = inner; l >= 0; l = prog_->layers[l].parent) {
+        if (l == outer) return true;
+      }
+      return outer == -1;
+    };
+    auto visible = [&](int v, int level) {
+      const PValue& pv = prog_->values[v];
+      if (pv.kind == PValue::LiteralValue || (pv.kind == PValue::InternalConstant)) return true;
+      if (level < 0) return true;
+      const PLayer& ly = prog_->layers[level];
+      if (std::find(ly.operands.begin(), ly.operands.end(), v) != ly.operands.end()) return true;
+      if (pv.def < 0) return false;                       // a program argument that is not an operand
+      const int defLevel = prog_->ops[pv.def].layer;
+      if (defLevel == level) return true;
+      // the result of a layer nested directly or deeper: visible only as a result of a child of `level`
+      for (int l = defLevel; l >= 0; l = prog_->layers[l].parent) {
+        if (prog_->layers[l].parent == level) {
+          const std::vector<int>& rs = prog_->layers[l].results;
+          return std::find(rs.begin(), rs.end(), v) != rs.end();
+        }
+      }
+      return false;
+    };
+    (void)inside;
+    for (const POp& op : prog_->ops) {
+      if (op.layer < 0) continue;
+      for (int v : op.operands) {
+        if (!visible(v, op.layer)) {
+          throw std::runtime_error("Layer '" + prog_->layers[op.layer].name + "' uses a tensor that is not among its operands" +
+                                   (prog_->values[v].name.empty() ? "" : " ('" + prog_->values[v].name + "')"));
+        }
+      }
+    }
+    for (size_t l = 0; l < prog_->layers.size(); ++l) {
+      for (int v : prog_->layers[l].results) {
+        if (!visible(v, static_cast<int>(l))) {
+          throw std::runtime_error("Layer '" + prog_->layers[l].name + "' returns a tensor that is not among its operands");
+        }
+      }
+    }
   }
 
   void bindInput(const ExprPtr& e, const TensorShape* shape) {
@@ -704,6 +899,7 @@ class Builder {
     v.shape.strides.clear();
     v.name = op.label;
     v.def = static_cast<int>(prog_->ops.size());
+    op.layer = layer_;
     op.result = addValue(v);
     prog_->ops.push_back(std::move(op));
     return prog_->ops.back().result;
@@ -724,6 +920,10 @@ class Builder {
   Evaluator ev;
 
  private:
+  int layer_ = -1;                                          // layer of the node being lowered
+  std::unordered_map<const ExprNode*, int> layerIds_;
+  std::vector<ExprPtr> layerNodes_;
+
   int literal(const ExprPtr& e, Literal lit, DType dt) {
     (void)e;
     PValue v;
@@ -1001,6 +1201,7 @@ std::shared_ptr<Program> buildProgram(const std::string& name, const std::vector
     seen.push_back(id);
     prog->outputs.push_back(id);
   }
+  b.finishLayers();
   return prog;
 }
 

@@ -74,13 +74,26 @@ struct POp {
   std::string attrs;     // "pragma": its attributes as printed, e.g. msg = "text"
   std::vector<int> operands;  // value ids; for contractions: sources then the init (if any)
   int result = -1;
+  int layer = -1;        // innermost enclosing layer (index into Program::layers), -1 at function level
   std::shared_ptr<BoundedContraction> c;
+};
+
+// A named region of the program (edsl `layer(...)`, pmlc/ast/builder.cc:704-762): the operations built while the
+// layer was open, isolated from the values around them except for its operands.  Execution ignores layers (the
+// operation list is flat); the printed program shows them as `layer.box` regions.
+struct PLayer {
+  std::string name;
+  std::string attrs;          // as printed inside {attrs = {...}}
+  int parent = -1;            // enclosing layer
+  std::vector<int> operands;  // values of the enclosing region, in the order given (block arguments)
+  std::vector<int> results;   // values of the body returned by the layer
 };
 
 struct Program {
   std::string name;
   std::vector<PValue> values;
   std::vector<POp> ops;
+  std::vector<PLayer> layers;
   std::vector<int> inputs;     // value ids, user order
   std::vector<int> constants;  // value ids, discovery order (appended program arguments)
   std::vector<int> outputs;    // value ids

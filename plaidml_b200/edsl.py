@@ -521,6 +521,35 @@ def pragma(x, op, attrs):
     return Tensor(expr=ffi_call(lib.plaidml_expr_pragma, t.as_ptr(), op.encode(), len(raw), raw))
 
 
+def layer(op, operands, fn, attrs=None):
+    """A named region of the program (edsl.h `layer(op, operands, attrs, fn)`): the operations `fn` builds are
+    printed as the body of a ``layer.box`` whose block arguments stand for `operands`; constants made inside are
+    added to the operands.  `fn` returns one Tensor or a list of them, and so does ``layer``.  The body may read
+    the tensors around it only through `operands` (the program is rejected otherwise)."""
+    ops = [_as_tensor(t) for t in operands]
+    keys, values, raw = [], [], []
+    for key, value in (attrs or {}).items():
+        keys.append(ffi.new("char[]", key.encode()))
+        values.append(Value(value))
+        raw.append(ffi.new("plaidml_attr*", {"key": keys[-1], "value": values[-1].as_ptr()}))
+    handle = ffi_call(lib.plaidml_expr_layer_begin, op.encode(), len(ops), [t.as_ptr() for t in ops], len(raw), raw)
+    try:
+        inner = fn()
+    except BaseException:
+        # close the layer so that later expressions do not end up inside it
+        done = ffi_call(lib.plaidml_expr_layer_end, handle, 0, [])
+        ffi_call(lib.plaidml_exprs_free, done)
+        ffi_call(lib.plaidml_expr_free, handle)
+        raise
+    single = isinstance(inner, Tensor)
+    outs = [inner] if single else list(inner)
+    outer = ffi_call(lib.plaidml_expr_layer_end, handle, len(outs), [t.as_ptr() for t in outs])
+    tensors = [Tensor(expr=outer.elts[i]) for i in range(outer.size)]
+    ffi_call(lib.plaidml_exprs_free, outer)
+    ffi_call(lib.plaidml_expr_free, handle)
+    return tensors[0] if single else tensors
+
+
 def trace(x, msg):
     """A trace point: ``pragma(x, "trace", msg=...)``; the cuda target records no host-side trace."""
     return pragma(x, "trace", dict(msg=msg))

@@ -5,7 +5,7 @@ tests/golden/edsl_filecheck.json, one list of [directive, pattern] per test name
     python tests/golden/make_filecheck_fixtures.py <path to a plaidml checkout>
 
 Only the tests named in WANTED are taken: those whose programs the contraction path's EDSL can
-build (no layers, no gather / argsort / prng)."""
+build (no gather / argsort / prng)."""
 
 import json
 import os
@@ -17,6 +17,7 @@ WANTED = [
     "Convolution", "MnistCnn", "RepeatElements", "GlobalMin", "CumSum", "ComplexConv2d", "Reciprocal",
     "DefractLong", "Select", "ConvI8", "UniqueNames", "dup_out", "HigherPrecisionConstants", "LarsMomentum4d",
     "ReshapeFold", "ReshapeScalar", "ReshapeIntoScalar", "ReshapeFromScalar", "Shape", "Trace",
+    "Layer", "LayerOperandOrder", "LayerEmbeddedConst", "LayerUnusedOperand",
 ]
 
 

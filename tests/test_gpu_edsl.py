@@ -340,6 +340,25 @@ def test_maxpool_and_mean_and_softmax():
     np.testing.assert_allclose(got_sm, e / e.sum(axis=1, keepdims=True), rtol=1e-5, atol=1e-7)
 
 
+def test_layers_run_like_the_operations_they_enclose():
+    # plaidml/edsl/tests/edsl_test.cc Layer, LayerOperandOrder, LayerEmbeddedConst: runProgram after the FileCheck lines
+    g = rng(1260)
+    a = g.standard_normal((10, 20)).astype(np.float32)
+    b = g.standard_normal((10, 20)).astype(np.float32)
+    A, B = Placeholder(DType.FLOAT32, [10, 20]), Placeholder(DType.FLOAT32, [10, 20])
+    relu_layer = edsl.layer("relu", [A], lambda: edsl.select(A < 0.0, 0.0, A))
+    sum_layer = edsl.layer("sum", [A, B], lambda: A + B)
+    const_layer = edsl.layer("sum", [A], lambda: A + edsl.Constant(b, name="B"))
+    nested = edsl.layer("outer", [A, B], lambda: op.relu(edsl.layer("inner", [A, B], lambda: op.dot(A, op.transpose(B)))))
+    runner = Runner(Program("layers", [A, B], [relu_layer, sum_layer, const_layer, nested]), "cuda.0")
+    assert "layer.box" in str(runner.program)
+    r, s, c, n = runner.run([a, b])
+    np.testing.assert_array_equal(r, np.maximum(a, 0))
+    np.testing.assert_array_equal(s, a + b)
+    np.testing.assert_array_equal(c, a + b)
+    np.testing.assert_allclose(n, np.maximum(a.astype(np.float64) @ b.astype(np.float64).T, 0), rtol=1e-5, atol=1e-5)
+
+
 def _stem_program(n, h, with_side_output=False, w_img=224):
     g = rng(1251)
     w = f32_to_bf16_bits(g.standard_normal((7, 7, 3, 64)) * np.sqrt(2.0 / 147))

@@ -11,8 +11,8 @@ import pytest
 
 import filecheck
 from plaidml_b200.core import DType, Program
-from plaidml_b200.edsl import (Constant, Contraction, Placeholder, TensorDims, TensorIndexes, cast, exp, reshape, select,
-                               shape, sqrt, trace)
+from plaidml_b200.edsl import (Constant, Contraction, Placeholder, TensorDims, TensorIndexes, cast, exp, layer, reshape,
+                               select, shape, sqrt, trace)
 
 with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "edsl_filecheck.json")) as f:
     CHECKS = json.load(f)
@@ -254,8 +254,37 @@ def build_trace():
     return Program("trace", [I], [trace(I, "msg")])
 
 
+def build_layer():
+    A = f32(10, 20)
+    return Program("relu", [A], [layer("relu", [A], lambda: select(A < 0.0, 0.0, A))])
+
+
+def build_layer_operand_order():
+    A, B = f32(10, 20), f32(10, 20)
+    return Program("LayerOperandOrder", [A, B], [layer("sum", [A, B], lambda: A + B)])
+
+
+def _const_10x20(name):
+    data = np.zeros(200, dtype=np.float32)
+    data[:4] = [1, 2, 3, 4]
+    return Constant(data.reshape(10, 20), name=name)
+
+
+def build_layer_embedded_const():
+    A = f32(10, 20)
+    return Program("LayerEmbeddedConst", [A], [layer("sum", [A], lambda: A + _const_10x20("B"))])
+
+
+def build_layer_unused_operand():
+    A = f32(10, 20)
+    B = _const_10x20("B")
+    return Program("LayerUnusedOperand", [A], [layer("sum", [A, B], lambda: A + _const_10x20("C"))])
+
+
 BUILDERS = {
     "Shape": build_shape, "Trace": build_trace,
+    "Layer": build_layer, "LayerOperandOrder": build_layer_operand_order, "LayerEmbeddedConst": build_layer_embedded_const,
+    "LayerUnusedOperand": build_layer_unused_operand,
     "HigherPrecisionConstants": build_higher_precision_constants, "LarsMomentum4d": build_lars_momentum_4d,
     "ReshapeFold": lambda: build_reshape("reshape_fold", [3, 3], [3, 3]),
     "ReshapeScalar": lambda: build_reshape("reshape_scalar", [], []),
@@ -293,3 +322,35 @@ def test_filecheck_itself_rejects_what_it_should():
     with pytest.raises(filecheck.CheckFailure):
         filecheck.run([["CHECK", "tile.add %[[u]]"]], text)                                # undefined variable
     filecheck.run([["CHECK-DAG", "return %0"], ["CHECK-DAG", "tile.constant"], ["CHECK", "}"]], text)
+
+
+def test_layer_that_reads_a_tensor_it_was_not_given_is_rejected():
+    # plaidml/edsl/tests/edsl_test.cc LayerMissingOperand: building the program throws
+    A, B = f32(10, 20), f32(10, 20)
+    O = layer("sum", [A], lambda: A + B)
+    with pytest.raises(Exception, match="not among its operands"):
+        Program("LayerMissingOperand", [A, B], [O])
+
+
+def test_nested_layers_and_several_results_print_as_nested_regions():
+    A, B = f32(4, 6), f32(4, 6)
+
+    def outer_body():
+        s = layer("inner_sum", [A, B], lambda: A + B, attrs={"axis": 1})
+        return [s * A, select(s < 0.0, 0.0, s)]
+
+    P, Q = layer("outer", [A, B], outer_body)
+    text = str(Program("nested", [A, B], [P + Q, Q]))
+    filecheck.run([
+        ["CHECK", "func @main(%[[A:.*]]: tensor<4x6xf32>, %[[B:.*]]: tensor<4x6xf32>) -> (tensor<4x6xf32>, tensor<4x6xf32>)"],
+        ["CHECK", "%[[OUT:.*]]:2 = layer.box \"outer\"(%[[A]], %[[B]]) {attrs = {}} : tensor<4x6xf32>, tensor<4x6xf32> -> tensor<4x6xf32>, tensor<4x6xf32>"],
+        ["CHECK-NEXT", "^bb0(%[[A1:.*]]: tensor<4x6xf32>, %[[B1:.*]]: tensor<4x6xf32>):"],
+        ["CHECK", "%[[IN:.*]] = layer.box \"inner_sum\"(%[[A1]], %[[B1]]) {attrs = {axis = 1 : i64}} : tensor<4x6xf32>, tensor<4x6xf32> -> tensor<4x6xf32>"],
+        ["CHECK-NEXT", "^bb0(%[[A2:.*]]: tensor<4x6xf32>, %[[B2:.*]]: tensor<4x6xf32>):"],
+        ["CHECK", "%[[S:.*]] = tile.add %[[A2]], %[[B2]]"],
+        ["CHECK", "layer.return %[[S]] : tensor<4x6xf32>"],
+        ["CHECK", "%[[M:.*]] = tile.mul %[[IN]], %[[A1]]"],
+        ["CHECK", "layer.return %[[M]], %{{.*}} : tensor<4x6xf32>, tensor<4x6xf32>"],
+        ["CHECK", "%[[T:.*]] = tile.add %[[OUT]]#0, %[[OUT]]#1"],
+        ["CHECK", "return %[[T]], %{{.*}} : tensor<4x6xf32>, tensor<4x6xf32>"],
+    ], text)
