@@ -14,16 +14,24 @@ int halo_fs_stages(int weight_bytes, int stage_bytes) {
 
 int halo_fs_tail_bytes() { return kFsTailBytes; }
 
-cudaError_t launch_halo_fs(const TcMaps& maps, const TcParams& p, int grid, int out_bytes, bool dependent_launch,
+cudaError_t launch_halo_fs(const TcMaps& maps, const TcParams& p, int grid, int out_bytes, bool pair, bool dependent_launch,
                            cudaStream_t stream) {
-  const int smem = 1024 + p.conv_r * 3 * 8192 + p.halo_stages * p.halo_stage_bytes + kFsTailBytes;
+  const int wts = p.conv_r * (pair ? 12288 : 24576);
+  const int smem = 1024 + wts + p.halo_stages * p.halo_stage_bytes + kFsTailBytes;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
   cfg.blockDim = dim3(kFsThreads, 1, 1);
   cfg.dynamicSmemBytes = static_cast<size_t>(smem);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   int na = 0;
+  if (pair) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 2;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   if (dependent_launch) {
     attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[na].val.programmaticStreamSerializationAllowed = 1;
@@ -31,14 +39,13 @@ cudaError_t launch_halo_fs(const TcMaps& maps, const TcParams& p, int grid, int 
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  if (out_bytes == 2) {
-    cudaError_t e = cudaFuncSetAttribute(conv_halo_fs_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  auto go = [&](auto kernel) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    return cudaLaunchKernelEx(&cfg, conv_halo_fs_kernel<2>, maps, p);
-  }
-  cudaError_t e = cudaFuncSetAttribute(conv_halo_fs_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return e;
-  return cudaLaunchKernelEx(&cfg, conv_halo_fs_kernel<4>, maps, p);
+    return cudaLaunchKernelEx(&cfg, kernel, maps, p);
+  };
+  if (pair) return out_bytes == 2 ? go(conv_halo_fs_kernel<2, 2>) : go(conv_halo_fs_kernel<4, 2>);
+  return out_bytes == 2 ? go(conv_halo_fs_kernel<2, 1>) : go(conv_halo_fs_kernel<4, 1>);
 }
 
 }  // namespace pmlb

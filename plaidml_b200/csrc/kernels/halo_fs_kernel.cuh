@@ -25,6 +25,15 @@
 // per tile into a ring), warp 1 MMA issuer (four TMEM accumulators of 128 columns), warps 2..9 two
 // epilogue groups of four warps (group g takes the tiles with local number = g mod 2).
 // Every wait is bounded, as in the general kernel.
+//
+// CTAS = 2: two CTAs (a cluster) work on two neighbouring tiles with one MMA stream: each MMA is 256 rows high
+// (cta_group::2; rows 0..127 = the first CTA's tile and accumulator, rows 128..255 the second's), issued by the
+// first CTA's issuer, and each CTA holds half of every weight tile's N rows (columns 0 / 1 of the filter for the
+// 128-wide MMA, 32 of the 64 output channels of column 2 for the 64-wide one): 36 KB of weights per CTA instead
+// of 72 KB, and per filter row and k-step 11 KB of operand reads per CTA (88 cycles of the 128 B/clk port)
+// for 96 cycles of math, where a CTA on its own reads 14 KB (112 cycles) for the same math.  Pixel loads are
+// per CTA (no multicast) and count on the first CTA's barrier; the second CTA's epilogue hands its accumulator
+// back through the first CTA's barrier.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -35,7 +44,7 @@
 
 namespace pmlb {
 
-constexpr int kFsGroups = 2;                      // epilogue groups of four warps
+constexpr int kFsGroups = 3;                      // epilogue groups of four warps
 constexpr int kFsThreads = 64 + 128 * kFsGroups;
 constexpr int kFsXbufBytes = kFsGroups * 3 * 256;   // per group: three warp boundaries x 64 floats
 constexpr int kFsTailBytes = kFsXbufBytes + 256 + 512;   // exchange buffers, bias, barriers
@@ -53,16 +62,19 @@ __device__ __forceinline__ void tmem_ld_32x32_x16(uint32_t taddr, uint32_t (&v)[
 }
 
 // OB: bytes per output element (2: bf16 / f16, 4: f32).
-template <int OB>
+template <int OB, int CTAS>
 __global__ void __launch_bounds__(kFsThreads, 1)
 conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ TcParams p) {
+  const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0u;
   grid_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t ring = (raw_addr + 1023u) & ~1023u;
   uint8_t* ring_ptr = smem_raw + (ring - raw_addr);
   const int nst = p.halo_stages;
-  const uint32_t wts_bytes = static_cast<uint32_t>(p.conv_r) * 3u * 8192u;
+  // weights per filter row: 3 x 8 KB, or (pairs) this CTA's 8 KB + 4 KB halves
+  const uint32_t wts_row_bytes = CTAS == 2 ? 12288u : 24576u;
+  const uint32_t wts_bytes = static_cast<uint32_t>(p.conv_r) * wts_row_bytes;
   const uint32_t stages0 = ring + wts_bytes;
   const uint32_t tail_off = wts_bytes + static_cast<uint32_t>(nst) * static_cast<uint32_t>(p.halo_stage_bytes);
   float* xbuf_all = reinterpret_cast<float*>(ring_ptr + tail_off);
@@ -91,7 +103,7 @@ conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ T
     }
     for (int a = 0; a < 4; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), 4 * CTAS);
     }
     for (int g = 0; g < kFsGroups; ++g) {
       mbar_init(xready_bar(g), 4);
@@ -106,11 +118,20 @@ conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ T
     tma_prefetch_desc(&tm.b0);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), 512);
-    tmem_relinquish();
+    if constexpr (CTAS == 2) {
+      tmem_alloc_pair(smem_u32(tmem_slot), 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (CTAS == 2) {
+    cluster_sync_all();   // the other CTA's barriers must exist before anything is sent to them
+  } else {
+    __syncthreads();
+  }
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   // set-up done: from here on the kernel reads and writes tensors, so the kernel before it must be complete
@@ -122,19 +143,37 @@ conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ T
   __syncthreads();   // (the staged bias, for the epilogue warps)
 
   const int total_tiles = p.batch;   // tiles of one 128-position block each
-  const int t_begin = blockIdx.x, t_step = gridDim.x;
+  // Work units: tiles, or (pairs) two neighbouring tiles, one per CTA; a unit's second tile may lie past the
+  // end (its loads then bring zeros and nothing of it is stored).
+  const int total_units = (total_tiles + CTAS - 1) / CTAS;
+  const int u_begin = static_cast<int>(blockIdx.x) / CTAS, u_step = static_cast<int>(gridDim.x) / CTAS;
+  auto tile_of = [&](int u) { return u * CTAS + static_cast<int>(cta_rank); };
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     const bool leader = elect_one();
-    if (leader) {
-      mbar_arrive_expect_tx(wts_bar, wts_bytes);
-      for (int tap = 0; tap < p.conv_r * 3; ++tap) {
-        tma_load_3d(ring + static_cast<uint32_t>(tap) * 8192u, &tm.b0, wts_bar, 0, tap, 0);
+    if (leader && u_begin < total_units) {
+      if constexpr (CTAS == 2) {
+        // this CTA's halves: filter column `rank` (64 rows) for the 128-wide MMA, output channels
+        // 32 * rank .. of column 2 for the 64-wide one; all bytes are counted on the first CTA's barrier
+        const uint32_t wb0 = mapa_rank(wts_bar, 0);
+        if (cta_rank == 0) mbar_arrive_expect_tx(wts_bar, 2u * wts_bytes);
+        for (int fr = 0; fr < p.conv_r; ++fr) {
+          const uint32_t dst = ring + static_cast<uint32_t>(fr) * wts_row_bytes;
+          tma_load_3d_pair(dst, &tm.b0, wb0, 0, fr * 3 + static_cast<int>(cta_rank), 0);
+          tma_load_3d_pair(dst + 8192u, &tm.b1, wb0, 0, fr * 3 + 2, 32 * static_cast<int>(cta_rank));
+        }
+      } else {
+        mbar_arrive_expect_tx(wts_bar, wts_bytes);
+        for (int tap = 0; tap < p.conv_r * 3; ++tap) {
+          tma_load_3d(ring + static_cast<uint32_t>(tap) * 8192u, &tm.b0, wts_bar, 0, tap, 0);
+        }
       }
     }
     uint32_t hs = 0, hphase = 0;
-    for (int t = t_begin; t < total_tiles; t += t_step) {
+    for (int u = u_begin; u < total_units; u += u_step) {
+      const int t = tile_of(u);
+      // (a tile past the end: image number = batch size, every pixel out of range, i.e. zeros)
       const int img = fast_div(t, p.fd_tiles_per_img);
       const int p0 = (t - img * p.halo_tiles_per_img) * p.halo_th;
       if (!mbar_wait_warp(empty_bar(hs), hphase ^ 1u, abort_flag)) {
@@ -142,38 +181,45 @@ conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ T
         break;
       }
       if (leader) {
-        mbar_arrive_expect_tx(full_bar(hs), static_cast<uint32_t>(p.halo_wp * p.halo_rows) * 128u);
-        tma_load_4d(stages0 + hs * static_cast<uint32_t>(p.halo_stage_bytes), &tm.a0, full_bar(hs), 0,
-                    p.conv_lower_w, p0 + p.conv_lower_h, img);
+        const uint32_t bytes = static_cast<uint32_t>(p.halo_wp * p.halo_rows) * 128u;
+        if constexpr (CTAS == 2) {
+          if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(hs), 2u * bytes);
+          tma_load_4d_pair(stages0 + hs * static_cast<uint32_t>(p.halo_stage_bytes), &tm.a0, mapa_rank(full_bar(hs), 0), 0,
+                           p.conv_lower_w, p0 + p.conv_lower_h, img);
+        } else {
+          mbar_arrive_expect_tx(full_bar(hs), bytes);
+          tma_load_4d(stages0 + hs * static_cast<uint32_t>(p.halo_stage_bytes), &tm.a0, full_bar(hs), 0,
+                      p.conv_lower_w, p0 + p.conv_lower_h, img);
+        }
       }
       if (++hs == static_cast<uint32_t>(nst)) {
         hs = 0;
         hphase ^= 1u;
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 && cta_rank == 0) {
+    // ------------------------------------------------------------ MMA issuer (pairs: the first CTA's)
     const bool leader = elect_one();
     const uint64_t desc_k = make_smem_desc_sw128(0, 16, 1024);
     const uint32_t dk_lo = static_cast<uint32_t>(desc_k), dk_hi = static_cast<uint32_t>(desc_k >> 32);
     auto lo_at = [](uint32_t base_lo, uint32_t saddr) { return base_lo | ((saddr & 0x3FFFFu) >> 4); };
     bool ok = true;
-    if (t_begin < total_tiles && !mbar_wait_warp(wts_bar, 0u, abort_flag)) {
+    if (u_begin < total_units && !mbar_wait_warp(wts_bar, 0u, abort_flag)) {
       if (leader && *abort_code == 0) *abort_code = 3;
       ok = false;
     }
     uint32_t hs = 0, hphase = 0;
     int it = 0;
-    for (int t = t_begin; t < total_tiles && ok; t += t_step, ++it) {
+    for (int u = u_begin; u < total_units && ok; u += u_step, ++it) {
       const int acc = it & 3;
       const uint32_t acc_phase = static_cast<uint32_t>(it >> 2) & 1u;
       // (in the steady state both barriers are long complete: probe first, without the suspension a
       // try_wait may take and without the warp vote, and wait properly only when the probe fails)
-      if (!mbar_test_wait(tempty_bar(acc), acc_phase ^ 1u) && !mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+      if (!mbar_test_wait_warp(tempty_bar(acc), acc_phase ^ 1u) && !mbar_wait_warp(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
         if (leader && *abort_code == 0) *abort_code = 2;
         break;
       }
-      if (!mbar_test_wait(full_bar(hs), hphase) && !mbar_wait_warp(full_bar(hs), hphase, abort_flag)) {
+      if (!mbar_test_wait_warp(full_bar(hs), hphase) && !mbar_wait_warp(full_bar(hs), hphase, abort_flag)) {
         if (leader && *abort_code == 0) *abort_code = 3;
         break;
       }
@@ -187,22 +233,29 @@ conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ T
       const uint32_t a_step = static_cast<uint32_t>(p.halo_wp) * 8u;   // 16-byte units per padded image row
       for (int fr = 0; fr < p.conv_r; ++fr) {
         if (leader) {
-          tc_mma_x4<kMmaF16, 1>(d_tmem, a_lo, b_lo, dk_hi, dk_hi, p.idesc, fr > 0 ? 1u : 0u, 2u, 2u);
-          tc_mma_x4<kMmaF16, 1>(d_tmem, a_lo + 16u, b_lo + 2u * 512u, dk_hi, dk_hi, p.idesc_half, 1u, 2u, 2u);
+          // (pairs: the weight halves of a filter row lie 8 KB apart, else the third tap two tiles on)
+          tc_mma_x4<kMmaF16, CTAS>(d_tmem, a_lo, b_lo, dk_hi, dk_hi, p.idesc, fr > 0 ? 1u : 0u, 2u, 2u);
+          tc_mma_x4<kMmaF16, CTAS>(d_tmem, a_lo + 16u, b_lo + (CTAS == 2 ? 512u : 2u * 512u), dk_hi, dk_hi, p.idesc_half, 1u,
+                                   2u, 2u);
         }
         a_lo += a_step;
-        b_lo += 3u * 512u;
+        b_lo += wts_row_bytes >> 4;
       }
       if (leader) {
-        tc_commit(empty_bar(hs));
-        tc_commit(tfull_bar(acc));
+        if constexpr (CTAS == 2) {
+          tc_commit_pair(empty_bar(hs), 3);    // the pixel buffer is free in both CTAs
+          tc_commit_pair(tfull_bar(acc), 3);   // both CTAs' epilogues may read their rows
+        } else {
+          tc_commit(empty_bar(hs));
+          tc_commit(tfull_bar(acc));
+        }
       }
       if (++hs == static_cast<uint32_t>(nst)) {
         hs = 0;
         hphase ^= 1u;
       }
     }
-  } else {
+  } else if (warp >= 2) {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;             // TMEM lane quarter this warp may read
     const int grp = (warp - 2) >> 2;    // group g takes the tiles with local number = g mod 2
@@ -221,14 +274,15 @@ conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ T
     const int qq = j - pr * p.halo_wp;
     const bool in_tile = pr < p.halo_th && qq < p.conv_q;
     uint32_t xphase = 0;
-    for (int it = grp; ; it += 2, xphase ^= 1u) {
-      const int t = t_begin + it * t_step;
-      if (t >= total_tiles) break;
+    for (int it = grp; ; it += kFsGroups, xphase ^= 1u) {
+      const int u = u_begin + it * u_step;
+      if (u >= total_units) break;
+      const int t = tile_of(u);
       const int acc = it & 3;
       const uint32_t acc_phase = static_cast<uint32_t>(it >> 2) & 1u;
       const int img = fast_div(t, p.fd_tiles_per_img);
       const int p0 = (t - img * p.halo_tiles_per_img) * p.halo_th;
-      const bool valid = in_tile && p0 + pr < p.conv_p;
+      const bool valid = in_tile && p0 + pr < p.conv_p && t < total_tiles;
       const long long row = (static_cast<long long>(img) * p.conv_p + p0 + pr) * p.conv_q + qq;
       char* dst = static_cast<char*>(p.out) + row * p.ldc * OB;
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
@@ -283,7 +337,13 @@ conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ T
           // accumulator fully read: hand it back to the issuer
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(tempty_bar(acc));
+          if (lane == 0) {
+            if constexpr (CTAS == 2) {
+              mbar_arrive_cluster(mapa_rank(tempty_bar(acc), 0));
+            } else {
+              mbar_arrive(tempty_bar(acc));
+            }
+          }
         }
         float o[16];
 #pragma unroll
@@ -327,7 +387,11 @@ conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ T
 
   // ---------------------------------------------------------------- teardown
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (CTAS == 2) {
+    cluster_sync_all();   // neither CTA's shared memory or barriers are touched by the other from here on
+  } else {
+    __syncthreads();
+  }
   if (*abort_flag != 0) {
     if (threadIdx.x == 0) {
       const int code = *abort_code != 0 ? *abort_code : 9;
@@ -340,10 +404,15 @@ conv_halo_fs_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ T
     }
     __syncthreads();
   }
+  if constexpr (CTAS == 2) cluster_sync_all();   // (a CTA that reported a time-out has waited above)
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
+    if constexpr (CTAS == 2) {
+      tmem_dealloc_pair(tmem_base, 512);
+    } else {
+      tmem_dealloc(tmem_base, 512);
+    }
   }
 }
 

@@ -102,6 +102,12 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same probe with one answer for the warp (all 32 lanes call it): true only if every lane saw the phase
+// complete, so that the lanes agree on whether a wait follows.
+__device__ __forceinline__ bool mbar_test_wait_warp(uint32_t bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_test_wait(bar, parity)) != 0;
+}
+
 // Wall-clock limit of one barrier wait.  A healthy pipeline waits microseconds.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
@@ -218,6 +224,16 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       " [%0], [%1, {%3, %4, %5}], [%2];"
       :
       : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x,
+                                                 int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
 

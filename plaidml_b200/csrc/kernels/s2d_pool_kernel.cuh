@@ -193,11 +193,11 @@ conv_s2d_pool_kernel(const __grid_constant__ S2dPoolParams p) {
       const int set = it & 1;
       const uint32_t d_set = tmem_base + static_cast<uint32_t>(set * 256);
       const uint32_t acc_phase = static_cast<uint32_t>(it >> 1) & 1u;
-      if (!mbar_test_wait(tempty_bar(set), acc_phase ^ 1u) && !mbar_wait_warp(tempty_bar(set), acc_phase ^ 1u, abort_flag)) {
+      if (!mbar_test_wait_warp(tempty_bar(set), acc_phase ^ 1u) && !mbar_wait_warp(tempty_bar(set), acc_phase ^ 1u, abort_flag)) {
         if (leader && *abort_code == 0) *abort_code = 2;
         break;
       }
-      if (!mbar_test_wait(full_bar(hs), hphase) && !mbar_wait_warp(full_bar(hs), hphase, abort_flag)) {
+      if (!mbar_test_wait_warp(full_bar(hs), hphase) && !mbar_wait_warp(full_bar(hs), hphase, abort_flag)) {
         if (leader && *abort_code == 0) *abort_code = 3;
         break;
       }

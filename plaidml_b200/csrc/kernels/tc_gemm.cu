@@ -417,19 +417,27 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     // Three filter columns on one channel block, no residual: the filter columns merge into the MMA's N
     // dimension (one 128 x 192 product per filter row; halo_fs_kernel.cuh) and the launch happens here.
     const int ob_out = out_bytes_of(L.out_dtype);
-    const int fs_stages = halo_fs_stages(wts_bytes, stage_bytes);
+    // CTA pairs (two tiles per MMA, each CTA half of every weight tile) unless asked not to or the device cannot
+    // hold a cluster; PMLB_CONV_NO_CTA_PAIRS keeps single CTAs
+    const bool fs_pair = L.pair_override != 0 && num_sms >= 2;
+    const int fs_stages = halo_fs_stages(fs_pair ? wts_bytes / 2 : wts_bytes, stage_bytes);
     const int fs_overread = std::max(0, ((g.r - 1) * wp + 2 + 128) * 128 - stage_bytes);   // last row's window, two pixels on
     if (L.halo_merge_columns != 0 && g.s == 3 && cblocks == 1 && g.c == 64 && (ob_out == 2 || ob_out == 4) &&
         (L.epi_flags & (kEpiResidual | kEpiRowMax)) == 0 && L.out != nullptr && L.ldc == 64 &&
         (reinterpret_cast<uintptr_t>(L.out) & 31u) == 0 && (!(L.epi_flags & kEpiBias) || L.bias != nullptr) &&
         fs_stages >= 2 && fs_overread <= halo_fs_tail_bytes()) {
       p.halo_stages = fs_stages;
-      p.idesc = make_idesc(eb, L.is_f16, false, 128);        // filter columns 0 and 1 side by side
-      p.idesc_half = make_idesc(eb, L.is_f16, false, 64);    // filter column 2
+      p.idesc = make_idesc(eb, L.is_f16, false, 128, fs_pair ? 256 : 128);        // filter columns 0 and 1 side by side
+      p.idesc_half = make_idesc(eb, L.is_f16, false, 64, fs_pair ? 256 : 128);    // filter column 2
+      if (fs_pair && !encode3d(&tb1, dt, eb, L.b0, g.c, taps, L.n, static_cast<uint64_t>(g.c) * eb,
+                               static_cast<uint64_t>(g.c) * taps * eb, bk, 1, 32, err)) {
+        return 1;
+      }
       p.fd_tiles_per_img = make_fastdiv(static_cast<uint32_t>(std::max(1, p.halo_tiles_per_img)));
       p.fd_wp = make_fastdiv(static_cast<uint32_t>(std::max(1, p.halo_wp)));
-      const int fs_grid = std::min(p.batch, L.grid_override > 0 ? L.grid_override : num_sms);
-      const cudaError_t fe = launch_halo_fs(maps, p, fs_grid, ob_out, dependent_launch_enabled(), stream);
+      int fs_grid = std::min(p.batch, L.grid_override > 0 ? L.grid_override : num_sms);
+      if (fs_pair) fs_grid = 2 * std::max(1, std::min((p.batch + 1) / 2, (L.grid_override > 0 ? L.grid_override : num_sms) / 2));
+      const cudaError_t fe = launch_halo_fs(maps, p, fs_grid, ob_out, fs_pair, dependent_launch_enabled(), stream);
       if (fe != cudaSuccess) {
         *err = std::string("kernel launch failed: ") + cudaGetErrorString(fe);
         return 2;
