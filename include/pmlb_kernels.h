@@ -133,6 +133,15 @@ typedef struct {
   int64_t ldr, stride_r;             /* residual row / batch strides (elements) */
   int32_t tile_n;                    /* 0 = choose; 64, 128 or 256 forces the tile width */
   int32_t flags;                     /* PMLB_GEMM_* */
+  /* A in two parts (0 = off): columns [0, k_first) of A come from `a`, columns [k_first, k) from a second
+   * matrix `a2` (its own column 0 first, rows lda2 elements apart), both with m rows; B and k describe the
+   * whole product.  C = [A1 | A2] * B is the sum of two GEMMs in one accumulator, which is how a residual
+   * block's shortcut projection joins its last convolution (C = A1 * W1 + A2 * W2 + (b1 + b2)) without the
+   * projection's output ever being written or read back.  8/16-bit inputs, batch 1, k_first a multiple of
+   * the 128-byte k-block; run with pmlb_gemm_invoke_two.  No counterpart in the reference. */
+  int32_t k_first;
+  int32_t reserved0;
+  int64_t lda2;
 } pmlb_gemm_desc;
 
 /* With b_is_nk == 0 the 16-bit and 8-bit kernels read B tiles straight from the [k][n]
@@ -167,6 +176,9 @@ pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* desc, pmlb_plan** plan);
 
 /* `rowmax` (f32[batch * m]) is written only with PMLB_EPI_ROWMAX; `c` may then be NULL to
  * skip materialising the product. */
+/* The same for a plan whose descriptor has k_first > 0: `a2` is the second part of A. */
+pmlb_status pmlb_gemm_invoke_two(pmlb_plan* plan, void* stream, const void* a, const void* a2, const void* b, void* c,
+                                 const void* bias, const void* residual, float* rowmax);
 pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream, const void* a, const void* b, void* c,
                              const void* bias, const void* residual, float* rowmax);
 

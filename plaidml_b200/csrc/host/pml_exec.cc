@@ -192,6 +192,7 @@ class Planner {
 
     fuseRowMaxima();
     fuseConvMaxPool();
+    fuseShortcutProjections();
 
     // ---- phase B: which steps are needed for the outputs
     std::vector<bool> needed(nv, false);
@@ -235,6 +236,9 @@ class Planner {
     pmlb_pool_desc pool;
     int a = -1, b = -1, bias = -1, residual = -1;  // value ids
     bool swapped = false;
+    int a2 = -1;                // GEMM with A in two parts (a fused shortcut projection): the second part's value
+    const void* bDerived = nullptr;     // ... its stacked weights and summed bias on the device (planner-owned)
+    const void* biasDerived = nullptr;
     int rowmax = -1;            // GEMM: value that receives the row maxima of the product (fused max-reduction)
     bool storeMain = true;      // GEMM with fused row maxima: false if nothing else reads the product
     bool dropped = false;       // folded into another step
@@ -279,6 +283,105 @@ class Planner {
         gm.rowmax = red.result;
         gm.fused += "+rowmax";
         red.dropped = true;
+        break;
+      }
+    }
+  }
+
+  // relu(A2 * W2 + b2 + (A1 * W1 + b1)): the last 1x1 convolution of a residual block whose residual is the block's
+  // shortcut projection, both GEMMs over the same rows.  One GEMM over [A2 | A1] and the stacked weights computes
+  // the sum in one accumulator; the projection's output (four times its input at ResNet's first stage) is neither
+  // written nor read back, and its launch goes away.  Needs both weights as constants stored [k][n] and both biases
+  // constant; kept only if the library accepts the descriptor.  (The sum is rounded once instead of the
+  // projection being rounded to 16 bits first: the fused form is the more accurate one.)
+  void fuseShortcutProjections() {
+    if (getenvFlag("PLAIDML_CUDA_NO_SHORTCUT_FUSION")) return;
+    auto hostConstant = [&](int v) -> const Buffer* {
+      if (v < 0) return nullptr;
+      const PValue& pv = val(root(v));
+      if (pv.kind != PValue::Constant && pv.kind != PValue::InternalConstant) return nullptr;
+      return pv.constant.get();
+    };
+    for (size_t m2 = 0; m2 < pending_.size(); ++m2) {
+      Pending& main = pending_[m2];
+      if (main.dropped || main.kind != Pending::Gemm || main.residual < 0 || main.a2 >= 0 || main.rowmax >= 0) continue;
+      const int mid = root(main.residual);
+      for (size_t m1 = 0; m1 < m2; ++m1) {
+        Pending& proj = pending_[m1];
+        if (proj.dropped || proj.kind != Pending::Gemm || root(proj.result) != mid) continue;
+        const pmlb_gemm_desc& g1 = proj.gemm;
+        const pmlb_gemm_desc& g2 = main.gemm;
+        if (proj.residual >= 0 || proj.rowmax >= 0 || proj.a2 >= 0 || (g1.epilogue & ~PMLB_EPI_BIAS) != 0) break;
+        if (g1.batch != 1 || g2.batch != 1 || g1.m != g2.m || g1.n != g2.n || g1.in_dtype != g2.in_dtype ||
+            g1.in_dtype == PMLB_F32 || g1.b_is_nk || g2.b_is_nk || g1.ldb != g1.n || g2.ldb != g2.n || g1.lda != g1.k ||
+            g2.lda != g2.k || g2.ldr != g2.n) {
+          break;
+        }
+        // the projection's output feeds this residual and nothing else
+        if (isOutput_[mid] || uses_[mid] != 1) break;
+        {
+          const POp& u = prog_.ops[users_[mid][0]];
+          if (u.kind == POp::Cast) {
+            if (isOutput_[u.result] || uses_[u.result] != 1 || !absorbed_[users_[u.result][0]]) break;
+          } else if (!absorbed_[users_[mid][0]]) {
+            break;
+          }
+        }
+        const Buffer* w1 = hostConstant(proj.b);
+        const Buffer* w2 = hostConstant(main.b);
+        const Buffer* b1 = hostConstant(proj.bias);
+        const Buffer* b2 = hostConstant(main.bias);
+        if (!w1 || !w2 || (proj.bias >= 0 && !b1) || (main.bias >= 0 && !b2)) break;
+        const size_t eb = g1.in_dtype == PMLB_I8 ? 1 : 2;
+        const bool intPath = g1.in_dtype == PMLB_I8;
+        if (w1->size() != static_cast<size_t>(g1.k) * g1.n * eb || w2->size() != static_cast<size_t>(g2.k) * g2.n * eb) break;
+        pmlb_gemm_desc trial = g2;
+        trial.k = g2.k + g1.k;
+        trial.k_first = g2.k;
+        trial.lda2 = g1.lda;
+        trial.epilogue = (g2.epilogue & ~PMLB_EPI_RESIDUAL) | ((b1 || b2) ? PMLB_EPI_BIAS : 0);
+        pmlb_plan* probe = nullptr;
+        const pmlb_status rc = pmlb_gemm_dispatch(&trial, &probe);
+        if (probe) pmlb_plan_free(probe);
+        if (rc != PMLB_OK) break;
+        // stacked weights [W2 ; W1] and the summed bias, on the device
+        void* wDev = nullptr;
+        cudaCheck(cudaMalloc(&wDev, w1->size() + w2->size()), "cudaMalloc(stacked weights)");
+        exe_->derived_.push_back(wDev);
+        cudaCheck(cudaMemcpy(wDev, w2->data(), w2->size(), cudaMemcpyHostToDevice), "upload of stacked weights");
+        cudaCheck(cudaMemcpy(static_cast<char*>(wDev) + w2->size(), w1->data(), w1->size(), cudaMemcpyHostToDevice),
+                  "upload of stacked weights");
+        void* bDev = nullptr;
+        if (b1 || b2) {
+          std::vector<char> sum(static_cast<size_t>(g2.n) * 4, 0);
+          for (const Buffer* b : {b2, b1}) {
+            if (!b) continue;
+            for (int j = 0; j < g2.n; ++j) {
+              if (intPath) {
+                reinterpret_cast<int32_t*>(sum.data())[j] += reinterpret_cast<const int32_t*>(b->data())[j];
+              } else {
+                reinterpret_cast<float*>(sum.data())[j] += reinterpret_cast<const float*>(b->data())[j];
+              }
+            }
+          }
+          cudaCheck(cudaMalloc(&bDev, sum.size()), "cudaMalloc(summed bias)");
+          exe_->derived_.push_back(bDev);
+          cudaCheck(cudaMemcpy(bDev, sum.data(), sum.size(), cudaMemcpyHostToDevice), "upload of the summed bias");
+        }
+        main.gemm = trial;
+        main.a2 = proj.a;
+        main.bDerived = wDev;
+        main.biasDerived = bDev;
+        main.residual = -1;
+        main.inputs.erase(std::remove_if(main.inputs.begin(), main.inputs.end(), [&](int v) { return root(v) == mid; }),
+                          main.inputs.end());
+        main.inputs.push_back(proj.a);
+        {
+          const size_t at = main.fused.find("+residual");
+          if (at != std::string::npos) main.fused.replace(at, 9, "+shortcut(k" + std::to_string(g1.k) + ")");
+          else main.fused += "+shortcut(k" + std::to_string(g1.k) + ")";
+        }
+        proj.dropped = true;
         break;
       }
     }
@@ -1009,13 +1112,14 @@ class Planner {
         // (+ the TF32 split of both operands, + the row-max fill, + the combining pass of a split K range)
         st.launches = 1 + (pd.gemm.in_dtype == PMLB_F32 ? 1 : 0) + (pd.rowmax >= 0 ? 1 : 0) + (pmlb_plan_split_k(plan) > 1 ? 1 : 0);
         const void* a = dev(pd.a);
-        const void* b = dev(pd.b);
+        const void* a2 = pd.a2 >= 0 ? dev(pd.a2) : nullptr;
+        const void* b = pd.bDerived ? pd.bDerived : dev(pd.b);
         void* c = pd.storeMain ? dev(pd.result) : nullptr;
-        const void* bias = pd.bias >= 0 ? dev(pd.bias) : nullptr;
+        const void* bias = pd.biasDerived ? pd.biasDerived : (pd.bias >= 0 && !pd.bDerived ? dev(pd.bias) : nullptr);
         const void* res = pd.residual >= 0 ? dev(pd.residual) : nullptr;
         float* rowmax = pd.rowmax >= 0 ? reinterpret_cast<float*>(dev(pd.rowmax)) : nullptr;
-        st.launch = [plan, a, b, c, bias, res, rowmax](cudaStream_t s) {
-          return pmlb_gemm_invoke(plan, s, a, b, c, bias, res, rowmax);
+        st.launch = [plan, a, a2, b, c, bias, res, rowmax](cudaStream_t s) {
+          return pmlb_gemm_invoke_two(plan, s, a, a2, b, c, bias, res, rowmax);
         };
         // row-sliceable: plain 8/16-bit GEMM from a program input to a program output
         if (pd.gemm.batch == 1 && pd.gemm.in_dtype != PMLB_F32 && pd.rowmax < 0 && pd.residual < 0 && pd.storeMain &&
@@ -1334,6 +1438,8 @@ Executable::Executable(std::shared_ptr<Program> program, int device) : prog_(std
   } catch (...) {
     for (Step& s : steps_) pmlb_plan_free(s.plan);
     steps_.clear();
+    for (void* q : derived_) cudaFree(q);
+    derived_.clear();
     if (arena_) cudaFree(arena_);
     cudaFree(status_);
     cudaEventDestroy(evStart_);
@@ -1353,6 +1459,7 @@ Executable::~Executable() {
   if (graphExec_) cudaGraphExecDestroy(graphExec_);
   if (graph_) cudaGraphDestroy(graph_);
   for (Step& s : steps_) pmlb_plan_free(s.plan);
+  for (void* q : derived_) cudaFree(q);
   if (arena_) cudaFree(arena_);
   if (flush_) cudaFree(flush_);
   if (gathered_) cudaFree(gathered_);

@@ -91,6 +91,7 @@ class Executable {
   char* flush_ = nullptr;
   size_t arenaBytes_ = 0;
   std::vector<char*> dev_;        // device address per value id (null if never materialised)
+  std::vector<void*> derived_;    // device copies of constants the planner combined (fused weights, summed biases)
   std::vector<Step> steps_;
   int* status_ = nullptr;          // device word shared by all tensor-core plans
   bool inputsResident_ = false;

@@ -288,7 +288,16 @@ pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* d, pmlb_plan** out) {
     return fail(PMLB_ERR_UNSUPPORTED, "gemm: row max cannot be combined with other epilogue steps");
   }
   const int eb = elem_bytes_of(in);
-  const long long min_lda = d->k;
+  if (d->k_first < 0 || d->k_first >= d->k) return fail(PMLB_ERR_INVALID, "gemm: k_first outside (0, k)");
+  if (d->k_first > 0) {
+    if (f32 || d->batch != 1 || (d->k_first * eb) % 128 != 0 || (d->epilogue & PMLB_EPI_ROWMAX)) {
+      return fail(PMLB_ERR_UNSUPPORTED, "gemm: A in two parts needs 8/16-bit inputs, one matrix, whole k-blocks in the first part");
+    }
+    if (d->lda2 < d->k - d->k_first || (d->lda2 * eb) % 16 != 0) {
+      return fail(PMLB_ERR_INVALID, "gemm: lda2 smaller than the second part's width, or rows not 16-byte aligned");
+    }
+  }
+  const long long min_lda = d->k_first > 0 ? d->k_first : d->k;
   const long long min_ldb = d->b_is_nk ? d->k : d->n;
   if (d->lda < min_lda || d->ldb < min_ldb || d->ldc < d->n) {
     return fail(PMLB_ERR_INVALID, "gemm: leading dimension smaller than the row length");
@@ -326,7 +335,7 @@ pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* d, pmlb_plan** out) {
   // Split K?  (8/16-bit inputs read in place, one matrix, no row maxima: see PMLB_GEMM_NO_SPLIT_K)
   const char* split_env = std::getenv("PMLB_SPLIT_K");   // "0": never split (sums then never depend on the tile count)
   const bool split_allowed = !(split_env && split_env[0] == '0') || (d->flags & PMLB_GEMM_SPLIT_K);
-  if (!f32 && !plan->transpose_b && d->batch == 1 && !(d->epilogue & PMLB_EPI_ROWMAX) &&
+  if (!f32 && !plan->transpose_b && d->batch == 1 && !(d->epilogue & PMLB_EPI_ROWMAX) && d->k_first == 0 &&
       !(d->flags & PMLB_GEMM_NO_SPLIT_K) && split_allowed) {
     const int bk = 128 / eb;
     int dev = 0, num_sms = 0;
@@ -364,10 +373,19 @@ pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* d, pmlb_plan** out) {
 
 pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream_v, const void* a, const void* b, void* c,
                              const void* bias, const void* residual, float* rowmax) {
+  return pmlb_gemm_invoke_two(plan, stream_v, a, nullptr, b, c, bias, residual, rowmax);
+}
+
+pmlb_status pmlb_gemm_invoke_two(pmlb_plan* plan, void* stream_v, const void* a, const void* a2, const void* b, void* c,
+                                 const void* bias, const void* residual, float* rowmax) {
   if (!plan || plan->kind != kPlanGemm) return fail(PMLB_ERR_INVALID, "not a gemm plan");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const pmlb_gemm_desc& d = plan->gemm;
   if (!a || !b) return fail(PMLB_ERR_INVALID, "gemm: null operand");
+  if ((d.k_first > 0) != (a2 != nullptr)) {
+    return fail(PMLB_ERR_INVALID, d.k_first > 0 ? "gemm: the second part of A is missing (pmlb_gemm_invoke_two)"
+                                                : "gemm: this plan takes A in one part");
+  }
   if ((d.epilogue & PMLB_EPI_BIAS) && !bias) return fail(PMLB_ERR_INVALID, "gemm: bias missing");
   if ((d.epilogue & PMLB_EPI_RESIDUAL) && !residual) return fail(PMLB_ERR_INVALID, "gemm: residual missing");
   if ((d.epilogue & PMLB_EPI_ROWMAX) && !rowmax) return fail(PMLB_ERR_INVALID, "gemm: rowmax missing");
@@ -392,6 +410,8 @@ pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream_v, const void* a, con
   L.rowmax = rowmax;
   L.status = plan->status;
   L.bn_override = d.tile_n;
+  L.k_first = d.k_first;
+  L.lda_second = d.lda2;
   L.force_slow_epilogue = (d.flags & PMLB_GEMM_PLAIN_STORES) != 0;
   L.residual_from_global = (d.flags & PMLB_GEMM_PLAIN_RESIDUAL) != 0;
   if (d.flags & PMLB_GEMM_CTA_PAIRS) L.pair_override = 1;
@@ -434,6 +454,7 @@ pmlb_status pmlb_gemm_invoke(pmlb_plan* plan, void* stream_v, const void* a, con
     L.b_mn = false;
   } else {
     L.a0 = a;
+    L.a1 = a2;   // (second part of A, plans with k_first > 0)
     L.lda = d.lda;
     L.a_batch_stride = d.stride_a;
     if (plan->transpose_b) {

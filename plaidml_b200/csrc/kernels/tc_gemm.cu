@@ -563,11 +563,24 @@ int tc_launch(const TcLaunch& L, cudaStream_t stream, std::string* err) {
     p.num_kb = (L.k + bk - 1) / bk;
     const uint64_t a_bs = p.a_bz ? static_cast<uint64_t>(L.a_batch_stride) * eb
                                  : static_cast<uint64_t>(L.lda) * eb * L.m;
-    if (!encode3d(&ta0, dt, eb, L.a0, L.k, L.m, p.a_bz ? L.batch : 1,
+    // A of two tensors side by side along K: each gets a map of its own columns (reads past a tensor's last
+    // column arrive as zeros, so only the first tensor's width must be whole k-blocks)
+    const bool two_a = L.k_first > 0;
+    if (two_a && (L.nsplit != 1 || L.batch != 1 || L.k_first >= L.k || L.k_first % bk != 0 || L.a1 == nullptr ||
+                  L.lda_second < L.k - L.k_first)) {
+      *err = "GEMM with A in two parts: needs 8/16-bit operands, one matrix, a first part of whole k-blocks";
+      return 3;
+    }
+    p.a_split_kb = two_a ? L.k_first / bk : 0;
+    if (!encode3d(&ta0, dt, eb, L.a0, two_a ? L.k_first : L.k, L.m, p.a_bz ? L.batch : 1,
                   static_cast<uint64_t>(L.lda) * eb, a_bs, bk, 128, 1, err)) {
       return 1;
     }
     ta1 = ta0;
+    if (two_a && !encode3d(&ta1, dt, eb, L.a1, L.k - L.k_first, L.m, 1, static_cast<uint64_t>(L.lda_second) * eb,
+                           static_cast<uint64_t>(L.lda_second) * eb * L.m, bk, 128, 1, err)) {
+      return 1;
+    }
     if (L.nsplit == 2 &&
         !encode3d(&ta1, dt, eb, L.a1, L.k, L.m, p.a_bz ? L.batch : 1,
                   static_cast<uint64_t>(L.lda) * eb, a_bs, bk, 128, 1, err)) {

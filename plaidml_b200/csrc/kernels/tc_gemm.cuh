@@ -108,6 +108,7 @@ struct TcParams {
   uint32_t idesc_half;   // the same for a half-width tile
   int wait_limit_us;     // wall-clock limit of every barrier wait of this launch in microseconds; 0 = two seconds
   int test_drop_load;    // testing the time-out path: CTA 0's producer never issues its first operand load
+  int a_split_kb;        // > 0: A's k-blocks from this one on come from the second tensor (map a1, its k from 0)
   int* status;           // device word: 0 = ok, otherwise the first error code seen
   long long* trace;      // debugging: CTA 0 logs (role, tile, event, clock64) records here, or null
 };

@@ -497,8 +497,10 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
     fence_mbar_init();
     tma_prefetch_desc(&tm.a0);
     tma_prefetch_desc(&tm.b0);
-    if (NSPLIT == 2) {
+    if (NSPLIT == 2 || p.a_split_kb > 0) {
       tma_prefetch_desc(&tm.a1);
+    }
+    if (NSPLIT == 2) {
       tma_prefetch_desc(&tm.b1);
     }
     if (p.fast_epi && p.out != nullptr) tma_prefetch_desc(&tm.c);
@@ -709,7 +711,14 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
               // both CTAs count their bytes on the first CTA's barrier, which expects both
               const uint32_t fb0 = mapa_rank(fb, 0);
               const int n0 = tc.n0 + static_cast<int>(cta_rank) * (tc.bn / 2);
-              tma_load_3d_pair(s_a, &tm.a0, fb0, kb * BK, tc.tm * 128, tc.b * p.a_bz);
+              if constexpr (NSPLIT == 1) {
+                // (A may be two tensors side by side along K: k-blocks from a_split_kb on come from the second)
+                const bool second = p.a_split_kb > 0 && kb >= p.a_split_kb;
+                tma_load_3d_pair(s_a, second ? &tm.a1 : &tm.a0, fb0, (second ? kb - p.a_split_kb : kb) * BK, tc.tm * 128,
+                                 tc.b * p.a_bz);
+              } else {
+                tma_load_3d_pair(s_a, &tm.a0, fb0, kb * BK, tc.tm * 128, tc.b * p.a_bz);
+              }
               if constexpr (Cfg::B_MN) {
 #pragma unroll
                 for (int ch = 0; ch < Cfg::B_CHUNKS; ++ch) {
@@ -720,7 +729,13 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
                 tma_load_3d_pair(s_b, &tm.b0, fb0, kb * BK, n0, tc.b * p.b_bz);
               }
             } else {
-              tma_load_3d(s_a, &tm.a0, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
+              if constexpr (NSPLIT == 1) {
+                const bool second = p.a_split_kb > 0 && kb >= p.a_split_kb;
+                tma_load_3d(s_a, second ? &tm.a1 : &tm.a0, fb, (second ? kb - p.a_split_kb : kb) * BK, tc.tm * 128,
+                            tc.b * p.a_bz);
+              } else {
+                tma_load_3d(s_a, &tm.a0, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
+              }
               if constexpr (NSPLIT == 2) {
                 tma_load_3d(s_a + Cfg::A_TILE, &tm.a1, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
               }

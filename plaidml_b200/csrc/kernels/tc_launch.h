@@ -54,6 +54,10 @@ struct TcLaunch {
   const void* a0 = nullptr;
   const void* a1 = nullptr;
   long long lda = 0;             // elements between rows of A
+  int k_first = 0;               // > 0 (plain 8/16-bit GEMMs, nsplit == 1, batch 1): A is two tensors side by side
+                                 // along K -- columns [0, k_first) from a0, [k_first, k) from a1 (rows lda_second
+                                 // apart, its own column 0 first); k_first a multiple of the k-block (128 bytes)
+  long long lda_second = 0;
   long long a_batch_stride = 0;  // elements between batch entries, 0 = shared
   const void* b0 = nullptr;
   const void* b1 = nullptr;

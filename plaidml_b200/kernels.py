@@ -47,6 +47,7 @@ class GemmDesc(C.Structure):
         ("b_is_nk", C.c_int32), ("epilogue", C.c_int32),
         ("ldr", C.c_int64), ("stride_r", C.c_int64),
         ("tile_n", C.c_int32), ("flags", C.c_int32),
+        ("k_first", C.c_int32), ("reserved0", C.c_int32), ("lda2", C.c_int64),
     ]
 
 
@@ -143,6 +144,7 @@ def load() -> C.CDLL:
                        ("contract", ContractDesc), ("eltwise", EltwiseDesc)):
         getattr(lib, f"pmlb_{name}_dispatch").argtypes = [C.POINTER(desc), C.POINTER(vp)]
     lib.pmlb_gemm_invoke.argtypes = [vp] * 8
+    lib.pmlb_gemm_invoke_two.argtypes = [vp] * 9
     lib.pmlb_conv_set_filter.argtypes = [vp, vp, vp, C.c_int32]
     lib.pmlb_conv_invoke.argtypes = [vp] * 6
     lib.pmlb_reduce_invoke.argtypes = [vp] * 4
@@ -196,6 +198,10 @@ class Plan:
     # invoke wrappers take raw device addresses (ints) and a stream handle (int, 0 = default)
     def gemm(self, a, b, c, bias=None, residual=None, rowmax=None, stream=0):
         check(self.lib.pmlb_gemm_invoke(self.handle, stream, a, b, c, bias, residual, rowmax))
+
+    def gemm_two(self, a, a2, b, c, bias=None, residual=None, rowmax=None, stream=0):
+        """A plan whose descriptor has k_first > 0: `a2` holds columns k_first.. of A."""
+        check(self.lib.pmlb_gemm_invoke_two(self.handle, stream, a, a2, b, c, bias, residual, rowmax))
 
     def set_filter(self, filt, dtype, stream=0):
         check(self.lib.pmlb_conv_set_filter(self.handle, stream, filt, dtype))

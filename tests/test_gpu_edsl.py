@@ -359,6 +359,41 @@ def test_layers_run_like_the_operations_they_enclose():
     np.testing.assert_allclose(n, np.maximum(a.astype(np.float64) @ b.astype(np.float64).T, 0), rtol=1e-5, atol=1e-5)
 
 
+def test_shortcut_projection_runs_inside_the_blocks_last_layer(monkeypatch):
+    # relu(y . W2 + b2 + cast(cast(x . W1 + b1, bf16), f32)): a residual block's last 1x1 layer whose residual is the
+    # block's shortcut projection.  One GEMM over [y | x] and the stacked weights; equal to the two-step form up to the
+    # one rounding of the projection that the fused form leaves out
+    g = rng(1262)
+    m, c_mid, c_in, c_out = 4 * 14 * 14, 64, 128, 256
+    y = f32_to_bf16_bits(g.standard_normal((m, c_mid)))
+    x = f32_to_bf16_bits(g.standard_normal((m, c_in)))
+    w2 = f32_to_bf16_bits(g.standard_normal((c_mid, c_out)) * 0.1)
+    w1 = f32_to_bf16_bits(g.standard_normal((c_in, c_out)) * 0.1)
+    b2 = g.standard_normal(c_out).astype(np.float32)
+    b1 = g.standard_normal(c_out).astype(np.float32)
+
+    def build():
+        Y, X = Placeholder(DType.BFLOAT16, [m, c_mid]), Placeholder(DType.BFLOAT16, [m, c_in])
+        W2 = cast(edsl.Constant(w2, name="w2", dtype=DType.BFLOAT16), DType.FLOAT32)
+        W1 = cast(edsl.Constant(w1, name="w1", dtype=DType.BFLOAT16), DType.FLOAT32)
+        shortcut = cast(op.dot(cast(X, DType.FLOAT32), W1) + edsl.Constant(b1, name="b1"), DType.BFLOAT16)
+        main = op.dot(cast(Y, DType.FLOAT32), W2) + edsl.Constant(b2, name="b2")
+        return Program("block_tail", [Y, X], [cast(op.relu(main + cast(shortcut, DType.FLOAT32)), DType.BFLOAT16)])
+
+    fused = Runner(build(), "cuda.0")
+    desc = fused.executable.describe()
+    assert desc.count("tc_gemm") == 1 and "+shortcut(k128)" in desc and "k192" in desc, desc
+    got = bf16_bits_to_f32(fused.run([y, x])[0])
+    yf, xf = bf16_bits_to_f32(y).astype(np.float64), bf16_bits_to_f32(x).astype(np.float64)
+    exact = np.maximum(yf @ bf16_bits_to_f32(w2) + b2 + xf @ bf16_bits_to_f32(w1) + b1, 0)
+    check_close(got, bf16_bits_to_f32(f32_to_bf16_bits(exact.astype(np.float32))), 1e-2)
+    monkeypatch.setenv("PLAIDML_CUDA_NO_SHORTCUT_FUSION", "1")
+    plain = Runner(build(), "cuda.0")
+    assert plain.executable.describe().count("tc_gemm") == 2
+    check_close(got, bf16_bits_to_f32(plain.run([y, x])[0]), 1e-2)
+    monkeypatch.delenv("PLAIDML_CUDA_NO_SHORTCUT_FUSION")
+
+
 def _stem_program(n, h, with_side_output=False, w_img=224):
     g = rng(1251)
     w = f32_to_bf16_bits(g.standard_normal((7, 7, 3, 64)) * np.sqrt(2.0 / 147))
@@ -437,7 +472,7 @@ def test_avgpool_counts_only_in_range_taps():
     np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-6)
 
 
-def test_residual_block_fusion_and_order():
+def test_residual_block_fusion_and_order(monkeypatch):
     # relu(conv_c(x) + bias + shortcut(x)) with the shortcut branch lowered after the main one
     g = rng(1241)
     n, h, w, c, k = 2, 14, 14, 64, 128
@@ -452,13 +487,20 @@ def test_residual_block_fusion_and_order():
     main = op.convolution(xi, F1, name="main") + edsl.Constant(b1)
     short = cast(cast(op.convolution(xi, F2, name="shortcut"), DType.BFLOAT16), DType.FLOAT32)
     O = cast(op.relu(main + short), DType.BFLOAT16)
+    xf = bf16_bits_to_f32(x)
+    sc = bf16_bits_to_f32(f32_to_bf16_bits(oracle.conv2d_nhwc_f32(xf, bf16_bits_to_f32(f2))))
+    ref = oracle.conv2d_nhwc_f32(xf, bf16_bits_to_f32(f1), b1, sc, relu=True)
+    # the shortcut is a projection of the same rows: it joins the main product in one GEMM over [x | x]
+    runner = Runner(Program("block", [I], [O]), "cuda.0")
+    desc = runner.executable.describe()
+    assert desc.count("tc_gemm") == 1 and "+bias+shortcut(k64)+relu+cast" in desc, desc
+    check_close(bf16_bits_to_f32(runner.run([x])[0]), bf16_bits_to_f32(f32_to_bf16_bits(ref)), 1e-2)
+    # ... and as the residual of the main product when that fusion is off
+    monkeypatch.setenv("PLAIDML_CUDA_NO_SHORTCUT_FUSION", "1")
     runner = Runner(Program("block", [I], [O]), "cuda.0")
     desc = runner.executable.describe()
     assert "+bias+residual+relu+cast" in desc, desc
     got = bf16_bits_to_f32(runner.run([x])[0])
-    xf = bf16_bits_to_f32(x)
-    sc = bf16_bits_to_f32(f32_to_bf16_bits(oracle.conv2d_nhwc_f32(xf, bf16_bits_to_f32(f2))))
-    ref = oracle.conv2d_nhwc_f32(xf, bf16_bits_to_f32(f1), b1, sc, relu=True)
     check_close(got, bf16_bits_to_f32(f32_to_bf16_bits(ref)), 1e-2)
 
 

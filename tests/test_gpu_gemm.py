@@ -533,3 +533,61 @@ def test_two_issuers_with_tiles_longer_than_the_ring():
     rows = np.concatenate([np.arange(0, 256), np.arange(25000, 25128), np.arange(m - 128, m)])
     ref = oracle.gemm_h16_f32(bits16(a)[:, rows], bits16(b), False, True)
     check_close(oracle.bf16_to_f32(first[:, rows]), oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+
+
+@pytest.mark.parametrize("kind,m,n,k1,k2,b_is_nk,epi", [
+    ("bf16", 300, 256, 64, 64, False, K.EPI_BIAS | K.EPI_RELU),        # a residual block's last 1x1 layer with its shortcut
+    ("bf16", 1000, 512, 128, 256, False, K.EPI_BIAS | K.EPI_RELU),     # several k-blocks per part
+    ("bf16", 4096, 1024, 256, 512, True, 0),                            # B as [n][k]; CTA pairs (256-wide tiles, 12 k-blocks)
+    ("bf16", 640, 192, 128, 72, False, K.EPI_BIAS),                    # second part ends inside a k-block (zero fill)
+    ("i8", 512, 256, 128, 384, False, 0),                               # int8, bit-exact
+    ("i8", 4096, 4096, 2048, 2048, True, 0),                            # pairs, 32 k-blocks
+])
+def test_gemm_with_a_in_two_parts(kind, m, n, k1, k2, b_is_nk, epi):
+    # C = [A1 | A2] * B with A1 and A2 separate matrices (own row strides): what sums a shortcut projection and a
+    # block's last convolution in one accumulator; against the oracle on the concatenated operand
+    g = rng(5200 + m + k2)
+    k = k1 + k2
+    bshape = (n, k) if b_is_nk else (k, n)
+    d = K.GemmDesc()
+    d.m, d.n, d.k, d.batch = m, n, k, 1
+    d.lda, d.lda2, d.k_first = k1, k2 + 8 * (16 if kind == "i8" else 8), k1     # (the second part with padded rows)
+    d.ldb, d.ldc = (k if b_is_nk else n), n
+    d.stride_a, d.stride_b, d.stride_c = m * k1, n * k, m * n
+    d.b_is_nk, d.epilogue = int(b_is_nk), epi
+    d.ldr, d.stride_r = n, m * n
+    bias = g.standard_normal(n).astype(np.float32) if epi & K.EPI_BIAS else None
+    if kind == "i8":
+        d.in_dtype, d.out_dtype = K.I8, K.I32
+        a1 = g.integers(-128, 128, size=(m, k1), dtype=np.int8)
+        a2 = np.zeros((m, d.lda2), dtype=np.int8)
+        a2[:, :k2] = g.integers(-128, 128, size=(m, k2), dtype=np.int8)
+        b = g.integers(-128, 128, size=bshape, dtype=np.int8)
+        plan = K.Plan("gemm", d)
+        out = empty((1, m, n), K.I32)
+        a1d, a2d, bd = dev(a1), dev(a2), dev(b)
+        plan.gemm_two(ptr(a1d), ptr(a2d), ptr(bd), ptr(out))
+        plan.check()
+        ref = oracle.gemm_i8_i32(np.concatenate([a1, a2[:, :k2]], axis=1), b, b_is_nk)
+        np.testing.assert_array_equal(out.cpu().numpy()[0], ref)
+        with pytest.raises(K.KernelError):
+            plan.gemm(ptr(a1d), ptr(bd), ptr(out))          # the plain call has no second part to give
+        return
+    d.in_dtype, d.out_dtype = K.BF16, K.F32
+    a1 = dev_bf16(g.standard_normal((m, k1)))
+    a2_host = np.zeros((m, d.lda2), dtype=np.float32)
+    a2_host[:, :k2] = g.standard_normal((m, k2))
+    a2 = dev_bf16(a2_host)
+    b = dev_bf16(g.standard_normal(bshape))
+    plan = K.Plan("gemm", d)
+    out = empty((1, m, n), K.F32)
+    bias_dev = dev(bias) if bias is not None else None
+    plan.gemm_two(ptr(a1), ptr(a2), ptr(b), ptr(out), ptr(bias_dev))
+    plan.check()
+    a_cat = np.concatenate([bits16(a1), bits16(a2)[:, :k2]], axis=1)
+    ref = oracle.gemm_h16_f32(a_cat[None], bits16(b)[None], False, b_is_nk)[0].astype(np.float64)
+    if bias is not None:
+        ref = ref + bias[None, :]
+    if epi & K.EPI_RELU:
+        ref = np.maximum(ref, 0)
+    check_close(out.cpu().numpy()[0], ref.astype(np.float32), 1e-4)

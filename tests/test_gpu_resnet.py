@@ -54,7 +54,9 @@ def test_resnet50_logits_match_oracle():
     # 53 convolutions + the FC contraction on tensor cores; pooling and the average on their kernels
     assert kinds.count("tc_conv_s2d_pool") == 1, plan      # the 7x7 / 2 first layer on 3 channels with its max pool
     assert kinds.count("tc_conv_halo") == 3, plan          # the 3x3, 64 -> 64 convolutions of the first stage
-    assert kinds.count("tc_conv_s2d_pool") + kinds.count("tc_conv_halo") + kinds.count("tc_conv") + kinds.count("tc_gemm") == 54, plan
+    # (53 launches for the 54 contractions: the first block's shortcut projection runs inside its last 1x1 layer)
+    assert kinds.count("tc_conv_s2d_pool") + kinds.count("tc_conv_halo") + kinds.count("tc_conv") + kinds.count("tc_gemm") == 53, plan
+    assert plan.count("+shortcut(k64)") == 1, plan
     assert "nhwc_pool" not in kinds and "strided_reduce" in kinds
     assert "generic_contract" not in kinds, plan
     g = rng(1234 + 4)
