@@ -140,8 +140,13 @@ typedef struct {
    * projection's output ever being written or read back.  8/16-bit inputs, batch 1, k_first a multiple of
    * the 128-byte k-block; run with pmlb_gemm_invoke_two.  No counterpart in the reference. */
   int32_t k_first;
-  int32_t reserved0;
+  int32_t a2_stride;                 /* 0: the second part is a matrix (rows lda2 apart); s >= 1: it is an NHWC
+                                      * activation [a2_n][a2_h][a2_w][k - k_first] and row i of the product is its
+                                      * pixel (i / (P Q), s * (i / Q % P), s * (i % Q)), P = ceil(a2_h / s),
+                                      * Q = ceil(a2_w / s), m = a2_n * P * Q: a strided 1x1 convolution's view of it
+                                      * (the shortcut projection of a block that halves the resolution) */
   int64_t lda2;
+  int32_t a2_n, a2_h, a2_w, reserved0;
 } pmlb_gemm_desc;
 
 /* With b_is_nk == 0 the 16-bit and 8-bit kernels read B tiles straight from the [k][n]

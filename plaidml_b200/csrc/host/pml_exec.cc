@@ -308,15 +308,35 @@ class Planner {
       const int mid = root(main.residual);
       for (size_t m1 = 0; m1 < m2; ++m1) {
         Pending& proj = pending_[m1];
-        if (proj.dropped || proj.kind != Pending::Gemm || root(proj.result) != mid) continue;
-        const pmlb_gemm_desc& g1 = proj.gemm;
+        if (proj.dropped || root(proj.result) != mid) continue;
+        if (proj.kind != Pending::Gemm && proj.kind != Pending::Conv) break;
         const pmlb_gemm_desc& g2 = main.gemm;
-        if (proj.residual >= 0 || proj.rowmax >= 0 || proj.a2 >= 0 || (g1.epilogue & ~PMLB_EPI_BIAS) != 0) break;
-        if (g1.batch != 1 || g2.batch != 1 || g1.m != g2.m || g1.n != g2.n || g1.in_dtype != g2.in_dtype ||
-            g1.in_dtype == PMLB_F32 || g1.b_is_nk || g2.b_is_nk || g1.ldb != g1.n || g2.ldb != g2.n || g1.lda != g1.k ||
-            g2.lda != g2.k || g2.ldr != g2.n) {
-          break;
+        if (proj.residual >= 0 || proj.rowmax >= 0 || proj.a2 >= 0) break;
+        // the projection as "rows x k1 times k1 x n": a GEMM over the same rows, or a 1x1 convolution (possibly
+        // strided: a block that halves the resolution) whose output pixels are those rows
+        int k1 = 0, a2Stride = 0, a2n = 0, a2h = 0, a2w = 0;
+        int64_t lda2 = 0;
+        if (proj.kind == Pending::Gemm) {
+          const pmlb_gemm_desc& g1 = proj.gemm;
+          if ((g1.epilogue & ~PMLB_EPI_BIAS) != 0 || g1.batch != 1 || g1.m != g2.m || g1.n != g2.n ||
+              g1.in_dtype != g2.in_dtype || g1.b_is_nk || g1.ldb != g1.n || g1.lda != g1.k) {
+            break;
+          }
+          k1 = g1.k;
+          lda2 = g1.lda;
+        } else {
+          const pmlb_conv_desc& c1 = proj.conv;
+          if ((c1.epilogue & ~PMLB_EPI_BIAS) != 0 || c1.r != 1 || c1.s != 1 || c1.pad_h != 0 || c1.pad_w != 0 ||
+              c1.stride_h != c1.stride_w || c1.dil_h != 1 || c1.dil_w != 1 || c1.k != g2.n || c1.in_dtype != g2.in_dtype ||
+              static_cast<int64_t>(c1.n) * c1.p * c1.q != g2.m || c1.p != (c1.h + c1.stride_h - 1) / c1.stride_h ||
+              c1.q != (c1.w + c1.stride_w - 1) / c1.stride_w) {
+            break;
+          }
+          k1 = c1.c;
+          a2Stride = c1.stride_h;
+          a2n = c1.n, a2h = c1.h, a2w = c1.w;
         }
+        if (g2.batch != 1 || g2.in_dtype == PMLB_F32 || g2.b_is_nk || g2.ldb != g2.n || g2.lda != g2.k || g2.ldr != g2.n) break;
         // the projection's output feeds this residual and nothing else
         if (isOutput_[mid] || uses_[mid] != 1) break;
         {
@@ -332,13 +352,15 @@ class Planner {
         const Buffer* b1 = hostConstant(proj.bias);
         const Buffer* b2 = hostConstant(main.bias);
         if (!w1 || !w2 || (proj.bias >= 0 && !b1) || (main.bias >= 0 && !b2)) break;
-        const size_t eb = g1.in_dtype == PMLB_I8 ? 1 : 2;
-        const bool intPath = g1.in_dtype == PMLB_I8;
-        if (w1->size() != static_cast<size_t>(g1.k) * g1.n * eb || w2->size() != static_cast<size_t>(g2.k) * g2.n * eb) break;
+        const size_t eb = g2.in_dtype == PMLB_I8 ? 1 : 2;
+        const bool intPath = g2.in_dtype == PMLB_I8;
+        if (w1->size() != static_cast<size_t>(k1) * g2.n * eb || w2->size() != static_cast<size_t>(g2.k) * g2.n * eb) break;
         pmlb_gemm_desc trial = g2;
-        trial.k = g2.k + g1.k;
+        trial.k = g2.k + k1;
         trial.k_first = g2.k;
-        trial.lda2 = g1.lda;
+        trial.lda2 = lda2;
+        trial.a2_stride = a2Stride;
+        trial.a2_n = a2n, trial.a2_h = a2h, trial.a2_w = a2w;
         trial.epilogue = (g2.epilogue & ~PMLB_EPI_RESIDUAL) | ((b1 || b2) ? PMLB_EPI_BIAS : 0);
         pmlb_plan* probe = nullptr;
         const pmlb_status rc = pmlb_gemm_dispatch(&trial, &probe);
@@ -378,8 +400,9 @@ class Planner {
         main.inputs.push_back(proj.a);
         {
           const size_t at = main.fused.find("+residual");
-          if (at != std::string::npos) main.fused.replace(at, 9, "+shortcut(k" + std::to_string(g1.k) + ")");
-          else main.fused += "+shortcut(k" + std::to_string(g1.k) + ")";
+          const std::string tag = "+shortcut(k" + std::to_string(k1) + (a2Stride > 1 ? "/" + std::to_string(a2Stride) : "") + ")";
+          if (at != std::string::npos) main.fused.replace(at, 9, tag);
+          else main.fused += tag;
         }
         proj.dropped = true;
         break;

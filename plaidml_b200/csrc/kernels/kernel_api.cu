@@ -293,8 +293,16 @@ pmlb_status pmlb_gemm_dispatch(const pmlb_gemm_desc* d, pmlb_plan** out) {
     if (f32 || d->batch != 1 || (d->k_first * eb) % 128 != 0 || (d->epilogue & PMLB_EPI_ROWMAX)) {
       return fail(PMLB_ERR_UNSUPPORTED, "gemm: A in two parts needs 8/16-bit inputs, one matrix, whole k-blocks in the first part");
     }
-    if (d->lda2 < d->k - d->k_first || (d->lda2 * eb) % 16 != 0) {
+    if (d->a2_stride < 0) return fail(PMLB_ERR_INVALID, "gemm: negative a2_stride");
+    if (d->a2_stride == 0 && (d->lda2 < d->k - d->k_first || (d->lda2 * eb) % 16 != 0)) {
       return fail(PMLB_ERR_INVALID, "gemm: lda2 smaller than the second part's width, or rows not 16-byte aligned");
+    }
+    if (d->a2_stride > 0) {
+      const long long pp = (d->a2_h + d->a2_stride - 1) / d->a2_stride, qq = (d->a2_w + d->a2_stride - 1) / d->a2_stride;
+      if (d->a2_n <= 0 || d->a2_h <= 0 || d->a2_w <= 0 || d->a2_n * pp * qq != d->m || d->a2_stride > 8 ||
+          ((d->k - d->k_first) * eb) % 16 != 0) {
+        return fail(PMLB_ERR_UNSUPPORTED, "gemm: the second part's pixels do not match m, or its channels are not whole 16-byte groups");
+      }
     }
   }
   const long long min_lda = d->k_first > 0 ? d->k_first : d->k;
@@ -412,6 +420,18 @@ pmlb_status pmlb_gemm_invoke_two(pmlb_plan* plan, void* stream_v, const void* a,
   L.bn_override = d.tile_n;
   L.k_first = d.k_first;
   L.lda_second = d.lda2;
+  pmlb::ConvGeom second_pixels;
+  if (d.k_first > 0 && d.a2_stride > 0) {
+    second_pixels = pmlb::ConvGeom{};
+    second_pixels.n = d.a2_n; second_pixels.h = d.a2_h; second_pixels.w = d.a2_w; second_pixels.c = d.k - d.k_first;
+    second_pixels.r = second_pixels.s = 1;
+    second_pixels.p = (d.a2_h + d.a2_stride - 1) / d.a2_stride;
+    second_pixels.q = (d.a2_w + d.a2_stride - 1) / d.a2_stride;
+    second_pixels.stride_h = second_pixels.stride_w = d.a2_stride;
+    second_pixels.pad_h = second_pixels.pad_w = 0;
+    second_pixels.dil_h = second_pixels.dil_w = 1;
+    L.a_second_pixels = &second_pixels;
+  }
   L.force_slow_epilogue = (d.flags & PMLB_GEMM_PLAIN_STORES) != 0;
   L.residual_from_global = (d.flags & PMLB_GEMM_PLAIN_RESIDUAL) != 0;
   if (d.flags & PMLB_GEMM_CTA_PAIRS) L.pair_override = 1;

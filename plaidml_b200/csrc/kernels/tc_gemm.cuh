@@ -109,6 +109,10 @@ struct TcParams {
   int wait_limit_us;     // wall-clock limit of every barrier wait of this launch in microseconds; 0 = two seconds
   int test_drop_load;    // testing the time-out path: CTA 0's producer never issues its first operand load
   int a_split_kb;        // > 0: A's k-blocks from this one on come from the second tensor (map a1, its k from 0)
+  int a2_pixels;         // 1: that second tensor is an NHWC activation sampled at a stride (im2col map a1): row i of
+                         // the product is its pixel (i / (a2_p * a2_q), stride * (i / a2_q % a2_p), stride * (i % a2_q))
+  int a2_p, a2_q, a2_stride;
+  FastDiv a2_fd_per_img, a2_fd_q;
   int* status;           // device word: 0 = ok, otherwise the first error code seen
   long long* trace;      // debugging: CTA 0 logs (role, tile, event, clock64) records here, or null
 };

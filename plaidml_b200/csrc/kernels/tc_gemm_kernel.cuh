@@ -678,6 +678,18 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
           pix_w = p.conv_lower_w + oq * p.conv_stride_w;
           pix_h = p.conv_lower_h + op * p.conv_stride_h;
         }
+        // second part of A as pixels: the tile's first row is pixel (a2_n, a2_h, a2_w) of that activation
+        int a2_w = 0, a2_h = 0, a2_n = 0;
+        if constexpr (!Cfg::A_IM2COL && NSPLIT == 1) {
+          if (p.a2_pixels) {
+            const int m0 = tc.tm * 128;
+            a2_n = fast_div(m0, p.a2_fd_per_img);
+            const int rem = m0 - a2_n * (p.a2_p * p.a2_q);
+            const int op = fast_div(rem, p.a2_fd_q);
+            a2_w = (rem - op * p.a2_q) * p.a2_stride;
+            a2_h = op * p.a2_stride;
+          }
+        }
         int tap = 0, cb = 0, fr = 0, fs = 0;   // im2col: k-block = (filter tap, channel block)
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait_warp(empty_bar(stage), phase ^ 1u, abort_flag)) {
@@ -712,10 +724,15 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
               const uint32_t fb0 = mapa_rank(fb, 0);
               const int n0 = tc.n0 + static_cast<int>(cta_rank) * (tc.bn / 2);
               if constexpr (NSPLIT == 1) {
-                // (A may be two tensors side by side along K: k-blocks from a_split_kb on come from the second)
+                // (A may be two tensors side by side along K: k-blocks from a_split_kb on come from the second,
+                // a matrix or the pixels of an activation sampled at a stride)
                 const bool second = p.a_split_kb > 0 && kb >= p.a_split_kb;
-                tma_load_3d_pair(s_a, second ? &tm.a1 : &tm.a0, fb0, (second ? kb - p.a_split_kb : kb) * BK, tc.tm * 128,
-                                 tc.b * p.a_bz);
+                if (second && p.a2_pixels) {
+                  tma_load_im2col_4d_pair(s_a, &tm.a1, fb0, (kb - p.a_split_kb) * BK, a2_w, a2_h, a2_n, 0, 0);
+                } else {
+                  tma_load_3d_pair(s_a, second ? &tm.a1 : &tm.a0, fb0, (second ? kb - p.a_split_kb : kb) * BK,
+                                   tc.tm * 128, tc.b * p.a_bz);
+                }
               } else {
                 tma_load_3d_pair(s_a, &tm.a0, fb0, kb * BK, tc.tm * 128, tc.b * p.a_bz);
               }
@@ -731,8 +748,12 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
             } else {
               if constexpr (NSPLIT == 1) {
                 const bool second = p.a_split_kb > 0 && kb >= p.a_split_kb;
-                tma_load_3d(s_a, second ? &tm.a1 : &tm.a0, fb, (second ? kb - p.a_split_kb : kb) * BK, tc.tm * 128,
-                            tc.b * p.a_bz);
+                if (second && p.a2_pixels) {
+                  tma_load_im2col_4d(s_a, &tm.a1, fb, (kb - p.a_split_kb) * BK, a2_w, a2_h, a2_n, 0, 0);
+                } else {
+                  tma_load_3d(s_a, second ? &tm.a1 : &tm.a0, fb, (second ? kb - p.a_split_kb : kb) * BK, tc.tm * 128,
+                              tc.b * p.a_bz);
+                }
               } else {
                 tma_load_3d(s_a, &tm.a0, fb, kb * BK, tc.tm * 128, tc.b * p.a_bz);
               }

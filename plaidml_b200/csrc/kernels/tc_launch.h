@@ -58,6 +58,9 @@ struct TcLaunch {
                                  // along K -- columns [0, k_first) from a0, [k_first, k) from a1 (rows lda_second
                                  // apart, its own column 0 first); k_first a multiple of the k-block (128 bytes)
   long long lda_second = 0;
+  const ConvGeom* a_second_pixels = nullptr;  // non-null: the second part is an NHWC activation [n][h][w][k - k_first]
+                                              // read as a 1x1 convolution with this stride (no padding): row i of the
+                                              // product is output pixel i, m = n * p * q
   long long a_batch_stride = 0;  // elements between batch entries, 0 = shared
   const void* b0 = nullptr;
   const void* b1 = nullptr;

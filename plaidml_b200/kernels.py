@@ -47,7 +47,8 @@ class GemmDesc(C.Structure):
         ("b_is_nk", C.c_int32), ("epilogue", C.c_int32),
         ("ldr", C.c_int64), ("stride_r", C.c_int64),
         ("tile_n", C.c_int32), ("flags", C.c_int32),
-        ("k_first", C.c_int32), ("reserved0", C.c_int32), ("lda2", C.c_int64),
+        ("k_first", C.c_int32), ("a2_stride", C.c_int32), ("lda2", C.c_int64),
+        ("a2_n", C.c_int32), ("a2_h", C.c_int32), ("a2_w", C.c_int32), ("reserved0", C.c_int32),
     ]
 
 

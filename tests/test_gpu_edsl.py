@@ -394,6 +394,33 @@ def test_shortcut_projection_runs_inside_the_blocks_last_layer(monkeypatch):
     monkeypatch.delenv("PLAIDML_CUDA_NO_SHORTCUT_FUSION")
 
 
+def test_strided_shortcut_projection_runs_inside_the_blocks_last_layer():
+    # a block that halves the resolution: main = conv1x1(y) on 14x14, shortcut = conv1x1 / 2 of x on 28x28; the
+    # projection's pixels are the second part of the last layer's A (an im2col load per k-block), its weights stacked
+    g = rng(1263)
+    n, c_mid, c_in, c_out = 3, 64, 128, 256
+    y = f32_to_bf16_bits(g.standard_normal((n, 14, 14, c_mid)))
+    x = f32_to_bf16_bits(g.standard_normal((n, 28, 28, c_in)))
+    w2 = f32_to_bf16_bits(g.standard_normal((1, 1, c_mid, c_out)) * 0.1)
+    w1 = f32_to_bf16_bits(g.standard_normal((1, 1, c_in, c_out)) * 0.1)
+    b2 = g.standard_normal(c_out).astype(np.float32)
+    b1 = g.standard_normal(c_out).astype(np.float32)
+    Y, X = Placeholder(DType.BFLOAT16, list(y.shape)), Placeholder(DType.BFLOAT16, list(x.shape))
+    W2 = cast(edsl.Constant(w2, name="w2", dtype=DType.BFLOAT16), DType.FLOAT32)
+    W1 = cast(edsl.Constant(w1, name="w1", dtype=DType.BFLOAT16), DType.FLOAT32)
+    shortcut = op.convolution(cast(X, DType.FLOAT32), W1, strides=[2, 2], autopad_mode=op.AutoPadMode.VALID, name="proj")
+    shortcut = cast(shortcut + edsl.Constant(b1, name="b1"), DType.BFLOAT16)
+    main = op.convolution(cast(Y, DType.FLOAT32), W2, name="last") + edsl.Constant(b2, name="b2")
+    O = cast(op.relu(main + cast(shortcut, DType.FLOAT32)), DType.BFLOAT16)
+    runner = Runner(Program("down_block_tail", [Y, X], [O]), "cuda.0")
+    desc = runner.executable.describe()
+    assert desc.count("\n") == 1 and "tc_gemm" in desc and "+shortcut(k128/2)" in desc, desc
+    got = bf16_bits_to_f32(runner.run([y, x])[0])
+    yf, xf = bf16_bits_to_f32(y), bf16_bits_to_f32(x)
+    ref = oracle.conv2d_nhwc_f32(yf, bf16_bits_to_f32(w2), b2) + oracle.conv2d_nhwc_f32(xf, bf16_bits_to_f32(w1), b1, None, (2, 2))
+    check_close(got, bf16_bits_to_f32(f32_to_bf16_bits(np.maximum(ref, 0))), 1e-2)
+
+
 def _stem_program(n, h, with_side_output=False, w_img=224):
     g = rng(1251)
     w = f32_to_bf16_bits(g.standard_normal((7, 7, 3, 64)) * np.sqrt(2.0 / 147))

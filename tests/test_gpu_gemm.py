@@ -591,3 +591,46 @@ def test_gemm_with_a_in_two_parts(kind, m, n, k1, k2, b_is_nk, epi):
     if epi & K.EPI_RELU:
         ref = np.maximum(ref, 0)
     check_close(out.cpu().numpy()[0], ref.astype(np.float32), 1e-4)
+
+
+@pytest.mark.parametrize("n,h,w,c1,c2,k,stride,pairs", [
+    (2, 28, 28, 128, 256, 512, 2, False),      # a block that halves the resolution: 392 rows, the last tile ragged
+    (64, 28, 28, 128, 256, 512, 2, True),      # 12544 rows, 6 k-blocks, 256-wide tiles as CTA pairs
+    (3, 15, 13, 64, 72, 128, 2, False),        # odd sizes (8 x 7 samples per image), channels ending inside a k-block
+    (4, 7, 9, 64, 64, 64, 1, False),           # stride 1: the activation's pixels as they are
+    (5, 20, 20, 64, 128, 256, 3, False),       # stride 3
+])
+def test_gemm_whose_second_part_of_a_is_an_activation_sampled_at_a_stride(n, h, w, c1, c2, k, stride, pairs):
+    # C = [Y | sample(X)] * B: Y a matrix of m = n * P * Q rows, X an NHWC activation of which every stride-th pixel in
+    # both directions is a row: the shortcut projection of a block that halves the resolution, inside the block's
+    # last 1x1 layer
+    g = rng(5300 + n + h)
+    pp, qq = -(-h // stride), -(-w // stride)
+    m = n * pp * qq
+    y = dev_bf16(g.standard_normal((m, c1)))
+    x = dev_bf16(g.standard_normal((n, h, w, c2)))
+    b = dev_bf16(g.standard_normal((c1 + c2, k)) * 0.1)
+    bias = g.standard_normal(k).astype(np.float32)
+    d = K.GemmDesc()
+    d.in_dtype, d.out_dtype = K.BF16, K.F32
+    d.m, d.n, d.k, d.batch = m, k, c1 + c2, 1
+    d.lda, d.k_first, d.ldb, d.ldc = c1, c1, k, k
+    d.a2_stride, d.a2_n, d.a2_h, d.a2_w = stride, n, h, w
+    d.stride_a, d.stride_b, d.stride_c = m * c1, (c1 + c2) * k, m * k
+    d.b_is_nk, d.epilogue = 0, K.EPI_BIAS | K.EPI_RELU
+    d.ldr, d.stride_r = k, m * k
+    d.flags = K.GEMM_CTA_PAIRS if pairs else 0
+    plan = K.Plan("gemm", d)
+    out = empty((1, m, k), K.F32)
+    out.fill_(float("nan"))
+    bias_dev = dev(bias)
+    plan.gemm_two(ptr(y), ptr(x), ptr(b), ptr(out), ptr(bias_dev))
+    plan.check()
+    sampled = bits16(x)[:, ::stride, ::stride, :].reshape(m, c2)
+    a_cat = np.concatenate([bits16(y), sampled], axis=1)
+    ref = oracle.gemm_h16_f32(a_cat[None], bits16(b)[None], False, False)[0].astype(np.float64) + bias[None, :]
+    check_close(out.cpu().numpy()[0], np.maximum(ref, 0).astype(np.float32), 1e-4)
+    # a pixel count that does not match m is refused
+    d.a2_h = h + stride
+    with pytest.raises(K.KernelError):
+        K.Plan("gemm", d)
