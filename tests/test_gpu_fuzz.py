@@ -8,9 +8,9 @@ import pytest
 
 import oracle
 from plaidml_b200 import kernels as K
-from gpu_util import as_f32, bits16, check_close, dev, dev_bf16, ptr, rng
+from gpu_util import as_f32, bits16, check_close, dev, dev_bf16, empty, ptr, rng
 
-from test_gpu_conv import run_conv
+from test_gpu_conv import out_size, run_conv
 from test_gpu_gemm import run_gemm
 
 pytestmark = pytest.mark.gpu
@@ -293,7 +293,6 @@ def test_random_halo_conv_with_merged_filter_columns(seed):
             pytest.skip(f"shape takes {plan.kernel}")
         f_dev = dev(f32)
         plan.set_filter(ptr(f_dev), K.F32)
-        from gpu_util import empty
         out = empty((n, p, q, 64), out_dtype)
         out.fill_(float("nan"))
         plan.conv(ptr(x), ptr(out), ptr(dev(bias)) if bias is not None else None, None)
@@ -308,6 +307,135 @@ def test_random_halo_conv_with_merged_filter_columns(seed):
             check_close(outs[0], outs[1], 1e-5)
         else:
             check_close(outs[0], oracle.bf16_to_f32(oracle.f32_to_bf16(ref)), 1e-2)
+    except AssertionError as e:
+        raise AssertionError(f"{case}: {e}") from None
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_gemm_with_a_in_two_parts(seed):
+    # C = [A1 | A2] * B (+ bias, ReLU): A2 a matrix with its own row stride or an NHWC activation sampled at a stride;
+    # int8 bit-exact, bf16 against the oracle on the concatenated operand
+    g = rng(9800 + seed)
+    kind = "i8" if seed % 4 == 0 else "bf16"
+    bk = 128 if kind == "i8" else 64
+    pixels = seed % 2 == 1
+    k1 = bk * int(g.integers(1, 5))
+    k2 = 8 * int(g.integers(1, 40)) if kind == "bf16" else 16 * int(g.integers(1, 24))
+    n_cols = 8 * int(g.integers(1, 70))
+    b_is_nk = bool(g.integers(0, 2))
+    epi = int(g.choice([0, K.EPI_BIAS, K.EPI_RELU, K.EPI_BIAS | K.EPI_RELU])) if kind == "bf16" else 0
+    d = K.GemmDesc()
+    if pixels:
+        stride = int(g.integers(1, 4))
+        n_img, h, w = int(g.integers(1, 5)), int(g.integers(3, 30)), int(g.integers(3, 30))
+        m = n_img * (-(-h // stride)) * (-(-w // stride))
+        d.a2_stride, d.a2_n, d.a2_h, d.a2_w = stride, n_img, h, w
+    else:
+        m = int(g.integers(1, 900))
+        d.lda2 = k2 + (16 if kind == "i8" else 8) * int(g.integers(0, 3))
+    k = k1 + k2
+    d.m, d.n, d.k, d.batch = m, n_cols, k, 1
+    d.lda, d.k_first = k1, k1
+    d.ldb, d.ldc = (k if b_is_nk else n_cols), n_cols
+    d.stride_a, d.stride_b, d.stride_c = m * k1, n_cols * k, m * n_cols
+    d.b_is_nk, d.epilogue = int(b_is_nk), epi
+    d.ldr, d.stride_r = n_cols, m * n_cols
+    d.flags = int(g.choice([0, 0, K.GEMM_CTA_PAIRS, K.GEMM_NO_CTA_PAIRS]))
+    d.tile_n = int(g.choice([0, 0, 64, 128]))
+    bshape = (n_cols, k) if b_is_nk else (k, n_cols)
+    case = dict(kind=kind, m=m, n=n_cols, k1=k1, k2=k2, pixels=pixels, b_is_nk=b_is_nk, epi=epi, flags=d.flags, tile=d.tile_n)
+    if kind == "i8":
+        d.in_dtype, d.out_dtype = K.I8, K.I32
+        a1 = g.integers(-128, 128, size=(m, k1), dtype=np.int8)
+        if pixels:
+            x = g.integers(-128, 128, size=(n_img, h, w, k2), dtype=np.int8)
+            a2_rows, a2_dev = x[:, ::stride, ::stride, :].reshape(m, k2), dev(x)
+        else:
+            a2 = np.zeros((m, d.lda2), dtype=np.int8)
+            a2[:, :k2] = g.integers(-128, 128, size=(m, k2), dtype=np.int8)
+            a2_rows, a2_dev = a2[:, :k2], dev(a2)
+        b = g.integers(-128, 128, size=bshape, dtype=np.int8)
+        if not b_is_nk and n_cols % 16 != 0:
+            pytest.skip("int8 B as [k][n] with rows that are not 16-byte multiples takes the transposed copy")
+        plan = K.Plan("gemm", d)
+        out = empty((1, m, n_cols), K.I32)
+        a1d, bd = dev(a1), dev(b)
+        plan.gemm_two(ptr(a1d), ptr(a2_dev), ptr(bd), ptr(out))
+        plan.check()
+        ref = oracle.gemm_i8_i32(np.concatenate([a1, a2_rows], axis=1), b, b_is_nk)
+        np.testing.assert_array_equal(out.cpu().numpy()[0], ref, err_msg=str(case))
+        return
+    d.in_dtype, d.out_dtype = K.BF16, K.F32
+    a1 = dev_bf16(g.standard_normal((m, k1)))
+    if pixels:
+        x = dev_bf16(g.standard_normal((n_img, h, w, k2)))
+        a2_rows, a2_dev = bits16(x)[:, ::stride, ::stride, :].reshape(m, k2), x
+    else:
+        a2_host = np.zeros((m, d.lda2), dtype=np.float32)
+        a2_host[:, :k2] = g.standard_normal((m, k2))
+        a2_dev = dev_bf16(a2_host)
+        a2_rows = bits16(a2_dev)[:, :k2]
+    b = dev_bf16(g.standard_normal(bshape))
+    bias = g.standard_normal(n_cols).astype(np.float32) if epi & K.EPI_BIAS else None
+    plan = K.Plan("gemm", d)
+    out = empty((1, m, n_cols), K.F32)
+    out.fill_(float("nan"))
+    bias_dev = dev(bias) if bias is not None else None
+    plan.gemm_two(ptr(a1), ptr(a2_dev), ptr(b), ptr(out), ptr(bias_dev))
+    plan.check()
+    a_cat = np.concatenate([bits16(a1), a2_rows], axis=1)
+    ref = oracle.gemm_h16_f32(a_cat[None], bits16(b)[None], False, b_is_nk)[0].astype(np.float64)
+    if bias is not None:
+        ref = ref + bias[None, :]
+    if epi & K.EPI_RELU:
+        ref = np.maximum(ref, 0)
+    try:
+        check_close(out.cpu().numpy()[0], ref.astype(np.float32), 1e-4)
+    except AssertionError as e:
+        raise AssertionError(f"{case}: {e}") from None
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_first_layer_with_fused_pool(seed):
+    # 7-wide stride-2 convolutions of 1..4 channels into 64 + bias / ReLU + 3x3 / 2 max pool as one kernel: random image
+    # counts and heights (runs of tiles that start inside images, fewer tiles than SMs, many tiles per CTA), widths
+    # over the accepted range, both paddings; against the oracle's convolution followed by its pool
+    g = rng(9900 + seed)
+    c = int(g.integers(1, 5))
+    pad = int(g.choice([2, 3]))
+    q = 4 * int(g.integers(24, 32))                      # 96 .. 124 output columns
+    w = 2 * (q - 1) + 7 - 2 * pad + int(g.integers(0, 2))
+    p = 4 * int(g.integers(1, 9))
+    h = 2 * (p - 1) + 7 - 2 * pad + int(g.integers(0, 2))
+    n = int(g.integers(1, 40)) if p <= 12 else int(g.integers(1, 8))
+    epi = int(g.choice([0, K.EPI_BIAS, K.EPI_RELU, K.EPI_BIAS | K.EPI_RELU]))
+    assert out_size(h, 7, 2, pad, pad, 1) == p and out_size(w, 7, 2, pad, pad, 1) == q
+    x = dev_bf16(g.uniform(-1, 1, size=(n, h, w, c)))
+    f32 = (g.standard_normal((7, 7, c, 64)) * np.sqrt(2.0 / (49 * c))).astype(np.float32)
+    bias = g.standard_normal(64).astype(np.float32) if epi & K.EPI_BIAS else None
+    d = K.ConvDesc()
+    d.in_dtype, d.out_dtype = K.BF16, K.BF16
+    d.n, d.h, d.w, d.c, d.r, d.s, d.k, d.p, d.q = n, h, w, c, 7, 7, 64, p, q
+    d.stride_h = d.stride_w = 2
+    d.pad_h = d.pad_w = pad
+    d.dil_h = d.dil_w = 1
+    d.epilogue, d.flags = epi, K.CONV_MAX_POOL_3X3_S2
+    plan = K.Plan("conv", d)
+    assert plan.kernel == "tc_conv_s2d_pool"
+    f_dev = dev(f32)
+    plan.set_filter(ptr(f_dev), K.F32)
+    out = empty((n, p // 2, q // 2, 64), K.BF16)
+    out.fill_(float("nan"))
+    bias_dev = dev(bias) if bias is not None else None
+    plan.conv(ptr(x), ptr(out), ptr(bias_dev), None)
+    plan.check()
+    conv_ref = oracle.conv2d_nhwc_f32(as_f32(x), oracle.bf16_to_f32(oracle.f32_to_bf16(f32)), bias, None, (2, 2), (pad, pad),
+                                      (1, 1), bool(epi & K.EPI_RELU), out_hw=(p, q))
+    conv_ref = oracle.bf16_to_f32(oracle.f32_to_bf16(conv_ref))
+    ref = oracle.pool2d_nhwc_f32(conv_ref, "max", (3, 3), (2, 2), (1, 1), (p // 2, q // 2))
+    case = dict(n=n, h=h, w=w, c=c, pad=pad, epi=epi)
+    try:
+        check_close(as_f32(out), ref, 1e-2)
     except AssertionError as e:
         raise AssertionError(f"{case}: {e}") from None
 
