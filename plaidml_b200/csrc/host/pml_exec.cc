@@ -566,6 +566,8 @@ class Planner {
     while (stage < 4) {
       if (uses_[cur] != 1 || isOutput_[cur] || users_[cur].size() != 1) break;
       const int ui = users_[cur][0];
+      // (an add of two contractions' results is the epilogue of one of them only: the one planned first)
+      if (absorbed_[ui]) break;
       const POp& u = prog_.ops[ui];
       const TensorShape& rs = val(u.result).shape;
       if (rs.sizes != val(cur).shape.sizes) break;
@@ -828,7 +830,7 @@ class Planner {
       }
       int a, b, inDtype, outDtype;
       if (!tcTypes(opI, opF, outShape.dtype, &a, &b, &inDtype, &outDtype)) continue;
-      if (inDtype != PMLB_BF16 && inDtype != PMLB_F16) continue;
+      if (inDtype != PMLB_BF16 && inDtype != PMLB_F16 && inDtype != PMLB_F32) continue;
       // plain 1x1 stride-1 convolutions are GEMMs; let that path take them
       if (fs.sizes[0] == 1 && fs.sizes[1] == 1 && stride[0] == 1 && stride[1] == 1 && pad[0] == 0 && pad[1] == 0) {
         return false;
@@ -853,7 +855,8 @@ class Planner {
       d.dil_w = static_cast<int32_t>(dil[1]);
       if (d.pad_h > 127 || d.pad_w > 127 || d.stride_h > 8 || d.stride_w > 8) continue;
       // the im2col route needs whole 16-byte channel groups; thin inputs take the packed-row route
-      if (d.c % 8 != 0 && !pmlb::conv_takes_packed_rows(d) && !pmlb::conv_takes_s2d(d)) continue;
+      // (fp32: any channel count, the split pre-pass pads it)
+      if (inDtype != PMLB_F32 && d.c % 8 != 0 && !pmlb::conv_takes_packed_rows(d) && !pmlb::conv_takes_s2d(d)) continue;
       pd->kind = Pending::Conv;
       pd->a = a;
       pd->b = b;

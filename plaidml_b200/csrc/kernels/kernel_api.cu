@@ -537,11 +537,16 @@ pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* d, pmlb_plan** out) {
   *out = nullptr;
   std::string why;
   if (!have_sm100(&why)) return fail(PMLB_ERR_UNSUPPORTED, why);
-  if (d->in_dtype != PMLB_BF16 && d->in_dtype != PMLB_F16) {
-    return fail(PMLB_ERR_UNSUPPORTED, "conv: activations must be bf16 or f16");
+  if (d->in_dtype != PMLB_BF16 && d->in_dtype != PMLB_F16 && d->in_dtype != PMLB_F32) {
+    return fail(PMLB_ERR_UNSUPPORTED, "conv: activations must be bf16, f16 or f32");
   }
   if (d->out_dtype != PMLB_F32 && d->out_dtype != PMLB_BF16 && d->out_dtype != PMLB_F16) {
     return fail(PMLB_ERR_UNSUPPORTED, "conv: output must be f32, bf16 or f16");
+  }
+  const bool f32 = d->in_dtype == PMLB_F32;
+  if (f32 && d->out_dtype != PMLB_F32) return fail(PMLB_ERR_UNSUPPORTED, "conv: f32 activations produce f32");
+  if (f32 && (d->flags & PMLB_CONV_MAX_POOL_3X3_S2)) {
+    return fail(PMLB_ERR_UNSUPPORTED, "conv: this shape does not take the fused max pool");
   }
   if (d->n <= 0 || d->h <= 0 || d->w <= 0 || d->c <= 0 || d->r <= 0 || d->s <= 0 || d->k <= 0 ||
       d->p <= 0 || d->q <= 0 || d->stride_h <= 0 || d->stride_w <= 0 || d->dil_h <= 0 ||
@@ -555,7 +560,7 @@ pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* d, pmlb_plan** out) {
   }
   const bool packed =
       !s2d && pmlb::conv_takes_packed_rows(*d) && (d->flags & PMLB_CONV_NO_PACKED_ROWS) == 0;
-  if (!packed && !s2d && d->c % 8 != 0) {
+  if (!f32 && !packed && !s2d && d->c % 8 != 0) {
     return fail(PMLB_ERR_UNSUPPORTED, "conv: channel count must be a multiple of 8");
   }
   // every output pixel's first tap must lie inside the im2col bounding box
@@ -572,6 +577,17 @@ pmlb_status pmlb_conv_dispatch(const pmlb_conv_desc* d, pmlb_plan** out) {
   plan->kind_name = "tc_conv";
   plan->conv = *d;
   size_t scratch = static_cast<size_t>(d->k) * d->r * d->s * d->c * 2;
+  if (f32) {
+    // fp32: three TF32 products per term (as the fp32 GEMM): the filter and, per call, the activation are split
+    // into high and low TF32 parts, channels padded to whole 16-byte groups; scratch = [w hi][w lo][x hi][x lo]
+    plan->split = true;
+    plan->kpad = round_up(d->c, 4);
+    plan->kind_name = "tc_conv";
+    const size_t wts = static_cast<size_t>(d->k) * d->r * d->s * plan->kpad * 4;
+    const size_t act = static_cast<size_t>(d->n) * d->h * d->w * plan->kpad * 4;
+    plan->packed_input_off = (2 * wts + 255) / 256 * 256;
+    scratch = plan->packed_input_off + 2 * ((act + 255) / 256 * 256);
+  }
   if (s2d) {
     const pmlb::S2dShape g = pmlb::conv_s2d_shape(*d);
     plan->s2d = true;
@@ -613,7 +629,12 @@ pmlb_status pmlb_conv_set_filter(pmlb_plan* plan, void* stream, const void* filt
   }
   const pmlb_conv_desc& d = plan->conv;
   cudaError_t e;
-  if (plan->s2d) {
+  if (plan->split) {
+    const size_t wts = static_cast<size_t>(d.k) * d.r * d.s * plan->kpad;   // elements of one part
+    e = pmlb::launch_filter_relayout_split(filter, dtype, static_cast<float*>(plan->scratch),
+                                           static_cast<float*>(plan->scratch) + wts, d.r * d.s, d.c,
+                                           static_cast<int>(plan->kpad), d.k, static_cast<cudaStream_t>(stream));
+  } else if (plan->s2d) {
     const pmlb::S2dShape g = pmlb::conv_s2d_shape(d);
     e = plan->s2d_pool ? pmlb::launch_filter_s2d_merged(filter, dtype, plan->scratch, d.in_dtype, d.r, d.s, d.c, d.k,
                                                         g.r2, g.s2, g.dh, g.dw, static_cast<cudaStream_t>(stream))
@@ -752,6 +773,30 @@ pmlb_status pmlb_conv_invoke(pmlb_plan* plan, void* stream, const void* input, v
   L.batch = 1;
   L.a0 = input;
   L.b0 = plan->scratch;
+  if (plan->split) {
+    // the activation's high and low TF32 parts, one image per z block of the pre-pass, channels padded
+    const int cp = static_cast<int>(plan->kpad);
+    const size_t wts = static_cast<size_t>(d.k) * d.r * d.s * cp;
+    const size_t act = (static_cast<size_t>(d.n) * d.h * d.w * cp * 4 + 255) / 256 * 256;
+    float* x_hi = reinterpret_cast<float*>(static_cast<char*>(plan->scratch) + plan->packed_input_off);
+    float* x_lo = reinterpret_cast<float*>(static_cast<char*>(plan->scratch) + plan->packed_input_off + act);
+    const long long img = static_cast<long long>(d.h) * d.w;
+    for (int n0 = 0; n0 < d.n; n0 += 32768) {
+      const int nb = d.n - n0 < 32768 ? d.n - n0 : 32768;
+      cudaError_t e = pmlb::launch_split_tf32(static_cast<const float*>(input) + n0 * img * d.c, d.c, img * d.c,
+                                              x_hi + n0 * img * cp, x_lo + n0 * img * cp, cp, img * cp, static_cast<int>(img),
+                                              d.c, nb, false, static_cast<cudaStream_t>(stream));
+      if (e != cudaSuccess) return cuda_fail(e, "split(activation)");
+    }
+    g.c = cp;
+    L.elem_bytes = 4;
+    L.nsplit = 2;
+    L.k = d.r * d.s * cp;
+    L.a0 = x_hi;
+    L.a1 = x_lo;
+    L.b0 = plan->scratch;
+    L.b1 = static_cast<float*>(plan->scratch) + wts;
+  }
   pmlb::HaloGeom hg;
   if (plan->halo) {
     hg.conv = g;

@@ -128,6 +128,23 @@ filter_relayout_kernel(const void* __restrict__ in, int in_dtype, void* __restri
   }
 }
 
+// fp32 convolutions: filter [taps][c][k] -> high and low TF32 parts, each [k][taps][cp] (cp >= c, zeros in the pad)
+__global__ void __launch_bounds__(256)
+filter_relayout_split_kernel(const void* __restrict__ in, int in_dtype, float* __restrict__ hi, float* __restrict__ lo,
+                             int taps, int c, int cp, int k) {
+  const long long id = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long total = static_cast<long long>(taps) * cp * k;
+  if (id >= total) return;
+  const int ci = static_cast<int>(id % cp);
+  const long long rem = id / cp;
+  const int t = static_cast<int>(rem % taps);
+  const int ko = static_cast<int>(rem / taps);
+  const float v = ci < c ? load_filter(in, in_dtype, (static_cast<long long>(t) * c + ci) * k + ko) : 0.f;
+  const float h = tf32_round(v);
+  hi[id] = h;
+  lo[id] = tf32_round(v - h);
+}
+
 // One thread per group of 8 output channels of one output pixel (16 bytes).
 __global__ void __launch_bounds__(256)
 pack_rows_kernel(const uint16_t* __restrict__ in, uint4* __restrict__ out, long long rows, int w,
@@ -412,6 +429,15 @@ cudaError_t launch_filter_relayout(const void* in, int in_dtype, void* out, int 
   if (total <= 0) return cudaSuccess;
   filter_relayout_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
       in, in_dtype, out, out_dtype, taps, c, k);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_filter_relayout_split(const void* in, int in_dtype, float* hi, float* lo, int taps, int c, int cp,
+                                         int k, cudaStream_t stream) {
+  const long long total = static_cast<long long>(taps) * cp * k;
+  if (total <= 0) return cudaSuccess;
+  filter_relayout_split_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(in, in_dtype, hi, lo, taps,
+                                                                                                c, cp, k);
   return cudaGetLastError();
 }
 

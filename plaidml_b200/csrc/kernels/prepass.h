@@ -36,6 +36,11 @@ cudaError_t launch_transpose(const void* in, long long ld, long long in_batch, v
 cudaError_t launch_filter_relayout(const void* in, int in_dtype, void* out, int out_dtype, int taps,
                                    int c, int k, cudaStream_t stream);
 
+// The same for fp32 convolutions (three TF32 products per term): the high and the low TF32 part of the filter,
+// each [k][taps][cp] in f32 storage, channels zero-padded from c to cp.
+cudaError_t launch_filter_relayout_split(const void* in, int in_dtype, float* hi, float* lo, int taps, int c, int cp,
+                                         int k, cudaStream_t stream);
+
 // Packed-row convolution operands (16-bit elements).
 // Activation [n][h][w][c] -> [n][h][wp][cp]: `pad_w` zero pixels before every row, zeros after
 // it up to `wp` pixels, channels zero-padded from c to cp (a multiple of 8).

@@ -719,6 +719,13 @@ tc_contract_kernel(const __grid_constant__ TcMaps tm, const __grid_constant__ Tc
                                  static_cast<uint16_t>(fr * p.conv_dil_h));
               // weights laid out [k_out][tap][c_in]: map dims (c_in, tap, k_out)
               tma_load_3d(s_b, &tm.b0, fb, cb * BK, tap, tc.n0);
+              if constexpr (NSPLIT == 2) {
+                // fp32 as three TF32 products: the low parts of the pixels and of the weights
+                tma_load_im2col_4d(s_a + Cfg::A_TILE, &tm.a1, fb, cb * BK, pix_w, pix_h, pix_n,
+                                   static_cast<uint16_t>(fs * p.conv_dil_w),
+                                   static_cast<uint16_t>(fr * p.conv_dil_h));
+                tma_load_3d(s_b + Cfg::B_TILE, &tm.b1, fb, cb * BK, tap, tc.n0);
+              }
             } else if constexpr (CTAS == 2) {
               // both CTAs count their bytes on the first CTA's barrier, which expects both
               const uint32_t fb0 = mapa_rank(fb, 0);

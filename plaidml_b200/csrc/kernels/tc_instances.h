@@ -42,7 +42,10 @@
   X(1, 128, 1, false, true, 4, 2)   \
   X(4, 64, 2, false, false, 4, 1)   \
   X(4, 128, 2, false, false, 4, 1)  \
-  X(4, 64, 2, false, false, 4, 2)
+  X(4, 64, 2, false, false, 4, 2)   \
+  X(4, 64, 2, 1, false, 4, 1)       \
+  X(4, 128, 2, 1, false, 4, 1)      \
+  X(4, 64, 2, 1, false, 4, 2)
 
 // CTA-pair instances (two CTAs per 256 x 256 tile, cta_group::2 MMAs): plain GEMMs with long
 // main loops; same columns, always one epilogue group per CTA.

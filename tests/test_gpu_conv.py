@@ -413,3 +413,45 @@ def test_first_layer_fused_with_its_max_pool(n, h, w, c, r, pad, epi):
     two = oracle.pool2d_nhwc_f32(as_f32(mid), "max", (3, 3), (2, 2), (1, 1), (p // 2, q // 2))
     check_close(got, two, 1e-2)
     assert (got != two).mean() < 0.02
+
+
+@pytest.mark.parametrize("n,h,w,c,r,k,stride,pad,epi", [
+    (2, 14, 14, 64, 3, 64, 1, 1, K.EPI_BIAS | K.EPI_RELU),
+    (3, 28, 28, 128, 3, 128, 1, 1, 0),
+    (2, 56, 56, 256, 1, 512, 2, 0, K.EPI_BIAS),                 # a strided 1x1 projection
+    (2, 64, 64, 3, 7, 64, 2, 3, K.EPI_BIAS | K.EPI_RELU),       # first layer: 3 channels, padded to 4
+    (1, 17, 19, 20, 5, 40, 2, 2, K.EPI_RELU),                   # channels that are not a multiple of 32, odd sizes
+    (2, 12, 12, 36, 3, 72, 1, 2, K.EPI_BIAS | K.EPI_RESIDUAL | K.EPI_RELU),   # residual, wide padding
+    (2, 8, 8, 32, 3, 32, 2, 1, K.EPI_BIAS | K.EPI_RESIDUAL | K.EPI_RELU),     # 32 output pixels in all: one ragged tile
+    (2, 8, 8, 32, 3, 32, 2, 1, K.EPI_BIAS | K.EPI_RESIDUAL),
+    (2, 8, 8, 32, 3, 32, 2, 1, K.EPI_BIAS),
+])
+def test_fp32_convolution_on_tensor_cores(n, h, w, c, r, k, stride, pad, epi):
+    # fp32 activations and filter: three TF32 products per term on the im2col route (activation and filter split into
+    # high and low parts by pre-passes), f32 accumulation; against the oracle's f64-accumulated loop nest to 1e-5
+    g = rng(6100 + h + c)
+    p, q = out_size(h, r, stride, pad, pad, 1), out_size(w, r, stride, pad, pad, 1)
+    x = g.uniform(-1, 1, size=(n, h, w, c)).astype(np.float32)
+    f = (g.standard_normal((r, r, c, k)) * np.sqrt(2.0 / (r * r * c))).astype(np.float32)
+    bias = g.standard_normal(k).astype(np.float32) if epi & K.EPI_BIAS else None
+    res = g.standard_normal((n, p, q, k)).astype(np.float32) if epi & K.EPI_RESIDUAL else None
+    d = K.ConvDesc()
+    d.in_dtype, d.out_dtype = K.F32, K.F32
+    d.n, d.h, d.w, d.c, d.r, d.s, d.k, d.p, d.q = n, h, w, c, r, r, k, p, q
+    d.stride_h = d.stride_w = stride
+    d.pad_h = d.pad_w = pad
+    d.dil_h = d.dil_w = 1
+    d.epilogue = epi
+    plan = K.Plan("conv", d)
+    assert plan.kernel == "tc_conv"
+    x_dev, f_dev = dev(x), dev(f)
+    plan.set_filter(ptr(f_dev), K.F32)
+    out = empty((n, p, q, k), K.F32)
+    out.fill_(float("nan"))
+    bias_dev = dev(bias) if bias is not None else None
+    res_dev = dev(res) if res is not None else None
+    for _ in range(2):
+        plan.conv(ptr(x_dev), ptr(out), ptr(bias_dev), ptr(res_dev))
+        plan.check()
+    ref = oracle.conv2d_nhwc_f32(x, f, bias, res, (stride, stride), (pad, pad), (1, 1), bool(epi & K.EPI_RELU), out_hw=(p, q))
+    check_close(out.cpu().numpy(), ref, 1e-5)

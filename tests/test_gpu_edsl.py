@@ -421,6 +421,39 @@ def test_strided_shortcut_projection_runs_inside_the_blocks_last_layer():
     check_close(got, bf16_bits_to_f32(f32_to_bf16_bits(np.maximum(ref, 0))), 1e-2)
 
 
+def test_fp32_network_layers_run_on_tensor_cores():
+    # the reference's own networks are fp32 (networks/oplib/resnet50.cc): its convolutions take the im2col route as three
+    # TF32 products per term, 1x1 stride-1 layers the fp32 GEMM; nothing falls to the general kernel; 1e-5 like the fp32 GEMM
+    g = rng(1264)
+    n = 2
+    x = g.uniform(-1, 1, (n, 32, 32, 3)).astype(np.float32)
+    w1 = (g.standard_normal((7, 7, 3, 64)) * np.sqrt(2.0 / 147)).astype(np.float32)
+    w2 = (g.standard_normal((1, 1, 64, 32)) * np.sqrt(2.0 / 64)).astype(np.float32)
+    w3 = (g.standard_normal((3, 3, 32, 32)) * np.sqrt(2.0 / 288)).astype(np.float32)
+    w4 = (g.standard_normal((1, 1, 64, 32)) * np.sqrt(2.0 / 64)).astype(np.float32)
+    b1 = g.standard_normal(64).astype(np.float32) * 0.1
+    b3 = g.standard_normal(32).astype(np.float32) * 0.1
+    I = Placeholder(DType.FLOAT32, list(x.shape))
+    y = op.relu(op.convolution(I, edsl.Constant(w1, name="w1"), strides=[2, 2], autopad_mode=op.AutoPadMode.EXPLICIT,
+                               manual_padding=[3, 3, 3, 3]) + edsl.Constant(b1, name="b1"))
+    y = op.pool(y, op.PoolMode.MAX, [3, 3], [2, 2], op.AutoPadMode.EXPLICIT, [1, 1, 1, 1], op.TensorLayout.NXC)
+    z = op.relu(op.convolution(y, edsl.Constant(w2, name="w2")))
+    z = op.convolution(z, edsl.Constant(w3, name="w3"), strides=[2, 2], autopad_mode=op.AutoPadMode.EXPLICIT,
+                       manual_padding=[1, 1, 1, 1]) + edsl.Constant(b3, name="b3")
+    sc = op.convolution(y, edsl.Constant(w4, name="w4"), strides=[2, 2], autopad_mode=op.AutoPadMode.VALID)
+    O = op.relu(z + sc)
+    runner = Runner(Program("fp32_block", [I], [O]), "cuda.0")
+    desc = runner.executable.describe()
+    assert "generic_contract" not in desc and desc.count("tc_conv") >= 3 and "tc_gemm" in desc, desc
+    got = runner.run([x])[0]
+    r1 = oracle.conv2d_nhwc_f32(x, w1, b1, None, (2, 2), (3, 3), (1, 1), True)
+    r1 = oracle.pool2d_nhwc_f32(r1, "max", (3, 3), (2, 2), (1, 1), (8, 8))
+    r2 = oracle.conv2d_nhwc_f32(r1, w2, None, None, (1, 1), (0, 0), (1, 1), True)
+    r3 = oracle.conv2d_nhwc_f32(r2, w3, b3, None, (2, 2), (1, 1))
+    r4 = oracle.conv2d_nhwc_f32(r1, w4, None, None, (2, 2))
+    check_close(got, np.maximum(r3 + r4, 0), 2e-5)
+
+
 def _stem_program(n, h, with_side_output=False, w_img=224):
     g = rng(1251)
     w = f32_to_bf16_bits(g.standard_normal((7, 7, 3, 64)) * np.sqrt(2.0 / 147))
