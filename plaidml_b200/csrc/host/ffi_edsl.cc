@@ -151,6 +151,7 @@ plaidml_expr* plaidml_expr_dim(plaidml_error* err, plaidml_dim_expr* expr) {
 
 plaidml_expr* plaidml_expr_input(plaidml_error* err, plaidml_shape* shape, const char* name) {
   return ffiWrap<plaidml_expr*>(err, nullptr, [&] {
+    if (shape->shape.dtype == pml::DType::invalid) throw std::runtime_error("Placeholder with an invalid data type");
     ExprPtr node = makeExpr(ExprNode::Input);
     node->shape = shape->shape;
     node->name = name ? name : "";

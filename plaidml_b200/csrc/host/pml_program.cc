@@ -1078,14 +1078,19 @@ class Builder {
     const std::string& name = e->op;
     if (name == "index") {
       int64_t axis = 0;
-      if (!getIntegerValue(&ev, e->operands[0], &axis) || axis < 0 || static_cast<size_t>(axis) >= shape.rank()) {
+      if (!getIntegerValue(&ev, e->operands[0], &axis) || axis < 0) {
         throw std::runtime_error("'index' requires a valid axis");
       }
       // depends on the shape only: computed here, uploaded once with the executable
       BufferPtr buf = Buffer::allocate(shape);
       int32_t* p = reinterpret_cast<int32_t*>(buf->data());
       const std::vector<int64_t> st = shape.denseStrides();
-      for (int64_t i = 0; i < shape.elements(); ++i) p[i] = static_cast<int32_t>((i / st[axis]) % shape.sizes[axis]);
+      // (an axis past the last dimension is accepted when the program is built, as by the reference --
+      // plaidml/edsl/tests/edsl_test.cc IndexOp builds index({X0}, 1); there is one position along it: 0)
+      const bool inside = static_cast<size_t>(axis) < shape.rank();
+      for (int64_t i = 0; i < shape.elements(); ++i) {
+        p[i] = inside ? static_cast<int32_t>((i / st[axis]) % shape.sizes[axis]) : 0;
+      }
       PValue v;
       v.kind = PValue::InternalConstant;
       v.constant = buf;

@@ -52,3 +52,17 @@ inline void fail(const std::string& what) {
   static int fixture##_##name##_registered =                                                         \
       ::testing::Registry::add(#fixture "." #name, [] { return new fixture##_##name##_Test(); });    \
   void fixture##_##name##_Test::TestBody()
+
+#define EXPECT_ANY_THROW(statement)                                                    \
+  do {                                                                                 \
+    bool pmlb_threw = false;                                                           \
+    try { statement; } catch (...) { pmlb_threw = true; }                              \
+    if (!pmlb_threw) ::testing::fail("expected an exception: " #statement);            \
+  } while (0)
+
+#define EXPECT_NO_THROW(statement)                                                     \
+  do {                                                                                 \
+    try { statement; } catch (const std::exception& e) {                               \
+      ::testing::fail(std::string("unexpected exception: ") + e.what());               \
+    } catch (...) { ::testing::fail("unexpected exception: " #statement); }            \
+  } while (0)

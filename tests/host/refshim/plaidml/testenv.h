@@ -1,5 +1,5 @@
 // Stand-in for the reference's plaidml/testenv.h (same fixture class and method signatures,
-// plaidml/testenv.h:33-46 there) without gflags / half.hpp: the fixture's methods are implemented in
+// plaidml/testenv.h:33-46 there) without gflags, with this directory's half.hpp: the fixture's methods are implemented in
 // ref_driver.cc on the reference's own C++ API (plaidml::Buffer, plaidml::exec::Executable), i.e. on
 // whatever libplaidml.so the binary is linked with.
 #pragma once
@@ -10,11 +10,13 @@
 #include <variant>
 #include <vector>
 
+#include "half.hpp"
 #include "plaidml/edsl/edsl.h"
 
 namespace plaidml {
 
-using MultiBuffer = std::variant<  //
+using MultiBuffer = std::variant<   //
+    std::vector<half_float::half>,  //
     std::vector<float>,            //
     std::vector<double>,           //
     std::vector<int8_t>,           //

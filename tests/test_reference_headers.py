@@ -3,9 +3,12 @@ linked with this repository's libplaidml.so (tests/host/ref_driver.cc and the st
 tests/host/refshim/ replace googletest, gflags and three LLVM ADT headers, nothing of plaidml):
 
   * plaidml/edsl/examples/gemm.cc: five GEMM tests with exact expected outputs;
-  * networks/oplib/resnet50.cc: the reference's ResNet-50 builder, built at batch 1.
+  * networks/oplib/resnet50.cc: the reference's ResNet-50 builder, built at batch 1;
+  * plaidml/edsl/tests/edsl_test.cc: the reference's whole C++ EDSL suite, 119 tests with their own checkExact /
+    checkClose / EXPECT_* expectations.  Every test passes except the 34 that use the gather / scatter / argsort /
+    prng intrinsics (not contractions; the cuda target refuses them by name): the test below pins that list.
 
-The CPU half needs the checkout (``PLAIDML_REFERENCE_DIR``; skipped when unset) and g++: it compiles both
+The CPU half needs the checkout (``PLAIDML_REFERENCE_DIR``; skipped when unset) and g++: it compiles the
 binaries into tests/host/_build/ and runs them with --build-only (programs are built, printed and compiled
 for the `cuda` target; no device).  The GPU half runs whatever binaries tests/host/_build/ already holds --
 they link libplaidml.so dynamically, so they always exercise the current library -- on cuda.0 and applies
@@ -27,7 +30,30 @@ LIB_DIR = ROOT / "plaidml_b200"
 BINARIES = {
     "ref_gemm": (["plaidml/edsl/examples/gemm.cc"], []),
     "ref_resnet": (["networks/oplib/resnet50.cc"], ["-DPMLB_REF_RESNET"]),
+    "ref_edsl": (["plaidml/edsl/tests/edsl_test.cc"], []),
 }
+
+# Tests of the reference's EDSL suite whose programs use an intrinsic that is not a contraction and that the cuda
+# target does not offer (gather, scatter, argsort, prng; `gatherND` of the op library is built on gather).
+NOT_OFFERED = (
+    ["Prng", "Gather", "GatherND", "GatherNDWithBatchDims", "LayerMultipleReturnValues"]
+    + ["InterpolatedGather" + s for s in ("Nearest", "Linear", "LinearOutOfBoundsReturnZero", "Cubic", "CubicOutOfBoundsReturnZero",
+                                          "CubicDouble", "CubicHalf", "MultiDIndices", "ND1", "ND2", "ND3")]
+    + ["Scatter" + s for s in ("1D", "3D", "Dup1D", "Dup3D", "1DUpdateSlice", "3DUpdateSlice", "NDUpdateSlice", "NDUpdateSlice2",
+                               "NDUpdateSlice3", "Elt")]
+    + ["ArgSort" + s for s in ("1d", "1dInt", "1dDup", "2dAxis0", "2dAxis1", "3dAxis0Asc", "3dAxis2Desc", "3dAxisNeg2Asc")]
+)
+
+
+def _check_edsl_suite(out: str) -> None:
+    ran = [ln.split("CppEdsl.")[1].strip() for ln in out.splitlines() if ln.startswith("[ RUN ]")]
+    failed = [ln.split("CppEdsl.")[1].strip() for ln in out.splitlines() if ln.startswith("[ FAIL]")]
+    assert len(ran) == 119, len(ran)
+    assert sorted(failed) == sorted(NOT_OFFERED), sorted(set(failed) ^ set(NOT_OFFERED))
+    for name in failed:      # ... and each of them for that reason, not another
+        at = out.index("[ RUN ] CppEdsl." + name + "\n")
+        body = out[at:out.index("[ FAIL] CppEdsl." + name, at)]
+        assert "not offered by the cuda target" in body or "not in the cuda target's op library" in body, body[-600:]
 
 
 def build_binaries(ref_dir: Path) -> list:
@@ -44,9 +70,9 @@ def build_binaries(ref_dir: Path) -> list:
     return built
 
 
-def _run(binary: Path, *args) -> str:
+def _run(binary: Path, *args, ok_codes=(0,)) -> str:
     res = subprocess.run([str(binary), *args], capture_output=True, text=True, timeout=600)
-    assert res.returncode == 0, (res.stdout[-3000:], res.stderr[-2000:])
+    assert res.returncode in ok_codes, (res.stdout[-3000:], res.stderr[-2000:])
     return res.stdout
 
 
@@ -56,7 +82,8 @@ def test_reference_sources_compile_and_build_their_programs():
         pytest.skip("PLAIDML_REFERENCE_DIR does not point at a checkout of the reference")
     if shutil.which("g++") is None or not (LIB_DIR / "libplaidml.so").exists():
         pytest.skip("needs g++ and a built libplaidml.so")
-    gemm, resnet = build_binaries(Path(ref))
+    gemm, resnet, edsl_suite = build_binaries(Path(ref))
+    _check_edsl_suite(_run(edsl_suite, "--build-only", ok_codes=(0, 1)))
     out = _run(gemm, "--build-only")
     assert "5 tests, 0 failures" in out
     # the printed programs are the tile module of the reference's own FileCheck expectations
@@ -74,3 +101,9 @@ def test_reference_sources_run_on_the_cuda_device():
     if (OUT / "ref_resnet").exists():
         out = _run(OUT / "ref_resnet", "--device", "cuda.0")
         assert "1 tests, 0 failures" in out
+    if (OUT / "ref_edsl").exists():
+        # the 85 tests of the reference's EDSL suite that the target offers, with their own expected values
+        # (checkExact / checkClose at the reference's tolerances), on the device
+        out = _run(OUT / "ref_edsl", "--device", "cuda.0", ok_codes=(0, 1))
+        assert "build only" not in out
+        _check_edsl_suite(out)
