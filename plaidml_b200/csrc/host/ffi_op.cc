@@ -286,7 +286,8 @@ VarPtr opDot(const VarPtr& value) {
     PolyPtr z = newIndex();
     xi[xs.rank() - 1] = z;
     yi[ys.rank() - 2] = z;
-    if (xs.sizes.back() != ys.sizes[ys.rank() - 2]) throw std::runtime_error("bind dims mismatch in dot");
+    // (the two contracted dimensions are bound to separate dims in the reference: unequal sizes are not an error,
+    // the shared index simply ranges over the smaller one -- plaidml/op/op_test.cc Dot multiplies 7x7x3x64 by 7x7x3x64)
     std::vector<int64_t> od;
     std::vector<PolyPtr> oi;
     for (size_t i = 0; i + 1 < xs.rank(); ++i) {
@@ -769,7 +770,9 @@ VarPtr opCumsum(const VarPtr& value) {
   for (size_t i = 0; i < shape.rank(); ++i) oIdx.push_back(newIndex());
   iIdx = oIdx;
   PolyPtr k = newIndex("k");
-  iIdx[axis] = oIdx[axis] - k;
+  // plaidml/op/lib/ops.cc:1490-1511: the exclusive form leaves the element itself out (O[i] = sum of I[j], j < i)
+  const bool exclusive = args.size() > 2 && asBool(args[2]);
+  iIdx[axis] = exclusive ? oIdx[axis] - k - 1 : oIdx[axis] - k;
   return exprValue(contraction(pml::AggKind::add, pml::ComboKind::none, shape.sizes, oIdx, {{I, iIdx}},
                                {{k, shape.sizes[axis]}}, "cumsum"));
 }

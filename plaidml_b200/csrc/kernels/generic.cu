@@ -162,12 +162,25 @@ __global__ void __launch_bounds__(256) contract_kernel(const __grid_constant__ G
   for (int j = 0; j < p.n_loop; ++j) {
     if (p.range[p.loop_var[j]] <= 0) alive = false;
   }
+  for (int s = 0; s < p.n_solve; ++s) {
+    if (p.range[p.solve_var[s]] <= 0) alive = false;
+  }
 
   T acc = p.has_init ? narrow<T>(load_as<T>(p.initp, p.init.dtype, init_off), p.out.dtype)
                      : agg_identity<T>(p.agg, p.out.dtype);
 
   while (alive) {
     bool ok = true;
+    for (int s = 0; s < p.n_solve && ok; ++s) {
+      const int d = p.solve_dim[s];
+      const int v = p.solve_var[s];
+      x[v] = 0;
+      long long num = oc[d] - p.out.off[d];
+      for (int i = 0; i < p.n_idx; ++i) num -= static_cast<long long>(p.out.coef[d][i]) * x[i];
+      const long long xv = floor_div_exact(num, p.out.coef[d][v], &ok);
+      if (xv < 0 || xv >= p.range[v]) ok = false;
+      x[v] = xv;
+    }
     if (!p.direct) {
       for (int d = 0; d < p.out.rank && ok; ++d) {
         long long num = p.out.off[d];

@@ -29,6 +29,11 @@ struct GenericParams {
   int out_var[PMLB_MAX_RANK];
   int n_loop;                    // variables the thread iterates over
   int loop_var[PMLB_MAX_IDX];
+  // Without `direct`: variable solve_var[s] follows from output dim solve_dim[s] once the loop variables and
+  // the variables of earlier entries are set (its coefficient there is non-zero), so it is not iterated over.
+  int n_solve;
+  int solve_dim[PMLB_MAX_RANK];
+  int solve_var[PMLB_MAX_RANK];
   long long range[PMLB_MAX_IDX];
   GAccess out, init;
   GAccess src[3];

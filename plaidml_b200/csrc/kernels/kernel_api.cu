@@ -963,8 +963,40 @@ pmlb_status pmlb_contract_dispatch(const pmlb_contract_desc* d, pmlb_plan** out)
   }
   p.direct = direct ? 1 : 0;
   p.n_loop = 0;
-  for (int i = 0; i < d->n_idx; ++i) {
-    if (!direct || !used[i]) p.loop_var[p.n_loop++] = i;
+  p.n_solve = 0;
+  bool solvable = !direct;
+  for (int dd = 0; dd < d->out.rank; ++dd) {
+    if (p.out.den[dd] != 1) solvable = false;
+  }
+  if (solvable) {
+    // Output dims that mix variables (a transposed convolution's `s*x + i - pad`, a resize's `f*y + j`): per
+    // dim, the not yet fixed variable of the widest range is solved for from the element's coordinate and the
+    // others are iterated over, so a thread visits the taps of its element instead of the whole index box.
+    bool fixed[PMLB_MAX_IDX] = {false};
+    for (int dd = 0; dd < d->out.rank; ++dd) {
+      int pivot = -1;
+      for (int i = 0; i < d->n_idx; ++i) {
+        if (d->out.coef[dd][i] == 0 || fixed[i]) continue;
+        if (pivot < 0 || d->range[i] > d->range[pivot]) pivot = i;
+      }
+      if (pivot < 0) continue;
+      for (int i = 0; i < d->n_idx; ++i) {
+        if (d->out.coef[dd][i] == 0 || fixed[i] || i == pivot) continue;
+        fixed[i] = true;
+        p.loop_var[p.n_loop++] = i;
+      }
+      fixed[pivot] = true;
+      p.solve_dim[p.n_solve] = dd;
+      p.solve_var[p.n_solve] = pivot;
+      ++p.n_solve;
+    }
+    for (int i = 0; i < d->n_idx; ++i) {
+      if (!fixed[i]) p.loop_var[p.n_loop++] = i;
+    }
+  } else {
+    for (int i = 0; i < d->n_idx; ++i) {
+      if (!direct || !used[i]) p.loop_var[p.n_loop++] = i;
+    }
   }
   cudaGetDevice(&plan->device);
   *out = plan;

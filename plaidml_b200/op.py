@@ -156,8 +156,8 @@ def flip(x, axis):
     return op("flip", [x, axis]).as_tensor()
 
 
-def cumsum(x, axis):
-    return op("cumsum", [x, axis]).as_tensor()
+def cumsum(x, axis, exclusive=False):
+    return op("cumsum", [x, axis, exclusive]).as_tensor()
 
 
 def elu(x, alpha):

@@ -8,6 +8,7 @@
 //
 // With PMLB_REF_RESNET defined the binary also carries networks/oplib/resnet50.cc and one test that builds
 // the network at batch 1 through it (zero weights: the softmax output must be uniform).
+#include <chrono>
 #include <cmath>
 #include <cstring>
 #include <iostream>
@@ -162,6 +163,7 @@ int main(int argc, char** argv) {
   for (auto& entry : ::testing::Registry::tests()) {
     std::cout << "[ RUN ] " << entry.name << std::endl;
     const int before = ::testing::Registry::failures();
+    const auto started = std::chrono::steady_clock::now();
     try {
       std::unique_ptr<::testing::Test> t(entry.make());
       t->SetUp();
@@ -170,7 +172,9 @@ int main(int argc, char** argv) {
     } catch (const std::exception& e) {
       ::testing::fail(std::string("exception: ") + e.what());
     }
-    std::cout << (::testing::Registry::failures() == before ? "[  OK ] " : "[ FAIL] ") << entry.name << std::endl;
+    const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - started).count();
+    std::cout << (::testing::Registry::failures() == before ? "[  OK ] " : "[ FAIL] ") << entry.name << " (" << static_cast<long>(ms)
+              << " ms)" << std::endl;
     ++ran;
   }
   std::cout << ran << " tests, " << ::testing::Registry::failures() << " failures" << (g_build_only ? " (build only)" : "") << std::endl;

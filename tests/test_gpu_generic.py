@@ -114,6 +114,56 @@ def test_contract_non_injective_output_and_fraction():
     np.testing.assert_array_equal(out, np.array([1, 0, 2, 0, 3, 0, 4, 0], dtype=np.int32))
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_contract_output_dims_that_mix_variables(seed):
+    # O[n, s*y + i - p, t*x - j + q, k] += I[n, y, x, c] * F[i, j, c, k] with random strides, signs, offsets and
+    # an output that may be cropped: every thread solves for (y, x) from its element and walks the taps only.
+    g = rng(900 + seed)
+    n, h, w, c, k = (int(v) for v in g.integers(1, 5, 5))
+    h, w = h + 2, w + 3
+    fi, fj = int(g.integers(1, 4)), int(g.integers(1, 4))
+    s, t = int(g.integers(1, 4)), int(g.integers(1, 4))
+    po, qo = int(g.integers(0, 2)), int(g.integers(0, 3))
+    oh = s * (h - 1) + fi - po - int(g.integers(0, 2))
+    ow = t * (w - 1) + qo + 1 - int(g.integers(0, 2))
+    x = g.integers(-4, 5, (n, h, w, c)).astype(np.int32)
+    f = g.integers(-4, 5, (fi, fj, c, k)).astype(np.int32)
+    d = K.ContractDesc()
+    d.agg, d.combo, d.n_idx, d.n_src = K.AGG_SUM, K.COMBO_MUL, 7, 2
+    for i, r in enumerate([n, h, w, k, fi, fj, c]):
+        d.range[i] = r
+    d.out = K.make_access(K.I32, [n, oh, ow, k], [{0: 1}, {1: s, 4: 1}, {2: t, 5: -1}, {3: 1}], offs=[0, -po, qo, 0])
+    d.src[0] = K.make_access(K.I32, [n, h, w, c], [{0: 1}, {1: 1}, {2: 1}, {6: 1}])
+    d.src[1] = K.make_access(K.I32, [fi, fj, c, k], [{4: 1}, {5: 1}, {6: 1}, {3: 1}])
+    out, ref = run_contract(d, [x, f], (n, oh, ow, k), K.I32)
+    np.testing.assert_array_equal(out, ref)
+    want = np.zeros((n, oh, ow, k), dtype=np.int64)
+    for y in range(h):
+        for xx in range(w):
+            for i in range(fi):
+                for j in range(fj):
+                    oy, ox = s * y + i - po, t * xx - j + qo
+                    if 0 <= oy < oh and 0 <= ox < ow:
+                        want[:, oy, ox, :] += x[:, y, xx, :].astype(np.int64) @ f[i, j].astype(np.int64)
+    np.testing.assert_array_equal(out, want.astype(np.int32))
+
+
+def test_contract_shared_variable_across_output_dims():
+    # O[i, i + j] = A[i, j]: the second dim's only free variable follows from the first
+    a = np.arange(12, dtype=np.int32).reshape(3, 4) + 1
+    d = K.ContractDesc()
+    d.agg, d.combo, d.n_idx, d.n_src = K.AGG_SUM, K.COMBO_NONE, 2, 1
+    d.range[0], d.range[1] = 3, 4
+    d.out = K.make_access(K.I32, [3, 6], [{0: 1}, {0: 1, 1: 1}])
+    d.src[0] = K.make_access(K.I32, [3, 4], [{0: 1}, {1: 1}])
+    out, ref = run_contract(d, [a], (3, 6), K.I32)
+    np.testing.assert_array_equal(out, ref)
+    want = np.zeros((3, 6), dtype=np.int32)
+    for i in range(3):
+        want[i, i:i + 4] = a[i]
+    np.testing.assert_array_equal(out, want)
+
+
 def test_contract_init_tensor_and_min_and_cond():
     g = rng(4)
     a = g.standard_normal((5, 6)).astype(np.float32)

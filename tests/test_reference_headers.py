@@ -6,7 +6,10 @@ tests/host/refshim/ replace googletest, gflags and three LLVM ADT headers, nothi
   * networks/oplib/resnet50.cc: the reference's ResNet-50 builder, built at batch 1;
   * plaidml/edsl/tests/edsl_test.cc: the reference's whole C++ EDSL suite, 119 tests with their own checkExact /
     checkClose / EXPECT_* expectations.  Every test passes except the 34 that use the gather / scatter / argsort /
-    prng intrinsics (not contractions; the cuda target refuses them by name): the test below pins that list.
+    prng intrinsics (not contractions; the cuda target refuses them by name): the test below pins that list;
+  * plaidml/op/op_test.cc: the reference's op-library suite, 60 tests (67 with the parameterised convolution cases),
+    among them exact expected outputs for explicit paddings, transposed and grouped convolutions; all pass but `Sort`
+    (built on argsort).
 
 The CPU half needs the checkout (``PLAIDML_REFERENCE_DIR``; skipped when unset) and g++: it compiles the
 binaries into tests/host/_build/ and runs them with --build-only (programs are built, printed and compiled
@@ -31,6 +34,7 @@ BINARIES = {
     "ref_gemm": (["plaidml/edsl/examples/gemm.cc"], []),
     "ref_resnet": (["networks/oplib/resnet50.cc"], ["-DPMLB_REF_RESNET"]),
     "ref_edsl": (["plaidml/edsl/tests/edsl_test.cc"], []),
+    "ref_op": (["plaidml/op/op_test.cc"], []),
 }
 
 # Tests of the reference's EDSL suite whose programs use an intrinsic that is not a contraction and that the cuda
@@ -47,7 +51,7 @@ NOT_OFFERED = (
 
 def _check_edsl_suite(out: str) -> None:
     ran = [ln.split("CppEdsl.")[1].strip() for ln in out.splitlines() if ln.startswith("[ RUN ]")]
-    failed = [ln.split("CppEdsl.")[1].strip() for ln in out.splitlines() if ln.startswith("[ FAIL]")]
+    failed = [ln.split("CppEdsl.")[1].split(" (")[0].strip() for ln in out.splitlines() if ln.startswith("[ FAIL]")]
     assert len(ran) == 119, len(ran)
     assert sorted(failed) == sorted(NOT_OFFERED), sorted(set(failed) ^ set(NOT_OFFERED))
     for name in failed:      # ... and each of them for that reason, not another
@@ -70,6 +74,12 @@ def build_binaries(ref_dir: Path) -> list:
     return built
 
 
+def _check_op_suite(out: str) -> None:
+    failed = [ln.split("]")[1].split(" (")[0].strip() for ln in out.splitlines() if ln.startswith("[ FAIL]")]
+    assert "67 tests, 1 failures" in out and failed == ["OpTest.Sort"], (failed, out[-1500:])
+    assert "'sort' is not in the cuda target's op library" in out
+
+
 def _run(binary: Path, *args, ok_codes=(0,)) -> str:
     res = subprocess.run([str(binary), *args], capture_output=True, text=True, timeout=600)
     assert res.returncode in ok_codes, (res.stdout[-3000:], res.stderr[-2000:])
@@ -82,8 +92,9 @@ def test_reference_sources_compile_and_build_their_programs():
         pytest.skip("PLAIDML_REFERENCE_DIR does not point at a checkout of the reference")
     if shutil.which("g++") is None or not (LIB_DIR / "libplaidml.so").exists():
         pytest.skip("needs g++ and a built libplaidml.so")
-    gemm, resnet, edsl_suite = build_binaries(Path(ref))
+    gemm, resnet, edsl_suite, op_suite = build_binaries(Path(ref))
     _check_edsl_suite(_run(edsl_suite, "--build-only", ok_codes=(0, 1)))
+    _check_op_suite(_run(op_suite, "--build-only", ok_codes=(0, 1)))
     out = _run(gemm, "--build-only")
     assert "5 tests, 0 failures" in out
     # the printed programs are the tile module of the reference's own FileCheck expectations
@@ -107,3 +118,7 @@ def test_reference_sources_run_on_the_cuda_device():
         out = _run(OUT / "ref_edsl", "--device", "cuda.0", ok_codes=(0, 1))
         assert "build only" not in out
         _check_edsl_suite(out)
+    if (OUT / "ref_op").exists():
+        out = _run(OUT / "ref_op", "--device", "cuda.0", ok_codes=(0, 1))
+        assert "build only" not in out
+        _check_op_suite(out)
