@@ -391,6 +391,66 @@ pmlb_status pmlb_eltwise_dispatch(const pmlb_eltwise_desc* desc, pmlb_plan** pla
 pmlb_status pmlb_eltwise_invoke(pmlb_plan* plan, void* stream, const void* in0, const void* in1,
                                 const void* in2, void* out);
 
+/* ---------------------------------------------------------------- gather, scatter, argsort, prng
+ * The four operations of the tile dialect that are not contractions (pmlc/dialect/tile/ir/ops.td: GatherOp,
+ * ScatterOp, ArgSortOp, PrngOp), with the meaning their lowering gives them
+ * (pmlc/conversion/linalg_to_pxa/tile_to_pxa_special_patterns.cc, pmlc/rt/prng.cc).  Tensors are dense row-major.
+ *
+ * gather   normal: out[o.., j.., i..] = tensor[o.., indices[j..], i..] along `axis` (out = tensor dims before the
+ *          axis, the dims of indices, tensor dims after the axis).  Integer indices select; float indices
+ *          interpolate (nearest with a rounding rule, linear, cubic with `cube_coeff`) in the tensor's float type,
+ *          rounding after every operation, between neighbours clamped to the axis; out_of_bounds = 1 returns 0 for
+ *          an index outside [0, len - 1].  A float index into an integer tensor is truncated.
+ *          nd: the last dim of indices (K entries) addresses dims [batch_dims, batch_dims + K) of the tensor; the
+ *          first batch_dims dims of indices and tensor run together.
+ *          An integer index outside the axis selects the nearest edge (the reference reads out of bounds there).
+ * scatter  out = data, then for every element of updates: out[dst] += u (mode 0) or out[dst] = u (modes 1..3), dst
+ *          built from the element's coordinates with the `axis` coordinate (or, mode 3, the first K coordinates)
+ *          replaced by entries of indices: mode 0 / 2 index with the first idx_rank coordinates of the element,
+ *          mode 1 with the idx_rank coordinates from `axis` on (which collapse into one), mode 3 with the first
+ *          idx_rank - 1 coordinates and the K = last-dim entries of indices.  An update that lands outside data is
+ *          dropped.  Equal destinations: sums accumulate atomically (in any order); with an assigning mode one of
+ *          the updates stays.
+ * argsort  int32 positions that sort the tensor along `axis`, ties in their original order (mode 0 ascending,
+ *          1 descending).
+ * prng     `state` holds three uint32 words of a combined Tausworthe generator; out0[i] = (s0 ^ s1 ^ s2) / 2^32 as
+ *          f32 for i in element order, the words stepping once per element; out1 = state with its first three
+ *          words replaced by the generator's words after the last element.  Computed in parallel by jumping each
+ *          thread's generator ahead with precomputed powers of the step matrices.
+ */
+#define PMLB_SPECIAL_GATHER 0
+#define PMLB_SPECIAL_SCATTER 1
+#define PMLB_SPECIAL_ARGSORT 2
+#define PMLB_SPECIAL_PRNG 3
+
+typedef struct {
+  int32_t op;                        /* PMLB_SPECIAL_* */
+  int32_t dtype;                     /* gather / argsort: the tensor; scatter: data, updates and result */
+  int32_t idx_dtype;                 /* gather / scatter: the indices */
+  int32_t rank, idx_rank, upd_rank;
+  int64_t sizes[PMLB_MAX_RANK];      /* gather / argsort: the tensor; scatter: data; prng: the result */
+  int64_t idx_sizes[PMLB_MAX_RANK];
+  int64_t upd_sizes[PMLB_MAX_RANK];  /* scatter: updates */
+  int32_t axis;
+  int32_t mode;                      /* gather: 0 normal, 1 nd; scatter: 0 add, 1 slice, 2 element, 3 nd;
+                                        argsort: 0 ascending, 1 descending */
+  int32_t batch_dims;                /* gather nd */
+  int32_t interpolation;             /* gather: 0 nearest, 1 linear, 2 cubic, 3 none */
+  int32_t nearest;                   /* 0 round (half down), 1 round (half up), 2 floor, 3 ceil, 4 truncate */
+  int32_t out_of_bounds;             /* 0 clamp to the edge, 1 return zero */
+  double cube_coeff;
+  int64_t state_elems;               /* prng: elements of the state tensor (>= 3) */
+} pmlb_special_desc;
+
+/* Elements of the result the descriptor implies (0 if the descriptor is inconsistent). */
+int64_t pmlb_special_out_elems(const pmlb_special_desc* desc);
+pmlb_status pmlb_special_dispatch(const pmlb_special_desc* desc, pmlb_plan** plan);
+/* gather: in0 tensor, in1 indices -> out0.  scatter: in0 data, in1 indices, in2 updates -> out0.
+ * argsort: in0 tensor -> out0 (int32).  prng: in0 state -> out0 (f32), out1 (new state, uint32); one of the two
+ * may be null, and then only the other is computed. */
+pmlb_status pmlb_special_invoke(pmlb_plan* plan, void* stream, const void* in0, const void* in1, const void* in2,
+                                void* out0, void* out1);
+
 #ifdef __cplusplus
 }
 #endif

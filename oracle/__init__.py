@@ -19,3 +19,4 @@ from .binding import (  # noqa: F401
     bf16_to_f32,
     f32_to_bf16,
 )
+from . import special  # noqa: F401,E402  (gather / scatter / argsort / prng, numpy)

@@ -5,6 +5,7 @@
 // Scope: the operations that build the contraction path's networks and tests -- convolution
 // (forward, ungrouped), pool, dot, relu, mean / sum / max / min / prod, softmax -- plus the
 // thin element-wise and layout ones that cost a few lines each.
+#include <array>
 #include <functional>
 #include <map>
 #include <set>
@@ -984,6 +985,174 @@ VarPtr opConcatenate(const VarPtr& value) {
   return exprValue(concatExprs(tensors, asInt(args[1])));
 }
 
+// ------------------------------------------------------------------ gather / sort family
+
+VarPtr intValue(int64_t i) {
+  auto v = std::make_shared<VarNode>();
+  v->kind = VarNode::Int;
+  v->i = i;
+  return v;
+}
+
+VarPtr tupleValue(std::vector<VarPtr> items) {
+  auto v = std::make_shared<VarNode>();
+  v->kind = VarNode::Tuple;
+  v->tuple = std::move(items);
+  return v;
+}
+
+VarPtr intTupleValue(const std::vector<int64_t>& items) {
+  std::vector<VarPtr> vs;
+  for (int64_t i : items) vs.push_back(intValue(i));
+  return tupleValue(std::move(vs));
+}
+
+// index(dims, axis): a tensor of shape `dims` whose elements are their own coordinate along `axis`
+ExprPtr indexExpr(const std::vector<int64_t>& dims, int64_t axis) {
+  std::vector<ExprPtr> args = {litInt(axis)};
+  for (int64_t d : dims) args.push_back(litInt(d));
+  return intrinsic("index", args);
+}
+
+// The gather intrinsic with its nine operands (plaidml/edsl/edsl.h:1645-1690); interpolation 3 = none.
+ExprPtr gatherExpr(const ExprPtr& x, const ExprPtr& y, int64_t axis, int64_t interpolation = 3, int64_t nearest = 0,
+                   double cubeCoeff = -0.75, int64_t mode = 0, int64_t batchDims = 0, int64_t outOfBounds = 0) {
+  return intrinsic("gather", {x, y, litInt(axis), litInt(interpolation), litInt(nearest), litFloat(cubeCoeff), litInt(mode),
+                              litInt(batchDims), litInt(outOfBounds)});
+}
+
+VarPtr opUnsqueeze(const VarPtr& value);
+VarPtr opSqueeze(const VarPtr& value);
+VarPtr opExplicitPadding(const VarPtr& value);
+VarPtr opBroadcast(const VarPtr& value);
+
+ExprPtr unsqueezeExpr(const ExprPtr& I, const std::vector<int64_t>& axes) {
+  return opUnsqueeze(tupleValue({exprValue(I), intTupleValue(axes)}))->expr;
+}
+
+ExprPtr squeezeExpr(const ExprPtr& I, const std::vector<int64_t>& axes) {
+  return opSqueeze(tupleValue({exprValue(I), intTupleValue(axes)}))->expr;
+}
+
+// plaidml/op/lib/ops.cc:1728-1801.  Without interpolation: the gather intrinsic in nd mode.  LINEAR: the data is
+// zero-padded by two along every addressed dim, and the 2^K corners around each (float) index row are gathered
+// and blended.
+ExprPtr gatherNDExpr(const ExprPtr& I, const ExprPtr& idx, int64_t batchDims, int64_t interpolation) {
+  const pml::TensorShape iShape = shapeOf(I);
+  const pml::TensorShape idxShape = shapeOf(idx);
+  if (idxShape.rank() == 0) throw std::runtime_error("gatherND: indices need at least one dimension");
+  const int64_t rank = static_cast<int64_t>(iShape.rank());
+  const int64_t k = idxShape.sizes.back();
+  if (k + batchDims > rank) {
+    throw std::runtime_error("Invalid Indices: Data(shape: '" + iShape.str() + "'), Indices(shape: '" + idxShape.str() +
+                             "'), BatchDims('" + std::to_string(batchDims) + "')");
+  }
+  if (interpolation == 3) return gatherExpr(I, idx, 0, interpolation, 0, -0.75, 1, batchDims, 0);
+  if (interpolation != 1) throw std::runtime_error("Unsupported InterpolationMode in gatherND");
+  const int64_t padLength = 2;
+  std::vector<int64_t> pads(rank, 0);
+  for (int64_t i = 0; i < k; ++i) pads[i + batchDims] = padLength;
+  ExprPtr X = opExplicitPadding(tupleValue({exprValue(I), intTupleValue(pads), intTupleValue(pads), intValue(0),
+                                            exprValue(litInt(0))}))->expr;
+  ExprPtr Y = binary("add", idx, litInt(padLength));
+  if (static_cast<int64_t>(idxShape.rank()) - batchDims != 2) {
+    throw std::runtime_error(
+        " Indices dimension should be batch_dims plus two in interpolated gatherND, please reshape indices to satisfy this "
+        "requirement.");
+  }
+  ExprPtr Yf = castTo(Y, pml::DType::f32);
+  const int64_t lastAxis = static_cast<int64_t>(idxShape.rank()) - 1;
+  std::vector<ExprPtr> dims;
+  std::vector<std::array<ExprPtr, 2>> bounds;
+  for (int64_t i = 0; i < k; ++i) {
+    ExprPtr at = binary("add", castTo(indexExpr({1}, 0), pml::DType::si32), litInt(i));
+    ExprPtr dim = gatherExpr(Yf, at, lastAxis);
+    dims.push_back(dim);
+    ExprPtr lo = intrinsic("floor", {dim});
+    bounds.push_back({lo, binary("add", intrinsic("floor", {dim}), litFloat(1.0))});
+  }
+  ExprPtr zero = castTo(indexExpr({1}, 0), pml::DType::f32);
+  ExprPtr result = zero;
+  const int64_t corners = int64_t{1} << k;
+  for (int64_t i = 0; i < corners; ++i) {
+    std::vector<ExprPtr> corner;
+    ExprPtr coeff = binary("add", zero, litInt(1));
+    int64_t j = i;
+    for (int64_t d = 0; d < k; ++d, j /= 2) {
+      const int side = static_cast<int>(j % 2);
+      corner.push_back(bounds[d][side]);
+      coeff = side == 0 ? binary("mul", coeff, squeezeExpr(binary("sub", bounds[d][1], dims[d]), {-1}))
+                        : binary("mul", coeff, squeezeExpr(binary("sub", dims[d], bounds[d][0]), {-1}));
+    }
+    ExprPtr cornerIdx = castTo(concatExprs(corner, -1), pml::DType::si32);
+    ExprPtr vertex = gatherNDExpr(X, cornerIdx, batchDims, 3);
+    const pml::TensorShape vShape = shapeOf(vertex);
+    std::vector<int64_t> axes;
+    for (size_t a = 0; a < shapeOf(coeff).rank(); ++a) axes.push_back(static_cast<int64_t>(a));
+    ExprPtr wide = opBroadcast(tupleValue({exprValue(coeff), intTupleValue(vShape.sizes), intTupleValue(axes)}))->expr;
+    result = binary("add", result, binary("mul", vertex, wide));
+  }
+  return result;
+}
+
+VarPtr opGatherND(const VarPtr& value) {
+  const auto& args = asTuple(value, "gatherND");
+  if (args.size() != 4) throw std::runtime_error("gatherND expects 4 arguments");
+  return exprValue(gatherNDExpr(asTensor(args[0]), asTensor(args[1]), asInt(args[2]), asInt(args[3])));
+}
+
+// plaidml/op/lib/ops.cc:3100-3127: the sorted positions along the axis, the element's own coordinates elsewhere,
+// joined into index rows for gatherND
+ExprPtr sortExpr(const ExprPtr& I, int64_t rawAxis, int64_t direction) {
+  if (direction != 0 && direction != 1) throw std::runtime_error("Invalid sort direction");
+  const pml::TensorShape shape = shapeOf(I);
+  const int64_t nd = static_cast<int64_t>(shape.rank());
+  const int64_t axis = normalizeAxis(rawAxis, shape.rank(), "sort");
+  std::vector<ExprPtr> parts;
+  for (int64_t i = 0; i < nd; ++i) {
+    if (i == axis) parts.push_back(unsqueezeExpr(intrinsic("argsort", {I, litInt(axis), litInt(direction)}), {nd}));
+    else parts.push_back(unsqueezeExpr(indexExpr(shape.sizes, i), {nd}));
+  }
+  return gatherNDExpr(I, concatExprs(parts, -1), 0, 3);
+}
+
+VarPtr opSort(const VarPtr& value) {
+  const auto& args = asTuple(value, "sort");
+  if (args.size() != 3) throw std::runtime_error("sort expects 3 arguments");
+  return exprValue(sortExpr(asTensor(args[0]), asInt(args[1]), asInt(args[2])));
+}
+
+// plaidml/op/lib/ops.cc:2420-2467: the first k sorted values and their positions; with sort type INDEX (1) the
+// positions are put in ascending order and the values follow them
+VarPtr opTopk(const VarPtr& value) {
+  const auto& args = asTuple(value, "topk");
+  if (args.size() != 6) throw std::runtime_error("topk expects 6 arguments");
+  ExprPtr I = asTensor(args[0]);
+  const int64_t k = asInt(args[1]);
+  const int64_t rawAxis = asInt(args[2]);
+  const int64_t direction = asInt(args[3]);
+  const int64_t sortType = asInt(args[4]);
+  if (direction != 0 && direction != 1) throw std::runtime_error("Invalid sort direction");
+  const pml::TensorShape shape = shapeOf(I);
+  const int64_t nd = static_cast<int64_t>(shape.rank());
+  const int64_t axis = normalizeAxis(rawAxis, shape.rank(), "topk");
+  ExprPtr values = sortExpr(I, axis, direction);
+  ExprPtr positions = intrinsic("argsort", {I, litInt(axis), litInt(direction)});
+  ExprPtr firstK = indexExpr({k}, 0);
+  ExprPtr topPositions = gatherExpr(positions, firstK, axis);
+  if (sortType == 0) return tupleValue({exprValue(gatherExpr(values, firstK, axis)), exprValue(topPositions)});
+  if (sortType != 1) throw std::runtime_error("invalid topk sort type");
+  ExprPtr ordered = sortExpr(topPositions, axis, 0);
+  const pml::TensorShape topShape = shapeOf(topPositions);
+  std::vector<ExprPtr> parts;
+  for (int64_t i = 0; i < nd; ++i) {
+    if (i == axis) parts.push_back(unsqueezeExpr(ordered, {nd}));
+    else parts.push_back(unsqueezeExpr(indexExpr(topShape.sizes, i), {nd}));
+  }
+  ExprPtr topValues = gatherNDExpr(I, concatExprs(parts, -1), 0, 3);
+  return tupleValue({exprValue(topValues), exprValue(ordered)});
+}
+
 // plaidml/op/lib/ops.cc:1469-1488
 VarPtr opCumprod(const VarPtr& value) {
   const auto& args = asTuple(value, "cumprod");
@@ -1392,6 +1561,9 @@ const std::map<std::string, std::function<VarPtr(const VarPtr&)>>& registry() {
       {"flip", opFlip},
       {"max", [](const VarPtr& v) { return reduceOp(v, pml::AggKind::max, "max"); }},
       {"maximum", opMaximum},
+      {"gatherND", opGatherND},
+      {"sort", opSort},
+      {"topk", opTopk},
       {"mean", opMean},
       {"min", [](const VarPtr& v) { return reduceOp(v, pml::AggKind::min, "min"); }},
       {"minimum", opMinimum},

@@ -297,8 +297,86 @@ std::vector<TensorShape> Evaluator::computeShapes(const ExprNode* node) {
         }
         return {TensorShape(dt, s.sizes)};
       }
-      if (op == "argsort" || op == "gather" || op == "scatter" || op == "prng") {
-        throw std::runtime_error("'" + op + "' is not a contraction and is not offered by the cuda target");
+      // the four operations that are not contractions (pmlc/ast/ast_ops.cc:54-72,101-264)
+      auto integerOperand = [&](size_t i, int64_t* v) { return getIntegerValue(this, node->operands[i], v); };
+      if (op == "argsort") {
+        int64_t v;
+        if (node->operands.size() != 3) throw std::runtime_error("'argsort' requires 3 arguments.");
+        if (!integerOperand(1, &v)) throw std::runtime_error("'argsort' requires operand #2 to be an integer.");
+        if (!integerOperand(2, &v)) throw std::runtime_error("'argsort' requires operand #3 to be an integer.");
+        return {TensorShape(DType::si32, shapes[0].sizes)};
+      }
+      if (op == "gather") {
+        if (node->operands.size() != 9) throw std::runtime_error("'gather' requires nine arguments.");
+        const TensorShape& tensor = shapes[0];
+        const TensorShape& idxs = shapes[1];
+        const int64_t rank = static_cast<int64_t>(tensor.rank());
+        if (!rank) throw std::runtime_error("'gather' requires first operand to have at least one dimension.");
+        int64_t axis, interpolation, nearest, mode, batchDims, outOfBounds;
+        if (!integerOperand(2, &axis) || axis >= rank || axis < 0) {
+          throw std::runtime_error(
+              "'gather' primitive expects the 'axis' argument to be a positive integer that is less than the tensor rank.");
+        }
+        if (!integerOperand(3, &interpolation)) {
+          throw std::runtime_error("'gather' primitive expects the 'interpolationMode' argument to be a constant integer");
+        }
+        if (!integerOperand(4, &nearest)) {
+          throw std::runtime_error("'gather' primitive expects the 'nearestMode' argument to be a constant integer");
+        }
+        if (node->operands[5]->kind != ExprNode::ConstFloat) {
+          throw std::runtime_error("'gather' primitive expects the 'cubeCoeff' argument to be a constant float");
+        }
+        if (!integerOperand(6, &mode)) {
+          throw std::runtime_error("'gather' primitive expects the 'mode' argument to be a constant integer");
+        }
+        if (mode == 1 && (isFloat(idxs.dtype) || idxs.dtype == DType::i1 || idxs.dtype == DType::invalid)) {
+          throw std::runtime_error("'gather' ND mode requires indices elements to be integers.");
+        }
+        if (!integerOperand(7, &batchDims)) {
+          throw std::runtime_error("'gather' primitive expects the 'batchDims' argument to be a constant integer");
+        }
+        if (!integerOperand(8, &outOfBounds)) {
+          throw std::runtime_error("'gather' primitive expects the 'outOfBoundsMode' argument to be a constant integer");
+        }
+        TensorShape ret(tensor.dtype);
+        if (mode == 0) {
+          for (int64_t i = 0; i < axis; ++i) ret.sizes.push_back(tensor.sizes[i]);
+          ret.sizes.insert(ret.sizes.end(), idxs.sizes.begin(), idxs.sizes.end());
+          for (int64_t i = axis + 1; i < rank; ++i) ret.sizes.push_back(tensor.sizes[i]);
+        } else {
+          if (idxs.rank() < 1) throw std::runtime_error("'gather' ND mode requires indices of at least one dimension.");
+          for (size_t i = 0; i + 1 < idxs.rank(); ++i) ret.sizes.push_back(idxs.sizes[i]);
+          for (int64_t i = idxs.sizes.back() + batchDims; i < rank; ++i) ret.sizes.push_back(tensor.sizes[i]);
+        }
+        return {ret};
+      }
+      if (op == "prng") {
+        if (node->operands.empty()) throw std::runtime_error("'prng' requires at least one argument.");
+        TensorShape ret(DType::f32);
+        for (size_t i = 1; i < node->operands.size(); ++i) {
+          int64_t v;
+          if (!integerOperand(i, &v)) throw std::runtime_error("'prng' has invalid operands, dims must be tensor dimensions");
+          ret.sizes.push_back(v);
+        }
+        return {ret, shapes[0]};
+      }
+      if (op == "scatter") {
+        if (node->operands.size() != 5) throw std::runtime_error("'scatter' requires 5 operands.");
+        const int64_t rank = static_cast<int64_t>(shapes[0].rank());
+        if (!rank) throw std::runtime_error("'scatter' requires operand #1 to have at least one dimension.");
+        if (shapes[1].dtype != DType::si32 && shapes[1].dtype != DType::ui32) {
+          throw std::runtime_error("'scatter' requires operand #2 to be an integer.");
+        }
+        int64_t axis, mode;
+        if (!integerOperand(3, &axis) || axis >= rank) {
+          throw std::runtime_error(
+              "'scatter' primitive expects the 'axis' argument to be a positive integer that is less than the updates "
+              "tensor rank.");
+        }
+        if (!integerOperand(4, &mode)) {
+          throw std::runtime_error("'scatter' primitive expects the 'mode' argument to be a constant integer.");
+        }
+        return {TensorShape(shapes[0].dtype, shapes[0].sizes)};
       }
       return {inferShape(shapes)};
     }

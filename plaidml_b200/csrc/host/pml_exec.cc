@@ -181,6 +181,10 @@ class Planner {
           pd.kind = Pending::Eltwise;
           pd.inputs = op.operands;
           break;
+        case POp::Special:
+          pd.kind = Pending::Special;
+          pd.inputs = op.operands;
+          break;
       }
       pending_.push_back(std::move(pd));
     }
@@ -224,7 +228,7 @@ class Planner {
 
  private:
   struct Pending {
-    enum Kind { Gemm, Conv, Reduce, Pool, Generic, Eltwise } kind = Generic;
+    enum Kind { Gemm, Conv, Reduce, Pool, Generic, Eltwise, Special } kind = Generic;
     int op = -1;
     int position = -1;          // program position the step runs at: its last fused operation
     int result = -1;            // value the step writes (after fused consumers)
@@ -1249,6 +1253,9 @@ class Planner {
       case Pending::Eltwise:
         emitEltwise(pd);
         return;
+      case Pending::Special:
+        emitSpecial(pd);
+        return;
     }
     exe_->steps_.push_back(std::move(st));
   }
@@ -1423,6 +1430,93 @@ class Planner {
     const void* i1 = ins[1];
     const void* i2 = ins[2];
     st.launch = [plan, i0, i1, i2, out](cudaStream_t s) { return pmlb_eltwise_invoke(plan, s, i0, i1, i2, out); };
+    exe_->steps_.push_back(std::move(st));
+  }
+
+  // gather / scatter / argsort / prng: one descriptor each, no fusion with their neighbours.
+  void emitSpecial(const Pending& pd) {
+    const POp& op = prog_.ops[pd.op];
+    const PSpecial& sp = *op.s;
+    const TensorShape& outShape = val(op.result).shape;
+    pmlb_special_desc d;
+    std::memset(&d, 0, sizeof(d));
+    auto sizes = [&](const TensorShape& shape, int32_t* rank, int64_t* into) {
+      if (shape.rank() > PMLB_MAX_RANK) throw std::runtime_error("Tensors of rank above 8 are not supported");
+      *rank = static_cast<int32_t>(shape.rank());
+      for (size_t i = 0; i < shape.rank(); ++i) into[i] = shape.sizes[i];
+    };
+    const TensorShape& first = val(op.operands[0]).shape;
+    const void* in0 = dev(op.operands[0]);
+    const void* in1 = op.operands.size() > 1 ? dev(op.operands[1]) : nullptr;
+    const void* in2 = op.operands.size() > 2 ? dev(op.operands[2]) : nullptr;
+    void* out0 = dev(op.result);
+    void* out1 = nullptr;
+    switch (sp.op) {
+      case PSpecial::Gather:
+        d.op = PMLB_SPECIAL_GATHER;
+        d.dtype = static_cast<int32_t>(first.dtype);
+        d.idx_dtype = static_cast<int32_t>(val(op.operands[1]).shape.dtype);
+        sizes(first, &d.rank, d.sizes);
+        sizes(val(op.operands[1]).shape, &d.idx_rank, d.idx_sizes);
+        d.axis = static_cast<int32_t>(sp.axis);
+        d.mode = static_cast<int32_t>(sp.mode);
+        d.batch_dims = static_cast<int32_t>(sp.batchDims);
+        d.interpolation = static_cast<int32_t>(sp.interpolation);
+        d.nearest = static_cast<int32_t>(sp.nearest);
+        d.out_of_bounds = static_cast<int32_t>(sp.outOfBounds);
+        d.cube_coeff = sp.cubeCoeff;
+        break;
+      case PSpecial::Scatter:
+        d.op = PMLB_SPECIAL_SCATTER;
+        d.dtype = static_cast<int32_t>(first.dtype);
+        d.idx_dtype = static_cast<int32_t>(val(op.operands[1]).shape.dtype);
+        sizes(first, &d.rank, d.sizes);
+        sizes(val(op.operands[1]).shape, &d.idx_rank, d.idx_sizes);
+        sizes(val(op.operands[2]).shape, &d.upd_rank, d.upd_sizes);
+        d.axis = static_cast<int32_t>(sp.axis);
+        d.mode = static_cast<int32_t>(sp.mode);
+        break;
+      case PSpecial::ArgSort:
+        d.op = PMLB_SPECIAL_ARGSORT;
+        d.dtype = static_cast<int32_t>(first.dtype);
+        sizes(first, &d.rank, d.sizes);
+        d.axis = static_cast<int32_t>(sp.axis < 0 ? sp.axis + static_cast<int64_t>(first.rank()) : sp.axis);
+        d.mode = static_cast<int32_t>(sp.mode);
+        break;
+      case PSpecial::Prng:
+        d.op = PMLB_SPECIAL_PRNG;
+        sizes(outShape, &d.rank, d.sizes);
+        d.state_elems = first.elements();
+        break;
+      case PSpecial::PrngState: {
+        // the state after the numbers of the paired operation: the same generator, nothing written but the state
+        d.op = PMLB_SPECIAL_PRNG;
+        TensorShape numbers(DType::f32, sp.dims);
+        sizes(numbers, &d.rank, d.sizes);
+        d.state_elems = first.elements();
+        out1 = out0;
+        out0 = nullptr;
+        break;
+      }
+    }
+    pmlb_plan* plan = nullptr;
+    pmlbCheck(pmlb_special_dispatch(&d, &plan), "dispatch of '" + op.mnemonic + "'");
+    if (sp.op != PSpecial::PrngState && pmlb_special_out_elems(&d) != outShape.elements()) {
+      pmlb_plan_free(plan);
+      throw std::runtime_error("'" + op.mnemonic + "': result shape " + outShape.str() + " does not follow from its operands");
+    }
+    Step st;
+    st.plan = plan;
+    st.kernel = op.mnemonic;
+    st.detail = op.mnemonic + " -> " + outShape.str();
+    if (sp.op == PSpecial::ArgSort) {
+      int passes = 0;
+      while ((int64_t{1} << passes) < first.sizes[d.axis]) ++passes;
+      st.launches = passes > 0 ? passes : 1;
+    }
+    st.launch = [plan, in0, in1, in2, out0, out1](cudaStream_t s) {
+      return pmlb_special_invoke(plan, s, in0, in1, in2, out0, out1);
+    };
     exe_->steps_.push_back(std::move(st));
   }
 

@@ -528,7 +528,7 @@ std::string Program::mlir() const {
   static const char* aggNames[] = {"assign", "add", "max", "min", "mul"};
   static const char* comboNames[] = {"none", "add", "cond", "eq", "mul"};
   std::ostringstream head;
-  size_t nargs = 0, nres = 0, ncst = 0;
+  size_t nargs = 0, nres = 0, ncst = 0, nprng = 0;
 
   // One region of the printed program: the function body or the body of a layer.  Names are per region
   // (a layer's body sees only its block arguments and what it defines itself).
@@ -647,6 +647,42 @@ std::string Program::mlir() const {
       return;
     }
     for (int id : op.operands) args.push_back(use(rg, id));
+    if (op.kind == POp::Special) {
+      const PSpecial& sp = *op.s;
+      if (sp.op == PSpecial::PrngState) return;  // printed with the operation that gives the numbers
+      auto types = [&]() {
+        body << " : (";
+        for (size_t i = 0; i < op.operands.size(); ++i) body << (i ? ", " : "") << values[op.operands[i]].shape.str();
+        body << ") -> ";
+      };
+      if (sp.op == PSpecial::Prng) {
+        const POp& tail = ops[sp.pair];
+        const std::string suffix = nprng == 0 ? "" : "_" + std::to_string(nprng - 1);
+        ++nprng;
+        rg.local[op.result] = "%result" + suffix;
+        rg.local[tail.result] = "%new_state" + suffix;
+        body << rg.indent << rg.local[op.result] << ", " << rg.local[tail.result] << " = tile.prng " << args[0];
+        types();
+        body << "(" << values[op.result].shape.str() << ", " << values[tail.result].shape.str() << ")\n";
+        return;
+      }
+      rg.local[op.result] = "%" + std::to_string(nres++);
+      body << rg.indent << rg.local[op.result] << " = tile." << op.mnemonic << " ";
+      if (sp.op == PSpecial::ArgSort) {
+        body << (sp.mode ? "desc " : "asc ") << args[0] << "[" << sp.axis << "]";
+      } else if (sp.op == PSpecial::Gather) {
+        body << args[0] << " " << args[1] << " {OutOfBoundsMode = " << sp.outOfBounds << " : i64, axis = " << sp.axis
+             << " : index, batchDims = " << sp.batchDims << " : index, cubeCoeff = " << mlirFloat(sp.cubeCoeff)
+             << " : f64, interpolationMode = " << sp.interpolation << " : i64, mode = " << sp.mode
+             << " : i64, nearestMode = " << sp.nearest << " : i64}";
+      } else {
+        body << args[0] << " " << args[1] << " " << args[2] << " {axis = " << sp.axis << " : index, mode = " << sp.mode
+             << " : i64}";
+      }
+      types();
+      body << values[op.result].shape.str() << "\n";
+      return;
+    }
     rg.local[op.result] = "%" + std::to_string(nres++);
     if (op.mnemonic == "pragma") {
       body << rg.indent << rg.local[op.result] << " = tile.pragma " << args[0] << " \"" << op.label << "\" {" << op.attrs
@@ -997,8 +1033,14 @@ class Builder {
           if (e->ordinal >= src->results.size()) throw std::runtime_error("Out of bounds element ordinal");
           return lower(src->results[e->ordinal]);
         }
+        if (src->kind == ExprNode::Intrinsic && src->op == "prng") {
+          if (e->ordinal > 1) throw std::runtime_error("Out of bounds element ordinal");
+          const int numbers = lower(src);
+          if (e->ordinal == 0) return numbers;
+          return prog_->ops[prog_->ops[prog_->values[numbers].def].s->pair].result;
+        }
         if (e->ordinal == 0) return lower(src);
-        throw std::runtime_error("Only layers have multiple results on the cuda target");
+        throw std::runtime_error("Out of bounds element ordinal");
       }
       case ExprNode::Layer:
         if (e->results.size() == 1) return lower(e->results[0]);
@@ -1074,8 +1116,9 @@ class Builder {
   }
 
   int lowerIntrinsic(const ExprPtr& e) {
-    const TensorShape shape = ev.getShape(e);
     const std::string& name = e->op;
+    if (name == "prng") return lowerSpecial(e, TensorShape());  // (two results: it reads both shapes itself)
+    const TensorShape shape = ev.getShape(e);
     if (name == "index") {
       int64_t axis = 0;
       if (!getIntegerValue(&ev, e->operands[0], &axis) || axis < 0) {
@@ -1133,6 +1176,7 @@ class Builder {
       op.operands = {src};
       return emit(op, shape);
     }
+    if (name == "argsort" || name == "gather" || name == "scatter") return lowerSpecial(e, shape);
     // element-wise
     std::vector<int> ids;
     DType promoted = DType::invalid;
@@ -1171,6 +1215,85 @@ class Builder {
       result.dtype = result.dtype == DType::fx ? DType::f32 : (result.dtype == DType::six ? DType::si32 : DType::ui32);
     }
     return emit(op, result);
+  }
+
+  int tensorOperand(const ExprPtr& e, const std::string& op) {
+    const int id = lower(e);
+    if (prog_->values[id].kind == PValue::LiteralValue) {
+      throw std::runtime_error("'" + op + "' needs tensors, not scalar constants, as its data operands");
+    }
+    return id;
+  }
+
+  // argsort / gather / scatter / prng; the operands after the tensors are compile-time constants
+  // (pmlc/ast/builder.cc:685-690 and the make*Op functions they name).
+  int lowerSpecial(const ExprPtr& e, const TensorShape& shape) {
+    const std::string& name = e->op;
+    auto constant = [&](size_t i) {
+      int64_t v = 0;
+      getIntegerValue(&ev, e->operands[i], &v);
+      return v;
+    };
+    POp op;
+    op.kind = POp::Special;
+    op.mnemonic = name;
+    op.label = e->name;
+    op.s = std::make_shared<PSpecial>();
+    if (name == "argsort") {
+      op.s->op = PSpecial::ArgSort;
+      op.s->axis = constant(1);
+      op.s->mode = constant(2);
+      const int64_t rank = static_cast<int64_t>(shape.rank());
+      if (op.s->axis < -rank || op.s->axis >= rank) throw std::runtime_error("'argsort' axis is outside the tensor's dimensions");
+      if (op.s->mode != 0 && op.s->mode != 1) throw std::runtime_error("'argsort' direction must be 0 (asc) or 1 (desc)");
+      op.operands = {tensorOperand(e->operands[0], name)};
+      return emit(op, shape);
+    }
+    if (name == "gather") {
+      op.s->op = PSpecial::Gather;
+      op.s->axis = constant(2);
+      op.s->interpolation = constant(3);
+      op.s->nearest = constant(4);
+      op.s->cubeCoeff = e->operands[5]->fvalue;
+      op.s->mode = constant(6);
+      op.s->batchDims = constant(7);
+      op.s->outOfBounds = constant(8);
+      op.operands = {tensorOperand(e->operands[0], name), tensorOperand(e->operands[1], name)};
+      return emit(op, shape);
+    }
+    if (name == "scatter") {
+      op.s->op = PSpecial::Scatter;
+      op.s->axis = constant(3);
+      op.s->mode = constant(4);
+      op.operands = {tensorOperand(e->operands[0], name), tensorOperand(e->operands[1], name),
+                     tensorOperand(e->operands[2], name)};
+      const DType dt = prog_->values[op.operands[0]].shape.dtype;
+      if (prog_->values[op.operands[2]].shape.dtype != dt) {
+        throw std::runtime_error("'scatter' needs data and updates of one element type, use a cast");
+      }
+      return emit(op, shape);
+    }
+    // prng: two operations over the same state
+    const std::vector<TensorShape> both = ev.getShapes(e.get());
+    const int state = tensorOperand(e->operands[0], name);
+    const TensorShape st = prog_->values[state].shape;
+    if (st.dtype != DType::ui32 && st.dtype != DType::si32) throw std::runtime_error("'prng' needs a state of 32-bit integers");
+    if (st.elements() < 3) throw std::runtime_error("'prng' needs a state of at least three words");
+    op.s->op = PSpecial::Prng;
+    op.operands = {state};
+    const int numbers = emit(op, both[0]);
+    const int first = prog_->values[numbers].def;
+    POp tail;
+    tail.kind = POp::Special;
+    tail.mnemonic = "prng_state";
+    tail.s = std::make_shared<PSpecial>();
+    tail.s->op = PSpecial::PrngState;
+    tail.s->pair = first;
+    tail.s->dims = both[0].sizes;
+    tail.operands = {state};
+    const int after = emit(tail, both[1]);
+    prog_->ops[first].s->pair = prog_->values[after].def;
+    return numbers;
   }
 
   Program* prog_;

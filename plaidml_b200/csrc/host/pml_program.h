@@ -67,9 +67,23 @@ struct PValue {
   int def = -1;         // defining op, -1 for arguments
 };
 
+// gather / scatter / argsort / prng: the tile operations that are not contractions
+// (pmlc/dialect/tile/ir/ops.td:97-191).  prng, the one operation with two results, is kept as two operations that
+// read the same state: Prng gives the numbers, PrngState the state after them; they print as one `tile.prng`.
+struct PSpecial {
+  enum Op { Gather, Scatter, ArgSort, Prng, PrngState } op = Gather;
+  int64_t axis = 0;           // argsort: as written (negative counts from the end)
+  int64_t mode = 0;           // gather: 0 along an axis, 1 nd; scatter: ScatterMode; argsort: 0 ascending, 1 descending
+  int64_t batchDims = 0, interpolation = 3, nearest = 0, outOfBounds = 0;
+  double cubeCoeff = -0.75;
+  int pair = -1;              // Prng: the PrngState operation; PrngState: the Prng operation
+  std::vector<int64_t> dims;  // PrngState: shape of the numbers generated
+};
+
 struct POp {
-  enum Kind { Contraction, Eltwise, Cast, Reshape } kind = Eltwise;
-  std::string mnemonic;  // eltwise op name ("add", "relu", ...), "cast", "reshape", "contract"
+  enum Kind { Contraction, Eltwise, Cast, Reshape, Special } kind = Eltwise;
+  std::shared_ptr<PSpecial> s;  // Special
+  std::string mnemonic;  // eltwise op name ("add", "relu", ...), "cast", "reshape", "contract", "gather", ...
   std::string label;     // user-given name (contraction / layer name); the pragma's name for "pragma"
   std::string attrs;     // "pragma": its attributes as printed, e.g. msg = "text"
   std::vector<int> operands;  // value ids; for contractions: sources then the init (if any)

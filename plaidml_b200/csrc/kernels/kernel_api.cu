@@ -13,6 +13,7 @@
 #include "prepass.h"
 #include "reduce.h"
 #include "s2d_pool.h"
+#include "special.h"
 #include "tc_gemm.cuh"
 #include "conv_route.h"
 #include "tc_launch.h"
@@ -80,7 +81,7 @@ bool have_sm100(std::string* why) {
 // launches logs its pipeline timeline to.
 long long* g_trace_buffer = nullptr;
 
-enum PlanKind { kPlanGemm, kPlanConv, kPlanReduce, kPlanPool, kPlanContract, kPlanEltwise };
+enum PlanKind { kPlanGemm, kPlanConv, kPlanReduce, kPlanPool, kPlanContract, kPlanEltwise, kPlanSpecial };
 
 }  // namespace
 
@@ -113,6 +114,7 @@ struct pmlb_plan {
   pmlb_pool_desc pool;
   pmlb::GenericParams generic;
   pmlb::EltwiseParams eltwise;
+  pmlb_special_desc special;
 };
 
 namespace {
@@ -1104,6 +1106,251 @@ pmlb_status pmlb_eltwise_invoke(pmlb_plan* plan, void* stream, const void* in0, 
   }
   cudaError_t e = pmlb::launch_eltwise(p, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "eltwise launch");
+  return PMLB_OK;
+}
+
+// ------------------------------------------------------------------ gather / scatter / argsort / prng
+
+namespace {
+
+int special_elem_bytes(int dtype) {
+  switch (dtype) {
+    case PMLB_BOOL:
+    case PMLB_I8:
+    case PMLB_U8: return 1;
+    case PMLB_I16:
+    case PMLB_U16:
+    case PMLB_F16:
+    case PMLB_BF16: return 2;
+    case PMLB_I32:
+    case PMLB_U32:
+    case PMLB_F32: return 4;
+    case PMLB_I64:
+    case PMLB_U64:
+    case PMLB_F64: return 8;
+    default: return 0;
+  }
+}
+
+bool special_is_float(int dtype) {
+  return dtype == PMLB_F16 || dtype == PMLB_BF16 || dtype == PMLB_F32 || dtype == PMLB_F64;
+}
+
+long long product(const int64_t* v, int from, int to) {
+  long long r = 1;
+  for (int i = from; i < to; ++i) r *= v[i];
+  return r;
+}
+
+// Empty string if the descriptor is consistent, else what is wrong with it.
+std::string special_problem(const pmlb_special_desc* d) {
+  auto ranks_ok = [](int r) { return r >= 0 && r <= PMLB_MAX_RANK; };
+  if (!ranks_ok(d->rank) || !ranks_ok(d->idx_rank) || !ranks_ok(d->upd_rank)) return "rank out of range";
+  for (int i = 0; i < d->rank; ++i) {
+    if (d->sizes[i] < 0) return "negative size";
+  }
+  switch (d->op) {
+    case PMLB_SPECIAL_GATHER: {
+      if (special_elem_bytes(d->dtype) == 0 || special_elem_bytes(d->idx_dtype) == 0) return "gather: bad element type";
+      if (d->rank < 1) return "gather: the tensor needs at least one dimension";
+      if (d->mode == 0) {
+        if (d->axis < 0 || d->axis >= d->rank) return "gather: axis outside the tensor's dimensions";
+        if (special_is_float(d->idx_dtype) && special_is_float(d->dtype)) {
+          if (d->interpolation < 0 || d->interpolation > 2) return "gather: float indices need an interpolation mode";
+          if (d->interpolation == 0 && (d->nearest < 0 || d->nearest > 4)) return "gather: unknown rounding rule";
+        }
+        if (d->out_of_bounds < 0 || d->out_of_bounds > 1) return "gather: unknown out-of-bounds rule";
+        return "";
+      }
+      if (d->mode != 1) return "gather: unknown mode";
+      if (special_is_float(d->idx_dtype)) return "gather: nd mode requires indices elements to be integers";
+      if (d->idx_rank < 1) return "gather: nd mode needs indices of at least one dimension";
+      const long long k = d->idx_sizes[d->idx_rank - 1];
+      if (d->batch_dims < 0 || d->batch_dims > d->idx_rank - 1 || k < 0 || k + d->batch_dims > d->rank) {
+        return "gather: indices address more dimensions than the tensor has";
+      }
+      for (int i = 0; i < d->batch_dims; ++i) {
+        if (d->idx_sizes[i] != d->sizes[i]) return "gather: batch dimensions of tensor and indices differ";
+      }
+      return "";
+    }
+    case PMLB_SPECIAL_SCATTER: {
+      if (special_elem_bytes(d->dtype) == 0) return "scatter: bad element type";
+      if (d->idx_dtype != PMLB_I32 && d->idx_dtype != PMLB_U32) return "scatter: indices must be 32-bit integers";
+      if (d->rank < 1 || d->idx_rank < 1) return "scatter: data and indices need at least one dimension";
+      if (d->mode < 0 || d->mode > 3) return "scatter: unknown mode";
+      int dst_rank;
+      if (d->mode == 3) {
+        if (d->upd_rank < d->idx_rank - 1) return "scatter: updates have fewer dimensions than the indices address";
+        dst_rank = static_cast<int>(d->idx_sizes[d->idx_rank - 1]) + d->upd_rank - (d->idx_rank - 1);
+        for (int i = 0; i < d->idx_rank - 1; ++i) {
+          if (d->upd_sizes[i] > d->idx_sizes[i]) return "scatter: updates run past the indices";
+        }
+      } else {
+        if (d->axis < 0 || d->axis >= d->rank) return "scatter: axis outside the data's dimensions";
+        const int first = d->mode == 1 ? d->axis : 0;
+        if (first + d->idx_rank > d->upd_rank) return "scatter: updates have fewer dimensions than the indices";
+        for (int i = 0; i < d->idx_rank; ++i) {
+          if (d->upd_sizes[first + i] > d->idx_sizes[i]) return "scatter: updates run past the indices";
+        }
+        dst_rank = d->mode == 1 ? d->upd_rank - d->idx_rank + 1 : d->upd_rank;
+      }
+      if (dst_rank != d->rank) return "scatter: updates and indices do not address the data's dimensions";
+      return "";
+    }
+    case PMLB_SPECIAL_ARGSORT: {
+      if (special_elem_bytes(d->dtype) == 0) return "argsort: bad element type";
+      if (d->rank < 1 || d->axis < 0 || d->axis >= d->rank) return "argsort: axis outside the tensor's dimensions";
+      if (d->mode < 0 || d->mode > 1) return "argsort: unknown direction";
+      if (d->sizes[d->axis] > 2147483647LL) return "argsort: positions do not fit 32 bits";
+      return "";
+    }
+    case PMLB_SPECIAL_PRNG: {
+      if (d->state_elems < 3) return "prng: the state needs three words";
+      if (product(d->sizes, 0, d->rank) >= (1LL << 32)) return "prng: more than 2^32 elements";
+      return "";
+    }
+    default: return "unknown operation";
+  }
+}
+
+}  // namespace
+
+int64_t pmlb_special_out_elems(const pmlb_special_desc* d) {
+  if (!d || !special_problem(d).empty()) return 0;
+  switch (d->op) {
+    case PMLB_SPECIAL_GATHER:
+      if (d->mode == 0) {
+        return product(d->sizes, 0, d->axis) * product(d->idx_sizes, 0, d->idx_rank) *
+               product(d->sizes, d->axis + 1, d->rank);
+      }
+      return product(d->idx_sizes, 0, d->idx_rank - 1) *
+             product(d->sizes, static_cast<int>(d->idx_sizes[d->idx_rank - 1]) + d->batch_dims, d->rank);
+    default: return product(d->sizes, 0, d->rank);
+  }
+}
+
+pmlb_status pmlb_special_dispatch(const pmlb_special_desc* d, pmlb_plan** out) {
+  if (!d || !out) return fail(PMLB_ERR_INVALID, "null argument");
+  *out = nullptr;
+  std::string why;
+  if (!have_sm100(&why)) return fail(PMLB_ERR_UNSUPPORTED, why);
+  const std::string problem = special_problem(d);
+  if (!problem.empty()) return fail(PMLB_ERR_INVALID, problem);
+  pmlb_plan* plan = new (std::nothrow) pmlb_plan();
+  if (!plan) return fail(PMLB_ERR_INVALID, "out of host memory");
+  plan->kind = kPlanSpecial;
+  static const char* const names[] = {"gather", "scatter", "argsort", "prng"};
+  plan->kind_name = names[d->op];
+  plan->special = *d;
+  size_t scratch = 0;
+  if (d->op == PMLB_SPECIAL_ARGSORT) scratch = static_cast<size_t>(product(d->sizes, 0, d->rank)) * sizeof(int32_t);
+  if (d->op == PMLB_SPECIAL_PRNG) scratch = pmlb::kPrngTableWords * sizeof(uint32_t);
+  pmlb_status st = alloc_plan_memory(plan, scratch, false);
+  if (st == PMLB_OK && d->op == PMLB_SPECIAL_PRNG) {
+    static uint32_t table[pmlb::kPrngTableWords];
+    static const bool filled = (pmlb::prng_jump_table(table), true);
+    (void)filled;
+    cudaError_t e = cudaMemcpy(plan->scratch, table, sizeof(table), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) st = cuda_fail(e, "cudaMemcpy(prng table)");
+  }
+  if (st != PMLB_OK) {
+    pmlb_plan_free(plan);
+    return st;
+  }
+  *out = plan;
+  return PMLB_OK;
+}
+
+pmlb_status pmlb_special_invoke(pmlb_plan* plan, void* stream_, const void* in0, const void* in1, const void* in2,
+                                void* out0, void* out1) {
+  if (!plan || plan->kind != kPlanSpecial) return fail(PMLB_ERR_INVALID, "not a gather / scatter / argsort / prng plan");
+  const pmlb_special_desc& d = plan->special;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  cudaError_t e = cudaSuccess;
+  switch (d.op) {
+    case PMLB_SPECIAL_GATHER: {
+      if (!in0 || !in1 || !out0) return fail(PMLB_ERR_INVALID, "gather: null tensor");
+      pmlb::GatherParams p{};
+      p.dtype = d.dtype;
+      p.idx_dtype = d.idx_dtype;
+      p.elem_bytes = special_elem_bytes(d.dtype);
+      p.nd = d.mode;
+      p.out_elems = pmlb_special_out_elems(&d);
+      p.interpolation = d.interpolation;
+      p.nearest = d.nearest;
+      p.out_of_bounds = d.out_of_bounds;
+      p.cube_coeff = d.cube_coeff;
+      if (d.mode == 0) {
+        p.axis_len = d.sizes[d.axis];
+        p.inner = product(d.sizes, d.axis + 1, d.rank);
+        p.n_idx = product(d.idx_sizes, 0, d.idx_rank);
+        if (p.axis_len == 0 && p.out_elems > 0) return fail(PMLB_ERR_INVALID, "gather: nothing to gather from");
+      } else {
+        p.k = static_cast<int>(d.idx_sizes[d.idx_rank - 1]);
+        for (int i = 0; i < p.k; ++i) {
+          p.dims[i] = d.sizes[d.batch_dims + i];
+          if (p.dims[i] == 0 && p.out_elems > 0) return fail(PMLB_ERR_INVALID, "gather: nothing to gather from");
+        }
+        p.inner = product(d.sizes, d.batch_dims + p.k, d.rank);
+        p.rows_per_batch = product(d.idx_sizes, d.batch_dims, d.idx_rank - 1);
+      }
+      p.tensor = in0;
+      p.indices = in1;
+      p.out = out0;
+      e = pmlb::launch_gather(p, stream);
+      break;
+    }
+    case PMLB_SPECIAL_SCATTER: {
+      if (!in0 || !in1 || !in2 || !out0) return fail(PMLB_ERR_INVALID, "scatter: null tensor");
+      pmlb::ScatterParams p{};
+      p.dtype = d.dtype;
+      p.idx_dtype = d.idx_dtype;
+      p.elem_bytes = special_elem_bytes(d.dtype);
+      p.mode = d.mode;
+      p.axis = d.axis;
+      p.rank = d.rank;
+      p.idx_rank = d.idx_rank;
+      p.upd_rank = d.upd_rank;
+      for (int i = 0; i < PMLB_MAX_RANK; ++i) {
+        p.sizes[i] = d.sizes[i];
+        p.idx_sizes[i] = d.idx_sizes[i];
+        p.upd_sizes[i] = d.upd_sizes[i];
+      }
+      p.upd_elems = product(d.upd_sizes, 0, d.upd_rank);
+      p.indices = in1;
+      p.updates = in2;
+      p.out = out0;
+      const size_t bytes = static_cast<size_t>(product(d.sizes, 0, d.rank)) * p.elem_bytes;
+      if (bytes > 0 && out0 != in0) {
+        e = cudaMemcpyAsync(out0, in0, bytes, cudaMemcpyDeviceToDevice, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "scatter copy");
+      }
+      e = pmlb::launch_scatter(p, stream);
+      break;
+    }
+    case PMLB_SPECIAL_ARGSORT: {
+      if (!in0 || !out0) return fail(PMLB_ERR_INVALID, "argsort: null tensor");
+      pmlb::ArgsortParams p{};
+      p.dtype = d.dtype;
+      p.descending = d.mode;
+      p.outer = product(d.sizes, 0, d.axis);
+      p.n = d.sizes[d.axis];
+      p.inner = product(d.sizes, d.axis + 1, d.rank);
+      p.tensor = in0;
+      e = pmlb::launch_argsort(p, static_cast<int32_t*>(out0), static_cast<int32_t*>(plan->scratch), stream);
+      break;
+    }
+    default: {
+      // either result may be left out: the numbers alone, or only the state after them
+      if (!in0 || (!out0 && !out1)) return fail(PMLB_ERR_INVALID, "prng: null tensor");
+      e = pmlb::launch_prng(static_cast<const uint32_t*>(in0), d.state_elems, static_cast<float*>(out0),
+                            product(d.sizes, 0, d.rank), static_cast<uint32_t*>(out1),
+                            static_cast<const uint32_t*>(plan->scratch), stream);
+      break;
+    }
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "gather / scatter / argsort / prng launch");
   return PMLB_OK;
 }
 

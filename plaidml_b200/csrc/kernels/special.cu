@@ -1,0 +1,428 @@
+// The four tile operations that are not contractions: gather, scatter, argsort, prng.  All of them move bytes and
+// indices; one thread per result element (gather), per update (scatter), per element and merge pass (argsort), per
+// run of elements (prng).
+//
+// gather    integer indices copy elements; float indices interpolate in the tensor's float type with a rounding
+//           after every operation, so an f16 / bf16 / f32 / f64 result is what scalar code in that type gives.
+// scatter   the result starts as a copy of the data (a device copy issued by the caller side of this file), then
+//           every update adds (atomically) or stores.
+// argsort   a stable merge sort of positions: pass w merges runs of w positions into runs of 2w, every element
+//           finding its place by a binary search in the sibling run (elements of the left run go before equal
+//           elements of the right run).  ceil(log2 n) passes between two int32 buffers.
+// prng      three linear shift-register generators; a thread jumps its generators to its first element by applying
+//           precomputed powers of the step matrices over GF(2), then steps through its run.
+#include "special.h"
+
+#include <math.h>
+
+#include "typed_access.cuh"
+
+namespace pmlb {
+
+namespace {
+
+__device__ __forceinline__ void copy_element(void* dst, long long di, const void* src, long long si, int bytes) {
+  switch (bytes) {
+    case 1: static_cast<uint8_t*>(dst)[di] = static_cast<const uint8_t*>(src)[si]; break;
+    case 2: static_cast<uint16_t*>(dst)[di] = static_cast<const uint16_t*>(src)[si]; break;
+    case 4: static_cast<uint32_t*>(dst)[di] = static_cast<const uint32_t*>(src)[si]; break;
+    default: static_cast<unsigned long long*>(dst)[di] = static_cast<const unsigned long long*>(src)[si]; break;
+  }
+}
+
+__device__ __forceinline__ long long clamp_ll(long long v, long long lo, long long hi) {
+  return v < lo ? lo : (v > hi ? hi : v);
+}
+
+// Float -> int32 as the lowering's fptosi, saturating where that is undefined.
+__device__ __forceinline__ long long to_i32(double v) {
+  if (!(v == v)) return 0;
+  if (v <= -2147483648.0) return -2147483648LL;
+  if (v >= 2147483647.0) return 2147483647LL;
+  return static_cast<long long>(v);
+}
+
+// ------------------------------------------------------------------ arithmetic classes of the interpolation
+
+struct ArF32 {
+  using T = float;
+  static __device__ __forceinline__ T r(T x) { return x; }
+};
+struct ArF16 {
+  using T = float;
+  static __device__ __forceinline__ T r(T x) { return __half2float(__float2half_rn(x)); }
+};
+struct ArBF16 {
+  using T = float;
+  static __device__ __forceinline__ T r(T x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+};
+struct ArF64 {
+  using T = double;
+  static __device__ __forceinline__ T r(T x) { return x; }
+};
+
+__device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(a, b); }
+
+template <class A>
+struct Arith {
+  using T = typename A::T;
+  static __device__ __forceinline__ T mul(T a, T b) { return A::r(mul_rn(a, b)); }
+  static __device__ __forceinline__ T add(T a, T b) { return A::r(add_rn(a, b)); }
+  static __device__ __forceinline__ T sub(T a, T b) { return A::r(add_rn(a, -b)); }
+};
+
+// One interpolated value: `idx` is the (float) index along the axis, `at(i)` the element at axis position i.
+template <class A, class At>
+__device__ __forceinline__ typename A::T interpolate(const GatherParams& p, typename A::T idx, At at) {
+  using T = typename A::T;
+  using M = Arith<A>;
+  const long long hi = p.axis_len - 1;
+  const T fl = floor(idx);
+  T result;
+  if (p.interpolation == 0) {
+    long long i;
+    const bool half = idx == A::r(add_rn(fl, T(0.5)));
+    const long long rounded = to_i32(floor(A::r(add_rn(idx, T(0.5)))));
+    switch (p.nearest) {
+      case 0: i = half ? to_i32(fl) : rounded; break;
+      case 1: i = half ? to_i32(ceil(idx)) : rounded; break;
+      case 2: i = to_i32(fl); break;
+      case 3: i = to_i32(ceil(idx)); break;
+      default: i = to_i32(idx); break;
+    }
+    result = at(clamp_ll(i, 0, hi));
+  } else if (p.interpolation == 1) {
+    const T g0 = at(clamp_ll(to_i32(ceil(idx)), 0, hi));
+    const T g1 = at(clamp_ll(to_i32(fl), 0, hi));
+    const T c0 = M::sub(idx, fl);
+    const T c1 = M::sub(T(1), c0);
+    result = M::add(M::mul(c0, g0), M::mul(c1, g1));
+  } else {
+    const T a = A::r(static_cast<T>(p.cube_coeff));
+    const long long fi = to_i32(fl), ci = to_i32(ceil(idx));
+    const T g0 = at(clamp_ll(fi - 1, 0, hi));
+    const T g1 = at(clamp_ll(fi, 0, hi));
+    const T g2 = at(clamp_ll(ci, 0, hi));
+    const T g3 = at(clamp_ll(ci + 1, 0, hi));
+    const T s = M::sub(idx, fl);
+    const T s2 = M::mul(s, s);
+    const T s3 = M::mul(s2, s);
+    const T s_a = M::mul(a, s);
+    const T s2_a = M::mul(a, s2);
+    const T s3_a = M::mul(a, s3);
+    const T s3_a2 = M::mul(M::add(a, T(2)), s3);
+    const T s2_a3 = M::mul(M::add(a, T(3)), s2);
+    const T s2_2a3 = M::mul(M::add(M::add(a, a), T(3)), s2);
+    const T p0 = M::add(M::sub(s3_a, M::mul(s2_a, T(2))), s_a);
+    const T p1 = M::add(M::sub(s3_a2, s2_a3), T(1));
+    const T p2 = M::sub(M::sub(s2_2a3, s3_a2), s_a);
+    const T p3 = M::sub(s2_a, s3_a);
+    result = M::add(M::add(M::add(M::mul(p0, g0), M::mul(p1, g1)), M::mul(p2, g2)), M::mul(p3, g3));
+  }
+  if (p.out_of_bounds == 1 && (idx > static_cast<T>(hi) || idx < T(0))) result = T(0);
+  return result;
+}
+
+template <class A>
+__device__ __forceinline__ void gather_interpolated(const GatherParams& p, long long e, long long src_base, double idx) {
+  using T = typename A::T;
+  auto at = [&](long long i) -> T { return load_as<T>(p.tensor, p.dtype, src_base + i * p.inner); };
+  const T v = interpolate<A>(p, A::r(static_cast<T>(idx)), at);
+  store_as<T>(p.out, p.dtype, e, v);
+}
+
+__global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ GatherParams p) {
+  const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= p.out_elems) return;
+  const long long in = e % p.inner;
+  if (p.nd) {
+    const long long row = e / p.inner;
+    long long off = row / p.rows_per_batch;
+    for (int k = 0; k < p.k; ++k) {
+      const long long i = clamp_ll(load_as<long long>(p.indices, p.idx_dtype, row * p.k + k), 0, p.dims[k] - 1);
+      off = off * p.dims[k] + i;
+    }
+    copy_element(p.out, e, p.tensor, off * p.inner + in, p.elem_bytes);
+    return;
+  }
+  const long long j = (e / p.inner) % p.n_idx;
+  const long long o = e / (p.inner * p.n_idx);
+  const long long src_base = o * p.axis_len * p.inner + in;
+  if (!dtype_is_float(p.idx_dtype)) {
+    const long long i = clamp_ll(load_as<long long>(p.indices, p.idx_dtype, j), 0, p.axis_len - 1);
+    copy_element(p.out, e, p.tensor, src_base + i * p.inner, p.elem_bytes);
+    return;
+  }
+  const double idx = load_as<double>(p.indices, p.idx_dtype, j);
+  if (!dtype_is_float(p.dtype)) {
+    const long long i = clamp_ll(to_i32(idx), 0, p.axis_len - 1);
+    copy_element(p.out, e, p.tensor, src_base + i * p.inner, p.elem_bytes);
+    return;
+  }
+  switch (p.dtype) {
+    case PMLB_F16: gather_interpolated<ArF16>(p, e, src_base, idx); break;
+    case PMLB_BF16: gather_interpolated<ArBF16>(p, e, src_base, idx); break;
+    case PMLB_F64: gather_interpolated<ArF64>(p, e, src_base, idx); break;
+    default: gather_interpolated<ArF32>(p, e, src_base, idx); break;
+  }
+}
+
+// ------------------------------------------------------------------ scatter
+
+// out[i] += updates[u] for 8- and 16-bit element types: compare-and-swap on the aligned word that holds the element.
+__device__ __forceinline__ void atomic_add_narrow(void* base, int dtype, long long i, const void* upd, long long u,
+                                                  int bytes) {
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(base) + static_cast<uintptr_t>(i) * bytes;
+  unsigned* word = reinterpret_cast<unsigned*>(addr & ~static_cast<uintptr_t>(3));
+  const unsigned shift = static_cast<unsigned>(addr & 3) * 8;
+  const unsigned mask = (bytes == 1 ? 0xFFu : 0xFFFFu) << shift;
+  unsigned add_bits;
+  if (bytes == 1) add_bits = static_cast<const uint8_t*>(upd)[u];
+  else add_bits = static_cast<const uint16_t*>(upd)[u];
+  unsigned old = *word, assumed;
+  do {
+    assumed = old;
+    const unsigned cur = (assumed & mask) >> shift;
+    unsigned next;
+    if (dtype == PMLB_F16) {
+      const float s = __half2float(__ushort_as_half(static_cast<unsigned short>(cur))) +
+                      __half2float(__ushort_as_half(static_cast<unsigned short>(add_bits)));
+      next = __half_as_ushort(__float2half_rn(s));
+    } else if (dtype == PMLB_BF16) {
+      const float s = __bfloat162float(__ushort_as_bfloat16(static_cast<unsigned short>(cur))) +
+                      __bfloat162float(__ushort_as_bfloat16(static_cast<unsigned short>(add_bits)));
+      next = __bfloat16_as_ushort(__float2bfloat16_rn(s));
+    } else if (dtype == PMLB_BOOL) {
+      next = (cur + add_bits) != 0 ? 1u : 0u;
+    } else {
+      next = cur + add_bits;  // integers wrap
+    }
+    next = (next << shift) & mask;
+    old = atomicCAS(word, assumed, (assumed & ~mask) | next);
+  } while (old != assumed);
+}
+
+__device__ __forceinline__ void atomic_add_element(void* out, int dtype, long long i, const void* upd, long long u,
+                                                   int bytes) {
+  switch (dtype) {
+    case PMLB_F32: atomicAdd(static_cast<float*>(out) + i, static_cast<const float*>(upd)[u]); break;
+    case PMLB_F64: atomicAdd(static_cast<double*>(out) + i, static_cast<const double*>(upd)[u]); break;
+    case PMLB_I32:
+    case PMLB_U32: atomicAdd(static_cast<unsigned*>(out) + i, static_cast<const unsigned*>(upd)[u]); break;
+    case PMLB_I64:
+    case PMLB_U64:
+      atomicAdd(static_cast<unsigned long long*>(out) + i, static_cast<const unsigned long long*>(upd)[u]);
+      break;
+    default: atomic_add_narrow(out, dtype, i, upd, u, bytes); break;
+  }
+}
+
+__global__ void __launch_bounds__(256) scatter_kernel(const __grid_constant__ ScatterParams p) {
+  const long long u = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (u >= p.upd_elems) return;
+  long long c[PMLB_MAX_RANK];
+  long long rem = u;
+  for (int d = p.upd_rank - 1; d >= 0; --d) {
+    c[d] = rem % p.upd_sizes[d];
+    rem /= p.upd_sizes[d];
+  }
+  long long dst[PMLB_MAX_RANK];
+  int nd = 0;
+  if (p.mode == 3) {
+    // the first idx_rank - 1 coordinates pick a row of indices; its K entries lead the destination
+    const int k = static_cast<int>(p.idx_sizes[p.idx_rank - 1]);
+    long long row = 0;
+    for (int d = 0; d < p.idx_rank - 1; ++d) row = row * p.idx_sizes[d] + c[d];
+    for (int i = 0; i < k; ++i) dst[nd++] = load_as<long long>(p.indices, p.idx_dtype, row * k + i);
+    for (int d = p.idx_rank - 1; d < p.upd_rank; ++d) dst[nd++] = c[d];
+  } else {
+    const int first = p.mode == 1 ? p.axis : 0;                       // coordinates that address the indices
+    const int tail = p.mode == 1 ? p.axis + p.idx_rank - 1 : p.axis;  // the axis coordinate and what follows it
+    long long at = 0;
+    for (int d = 0; d < p.idx_rank; ++d) at = at * p.idx_sizes[d] + c[first + d];
+    for (int d = 0; d < p.axis; ++d) dst[nd++] = c[d];
+    for (int d = tail; d < p.upd_rank; ++d) dst[nd++] = c[d];
+    dst[p.axis] = load_as<long long>(p.indices, p.idx_dtype, at);
+  }
+  long long off = 0;
+  for (int d = 0; d < p.rank; ++d) {
+    if (dst[d] < 0 || dst[d] >= p.sizes[d]) return;  // lands outside the data: dropped
+    off = off * p.sizes[d] + dst[d];
+  }
+  if (p.mode == 0) atomic_add_element(p.out, p.dtype, off, p.updates, u, p.elem_bytes);
+  else copy_element(p.out, off, p.updates, u, p.elem_bytes);
+}
+
+// ------------------------------------------------------------------ argsort
+
+template <class V>
+__global__ void __launch_bounds__(256) argsort_pass_kernel(const __grid_constant__ ArgsortParams p,
+                                                           const int32_t* __restrict__ src, int32_t* __restrict__ dst,
+                                                           long long w, long long total) {
+  const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const long long in = e % p.inner;
+  const long long j = (e / p.inner) % p.n;
+  const long long line = (e / (p.inner * p.n)) * p.n * p.inner + in;  // element q of the line is at line + q * inner
+  auto pos_at = [&](long long q) -> long long { return src ? src[line + q * p.inner] : q; };
+  auto key_at = [&](long long q) -> V { return load_as<V>(p.tensor, p.dtype, line + pos_at(q) * p.inner); };
+  auto before = [&](V a, V b) -> bool { return p.descending ? a > b : a < b; };
+  if (w <= 0) {  // no merging to do: positions in order
+    dst[line + j * p.inner] = static_cast<int32_t>(j);
+    return;
+  }
+  const long long base = (j / (2 * w)) * 2 * w;
+  const long long mid = base + w < p.n ? base + w : p.n;
+  const long long end = base + 2 * w < p.n ? base + 2 * w : p.n;
+  const V key = key_at(j);
+  long long lo, hi, dest;
+  if (j < mid) {
+    // elements of the right run that go strictly before this one
+    lo = mid;
+    hi = end;
+    while (lo < hi) {
+      const long long m = (lo + hi) >> 1;
+      if (before(key_at(m), key)) lo = m + 1; else hi = m;
+    }
+    dest = j + (lo - mid);
+  } else {
+    // elements of the left run that do not go after this one
+    lo = base;
+    hi = mid;
+    while (lo < hi) {
+      const long long m = (lo + hi) >> 1;
+      if (before(key, key_at(m))) hi = m; else lo = m + 1;
+    }
+    dest = (lo - base) + (j - mid) + base;
+  }
+  dst[line + dest * p.inner] = static_cast<int32_t>(pos_at(j));
+}
+
+// ------------------------------------------------------------------ prng
+
+__host__ __device__ __forceinline__ uint32_t prng_step(int c, uint32_t s) {
+  switch (c) {
+    case 0: return ((s & 4294967294u) << 12) ^ (((s << 13) ^ s) >> 19);
+    case 1: return ((s & 4294967288u) << 4) ^ (((s << 2) ^ s) >> 25);
+    default: return ((s & 4294967280u) << 17) ^ (((s << 3) ^ s) >> 11);
+  }
+}
+
+__host__ __device__ __forceinline__ uint32_t gf2_apply(const uint32_t* cols, uint32_t x) {
+  uint32_t y = 0;
+  for (int b = 0; b < 32; ++b) {
+    if ((x >> b) & 1u) y ^= cols[b];
+  }
+  return y;
+}
+
+__device__ __forceinline__ uint32_t prng_jump(const uint32_t* table, int c, uint32_t s, unsigned long long steps) {
+  for (int level = 0; level < kPrngLevels && steps != 0; ++level, steps >>= 1) {
+    if (steps & 1ull) s = gf2_apply(table + (c * kPrngLevels + level) * 32, s);
+  }
+  return s;
+}
+
+__global__ void __launch_bounds__(128) prng_kernel(const uint32_t* __restrict__ state, long long state_elems,
+                                                   float* __restrict__ out, long long count,
+                                                   uint32_t* __restrict__ new_state,
+                                                   const uint32_t* __restrict__ table, long long threads) {
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= threads) return;
+  // without a place for the numbers only the state after them is wanted: one thread jumps there
+  const long long first = out ? t * kPrngChunk : count;
+  uint32_t s0 = prng_jump(table, 0, state[0], static_cast<unsigned long long>(first));
+  uint32_t s1 = prng_jump(table, 1, state[1], static_cast<unsigned long long>(first));
+  uint32_t s2 = prng_jump(table, 2, state[2], static_cast<unsigned long long>(first));
+  const long long last = first + kPrngChunk < count ? first + kPrngChunk : count;
+  for (long long i = first; i < last; ++i) {
+    out[i] = static_cast<float>(static_cast<double>(s0 ^ s1 ^ s2) / 4294967296.0);
+    s0 = prng_step(0, s0);
+    s1 = prng_step(1, s1);
+    s2 = prng_step(2, s2);
+  }
+  if (last == count && new_state) {  // the thread that holds the last element (thread 0 when there are none)
+    new_state[0] = s0;
+    new_state[1] = s1;
+    new_state[2] = s2;
+    for (long long i = 3; i < state_elems; ++i) new_state[i] = state[i];
+  }
+}
+
+unsigned blocks_for(long long n, int threads) { return static_cast<unsigned>((n + threads - 1) / threads); }
+
+}  // namespace
+
+cudaError_t launch_gather(const GatherParams& p, cudaStream_t stream) {
+  if (p.out_elems <= 0) return cudaSuccess;
+  gather_kernel<<<blocks_for(p.out_elems, 256), 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scatter(const ScatterParams& p, cudaStream_t stream) {
+  if (p.upd_elems <= 0) return cudaSuccess;
+  scatter_kernel<<<blocks_for(p.upd_elems, 256), 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+namespace {
+
+template <class V>
+cudaError_t argsort_passes(const ArgsortParams& p, int32_t* out, int32_t* scratch, cudaStream_t stream) {
+  const long long total = p.outer * p.n * p.inner;
+  const unsigned blocks = blocks_for(total, 256);
+  int passes = 0;
+  while ((1LL << passes) < p.n) ++passes;
+  if (passes == 0) {
+    argsort_pass_kernel<V><<<blocks, 256, 0, stream>>>(p, nullptr, out, 0, total);
+    return cudaGetLastError();
+  }
+  for (int k = 0; k < passes; ++k) {
+    // the last pass writes `out`; the passes before it alternate
+    int32_t* dst = ((passes - 1 - k) % 2 == 0) ? out : scratch;
+    const int32_t* src = k == 0 ? nullptr : (dst == out ? scratch : out);
+    argsort_pass_kernel<V><<<blocks, 256, 0, stream>>>(p, src, dst, 1LL << k, total);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+}  // namespace
+
+cudaError_t launch_argsort(const ArgsortParams& p, int32_t* out, int32_t* scratch, cudaStream_t stream) {
+  if (p.outer * p.n * p.inner <= 0) return cudaSuccess;
+  switch (p.dtype) {
+    case PMLB_F16:
+    case PMLB_BF16:
+    case PMLB_F32:
+    case PMLB_F64: return argsort_passes<double>(p, out, scratch, stream);
+    case PMLB_U64: return argsort_passes<unsigned long long>(p, out, scratch, stream);
+    default: return argsort_passes<long long>(p, out, scratch, stream);
+  }
+}
+
+cudaError_t launch_prng(const uint32_t* state, long long state_elems, float* out, long long count, uint32_t* new_state,
+                        const uint32_t* table, cudaStream_t stream) {
+  long long threads = out ? (count + kPrngChunk - 1) / kPrngChunk : 1;
+  if (threads < 1) threads = 1;
+  prng_kernel<<<blocks_for(threads, 128), 128, 0, stream>>>(state, state_elems, out, count, new_state, table, threads);
+  return cudaGetLastError();
+}
+
+void prng_jump_table(uint32_t* table) {
+  for (int c = 0; c < 3; ++c) {
+    uint32_t* level0 = table + c * kPrngLevels * 32;
+    for (int b = 0; b < 32; ++b) level0[b] = prng_step(c, 1u << b);
+    for (int level = 1; level < kPrngLevels; ++level) {
+      const uint32_t* prev = table + (c * kPrngLevels + level - 1) * 32;
+      uint32_t* cur = table + (c * kPrngLevels + level) * 32;
+      for (int b = 0; b < 32; ++b) cur[b] = gf2_apply(prev, prev[b]);
+    }
+  }
+}
+
+}  // namespace pmlb

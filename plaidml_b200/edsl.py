@@ -7,6 +7,8 @@ names, same operator overloads) so that programs written against it run unchange
 
 from __future__ import annotations
 
+import enum
+
 import numpy as np
 
 from .core import Buffer, DType, Program, TensorShape
@@ -509,6 +511,78 @@ def shape(x):
     return intrinsic("shape", x)
 
 
+# The operations that are not contractions (plaidml/edsl/edsl.h:809-811, 971-979, 1034-1068, 1623-1770); the
+# enumerations carry the reference's values.
+class SortDirection(enum.IntEnum):
+    ASC = 0
+    DESC = 1
+
+
+class InterpolationMode(enum.IntEnum):
+    NEAREST = 0
+    LINEAR = 1
+    CUBIC = 2
+    NONE = 3
+
+
+class NearestMode(enum.IntEnum):
+    ROUND_PREFER_FLOOR = 0
+    ROUND_PREFER_CEIL = 1
+    FLOOR = 2
+    CEIL = 3
+    SIMPLE = 4
+    NONE = 5
+
+
+class GatherMode(enum.IntEnum):
+    NORMAL = 0
+    ND = 1
+
+
+class OutOfBoundsMode(enum.IntEnum):
+    GATHER_EDGE_PADDED_INPUT = 0
+    RETURN_ZERO = 1
+
+
+class ScatterMode(enum.IntEnum):
+    NORMAL = 0
+    UPDATE_SLICE = 1
+    UPDATE_ELT = 2
+    UPDATE_ND = 3
+
+
+def argsort(x, axis=-1, direction=SortDirection.ASC):
+    """int32 positions that sort `x` along `axis`; equal elements keep their order."""
+    return intrinsic("argsort", x, int(axis), int(direction))
+
+
+def gather(x, y, axis=0, interpolation_mode=InterpolationMode.NONE, nearest_mode=NearestMode.ROUND_PREFER_FLOOR,
+           cube_coeff=-0.75, out_of_bounds_mode=OutOfBoundsMode.GATHER_EDGE_PADDED_INPUT, mode=GatherMode.NORMAL,
+           batch_dims=0):
+    """`x` gathered along `axis` at the positions in `y` (float positions interpolate); with ``mode=GatherMode.ND``
+    the last dim of `y` addresses `batch_dims`.. dims of `x`.  A Python number for `y` picks one position."""
+    if not isinstance(y, Tensor):
+        kind = DType.FLOAT32 if isinstance(y, (float, np.floating)) else DType.INT32
+        y = cast(index([1], 0), kind) + y
+    if axis < 0:
+        axis += x.rank
+    return intrinsic("gather", x, y, int(axis), int(interpolation_mode), int(nearest_mode), float(cube_coeff), int(mode),
+                     int(batch_dims), int(out_of_bounds_mode))
+
+
+def scatter(data, indices, updates, axis=0, mode=ScatterMode.NORMAL):
+    """A copy of `data` with `updates` added (NORMAL) or stored (the UPDATE modes) at the places `indices` name."""
+    if axis < 0:
+        axis += data.rank
+    return intrinsic("scatter", data, indices, updates, int(axis), int(mode))
+
+
+def prng(state, dims):
+    """(numbers in [0, 1) of shape `dims` as f32, the state after them) from a state of three uint32 words."""
+    both = intrinsic("prng", state, *[_as_dim(d) if not isinstance(d, (int, np.integer)) else int(d) for d in dims])
+    return both.element(0), both.element(1)
+
+
 def pragma(x, op, attrs):
     """``tile.pragma``: `x` annotated with an operation name and attributes (plaidml/edsl/__init__.py:1159-1171).
     The cuda target runs it as a copy of `x`."""
@@ -591,6 +665,14 @@ class Value(ForeignObject):
 
     def as_tensor(self) -> Tensor:
         return Tensor(expr=ffi_call(lib.plaidml_value_expr_get, self.as_ptr()))
+
+    def as_tuple(self):
+        """The elements of a tuple value, each as its own ``Value`` (plaidml/edsl/__init__.py Value.as_tuple)."""
+        raw = ffi_call(lib.plaidml_value_tuple_get, self.as_ptr())
+        try:
+            return [Value(ffi_call(lib.plaidml_value_clone, raw.elts[i])) for i in range(raw.size)]
+        finally:
+            ffi_call(lib.plaidml_tuple_free, raw)
 
 
 def build_program(name, inputs, outputs, shapes=None) -> Program:

@@ -33,6 +33,7 @@ CONV_CTA_PAIRS = 8
 CONV_NO_CTA_PAIRS = 16
 CONV_NO_COLUMN_MERGE = 32
 CONV_MAX_POOL_3X3_S2 = 64
+SPECIAL_GATHER, SPECIAL_SCATTER, SPECIAL_ARGSORT, SPECIAL_PRNG = range(4)
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = range(5)
 
 MAX_IDX, MAX_RANK, MAX_CONS = 10, 8, 8
@@ -100,6 +101,18 @@ class EltwiseDesc(C.Structure):
     ]
 
 
+class SpecialDesc(C.Structure):
+    """gather / scatter / argsort / prng (``pmlb_special_desc``)."""
+    _fields_ = [
+        ("op", C.c_int32), ("dtype", C.c_int32), ("idx_dtype", C.c_int32),
+        ("rank", C.c_int32), ("idx_rank", C.c_int32), ("upd_rank", C.c_int32),
+        ("sizes", C.c_int64 * MAX_RANK), ("idx_sizes", C.c_int64 * MAX_RANK), ("upd_sizes", C.c_int64 * MAX_RANK),
+        ("axis", C.c_int32), ("mode", C.c_int32), ("batch_dims", C.c_int32), ("interpolation", C.c_int32),
+        ("nearest", C.c_int32), ("out_of_bounds", C.c_int32),
+        ("cube_coeff", C.c_double), ("state_elems", C.c_int64),
+    ]
+
+
 class KernelError(RuntimeError):
     def __init__(self, status: int, message: str):
         super().__init__(f"pmlb status {status}: {message}")
@@ -142,7 +155,7 @@ def load() -> C.CDLL:
     lib.pmlb_plan_scratch_bytes.restype = C.c_size_t
     lib.pmlb_plan_check.argtypes = [vp, vp]
     for name, desc in (("gemm", GemmDesc), ("conv", ConvDesc), ("reduce", ReduceDesc), ("pool", PoolDesc),
-                       ("contract", ContractDesc), ("eltwise", EltwiseDesc)):
+                       ("contract", ContractDesc), ("eltwise", EltwiseDesc), ("special", SpecialDesc)):
         getattr(lib, f"pmlb_{name}_dispatch").argtypes = [C.POINTER(desc), C.POINTER(vp)]
     lib.pmlb_gemm_invoke.argtypes = [vp] * 8
     lib.pmlb_gemm_invoke_two.argtypes = [vp] * 9
@@ -152,6 +165,9 @@ def load() -> C.CDLL:
     lib.pmlb_pool_invoke.argtypes = [vp] * 4
     lib.pmlb_contract_invoke.argtypes = [vp] * 7
     lib.pmlb_eltwise_invoke.argtypes = [vp] * 6
+    lib.pmlb_special_invoke.argtypes = [vp] * 7
+    lib.pmlb_special_out_elems.argtypes = [C.POINTER(SpecialDesc)]
+    lib.pmlb_special_out_elems.restype = C.c_int64
     _lib = lib
     return lib
 
@@ -162,7 +178,7 @@ def check(status: int) -> None:
 
 
 class Plan:
-    """Owns a ``pmlb_plan``; ``kind`` is 'gemm', 'conv', 'reduce', 'pool', 'contract' or 'eltwise'."""
+    """Owns a ``pmlb_plan``; ``kind`` is 'gemm', 'conv', 'reduce', 'pool', 'contract', 'eltwise' or 'special'."""
 
     def __init__(self, kind: str, desc):
         self.lib = load()
@@ -223,6 +239,30 @@ class Plan:
     def eltwise(self, ins, out, stream=0):
         s = list(ins) + [None] * (3 - len(ins))
         check(self.lib.pmlb_eltwise_invoke(self.handle, stream, s[0], s[1], s[2], out))
+
+
+    def special(self, ins, out0, out1=None, stream=0):
+        """gather (tensor, indices), scatter (data, indices, updates), argsort (tensor), prng (state -> out0, out1)."""
+        s = list(ins) + [None] * (3 - len(ins))
+        check(self.lib.pmlb_special_invoke(self.handle, stream, s[0], s[1], s[2], out0, out1))
+
+
+def special_desc(op: int, dtype: int = 0, sizes=(), idx_dtype: int = 0, idx_sizes=(), upd_sizes=(), axis: int = 0,
+                 mode: int = 0, batch_dims: int = 0, interpolation: int = 3, nearest: int = 0, out_of_bounds: int = 0,
+                 cube_coeff: float = -0.75, state_elems: int = 0) -> SpecialDesc:
+    d = SpecialDesc()
+    d.op, d.dtype, d.idx_dtype = op, dtype, idx_dtype
+    d.rank, d.idx_rank, d.upd_rank = len(sizes), len(idx_sizes), len(upd_sizes)
+    for i, v in enumerate(sizes):
+        d.sizes[i] = v
+    for i, v in enumerate(idx_sizes):
+        d.idx_sizes[i] = v
+    for i, v in enumerate(upd_sizes):
+        d.upd_sizes[i] = v
+    d.axis, d.mode, d.batch_dims = axis, mode, batch_dims
+    d.interpolation, d.nearest, d.out_of_bounds = interpolation, nearest, out_of_bounds
+    d.cube_coeff, d.state_elems = cube_coeff, state_elems
+    return d
 
 
 def make_access(dtype: int, sizes, coef_rows, offs=None, dens=None, strides=None) -> Access:

@@ -267,3 +267,26 @@ def slice_of(x, slices):
 
 def tile(x, n):
     return op("tile", [x, list(n)]).as_tensor()
+
+
+class TopKSortType(enum.IntEnum):
+    VALUE = 0
+    INDEX = 1
+
+
+def gatherND(x, indices, batch_dims=0, interpolation_mode=edsl.InterpolationMode.NONE):
+    """`x` at the index rows of `indices` (their last dim addresses dims batch_dims.. of `x`); LINEAR blends the
+    corners around float rows, the data seen as zero-padded."""
+    return op("gatherND", [x, indices, batch_dims, int(interpolation_mode)]).as_tensor()
+
+
+def sort(x, axis=-1, direction=edsl.SortDirection.ASC):
+    return op("sort", [x, axis, int(direction)]).as_tensor()
+
+
+def topk(x, k, axis=-1, sort_direction=edsl.SortDirection.DESC, sort_type=TopKSortType.VALUE, index_element_type=None):
+    """(values, positions) of the first `k` elements along `axis` in sorted order."""
+    from .core import DType
+    values, positions = op("topk", [x, k, axis, int(sort_direction), int(sort_type),
+                                    int(index_element_type if index_element_type is not None else DType.INT32)]).as_tuple()
+    return values.as_tensor(), positions.as_tensor()

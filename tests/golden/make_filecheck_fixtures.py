@@ -4,8 +4,7 @@ tests/golden/edsl_filecheck.json, one list of [directive, pattern] per test name
 
     python tests/golden/make_filecheck_fixtures.py <path to a plaidml checkout>
 
-Only the tests named in WANTED are taken: those whose programs the contraction path's EDSL can
-build (no gather / argsort / prng)."""
+Only the tests named in WANTED are taken (those with expectations worth replaying)."""
 
 import json
 import os
@@ -17,7 +16,9 @@ WANTED = [
     "Convolution", "MnistCnn", "RepeatElements", "GlobalMin", "CumSum", "ComplexConv2d", "Reciprocal",
     "DefractLong", "Select", "ConvI8", "UniqueNames", "dup_out", "HigherPrecisionConstants", "LarsMomentum4d",
     "ReshapeFold", "ReshapeScalar", "ReshapeIntoScalar", "ReshapeFromScalar", "Shape", "Trace",
-    "Layer", "LayerOperandOrder", "LayerEmbeddedConst", "LayerUnusedOperand",
+    "Layer", "LayerOperandOrder", "LayerEmbeddedConst", "LayerUnusedOperand", "LayerMultipleReturnValues",
+    "Prng", "ArgSort1d", "ArgSort1dInt", "ArgSort1dDup", "ArgSort2dAxis0", "ArgSort2dAxis1", "ArgSort3dAxis0Asc",
+    "ArgSort3dAxis2Desc", "ArgSort3dAxisNeg2Asc",
 ]
 
 

@@ -11,6 +11,7 @@ import pytest
 
 import filecheck
 from plaidml_b200.core import DType, Program
+from plaidml_b200 import edsl
 from plaidml_b200.edsl import (Constant, Contraction, Placeholder, TensorDims, TensorIndexes, cast, exp, layer, reshape,
                                select, shape, sqrt, trace)
 
@@ -281,7 +282,37 @@ def build_layer_unused_operand():
     return Program("LayerUnusedOperand", [A], [layer("sum", [A, B], lambda: A + _const_10x20("C"))])
 
 
+def build_layer_multiple_return_values():
+    A = f32(10, 5)
+
+    def body():
+        idxs = edsl.argsort(A, 0)
+        return [edsl.gather(A, idxs), idxs]
+
+    return Program("LayerMultipleReturnValues", [A], layer("two_output", [A], body))
+
+
+def build_prng():
+    S = Constant(np.array([[5, 6, 7]], dtype=np.uint32), name="S")
+    O, NS = edsl.prng(S, [2, 3])
+    return Program("prng", [], [O, NS])
+
+
+def build_argsort(dtype, dims, axis, direction=edsl.SortDirection.ASC):
+    I = Placeholder(dtype, dims)
+    return Program("argsort", [I], [edsl.argsort(I, axis, direction)])
+
+
 BUILDERS = {
+    "LayerMultipleReturnValues": build_layer_multiple_return_values, "Prng": build_prng,
+    "ArgSort1d": lambda: build_argsort(DType.FLOAT32, [20], 0),
+    "ArgSort1dInt": lambda: build_argsort(DType.INT32, [20], 0),
+    "ArgSort1dDup": lambda: build_argsort(DType.FLOAT32, [20], 0),
+    "ArgSort2dAxis0": lambda: build_argsort(DType.FLOAT32, [5, 4], 0),
+    "ArgSort2dAxis1": lambda: build_argsort(DType.FLOAT32, [5, 4], 1),
+    "ArgSort3dAxis0Asc": lambda: build_argsort(DType.FLOAT32, [3, 4, 5], 0),
+    "ArgSort3dAxis2Desc": lambda: build_argsort(DType.FLOAT32, [3, 4, 5], 2, edsl.SortDirection.DESC),
+    "ArgSort3dAxisNeg2Asc": lambda: build_argsort(DType.FLOAT32, [2, 2, 2], -2),
     "Shape": build_shape, "Trace": build_trace,
     "Layer": build_layer, "LayerOperandOrder": build_layer_operand_order, "LayerEmbeddedConst": build_layer_embedded_const,
     "LayerUnusedOperand": build_layer_unused_operand,

@@ -5,11 +5,10 @@ tests/host/refshim/ replace googletest, gflags and three LLVM ADT headers, nothi
   * plaidml/edsl/examples/gemm.cc: five GEMM tests with exact expected outputs;
   * networks/oplib/resnet50.cc: the reference's ResNet-50 builder, built at batch 1;
   * plaidml/edsl/tests/edsl_test.cc: the reference's whole C++ EDSL suite, 119 tests with their own checkExact /
-    checkClose / EXPECT_* expectations.  Every test passes except the 34 that use the gather / scatter / argsort /
-    prng intrinsics (not contractions; the cuda target refuses them by name): the test below pins that list;
+    checkClose / EXPECT_* expectations (contractions, element-wise operations, layers, gather / scatter / argsort /
+    prng): all pass;
   * plaidml/op/op_test.cc: the reference's op-library suite, 60 tests (67 with the parameterised convolution cases),
-    among them exact expected outputs for explicit paddings, transposed and grouped convolutions; all pass but `Sort`
-    (built on argsort).
+    among them exact expected outputs for explicit paddings, transposed and grouped convolutions and a sort: all pass.
 
 The CPU half needs the checkout (``PLAIDML_REFERENCE_DIR``; skipped when unset) and g++: it compiles the
 binaries into tests/host/_build/ and runs them with --build-only (programs are built, printed and compiled
@@ -37,27 +36,10 @@ BINARIES = {
     "ref_op": (["plaidml/op/op_test.cc"], []),
 }
 
-# Tests of the reference's EDSL suite whose programs use an intrinsic that is not a contraction and that the cuda
-# target does not offer (gather, scatter, argsort, prng; `gatherND` of the op library is built on gather).
-NOT_OFFERED = (
-    ["Prng", "Gather", "GatherND", "GatherNDWithBatchDims", "LayerMultipleReturnValues"]
-    + ["InterpolatedGather" + s for s in ("Nearest", "Linear", "LinearOutOfBoundsReturnZero", "Cubic", "CubicOutOfBoundsReturnZero",
-                                          "CubicDouble", "CubicHalf", "MultiDIndices", "ND1", "ND2", "ND3")]
-    + ["Scatter" + s for s in ("1D", "3D", "Dup1D", "Dup3D", "1DUpdateSlice", "3DUpdateSlice", "NDUpdateSlice", "NDUpdateSlice2",
-                               "NDUpdateSlice3", "Elt")]
-    + ["ArgSort" + s for s in ("1d", "1dInt", "1dDup", "2dAxis0", "2dAxis1", "3dAxis0Asc", "3dAxis2Desc", "3dAxisNeg2Asc")]
-)
-
-
 def _check_edsl_suite(out: str) -> None:
-    ran = [ln.split("CppEdsl.")[1].strip() for ln in out.splitlines() if ln.startswith("[ RUN ]")]
-    failed = [ln.split("CppEdsl.")[1].split(" (")[0].strip() for ln in out.splitlines() if ln.startswith("[ FAIL]")]
-    assert len(ran) == 119, len(ran)
-    assert sorted(failed) == sorted(NOT_OFFERED), sorted(set(failed) ^ set(NOT_OFFERED))
-    for name in failed:      # ... and each of them for that reason, not another
-        at = out.index("[ RUN ] CppEdsl." + name + "\n")
-        body = out[at:out.index("[ FAIL] CppEdsl." + name, at)]
-        assert "not offered by the cuda target" in body or "not in the cuda target's op library" in body, body[-600:]
+    ran = [ln for ln in out.splitlines() if ln.startswith("[ RUN ]")]
+    failed = [ln for ln in out.splitlines() if ln.startswith("[ FAIL]")]
+    assert len(ran) == 119 and not failed and "119 tests, 0 failures" in out, (failed, out[-1500:])
 
 
 def build_binaries(ref_dir: Path) -> list:
@@ -75,9 +57,8 @@ def build_binaries(ref_dir: Path) -> list:
 
 
 def _check_op_suite(out: str) -> None:
-    failed = [ln.split("]")[1].split(" (")[0].strip() for ln in out.splitlines() if ln.startswith("[ FAIL]")]
-    assert "67 tests, 1 failures" in out and failed == ["OpTest.Sort"], (failed, out[-1500:])
-    assert "'sort' is not in the cuda target's op library" in out
+    failed = [ln for ln in out.splitlines() if ln.startswith("[ FAIL]")]
+    assert "67 tests, 0 failures" in out and not failed, (failed, out[-1500:])
 
 
 def _run(binary: Path, *args, ok_codes=(0,)) -> str:
@@ -93,8 +74,8 @@ def test_reference_sources_compile_and_build_their_programs():
     if shutil.which("g++") is None or not (LIB_DIR / "libplaidml.so").exists():
         pytest.skip("needs g++ and a built libplaidml.so")
     gemm, resnet, edsl_suite, op_suite = build_binaries(Path(ref))
-    _check_edsl_suite(_run(edsl_suite, "--build-only", ok_codes=(0, 1)))
-    _check_op_suite(_run(op_suite, "--build-only", ok_codes=(0, 1)))
+    _check_edsl_suite(_run(edsl_suite, "--build-only"))
+    _check_op_suite(_run(op_suite, "--build-only"))
     out = _run(gemm, "--build-only")
     assert "5 tests, 0 failures" in out
     # the printed programs are the tile module of the reference's own FileCheck expectations
@@ -113,12 +94,12 @@ def test_reference_sources_run_on_the_cuda_device():
         out = _run(OUT / "ref_resnet", "--device", "cuda.0")
         assert "1 tests, 0 failures" in out
     if (OUT / "ref_edsl").exists():
-        # the 85 tests of the reference's EDSL suite that the target offers, with their own expected values
-        # (checkExact / checkClose at the reference's tolerances), on the device
-        out = _run(OUT / "ref_edsl", "--device", "cuda.0", ok_codes=(0, 1))
+        # the reference's EDSL suite with its own expected values (checkExact / checkClose at the reference's
+        # tolerances), on the device
+        out = _run(OUT / "ref_edsl", "--device", "cuda.0")
         assert "build only" not in out
         _check_edsl_suite(out)
     if (OUT / "ref_op").exists():
-        out = _run(OUT / "ref_op", "--device", "cuda.0", ok_codes=(0, 1))
+        out = _run(OUT / "ref_op", "--device", "cuda.0")
         assert "build only" not in out
         _check_op_suite(out)
