@@ -1510,9 +1510,10 @@ class Planner {
     st.kernel = op.mnemonic;
     st.detail = op.mnemonic + " -> " + outShape.str();
     if (sp.op == PSpecial::ArgSort) {
+      // one block sort of runs of up to 4096 positions, then a merge pass per doubling beyond that
       int passes = 0;
       while ((int64_t{1} << passes) < first.sizes[d.axis]) ++passes;
-      st.launches = passes > 0 ? passes : 1;
+      st.launches = 1 + (passes > 12 ? passes - 12 : 0);
     }
     st.launch = [plan, in0, in1, in2, out0, out1](cudaStream_t s) {
       return pmlb_special_invoke(plan, s, in0, in1, in2, out0, out1);

@@ -26,7 +26,8 @@ __device__ __forceinline__ void copy_element(void* dst, long long di, const void
     case 1: static_cast<uint8_t*>(dst)[di] = static_cast<const uint8_t*>(src)[si]; break;
     case 2: static_cast<uint16_t*>(dst)[di] = static_cast<const uint16_t*>(src)[si]; break;
     case 4: static_cast<uint32_t*>(dst)[di] = static_cast<const uint32_t*>(src)[si]; break;
-    default: static_cast<unsigned long long*>(dst)[di] = static_cast<const unsigned long long*>(src)[si]; break;
+    case 8: static_cast<unsigned long long*>(dst)[di] = static_cast<const unsigned long long*>(src)[si]; break;
+    default: static_cast<uint4*>(dst)[di] = static_cast<const uint4*>(src)[si]; break;  // 16: several elements at once
   }
 }
 
@@ -34,13 +35,10 @@ __device__ __forceinline__ long long clamp_ll(long long v, long long lo, long lo
   return v < lo ? lo : (v > hi ? hi : v);
 }
 
-// Float -> int32 as the lowering's fptosi, saturating where that is undefined.
-__device__ __forceinline__ long long to_i32(double v) {
-  if (!(v == v)) return 0;
-  if (v <= -2147483648.0) return -2147483648LL;
-  if (v >= 2147483647.0) return 2147483647LL;
-  return static_cast<long long>(v);
-}
+// Float -> int32 as the lowering's fptosi (towards zero); where that is undefined the conversion saturates and a
+// NaN gives 0.
+__device__ __forceinline__ long long to_i32(double v) { return __double2int_rz(v); }
+__device__ __forceinline__ long long to_i32(float v) { return __float2int_rz(v); }
 
 // ------------------------------------------------------------------ arithmetic classes of the interpolation
 
@@ -127,46 +125,49 @@ __device__ __forceinline__ typename A::T interpolate(const GatherParams& p, type
 }
 
 template <class A>
-__device__ __forceinline__ void gather_interpolated(const GatherParams& p, long long e, long long src_base, double idx) {
+__device__ __forceinline__ void gather_interpolated(const GatherParams& p, long long e, long long src_base, long long j) {
   using T = typename A::T;
   auto at = [&](long long i) -> T { return load_as<T>(p.tensor, p.dtype, src_base + i * p.inner); };
-  const T v = interpolate<A>(p, A::r(static_cast<T>(idx)), at);
+  const T v = interpolate<A>(p, A::r(load_as<T>(p.indices, p.idx_dtype, j)), at);
   store_as<T>(p.out, p.dtype, e, v);
 }
 
+// `I` is the type of the position arithmetic: 32 bits when every extent fits, else 64.
+template <class I>
 __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ GatherParams p) {
-  const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (e >= p.out_elems) return;
-  const long long in = e % p.inner;
+  const I e = static_cast<I>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= static_cast<I>(p.out_elems)) return;
+  const I inner = static_cast<I>(p.inner);
+  const I in = inner == 1 ? 0 : e % inner;
+  const I row = inner == 1 ? e : e / inner;
   if (p.nd) {
-    const long long row = e / p.inner;
-    long long off = row / p.rows_per_batch;
+    const I per_batch = static_cast<I>(p.rows_per_batch);
+    long long off = per_batch == 1 ? row : row / per_batch;
     for (int k = 0; k < p.k; ++k) {
-      const long long i = clamp_ll(load_as<long long>(p.indices, p.idx_dtype, row * p.k + k), 0, p.dims[k] - 1);
+      const long long i = clamp_ll(load_as<long long>(p.indices, p.idx_dtype, static_cast<long long>(row) * p.k + k), 0,
+                                   p.dims[k] - 1);
       off = off * p.dims[k] + i;
     }
     copy_element(p.out, e, p.tensor, off * p.inner + in, p.elem_bytes);
     return;
   }
-  const long long j = (e / p.inner) % p.n_idx;
-  const long long o = e / (p.inner * p.n_idx);
-  const long long src_base = o * p.axis_len * p.inner + in;
-  if (!dtype_is_float(p.idx_dtype)) {
-    const long long i = clamp_ll(load_as<long long>(p.indices, p.idx_dtype, j), 0, p.axis_len - 1);
-    copy_element(p.out, e, p.tensor, src_base + i * p.inner, p.elem_bytes);
-    return;
-  }
-  const double idx = load_as<double>(p.indices, p.idx_dtype, j);
-  if (!dtype_is_float(p.dtype)) {
-    const long long i = clamp_ll(to_i32(idx), 0, p.axis_len - 1);
-    copy_element(p.out, e, p.tensor, src_base + i * p.inner, p.elem_bytes);
+  const I n_idx = static_cast<I>(p.n_idx);
+  const bool one_outer = static_cast<I>(p.out_elems) == inner * n_idx;
+  const I j = one_outer ? row : row % n_idx;
+  const I o = one_outer ? 0 : row / n_idx;
+  const long long src_base = static_cast<long long>(o) * p.axis_len * p.inner + in;
+  if (p.copies) {
+    // integer positions select; float positions into an integer tensor are truncated
+    const long long at = dtype_is_float(p.idx_dtype) ? to_i32(load_as<double>(p.indices, p.idx_dtype, j))
+                                                     : load_as<long long>(p.indices, p.idx_dtype, j);
+    copy_element(p.out, e, p.tensor, src_base + clamp_ll(at, 0, p.axis_len - 1) * p.inner, p.elem_bytes);
     return;
   }
   switch (p.dtype) {
-    case PMLB_F16: gather_interpolated<ArF16>(p, e, src_base, idx); break;
-    case PMLB_BF16: gather_interpolated<ArBF16>(p, e, src_base, idx); break;
-    case PMLB_F64: gather_interpolated<ArF64>(p, e, src_base, idx); break;
-    default: gather_interpolated<ArF32>(p, e, src_base, idx); break;
+    case PMLB_F16: gather_interpolated<ArF16>(p, e, src_base, j); break;
+    case PMLB_BF16: gather_interpolated<ArBF16>(p, e, src_base, j); break;
+    case PMLB_F64: gather_interpolated<ArF64>(p, e, src_base, j); break;
+    default: gather_interpolated<ArF32>(p, e, src_base, j); break;
   }
 }
 
@@ -301,6 +302,124 @@ __global__ void __launch_bounds__(256) argsort_pass_kernel(const __grid_constant
   dst[line + dest * p.inner] = static_cast<int32_t>(pos_at(j));
 }
 
+// Sorts segments of up to kSortSlots positions in shared memory (a bitonic network over (key, position) pairs, so the
+// order is total and ties keep their original order): whole lines when they fit -- several short lines per block --
+// or 4096-position runs of longer lines, which the merge passes above then combine.
+enum : int { kSortSlots = 4096, kSortThreads = 512 };
+
+template <class V>
+__global__ void __launch_bounds__(kSortThreads) argsort_block_kernel(const __grid_constant__ ArgsortParams p,
+                                                                     int32_t* __restrict__ dst, int seg_len,
+                                                                     long long segs_per_line, long long segments) {
+  __shared__ V keys[kSortSlots];
+  __shared__ int32_t pos[kSortSlots];
+  const int segs_per_block = kSortSlots / seg_len;
+  const long long first_seg = static_cast<long long>(blockIdx.x) * segs_per_block;
+  auto line_base = [&](long long line) { return (line / p.inner) * p.n * p.inner + line % p.inner; };
+  for (int s = threadIdx.x; s < kSortSlots; s += kSortThreads) {
+    const long long seg = first_seg + s / seg_len;
+    const long long q = (seg % segs_per_line) * seg_len + s % seg_len;
+    const bool valid = seg < segments && q < p.n;
+    pos[s] = valid ? static_cast<int32_t>(q) : 0x7FFFFFFF;   // (an empty slot sorts behind every element)
+    keys[s] = valid ? load_as<V>(p.tensor, p.dtype, line_base(seg / segs_per_line) + q * p.inner) : V(0);
+  }
+  __syncthreads();
+  auto goes_first = [&](int a, int b) -> bool {   // slot a's element before slot b's
+    if (pos[a] == 0x7FFFFFFF) return false;
+    if (pos[b] == 0x7FFFFFFF) return true;
+    const V ka = keys[a], kb = keys[b];
+    if (p.descending ? ka > kb : ka < kb) return true;
+    if (p.descending ? kb > ka : kb < ka) return false;
+    return pos[a] < pos[b];
+  };
+  for (int size = 2; size <= seg_len; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < kSortSlots / 2; t += kSortThreads) {
+        const int a = 2 * t - (t & (stride - 1));
+        const int b = a + stride;
+        const bool up = (a & (seg_len - 1) & size) == 0;   // this pair's run is being ordered forwards (the last
+                                                           // stage orders every segment forwards)
+        if (goes_first(b, a) == up) {
+          const V k = keys[a];
+          keys[a] = keys[b];
+          keys[b] = k;
+          const int32_t q = pos[a];
+          pos[a] = pos[b];
+          pos[b] = q;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int s = threadIdx.x; s < kSortSlots; s += kSortThreads) {
+    const long long seg = first_seg + s / seg_len;
+    const long long q = (seg % segs_per_line) * seg_len + s % seg_len;
+    if (seg < segments && q < p.n) dst[line_base(seg / segs_per_line) + q * p.inner] = pos[s];
+  }
+}
+
+// The same network for element types of at most 32 bits: key and position share one 64-bit word -- an order-preserving
+// 32-bit image of the element (inverted for a descending sort) above the position -- so that one integer comparison
+// orders a pair, ties by position included.  -0.0 is ordered as +0.0 (they compare equal); NaNs go to the ends.
+__device__ __forceinline__ uint32_t sortable_bits(const void* base, int dtype, long long i) {
+  switch (dtype) {
+    case PMLB_F32:
+    case PMLB_F16:
+    case PMLB_BF16: {
+      float f = load_as<float>(base, dtype, i);
+      if (f == 0.0f) f = 0.0f;
+      const uint32_t u = __float_as_uint(f);
+      return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    }
+    case PMLB_U32:
+    case PMLB_U16:
+    case PMLB_U8:
+    case PMLB_BOOL: return static_cast<uint32_t>(load_as<long long>(base, dtype, i));
+    default: return static_cast<uint32_t>(load_as<long long>(base, dtype, i)) ^ 0x80000000u;   // signed integers
+  }
+}
+
+__global__ void __launch_bounds__(kSortThreads) argsort_block32_kernel(const __grid_constant__ ArgsortParams p,
+                                                                       int32_t* __restrict__ dst, int seg_len,
+                                                                       long long segs_per_line, long long segments) {
+  __shared__ unsigned long long slot[kSortSlots];
+  const int segs_per_block = kSortSlots / seg_len;
+  const long long first_seg = static_cast<long long>(blockIdx.x) * segs_per_block;
+  auto line_base = [&](long long line) { return (line / p.inner) * p.n * p.inner + line % p.inner; };
+  for (int s = threadIdx.x; s < kSortSlots; s += kSortThreads) {
+    const long long seg = first_seg + s / seg_len;
+    const long long q = (seg % segs_per_line) * seg_len + s % seg_len;
+    unsigned long long v = ~0ull;   // an empty slot sorts behind every element
+    if (seg < segments && q < p.n) {
+      uint32_t key = sortable_bits(p.tensor, p.dtype, line_base(seg / segs_per_line) + q * p.inner);
+      if (p.descending) key = ~key;
+      v = (static_cast<unsigned long long>(key) << 32) | static_cast<uint32_t>(q);
+    }
+    slot[s] = v;
+  }
+  __syncthreads();
+  for (int size = 2; size <= seg_len; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < kSortSlots / 2; t += kSortThreads) {
+        const int a = 2 * t - (t & (stride - 1));
+        const int b = a + stride;
+        const bool up = (a & (seg_len - 1) & size) == 0;
+        const unsigned long long va = slot[a], vb = slot[b];
+        if ((vb < va) == up) {
+          slot[a] = vb;
+          slot[b] = va;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int s = threadIdx.x; s < kSortSlots; s += kSortThreads) {
+    const long long seg = first_seg + s / seg_len;
+    const long long q = (seg % segs_per_line) * seg_len + s % seg_len;
+    if (seg < segments && q < p.n) dst[line_base(seg / segs_per_line) + q * p.inner] = static_cast<int32_t>(slot[s]);
+  }
+}
+
 // ------------------------------------------------------------------ prng
 
 __host__ __device__ __forceinline__ uint32_t prng_step(int c, uint32_t s) {
@@ -326,29 +445,43 @@ __device__ __forceinline__ uint32_t prng_jump(const uint32_t* table, int c, uint
   return s;
 }
 
+// Every thread produces `chunk` consecutive numbers (a multiple of 8), eight at a time so that each 32-byte sector of
+// the result is written whole by one thread.
 __global__ void __launch_bounds__(128) prng_kernel(const uint32_t* __restrict__ state, long long state_elems,
                                                    float* __restrict__ out, long long count,
                                                    uint32_t* __restrict__ new_state,
-                                                   const uint32_t* __restrict__ table, long long threads) {
+                                                   const uint32_t* __restrict__ table, long long threads, int chunk) {
   const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (t >= threads) return;
   // without a place for the numbers only the state after them is wanted: one thread jumps there
-  const long long first = out ? t * kPrngChunk : count;
+  const long long first = out ? t * chunk : count;
   uint32_t s0 = prng_jump(table, 0, state[0], static_cast<unsigned long long>(first));
   uint32_t s1 = prng_jump(table, 1, state[1], static_cast<unsigned long long>(first));
   uint32_t s2 = prng_jump(table, 2, state[2], static_cast<unsigned long long>(first));
-  const long long last = first + kPrngChunk < count ? first + kPrngChunk : count;
-  for (long long i = first; i < last; ++i) {
-    out[i] = static_cast<float>(static_cast<double>(s0 ^ s1 ^ s2) / 4294967296.0);
+  const long long last = first + chunk < count ? first + chunk : count;
+  auto next = [&]() -> float {
+    const float v = static_cast<float>(static_cast<double>(s0 ^ s1 ^ s2) / 4294967296.0);
     s0 = prng_step(0, s0);
     s1 = prng_step(1, s1);
     s2 = prng_step(2, s2);
+    return v;
+  };
+  long long i = first;
+  if (reinterpret_cast<uintptr_t>(out) % 32 == 0) {
+    for (; i + 8 <= last; i += 8) {
+      float4 lo, hi;
+      lo.x = next(); lo.y = next(); lo.z = next(); lo.w = next();
+      hi.x = next(); hi.y = next(); hi.z = next(); hi.w = next();
+      __stcs(reinterpret_cast<float4*>(out + i), lo);
+      __stcs(reinterpret_cast<float4*>(out + i) + 1, hi);
+    }
   }
+  for (; i < last; ++i) out[i] = next();
   if (last == count && new_state) {  // the thread that holds the last element (thread 0 when there are none)
     new_state[0] = s0;
     new_state[1] = s1;
     new_state[2] = s2;
-    for (long long i = 3; i < state_elems; ++i) new_state[i] = state[i];
+    for (long long w = 3; w < state_elems; ++w) new_state[w] = state[w];
   }
 }
 
@@ -356,9 +489,33 @@ unsigned blocks_for(long long n, int threads) { return static_cast<unsigned>((n 
 
 }  // namespace
 
-cudaError_t launch_gather(const GatherParams& p, cudaStream_t stream) {
-  if (p.out_elems <= 0) return cudaSuccess;
-  gather_kernel<<<blocks_for(p.out_elems, 256), 256, 0, stream>>>(p);
+cudaError_t launch_gather(const GatherParams& given, cudaStream_t stream) {
+  if (given.out_elems <= 0) return cudaSuccess;
+  GatherParams p = given;
+  const bool float_idx = p.idx_dtype == PMLB_F16 || p.idx_dtype == PMLB_BF16 || p.idx_dtype == PMLB_F32 || p.idx_dtype == PMLB_F64;
+  const bool float_data = p.dtype == PMLB_F16 || p.dtype == PMLB_BF16 || p.dtype == PMLB_F32 || p.dtype == PMLB_F64;
+  p.copies = p.nd || !float_idx || !float_data;
+  // whole runs of the inner dims move as 16-byte pieces when they and the buffers allow it
+  const long long run_bytes = p.inner * p.elem_bytes;
+  const bool aligned = (reinterpret_cast<uintptr_t>(p.tensor) | reinterpret_cast<uintptr_t>(p.out)) % 16 == 0;
+  if (p.copies && p.elem_bytes < 16 && run_bytes % 16 == 0 && aligned) {
+    p.out_elems = p.out_elems / p.inner * (run_bytes / 16);
+    p.inner = run_bytes / 16;
+    p.elem_bytes = 16;
+  }
+  long long source = p.inner;
+  if (p.nd) {
+    for (int k = 0; k < p.k; ++k) source *= p.dims[k];
+    source *= (p.out_elems / p.inner + p.rows_per_batch - 1) / p.rows_per_batch;
+  } else {
+    source *= p.axis_len * ((p.out_elems / p.inner + p.n_idx - 1) / p.n_idx);
+  }
+  const long long limit = 1LL << 31;
+  if (p.out_elems < limit && source < limit && p.out_elems / p.inner * (p.nd ? p.k : 1) < limit) {
+    gather_kernel<unsigned><<<blocks_for(p.out_elems, 256), 256, 0, stream>>>(p);
+  } else {
+    gather_kernel<unsigned long long><<<blocks_for(p.out_elems, 256), 256, 0, stream>>>(p);
+  }
   return cudaGetLastError();
 }
 
@@ -376,17 +533,32 @@ cudaError_t argsort_passes(const ArgsortParams& p, int32_t* out, int32_t* scratc
   const unsigned blocks = blocks_for(total, 256);
   int passes = 0;
   while ((1LL << passes) < p.n) ++passes;
-  if (passes == 0) {
-    argsort_pass_kernel<V><<<blocks, 256, 0, stream>>>(p, nullptr, out, 0, total);
-    return cudaGetLastError();
+  // runs of up to 4096 positions are sorted in shared memory; longer lines go on with merge passes from there
+  int seg_bits = passes < 12 ? passes : 12;
+  if (seg_bits < 1) seg_bits = 1;
+  const int seg_len = 1 << seg_bits;
+  const long long segs_per_line = (p.n + seg_len - 1) / seg_len;
+  const long long segments = p.outer * p.inner * segs_per_line;
+  const int merges = passes > seg_bits ? passes - seg_bits : 0;
+  int32_t* first = (merges % 2 == 0) ? out : scratch;
+  const long long sort_blocks = (segments + kSortSlots / seg_len - 1) / (kSortSlots / seg_len);
+  const bool narrow = p.dtype != PMLB_F64 && p.dtype != PMLB_I64 && p.dtype != PMLB_U64;
+  if (narrow) {
+    argsort_block32_kernel<<<static_cast<unsigned>(sort_blocks), kSortThreads, 0, stream>>>(p, first, seg_len,
+                                                                                           segs_per_line, segments);
+  } else {
+    argsort_block_kernel<V><<<static_cast<unsigned>(sort_blocks), kSortThreads, 0, stream>>>(p, first, seg_len,
+                                                                                            segs_per_line, segments);
   }
-  for (int k = 0; k < passes; ++k) {
-    // the last pass writes `out`; the passes before it alternate
-    int32_t* dst = ((passes - 1 - k) % 2 == 0) ? out : scratch;
-    const int32_t* src = k == 0 ? nullptr : (dst == out ? scratch : out);
-    argsort_pass_kernel<V><<<blocks, 256, 0, stream>>>(p, src, dst, 1LL << k, total);
-    const cudaError_t e = cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int32_t* src = first;
+  for (int k = 0; k < merges; ++k) {
+    int32_t* dst = src == out ? scratch : out;
+    argsort_pass_kernel<V><<<blocks, 256, 0, stream>>>(p, src, dst, static_cast<long long>(seg_len) << k, total);
+    e = cudaGetLastError();
     if (e != cudaSuccess) return e;
+    src = dst;
   }
   return cudaSuccess;
 }
@@ -407,9 +579,13 @@ cudaError_t launch_argsort(const ArgsortParams& p, int32_t* out, int32_t* scratc
 
 cudaError_t launch_prng(const uint32_t* state, long long state_elems, float* out, long long count, uint32_t* new_state,
                         const uint32_t* table, cudaStream_t stream) {
-  long long threads = out ? (count + kPrngChunk - 1) / kPrngChunk : 1;
+  // longer runs per thread amortise the jump to the run's first element; short ones keep small results parallel
+  int chunk = kPrngChunk;
+  while (chunk < 1024 && count / chunk > 2LL * 148 * 2048) chunk *= 2;
+  long long threads = out ? (count + chunk - 1) / chunk : 1;
   if (threads < 1) threads = 1;
-  prng_kernel<<<blocks_for(threads, 128), 128, 0, stream>>>(state, state_elems, out, count, new_state, table, threads);
+  prng_kernel<<<blocks_for(threads, 128), 128, 0, stream>>>(state, state_elems, out, count, new_state, table, threads,
+                                                           chunk);
   return cudaGetLastError();
 }
 

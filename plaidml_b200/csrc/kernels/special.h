@@ -11,6 +11,7 @@ namespace pmlb {
 struct GatherParams {
   int dtype, idx_dtype, elem_bytes;
   int nd;  // 0: along one axis, 1: the last dim of indices addresses several dims
+  int copies;  // set by the launcher: elements are copied (no interpolation)
   long long out_elems;
   // along one axis: the tensor seen as [outer][axis_len][inner], the indices as a flat list of n_idx
   long long axis_len, inner, n_idx;

@@ -24,6 +24,12 @@ launches of the kernel of interest:
                PLAIDML_CUDA_NO_POOL_FUSION=1 in the environment the two-kernel form (tc_contract_kernel on the
                space-to-depth route, pool16_kernel)
     stem_full  the same at batch 256 (120 MB of packed pixels in, 103 MB out)
+    gather_rows   2 M rows of 64 f32 gathered from a table of 1 M rows (gather_kernel: 8 MB of indices, 512 MB read at
+               random row granularity, 512 MB written)
+    gather_lin    64 M linearly interpolated samples of a 16 M-element f32 signal (256 MB of positions in, 256 MB out)
+    scatter_add   16 M f32 updates added into 4 M cells (64 MB + 64 MB in, one 16 MB copy, atomics)
+    argsort       4096 lines of 4096 f32 sorted along the line (12 merge passes of argsort_pass_kernel)
+    prng          256 M numbers (prng_kernel: 1 GiB written) and the state after them
     resnet N   ResNet-50 v1.5 at batch N
     resnet_steps N   the same, followed by a table of every kernel step on its own (CUDA events around 20 launches
                of the step replayed from a CUDA graph: device time without the host's launch cost) beside the time of
@@ -107,6 +113,32 @@ def main(argv) -> None:
         y = op.pool(y, op.PoolMode.MAX, [3, 3], [2, 2], op.AutoPadMode.EXPLICIT, [1, 1, 1, 1], op.TensorLayout.NXC)
         r = Runner(Program(case, [I], [y]), "cuda.0")
         ins = [f32_to_bf16_bits(g.uniform(0, 1, (nimg, 224, 224, 3)).astype(np.float32))]
+    elif case in ("gather_rows", "gather_lin", "scatter_add", "argsort", "prng"):
+        from plaidml_b200 import edsl
+        from plaidml_b200.edsl import Placeholder
+        if case == "gather_rows":
+            T, I = Placeholder(DType.FLOAT32, [1 << 20, 64]), Placeholder(DType.INT32, [1 << 21])
+            r = Runner(Program(case, [T, I], [edsl.gather(T, I)]), "cuda.0")
+            ins = [g.standard_normal((1 << 20, 64), dtype=np.float32), g.integers(0, 1 << 20, 1 << 21, dtype=np.int32)]
+        elif case == "gather_lin":
+            T, I = Placeholder(DType.FLOAT32, [1 << 24]), Placeholder(DType.FLOAT32, [1 << 26])
+            r = Runner(Program(case, [T, I], [edsl.gather(T, I, interpolation_mode=edsl.InterpolationMode.LINEAR)]), "cuda.0")
+            pos = (np.arange(1 << 26, dtype=np.float64) * 0.25 + g.uniform(0, 0.25, 1 << 26)).astype(np.float32)
+            ins = [g.standard_normal(1 << 24, dtype=np.float32), pos]
+        elif case == "scatter_add":
+            D, I, U = (Placeholder(DType.FLOAT32, [1 << 22]), Placeholder(DType.INT32, [1 << 24]),
+                       Placeholder(DType.FLOAT32, [1 << 24]))
+            r = Runner(Program(case, [D, I, U], [edsl.scatter(D, I, U)]), "cuda.0")
+            ins = [np.zeros(1 << 22, np.float32), g.integers(0, 1 << 22, 1 << 24, dtype=np.int32),
+                   g.standard_normal(1 << 24, dtype=np.float32)]
+        elif case == "argsort":
+            X = Placeholder(DType.FLOAT32, [4096, 4096])
+            r = Runner(Program(case, [X], [edsl.argsort(X, 1)]), "cuda.0")
+            ins = [g.standard_normal((4096, 4096), dtype=np.float32)]
+        else:
+            S = Placeholder(DType.UINT32, [3])
+            r = Runner(Program(case, [S], list(edsl.prng(S, [1 << 28]))), "cuda.0")
+            ins = [np.array([5, 6, 7], dtype=np.uint32)]
     elif case in ("resnet", "resnet_steps"):
         batch = int(argv[2]) if len(argv) > 2 else 32
         prog, _ = programs.resnet50(batch)
@@ -131,6 +163,9 @@ def main(argv) -> None:
             print(f"{t * 1e3:8.1f} us  {line}")
     else:
         print(r.executable.describe())
+        if case in ("gather_rows", "gather_lin", "scatter_add", "argsort", "prng"):
+            for line, t in r.executable.time_each_step(20, False):
+                print(f"{t * 1e3:8.1f} us  {line}")
 
 
 if __name__ == "__main__":
