@@ -44,19 +44,35 @@ __device__ __forceinline__ long long to_i32(float v) { return __float2int_rz(v);
 
 struct ArF32 {
   using T = float;
+  enum : int { kDtype = PMLB_F32 };
   static __device__ __forceinline__ T r(T x) { return x; }
+  static __device__ __forceinline__ T load(const void* b, long long i) { return static_cast<const float*>(b)[i]; }
+  static __device__ __forceinline__ void store(void* b, long long i, T v) { static_cast<float*>(b)[i] = v; }
 };
 struct ArF16 {
   using T = float;
+  enum : int { kDtype = PMLB_F16 };
   static __device__ __forceinline__ T r(T x) { return __half2float(__float2half_rn(x)); }
+  static __device__ __forceinline__ T load(const void* b, long long i) { return __half2float(static_cast<const __half*>(b)[i]); }
+  static __device__ __forceinline__ void store(void* b, long long i, T v) { static_cast<__half*>(b)[i] = __float2half_rn(v); }
 };
 struct ArBF16 {
   using T = float;
+  enum : int { kDtype = PMLB_BF16 };
   static __device__ __forceinline__ T r(T x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+  static __device__ __forceinline__ T load(const void* b, long long i) {
+    return __bfloat162float(static_cast<const __nv_bfloat16*>(b)[i]);
+  }
+  static __device__ __forceinline__ void store(void* b, long long i, T v) {
+    static_cast<__nv_bfloat16*>(b)[i] = __float2bfloat16_rn(v);
+  }
 };
 struct ArF64 {
   using T = double;
+  enum : int { kDtype = PMLB_F64 };
   static __device__ __forceinline__ T r(T x) { return x; }
+  static __device__ __forceinline__ T load(const void* b, long long i) { return static_cast<const double*>(b)[i]; }
+  static __device__ __forceinline__ void store(void* b, long long i, T v) { static_cast<double*>(b)[i] = v; }
 };
 
 __device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
@@ -72,14 +88,13 @@ struct Arith {
   static __device__ __forceinline__ T sub(T a, T b) { return A::r(add_rn(a, -b)); }
 };
 
-// One interpolated value: `idx` is the (float) index along the axis, `at(i)` the element at axis position i.
-template <class A, class At>
-__device__ __forceinline__ typename A::T interpolate(const GatherParams& p, typename A::T idx, At at) {
+// An interpolated value in two parts, so that a thread can have the loads of several values in flight: the axis
+// positions the value reads (1 for nearest, 2 for linear, 4 for cubic; clamped to the axis) ...
+template <class A>
+__device__ __forceinline__ void neighbours(const GatherParams& p, typename A::T idx, long long pos[4]) {
   using T = typename A::T;
-  using M = Arith<A>;
   const long long hi = p.axis_len - 1;
   const T fl = floor(idx);
-  T result;
   if (p.interpolation == 0) {
     long long i;
     const bool half = idx == A::r(add_rn(fl, T(0.5)));
@@ -91,20 +106,34 @@ __device__ __forceinline__ typename A::T interpolate(const GatherParams& p, type
       case 3: i = to_i32(ceil(idx)); break;
       default: i = to_i32(idx); break;
     }
-    result = at(clamp_ll(i, 0, hi));
+    pos[0] = clamp_ll(i, 0, hi);
   } else if (p.interpolation == 1) {
-    const T g0 = at(clamp_ll(to_i32(ceil(idx)), 0, hi));
-    const T g1 = at(clamp_ll(to_i32(fl), 0, hi));
+    pos[0] = clamp_ll(to_i32(ceil(idx)), 0, hi);
+    pos[1] = clamp_ll(to_i32(fl), 0, hi);
+  } else {
+    const long long fi = to_i32(fl), ci = to_i32(ceil(idx));
+    pos[0] = clamp_ll(fi - 1, 0, hi);
+    pos[1] = clamp_ll(fi, 0, hi);
+    pos[2] = clamp_ll(ci, 0, hi);
+    pos[3] = clamp_ll(ci + 1, 0, hi);
+  }
+}
+
+// ... and the value from the elements at those positions.
+template <class A>
+__device__ __forceinline__ typename A::T blend(const GatherParams& p, typename A::T idx, const typename A::T g[4]) {
+  using T = typename A::T;
+  using M = Arith<A>;
+  const T fl = floor(idx);
+  T result;
+  if (p.interpolation == 0) {
+    result = g[0];
+  } else if (p.interpolation == 1) {
     const T c0 = M::sub(idx, fl);
     const T c1 = M::sub(T(1), c0);
-    result = M::add(M::mul(c0, g0), M::mul(c1, g1));
+    result = M::add(M::mul(c0, g[0]), M::mul(c1, g[1]));
   } else {
     const T a = A::r(static_cast<T>(p.cube_coeff));
-    const long long fi = to_i32(fl), ci = to_i32(ceil(idx));
-    const T g0 = at(clamp_ll(fi - 1, 0, hi));
-    const T g1 = at(clamp_ll(fi, 0, hi));
-    const T g2 = at(clamp_ll(ci, 0, hi));
-    const T g3 = at(clamp_ll(ci + 1, 0, hi));
     const T s = M::sub(idx, fl);
     const T s2 = M::mul(s, s);
     const T s3 = M::mul(s2, s);
@@ -118,21 +147,58 @@ __device__ __forceinline__ typename A::T interpolate(const GatherParams& p, type
     const T p1 = M::add(M::sub(s3_a2, s2_a3), T(1));
     const T p2 = M::sub(M::sub(s2_2a3, s3_a2), s_a);
     const T p3 = M::sub(s2_a, s3_a);
-    result = M::add(M::add(M::add(M::mul(p0, g0), M::mul(p1, g1)), M::mul(p2, g2)), M::mul(p3, g3));
+    result = M::add(M::add(M::add(M::mul(p0, g[0]), M::mul(p1, g[1])), M::mul(p2, g[2])), M::mul(p3, g[3]));
   }
-  if (p.out_of_bounds == 1 && (idx > static_cast<T>(hi) || idx < T(0))) result = T(0);
+  if (p.out_of_bounds == 1 && (idx > static_cast<T>(p.axis_len - 1) || idx < T(0))) result = T(0);
   return result;
 }
 
-template <class A>
-__device__ __forceinline__ void gather_interpolated(const GatherParams& p, long long e, long long src_base, long long j) {
+// Interpolating gather along one axis: four results per thread, a grid apart, computed into registers before any of
+// them is stored, so that the four chains position -> neighbours -> value are in flight together.
+template <class A, class I>
+__global__ void __launch_bounds__(256) gather_interp_kernel(const __grid_constant__ GatherParams p, I threads) {
   using T = typename A::T;
-  auto at = [&](long long i) -> T { return load_as<T>(p.tensor, p.dtype, src_base + i * p.inner); };
-  const T v = interpolate<A>(p, A::r(load_as<T>(p.indices, p.idx_dtype, j)), at);
-  store_as<T>(p.out, p.dtype, e, v);
+  const I t = static_cast<I>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= threads) return;
+  const I total = static_cast<I>(p.out_elems);
+  const I inner = static_cast<I>(p.inner);
+  const I n_idx = static_cast<I>(p.n_idx);
+  const bool one_outer = total == inner * n_idx;
+  const bool same_type = p.idx_dtype == A::kDtype;
+  const int reads = p.interpolation == 0 ? 1 : (p.interpolation == 1 ? 2 : 4);
+  T idx[4];
+  long long base[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    I e = t + static_cast<I>(u) * threads;
+    if (e >= total) e = total - 1;   // (a spare slot repeats the last element; it is not stored)
+    const I in = inner == 1 ? 0 : e % inner;
+    const I row = inner == 1 ? e : e / inner;
+    const I j = one_outer ? row : row % n_idx;
+    const I o = one_outer ? 0 : row / n_idx;
+    base[u] = static_cast<long long>(o) * p.axis_len * p.inner + in;
+    idx[u] = same_type ? A::load(p.indices, j) : A::r(load_as<T>(p.indices, p.idx_dtype, j));
+  }
+  T g[4][4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    long long pos[4] = {0, 0, 0, 0};
+    neighbours<A>(p, idx[u], pos);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) g[u][k] = k < reads ? A::load(p.tensor, base[u] + pos[k] * p.inner) : T(0);
+  }
+  T res[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) res[u] = blend<A>(p, idx[u], g[u]);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const I e = t + static_cast<I>(u) * threads;
+    if (e < total) A::store(p.out, e, res[u]);
+  }
 }
 
-// `I` is the type of the position arithmetic: 32 bits when every extent fits, else 64.
+// Copying gather (integer positions, nd mode).  `I` is the type of the position arithmetic: 32 bits when every extent
+// fits, else 64.
 template <class I>
 __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ GatherParams p) {
   const I e = static_cast<I>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -156,19 +222,10 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Gat
   const I j = one_outer ? row : row % n_idx;
   const I o = one_outer ? 0 : row / n_idx;
   const long long src_base = static_cast<long long>(o) * p.axis_len * p.inner + in;
-  if (p.copies) {
-    // integer positions select; float positions into an integer tensor are truncated
-    const long long at = dtype_is_float(p.idx_dtype) ? to_i32(load_as<double>(p.indices, p.idx_dtype, j))
-                                                     : load_as<long long>(p.indices, p.idx_dtype, j);
-    copy_element(p.out, e, p.tensor, src_base + clamp_ll(at, 0, p.axis_len - 1) * p.inner, p.elem_bytes);
-    return;
-  }
-  switch (p.dtype) {
-    case PMLB_F16: gather_interpolated<ArF16>(p, e, src_base, j); break;
-    case PMLB_BF16: gather_interpolated<ArBF16>(p, e, src_base, j); break;
-    case PMLB_F64: gather_interpolated<ArF64>(p, e, src_base, j); break;
-    default: gather_interpolated<ArF32>(p, e, src_base, j); break;
-  }
+  // integer positions select; float positions into an integer tensor are truncated
+  const long long at = dtype_is_float(p.idx_dtype) ? to_i32(load_as<double>(p.indices, p.idx_dtype, j))
+                                                   : load_as<long long>(p.indices, p.idx_dtype, j);
+  copy_element(p.out, e, p.tensor, src_base + clamp_ll(at, 0, p.axis_len - 1) * p.inner, p.elem_bytes);
 }
 
 // ------------------------------------------------------------------ scatter
@@ -511,11 +568,24 @@ cudaError_t launch_gather(const GatherParams& given, cudaStream_t stream) {
     source *= p.axis_len * ((p.out_elems / p.inner + p.n_idx - 1) / p.n_idx);
   }
   const long long limit = 1LL << 31;
-  if (p.out_elems < limit && source < limit && p.out_elems / p.inner * (p.nd ? p.k : 1) < limit) {
-    gather_kernel<unsigned><<<blocks_for(p.out_elems, 256), 256, 0, stream>>>(p);
-  } else {
-    gather_kernel<unsigned long long><<<blocks_for(p.out_elems, 256), 256, 0, stream>>>(p);
+  const bool narrow = p.out_elems < limit && source < limit && p.out_elems / p.inner * (p.nd ? p.k : 1) < limit;
+  if (p.copies) {
+    if (narrow) gather_kernel<unsigned><<<blocks_for(p.out_elems, 256), 256, 0, stream>>>(p);
+    else gather_kernel<unsigned long long><<<blocks_for(p.out_elems, 256), 256, 0, stream>>>(p);
+    return cudaGetLastError();
   }
+  const long long threads = (p.out_elems + 3) / 4;
+  const unsigned blocks = blocks_for(threads, 256);
+#define PMLB_INTERP(A)                                                                                              \
+  if (narrow) gather_interp_kernel<A, unsigned><<<blocks, 256, 0, stream>>>(p, static_cast<unsigned>(threads));     \
+  else gather_interp_kernel<A, unsigned long long><<<blocks, 256, 0, stream>>>(p, static_cast<unsigned long long>(threads))
+  switch (p.dtype) {
+    case PMLB_F16: PMLB_INTERP(ArF16); break;
+    case PMLB_BF16: PMLB_INTERP(ArBF16); break;
+    case PMLB_F64: PMLB_INTERP(ArF64); break;
+    default: PMLB_INTERP(ArF32); break;
+  }
+#undef PMLB_INTERP
   return cudaGetLastError();
 }
 
