@@ -118,67 +118,73 @@ def test_gather_nd_matches_the_restatement(seed):
     np.testing.assert_array_equal(got, want)
 
 
-@pytest.mark.parametrize("seed", range(16))
-def test_scatter_matches_the_restatement(seed):
+def scatter_case(seed):
+    """Seeded data / indices / updates for one scatter mode; storing modes get distinct destinations (with equal
+    destinations one of the updates stays, which no comparison can pin), the adding mode gets duplicates."""
     g = rng(4200 + seed)
     mode = seed % 4
     tdt = [np.float32, np.int32, np.float16, np.int8, np.float64, np.int64, np.int16, np.uint8][seed % 8]
-    if mode in (0, 2):
+    if mode == 0:
+        rank = int(g.integers(1, 4))
+        data_shape = [int(v) for v in g.integers(2, 9, rank)]
+        axis = int(g.integers(0, rank))
+        upd_shape = [int(g.integers(1, n + 1)) for n in data_shape]
+        idx_shape = upd_shape[:int(g.integers(1, rank + 1))]
+        idx = g.integers(-1, data_shape[axis] + 1, idx_shape).astype(np.int32)      # duplicates add up, some land outside
+    elif mode == 2:
         rank = int(g.integers(1, 4))
         data_shape = [int(v) for v in g.integers(2, 9, rank)]
         axis = int(g.integers(0, rank))
         upd_shape = [int(g.integers(1, n + 1)) for n in data_shape]
         idx_rank = int(g.integers(1, rank + 1))
+        if axis >= idx_rank:
+            upd_shape[axis] = 1          # the index does not depend on the axis coordinate: one update per line
         idx_shape = upd_shape[:idx_rank]
+        perm = g.permutation(data_shape[axis] + 1)       # (one value points outside)
+        along = np.arange(idx_shape[axis]) if axis < idx_rank else np.zeros(1, dtype=np.int64)
+        shape = [1] * idx_rank
+        if axis < idx_rank:
+            shape[axis] = idx_shape[axis]
+        idx = np.broadcast_to(perm[along].reshape(shape), idx_shape).astype(np.int32)
     elif mode == 1:
         rank = int(g.integers(1, 4))
         data_shape = [int(v) for v in g.integers(2, 9, rank)]
         axis = int(g.integers(0, rank))
-        idx_shape = [int(v) for v in g.integers(1, 5, int(g.integers(1, 3)))]
+        data_shape[axis] = int(g.integers(6, 12))
+        idx_shape = [[2], [3], [2, 2], [5], [3, 2]][int(g.integers(0, 5))]
         upd_shape = [int(g.integers(1, n + 1)) for n in data_shape[:axis]] + idx_shape + \
                     [int(g.integers(1, n + 1)) for n in data_shape[axis + 1:]]
+        n = int(np.prod(idx_shape))
+        idx = g.permutation(data_shape[axis] + 1)[:n].reshape(idx_shape).astype(np.int32)
     else:
         rank = int(g.integers(1, 5))
         data_shape = [int(v) for v in g.integers(2, 7, rank)]
         axis = 0
         k = int(g.integers(1, rank + 1))
+        cells = int(np.prod(data_shape[:k]))
         lead = [int(v) for v in g.integers(1, 5, int(g.integers(1, 3)))]
+        while int(np.prod(lead)) > cells + 1:
+            lead = lead[:-1] if len(lead) > 1 else [cells]
         idx_shape = lead + [k]
         upd_shape = lead + [int(g.integers(1, n + 1)) for n in data_shape[k:]]
+        rows = int(np.prod(lead))
+        pick = g.permutation(cells + 1)[:rows]
+        coords = np.stack(np.unravel_index(np.minimum(pick, cells - 1), data_shape[:k]), axis=-1)
+        coords[pick == cells] = data_shape[0]          # one row may point outside: dropped
+        idx = coords.reshape(idx_shape).astype(np.int32)
     # small integer values: sums are exact in every type and order
     data = g.integers(0, 3, data_shape).astype(tdt)
     upd = g.integers(1, 4, upd_shape).astype(tdt)
-    if mode == 3:
-        rows = int(np.prod(idx_shape[:-1]))
-        cells = int(np.prod(data_shape[:k]))
-        # storing mode: distinct destinations (one extra row may point outside and is dropped)
-        pick = g.permutation(cells + 1)[:rows] if rows <= cells + 1 else None
-        if pick is None:
-            pytest.skip("more index rows than destinations")
-        coords = np.stack(np.unravel_index(np.minimum(pick, cells - 1), data_shape[:k]), axis=-1)
-        coords[pick == cells] = data_shape[0]          # outside
-        idx = coords.reshape(idx_shape).astype(np.int32)
-    elif mode == 0:
-        idx = g.integers(-1, data_shape[axis] + 1, idx_shape).astype(np.int32)      # duplicates add up
-    else:
-        n = int(np.prod(idx_shape))
-        if n > data_shape[axis] + 1:
-            pytest.skip("more indices than destinations along the axis")
-        idx = g.permutation(data_shape[axis] + 1)[:n].reshape(idx_shape).astype(np.int32)
-        if mode == 2 and len(idx_shape) > 1:
-            pass   # element mode: every update has its own index entry; rows may still collide off the axis
+    return data, idx, upd, axis, mode
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_scatter_matches_the_restatement(seed):
+    data, idx, upd, axis, mode = scatter_case(seed)
     want = S.scatter(data, idx, upd, axis, mode)
-    if mode == 2:
-        # distinct destinations are needed for a storing mode: recount and skip colliding draws
-        seen = set()
-        for c in np.ndindex(*upd_shape):
-            dst = list(c)
-            dst[axis] = int(idx[c[:len(idx_shape)]])
-            if tuple(dst) in seen:
-                pytest.skip("colliding destinations in a storing mode")
-            seen.add(tuple(dst))
-    d = K.special_desc(K.SPECIAL_SCATTER, K_OF[np.dtype(tdt)], data_shape, K.I32, idx_shape, upd_shape, axis=axis, mode=mode)
-    got, _ = run_special(d, [data, idx, upd], data_shape, tdt)
+    d = K.special_desc(K.SPECIAL_SCATTER, K_OF[data.dtype], list(data.shape), K.I32, list(idx.shape), list(upd.shape),
+                       axis=axis, mode=mode)
+    got, _ = run_special(d, [data, idx, upd], data.shape, data.dtype)
     np.testing.assert_array_equal(got, want)
 
 
