@@ -5,6 +5,7 @@
 
 #include <functional>
 #include <iostream>
+#include <limits>   // (googletest's own header brings it in; one of the reference's examples relies on that)
 #include <string>
 #include <vector>
 

@@ -7,6 +7,8 @@ tests/host/refshim/ replace googletest, gflags and three LLVM ADT headers, nothi
   * plaidml/edsl/tests/edsl_test.cc: the reference's whole C++ EDSL suite, 119 tests with their own checkExact /
     checkClose / EXPECT_* expectations (contractions, element-wise operations, layers, gather / scatter / argsort /
     prng): all pass;
+  * plaidml/edsl/examples/{complex_conv_2d,conv_1d,conv_2d_dilated,gemv,max_pool_1d,quantize}.cc and
+    plaidml/edsl/edsl_docs.cc (the code blocks of the documentation): 23 tests, all pass;
   * plaidml/op/op_test.cc: the reference's op-library suite, 60 tests (67 with the parameterised convolution cases),
     among them exact expected outputs for explicit paddings, transposed and grouped convolutions and a sort: all pass.
 
@@ -34,6 +36,12 @@ BINARIES = {
     "ref_resnet": (["networks/oplib/resnet50.cc"], ["-DPMLB_REF_RESNET"]),
     "ref_edsl": (["plaidml/edsl/tests/edsl_test.cc"], []),
     "ref_op": (["plaidml/op/op_test.cc"], []),
+    # the other EDSL examples (gemm.cc has its own binary above) and the documentation's code blocks
+    # (not taken: plaidml/exec/tests/list_devices_test.cc, one test that looks for the device "llvm_cpu.0")
+    "ref_examples": (["plaidml/edsl/examples/complex_conv_2d.cc", "plaidml/edsl/examples/conv_1d.cc",
+                      "plaidml/edsl/examples/conv_2d_dilated.cc", "plaidml/edsl/examples/gemv.cc",
+                      "plaidml/edsl/examples/max_pool_1d.cc", "plaidml/edsl/examples/quantize.cc",
+                      "plaidml/edsl/edsl_docs.cc"], []),
 }
 
 def _check_edsl_suite(out: str) -> None:
@@ -73,7 +81,8 @@ def test_reference_sources_compile_and_build_their_programs():
         pytest.skip("PLAIDML_REFERENCE_DIR does not point at a checkout of the reference")
     if shutil.which("g++") is None or not (LIB_DIR / "libplaidml.so").exists():
         pytest.skip("needs g++ and a built libplaidml.so")
-    gemm, resnet, edsl_suite, op_suite = build_binaries(Path(ref))
+    gemm, resnet, edsl_suite, op_suite, examples = build_binaries(Path(ref))
+    assert "23 tests, 0 failures" in _run(examples, "--build-only")
     _check_edsl_suite(_run(edsl_suite, "--build-only"))
     _check_op_suite(_run(op_suite, "--build-only"))
     out = _run(gemm, "--build-only")
@@ -103,3 +112,8 @@ def test_reference_sources_run_on_the_cuda_device():
         out = _run(OUT / "ref_op", "--device", "cuda.0")
         assert "build only" not in out
         _check_op_suite(out)
+    if (OUT / "ref_examples").exists():
+        # the remaining EDSL examples (1-D / dilated / complex convolutions, GEMV, max pool, quantisation) and the
+        # code blocks of the reference's documentation
+        out = _run(OUT / "ref_examples", "--device", "cuda.0")
+        assert "23 tests, 0 failures" in out and "build only" not in out
