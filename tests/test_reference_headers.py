@@ -9,6 +9,8 @@ tests/host/refshim/ replace googletest, gflags and three LLVM ADT headers, nothi
     prng): all pass;
   * plaidml/edsl/examples/{complex_conv_2d,conv_1d,conv_2d_dilated,gemv,max_pool_1d,quantize}.cc and
     plaidml/edsl/edsl_docs.cc (the code blocks of the documentation): 23 tests, all pass;
+  * networks/oplib/benchmark.cc: the reference's ResNet-50 benchmark program (with its own main(); a stand-in for Google
+    Benchmark under refshim/benchmark/ runs and times the registered benchmarks);
   * plaidml/op/op_test.cc: the reference's op-library suite, 60 tests (67 with the parameterised convolution cases),
     among them exact expected outputs for explicit paddings, transposed and grouped convolutions and a sort: all pass.
 
@@ -42,6 +44,8 @@ BINARIES = {
                       "plaidml/edsl/examples/conv_2d_dilated.cc", "plaidml/edsl/examples/gemv.cc",
                       "plaidml/edsl/examples/max_pool_1d.cc", "plaidml/edsl/examples/quantize.cc",
                       "plaidml/edsl/edsl_docs.cc"], []),
+    # the reference's ResNet-50 benchmark program (its own main(); Google Benchmark replaced by refshim/benchmark/)
+    "ref_benchmark": (["networks/oplib/benchmark.cc", "networks/oplib/resnet50.cc"], ["-DPMLB_OWN_MAIN"]),
 }
 
 def _check_edsl_suite(out: str) -> None:
@@ -55,8 +59,9 @@ def build_binaries(ref_dir: Path) -> list:
     OUT.mkdir(parents=True, exist_ok=True)
     built = []
     for name, (sources, defines) in BINARIES.items():
+        driver = [] if "-DPMLB_OWN_MAIN" in defines else [str(HOST / "ref_driver.cc")]
         cmd = ["g++", "-std=c++17", "-O1", "-w", *defines, "-I", str(HOST / "refshim"), "-I", str(ref_dir), "-o", str(OUT / name),
-               str(HOST / "ref_driver.cc"), *[str(ref_dir / s) for s in sources], "-L", str(LIB_DIR), "-l:libplaidml.so",
+               *driver, *[str(ref_dir / s) for s in sources], "-L", str(LIB_DIR), "-l:libplaidml.so",
                "-Wl,-rpath,$ORIGIN/../../../plaidml_b200"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         assert res.returncode == 0, res.stderr[-4000:]
@@ -81,7 +86,7 @@ def test_reference_sources_compile_and_build_their_programs():
         pytest.skip("PLAIDML_REFERENCE_DIR does not point at a checkout of the reference")
     if shutil.which("g++") is None or not (LIB_DIR / "libplaidml.so").exists():
         pytest.skip("needs g++ and a built libplaidml.so")
-    gemm, resnet, edsl_suite, op_suite, examples = build_binaries(Path(ref))
+    gemm, resnet, edsl_suite, op_suite, examples, _benchmark = build_binaries(Path(ref))   # (the benchmark needs a device)
     assert "23 tests, 0 failures" in _run(examples, "--build-only")
     _check_edsl_suite(_run(edsl_suite, "--build-only"))
     _check_op_suite(_run(op_suite, "--build-only"))
@@ -112,6 +117,12 @@ def test_reference_sources_run_on_the_cuda_device():
         out = _run(OUT / "ref_op", "--device", "cuda.0")
         assert "build only" not in out
         _check_op_suite(out)
+    if (OUT / "ref_benchmark").exists():
+        # networks/oplib/benchmark.cc: compile and run of the reference's ResNet-50 (batch 1, fp32, 109 host buffers per run)
+        env = dict(os.environ, PLAIDML_TARGET="cuda", PLAIDML_DEVICE="cuda.0", PMLB_BENCH_ITERS="12")
+        res = subprocess.run([str(OUT / "ref_benchmark")], capture_output=True, text=True, timeout=600, env=env)
+        assert res.returncode == 0, (res.stdout[-2000:], res.stderr[-2000:])
+        assert "resnet50/compile: 12 iterations" in res.stdout and "resnet50/run: 12 iterations" in res.stdout, res.stdout
     if (OUT / "ref_examples").exists():
         # the remaining EDSL examples (1-D / dilated / complex convolutions, GEMV, max pool, quantisation) and the
         # code blocks of the reference's documentation
