@@ -45,6 +45,69 @@ split_tf32_pair_kernel(SplitTf32Args a, SplitTf32Args b, int a_gx, int a_gy, int
                   s.hi, s.lo, s.out_ld, s.out_batch, s.rows, s.cols, s.transpose);
 }
 
+__device__ __forceinline__ void split4(const float4& v, float4* h, float4* l) {
+  h->x = tf32_round(v.x);
+  h->y = tf32_round(v.y);
+  h->z = tf32_round(v.z);
+  h->w = tf32_round(v.w);
+  l->x = tf32_round(v.x - h->x);
+  l->y = tf32_round(v.y - h->y);
+  l->z = tf32_round(v.z - h->z);
+  l->w = tf32_round(v.w - h->w);
+}
+
+// The same split on 64 x 64 tiles with 16-byte loads and stores, for operands whose rows, leading dimensions and
+// addresses are multiples of four floats (the launcher checks): a plain operand needs no shared memory at all, a
+// transposed one is read in rows of the input and written in rows of the output.
+__global__ void __launch_bounds__(256)
+split_tf32_pair64_kernel(SplitTf32Args a, SplitTf32Args b, int a_gx, int a_gy, int b_gx, int b_gy) {
+  __shared__ float tile[64][65];
+  const bool first = static_cast<int>(blockIdx.z) < a.batch;
+  const SplitTf32Args& s = first ? a : b;
+  if (static_cast<int>(blockIdx.x) >= (first ? a_gx : b_gx) || static_cast<int>(blockIdx.y) >= (first ? a_gy : b_gy)) return;
+  const long long bz = first ? blockIdx.z : blockIdx.z - a.batch;
+  const float* __restrict__ src = s.in + bz * s.in_batch;
+  float* __restrict__ dhi = s.hi + bz * s.out_batch;
+  float* __restrict__ dlo = s.lo + bz * s.out_batch;
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const int tq = threadIdx.x & 15, tr = threadIdx.x >> 4;   // 16 quads per tile row, 16 tile rows per step
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!s.transpose) {
+    for (int i = tr; i < 64; i += 16) {
+      const int r = r0 + i, c = c0 + tq * 4;
+      if (r < s.rows && c < s.out_ld) {
+        const float4 v = c < s.cols ? *reinterpret_cast<const float4*>(src + static_cast<long long>(r) * s.ld + c) : zero;
+        float4 h, l;
+        split4(v, &h, &l);
+        *reinterpret_cast<float4*>(dhi + static_cast<long long>(r) * s.out_ld + c) = h;
+        *reinterpret_cast<float4*>(dlo + static_cast<long long>(r) * s.out_ld + c) = l;
+      }
+    }
+    return;
+  }
+  for (int i = tr; i < 64; i += 16) {
+    const int r = r0 + i, c = c0 + tq * 4;
+    const float4 v = (r < s.rows && c < s.cols) ? *reinterpret_cast<const float4*>(src + static_cast<long long>(r) * s.ld + c)
+                                                : zero;
+    tile[i][tq * 4 + 0] = v.x;
+    tile[i][tq * 4 + 1] = v.y;
+    tile[i][tq * 4 + 2] = v.z;
+    tile[i][tq * 4 + 3] = v.w;
+  }
+  __syncthreads();
+  for (int i = tr; i < 64; i += 16) {
+    // output row = input column c0 + i; four output columns = input rows r0 + 4 tq .. + 3 (zeros past the input's rows)
+    const int oc = c0 + i, orow = r0 + tq * 4;
+    if (oc < s.cols && orow < s.out_ld) {
+      const float4 v = make_float4(tile[tq * 4 + 0][i], tile[tq * 4 + 1][i], tile[tq * 4 + 2][i], tile[tq * 4 + 3][i]);
+      float4 h, l;
+      split4(v, &h, &l);
+      *reinterpret_cast<float4*>(dhi + static_cast<long long>(oc) * s.out_ld + orow) = h;
+      *reinterpret_cast<float4*>(dlo + static_cast<long long>(oc) * s.out_ld + orow) = l;
+    }
+  }
+}
+
 __device__ __forceinline__ void split_tf32_tile(float (&tile)[32][33], int b, int bx, int by,
                                                 const float* __restrict__ in, long long ld,
                                                 long long in_batch, float* __restrict__ hi,
@@ -382,10 +445,25 @@ void split_grid(const SplitTf32Args& s, int* gx, int* gy) {
 }
 }  // namespace
 
+namespace {
+bool quads_ok(const SplitTf32Args& s) {
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(s.in) | reinterpret_cast<uintptr_t>(s.hi) | reinterpret_cast<uintptr_t>(s.lo);
+  return bits % 16 == 0 && s.ld % 4 == 0 && s.in_batch % 4 == 0 && s.out_ld % 4 == 0 && s.out_batch % 4 == 0 && s.cols % 4 == 0;
+}
+}  // namespace
+
 cudaError_t launch_split_tf32_pair(const SplitTf32Args& a, const SplitTf32Args& b, cudaStream_t stream) {
   int agx, agy, bgx, bgy;
   split_grid(a, &agx, &agy);
   split_grid(b, &bgx, &bgy);
+  if (quads_ok(a) && quads_ok(b)) {
+    const int ax = (agx + 1) / 2, ay = (agy + 1) / 2, bx = (bgx + 1) / 2, by = (bgy + 1) / 2;   // 64-wide tiles
+    dim3 grid64(ax > bx ? ax : bx, ay > by ? ay : by, a.batch + b.batch);
+    if (grid64.y <= 65535u && grid64.z <= 65535u) {
+      split_tf32_pair64_kernel<<<grid64, 256, 0, stream>>>(a, b, ax, ay, bx, by);
+      return cudaGetLastError();
+    }
+  }
   dim3 grid(agx > bgx ? agx : bgx, agy > bgy ? agy : bgy, a.batch + b.batch);
   if (grid.y > 65535u || grid.z > 65535u) {
     cudaError_t e = launch_split_tf32(a.in, a.ld, a.in_batch, a.hi, a.lo, a.out_ld, a.out_batch, a.rows, a.cols,
