@@ -283,6 +283,11 @@ size_t pmlb_exec_launch_count(plaidml_error* err, plaidml_executable* exec);
 /* 1 once the kernel sequence has been captured into a CUDA graph and passes replay it (from the
  * second pass on, for programs of two or more steps, unless PLAIDML_CUDA_GRAPH=0), else 0. */
 int pmlb_exec_uses_graph(plaidml_error* err, plaidml_executable* exec);
+/* Number of groups plaidml_executable_run uploads the inputs in (known after the first run).  1: all inputs, then the
+ * kernels.  More: the program has several inputs first used at different depths (weights passed as inputs), so the
+ * step list is cut where a group of a few megabytes is first needed and each part starts when its group has arrived,
+ * the later groups still crossing the host link (PLAIDML_CUDA_UPLOAD_OVERLAP=0 turns it off). */
+size_t pmlb_exec_upload_groups(plaidml_error* err, plaidml_executable* exec);
 /* Re-runs the kernel sequence `iters` times on the inputs already resident on the device from
  * the last plaidml_executable_run (no host copies) and returns the mean milliseconds per
  * iteration measured with CUDA events on the executable's stream. */

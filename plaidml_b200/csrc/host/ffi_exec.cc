@@ -59,6 +59,10 @@ int pmlb_exec_uses_graph(plaidml_error* err, plaidml_executable* exec) {
   return ffiWrap<int>(err, 0, [&] { return exec->exec->usesGraph() ? 1 : 0; });
 }
 
+size_t pmlb_exec_upload_groups(plaidml_error* err, plaidml_executable* exec) {
+  return ffiWrap<size_t>(err, 0, [&] { return exec->exec->uploadGroups(); });
+}
+
 double pmlb_exec_run_resident(plaidml_error* err, plaidml_executable* exec, size_t iters) {
   return ffiWrap<double>(err, 0.0, [&] { return exec->exec->runResident(iters); });
 }

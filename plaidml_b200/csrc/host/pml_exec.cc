@@ -219,10 +219,18 @@ class Planner {
       for (int in : pd.inputs) needed[root(in)] = true;
     }
 
+    // an input that no kept step reads and that is not returned stays on the host (a network builder may list its
+    // weights as inputs although the operations use constants: networks/oplib/resnet50.cc does)
+    exe_->inputUsed_.assign(prog_.inputs.size(), true);
+    for (size_t i = 0; i < prog_.inputs.size(); ++i) exe_->inputUsed_[i] = needed[root(prog_.inputs[i])];
+
     // ---- phase C: device memory, then kernel plans
     allocate(needed);
     for (size_t k = 0; k < pending_.size(); ++k) {
-      if (keep[k]) emit(pending_[k]);
+      if (!keep[k]) continue;
+      const size_t before = exe_->steps_.size();
+      emit(pending_[k]);
+      for (size_t s = before; s < exe_->steps_.size(); ++s) exe_->steps_[s].position = pending_[k].position;
     }
   }
 
@@ -1577,8 +1585,9 @@ Executable::~Executable() {
   for (pmlb_plan* q : blockPlans_) pmlb_plan_free(q);
   for (cudaEvent_t ev : sliceDone_) cudaEventDestroy(ev);
   if (copyStream_) cudaStreamDestroy(copyStream_);
-  if (graphExec_) cudaGraphExecDestroy(graphExec_);
-  if (graph_) cudaGraphDestroy(graph_);
+  for (cudaGraphExec_t g : graphs_) cudaGraphExecDestroy(g);
+  for (cudaEvent_t ev : groupReady_) cudaEventDestroy(ev);
+  if (uploadStream_) cudaStreamDestroy(uploadStream_);
   for (Step& s : steps_) pmlb_plan_free(s.plan);
   for (void* q : derived_) cudaFree(q);
   if (arena_) cudaFree(arena_);
@@ -1591,48 +1600,43 @@ Executable::~Executable() {
   if (stream_) cudaStreamDestroy(stream_);
 }
 
-void Executable::launchStepsDirect() {
-  for (Step& s : steps_) {
+void Executable::launchStepsDirect(size_t first, size_t last) {
+  for (size_t i = first; i < last; ++i) {
+    Step& s = steps_[i];
     const pmlb_status rc = s.launch(stream_);
     if (rc != PMLB_OK) throw std::runtime_error("Kernel step '" + s.kernel + " " + s.detail + "' failed: " + pmlb_last_error());
   }
 }
 
-// Records the kernel sequence once; the same launches, replayed by the driver without the
+// Records the kernel sequence once (one graph per segment); the same launches, replayed by the driver without the
 // per-launch host work (tensor-map encoding, attribute calls, argument marshalling).  Any
 // failure leaves the executable on direct launches.
 void Executable::captureGraph() {
   graphState_ = 2;
-  if (cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
-    cudaGetLastError();
-    return;
-  }
-  bool ok = true;
-  for (Step& s : steps_) {
-    if (s.launch(stream_) != PMLB_OK) {
-      ok = false;
-      break;
+  std::vector<cudaGraphExec_t> made;
+  for (size_t k = 0; k < segStart_.size(); ++k) {
+    const size_t first = segStart_[k], last = k + 1 < segStart_.size() ? segStart_[k + 1] : steps_.size();
+    bool ok = cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+    cudaGraph_t g = nullptr;
+    if (ok) {
+      for (size_t i = first; i < last && ok; ++i) ok = steps_[i].launch(stream_) == PMLB_OK;
+      ok = (cudaStreamEndCapture(stream_, &g) == cudaSuccess) && ok && g != nullptr;
     }
-  }
-  cudaGraph_t g = nullptr;
-  const cudaError_t endErr = cudaStreamEndCapture(stream_, &g);
-  if (!ok || endErr != cudaSuccess || g == nullptr) {
+    cudaGraphExec_t exec = nullptr;
+    if (ok) ok = cudaGraphInstantiate(&exec, g, 0) == cudaSuccess && exec != nullptr;
     if (g) cudaGraphDestroy(g);
-    cudaGetLastError();
-    return;
+    if (!ok) {
+      for (cudaGraphExec_t e : made) cudaGraphExecDestroy(e);
+      cudaGetLastError();
+      return;
+    }
+    made.push_back(exec);
   }
-  cudaGraphExec_t exec = nullptr;
-  if (cudaGraphInstantiate(&exec, g, 0) != cudaSuccess || exec == nullptr) {
-    cudaGraphDestroy(g);
-    cudaGetLastError();
-    return;
-  }
-  graph_ = g;
-  graphExec_ = exec;
+  graphs_ = std::move(made);
   graphState_ = 1;
 }
 
-void Executable::enqueueSteps() {
+void Executable::enqueueSteps(const std::vector<cudaEvent_t>* waits) {
   ++passes_;
   if (graphState_ == 0 && passes_ >= 2) {
     const bool wanted = steps_.size() >= 2 && Settings::instance().getOr("PLAIDML_CUDA_GRAPH", "1") != "0";
@@ -1642,11 +1646,91 @@ void Executable::enqueueSteps() {
       graphState_ = 2;
     }
   }
-  if (graphState_ == 1) {
-    cudaCheck(cudaGraphLaunch(graphExec_, stream_), "cudaGraphLaunch");
+  for (size_t k = 0; k < segStart_.size(); ++k) {
+    if (waits) cudaCheck(cudaStreamWaitEvent(stream_, (*waits)[k], 0), "cudaStreamWaitEvent");
+    if (graphState_ == 1) {
+      cudaCheck(cudaGraphLaunch(graphs_[k], stream_), "cudaGraphLaunch");
+    } else {
+      launchStepsDirect(segStart_[k], k + 1 < segStart_.size() ? segStart_[k + 1] : steps_.size());
+    }
+  }
+}
+
+// Decides once whether a run's uploads overlap its kernels.  An input is needed by the first step whose program
+// position is not before the first operation that uses it (looking through reshapes): a step reads an input only
+// through an operation fused into it, and a step's position is that of its last fused operation, so in the
+// position-ordered step list no step before that one can read it.  Inputs are grouped in order of need until a
+// group holds a few megabytes; a group's first step starts a segment.
+void Executable::planUploadOverlap() {
+  overlapState_ = 2;
+  if (Settings::instance().getOr("PLAIDML_CUDA_UPLOAD_OVERLAP", "1") == "0") return;
+  if (ShardComm::instance().world() > 1 || prog_->inputs.size() < 2 || steps_.size() < 2) return;
+  const size_t nv = prog_->values.size();
+  std::vector<int> root(nv);
+  for (size_t v = 0; v < nv; ++v) root[v] = static_cast<int>(v);
+  for (const POp& op : prog_->ops) {     // (operations are in definition order: an operand's root is final here)
+    if (op.kind == POp::Reshape && op.result >= 0) root[op.result] = root[op.operands[0]];
+  }
+  std::vector<int> firstOp(nv, -1);
+  for (size_t j = 0; j < prog_->ops.size(); ++j) {
+    const POp& op = prog_->ops[j];
+    if (op.kind == POp::Reshape) continue;
+    for (int o : op.operands) {
+      if (firstOp[root[o]] < 0) firstOp[root[o]] = static_cast<int>(j);
+    }
+  }
+  struct Need {
+    size_t step, input, bytes;
+  };
+  std::vector<Need> needs;
+  size_t total = 0;
+  for (size_t i = 0; i < prog_->inputs.size(); ++i) {
+    const int id = prog_->inputs[i];
+    size_t step = 0;   // an input no operation uses (or that is itself an output) travels with the first group
+    const bool isOutput = std::find(prog_->outputs.begin(), prog_->outputs.end(), id) != prog_->outputs.end();
+    if (firstOp[id] >= 0 && !isOutput) {
+      while (step < steps_.size() && steps_[step].position < firstOp[id]) ++step;
+      if (step == steps_.size()) step = 0;
+    }
+    const size_t bytes = inputUsed_[i] ? prog_->values[id].shape.byteSize() : 0;
+    needs.push_back({step, i, bytes});
+    total += bytes;
+  }
+  for (size_t i = 0; i < steps_.size(); ++i) {
+    // (a step without a position, or a list that is not in position order: stay on the plain path)
+    if (steps_[i].position < 0 || (i > 0 && steps_[i].position < steps_[i - 1].position)) return;
+  }
+  std::stable_sort(needs.begin(), needs.end(), [](const Need& a, const Need& b) { return a.step < b.step; });
+  const size_t quantum = std::max<size_t>(size_t{4} << 20, total / 12);
+  std::vector<size_t> starts{0};
+  std::vector<std::vector<size_t>> groups(1);
+  size_t inGroup = 0;
+  for (const Need& n : needs) {
+    if (inGroup >= quantum && n.step > starts.back()) {
+      starts.push_back(n.step);
+      groups.emplace_back();
+      inGroup = 0;
+    }
+    groups.back().push_back(n.input);
+    inGroup += n.bytes;
+  }
+  if (groups.size() < 2) return;
+  if (cudaStreamCreateWithFlags(&uploadStream_, cudaStreamNonBlocking) != cudaSuccess) {
+    cudaGetLastError();
+    uploadStream_ = nullptr;
     return;
   }
-  launchStepsDirect();
+  for (size_t k = 0; k < groups.size(); ++k) {
+    cudaEvent_t ev = nullptr;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      return;
+    }
+    groupReady_.push_back(ev);
+  }
+  segStart_ = std::move(starts);
+  inputGroup_ = std::move(groups);
+  overlapState_ = 1;
 }
 
 void Executable::checkStatus() {
@@ -1687,9 +1771,27 @@ double Executable::run(const std::vector<BufferPtr>& inputs, const std::vector<B
   if (slicedState_ == 0) slicedState_ = prepareSlicedRun() ? 1 : 2;
   if (slicedState_ == 1) return runSliced(inputs, outputs);
   const auto t0 = std::chrono::steady_clock::now();
-  for (size_t i = 0; i < inputs.size(); ++i) uploadInput(i, inputs[i]);
-  inputsResident_ = true;
-  enqueueSteps();
+  if (overlapState_ == 0) planUploadOverlap();   // (before the graph is captured: it fixes the segments)
+  if (overlapState_ == 1) {
+    for (size_t k = 0; k < inputGroup_.size(); ++k) {
+      for (size_t i : inputGroup_[k]) {
+        const int id = prog_->inputs[i];
+        const size_t bytes = prog_->values[id].shape.byteSize();
+        if (bytes && inputUsed_[i]) {
+          cudaCheck(cudaMemcpyAsync(dev_[id], inputs[i]->data(), bytes, cudaMemcpyHostToDevice, uploadStream_), "input upload");
+        }
+      }
+      cudaCheck(cudaEventRecord(groupReady_[k], uploadStream_), "cudaEventRecord");
+    }
+    inputsResident_ = true;
+    enqueueSteps(&groupReady_);
+  } else {
+    for (size_t i = 0; i < inputs.size(); ++i) {
+      if (inputUsed_[i]) uploadInput(i, inputs[i]);
+    }
+    inputsResident_ = true;
+    enqueueSteps();
+  }
   for (size_t i = 0; i < outputs.size(); ++i) {
     const int id = prog_->outputs[i];
     const size_t bytes = prog_->values[id].shape.byteSize();

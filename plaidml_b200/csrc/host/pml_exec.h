@@ -29,6 +29,7 @@ struct Step {
   std::string detail;   // human-readable description (operation name, shape, fusions)
   pmlb_plan* plan = nullptr;
   int launches = 1;     // kernel launches this step enqueues
+  int position = -1;    // program position (index of the last operation fused into the step)
   std::function<pmlb_status(cudaStream_t)> launch;
   // GEMM steps whose A operand is a program input and whose product is a program output, with
   // nothing else reading or feeding them: rows of A / C can be processed in slices.
@@ -68,15 +69,17 @@ class Executable {
   std::string describe() const;
   size_t launchCount() const;
   bool usesGraph() const { return graphState_ == 1; }
+  size_t uploadGroups() const { return overlapState_ == 1 ? inputGroup_.size() : 1; }
   void* outputDevicePtr(size_t index, size_t* nbytes) const;
   cudaStream_t stream() const { return stream_; }
   const Program& program() const { return *prog_; }
 
  private:
   friend class Planner;
-  void enqueueSteps();
-  void launchStepsDirect();
+  void enqueueSteps(const std::vector<cudaEvent_t>* waits = nullptr);
+  void launchStepsDirect(size_t first, size_t last);
   void captureGraph();
+  void planUploadOverlap();
   bool prepareSlicedRun();
   double runSliced(const std::vector<BufferPtr>& inputs, const std::vector<BufferPtr>& outputs);
   void checkStatus();
@@ -95,12 +98,20 @@ class Executable {
   std::vector<Step> steps_;
   int* status_ = nullptr;          // device word shared by all tensor-core plans
   bool inputsResident_ = false;
+  std::vector<bool> inputUsed_;    // per program input: read by a kernel step or returned (others are never uploaded)
   // The kernel sequence as a CUDA graph: captured on the second pass (the first one has done every
   // one-time host-side set-up), launched as one node list afterwards.  0 = not tried, 1 = in use, 2 = off.
   int graphState_ = 0;
   size_t passes_ = 0;
-  cudaGraph_t graph_ = nullptr;
-  cudaGraphExec_t graphExec_ = nullptr;
+  std::vector<cudaGraphExec_t> graphs_;  // one per segment of the step list (one segment unless uploads overlap)
+  // Upload / compute overlap for programs with many inputs (weights passed as inputs): the step list is cut into
+  // segments, every input belongs to the segment of its first use, and a segment starts as soon as its group has
+  // arrived while the later groups are still crossing the host link.  0 = not tried, 1 = in use, 2 = off.
+  int overlapState_ = 0;
+  std::vector<size_t> segStart_{0};             // first step of each segment
+  std::vector<std::vector<size_t>> inputGroup_; // program inputs per segment
+  std::vector<cudaEvent_t> groupReady_;
+  cudaStream_t uploadStream_ = nullptr;
   // Sliced run of a single-GEMM program (see Executable::runSliced): 0 = not tried, 1 = in use, 2 = off.
   int slicedState_ = 0;
   std::vector<pmlb_plan*> slicePlans_;

@@ -38,6 +38,11 @@ class Executable(ForeignObject):
         """True once passes replay a captured CUDA graph of the kernel sequence."""
         return bool(ffi_call(lib.pmlb_exec_uses_graph, self.as_ptr()))
 
+    @property
+    def upload_groups(self) -> int:
+        """Groups the inputs are uploaded in (1: all, then the kernels; more: uploads overlap the kernels)."""
+        return int(ffi_call(lib.pmlb_exec_upload_groups, self.as_ptr()))
+
     def run_resident(self, iters: int = 1) -> float:
         """Mean milliseconds per iteration of the kernel sequence on device-resident inputs."""
         return ffi_call(lib.pmlb_exec_run_resident, self.as_ptr(), iters)

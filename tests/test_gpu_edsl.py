@@ -613,3 +613,59 @@ def test_shape_and_trace_run():
     np.testing.assert_array_equal(got[0], np.array([2, 3], np.int32))
     np.testing.assert_array_equal(got[1], a * 2.0)
     np.testing.assert_array_equal(got[2], a)
+
+
+def test_uploads_of_late_inputs_overlap_the_kernels_and_results_follow_the_inputs():
+    # x . W1 . W2 ... W6 with every weight a program INPUT (as the reference's network builders pass them): the
+    # weights are first needed at increasing depths, so the run uploads them in groups and starts each part of the
+    # kernel sequence when its group is there.  Every run gets new contents for every input; a step that started
+    # before its weights arrived would multiply by the previous run's.
+    from plaidml_b200 import op
+    n, depth = 1024, 6
+    X = Placeholder(DType.FLOAT32, [256, n])
+    Ws = [Placeholder(DType.FLOAT32, [n, n]) for _ in range(depth)]
+    y = X
+    for W in Ws:
+        y = op.dot(y, W)
+    r = Runner(Program("chain", [X] + Ws, [y]), "cuda.0")
+    g = rng(77)
+    for run in range(4):
+        x = g.standard_normal((256, n)).astype(np.float32)
+        ws = [(g.standard_normal((n, n)) / np.sqrt(n)).astype(np.float32) for _ in range(depth)]
+        out, = r.run([x] + ws)
+        ref = x.astype(np.float64)
+        for w in ws:
+            ref = ref @ w.astype(np.float64)
+        check_close(out, ref, 1e-4)
+        assert r.executable.upload_groups >= 2, r.executable.upload_groups
+    assert r.executable.uses_graph
+
+
+def test_upload_overlap_can_be_turned_off():
+    from plaidml_b200 import op
+    from plaidml_b200.core import settings_set
+    settings_set("PLAIDML_CUDA_UPLOAD_OVERLAP", "0")
+    try:
+        A = Placeholder(DType.FLOAT32, [256, 1024])
+        B = Placeholder(DType.FLOAT32, [1024, 2048])
+        C = Placeholder(DType.FLOAT32, [2048, 2048])
+        r = Runner(Program("two", [A, B, C], [op.dot(op.dot(A, B), C)]), "cuda.0")
+        g = rng(78)
+        a, b, c = (g.standard_normal(s).astype(np.float32) for s in ((256, 1024), (1024, 2048), (2048, 2048)))
+        out, = r.run([a, b, c])
+        check_close(out, (a.astype(np.float64) @ b) @ c, 1e-4)
+        assert r.executable.upload_groups == 1
+    finally:
+        settings_set("PLAIDML_CUDA_UPLOAD_OVERLAP", "1")
+
+
+def test_an_input_no_operation_reads_is_accepted_and_left_on_the_host():
+    # (the reference's ResNet-50 builder lists its 108 weight tensors as inputs although its operations use constants)
+    A = Placeholder(DType.FLOAT32, [64, 64])
+    unused = Placeholder(DType.FLOAT32, [4096, 4096])
+    B = Placeholder(DType.FLOAT32, [64, 64])
+    r = Runner(Program("unused", [A, unused, B], [A + B]), "cuda.0")
+    g = rng(79)
+    a, b = g.standard_normal((64, 64)).astype(np.float32), g.standard_normal((64, 64)).astype(np.float32)
+    out, = r.run([a, np.full((4096, 4096), np.nan, dtype=np.float32), b])
+    np.testing.assert_array_equal(out, a + b)
