@@ -9,6 +9,8 @@ tests/host/refshim/ replace googletest, gflags and three LLVM ADT headers, nothi
     prng): all pass;
   * plaidml/edsl/examples/{complex_conv_2d,conv_1d,conv_2d_dilated,gemv,max_pool_1d,quantize}.cc and
     plaidml/edsl/edsl_docs.cc (the code blocks of the documentation): 23 tests, all pass;
+  * networks/oplib/run.cc and layer.cc: the reference's two command-line programs (one ResNet-50 pass; one convolution
+    layer of a given shape ten times);
   * networks/oplib/benchmark.cc: the reference's ResNet-50 benchmark program (with its own main(); a stand-in for Google
     Benchmark under refshim/benchmark/ runs and times the registered benchmarks);
   * plaidml/op/op_test.cc: the reference's op-library suite, 60 tests (67 with the parameterised convolution cases),
@@ -46,6 +48,9 @@ BINARIES = {
                       "plaidml/edsl/edsl_docs.cc"], []),
     # the reference's ResNet-50 benchmark program (its own main(); Google Benchmark replaced by refshim/benchmark/)
     "ref_benchmark": (["networks/oplib/benchmark.cc", "networks/oplib/resnet50.cc"], ["-DPMLB_OWN_MAIN"]),
+    # ... and its two small command-line programs: run the ResNet-50 once; one convolution layer of given shape 10 times
+    "ref_run": (["networks/oplib/run.cc", "networks/oplib/resnet50.cc"], ["-DPMLB_OWN_MAIN"]),
+    "ref_layer": (["networks/oplib/layer.cc"], ["-DPMLB_OWN_MAIN"]),
 }
 
 def _check_edsl_suite(out: str) -> None:
@@ -86,7 +91,7 @@ def test_reference_sources_compile_and_build_their_programs():
         pytest.skip("PLAIDML_REFERENCE_DIR does not point at a checkout of the reference")
     if shutil.which("g++") is None or not (LIB_DIR / "libplaidml.so").exists():
         pytest.skip("needs g++ and a built libplaidml.so")
-    gemm, resnet, edsl_suite, op_suite, examples, _benchmark = build_binaries(Path(ref))   # (the benchmark needs a device)
+    gemm, resnet, edsl_suite, op_suite, examples = build_binaries(Path(ref))[:5]   # (the three programs with a main() of their own need a device)
     assert "23 tests, 0 failures" in _run(examples, "--build-only")
     _check_edsl_suite(_run(edsl_suite, "--build-only"))
     _check_op_suite(_run(op_suite, "--build-only"))
@@ -123,6 +128,16 @@ def test_reference_sources_run_on_the_cuda_device():
         res = subprocess.run([str(OUT / "ref_benchmark")], capture_output=True, text=True, timeout=600, env=env)
         assert res.returncode == 0, (res.stdout[-2000:], res.stderr[-2000:])
         assert "resnet50/compile: 12 iterations" in res.stdout and "resnet50/run: 12 iterations" in res.stdout, res.stdout
+    env = dict(os.environ, PLAIDML_TARGET="cuda", PLAIDML_DEVICE="cuda.0")
+    if (OUT / "ref_run").exists():
+        res = subprocess.run([str(OUT / "ref_run")], capture_output=True, text=True, timeout=600, env=env)
+        assert res.returncode == 0 and "Running..." in res.stdout and "tile.contract" in res.stdout, (res.stdout[-1500:], res.stderr[-1500:])
+    if (OUT / "ref_layer").exists():
+        # N K C H W R S stride: a 3 x 3 convolution on 56 x 56 x 64 in fp32 (the tensor-core route with three TF32 products)
+        res = subprocess.run([str(OUT / "ref_layer"), "8", "64", "64", "56", "56", "3", "3", "1"], capture_output=True, text=True,
+                             timeout=600, env=env)
+        assert res.returncode == 0 and "Running..." in res.stdout and "conv2d:8:64:64:56:56:3:3:1" in res.stdout, \
+            (res.stdout[-1500:], res.stderr[-1500:])
     if (OUT / "ref_examples").exists():
         # the remaining EDSL examples (1-D / dilated / complex convolutions, GEMV, max pool, quantisation) and the
         # code blocks of the reference's documentation
