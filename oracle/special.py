@@ -158,3 +158,85 @@ def prng(state: np.ndarray, count: int):
     new_state = state.copy().reshape(-1)
     new_state[:3] = np.array([s0, s1, s2], dtype=np.uint64).astype(state.dtype)
     return out, new_state.reshape(state.shape)
+
+
+def nms(boxes: np.ndarray, scores: np.ndarray, iou_threshold: float, score_threshold: float, max_per_class: int,
+        soft_sigma: float = 0.0, center_point_box: bool = False, sort_descending: bool = True, clip_before: bool = False,
+        style: int = 2, share_location: bool = True, hard_suppression: bool = True):
+    """Non-maximum suppression as the op library builds it (plaidml/op/lib/ops.cc:2034-2419, NMS box decoding), as plain
+    loops in float32.  PARITY UNPINNED: the reference's tests hold no expected values for this operation; this
+    restatement follows the reference's sequence of operations (so that float results agree) and pins only that the
+    device and the CPU compute the same thing, plus properties any NMS has (tests/test_gpu_special.py).
+
+    boxes [batch, boxes, 4], scores [batch, classes, boxes].  Returns (rows of (batch, class, box) int32, rows of
+    (batch, class, score) float32, number of valid picks); rows that found nothing hold -1.  style: 0 CAFFE (only a
+    class's best `max_per_class` boxes compete), 1 MXNET (a box competes in its best class only), 2 OV."""
+    f = np.float32
+    nb, nc, nx = scores.shape
+    b = boxes.astype(f)
+    if center_point_box:
+        xc, yc, hw, hh = b[..., 0], b[..., 1], b[..., 2] / f(2), b[..., 3] / f(2)
+        x1, x2, y1, y2 = xc - hw, xc + hw, yc - hh, yc + hh
+    else:
+        y1, y2 = np.minimum(b[..., 0], b[..., 2]), np.maximum(b[..., 0], b[..., 2])
+        x1, x2 = np.minimum(b[..., 1], b[..., 3]), np.maximum(b[..., 1], b[..., 3])
+    if clip_before:
+        y1, x1, y2, x2 = (np.clip(v, f(0), f(1)) for v in (y1, x1, y2, x2))
+    if not share_location:
+        raise ValueError("boxes per class need boxes of shape [batch, classes * boxes, 4]; not restated")
+    area = (y2 - y1) * (x2 - x1)
+    ygap = np.minimum(y2[:, :, None], y2[:, None, :]) - np.maximum(y1[:, :, None], y1[:, None, :])
+    xgap = np.minimum(x2[:, :, None], x2[:, None, :]) - np.maximum(x1[:, :, None], x1[:, None, :])
+    inter = np.where(ygap > 0, ygap, f(0)) * np.where(xgap > 0, xgap, f(0))
+    denom = area[:, :, None] + area[:, None, :] - inter
+    with np.errstate(divide="ignore", invalid="ignore"):
+        iou = inter * np.where(denom <= 0, f(0), f(1) / denom)          # [batch, boxes, boxes]
+    per_class = min(nx, max_per_class) if max_per_class else nx
+    live = np.where(scores.astype(f) > f(score_threshold), scores.astype(f), f(0))
+
+    def stable_desc(line):
+        return argsort(line, 0, True)
+
+    if style == 0:
+        kept = np.zeros_like(live)
+        for bi in range(nb):
+            for ci in range(nc):
+                top = stable_desc(live[bi, ci])[:per_class]
+                kept[bi, ci, top] = live[bi, ci, top]
+        live = kept
+    elif style == 1:
+        kept = np.zeros_like(live)
+        for bi in range(nb):
+            best_class = np.array([stable_desc(live[bi, :, x])[0] for x in range(nx)])
+            best_score = live[bi, best_class, np.arange(nx)]
+            top = np.sort(stable_desc(best_score)[:per_class])
+            kept[bi, best_class[top], top] = best_score[top]
+        live = kept
+    weight = f(-0.5 / soft_sigma) if soft_sigma else f(0)
+    box_rows = np.full((nb, nc, per_class, 3), -1, dtype=np.int32)
+    score_rows = np.full((nb, nc, per_class, 3), -1, dtype=f)
+    valid = 0
+    for k in range(per_class):
+        for bi in range(nb):
+            for ci in range(nc):
+                cand = int(stable_desc(live[bi, ci])[0])
+                score = live[bi, ci].max()
+                if score != 0:
+                    valid += 1
+                if score > 0:
+                    box_rows[bi, ci, k] = (bi, ci, cand)
+                    score_rows[bi, ci, k] = (bi, ci, score)
+                live[bi, ci, cand] = 0
+                overlap = iou[bi, cand]
+                hit = overlap >= f(iou_threshold) if hard_suppression else overlap > f(iou_threshold)
+                live[bi, ci] = np.where(hit, f(0), live[bi, ci])
+                if soft_sigma:
+                    live[bi, ci] = live[bi, ci] * np.exp(overlap * overlap * weight).astype(f)
+                    live[bi, ci] = np.where(live[bi, ci] > f(score_threshold), live[bi, ci], f(0))
+    box_rows = box_rows.reshape(-1, 3)
+    score_rows = score_rows.reshape(-1, 3)
+    if sort_descending:
+        order = argsort(score_rows[:, 2], 0, True)
+    else:
+        order = np.argsort(np.where(score_rows[:, 2] != -1, np.arange(len(score_rows)), len(score_rows)), kind="stable")
+    return box_rows[order], score_rows[order], valid

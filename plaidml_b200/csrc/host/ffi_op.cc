@@ -1175,6 +1175,191 @@ double asFloat(const VarPtr& v) {
   throw std::runtime_error("Expected a float argument");
 }
 
+// ------------------------------------------------------------------ non-maximum suppression
+//
+// plaidml/op/lib/ops.cc:2034-2419 (decode_boxes, compute_iou, nms).  Boxes [batch, boxes, 4], scores
+// [batch, classes, boxes]; per (batch, class) the best-scoring box is taken `max_output_boxes_per_class` times, every
+// box whose overlap with it reaches the threshold loses its score (or, with a soft-NMS sigma, part of it).  Results:
+// [rows, 3] (batch, class, box) and [rows, 3] (batch, class, score) with -1 rows for picks that found nothing, and the
+// number of valid picks.  Built from the same operations as the reference builds it from, so the printed program and
+// the arithmetic are its own: comparisons and selects, reshapes, argsort / gather / scatter / topk / gatherND.
+// BoxesDecodeMode::SSD (prior boxes with variances and location offsets) is not offered.
+
+struct Ex {
+  ExprPtr e;
+};
+Ex operator+(const Ex& a, const Ex& b) { return {binary("add", a.e, b.e)}; }
+Ex operator-(const Ex& a, const Ex& b) { return {binary("sub", a.e, b.e)}; }
+Ex operator*(const Ex& a, const Ex& b) { return {binary("mul", a.e, b.e)}; }
+Ex operator/(const Ex& a, const Ex& b) { return {binary("div", a.e, b.e)}; }
+Ex flt(double v) { return {litFloat(v)}; }
+Ex cmp(const char* fn, const Ex& a, const Ex& b) { return {binary(fn, a.e, b.e)}; }
+Ex sel(const Ex& c, const Ex& a, const Ex& b) { return {intrinsic("select", {c.e, a.e, b.e})}; }
+Ex maxOf(const Ex& a, const Ex& b) { return sel(cmp("cmp_lt", a, b), b, a); }
+Ex minOf(const Ex& a, const Ex& b) { return sel(cmp("cmp_lt", a, b), a, b); }
+Ex shaped(const Ex& a, const std::vector<int64_t>& dims) { return {reshapeTo(a.e, dims)}; }
+Ex typed(const Ex& a, pml::DType dt) { return {castTo(a.e, dt)}; }
+// position `i` along `axis`, keeping the axis with extent 1 (edsl::gather(x, i).axis(axis))
+Ex pick(const Ex& a, int64_t i, int64_t axis) {
+  ExprPtr at = binary("add", castTo(indexExpr({1}, 0), pml::DType::si32), litInt(i));
+  return {gatherExpr(a.e, at, normalizeAxis(axis, shapeOf(a.e).rank(), "nms"))};
+}
+Ex clip01(const Ex& a) {
+  return minOf(maxOf(a, typed(flt(0.0), pml::DType::f32)), typed(flt(1.0), pml::DType::f32));
+}
+
+VarPtr opNms(const VarPtr& value) {
+  const auto& args = asTuple(value, "nms");
+  if (args.size() != 21) throw std::runtime_error("nms expects 21 arguments");
+  Ex boxes{asTensor(args[0])}, scores{asTensor(args[1])}, iouThreshold{asTensor(args[2])}, scoreThreshold{asTensor(args[3])};
+  const int64_t maxPerClass = asInt(args[4]);
+  const double softSigma = asFloat(args[5]);
+  const bool centerPoint = asBool(args[6]), sortDescending = asBool(args[7]);
+  const pml::DType boxOutType = static_cast<pml::DType>(asInt(args[8]));
+  if (asInt(args[9]) != 0) throw std::runtime_error("nms: the SSD box decoding is not in the cuda target's op library");
+  const bool clipBefore = asBool(args[10]);
+  if (asBool(args[16])) throw std::runtime_error("nms: the SSD box decoding is not in the cuda target's op library");
+  const int64_t style = asInt(args[18]);
+  if (style < 0 || style > 2) throw std::runtime_error("Invalid nms style");
+  const bool shareLocation = asBool(args[19]), hardSuppression = asBool(args[20]);
+
+  const pml::DType boxType = shapeOf(boxes.e).dtype;
+  pml::DType thresType = shapeOf(iouThreshold.e).dtype;
+  if (pml::isAmbiguous(thresType)) thresType = pml::DType::f32;
+  const pml::TensorShape scoreShape = shapeOf(scores.e);
+  if (scoreShape.rank() != 3 || shapeOf(boxes.e).rank() != 3) throw std::runtime_error("nms expects boxes and scores of rank 3");
+  const int64_t nb = scoreShape.sizes[0], nc = scoreShape.sizes[1], nx = scoreShape.sizes[2];
+  const int64_t locClasses = shareLocation ? 1 : nc;
+
+  const Ex zero = typed(Ex{indexExpr({1}, 0)}, boxType);
+  const Ex zeroInt = typed(zero, pml::DType::si32);
+  const Ex one = zero + Ex{litInt(1)};
+  const Ex neg1{intrinsic("neg", {one.e})};
+  const Ex neg1Out = typed(neg1, boxOutType);
+
+  // corners (y1, x1, y2, x2) of every box: [batch, 1, boxes, 1]
+  const Ex b4 = shaped(boxes, {nb, 1, shapeOf(boxes.e).sizes[1], shapeOf(boxes.e).sizes[2]});
+  Ex y1, x1, y2, x2;
+  if (centerPoint) {
+    const Ex xc = pick(b4, 0, 3), yc = pick(b4, 1, 3), hw = pick(b4, 2, 3) / flt(2.0), hh = pick(b4, 3, 3) / flt(2.0);
+    x1 = xc - hw;
+    x2 = xc + hw;
+    y1 = yc - hh;
+    y2 = yc + hh;
+  } else {
+    const Ex ya = pick(b4, 0, 3), xa = pick(b4, 1, 3), yb = pick(b4, 2, 3), xb = pick(b4, 3, 3);
+    y1 = minOf(ya, yb);
+    x1 = minOf(xa, xb);
+    y2 = maxOf(ya, yb);
+    x2 = maxOf(xa, xb);
+  }
+  if (clipBefore) {
+    y1 = clip01(y1);
+    x1 = clip01(x1);
+    y2 = clip01(y2);
+    x2 = clip01(x2);
+  }
+  // overlap of every pair of boxes: [batch, location classes, boxes, boxes]
+  y1 = shaped(y1, {nb, locClasses, nx});
+  x1 = shaped(x1, {nb, locClasses, nx});
+  y2 = shaped(y2, {nb, locClasses, nx});
+  x2 = shaped(x2, {nb, locClasses, nx});
+  const std::vector<int64_t> asRows{nb, locClasses, nx, 1}, asCols{nb, locClasses, 1, nx};
+  const Ex area = (y2 - y1) * (x2 - x1);
+  const Ex ygap = minOf(shaped(y2, asRows), shaped(y2, asCols)) - maxOf(shaped(y1, asRows), shaped(y1, asCols));
+  const Ex xgap = minOf(shaped(x2, asRows), shaped(x2, asCols)) - maxOf(shaped(x1, asRows), shaped(x1, asCols));
+  const Ex inter = sel(cmp("cmp_gt", ygap, flt(0.0)), ygap, zero) * sel(cmp("cmp_gt", xgap, flt(0.0)), xgap, zero);
+  const Ex denom = shaped(area, asRows) + shaped(area, asCols) - inter;
+  const Ex iou = inter * sel(cmp("cmp_le", denom, flt(0.0)), zero, flt(1.0) / denom);
+
+  const double weight = softSigma != 0 ? -0.5 / softSigma : 0.0;
+  pml::TensorShape nodeShape(pml::DType::f32, {1, 1, 2});
+  pml::BufferPtr nodeBuffer = pml::Buffer::allocate(nodeShape);
+  reinterpret_cast<float*>(nodeBuffer->data())[0] = -1.0f;
+  reinterpret_cast<float*>(nodeBuffer->data())[1] = -1.0f;
+  auto nodeConstant = std::make_shared<ExprNode>(ExprNode::ConstTensor);
+  nodeConstant->buffer = nodeBuffer;
+  nodeConstant->name = "invalid_node";
+  const Ex invalidNode = typed(Ex{nodeConstant}, boxOutType);
+
+  const int64_t perClass = maxPerClass != 0 ? std::min(nx, maxPerClass) : nx;
+  const Ex indexBC = typed(Ex{concatExprs({indexExpr({nb, nc, 1}, 0), indexExpr({nb, nc, 1}, 1)}, 2)}, boxOutType);
+  const Ex scoreThr = typed(scoreThreshold, boxType), iouThr = typed(iouThreshold, boxType);
+  Ex live = sel(cmp("cmp_gt", scores, scoreThr), scores, zero);
+
+  auto zeros = [&](const std::vector<int64_t>& dims) {
+    std::vector<PolyPtr> idx;
+    for (size_t i = 0; i < dims.size(); ++i) idx.push_back(newIndex());
+    return Ex{contraction(pml::AggKind::assign, pml::ComboKind::none, dims, idx, {{zero.e, {polyLit(0)}}}, {}, "nms")};
+  };
+  auto topk = [&](const Ex& x, int64_t k, int64_t axis, int64_t sortType) {
+    VarPtr r = opTopk(tupleValue({exprValue(x.e), intValue(k), intValue(axis), intValue(1), intValue(sortType),
+                                  intValue(static_cast<int64_t>(pml::DType::si32))}));
+    return std::make_pair(Ex{r->tuple[0]->expr}, Ex{r->tuple[1]->expr});
+  };
+  if (style == 0) {            // CAFFE: only the best `perClass` boxes of a class compete
+    auto [vals, pos] = topk(live, perClass, 2, 0);
+    live = Ex{intrinsic("scatter", {zeros({nb, nc, nx}).e, pos.e, vals.e, litInt(2), litInt(2)})};
+  } else if (style == 1) {     // MXNET: every box keeps its best class only, then the best `perClass` boxes
+    const Ex classOf = shaped(pick(Ex{intrinsic("argsort", {live.e, litInt(1), litInt(1)})}, 0, 1), {nb, nx});
+    const Ex bestScore = shaped(pick(Ex{sortExpr(live.e, 1, 1)}, 0, 1), {nb, nx});
+    auto [vals, boxPos] = topk(bestScore, perClass, 1, 1);
+    const Ex classes{gatherNDExpr(classOf.e, unsqueezeExpr(boxPos.e, {-1}), 1, 3)};
+    const pml::TensorShape cs = shapeOf(classes.e);
+    const Ex where{concatExprs({unsqueezeExpr(indexExpr(cs.sizes, 0), {-1}), unsqueezeExpr(classes.e, {-1}),
+                                unsqueezeExpr(boxPos.e, {-1})}, -1)};
+    live = Ex{intrinsic("scatter", {zeros({nb, nc, nx}).e, where.e, vals.e, litInt(0), litInt(3)})};
+  }
+  const Ex zeroColumn = zeros({nb, nc, 1});
+
+  std::vector<ExprPtr> boxParts, scoreParts;
+  Ex valid = zero;
+  for (int64_t k = 0; k < perClass; ++k) {
+    const Ex candidate = pick(Ex{intrinsic("argsort", {live.e, litInt(2), litInt(1)})}, 0, 2);   // [batch, classes, 1]
+    const VarPtr none = std::make_shared<VarNode>();
+    Ex score = shaped(Ex{reduceOp(tupleValue({exprValue(live.e), intValue(2), intValue(0)}), pml::AggKind::max, "max")->expr},
+                      {nb, nc, 1});
+    const Ex node = sel(cmp("cmp_gt", score, flt(0.0)), indexBC, invalidNode);
+    valid = valid + Ex{reduceOp(tupleValue({exprValue(sel(cmp("cmp_ne", score, flt(0.0)), one, zero).e), none, intValue(0)}),
+                                pml::AggKind::add, "sum")->expr};
+    scoreParts.push_back(typed(node, thresType).e);
+    score = sel(cmp("cmp_gt", score, flt(0.0)), score, neg1);
+    scoreParts.push_back(typed(score, thresType).e);
+    // the pick leaves the competition ...
+    live = shaped(Ex{intrinsic("scatter", {live.e, candidate.e, zeroColumn.e, litInt(2), litInt(2)})}, {nb, nc, nx});
+    // ... and so does every box that overlaps it too much
+    const Ex classIdx = shareLocation ? Ex{opBroadcast(tupleValue({exprValue(zeroInt.e), intTupleValue({nb, nc, 1}),
+                                                                   intTupleValue({1})}))->expr}
+                                      : Ex{indexExpr({nb, nc, 1}, 1)};
+    const Ex overlap{gatherNDExpr(iou.e, concatExprs({classIdx.e, candidate.e}, 2), 1, 3)};   // [batch, classes, boxes]
+    live = sel(cmp(hardSuppression ? "cmp_ge" : "cmp_gt", overlap, iouThr), zero, live);
+    boxParts.push_back(node.e);
+    boxParts.push_back(shaped(sel(cmp("cmp_gt", score, flt(0.0)), typed(candidate, boxOutType), neg1Out), {nb, nc, 1}).e);
+    if (softSigma != 0) {
+      live = live * Ex{intrinsic("exp", {(overlap * overlap * flt(weight)).e})};
+      live = sel(cmp("cmp_gt", live, scoreThr), live, zero);
+    }
+  }
+  const int64_t rows = nb * nc * perClass;
+  Ex scoreRows = shaped(Ex{concatExprs(scoreParts, 2)}, {rows, 3});
+  Ex boxRows = shaped(Ex{concatExprs(boxParts, 2)}, {rows, 3});
+  if (sortDescending) {
+    const Ex order{intrinsic("argsort", {shaped(pick(scoreRows, 2, 1), {rows}).e, litInt(0), litInt(1)})};
+    scoreRows = Ex{gatherExpr(scoreRows.e, order.e, 0)};
+    boxRows = Ex{gatherExpr(boxRows.e, order.e, 0)};
+  } else {
+    // valid entries first, in their order: every -1 entry is sent behind them
+    const int64_t flat = rows * 3;
+    const Ex flatScores = shaped(scoreRows, {flat}), flatBoxes = shaped(boxRows, {flat});
+    const Ex key = sel(cmp("cmp_ne", flatScores, typed(Ex{litInt(-1)}, thresType)), Ex{indexExpr({flat}, 0)},
+                       typed(Ex{litInt(flat)}, pml::DType::si32));
+    const Ex order{intrinsic("argsort", {typed(key, pml::DType::f32).e, litInt(0), litInt(0)})};
+    scoreRows = shaped(Ex{gatherExpr(flatScores.e, order.e, 0)}, {rows, 3});
+    boxRows = shaped(Ex{gatherExpr(flatBoxes.e, order.e, 0)}, {rows, 3});
+  }
+  return tupleValue({exprValue(boxRows.e), exprValue(scoreRows.e), exprValue(typed(valid, boxOutType).e)});
+}
+
 // plaidml/op/lib/ops.cc:1586-1685: CONSTANT (0) pads with a value through the contraction's
 // initial tensor, EDGE (1) repeats the border by concatenating slices; SYMMETRIC / REFLECT are
 // unimplemented there too
@@ -1562,6 +1747,7 @@ const std::map<std::string, std::function<VarPtr(const VarPtr&)>>& registry() {
       {"max", [](const VarPtr& v) { return reduceOp(v, pml::AggKind::max, "max"); }},
       {"maximum", opMaximum},
       {"gatherND", opGatherND},
+      {"nms", opNms},
       {"sort", opSort},
       {"topk", opTopk},
       {"mean", opMean},

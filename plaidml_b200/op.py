@@ -290,3 +290,29 @@ def topk(x, k, axis=-1, sort_direction=edsl.SortDirection.DESC, sort_type=TopKSo
     values, positions = op("topk", [x, k, axis, int(sort_direction), int(sort_type),
                                     int(index_element_type if index_element_type is not None else DType.INT32)]).as_tuple()
     return values.as_tensor(), positions.as_tensor()
+
+
+class BoxesDecodeMode(enum.IntEnum):
+    NMS = 0
+    SSD = 1
+
+
+class NmsStyle(enum.IntEnum):
+    CAFFE = 0
+    MXNET = 1
+    OV = 2
+
+
+def nms(boxes, scores, iou_threshold, score_threshold, max_output_boxes_per_class, soft_nms_sigma=0.0,
+        center_point_box=False, sort_result_descending=True, box_output_type=None, clip_before_nms=False,
+        nms_style=NmsStyle.OV, share_location=True, hard_suppression=True):
+    """Non-maximum suppression over boxes [batch, boxes, 4] and scores [batch, classes, boxes]: returns (rows of
+    (batch, class, box), rows of (batch, class, score), number of valid rows); rows that found nothing hold -1.
+    (plaidml/op/op.h `nms`; the SSD box decoding is not offered.)"""
+    from .core import DType
+    out_type = int(box_output_type if box_output_type is not None else DType.INT32)
+    b, s, v = op("nms", [boxes, scores, iou_threshold, score_threshold, int(max_output_boxes_per_class), float(soft_nms_sigma),
+                         bool(center_point_box), bool(sort_result_descending), out_type, int(BoxesDecodeMode.NMS),
+                         bool(clip_before_nms), False, 0, 0, None, None, False, None, int(nms_style), bool(share_location),
+                         bool(hard_suppression)]).as_tuple()
+    return b.as_tensor(), s.as_tensor(), v.as_tensor()

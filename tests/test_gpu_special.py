@@ -323,3 +323,62 @@ def test_programs_mix_them_with_contractions():
     order = np.argsort(-s, axis=1, kind="stable")[:, :3]
     np.put_along_axis(want, order, np.take_along_axis(s, order, axis=1), axis=1)
     np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5)
+
+
+# ------------------------------------------------------------------ non-maximum suppression (parity unpinned: see the oracle)
+
+def nms_case(seed, nb=2, nc=3, nx=24):
+    g = rng(4800 + seed)
+    centre = g.uniform(0.1, 0.9, (nb, nx, 2))
+    size = g.uniform(0.05, 0.4, (nb, nx, 2))
+    corners = np.concatenate([centre - size / 2, centre + size / 2], axis=-1).astype(np.float32)   # y1 x1 y2 x2
+    scores = g.uniform(0.0, 1.0, (nb, nc, nx)).astype(np.float32)
+    return corners, scores
+
+
+def run_nms(boxes, scores, iou_thr, score_thr, k, **kw):
+    B = Placeholder(DType.FLOAT32, list(boxes.shape))
+    S_ = Placeholder(DType.FLOAT32, list(scores.shape))
+    I = Placeholder(DType.FLOAT32, [1])
+    T = Placeholder(DType.FLOAT32, [1])
+    outs = op.nms(B, S_, I, T, k, **kw)
+    return Runner(Program("nms", [B, S_, I, T], list(outs)), "cuda.0").run(
+        [boxes, scores, np.array([iou_thr], np.float32), np.array([score_thr], np.float32)])
+
+
+@pytest.mark.parametrize("style", [op.NmsStyle.OV, op.NmsStyle.CAFFE, op.NmsStyle.MXNET])
+@pytest.mark.parametrize("sort_desc", [True, False])
+def test_nms_matches_the_restatement(style, sort_desc):
+    boxes, scores = nms_case(int(style) * 2 + int(sort_desc))
+    got_b, got_s, got_v = run_nms(boxes, scores, 0.4, 0.3, 5, nms_style=style, sort_result_descending=sort_desc)
+    want_b, want_s, want_v = S.nms(boxes, scores, 0.4, 0.3, 5, style=int(style), sort_descending=sort_desc)
+    np.testing.assert_array_equal(got_b, want_b)
+    np.testing.assert_array_equal(got_s, want_s)
+    assert int(got_v.reshape(-1)[0]) == want_v
+    # what any non-maximum suppression guarantees: picks of one (batch, class) overlap each other by less than the
+    # threshold, score above the score threshold, and no box is picked twice
+    y1, x1, y2, x2 = (boxes[..., i] for i in range(4))
+    rows = got_b[got_b[:, 0] >= 0]
+    assert len(rows) == want_v and len({tuple(r) for r in rows}) == len(rows)
+    for b_, c_ in {(r[0], r[1]) for r in rows}:
+        picked = [r[2] for r in rows if r[0] == b_ and r[1] == c_]
+        assert all(scores[b_, c_, p] > 0.3 for p in picked)
+        for i, p in enumerate(picked):
+            for q in picked[i + 1:]:
+                ih = max(0.0, min(y2[b_, p], y2[b_, q]) - max(y1[b_, p], y1[b_, q]))
+                iw = max(0.0, min(x2[b_, p], x2[b_, q]) - max(x1[b_, p], x1[b_, q]))
+                union = (y2[b_, p] - y1[b_, p]) * (x2[b_, p] - x1[b_, p]) + (y2[b_, q] - y1[b_, q]) * (x2[b_, q] - x1[b_, q]) - ih * iw
+                assert ih * iw / union < 0.4 + 1e-6
+
+
+def test_nms_centre_boxes_clipping_soft_suppression():
+    boxes, scores = nms_case(9, nb=1, nc=2, nx=16)
+    centre = np.concatenate([(boxes[..., 1:2] + boxes[..., 3:4]) / 2, (boxes[..., 0:1] + boxes[..., 2:3]) / 2,
+                             boxes[..., 3:4] - boxes[..., 1:2], boxes[..., 2:3] - boxes[..., 0:1]], axis=-1).astype(np.float32)
+    kw = dict(center_point_box=True, clip_before_nms=True, soft_nms_sigma=0.5, hard_suppression=False)
+    got_b, got_s, got_v = run_nms(centre, scores, 0.5, 0.2, 4, **kw)
+    want_b, want_s, want_v = S.nms(centre, scores, 0.5, 0.2, 4, soft_sigma=0.5, center_point_box=True, clip_before=True,
+                                   hard_suppression=False)
+    np.testing.assert_array_equal(got_b, want_b)
+    np.testing.assert_allclose(got_s, want_s, rtol=1e-5, atol=1e-6)
+    assert int(got_v.reshape(-1)[0]) == want_v

@@ -410,3 +410,20 @@ def test_image_resize_shapes_and_argument_errors():
         op.image_resize(x, [2, 2], op.InterpolationMode.BILINEAR, op.TensorLayout.KCX)
     with pytest.raises(Error, match="2 spatial dims"):
         op.image_resize(Placeholder(DType.FLOAT32, [2, 5, 3]), [2, 2], op.InterpolationMode.NEAREST, op.TensorLayout.NXC)
+
+
+def test_nms_builds_and_refuses_the_ssd_decoding():
+    from plaidml_b200 import op as oplib
+    B = Placeholder(DType.FLOAT32, [2, 10, 4])
+    S = Placeholder(DType.FLOAT32, [2, 3, 10])
+    I = Placeholder(DType.FLOAT32, [1])
+    T = Placeholder(DType.FLOAT32, [1])
+    boxes, scores, valid = oplib.nms(B, S, I, T, 4)
+    assert boxes.compute_shape().sizes == [24, 3] and boxes.dtype == DType.INT32
+    assert scores.compute_shape().sizes == [24, 3] and scores.dtype == DType.FLOAT32
+    assert valid.compute_shape().sizes == [1]
+    text = str(Program("nms", [B, S, I, T], [boxes, scores, valid]))
+    assert "tile.argsort desc" in text and "tile.gather" in text and "tile.scatter" in text
+    with pytest.raises(Error):      # BoxesDecodeMode::SSD
+        oplib.op("nms", [B, S, I, T, 4, 0.0, False, True, int(DType.INT32), 1, False, False, 0, 0, None, None, False, None, 2,
+                         True, True])
