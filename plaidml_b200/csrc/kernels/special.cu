@@ -197,6 +197,41 @@ __global__ void __launch_bounds__(256) gather_interp_kernel(const __grid_constan
   }
 }
 
+// Copying gather along one axis in 16-byte pieces: four pieces per thread, a grid apart, all four positions read
+// before any piece is loaded and all four pieces loaded before any is stored (the kernel waits on memory, not on
+// arithmetic: one piece per thread left DRAM at half its rate).
+template <class I>
+__global__ void __launch_bounds__(256) gather_pieces_kernel(const __grid_constant__ GatherParams p, I threads) {
+  const I t = static_cast<I>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= threads) return;
+  const I total = static_cast<I>(p.out_elems);
+  const I inner = static_cast<I>(p.inner);
+  const I n_idx = static_cast<I>(p.n_idx);
+  const bool one_outer = total == inner * n_idx;
+  const bool float_idx = dtype_is_float(p.idx_dtype);
+  long long src[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    I e = t + static_cast<I>(u) * threads;
+    if (e >= total) e = total - 1;   // (a spare slot repeats the last piece; it is not stored)
+    const I in = inner == 1 ? 0 : e % inner;
+    const I row = inner == 1 ? e : e / inner;
+    const I j = one_outer ? row : row % n_idx;
+    const I o = one_outer ? 0 : row / n_idx;
+    const long long at = float_idx ? to_i32(load_as<double>(p.indices, p.idx_dtype, j))
+                                   : load_as<long long>(p.indices, p.idx_dtype, j);
+    src[u] = (static_cast<long long>(o) * p.axis_len + clamp_ll(at, 0, p.axis_len - 1)) * p.inner + in;
+  }
+  uint4 piece[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) piece[u] = static_cast<const uint4*>(p.tensor)[src[u]];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const I e = t + static_cast<I>(u) * threads;
+    if (e < total) static_cast<uint4*>(p.out)[e] = piece[u];
+  }
+}
+
 // Copying gather (integer positions, nd mode).  `I` is the type of the position arithmetic: 32 bits when every extent
 // fits, else 64.
 template <class I>
@@ -275,6 +310,33 @@ __device__ __forceinline__ void atomic_add_element(void* out, int dtype, long lo
       atomicAdd(static_cast<unsigned long long*>(out) + i, static_cast<const unsigned long long*>(upd)[u]);
       break;
     default: atomic_add_narrow(out, dtype, i, upd, u, bytes); break;
+  }
+}
+
+// The common form -- whole rows of the data named by a list of indices (axis 0, updates [n][row...]) -- with four
+// updates per thread, a grid apart: the four index and update loads are in flight together, and the additions leave
+// as fire-and-forget reductions.
+__global__ void __launch_bounds__(256) scatter_rows_kernel(const __grid_constant__ ScatterParams p, long long inner,
+                                                           long long threads) {
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= threads) return;
+  long long row[4], dst[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    long long e = t + u * threads;
+    if (e >= p.upd_elems) e = p.upd_elems - 1;
+    row[u] = inner == 1 ? e : e / inner;
+    dst[u] = e - row[u] * inner;
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) row[u] = load_as<long long>(p.indices, p.idx_dtype, row[u]);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const long long e = t + u * threads;
+    if (e >= p.upd_elems || row[u] < 0 || row[u] >= p.sizes[0]) continue;   // spare slot, or lands outside the data
+    const long long off = row[u] * inner + dst[u];
+    if (p.mode == 0) atomic_add_element(p.out, p.dtype, off, p.updates, e, p.elem_bytes);
+    else copy_element(p.out, off, p.updates, e, p.elem_bytes);
   }
 }
 
@@ -569,6 +631,12 @@ cudaError_t launch_gather(const GatherParams& given, cudaStream_t stream) {
   }
   const long long limit = 1LL << 31;
   const bool narrow = p.out_elems < limit && source < limit && p.out_elems / p.inner * (p.nd ? p.k : 1) < limit;
+  if (p.copies && !p.nd && p.elem_bytes == 16) {
+    const long long quarter = (p.out_elems + 3) / 4;
+    if (narrow) gather_pieces_kernel<unsigned><<<blocks_for(quarter, 256), 256, 0, stream>>>(p, static_cast<unsigned>(quarter));
+    else gather_pieces_kernel<unsigned long long><<<blocks_for(quarter, 256), 256, 0, stream>>>(p, static_cast<unsigned long long>(quarter));
+    return cudaGetLastError();
+  }
   if (p.copies) {
     if (narrow) gather_kernel<unsigned><<<blocks_for(p.out_elems, 256), 256, 0, stream>>>(p);
     else gather_kernel<unsigned long long><<<blocks_for(p.out_elems, 256), 256, 0, stream>>>(p);
@@ -591,6 +659,17 @@ cudaError_t launch_gather(const GatherParams& given, cudaStream_t stream) {
 
 cudaError_t launch_scatter(const ScatterParams& p, cudaStream_t stream) {
   if (p.upd_elems <= 0) return cudaSuccess;
+  bool rows = p.mode != 3 && p.axis == 0 && p.idx_rank == 1 && p.upd_rank == p.rank;
+  long long inner = 1;
+  for (int d = 1; d < p.rank && rows; ++d) {
+    rows = p.upd_sizes[d] == p.sizes[d];
+    inner *= p.sizes[d];
+  }
+  if (rows) {
+    const long long quarter = (p.upd_elems + 3) / 4;
+    scatter_rows_kernel<<<blocks_for(quarter, 256), 256, 0, stream>>>(p, inner, quarter);
+    return cudaGetLastError();
+  }
   scatter_kernel<<<blocks_for(p.upd_elems, 256), 256, 0, stream>>>(p);
   return cudaGetLastError();
 }

@@ -382,3 +382,35 @@ def test_nms_centre_boxes_clipping_soft_suppression():
     np.testing.assert_array_equal(got_b, want_b)
     np.testing.assert_allclose(got_s, want_s, rtol=1e-5, atol=1e-6)
     assert int(got_v.reshape(-1)[0]) == want_v
+
+
+def test_gather_of_whole_rows_moves_16_byte_pieces():
+    # rows of 64 f32 and of 24 int8 x 2 (48 bytes): the 16-byte path, four pieces per thread, counts that are not
+    # multiples of four, positions outside the table on both sides
+    g = rng(4900)
+    for dtype, tail, n_rows, n_idx in ((np.float32, (64,), 1000, 4099), (np.int8, (24, 2), 77, 1001), (np.float64, (3, 2), 50, 7)):
+        table = g.integers(-100, 100, (n_rows,) + tail).astype(dtype)
+        idx = g.integers(-3, n_rows + 3, n_idx).astype(np.int32)
+        d = K.special_desc(K.SPECIAL_GATHER, K_OF[np.dtype(dtype)], list(table.shape), K.I32, [n_idx], axis=0)
+        got, _ = run_special(d, [table, idx], (n_idx,) + tail, dtype)
+        np.testing.assert_array_equal(got, table[np.clip(idx, 0, n_rows - 1)])
+    # an outer dimension in front of the axis
+    table = g.standard_normal((5, 40, 8)).astype(np.float32)
+    idx = g.integers(0, 40, (6, 3)).astype(np.int64)
+    d = K.special_desc(K.SPECIAL_GATHER, K.F32, list(table.shape), K.I64, list(idx.shape), axis=1)
+    got, _ = run_special(d, [table, idx], (5, 6, 3, 8), np.float32)
+    np.testing.assert_array_equal(got, table[:, idx, :])
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_scatter_of_whole_rows(mode):
+    # data [rows][5][3], a list of row numbers, updates [n][5][3]: the four-updates-per-thread form
+    g = rng(4950 + mode)
+    for dtype in (np.float32, np.int16, np.float64):
+        data = g.integers(0, 5, (37, 5, 3)).astype(dtype)
+        n = 33 if mode else 201
+        idx = (g.permutation(39)[:n] - 1 if mode else g.integers(-1, 38, n)).astype(np.int32)    # storing modes: distinct rows
+        upd = g.integers(1, 4, (n, 5, 3)).astype(dtype)
+        d = K.special_desc(K.SPECIAL_SCATTER, K_OF[np.dtype(dtype)], list(data.shape), K.I32, [n], list(upd.shape), axis=0, mode=mode)
+        got, _ = run_special(d, [data, idx, upd], data.shape, dtype)
+        np.testing.assert_array_equal(got, S.scatter(data, idx, upd, 0, mode))
