@@ -320,3 +320,35 @@ def test_avgpool_excludes_padding():
     torch.cuda.synchronize()
     ref = oracle.pool2d_nhwc_f32(x, "sum", (3, 3), (1, 1), (1, 1), (7, 7), average=True)
     check_close(out.cpu().numpy(), ref, 1e-6)
+
+
+def test_eltwise_dense_f32_form_gives_the_bits_of_the_general_form():
+    # f32 in and out, operands dense or one value: eight elements per thread as two 16-byte pieces.  The same
+    # operation on a view that is not a multiple of four elements takes the general kernel; both call one
+    # arithmetic function, so the common part of their results must be equal bit for bit.
+    g = rng(31)
+    n = 4 * 1000 + 8
+    a = g.standard_normal(n).astype(np.float32)
+    b = g.uniform(0.5, 2.0, n).astype(np.float32)
+    one = np.array([1.5], dtype=np.float32)
+    for op_name, ins in (("add", [a, b]), ("div", [a, b]), ("max", [a, b]), ("relu", [a]), ("exp", [a]), ("tanh", [a]),
+                         ("mul", [a, one]), ("sub", [one, b]), ("sqrt", [b]), ("pow", [b, a])):
+        outs = []
+        for count in (n, n - 3):          # dense form; general form
+            arrays = [x if x.size == 1 else x[:count] for x in ins]
+            strides = [[0] if x.size == 1 else [1] for x in arrays]
+            d = K.EltwiseDesc()
+            d.op = op_name.encode()
+            d.n_in, d.rank, d.out_dtype = len(arrays), 1, K.F32
+            d.sizes[0] = count
+            for k, x in enumerate(arrays):
+                d.in_dtype[k] = K.F32
+                d.in_strides[k][0] = strides[k][0]
+            plan = K.Plan("eltwise", d)
+            devs = [dev(x) for x in arrays]
+            out = empty((count,), K.F32)
+            plan.eltwise([ptr(t) for t in devs], ptr(out))
+            torch.cuda.synchronize()
+            outs.append(out.cpu().numpy())
+        np.testing.assert_array_equal(outs[0][:n - 3].view(np.uint32), outs[1].view(np.uint32), err_msg=op_name)
+    np.testing.assert_array_equal(outs[0][:4], np.power(b[:4].astype(np.float64), a[:4].astype(np.float64)).astype(np.float32))
