@@ -287,18 +287,7 @@ __device__ __forceinline__ T ew_apply(int op, T a, T b, T c, bool a_nz) {
 // comparisons, from the result type otherwise); `arith_dtype` is the element type results
 // are rounded / wrapped to before the final conversion to the output type.
 template <class T>
-__global__ void __launch_bounds__(256) eltwise_kernel(const __grid_constant__ EltwiseParams p) {
-  const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (e >= p.elems) return;
-  long long rem = e;
-  long long off[3] = {0, 0, 0};
-  for (int d = p.rank - 1; d >= 0; --d) {
-    const long long c = rem % p.sizes[d];
-    rem /= p.sizes[d];
-    off[0] += c * p.in_strides[0][d];
-    off[1] += c * p.in_strides[1][d];
-    off[2] += c * p.in_strides[2][d];
-  }
+__device__ __forceinline__ void eltwise_one(const EltwiseParams& p, long long e, const long long (&off)[3]) {
   T a = T(0), b = T(0), c = T(0);
   bool a_nz = false;
   if (p.op == kEwSelect) {
@@ -319,6 +308,38 @@ __global__ void __launch_bounds__(256) eltwise_kernel(const __grid_constant__ El
   T r = ew_apply<T>(p.op, a, b, c, a_nz);
   if (p.narrow_result) r = narrow<T>(r, p.arith_dtype);
   store_as<T>(p.out, p.out_dtype, e, r);
+}
+
+template <class T>
+__global__ void __launch_bounds__(256) eltwise_kernel(const __grid_constant__ EltwiseParams p) {
+  const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= p.elems) return;
+  long long rem = e;
+  long long off[3] = {0, 0, 0};
+  for (int d = p.rank - 1; d >= 0; --d) {
+    const long long c = rem % p.sizes[d];
+    rem /= p.sizes[d];
+    off[0] += c * p.in_strides[0][d];
+    off[1] += c * p.in_strides[1][d];
+    off[2] += c * p.in_strides[2][d];
+  }
+  eltwise_one<T>(p, e, off);
+}
+
+// Every operand as dense as the result or one value for all of it, any element types: no index arithmetic, four
+// elements per thread a grid apart (`one_value` has bit k set if operand k is a single value).
+template <class T>
+__global__ void __launch_bounds__(256) eltwise_dense_kernel(const __grid_constant__ EltwiseParams p, int one_value,
+                                                            long long threads) {
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= threads) return;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const long long e = t + u * threads;
+    if (e >= p.elems) return;
+    const long long off[3] = {(one_value & 1) ? 0 : e, (one_value & 2) ? 0 : e, (one_value & 4) ? 0 : e};
+    eltwise_one<T>(p, e, off);
+  }
 }
 
 // The common case of the kernel above -- f32 in and out, every operand either as dense as the result or one value
@@ -448,6 +469,39 @@ cudaError_t launch_eltwise(const EltwiseParams& p, cudaStream_t stream) {
     const long long threads = (dense.quads + 1) / 2;
     eltwise_f32_dense_kernel<<<grid_for(threads), 256, 0, stream>>>(dense, threads);
     return cudaGetLastError();
+  }
+  // every operand dense like the result or a single value?
+  {
+    long long dense_stride[PMLB_MAX_RANK];
+    long long stride = 1;
+    for (int dd = p.rank - 1; dd >= 0; --dd) {
+      dense_stride[dd] = stride;
+      stride *= p.sizes[dd];
+    }
+    int one_value = 0;
+    bool all = true;
+    for (int k = 0; k < p.n_in && all; ++k) {
+      bool as_result = true, single = true;
+      for (int dd = 0; dd < p.rank; ++dd) {
+        if (p.sizes[dd] == 1) continue;
+        if (p.in_strides[k][dd] != dense_stride[dd]) as_result = false;
+        if (p.in_strides[k][dd] != 0) single = false;
+      }
+      if (!as_result && !single) all = false;
+      if (!as_result && single) one_value |= 1 << k;
+    }
+    if (all) {
+      const long long threads = (p.elems + 3) / 4;
+      const unsigned g4 = grid_for(threads);
+      switch (p.compute_class) {
+        case kClassF32: eltwise_dense_kernel<float><<<g4, 256, 0, stream>>>(p, one_value, threads); break;
+        case kClassF64: eltwise_dense_kernel<double><<<g4, 256, 0, stream>>>(p, one_value, threads); break;
+        case kClassI64: eltwise_dense_kernel<long long><<<g4, 256, 0, stream>>>(p, one_value, threads); break;
+        case kClassU64: eltwise_dense_kernel<unsigned long long><<<g4, 256, 0, stream>>>(p, one_value, threads); break;
+        default: return cudaErrorInvalidValue;
+      }
+      return cudaGetLastError();
+    }
   }
   const unsigned grid = grid_for(p.elems);
   switch (p.compute_class) {
