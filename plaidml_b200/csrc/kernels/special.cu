@@ -1,16 +1,21 @@
 // The four tile operations that are not contractions: gather, scatter, argsort, prng.  All of them move bytes and
-// indices; one thread per result element (gather), per update (scatter), per element and merge pass (argsort), per
-// run of elements (prng).
+// indices and wait on memory, so the kernels keep several independent loads per thread in flight and do their position
+// arithmetic in 32 bits where the extents allow.
 //
-// gather    integer indices copy elements; float indices interpolate in the tensor's float type with a rounding
-//           after every operation, so an f16 / bf16 / f32 / f64 result is what scalar code in that type gives.
-// scatter   the result starts as a copy of the data (a device copy issued by the caller side of this file), then
-//           every update adds (atomically) or stores.
-// argsort   a stable merge sort of positions: pass w merges runs of w positions into runs of 2w, every element
-//           finding its place by a binary search in the sibling run (elements of the left run go before equal
-//           elements of the right run).  ceil(log2 n) passes between two int32 buffers.
+// gather    integer positions copy elements -- whole runs of the inner dims as 16-byte pieces, four pieces per thread;
+//           float positions interpolate in the tensor's float type with a rounding after every operation, so an
+//           f16 / bf16 / f32 / f64 result is what scalar code in that type gives (four results per thread: positions,
+//           then all neighbour loads, then the blends).
+// scatter   the result starts as a copy of the data (a device copy issued by the launcher side), then every update adds
+//           (atomically) or stores; whole rows named by a list of indices go four updates per thread.
+// argsort   runs of up to 4096 positions are sorted in shared memory by one block (a bitonic network over (key,
+//           position) pairs: a total order, so ties keep their original order; keys of at most 32 bits share a 64-bit
+//           word with the position).  Longer lines go on with stable merge passes between two int32 buffers: pass w
+//           merges runs of w positions into runs of 2w, every element finding its place by a binary search in the
+//           sibling run (elements of the left run go before equal elements of the right run).
 // prng      three linear shift-register generators; a thread jumps its generators to its first element by applying
-//           precomputed powers of the step matrices over GF(2), then steps through its run.
+//           precomputed powers of the step matrices over GF(2), then steps through its run, eight numbers per pair of
+//           16-byte stores.
 #include "special.h"
 
 #include <math.h>
