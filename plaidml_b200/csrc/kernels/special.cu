@@ -383,6 +383,8 @@ __global__ void __launch_bounds__(256) scatter_kernel(const __grid_constant__ Sc
 
 // ------------------------------------------------------------------ argsort
 
+// One merge pass over lines longer than a block sorts: `src` holds positions in sorted runs of `w`, `dst` receives
+// them in sorted runs of 2 w.
 template <class V>
 __global__ void __launch_bounds__(256) argsort_pass_kernel(const __grid_constant__ ArgsortParams p,
                                                            const int32_t* __restrict__ src, int32_t* __restrict__ dst,
@@ -392,13 +394,9 @@ __global__ void __launch_bounds__(256) argsort_pass_kernel(const __grid_constant
   const long long in = e % p.inner;
   const long long j = (e / p.inner) % p.n;
   const long long line = (e / (p.inner * p.n)) * p.n * p.inner + in;  // element q of the line is at line + q * inner
-  auto pos_at = [&](long long q) -> long long { return src ? src[line + q * p.inner] : q; };
+  auto pos_at = [&](long long q) -> long long { return src[line + q * p.inner]; };
   auto key_at = [&](long long q) -> V { return load_as<V>(p.tensor, p.dtype, line + pos_at(q) * p.inner); };
   auto before = [&](V a, V b) -> bool { return p.descending ? a > b : a < b; };
-  if (w <= 0) {  // no merging to do: positions in order
-    dst[line + j * p.inner] = static_cast<int32_t>(j);
-    return;
-  }
   const long long base = (j / (2 * w)) * 2 * w;
   const long long mid = base + w < p.n ? base + w : p.n;
   const long long end = base + 2 * w < p.n ? base + 2 * w : p.n;
