@@ -352,3 +352,37 @@ def test_eltwise_dense_f32_form_gives_the_bits_of_the_general_form():
             outs.append(out.cpu().numpy())
         np.testing.assert_array_equal(outs[0][:n - 3].view(np.uint32), outs[1].view(np.uint32), err_msg=op_name)
     np.testing.assert_array_equal(outs[0][:4], np.power(b[:4].astype(np.float64), a[:4].astype(np.float64)).astype(np.float32))
+
+
+def test_dense_casts_between_f32_and_16_bit_floats_match_the_general_kernel():
+    g = rng(32)
+    n = 8 * 513
+    x = (g.standard_normal(n) * 100).astype(np.float32)
+    x[:6] = [np.inf, -np.inf, 0.0, -0.0, 65504.0, 1e-8]
+    for narrow_dt, torch_dt in ((K.F16, torch.float16), (K.BF16, torch.bfloat16)):
+        results = []
+        for count in (n, n - 5):            # eight at a time; general kernel
+            d = K.EltwiseDesc()
+            d.op = b"cast"
+            d.n_in, d.rank, d.out_dtype = 1, 1, narrow_dt
+            d.sizes[0] = count
+            d.in_dtype[0] = K.F32
+            d.in_strides[0][0] = 1
+            down = K.Plan("eltwise", d)
+            src = dev(x[:count])
+            half = torch.empty(count, dtype=torch_dt, device="cuda")
+            down.eltwise([ptr(src)], ptr(half))
+            u = K.EltwiseDesc()
+            u.op = b"cast"
+            u.n_in, u.rank, u.out_dtype = 1, 1, K.F32
+            u.sizes[0] = count
+            u.in_dtype[0] = narrow_dt
+            u.in_strides[0][0] = 1
+            up = K.Plan("eltwise", u)
+            back = torch.empty(count, dtype=torch.float32, device="cuda")
+            up.eltwise([ptr(half)], ptr(back))
+            torch.cuda.synchronize()
+            results.append((half.view(torch.int16).cpu().numpy(), back.cpu().numpy()))
+            np.testing.assert_array_equal(back.cpu().numpy().view(np.uint32), src.to(torch_dt).to(torch.float32).cpu().numpy().view(np.uint32))
+        np.testing.assert_array_equal(results[0][0][:n - 5], results[1][0])
+        np.testing.assert_array_equal(results[0][1][:n - 5].view(np.uint32), results[1][1].view(np.uint32))
