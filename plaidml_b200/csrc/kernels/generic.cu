@@ -386,6 +386,51 @@ __global__ void __launch_bounds__(256) eltwise_f32_dense_kernel(const DenseF32 p
   }
 }
 
+// The dense form for f16 / bf16 in and out: eight elements per 16-byte piece, the operation evaluated in f32 and
+// rounded to the 16-bit type as the general kernel does (operands of that type need no rounding).
+template <class S>
+struct Dense16 {
+  const S* in[3];
+  int scalar[3];
+  S* out;
+  long long octets;
+  int op, n_in, dtype;
+};
+
+__device__ __forceinline__ float widen(__half v) { return __half2float(v); }
+__device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <class S> __device__ __forceinline__ S shorten(float v);
+template <> __device__ __forceinline__ __half shorten<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 shorten<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <class S>
+__global__ void __launch_bounds__(256) eltwise_16bit_dense_kernel(const Dense16<S> p) {
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= p.octets) return;
+  struct alignas(16) Vec { S v[8]; };
+  Vec a[3];
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    if (k >= p.n_in) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a[k].v[i] = shorten<S>(0.f);
+    } else if (p.scalar[k]) {
+      const S s = p.in[k][0];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a[k].v[i] = s;
+    } else {
+      a[k] = reinterpret_cast<const Vec*>(p.in[k])[t];
+    }
+  }
+  Vec r;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float x = ew_apply<float>(p.op, widen(a[0].v[i]), widen(a[1].v[i]), widen(a[2].v[i]), false);
+    r.v[i] = shorten<S>(narrow<float>(x, p.dtype));
+  }
+  reinterpret_cast<Vec*>(p.out)[t] = r;
+}
+
 // Dense casts between f32 and the two 16-bit float types (round to nearest even, as the general kernel's store does):
 // eight elements per thread, 16- and 32-byte accesses.
 template <class In, class Out>
@@ -514,9 +559,47 @@ bool launch_dense_convert(const EltwiseParams& p, cudaStream_t stream) {
 }
 }  // namespace
 
+namespace {
+template <class S>
+bool launch_dense_16bit(const EltwiseParams& p, int dtype, cudaStream_t stream) {
+  if (p.compute_class != kClassF32 || p.out_dtype != dtype || p.arith_dtype != dtype || p.op == kEwSelect) return false;
+  if (p.elems % 8 != 0 || reinterpret_cast<uintptr_t>(p.out) % 16 != 0) return false;
+  long long dense[PMLB_MAX_RANK];
+  long long stride = 1;
+  for (int dd = p.rank - 1; dd >= 0; --dd) {
+    dense[dd] = stride;
+    stride *= p.sizes[dd];
+  }
+  Dense16<S> d{};
+  for (int k = 0; k < p.n_in; ++k) {
+    if (p.in_dtype[k] != dtype) return false;
+    bool as_result = true, one_value = true;
+    for (int dd = 0; dd < p.rank; ++dd) {
+      if (p.sizes[dd] == 1) continue;
+      if (p.in_strides[k][dd] != dense[dd]) as_result = false;
+      if (p.in_strides[k][dd] != 0) one_value = false;
+    }
+    if (!as_result && !one_value) return false;
+    if (as_result && reinterpret_cast<uintptr_t>(p.in[k]) % 16 != 0) return false;
+    d.in[k] = static_cast<const S*>(p.in[k]);
+    d.scalar[k] = as_result ? 0 : 1;
+  }
+  d.out = static_cast<S*>(p.out);
+  d.octets = p.elems / 8;
+  d.op = p.op;
+  d.n_in = p.n_in;
+  d.dtype = dtype;
+  eltwise_16bit_dense_kernel<S><<<grid_for(d.octets), 256, 0, stream>>>(d);
+  return true;
+}
+}  // namespace
+
 cudaError_t launch_eltwise(const EltwiseParams& p, cudaStream_t stream) {
   if (p.elems <= 0) return cudaSuccess;
   if (launch_dense_convert(p, stream)) return cudaGetLastError();
+  if (launch_dense_16bit<__half>(p, PMLB_F16, stream) || launch_dense_16bit<__nv_bfloat16>(p, PMLB_BF16, stream)) {
+    return cudaGetLastError();
+  }
   DenseF32 dense{};
   if (dense_f32_form(p, &dense)) {
     const long long threads = (dense.quads + 1) / 2;

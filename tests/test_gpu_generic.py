@@ -386,3 +386,42 @@ def test_dense_casts_between_f32_and_16_bit_floats_match_the_general_kernel():
             np.testing.assert_array_equal(back.cpu().numpy().view(np.uint32), src.to(torch_dt).to(torch.float32).cpu().numpy().view(np.uint32))
         np.testing.assert_array_equal(results[0][0][:n - 5], results[1][0])
         np.testing.assert_array_equal(results[0][1][:n - 5].view(np.uint32), results[1][1].view(np.uint32))
+
+
+@pytest.mark.parametrize("dt,torch_dt", [(K.F16, torch.float16), (K.BF16, torch.bfloat16)])
+def test_eltwise_dense_16_bit_form_gives_the_bits_of_the_general_form(dt, torch_dt):
+    g = rng(33)
+    n = 8 * 700 + 16
+    a = torch.from_numpy(g.standard_normal(n).astype(np.float32)).cuda().to(torch_dt)
+    b = torch.from_numpy(g.uniform(0.5, 2.0, n).astype(np.float32)).cuda().to(torch_dt)
+    one = torch.tensor([1.5], device="cuda").to(torch_dt)
+    for op_name, ins in (("add", [a, b]), ("mul", [a, b]), ("div", [a, b]), ("relu", [a]), ("exp", [a]), ("sub", [one, b]),
+                         ("max", [a, one]), ("sqrt", [b])):
+        outs = []
+        for count in (n, n - 3):          # dense form; general form
+            arrays = [x if x.numel() == 1 else x[:count].contiguous() for x in ins]
+            d = K.EltwiseDesc()
+            d.op = op_name.encode()
+            d.n_in, d.rank, d.out_dtype = len(arrays), 1, dt
+            d.sizes[0] = count
+            for k, x in enumerate(arrays):
+                d.in_dtype[k] = dt
+                d.in_strides[k][0] = 0 if x.numel() == 1 else 1
+            plan = K.Plan("eltwise", d)
+            out = torch.empty(count, dtype=torch_dt, device="cuda")
+            plan.eltwise([ptr(t) for t in arrays], ptr(out))
+            torch.cuda.synchronize()
+            outs.append(out.view(torch.int16).cpu().numpy())
+        np.testing.assert_array_equal(outs[0][:n - 3], outs[1], err_msg=op_name)
+    # and against torch for an operation whose rounding is unambiguous
+    d = K.EltwiseDesc()
+    d.op = b"add"
+    d.n_in, d.rank, d.out_dtype = 2, 1, dt
+    d.sizes[0] = n
+    for k in range(2):
+        d.in_dtype[k] = dt
+        d.in_strides[k][0] = 1
+    out = torch.empty(n, dtype=torch_dt, device="cuda")
+    K.Plan("eltwise", d).eltwise([ptr(a), ptr(b)], ptr(out))
+    torch.cuda.synchronize()
+    assert torch.equal(out, (a.float() + b.float()).to(torch_dt))
