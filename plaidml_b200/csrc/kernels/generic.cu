@@ -347,7 +347,9 @@ __global__ void __launch_bounds__(256) eltwise_dense_kernel(const __grid_constan
 // apart, all loads before the arithmetic.  The arithmetic is the same function, so the results are the same bits.
 struct DenseF32 {
   const float* in[3];
-  int scalar[3];   // operand k is one value
+  int scalar[3];   // operand k: 0 dense, 1 one value, 2 repeats every `period` quads (a bias along the trailing dims),
+                   // 3 one value per `period` quads (a column along the leading dims)
+  long long period[3];
   float* out;
   long long quads;  // elements / 4
   int op, n_in;
@@ -365,8 +367,13 @@ __global__ void __launch_bounds__(256) eltwise_f32_dense_kernel(const DenseF32 p
     for (int k = 0; k < 3; ++k) {
       if (k >= p.n_in) {
         v[u][k] = make_float4(0.f, 0.f, 0.f, 0.f);
-      } else if (p.scalar[k]) {
+      } else if (p.scalar[k] == 1) {
         const float s = p.in[k][0];
+        v[u][k] = make_float4(s, s, s, s);
+      } else if (p.scalar[k] == 2) {
+        v[u][k] = reinterpret_cast<const float4*>(p.in[k])[q % p.period[k]];
+      } else if (p.scalar[k] == 3) {
+        const float s = p.in[k][q / p.period[k]];
         v[u][k] = make_float4(s, s, s, s);
       } else {
         v[u][k] = reinterpret_cast<const float4*>(p.in[k])[q];
@@ -516,10 +523,49 @@ bool dense_f32_form(const EltwiseParams& p, DenseF32* d) {
       if (p.in_strides[k][dd] != dense[dd]) as_result = false;
       if (p.in_strides[k][dd] != 0) one_value = false;
     }
-    if (!as_result && !one_value) return false;
-    if (as_result && reinterpret_cast<uintptr_t>(p.in[k]) % 16 != 0) return false;
+    int mode = as_result ? 0 : (one_value ? 1 : -1);
+    long long period = 0;
+    if (mode < 0) {
+      // dense over the trailing dims and repeated over the leading ones (a bias), or one value per run of the
+      // trailing dims (a column)?
+      int split = -1;   // first dim of the trailing part
+      bool bias = true, column = true;
+      for (int dd = 0; dd < p.rank; ++dd) {
+        if (p.sizes[dd] == 1) continue;
+        if (p.in_strides[k][dd] != 0 && split < 0) split = dd;
+      }
+      // bias: stride 0 before `split`, dense strides from `split` on
+      for (int dd = 0; dd < p.rank && split >= 0; ++dd) {
+        if (p.sizes[dd] == 1) continue;
+        if (dd < split ? p.in_strides[k][dd] != 0 : p.in_strides[k][dd] != dense[dd]) bias = false;
+      }
+      if (split >= 0 && bias) {
+        period = dense[split] * p.sizes[split];          // elements of the trailing part
+        if (period % 4 == 0) mode = 2;
+      }
+      if (mode < 0) {
+        // column: non-zero strides on a leading part only, dense within that part; zero on the trailing part
+        int last = -1;
+        for (int dd = 0; dd < p.rank; ++dd) {
+          if (p.sizes[dd] != 1 && p.in_strides[k][dd] != 0) last = dd;
+        }
+        long long run = last >= 0 ? dense[last] : 0;     // elements of the trailing part behind `last`
+        for (int dd = 0; dd < p.rank && last >= 0; ++dd) {
+          if (p.sizes[dd] == 1) continue;
+          if (dd <= last ? p.in_strides[k][dd] * run != dense[dd] : p.in_strides[k][dd] != 0) column = false;
+        }
+        if (last >= 0 && column && run % 4 == 0) {
+          period = run;
+          mode = 3;
+        }
+      }
+      if (mode < 0) return false;
+      period /= 4;
+    }
+    if ((mode == 0 || mode == 2) && reinterpret_cast<uintptr_t>(p.in[k]) % 16 != 0) return false;
     d->in[k] = static_cast<const float*>(p.in[k]);
-    d->scalar[k] = as_result ? 0 : 1;
+    d->scalar[k] = mode;
+    d->period[k] = period;
   }
   d->out = static_cast<float*>(p.out);
   d->quads = p.elems / 4;

@@ -425,3 +425,21 @@ def test_eltwise_dense_16_bit_form_gives_the_bits_of_the_general_form(dt, torch_
     K.Plan("eltwise", d).eltwise([ptr(a), ptr(b)], ptr(out))
     torch.cuda.synchronize()
     assert torch.equal(out, (a.float() + b.float()).to(torch_dt))
+
+
+def test_eltwise_dense_f32_with_bias_and_column_operands():
+    # an operand repeated over the leading dims (a bias) or holding one value per run of the trailing dims (a column)
+    # stays on the 16-byte path; +, -, *, / are correctly rounded, so numpy's float32 results are the expected bits
+    from plaidml_b200.core import DType, Program
+    from plaidml_b200.edsl import Placeholder
+    from plaidml_b200.exec import Runner
+    g = rng(34)
+    cases = [((64, 256), (256,)), ((64, 256), (64, 1)), ((4, 8, 16), (8, 16)), ((4, 8, 16), (4, 8, 1)), ((4, 8, 16), (4, 1, 16)),
+             ((6, 20), (20,)), ((5, 8), (5, 1))]
+    for big, small in cases:
+        x = g.standard_normal(big).astype(np.float32)
+        y = g.uniform(0.5, 2.0, small).astype(np.float32)
+        X, Y = Placeholder(DType.FLOAT32, list(big)), Placeholder(DType.FLOAT32, list(small))
+        outs = Runner(Program("bcast", [X, Y], [X + Y, X * Y, Y - X, X / Y]), "cuda.0").run([x, y])
+        for got, want in zip(outs, (x + y, x * y, y - x, x / y)):
+            np.testing.assert_array_equal(got.view(np.uint32), want.astype(np.float32).view(np.uint32), err_msg=f"{big} {small}")
