@@ -80,3 +80,29 @@ def test_version_and_error_calls_work_without_a_gpu(library):
     assert library.pmlb_version()
     library.pmlb_device_count.restype = ctypes.c_int
     assert library.pmlb_device_count() >= 0
+
+
+def test_special_descriptor_layout_and_result_sizes_without_a_device():
+    # pmlb_special_out_elems is host arithmetic on the descriptor: it checks that the ctypes mirror of
+    # pmlb_special_desc has the layout of the C struct and that inconsistent descriptors are recognised
+    from plaidml_b200 import kernels as K
+    lib = K.load()
+    C = K.C
+
+    def count(d):
+        return lib.pmlb_special_out_elems(C.byref(d))
+
+    # gather along axis 1 of [3, 5, 7] with indices [2, 4]: 3 * (2 * 4) * 7
+    assert count(K.special_desc(K.SPECIAL_GATHER, K.F32, [3, 5, 7], K.I32, [2, 4], axis=1)) == 168
+    # nd with one batch dim: indices [3, 6, 2] address dims 1..2 of [3, 5, 7, 9]: 3 * 6 * 9
+    assert count(K.special_desc(K.SPECIAL_GATHER, K.F32, [3, 5, 7, 9], K.I32, [3, 6, 2], mode=1, batch_dims=1)) == 162
+    assert count(K.special_desc(K.SPECIAL_SCATTER, K.F32, [8, 4], K.I32, [3], [3, 4])) == 32
+    assert count(K.special_desc(K.SPECIAL_ARGSORT, K.I32, [6, 5], axis=1)) == 30
+    assert count(K.special_desc(K.SPECIAL_PRNG, sizes=[2, 3], state_elems=3)) == 6
+    # refused: axis outside the tensor, float indices without an interpolation, nd indices past the rank,
+    # 64-bit scatter indices, a state of two words
+    assert count(K.special_desc(K.SPECIAL_GATHER, K.F32, [3, 5], K.I32, [2], axis=2)) == 0
+    assert count(K.special_desc(K.SPECIAL_GATHER, K.F32, [3, 5], K.F32, [2], interpolation=3)) == 0
+    assert count(K.special_desc(K.SPECIAL_GATHER, K.F32, [3, 5], K.I32, [2, 3], mode=1)) == 0
+    assert count(K.special_desc(K.SPECIAL_SCATTER, K.F32, [8], K.I64, [3], [3])) == 0
+    assert count(K.special_desc(K.SPECIAL_PRNG, sizes=[4], state_elems=2)) == 0
