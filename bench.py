@@ -486,6 +486,68 @@ def extras(device: str, local_rank: int, peaks: dict) -> dict:
         "check": {"equals_rowmax_with_S_stored": bool(np.array_equal(r_only, r_out)), "ok": bool(np.array_equal(r_only, r_out))},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst, "traffic": None,
                      "peak_source": "bf16_tflops of MEASURED_PEAKS.json"}}
+    # the operations beside the path that are not contractions; a failure here must not take the line down
+    try:
+        out["gather_argsort_prng"] = special_extras(device, hbm, timed)
+    except Exception as exc:  # noqa: BLE001
+        out["gather_argsort_prng"] = {"error": str(exc)[:300]}
+    return out
+
+
+def special_extras(device: str, hbm: float, timed) -> dict:
+    """gather / argsort / prng on large inputs: device time per launch, algorithmic bytes, a check of sampled results."""
+    from plaidml_b200 import edsl
+    from plaidml_b200.core import DType, Program
+    from plaidml_b200.edsl import Placeholder
+    from plaidml_b200.exec import Runner
+    out = {}
+    g = np.random.Generator(np.random.PCG64(1234 + 7))
+    rows, width, picks = 1 << 20, 64, 1 << 21
+    T, I = Placeholder(DType.FLOAT32, [rows, width]), Placeholder(DType.INT32, [picks])
+    r = Runner(Program("gather_rows", [T, I], [edsl.gather(T, I)]), device)
+    table = g.standard_normal((rows, width), dtype=np.float32)
+    idx = g.integers(0, rows, picks, dtype=np.int32)
+    got = r.run([table, idx])[0]
+    sample = g.integers(0, picks, 2000)
+    ok = bool(np.array_equal(got[sample], table[idx[sample]]))
+    del got
+    sp = timed(r, 50)
+    alg = picks * 4 + 2 * picks * width * 4
+    gbs = alg / sp["mean_ms"] / 1e6
+    out["gather_2m_rows_of_64_f32"] = {**sp, "check": {"sampled_rows_equal": ok, "ok": ok},
+                                       "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
+                                                    "traffic": None, "algorithmic_bytes": alg,
+                                                    "peak_source": "hbm_gbs of MEASURED_PEAKS.json"}}
+    lines, n = 2048, 4096
+    X = Placeholder(DType.FLOAT32, [lines, n])
+    r = Runner(Program("argsort", [X], [edsl.argsort(X, 1)]), device)
+    x = g.standard_normal((lines, n), dtype=np.float32)
+    got = r.run([x])[0]
+    ok = bool(np.array_equal(got[:8], np.argsort(x[:8], axis=1, kind="stable").astype(np.int32)))
+    sp = timed(r, 50)
+    out["argsort_2048_lines_of_4096_f32"] = {**sp, "keys_per_s": lines * n / sp["mean_ms"] * 1e3,
+                                             "check": {"first_lines_equal_stable_sort": ok, "ok": ok}}
+    count = 1 << 26
+    S = Placeholder(DType.UINT32, [3])
+    numbers, state = edsl.prng(S, [count])
+    r = Runner(Program("prng", [S], [numbers, state]), device)
+    got, after = r.run([np.array([5, 6, 7], dtype=np.uint32)])
+    s = [5, 6, 7]
+    want = []
+    for _ in range(64):   # the sequential generator (pmlc/rt/prng.cc:26-39)
+        want.append(np.float32((s[0] ^ s[1] ^ s[2]) / 4294967296.0))
+        s = [(((s[0] & 4294967294) << 12) & 0xFFFFFFFF) ^ ((((s[0] << 13) & 0xFFFFFFFF) ^ s[0]) >> 19),
+             (((s[1] & 4294967288) << 4) & 0xFFFFFFFF) ^ ((((s[1] << 2) & 0xFFFFFFFF) ^ s[1]) >> 25),
+             (((s[2] & 4294967280) << 17) & 0xFFFFFFFF) ^ ((((s[2] << 3) & 0xFFFFFFFF) ^ s[2]) >> 11)]
+    ok = bool(np.array_equal(got[:64], np.array(want, dtype=np.float32)))
+    del got
+    sp = timed(r, 50)
+    gbs = count * 4 / sp["mean_ms"] / 1e6
+    out["prng_64m_numbers"] = {**sp, "check": {"first_64_equal_the_sequential_generator": ok, "ok": ok},
+                               "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
+                                            "traffic": None, "algorithmic_bytes": count * 4,
+                                            "peak_source": "hbm_gbs of MEASURED_PEAKS.json",
+                                            "note": "bound by the generators' integer operations, not by HBM"}}
     return out
 
 
