@@ -560,9 +560,17 @@ __host__ __device__ __forceinline__ uint32_t gf2_apply(const uint32_t* cols, uin
   return y;
 }
 
+// The same product from the matrix stored as eight 16-entry tables, one per 4-bit group of x.
+__host__ __device__ __forceinline__ uint32_t gf2_apply_groups(const uint32_t* groups, uint32_t x) {
+  uint32_t y = 0;
+#pragma unroll
+  for (int n = 0; n < 8; ++n) y ^= groups[n * 16 + ((x >> (4 * n)) & 15u)];
+  return y;
+}
+
 __device__ __forceinline__ uint32_t prng_jump(const uint32_t* table, int c, uint32_t s, unsigned long long steps) {
   for (int level = 0; level < kPrngLevels && steps != 0; ++level, steps >>= 1) {
-    if (steps & 1ull) s = gf2_apply(table + (c * kPrngLevels + level) * 32, s);
+    if (steps & 1ull) s = gf2_apply_groups(table + (c * kPrngLevels + level) * kPrngNibbleWords, s);
   }
   return s;
 }
@@ -731,9 +739,10 @@ cudaError_t launch_argsort(const ArgsortParams& p, int32_t* out, int32_t* scratc
 
 cudaError_t launch_prng(const uint32_t* state, long long state_elems, float* out, long long count, uint32_t* new_state,
                         const uint32_t* table, cudaStream_t stream) {
-  // longer runs per thread amortise the jump to the run's first element; short ones keep small results parallel
+  // longer runs per thread amortise the jump to the run's first element (it costs as much as ~200 numbers); short
+  // ones keep small results parallel
   int chunk = kPrngChunk;
-  while (chunk < 1024 && count / chunk > 2LL * 148 * 2048) chunk *= 2;
+  while (chunk < 512 && count / chunk > 256LL * 1024) chunk *= 2;   // (measured: ~256 K threads, runs of at most 512)
   long long threads = out ? (count + chunk - 1) / chunk : 1;
   if (threads < 1) threads = 1;
   prng_kernel<<<blocks_for(threads, 128), 128, 0, stream>>>(state, state_elems, out, count, new_state, table, threads,
@@ -743,12 +752,21 @@ cudaError_t launch_prng(const uint32_t* state, long long state_elems, float* out
 
 void prng_jump_table(uint32_t* table) {
   for (int c = 0; c < 3; ++c) {
-    uint32_t* level0 = table + c * kPrngLevels * 32;
-    for (int b = 0; b < 32; ++b) level0[b] = prng_step(c, 1u << b);
-    for (int level = 1; level < kPrngLevels; ++level) {
-      const uint32_t* prev = table + (c * kPrngLevels + level - 1) * 32;
-      uint32_t* cur = table + (c * kPrngLevels + level) * 32;
-      for (int b = 0; b < 32; ++b) cur[b] = gf2_apply(prev, prev[b]);
+    uint32_t cols[32], next[32];
+    for (int b = 0; b < 32; ++b) cols[b] = prng_step(c, 1u << b);      // columns of the one-step matrix
+    for (int level = 0; level < kPrngLevels; ++level) {
+      uint32_t* groups = table + (c * kPrngLevels + level) * kPrngNibbleWords;
+      for (int n = 0; n < 8; ++n) {
+        for (uint32_t v = 0; v < 16; ++v) {
+          uint32_t y = 0;
+          for (int b = 0; b < 4; ++b) {
+            if ((v >> b) & 1u) y ^= cols[4 * n + b];
+          }
+          groups[n * 16 + v] = y;
+        }
+      }
+      for (int b = 0; b < 32; ++b) next[b] = gf2_apply(cols, cols[b]);  // the matrix squared
+      for (int b = 0; b < 32; ++b) cols[b] = next[b];
     }
   }
 }

@@ -42,7 +42,9 @@ struct ArgsortParams {
   const void* tensor;
 };
 
-enum : int { kPrngChunk = 64, kPrngLevels = 32, kPrngTableWords = 3 * kPrngLevels * 32 };
+// The jump table holds, per generator word and power-of-two step count, the step matrix as eight 16-entry tables (one
+// per 4-bit group of the state word): applying it is eight look-ups and exclusive-ors.
+enum : int { kPrngChunk = 64, kPrngLevels = 32, kPrngNibbleWords = 8 * 16, kPrngTableWords = 3 * kPrngLevels * kPrngNibbleWords };
 
 cudaError_t launch_gather(const GatherParams& p, cudaStream_t stream);
 cudaError_t launch_scatter(const ScatterParams& p, cudaStream_t stream);
@@ -51,7 +53,7 @@ cudaError_t launch_argsort(const ArgsortParams& p, int32_t* out, int32_t* scratc
 // `table` is prng_jump_table() on the device.
 cudaError_t launch_prng(const uint32_t* state, long long state_elems, float* out, long long count, uint32_t* new_state,
                         const uint32_t* table, cudaStream_t stream);
-// Columns of the three step matrices raised to the powers 2^0 .. 2^31: table[c][level][bit].
+// The three step matrices raised to the powers 2^0 .. 2^31: table[c][level][4-bit group][value].
 void prng_jump_table(uint32_t* table);
 
 }  // namespace pmlb
