@@ -427,3 +427,37 @@ def test_nms_builds_and_refuses_the_ssd_decoding():
     with pytest.raises(Error):      # BoxesDecodeMode::SSD
         oplib.op("nms", [B, S, I, T, 4, 0.0, False, True, int(DType.INT32), 1, False, False, 0, 0, None, None, False, None, 2,
                          True, True])
+
+
+def test_gather_family_shape_rules():
+    # pmlc/ast/ast_ops.cc:54-72 (argsort), :101-186 (gather), :188-205 (prng), :226-264 (scatter)
+    from plaidml_b200 import edsl as E
+    from plaidml_b200 import op as oplib
+    X = Placeholder(DType.FLOAT16, [3, 5, 7])
+    I = Placeholder(DType.INT32, [2, 4])
+    assert E.gather(X, I, axis=1).compute_shape().sizes == [3, 2, 4, 7] and E.gather(X, I, axis=1).dtype == DType.FLOAT16
+    assert E.gather(X, I, axis=-1).compute_shape().sizes == [3, 5, 2, 4]
+    assert E.gather(X, 2, axis=0).compute_shape().sizes == [1, 5, 7]
+    nd = Placeholder(DType.INT32, [3, 6, 2])
+    assert oplib.gatherND(X, nd, batch_dims=1).compute_shape().sizes == [3, 6]
+    assert oplib.gatherND(X, Placeholder(DType.INT32, [9, 2])).compute_shape().sizes == [9, 7]
+    with pytest.raises(Error):
+        E.gather(X, Placeholder(DType.FLOAT32, [9, 2]), mode=E.GatherMode.ND)      # nd indices must be integers
+    with pytest.raises(Error):
+        oplib.gatherND(X, Placeholder(DType.INT32, [9, 4]))                          # addresses 4 dims of a rank-3 tensor
+    A = E.argsort(X, -2, E.SortDirection.DESC)
+    assert A.compute_shape().sizes == [3, 5, 7] and A.dtype == DType.INT32
+    assert oplib.sort(X, 1).compute_shape().sizes == [3, 5, 7] and oplib.sort(X, 1).dtype == DType.FLOAT16
+    vals, pos = oplib.topk(X, 2, axis=1)
+    assert vals.compute_shape().sizes == [3, 2, 7] and pos.compute_shape().sizes == [3, 2, 7] and pos.dtype == DType.INT32
+    D = Placeholder(DType.FLOAT32, [8, 4])
+    U = Placeholder(DType.FLOAT32, [3, 4])
+    S = E.scatter(D, Placeholder(DType.INT32, [3]), U)
+    assert S.compute_shape().sizes == [8, 4] and S.dtype == DType.FLOAT32
+    with pytest.raises(Error):
+        E.scatter(D, Placeholder(DType.INT64, [3]), U)                               # 32-bit indices only
+    numbers, state = E.prng(Placeholder(DType.UINT32, [1, 3]), [2, 3])
+    assert numbers.compute_shape().sizes == [2, 3] and numbers.dtype == DType.FLOAT32
+    assert state.compute_shape().sizes == [1, 3] and state.dtype == DType.UINT32
+    text = str(Program("family", [X, I], [E.gather(X, I, axis=1), A]))
+    assert "tile.gather" in text and "tile.argsort desc" in text and "[-2]" in text
