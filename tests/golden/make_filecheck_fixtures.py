@@ -16,7 +16,8 @@ WANTED = [
     "Convolution", "MnistCnn", "RepeatElements", "GlobalMin", "CumSum", "ComplexConv2d", "Reciprocal",
     "DefractLong", "Select", "ConvI8", "UniqueNames", "dup_out", "HigherPrecisionConstants", "LarsMomentum4d",
     "ReshapeFold", "ReshapeScalar", "ReshapeIntoScalar", "ReshapeFromScalar", "Shape", "Trace",
-    "Layer", "LayerOperandOrder", "LayerEmbeddedConst", "LayerUnusedOperand", "LayerMultipleReturnValues",
+    "Layer", "LayerOperandOrder", "LayerEmbeddedConst", "LayerUnusedOperand", "LayerMultipleReturnValues", "LayerMulti",
+    "LayerException",
     "Prng", "ArgSort1d", "ArgSort1dInt", "ArgSort1dDup", "ArgSort2dAxis0", "ArgSort2dAxis1", "ArgSort3dAxis0Asc",
     "ArgSort3dAxis2Desc", "ArgSort3dAxisNeg2Asc",
 ]

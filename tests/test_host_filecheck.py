@@ -282,6 +282,26 @@ def build_layer_unused_operand():
     return Program("LayerUnusedOperand", [A], [layer("sum", [A, B], lambda: A + _const_10x20("C"))])
 
 
+def build_layer_multi():
+    A = f32(10, 20)
+    B = layer("sum", [A], lambda: A + _const_10x20("C"))
+    O = layer("sum", [B], lambda: B + _const_10x20("C"))
+    return Program("LayerMulti", [A], [O])
+
+
+def build_layer_exception():
+    A = f32(10, 20)
+
+    def failing():
+        _const_10x20("C")
+        raise RuntimeError("exception")
+
+    with pytest.raises(RuntimeError):
+        layer("sum", [A], failing)
+    # the failed layer is closed: the next one is built at the function's level again
+    return Program("LayerException", [A], [layer("sum", [A], lambda: A + _const_10x20("C"))])
+
+
 def build_layer_multiple_return_values():
     A = f32(10, 5)
 
@@ -305,6 +325,7 @@ def build_argsort(dtype, dims, axis, direction=edsl.SortDirection.ASC):
 
 BUILDERS = {
     "LayerMultipleReturnValues": build_layer_multiple_return_values, "Prng": build_prng,
+    "LayerMulti": build_layer_multi, "LayerException": build_layer_exception,
     "ArgSort1d": lambda: build_argsort(DType.FLOAT32, [20], 0),
     "ArgSort1dInt": lambda: build_argsort(DType.INT32, [20], 0),
     "ArgSort1dDup": lambda: build_argsort(DType.FLOAT32, [20], 0),
