@@ -22,8 +22,11 @@ def build_only_patches():
         program.compile()
         return [np.zeros(shape.sizes, dtype=shape.dtype.into_numpy()) for shape in program.outputs]
 
+    def compile_only(self, program, device=''):
+        program.compile()
+
     plaidml.exec.run = run
-    plaidml.exec.Executable.__init__ = lambda self, program, device='': program.compile()
+    plaidml.exec.Executable.__init__ = compile_only
     plaidml.exec.Executable.run = lambda self, inputs, outputs: None
     unittest.TestCase.assertEqual = lambda self, first, second, msg=None: None
     unittest.TestCase.assertTrue = lambda self, expr, msg=None: None

@@ -8,6 +8,10 @@ tests/host/_build/pyref/ (byte code without sources, like the compiled C++ test 
 completed by the two modules the reference's build generates (tests/host/pyshim/plaidml/_ffi.py: the C declarations,
 taken from include/plaidml_ffi.h; core/_version.py) and pointed at this library through PLAIDML_LIB_PATH.
 
+The same edsl_test.py also runs on this repository's OWN Python package (`plaidml_b200.{core,edsl,exec,op}`) reached
+under the name `plaidml` through a few lines of aliasing (tests/host/pyshim_mirror/plaidml/__init__.py): the mirror of
+the reference's Python API is a drop-in for code written against it.
+
 The CPU half needs the checkout (``PLAIDML_REFERENCE_DIR``; skipped when unset): it assembles the package and runs the
 tests with --build-only (every program is built and compiled for the `cuda` target through the reference's Python API;
 nothing runs).  The GPU half runs whatever tests/host/_build/pyref/ holds on cuda.0 with the tests' own expected
@@ -97,6 +101,29 @@ def check(out: str, suffix: str) -> None:
     assert out.count("[ SKIP]") == 1 and out.count("[  OK ]") == EXPECTED_TESTS - len(NOT_THIS_LIBRARY) - 1
 
 
+def run_against_own_package(scratch: Path, *flags) -> str:
+    """The reference's edsl_test.py on this repository's own Python package, reached under the name `plaidml`."""
+    tree = scratch / "mirror"
+    tree.mkdir(parents=True, exist_ok=True)
+    shutil.copy(OUT / ("ref_edsl_test" + STORED), tree / "ref_edsl_test.pyc")
+    env = dict(os.environ)
+    env.update({
+        "PYTHONPATH": os.pathsep.join([str(SHIM.parent / "pyshim_mirror"), str(ROOT), str(tree)]),
+        "PLAIDML_DEVICE": "cuda.0",
+        "PLAIDML_TARGET": "cuda",
+    })
+    env.pop("PLAIDML_LIB_PATH", None)
+    res = subprocess.run([sys.executable, str(SHIM / "run_reference_tests.py"), *flags, "ref_edsl_test"], cwd=str(tree), env=env,
+                         capture_output=True, text=True, timeout=900)
+    assert res.returncode in (0, 1), (res.stdout[-2000:], res.stderr[-3000:])
+    return res.stdout + "\n--- stderr ---\n" + res.stderr
+
+
+def check_own_package(out: str, suffix: str) -> None:
+    failed = [ln for ln in out.splitlines() if ln.startswith("[ FAIL]")]
+    assert not failed and f"37 tests, 0 failures{suffix}" in out, (failed, out[-4000:])
+
+
 def test_reference_python_package_builds_its_programs(tmp_path):
     ref = os.environ.get("PLAIDML_REFERENCE_DIR")
     if not ref or not (Path(ref) / "plaidml/edsl/__init__.py").exists():
@@ -105,6 +132,8 @@ def test_reference_python_package_builds_its_programs(tmp_path):
         pytest.skip("needs a built libplaidml.so")
     assemble(Path(ref))
     check(run_tests(tmp_path, "--build-only"), " (build only)")
+    # ... and the same EDSL tests on this repository's own Python package under the reference's name
+    check_own_package(run_against_own_package(tmp_path, "--build-only"), " (build only)")
 
 
 @pytest.mark.gpu
@@ -114,3 +143,6 @@ def test_reference_python_tests_run_on_the_cuda_device(tmp_path):
     out = run_tests(tmp_path)
     assert "build only" not in out
     check(out, "")
+    out = run_against_own_package(tmp_path)
+    assert "build only" not in out
+    check_own_package(out, "")
